@@ -1,0 +1,151 @@
+/* yahkv: the paged, quantized KV-cache path of yet-another-halo-engine for NVIDIA B200 (sm_100a), as a C ABI.
+ *
+ * The reference engine has no FFI for this path: its "operator API" is a struct of buffer views plus kernel launches
+ * by name with an ordered binding list. Each entry point below names the reference interface it stands in for
+ * (paths relative to the reference project's root). One context serves one GPU and, like the reference engine
+ * (engine/model/generator.hpp:56), is not reentrant: callers serialise calls on a context. Every call returns 0 or a
+ * negative YAHKV_ERR_* code; nothing throws across this boundary and nothing is launched after a failed check
+ * (the reference validates before launching, engine/model/loom_decoder.hpp:186-209, :230-234).
+ *
+ * Geometry is the engine's: 24 query heads, 4 KV heads (GQA 6), head_dim 256 (engine/model/loom_decoder.hpp:55-57),
+ * score scale 1/16, optional sigmoid output gate. Pages hold 64 tokens. Cache formats are GGUF q8_0 / q4_0 blocks of
+ * 32 elements with fp16 scales (engine/core/gguf_quant.cpp:310-320, :72-75, :48-51).
+ *
+ * Pool layout (per layer, per side K|V; all layers of a side live in one allocation):
+ *   codes  [num_pages][4 kv heads][64 tokens][256 B (q8_0) | 128 B (q4_0)]
+ *   scales [num_pages][4 kv heads][64 tokens][8] fp16
+ * slot(pos) = table[pos / 64] * 64 + pos % 64 (the reference's rule with 256 -> 64,
+ * engine/gpu/loom/tools/gen_decode_attn.py:5, :64-72). One block table per sequence is shared by all layers
+ * (docs/architecture.md:212).
+ */
+#ifndef YAHKV_H_
+#define YAHKV_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define YAHKV_FMT_Q8_0 0
+#define YAHKV_FMT_Q4_0 1
+
+#define YAHKV_SIDE_K 0
+#define YAHKV_SIDE_V 1
+
+#define YAHKV_OUT_F16 0
+#define YAHKV_OUT_F32 1
+
+#define YAHKV_OK 0
+#define YAHKV_ERR_INVALID (-1)   /* bad argument, id, size or table entry */
+#define YAHKV_ERR_NO_PAGES (-2)  /* the page pool is exhausted */
+#define YAHKV_ERR_CUDA (-3)      /* a CUDA call failed; the message carries its text */
+#define YAHKV_ERR_NO_DEVICE (-4) /* a hot-path call on a host-only context, or no usable GPU */
+#define YAHKV_ERR_ORDER (-5)     /* positions appended out of order, or attend before any append */
+#define YAHKV_ERR_CAPACITY (-6)  /* more sequences, pages per sequence, tokens or splits than configured */
+
+typedef struct yahkv_ctx yahkv_ctx;
+
+typedef struct yahkv_config {
+  int32_t device;            /* CUDA ordinal; -1 = host-only context: allocator and tables work, hot calls fail */
+  int32_t n_layers;          /* full-attention layers sharing the block tables */
+  int32_t n_q_heads;         /* 24 */
+  int32_t n_kv_heads;        /* 4 */
+  int32_t head_dim;          /* 256 */
+  int32_t page_tokens;       /* 64 */
+  int32_t num_pages;         /* physical pages per layer */
+  int32_t fmt;               /* YAHKV_FMT_* */
+  int32_t max_seqs;          /* live sequences */
+  int32_t max_pages_per_seq; /* block table width */
+  int32_t max_splits;        /* split-K units per (sequence, kv head); 0 = 64 */
+  int32_t max_batch_tokens;  /* tokens per append call and query rows per prefill call; 0 = 8192 */
+  float softmax_scale;       /* 0 = 1/16 */
+} yahkv_config;
+
+/* Replaces LoomDecoder::OwnState / LoomPrefill's pool allocation (engine/model/loom_decoder.hpp:159-183,
+ * engine/model/loom_prefill.hpp:1306-1318): allocates the pools, the device block tables and the split-K workspace
+ * once, zero-filled. On failure *out is NULL and yahkv_last_error(NULL) holds the reason. */
+int yahkv_create(const yahkv_config* cfg, yahkv_ctx** out);
+void yahkv_destroy(yahkv_ctx* ctx);
+/* Message of the last failed call on ctx (ctx == NULL: of the last failed yahkv_create). Never NULL. */
+const char* yahkv_last_error(const yahkv_ctx* ctx);
+const char* yahkv_error_name(int code);
+
+/* ---- host page allocator and block tables ------------------------------------------------------------------
+ * The reference has one sequence and an identity table (engine/model/loom_decoder.hpp:175-179); its checkers
+ * scramble the table (engine/gpu/loom/tools/dattn_q_check.py:151). Here a LIFO free list hands out pages; the host
+ * copy of every table is the truth and changed rows reach the device as async copies ahead of the next hot call. */
+int yahkv_seq_create(yahkv_ctx* ctx, int32_t* seq);
+/* Returns the sequence's pages to the pool. Work already queued for it must have been ordered before (same stream). */
+int yahkv_seq_free(yahkv_ctx* ctx, int32_t seq);
+/* Grows the table so positions < n_tokens have a page. YAHKV_ERR_NO_PAGES leaves the sequence unchanged. */
+int yahkv_seq_reserve(yahkv_ctx* ctx, int32_t seq, int64_t n_tokens);
+/* Tests and imports: replace the table with caller-chosen pages (each in [0, num_pages), none owned by another
+ * sequence; the reference's check is engine/model/loom_prefill.hpp:1314-1316). Pages the sequence held are freed. */
+int yahkv_seq_set_table(yahkv_ctx* ctx, int32_t seq, const int32_t* pages, int32_t n);
+int yahkv_seq_table(const yahkv_ctx* ctx, int32_t seq, const int32_t** pages, int32_t* n);
+/* Appended length of a sequence in one layer (= highest appended position + 1). */
+int yahkv_seq_len(const yahkv_ctx* ctx, int32_t seq, int32_t layer, int64_t* len);
+/* Declare the length (after yahkv_append_slots, or to roll a sequence back to a prefix). layer -1 = all layers. */
+int yahkv_seq_set_len(yahkv_ctx* ctx, int32_t seq, int32_t layer, int64_t len);
+int yahkv_pages_free(const yahkv_ctx* ctx, int32_t* n);
+
+/* ---- hot path (asynchronous on `stream`, a cudaStream_t; NULL = the context's own stream) -------------------- */
+
+/* Replaces dattn_kvappend / dattn_kappend_q + dattn_vappend_q (engine/model/loom_decoder.hpp:254-264) and the chunk
+ * writers yah_kq8 / yah_vq8 (engine/model/loom_prefill.hpp:3346-3366): quantizes n_tokens fp16 K and V rows
+ * ([n_tokens][4][256], device) and scatters them through the block tables. seq_ids / positions are host arrays; each
+ * sequence's positions must continue its length in this layer (the q8_0 analogue of the reference's contiguity rule,
+ * engine/model/loom_decoder.hpp:233-234) and be covered by yahkv_seq_reserve. */
+int yahkv_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int32_t* seq_ids, const int64_t* positions,
+                 const void* k_dev, const void* v_dev, void* stream);
+/* The same with a device-resident slot mapping (slot = page * 64 + token in page; negative = skip the token).
+ * Lengths are not tracked by this call: declare them with yahkv_seq_set_len. */
+int yahkv_append_slots(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int64_t* slot_mapping_dev,
+                       const void* k_dev, const void* v_dev, void* stream);
+
+/* Replaces dattn_part(_q) + dattn_reduce (engine/model/loom_decoder.hpp:259-268): one query token per sequence over
+ * keys 0 .. len-1 of that sequence in `layer` (append first, then attend: engine/gpu/loom/tools/gen_decode_attn.py:7).
+ * q_dev [n_seqs][24][256] fp16; gate_dev [n_seqs][24][256] f32 or NULL (out *= sigmoid(gate), gen_decode_attn.py:402-407);
+ * out_dev [n_seqs][24][256] fp16 or f32 by out_dtype. n_splits: split-K units per (sequence, kv head), 0 = automatic. */
+int yahkv_attend_decode(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids, const void* q_dev,
+                        const float* gate_dev, void* out_dev, int32_t out_dtype, int32_t n_splits, void* stream);
+
+/* Replaces yah_attn_wmma (engine/model/loom_prefill.hpp:3393-3447): causal attention of one chunk per sequence over
+ * the cache, which already holds the chunk (append first). Sequence i contributes chunk_lens[i] query rows, packed in
+ * order: q_dev [sum chunk_lens][24][256] fp16; row j of sequence i sits at position len_i - chunk_lens[i] + j and sees
+ * keys <= that position (engine/gpu/loom/tools/gen_attn_fa.py:2897-2904). gate / out as above, same packing. */
+int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids,
+                         const int32_t* chunk_lens, const void* q_dev, const float* gate_dev, void* out_dev,
+                         int32_t out_dtype, void* stream);
+
+/* One decode step of one layer with HOST buffers (what an engine without device-resident activations calls):
+ * copies k/v/q (and gate) in, appends one token per sequence at its current length, attends, copies out back and
+ * waits for it. k_host, v_host [n_seqs][4][256] fp16; q_host [n_seqs][24][256] fp16; out_host by out_dtype. */
+int yahkv_decode_step_host(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids, const void* k_host,
+                           const void* v_host, const void* q_host, const float* gate_host, void* out_host,
+                           int32_t out_dtype);
+
+/* ---- inspection (parity tests, checkpoints); these block until the context's queued work is done ------------- */
+
+/* One page record of one layer and side: codes [4][64][256|128] bytes to codes_host, scales [4][64][8] fp16 to
+ * scales_host (either may be NULL). The reference's checkers read whole pools back the same way
+ * (engine/gpu/loom/tools/dattn_q_check.py:219-220). */
+int yahkv_read_page(yahkv_ctx* ctx, int32_t layer, int32_t side, int32_t page, void* codes_host, void* scales_host);
+int yahkv_write_page(yahkv_ctx* ctx, int32_t layer, int32_t side, int32_t page, const void* codes_host,
+                     const void* scales_host);
+/* The token at (seq, pos) as GGUF blocks, 4 heads x 8 blocks of [fp16 d][codes] (34 or 18 bytes each), the form
+ * QuantizeQ8_0 writes (engine/core/gguf_quant.cpp:310-320). k_blocks / v_blocks may be NULL. */
+int yahkv_export_token(yahkv_ctx* ctx, int32_t layer, int32_t seq, int64_t pos, void* k_blocks, void* v_blocks);
+int yahkv_sync(yahkv_ctx* ctx);
+
+/* Bytes of device memory the context holds, and kernels it has launched since creation (for benchmarks). */
+int yahkv_device_bytes(const yahkv_ctx* ctx, int64_t* bytes);
+int yahkv_launch_count(const yahkv_ctx* ctx, int64_t* launches);
+/* Device time of the last yahkv_attend_decode's kernels is not measured here: callers time with events on `stream`. */
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* YAHKV_H_ */

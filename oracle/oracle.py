@@ -1,0 +1,173 @@
+"""ctypes binding of the CPU oracle (oracle/yahkv_oracle.cpp) and of the reference's own codecs (oracle/_ref).
+
+TEST INFRASTRUCTURE ONLY. Importers: tests/, the smoke check and the CPU-baseline / reference arm of bench.py. The
+shipped library and its Python binding never import this module.
+
+`PagedPool` models one layer's K and V pools in host memory in the library's layout, so a test can run the same
+appends through the oracle and the GPU and compare the bytes.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(_HERE, "libyahkv_oracle.so")
+REF_SO = os.path.join(_HERE, "_ref", "libyah_ref_codec.so")
+
+Q_HEADS, KV_HEADS, HEAD_DIM, PAGE_TOKENS, BLOCKS = 24, 4, 256, 64, 8
+FMT_Q8_0, FMT_Q4_0 = 0, 1
+GGML_Q4_0, GGML_Q8_0 = 2, 8  # ggml type ids the reference's Dequantize takes
+
+
+def build():
+    """Compile the oracle, and the reference's codecs when its checkout is present (oracle/Makefile)."""
+    r = subprocess.run(["make", "-C", _HERE], capture_output=True, text=True)
+    if r.returncode:
+        raise RuntimeError("building the oracle failed:\n" + r.stdout[-2000:] + r.stderr[-2000:])
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
+
+
+if not os.path.exists(ORACLE_SO):
+    build()
+_o = ctypes.CDLL(ORACLE_SO)
+_o.yahkv_oracle_slot.restype = ctypes.c_int64
+_ref = ctypes.CDLL(REF_SO) if os.path.exists(REF_SO) else None
+THREADS = _o.yahkv_oracle_hardware_threads()
+
+
+def have_ref():
+    return _ref is not None
+
+
+def code_bytes(fmt):
+    return 256 if fmt == FMT_Q8_0 else 128
+
+
+def block_bytes(fmt):
+    return 34 if fmt == FMT_Q8_0 else 18
+
+
+def quantize(x, fmt):
+    """f32 array (size a multiple of 32) -> GGUF blocks as uint8."""
+    x = np.ascontiguousarray(x, np.float32).reshape(-1)
+    out = np.zeros(x.size // 32 * block_bytes(fmt), np.uint8)
+    fn = _o.yahkv_oracle_quantize_q8_0 if fmt == FMT_Q8_0 else _o.yahkv_oracle_quantize_q4_0
+    fn(_p(x), ctypes.c_uint64(x.size), _p(out))
+    return out
+
+
+def dequantize(blocks, fmt):
+    blocks = np.ascontiguousarray(blocks, np.uint8).reshape(-1)
+    n = blocks.size // block_bytes(fmt) * 32
+    y = np.zeros(n, np.float32)
+    fn = _o.yahkv_oracle_dequantize_q8_0 if fmt == FMT_Q8_0 else _o.yahkv_oracle_dequantize_q4_0
+    fn(_p(blocks), ctypes.c_uint64(n), _p(y))
+    return y
+
+
+def ref_quantize_q8_0(x):
+    """The reference's QuantizeQ8_0 itself (engine/core/gguf_quant.cpp:310-320), compiled from its sources."""
+    x = np.ascontiguousarray(x, np.float32).reshape(-1)
+    out = np.zeros(x.size // 32 * 34, np.uint8)
+    _ref.yah_ref_quantize_q8_0(_p(x), ctypes.c_uint64(x.size), _p(out))
+    return out
+
+
+def ref_dequantize(blocks, fmt):
+    """The reference's Dequantize itself (engine/core/gguf_quant.cpp:291-308)."""
+    blocks = np.ascontiguousarray(blocks, np.uint8).reshape(-1)
+    n = blocks.size // block_bytes(fmt) * 32
+    y = np.zeros(n, np.float32)
+    rc = _ref.yah_ref_dequantize(GGML_Q8_0 if fmt == FMT_Q8_0 else GGML_Q4_0, _p(blocks), _p(y), ctypes.c_uint64(n))
+    assert rc == 0
+    return y
+
+
+def validate_table(table, num_pages):
+    table = np.ascontiguousarray(table, np.int32)
+    return _o.yahkv_oracle_validate_table(_p(table), len(table), num_pages)
+
+
+def slot(table, pos, num_pages, page_tokens=PAGE_TOKENS):
+    table = np.ascontiguousarray(table, np.int32)
+    return _o.yahkv_oracle_slot(page_tokens, num_pages, _p(table), len(table), ctypes.c_int64(pos))
+
+
+class PagedPool:
+    """One layer's pools on the host: codes [P][4][64][cb] u8 and scales [P][4][64][8] u16, for K and for V."""
+
+    def __init__(self, fmt, num_pages):
+        self.fmt, self.num_pages = fmt, num_pages
+        cb = code_bytes(fmt)
+        self.kcodes = np.zeros((num_pages, KV_HEADS, PAGE_TOKENS, cb), np.uint8)
+        self.vcodes = np.zeros_like(self.kcodes)
+        self.kscales = np.zeros((num_pages, KV_HEADS, PAGE_TOKENS, BLOCKS), np.uint16)
+        self.vscales = np.zeros_like(self.kscales)
+
+    def append(self, table, pos0, k, v, threads=THREADS):
+        """k, v: [n][4][256] float16 at logical positions pos0 .. pos0 + n - 1 of a sequence with this table."""
+        table = np.ascontiguousarray(table, np.int32)
+        for x, codes, scales in ((k, self.kcodes, self.kscales), (v, self.vcodes, self.vscales)):
+            x = np.ascontiguousarray(x, np.float16)
+            n = x.shape[0]
+            _o.yahkv_oracle_append_seq(self.fmt, PAGE_TOKENS, self.num_pages, _p(codes), _p(scales), _p(table),
+                                       len(table), ctypes.c_int64(pos0), n, _p(x.view(np.uint16)), threads)
+
+    def append_slots(self, slots, k, v, threads=THREADS):
+        slots = np.ascontiguousarray(slots, np.int64)
+        for x, codes, scales in ((k, self.kcodes, self.kscales), (v, self.vcodes, self.vscales)):
+            x = np.ascontiguousarray(x, np.float16)
+            _o.yahkv_oracle_append_slots(self.fmt, PAGE_TOKENS, self.num_pages, _p(codes), _p(scales), _p(slots),
+                                         len(slots), _p(x.view(np.uint16)), threads)
+
+    def export_row(self, side, slot_):
+        codes, scales = (self.kcodes, self.kscales) if side == 0 else (self.vcodes, self.vscales)
+        out = np.zeros(KV_HEADS * BLOCKS * block_bytes(self.fmt), np.uint8)
+        _o.yahkv_oracle_export_row(self.fmt, PAGE_TOKENS, self.num_pages, _p(codes), _p(scales),
+                                   ctypes.c_int64(slot_), _p(out))
+        return out
+
+    def attend_decode_f64(self, table, n_keys, q, gate=None, scale=1.0 / 16.0, threads=THREADS):
+        """q [24][256] float16, gate [24][256] float32 or None -> out [24][256] float64."""
+        table = np.ascontiguousarray(table, np.int32)
+        q = np.ascontiguousarray(q, np.float16)
+        gate = None if gate is None else np.ascontiguousarray(gate, np.float32)
+        out = np.zeros((Q_HEADS, HEAD_DIM), np.float64)
+        _o.yahkv_oracle_attend_decode_f64(self.fmt, PAGE_TOKENS, self.num_pages, _p(self.kcodes), _p(self.kscales),
+                                          _p(self.vcodes), _p(self.vscales), _p(table), len(table),
+                                          ctypes.c_int64(n_keys), _p(q.view(np.uint16)), _p(gate),
+                                          ctypes.c_double(scale), _p(out), threads)
+        return out
+
+    def attend_decode_f32(self, tables, n_keys, q, gate=None, scale=1.0 / 16.0, threads=THREADS):
+        """Batched two-level f32 attention: tables [n][stride] int32, n_keys [n], q [n][24][256] float16."""
+        tables = np.ascontiguousarray(tables, np.int32)
+        n_keys = np.ascontiguousarray(n_keys, np.int32)
+        q = np.ascontiguousarray(q, np.float16)
+        gate = None if gate is None else np.ascontiguousarray(gate, np.float32)
+        out = np.zeros((len(n_keys), Q_HEADS, HEAD_DIM), np.float32)
+        _o.yahkv_oracle_attend_decode_f32(self.fmt, PAGE_TOKENS, self.num_pages, _p(self.kcodes), _p(self.kscales),
+                                          _p(self.vcodes), _p(self.vscales), _p(tables), tables.shape[1], _p(n_keys),
+                                          len(n_keys), _p(q.view(np.uint16)), _p(gate), ctypes.c_float(scale),
+                                          _p(out), threads)
+        return out
+
+    def attend_prefill_f64(self, table, start, q, q_begin=0, q_end=None, gate=None, scale=1.0 / 16.0,
+                           threads=THREADS):
+        """q [n_q][24][256] float16 for a chunk at positions start .. start + n_q - 1 (already appended)."""
+        table = np.ascontiguousarray(table, np.int32)
+        q = np.ascontiguousarray(q, np.float16)
+        n_q = q.shape[0]
+        q_end = n_q if q_end is None else q_end
+        gate = None if gate is None else np.ascontiguousarray(gate, np.float32)
+        out = np.zeros((q_end - q_begin, Q_HEADS, HEAD_DIM), np.float64)
+        _o.yahkv_oracle_attend_prefill_f64(self.fmt, PAGE_TOKENS, self.num_pages, _p(self.kcodes), _p(self.kscales),
+                                           _p(self.vcodes), _p(self.vscales), _p(table), len(table),
+                                           ctypes.c_int64(start), n_q, q_begin, q_end, _p(q.view(np.uint16)),
+                                           _p(gate), ctypes.c_double(scale), _p(out), threads)
+        return out

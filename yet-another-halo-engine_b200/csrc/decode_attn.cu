@@ -1,0 +1,469 @@
+// Paged split-K decode attention over the quantized cache, and its combine pass.
+//
+// Stands in for the reference's dattn_part / dattn_part_q (one workgroup per kv head and page, partial softmax and
+// P.V) and dattn_reduce (merge, divide, sigmoid gate): engine/gpu/loom/tools/gen_decode_attn.py:97-335, :576-1040,
+// :338-411. Numeric contract kept from there: keys 0 .. len-1 visible, invalid keys get weight 0, score = q.k * scale,
+// fp32 softmax statistics, partials (max, sum, unnormalised acc) merged in unit order, out = A / L * sigmoid(gate).
+//
+// Shape of the work. One CTA processes one split-K unit: a run of pages of one sequence for one kv head, all six query
+// heads of the GQA group at once, so every cache byte is read from HBM exactly once per call. A producer warp walks
+// the block table and gathers each page's K and V records with non-multicast TMA: two 2-D tiled copies per side
+// (64 token rows x 128 B, 128-byte swizzle, so the ldmatrix reads below are bank-conflict free) plus one bulk copy
+// per side for the 64 x 8 fp16 scales, all completing on one mbarrier per stage. Four consumer warps take 16 keys of
+// the page each.
+//
+// The path is HBM-bound (2176 B per token per layer in q8_0), but at GQA 6 it needs 5.6 multiply-adds per byte, more
+// than the fp32 pipes can give at HBM rate, so the dot products run on the warp-level f16 tensor-core MMA with
+// register operands (dequantization stays in registers): codes become exact f16 integers by a byte permute and a
+// magic-number subtract, the products accumulate in fp32 per 32-element block, and the block's fp16 scale multiplies
+// the block sum in fp32. For P.V the per-(key, block) V scale is folded into the weights, which are split into an
+// f16 high and low part (two MMAs) so the weights keep ~22 bits: a single f16 weight would cost up to 3e-3 absolute
+// error on outlier channels.
+//
+// MMA orientation. S^T[head][key] = Q[head][dim] . K[key][dim]: A = Q (rows 0-5 real heads, the rest zero), B = K^T
+// read with ldmatrix straight from the token-major page. O^T[dim][head] = V^T[dim][key] . P^T[key][head]: A = V^T read
+// with ldmatrix.trans from the same token-major layout, B = the weights, which the first MMA left in exactly the
+// register layout the second one wants. The dims inside a 16-wide MMA step are a fixed permutation of the page's
+// dims; Q is loaded with the same permutation, so the dot products are unchanged.
+#include <cuda_fp16.h>
+
+#include <cmath>
+
+#include "kernels.cuh"
+#include "ptx.cuh"
+
+namespace yahkv {
+namespace {
+
+constexpr int kConsumerWarps = 4;
+constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
+constexpr int kBoxBytes = 64 * 128;  // one swizzled TMA box: 64 token rows x 128 B
+
+template <int kFmt>
+struct StageLayout {
+  static constexpr int kBoxesPerSide = kFmt == kFmtQ8 ? 2 : 1;
+  static constexpr int kKOff = 0;
+  static constexpr int kVOff = kBoxesPerSide * kBoxBytes;
+  static constexpr int kKsOff = 2 * kBoxesPerSide * kBoxBytes;
+  static constexpr int kVsOff = kKsOff + kRecordScaleBytes;
+  static constexpr int kBytes = kVsOff + kRecordScaleBytes;  // 34816 (q8_0) or 18432 (q4_0), a multiple of 1024
+  static constexpr int kStages = kFmt == kFmtQ8 ? 3 : 5;
+};
+// Cross-warp merge scratch at the end of a unit: per consumer warp acc [6][kMergeStride] f32 and (m, l) [8][2].
+constexpr int kMergeStride = kHeadDim + 8;
+constexpr int kMergeBytes = kConsumerWarps * (kGroup * kMergeStride + 16) * 4;
+
+// fp16 number b (0..7) of eight packed in a uint4, widened to f32. b is a compile-time constant after unrolling.
+__device__ __forceinline__ float ScaleOf(const uint4& v, int b) {
+  const std::uint32_t w = (b >> 1) == 0 ? v.x : (b >> 1) == 1 ? v.y : (b >> 1) == 2 ? v.z : v.w;
+  return __half2float(__ushort_as_half(static_cast<unsigned short>((b & 1) ? (w >> 16) : (w & 0xFFFFU))));
+}
+
+// One S^T MMA step: the Q fragment of the step comes from shared memory at use (volatile, so the compiler does not
+// hoist all sixteen fragments into registers), rows 8-15 of A are zero.
+__device__ __forceinline__ void MmaQ(float (&d)[4], std::uint32_t q_addr, std::uint32_t b0, std::uint32_t b1) {
+  std::uint32_t a0, a2;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(a0), "=r"(a2) : "r"(q_addr));
+  MmaF16(d, a0, 0U, a2, 0U, b0, b1);
+}
+
+template <int kFmt>
+constexpr int DecodeSmemBytes() {
+  constexpr int ring = StageLayout<kFmt>::kStages * StageLayout<kFmt>::kBytes;
+  return (ring > kMergeBytes ? ring : kMergeBytes) + 1024;  // + slack to align the ring to 1024 B
+}
+
+// Running max may lag the true max by this much (log2 units) before the accumulators are rescaled; weights stay
+// <= 2^4, so weight x scale fits fp16 for every representable fp16 input.
+constexpr float kLazyRescale = 4.0F;
+
+template <int kFmt>
+__global__ void __launch_bounds__(kDecodeThreads, 2)
+    DecodePartKernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                     PoolView pool, int layer, const std::int32_t* __restrict__ tables, int table_stride,
+                     const DecodeUnit* __restrict__ units, const __half* __restrict__ q, float scale_log2,
+                     float* __restrict__ partial_acc, float* __restrict__ partial_ml, int* status) {
+  using L = StageLayout<kFmt>;
+  extern __shared__ std::uint8_t smem_raw[];
+  __shared__ __align__(8) std::uint64_t full_bar[L::kStages];
+  __shared__ __align__(8) std::uint64_t empty_bar[L::kStages];
+  __shared__ uint2 qfrag[16 * 32];
+  std::uint8_t* ring = reinterpret_cast<std::uint8_t*>((reinterpret_cast<std::uintptr_t>(smem_raw) + 1023) &
+                                                       ~static_cast<std::uintptr_t>(1023));
+
+  const DecodeUnit u = units[blockIdx.x];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_pages = u.page_end - u.page_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < L::kStages; ++s) {
+      MbarInit(&full_bar[s], 1);
+      MbarInit(&empty_bar[s], kConsumerWarps);
+    }
+    FenceBarrierInit();
+  }
+  __syncthreads();
+
+  if (warp == kConsumerWarps) {
+    // ---------------- producer: block-table walk + TMA gathers ----------------
+    if (lane == 0) {
+      PrefetchTensorMap(&kmap);
+      PrefetchTensorMap(&vmap);
+    }
+    const std::int32_t* row = tables + static_cast<std::size_t>(u.seq) * table_stride + u.page_begin;
+    bool ok = true;
+    for (int base = 0; base < n_pages && ok; base += 32) {
+      const int cnt = min(32, n_pages - base);
+      std::int32_t mine = lane < cnt ? __ldg(row + base + lane) : 0;
+      mine = min(max(mine, 0), pool.num_pages - 1);
+      for (int j = 0; j < cnt; ++j) {
+        const std::int32_t page = __shfl_sync(0xFFFFFFFFU, mine, j);
+        const int i = base + j, s = i % L::kStages;
+        if (lane == 0) {
+          if (i >= L::kStages) ok = MbarWait(&empty_bar[s], ((i / L::kStages) - 1) & 1);
+          if (ok) {
+            const std::size_t rec = (static_cast<std::size_t>(layer) * pool.num_pages + page) * kKvHeads + u.kvh;
+            const int y = static_cast<int>(rec * kPageTokens);
+            std::uint8_t* st = ring + s * L::kBytes;
+            MbarArriveExpectTx(&full_bar[s], L::kBytes);
+#pragma unroll
+            for (int b = 0; b < L::kBoxesPerSide; ++b) {
+              TmaLoad2D(st + L::kKOff + b * kBoxBytes, &kmap, b * 128, y, &full_bar[s]);
+              TmaLoad2D(st + L::kVOff + b * kBoxBytes, &vmap, b * 128, y, &full_bar[s]);
+            }
+            BulkLoad(st + L::kKsOff, pool.kscales + rec * (kPageTokens * kBlocksPerRow), kRecordScaleBytes,
+                     &full_bar[s]);
+            BulkLoad(st + L::kVsOff, pool.vscales + rec * (kPageTokens * kBlocksPerRow), kRecordScaleBytes,
+                     &full_bar[s]);
+          }
+        }
+        ok = __shfl_sync(0xFFFFFFFFU, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+      }
+    }
+    if (!ok && lane == 0) atomicExch(status, kStatusWaitTimeout);
+    // The copies this warp issued are all awaited by the consumers (or by their bounded waits) before the CTA ends:
+    // the final __syncthreads below keeps this warp resident until then.
+  }
+
+  // ---------------- consumers ----------------
+  const int g = lane >> 2, t = lane & 3;
+  float o_acc[16][4];
+  float m_run = -INFINITY, l_run = 0.0F;
+  bool alive = true;
+
+  if (warp < kConsumerWarps) {
+#pragma unroll
+    for (int c = 0; c < 16; ++c)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o_acc[c][i] = 0.0F;
+
+    // Q fragments, shared by the four warps through shared memory (keeping them in registers would spill): MMA step c
+    // (16 dims) uses dims 16c + 4t + {0, 2} in k-slots (2t, 2t+1) and + {1, 3} in (2t+8, 2t+9).
+    {
+      const __half* qrow = q + (static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + g) * kHeadDim;
+#pragma unroll
+      for (int cc = 0; cc < 16 / kConsumerWarps; ++cc) {
+        const int c = warp * (16 / kConsumerWarps) + cc;
+        uint2 v = make_uint2(0, 0);
+        if (g < kGroup) v = *reinterpret_cast<const uint2*>(qrow + 16 * c + 4 * t);
+        qfrag[c * 32 + lane] = make_uint2(__byte_perm(v.x, v.y, 0x5410),   // halves (0, 2)
+                                          __byte_perm(v.x, v.y, 0x7632));  // halves (1, 3)
+      }
+    }
+    NamedBarrierSync(1, kConsumerWarps * 32);
+    const std::uint32_t qa_addr = SmemAddr(qfrag + lane);
+
+    // ldmatrix row address pieces: lane supplies row (lane & 7) + 8 * ((lane >> 3) & 1) of the warp's 16 keys and
+    // 16-byte chunk (lane >> 4) of a chunk pair.
+    const int lm_key = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+    const int lm_half = lane >> 4;
+    // Keys whose scores this thread holds: kt * 8 + 2t + j of the warp's 16.
+    const int my_key0 = warp * 16 + 2 * t;
+
+    for (int i = 0; i < n_pages; ++i) {
+      const int s = i % L::kStages;
+      if (!MbarWait(&full_bar[s], (i / L::kStages) & 1)) {
+        alive = false;
+        break;
+      }
+      const std::uint8_t* st = ring + s * L::kBytes;
+      const std::uint32_t k_base = SmemAddr(st + L::kKOff), v_base = SmemAddr(st + L::kVOff);
+
+      // scales of this thread's four keys, all eight blocks
+      uint4 ks_raw[2][2], vs_raw[2][2];
+#pragma unroll
+      for (int kt = 0; kt < 2; ++kt)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int key = my_key0 + kt * 8 + j;
+          ks_raw[kt][j] = *reinterpret_cast<const uint4*>(st + L::kKsOff + key * 16);
+          vs_raw[kt][j] = *reinterpret_cast<const uint4*>(st + L::kVsOff + key * 16);
+        }
+
+      // ---- S^T = Q K^T ----
+      float sc[2][2] = {{0.0F, 0.0F}, {0.0F, 0.0F}};
+      if constexpr (kFmt == kFmtQ8) {
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+          const int c = 2 * b + lm_half;  // 16-byte chunk of the 256-byte row
+          const std::uint32_t addr =
+              k_base + (c >> 3) * kBoxBytes + lm_key * 128 + (((c & 7) ^ (lm_key & 7)) << 4);
+          std::uint32_t w[4];
+          LdMatrixX4(addr, w);
+          float a0[4] = {0, 0, 0, 0}, a1[4] = {0, 0, 0, 0};
+          std::uint32_t x0, x1;
+          Int8x4ToHalf2(w[0], x0, x1);
+          MmaQ(a0, qa_addr + (2 * b) * 256, x0, x1);
+          Int8x4ToHalf2(w[2], x0, x1);
+          MmaQ(a0, qa_addr + (2 * b + 1) * 256, x0, x1);
+          Int8x4ToHalf2(w[1], x0, x1);
+          MmaQ(a1, qa_addr + (2 * b) * 256, x0, x1);
+          Int8x4ToHalf2(w[3], x0, x1);
+          MmaQ(a1, qa_addr + (2 * b + 1) * 256, x0, x1);
+          sc[0][0] = fmaf(ScaleOf(ks_raw[0][0], b), a0[0], sc[0][0]);
+          sc[0][1] = fmaf(ScaleOf(ks_raw[0][1], b), a0[1], sc[0][1]);
+          sc[1][0] = fmaf(ScaleOf(ks_raw[1][0], b), a1[0], sc[1][0]);
+          sc[1][1] = fmaf(ScaleOf(ks_raw[1][1], b), a1[1], sc[1][1]);
+        }
+      } else {
+        // q4_0 rows are 128 B = 8 blocks of 16 packed bytes; one ldmatrix.x4 covers two blocks of 16 keys.
+#pragma unroll
+        for (int bp = 0; bp < 4; ++bp) {
+          const int c = 2 * bp + lm_half;  // block index = 16-byte chunk
+          const std::uint32_t addr = k_base + lm_key * 128 + ((c ^ (lm_key & 7)) << 4);
+          std::uint32_t w[4];
+          LdMatrixX4(addr, w);
+#pragma unroll
+          for (int hb = 0; hb < 2; ++hb) {
+            const int b = 2 * bp + hb;
+            float a0[4] = {0, 0, 0, 0}, a1[4] = {0, 0, 0, 0};
+            std::uint32_t l0, l1, h0, h1;
+            Nib4x4ToHalf2(w[2 * hb], l0, l1, h0, h1);
+            MmaQ(a0, qa_addr + (2 * b) * 256, l0, l1);
+            MmaQ(a0, qa_addr + (2 * b + 1) * 256, h0, h1);
+            Nib4x4ToHalf2(w[2 * hb + 1], l0, l1, h0, h1);
+            MmaQ(a1, qa_addr + (2 * b) * 256, l0, l1);
+            MmaQ(a1, qa_addr + (2 * b + 1) * 256, h0, h1);
+            sc[0][0] = fmaf(ScaleOf(ks_raw[0][0], b), a0[0], sc[0][0]);
+            sc[0][1] = fmaf(ScaleOf(ks_raw[0][1], b), a0[1], sc[0][1]);
+            sc[1][0] = fmaf(ScaleOf(ks_raw[1][0], b), a1[0], sc[1][0]);
+            sc[1][1] = fmaf(ScaleOf(ks_raw[1][1], b), a1[1], sc[1][1]);
+          }
+        }
+      }
+
+      // ---- softmax statistics (per head g, the 16 keys spread over the four lanes of a quad) ----
+      const int key_pos0 = (u.page_begin + i) * kPageTokens + my_key0;
+      float tmax = -INFINITY;
+#pragma unroll
+      for (int kt = 0; kt < 2; ++kt)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const bool valid = key_pos0 + kt * 8 + j < u.n_keys;
+          sc[kt][j] = valid ? sc[kt][j] * scale_log2 : -INFINITY;
+          tmax = fmaxf(tmax, sc[kt][j]);
+        }
+      tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFU, tmax, 1));
+      tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFU, tmax, 2));
+      if (__any_sync(0xFFFFFFFFU, tmax > m_run + kLazyRescale)) {
+        const float m_new = fmaxf(m_run, tmax);
+        const float alpha = m_new == -INFINITY ? 1.0F : exp2f(m_run - m_new);  // m_run = -inf gives 0
+        m_run = m_new;
+        l_run *= alpha;
+        const float al0 = __shfl_sync(0xFFFFFFFFU, alpha, (2 * t) * 4);
+        const float al1 = __shfl_sync(0xFFFFFFFFU, alpha, (2 * t + 1) * 4);
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          o_acc[c][0] *= al0, o_acc[c][2] *= al0;
+          o_acc[c][1] *= al1, o_acc[c][3] *= al1;
+        }
+      }
+      const float m_use = m_run == -INFINITY ? 0.0F : m_run;
+      float p[2][2];
+#pragma unroll
+      for (int kt = 0; kt < 2; ++kt)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          p[kt][j] = exp2f(sc[kt][j] - m_use);
+          l_run += p[kt][j];
+        }
+
+      // ---- O^T += V^T P^T ----
+      auto weights = [&](int b, std::uint32_t (&hi)[2], std::uint32_t (&lo)[2]) {
+#pragma unroll
+        for (int kt = 0; kt < 2; ++kt) {
+          const float w0 = p[kt][0] * ScaleOf(vs_raw[kt][0], b);
+          const float w1 = p[kt][1] * ScaleOf(vs_raw[kt][1], b);
+          const __half2 h = __floats2half2_rn(w0, w1);
+          const float2 hf = __half22float2(h);
+          const __half2 l = __floats2half2_rn(w0 - hf.x, w1 - hf.y);
+          hi[kt] = *reinterpret_cast<const std::uint32_t*>(&h);
+          lo[kt] = *reinterpret_cast<const std::uint32_t*>(&l);
+        }
+      };
+      if constexpr (kFmt == kFmtQ8) {
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+          std::uint32_t hi[2], lo[2];
+          weights(b, hi, lo);
+          const int c = 2 * b + lm_half;
+          const std::uint32_t addr =
+              v_base + (c >> 3) * kBoxBytes + lm_key * 128 + (((c & 7) ^ (lm_key & 7)) << 4);
+          std::uint32_t w[4];
+          LdMatrixX4Trans(addr, w);
+          std::uint32_t a0, a1, a2, a3;
+          Int8x4ToHalf2(w[0], a0, a1);
+          Int8x4ToHalf2(w[1], a2, a3);
+          MmaF16(o_acc[2 * b], a0, a1, a2, a3, hi[0], hi[1]);
+          MmaF16(o_acc[2 * b], a0, a1, a2, a3, lo[0], lo[1]);
+          Int8x4ToHalf2(w[2], a0, a1);
+          Int8x4ToHalf2(w[3], a2, a3);
+          MmaF16(o_acc[2 * b + 1], a0, a1, a2, a3, hi[0], hi[1]);
+          MmaF16(o_acc[2 * b + 1], a0, a1, a2, a3, lo[0], lo[1]);
+        }
+      } else {
+#pragma unroll
+        for (int bp = 0; bp < 4; ++bp) {
+          const int c = 2 * bp + lm_half;
+          const std::uint32_t addr = v_base + lm_key * 128 + ((c ^ (lm_key & 7)) << 4);
+          std::uint32_t w[4];
+          LdMatrixX4Trans(addr, w);
+#pragma unroll
+          for (int hb = 0; hb < 2; ++hb) {
+            const int b = 2 * bp + hb;
+            std::uint32_t hi[2], lo[2];
+            weights(b, hi, lo);
+            std::uint32_t la0, la1, ha0, ha1, la2, la3, ha2, ha3;
+            Nib4x4ToHalf2(w[2 * hb], la0, la1, ha0, ha1);      // keys 0-7 of the warp's 16
+            Nib4x4ToHalf2(w[2 * hb + 1], la2, la3, ha2, ha3);  // keys 8-15
+            MmaF16(o_acc[2 * b], la0, la1, la2, la3, hi[0], hi[1]);
+            MmaF16(o_acc[2 * b], la0, la1, la2, la3, lo[0], lo[1]);
+            MmaF16(o_acc[2 * b + 1], ha0, ha1, ha2, ha3, hi[0], hi[1]);
+            MmaF16(o_acc[2 * b + 1], ha0, ha1, ha2, ha3, lo[0], lo[1]);
+          }
+        }
+      }
+
+      __syncwarp();
+      if (lane == 0) MbarArrive(&empty_bar[s]);
+    }
+    if (!alive && lane == 0) atomicExch(status, kStatusWaitTimeout);
+    l_run += __shfl_xor_sync(0xFFFFFFFFU, l_run, 1);
+    l_run += __shfl_xor_sync(0xFFFFFFFFU, l_run, 2);
+  }
+
+  // Every stage has been consumed (or a wait gave up): the ring is free to hold the merge scratch.
+  __syncthreads();
+  float* merge = reinterpret_cast<float*>(ring);
+  if (warp < kConsumerWarps) {
+    float* mine = merge + warp * (kGroup * kMergeStride + 16);
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      // o_acc[c][0..3] = (dim 16c + 2g, head 2t), (dim 16c + 2g, head 2t+1), (dim 16c + 2g + 1, head 2t), (.., 2t+1)
+      if (2 * t < kGroup) {
+        *reinterpret_cast<float2*>(mine + (2 * t) * kMergeStride + 16 * c + 2 * g) =
+            make_float2(o_acc[c][0], o_acc[c][2]);
+        *reinterpret_cast<float2*>(mine + (2 * t + 1) * kMergeStride + 16 * c + 2 * g) =
+            make_float2(o_acc[c][1], o_acc[c][3]);
+      }
+    }
+    if (t == 0 && g < kGroup) {
+      mine[kGroup * kMergeStride + 2 * g] = m_run;
+      mine[kGroup * kMergeStride + 2 * g + 1] = l_run;
+    }
+  }
+  __syncthreads();
+  if (warp < kConsumerWarps) {
+    const int tid = threadIdx.x;  // 0..127: two dims per thread per head
+    float* acc_out = partial_acc + static_cast<std::size_t>(u.partial) * kPartialAccFloats;
+    float* ml_out = partial_ml + static_cast<std::size_t>(u.partial) * kPartialMlFloats;
+#pragma unroll
+    for (int h = 0; h < kGroup; ++h) {
+      float mw[kConsumerWarps], M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) {
+        mw[w] = merge[w * (kGroup * kMergeStride + 16) + kGroup * kMergeStride + 2 * h];
+        M = fmaxf(M, mw[w]);
+      }
+      float2 a = make_float2(0.0F, 0.0F);
+      float lsum = 0.0F;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) {
+        const float wgt = mw[w] == -INFINITY ? 0.0F : exp2f(mw[w] - M);
+        const float* src = merge + w * (kGroup * kMergeStride + 16);
+        const float2 v = *reinterpret_cast<const float2*>(src + h * kMergeStride + 2 * tid);
+        a.x = fmaf(wgt, v.x, a.x), a.y = fmaf(wgt, v.y, a.y);
+        lsum = fmaf(wgt, src[kGroup * kMergeStride + 2 * h + 1], lsum);
+      }
+      *reinterpret_cast<float2*>(acc_out + h * kHeadDim + 2 * tid) = a;
+      if (tid == 0) ml_out[2 * h] = M, ml_out[2 * h + 1] = lsum;
+    }
+  }
+}
+
+// Merge the units of one (batch row, query head): out = (sum w_i acc_i) / (sum w_i l_i) * sigmoid(gate), with
+// w_i = 2^(m_i - M), accumulated in unit order (engine/gpu/loom/tools/gen_decode_attn.py:373-408).
+__global__ void __launch_bounds__(kHeadDim / 2)
+    DecodeCombineKernel(const CombineItem* __restrict__ items, const float* __restrict__ partial_acc,
+                        const float* __restrict__ partial_ml, const float* __restrict__ gate, void* out, int out_f32) {
+  const int b = blockIdx.x / kQHeads, hh = blockIdx.x % kQHeads;
+  const int kvh = hh / kGroup, j = hh % kGroup;
+  const CombineItem it = items[b * kKvHeads + kvh];
+  float M = -INFINITY;
+  for (int i = 0; i < it.n_partials; ++i)
+    M = fmaxf(M, partial_ml[static_cast<std::size_t>(it.first_partial + i) * kPartialMlFloats + 2 * j]);
+  float2 A = make_float2(0.0F, 0.0F);
+  float Lsum = 0.0F;
+  const int d = 2 * threadIdx.x;
+  for (int i = 0; i < it.n_partials; ++i) {
+    const std::size_t pi = static_cast<std::size_t>(it.first_partial + i);
+    const float m = partial_ml[pi * kPartialMlFloats + 2 * j];
+    const float w = m == -INFINITY ? 0.0F : exp2f(m - M);
+    const float2 v = *reinterpret_cast<const float2*>(partial_acc + pi * kPartialAccFloats + j * kHeadDim + d);
+    A.x = fmaf(w, v.x, A.x), A.y = fmaf(w, v.y, A.y);
+    Lsum = fmaf(w, partial_ml[pi * kPartialMlFloats + 2 * j + 1], Lsum);
+  }
+  const float inv = 1.0F / Lsum;
+  float2 o = make_float2(A.x * inv, A.y * inv);
+  const std::size_t oi = (static_cast<std::size_t>(b) * kQHeads + hh) * kHeadDim + d;
+  if (gate != nullptr) {
+    const float2 gt = *reinterpret_cast<const float2*>(gate + oi);
+    o.x *= 1.0F / (1.0F + expf(-gt.x));
+    o.y *= 1.0F / (1.0F + expf(-gt.y));
+  }
+  if (out_f32)
+    *reinterpret_cast<float2*>(static_cast<float*>(out) + oi) = o;
+  else
+    *reinterpret_cast<__half2*>(static_cast<__half*>(out) + oi) = __floats2half2_rn(o.x, o.y);
+}
+
+}  // namespace
+
+cudaError_t ConfigureDecodeKernels() {
+  cudaError_t e = cudaFuncSetAttribute(DecodePartKernel<kFmtQ8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       DecodeSmemBytes<kFmtQ8>());
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(DecodePartKernel<kFmtQ4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              DecodeSmemBytes<kFmtQ4>());
+}
+
+cudaError_t LaunchDecode(const DecodeLaunch& a, cudaStream_t stream) {
+  if (a.n_units <= 0 || a.n_seqs <= 0) return cudaSuccess;
+  const auto* q = static_cast<const __half*>(a.q_dev);
+  if (a.pool.fmt == kFmtQ8)
+    DecodePartKernel<kFmtQ8><<<a.n_units, kDecodeThreads, DecodeSmemBytes<kFmtQ8>(), stream>>>(
+        *a.kmap, *a.vmap, a.pool, a.layer, a.tables_dev, a.table_stride, a.units_dev, q, a.scale_log2, a.partial_acc,
+        a.partial_ml, a.status_dev);
+  else
+    DecodePartKernel<kFmtQ4><<<a.n_units, kDecodeThreads, DecodeSmemBytes<kFmtQ4>(), stream>>>(
+        *a.kmap, *a.vmap, a.pool, a.layer, a.tables_dev, a.table_stride, a.units_dev, q, a.scale_log2, a.partial_acc,
+        a.partial_ml, a.status_dev);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  DecodeCombineKernel<<<a.n_seqs * kQHeads, kHeadDim / 2, 0, stream>>>(a.items_dev, a.partial_acc, a.partial_ml,
+                                                                      a.gate_dev, a.out_dev, a.out_f32);
+  return cudaGetLastError();
+}
+
+}  // namespace yahkv

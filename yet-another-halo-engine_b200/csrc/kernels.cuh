@@ -1,0 +1,119 @@
+// Device-side contracts shared by the kernels and the host library: geometry constants, the work descriptors the host
+// plans per call, and one launch function per kernel. Launchers enqueue on the given stream and return the CUDA error.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace yahkv {
+
+constexpr int kQHeads = 24;
+constexpr int kKvHeads = 4;
+constexpr int kGroup = 6;        // query heads per kv head
+constexpr int kHeadDim = 256;
+constexpr int kPageTokens = 64;
+constexpr int kBlocksPerRow = 8; // 32-element blocks per head row
+
+constexpr int kFmtQ8 = 0;
+constexpr int kFmtQ4 = 1;
+
+__host__ __device__ constexpr int CodeBytes(int fmt) { return fmt == kFmtQ8 ? 256 : 128; }
+// One page record of one kv head: codes then (in a separate pool) scales.
+__host__ __device__ constexpr int RecordCodeBytes(int fmt) { return kPageTokens * CodeBytes(fmt); }
+constexpr int kRecordScaleBytes = kPageTokens * kBlocksPerRow * 2;
+
+// The pools of one context. Codes are addressed both by pointer (append, inspection) and through 2-D tensor maps
+// whose rows are token rows of CodeBytes(fmt) bytes (attention's gathers).
+struct PoolView {
+  std::uint8_t* kcodes;
+  std::uint8_t* vcodes;
+  std::uint16_t* kscales;
+  std::uint16_t* vscales;
+  int fmt;
+  int num_pages;
+  int n_layers;
+};
+
+// One split-K unit of decode attention: pages [page_begin, page_end) of one sequence for one kv head.
+struct DecodeUnit {
+  std::int32_t batch;       // row of q / out
+  std::int32_t seq;         // block-table row
+  std::int32_t kvh;
+  std::int32_t page_begin;
+  std::int32_t page_end;
+  std::int32_t n_keys;      // visible keys of the sequence (its length)
+  std::int32_t partial;     // row of the partial workspace this unit writes
+  std::int32_t pad;
+};
+// Where the partials of one (batch row, kv head) lie, for the combine pass.
+struct CombineItem {
+  std::int32_t first_partial;
+  std::int32_t n_partials;
+};
+
+// One tile of prefill attention: 64 query rows of one sequence for one kv head.
+struct PrefillTile {
+  std::int32_t seq;         // block-table row
+  std::int32_t kvh;
+  std::int32_t q_row0;      // first packed query row of the tile
+  std::int32_t n_rows;      // valid query rows in the tile (<= 64)
+  std::int32_t pos0;        // position of the tile's first query row
+  std::int32_t pad[3];
+};
+
+// Partial workspace per unit: acc [6][256] f32 (unnormalised), then ml [6][2] f32 (max in log2 units, sum).
+constexpr int kPartialAccFloats = kGroup * kHeadDim;
+constexpr int kPartialMlFloats = kGroup * 2;
+
+cudaError_t LaunchAppend(const PoolView& pool, int layer, int n_tokens, const std::int64_t* slots_dev,
+                         const void* k_dev, const void* v_dev, cudaStream_t stream);
+
+struct DecodeLaunch {
+  const CUtensorMap* kmap;  // host pointers to the encoded maps (passed by value to the kernel)
+  const CUtensorMap* vmap;
+  PoolView pool;
+  int layer;
+  const std::int32_t* tables_dev;
+  int table_stride;
+  const DecodeUnit* units_dev;
+  int n_units;
+  const CombineItem* items_dev;
+  int n_seqs;
+  const void* q_dev;
+  const float* gate_dev;
+  void* out_dev;
+  int out_f32;
+  float scale_log2;         // softmax scale * log2(e)
+  float* partial_acc;
+  float* partial_ml;
+  int* status_dev;          // sticky error word, 0 = ok
+};
+cudaError_t LaunchDecode(const DecodeLaunch& a, cudaStream_t stream);
+// Shared-memory bytes the decode kernel asks for (for the one-time attribute set-up).
+cudaError_t ConfigureDecodeKernels();
+
+struct PrefillLaunch {
+  const CUtensorMap* kmap;
+  const CUtensorMap* vmap;
+  PoolView pool;
+  int layer;
+  const std::int32_t* tables_dev;
+  int table_stride;
+  const PrefillTile* tiles_dev;
+  int n_tiles;
+  const void* q_dev;
+  const float* gate_dev;
+  void* out_dev;
+  int out_f32;
+  float scale_log2;
+  int* status_dev;
+};
+cudaError_t LaunchPrefill(const PrefillLaunch& a, cudaStream_t stream);
+cudaError_t ConfigurePrefillKernels();
+
+// Status codes the kernels write into the sticky status word.
+constexpr int kStatusWaitTimeout = 1;
+
+}  // namespace yahkv

@@ -1,0 +1,350 @@
+// Host side of the cache: the page allocator, the per-sequence block tables, per-layer lengths, validation, and the
+// planners that turn a batch of sequences into the work lists the kernels read. No CUDA in this header.
+//
+// The reference keeps one sequence with an identity page table (engine/model/loom_decoder.hpp:175-179) and validates
+// every table entry before upload (engine/model/loom_prefill.hpp:1314-1316); batching, the free list and the split-K
+// planner are this library's own. Errors are reported as codes plus a message, never thrown across the C ABI, and
+// every check runs before anything is queued (engine/model/loom_decoder.hpp:186-209).
+#pragma once
+
+#include <algorithm>
+#include <cstdint>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "../../include/yahkv.h"
+#include "kernels.cuh"
+
+namespace yahkv {
+
+struct HostError {
+  int code = YAHKV_OK;
+  std::string message;
+};
+
+class KvHost {
+ public:
+  explicit KvHost(const yahkv_config& cfg) : cfg_(cfg) {
+    const std::size_t ns = static_cast<std::size_t>(cfg.max_seqs);
+    table_.assign(ns * static_cast<std::size_t>(cfg.max_pages_per_seq), 0);
+    n_pages_.assign(ns, 0);
+    live_.assign(ns, 0);
+    len_.assign(ns * static_cast<std::size_t>(cfg.n_layers), 0);
+    dirty_lo_.assign(ns, 0);
+    dirty_hi_.assign(ns, 0);
+    owner_.assign(static_cast<std::size_t>(cfg.num_pages), -1);
+    // LIFO free list: page 0 is handed out first.
+    free_pages_.reserve(static_cast<std::size_t>(cfg.num_pages));
+    for (int p = cfg.num_pages - 1; p >= 0; --p) free_pages_.push_back(p);
+    free_seqs_.reserve(ns);
+    for (int s = cfg.max_seqs - 1; s >= 0; --s) free_seqs_.push_back(s);
+  }
+
+  static int ValidateConfig(const yahkv_config& c, std::string* why) {
+    auto bad = [&](const char* m) {
+      *why = m;
+      return YAHKV_ERR_INVALID;
+    };
+    if (c.n_q_heads != kQHeads || c.n_kv_heads != kKvHeads || c.head_dim != kHeadDim)
+      return bad("geometry must be 24 query heads, 4 kv heads, head_dim 256");
+    if (c.page_tokens != kPageTokens) return bad("page_tokens must be 64");
+    if (c.fmt != YAHKV_FMT_Q8_0 && c.fmt != YAHKV_FMT_Q4_0) return bad("fmt must be YAHKV_FMT_Q8_0 or YAHKV_FMT_Q4_0");
+    if (c.n_layers < 1 || c.n_layers > 1024) return bad("n_layers out of range");
+    if (c.num_pages < 1) return bad("num_pages must be positive");
+    if (c.max_seqs < 1 || c.max_pages_per_seq < 1) return bad("max_seqs and max_pages_per_seq must be positive");
+    if (c.max_splits < 0 || c.max_batch_tokens < 0) return bad("max_splits and max_batch_tokens must not be negative");
+    // Token rows of all layers are addressed by a signed 32-bit tensor-map coordinate.
+    const long long rows = 1LL * c.n_layers * c.num_pages * kKvHeads * kPageTokens;
+    if (rows >= (1LL << 31)) return bad("n_layers * num_pages too large for the pool's row index");
+    return YAHKV_OK;
+  }
+
+  const yahkv_config& cfg() const { return cfg_; }
+  int pages_free() const { return static_cast<int>(free_pages_.size()); }
+  bool live(int seq) const { return seq >= 0 && seq < cfg_.max_seqs && live_[static_cast<std::size_t>(seq)] != 0; }
+  int n_pages(int seq) const { return n_pages_[static_cast<std::size_t>(seq)]; }
+  const std::int32_t* table_row(int seq) const {
+    return table_.data() + static_cast<std::size_t>(seq) * static_cast<std::size_t>(cfg_.max_pages_per_seq);
+  }
+  std::int64_t len(int seq, int layer) const {
+    return len_[static_cast<std::size_t>(seq) * static_cast<std::size_t>(cfg_.n_layers) + static_cast<std::size_t>(layer)];
+  }
+
+  HostError SeqCreate(std::int32_t* seq) {
+    if (free_seqs_.empty()) return {YAHKV_ERR_CAPACITY, "no free sequence slot (max_seqs reached)"};
+    const int s = free_seqs_.back();
+    free_seqs_.pop_back();
+    live_[static_cast<std::size_t>(s)] = 1;
+    n_pages_[static_cast<std::size_t>(s)] = 0;
+    SetLenAll(s, 0);
+    *seq = s;
+    return {};
+  }
+
+  HostError SeqFree(int seq) {
+    if (!live(seq)) return {YAHKV_ERR_INVALID, "seq_free: not a live sequence: " + std::to_string(seq)};
+    ReleasePages(seq);
+    live_[static_cast<std::size_t>(seq)] = 0;
+    SetLenAll(seq, 0);
+    free_seqs_.push_back(seq);
+    return {};
+  }
+
+  HostError SeqReserve(int seq, std::int64_t n_tokens) {
+    if (!live(seq)) return {YAHKV_ERR_INVALID, "seq_reserve: not a live sequence: " + std::to_string(seq)};
+    if (n_tokens < 0) return {YAHKV_ERR_INVALID, "seq_reserve: negative token count"};
+    const std::int64_t need = (n_tokens + kPageTokens - 1) / kPageTokens;
+    const int have = n_pages_[static_cast<std::size_t>(seq)];
+    if (need <= have) return {};
+    if (need > cfg_.max_pages_per_seq)
+      return {YAHKV_ERR_CAPACITY, "seq_reserve: " + std::to_string(n_tokens) + " tokens need more than max_pages_per_seq pages"};
+    if (need - have > static_cast<std::int64_t>(free_pages_.size()))
+      return {YAHKV_ERR_NO_PAGES, "seq_reserve: page pool exhausted (" + std::to_string(free_pages_.size()) +
+                                      " free, " + std::to_string(need - have) + " needed)"};
+    std::int32_t* row = mutable_row(seq);
+    for (int i = have; i < need; ++i) {
+      const std::int32_t p = free_pages_.back();
+      free_pages_.pop_back();
+      owner_[static_cast<std::size_t>(p)] = seq;
+      row[i] = p;
+    }
+    n_pages_[static_cast<std::size_t>(seq)] = static_cast<int>(need);
+    MarkDirty(seq, have, static_cast<int>(need));
+    return {};
+  }
+
+  HostError SeqSetTable(int seq, const std::int32_t* pages, int n) {
+    if (!live(seq)) return {YAHKV_ERR_INVALID, "seq_set_table: not a live sequence: " + std::to_string(seq)};
+    if (n < 0 || (n > 0 && pages == nullptr)) return {YAHKV_ERR_INVALID, "seq_set_table: bad page list"};
+    if (n > cfg_.max_pages_per_seq) return {YAHKV_ERR_CAPACITY, "seq_set_table: more pages than max_pages_per_seq"};
+    // Validate everything before changing anything.
+    std::vector<std::int32_t> sorted(pages, pages + n);
+    std::sort(sorted.begin(), sorted.end());
+    for (int i = 0; i < n; ++i) {
+      const std::int32_t p = sorted[static_cast<std::size_t>(i)];
+      if (p < 0 || p >= cfg_.num_pages)
+        return {YAHKV_ERR_INVALID, "page table entry out of range: " + std::to_string(p)};
+      if (i > 0 && sorted[static_cast<std::size_t>(i - 1)] == p)
+        return {YAHKV_ERR_INVALID, "page table names page " + std::to_string(p) + " twice"};
+      const int own = owner_[static_cast<std::size_t>(p)];
+      if (own != -1 && own != seq)
+        return {YAHKV_ERR_INVALID, "page " + std::to_string(p) + " belongs to sequence " + std::to_string(own)};
+    }
+    ReleasePages(seq);
+    // Take the named pages out of the free list.
+    std::vector<char> take(static_cast<std::size_t>(cfg_.num_pages), 0);
+    for (int i = 0; i < n; ++i) take[static_cast<std::size_t>(pages[i])] = 1;
+    free_pages_.erase(std::remove_if(free_pages_.begin(), free_pages_.end(),
+                                     [&](std::int32_t p) { return take[static_cast<std::size_t>(p)] != 0; }),
+                      free_pages_.end());
+    std::int32_t* row = mutable_row(seq);
+    for (int i = 0; i < n; ++i) {
+      row[i] = pages[i];
+      owner_[static_cast<std::size_t>(pages[i])] = seq;
+    }
+    n_pages_[static_cast<std::size_t>(seq)] = n;
+    MarkDirty(seq, 0, n);
+    return {};
+  }
+
+  HostError SeqSetLen(int seq, int layer, std::int64_t len) {
+    if (!live(seq)) return {YAHKV_ERR_INVALID, "seq_set_len: not a live sequence: " + std::to_string(seq)};
+    if (layer < -1 || layer >= cfg_.n_layers) return {YAHKV_ERR_INVALID, "seq_set_len: layer out of range"};
+    if (len < 0 || len > static_cast<std::int64_t>(n_pages_[static_cast<std::size_t>(seq)]) * kPageTokens)
+      return {YAHKV_ERR_INVALID, "seq_set_len: length beyond the reserved pages"};
+    if (layer == -1)
+      SetLenAll(seq, len);
+    else
+      len_ref(seq, layer) = len;
+    return {};
+  }
+
+  // Checks one append call and computes its slots; on success also advances the lengths. Nothing changes on error.
+  HostError PlanAppend(int layer, int n_tokens, const std::int32_t* seq_ids, const std::int64_t* positions,
+                       std::int64_t* slots_out) {
+    if (layer < 0 || layer >= cfg_.n_layers) return {YAHKV_ERR_INVALID, "append: layer out of range"};
+    if (n_tokens < 0) return {YAHKV_ERR_INVALID, "append: negative token count"};
+    if (n_tokens > 0 && (seq_ids == nullptr || positions == nullptr)) return {YAHKV_ERR_INVALID, "append: null id or position array"};
+    scratch_len_.clear();
+    for (int t = 0; t < n_tokens; ++t) {
+      const int s = seq_ids[t];
+      if (!live(s)) return {YAHKV_ERR_INVALID, "append: not a live sequence: " + std::to_string(s)};
+      std::int64_t cur = -1;
+      for (auto& e : scratch_len_)
+        if (e.first == s) cur = e.second;
+      if (cur < 0) cur = len(s, layer);
+      const std::int64_t pos = positions[t];
+      if (pos != cur)
+        return {YAHKV_ERR_ORDER, "append: sequence " + std::to_string(s) + " layer " + std::to_string(layer) +
+                                     " expects position " + std::to_string(cur) + ", got " + std::to_string(pos)};
+      if (pos >= static_cast<std::int64_t>(n_pages_[static_cast<std::size_t>(s)]) * kPageTokens)
+        return {YAHKV_ERR_INVALID, "append: position " + std::to_string(pos) + " of sequence " + std::to_string(s) +
+                                       " is past its reserved pages"};
+      slots_out[t] = static_cast<std::int64_t>(table_row(s)[pos / kPageTokens]) * kPageTokens + pos % kPageTokens;
+      bool found = false;
+      for (auto& e : scratch_len_)
+        if (e.first == s) e.second = pos + 1, found = true;
+      if (!found) scratch_len_.emplace_back(s, pos + 1);
+    }
+    for (auto& e : scratch_len_) len_ref(e.first, layer) = e.second;
+    return {};
+  }
+
+  // Split-K plan of one decode call. units / items are rebuilt only when the (sequence, length) list or the split
+  // request differs from the cached one; *changed says whether they must be uploaded again.
+  HostError PlanDecode(int layer, int n_seqs, const std::int32_t* seq_ids, int n_splits, int max_splits,
+                       int max_units, bool* changed) {
+    if (layer < 0 || layer >= cfg_.n_layers) return {YAHKV_ERR_INVALID, "attend_decode: layer out of range"};
+    if (n_seqs < 0 || (n_seqs > 0 && seq_ids == nullptr)) return {YAHKV_ERR_INVALID, "attend_decode: bad sequence list"};
+    if (n_seqs > cfg_.max_seqs) return {YAHKV_ERR_CAPACITY, "attend_decode: more rows than max_seqs"};
+    if (n_splits < 0) return {YAHKV_ERR_INVALID, "attend_decode: negative n_splits"};
+    if (n_splits > max_splits) return {YAHKV_ERR_CAPACITY, "attend_decode: n_splits above max_splits"};
+    key_scratch_.clear();
+    key_scratch_.push_back(n_splits);
+    long long total_pages = 0;
+    for (int b = 0; b < n_seqs; ++b) {
+      const int s = seq_ids[b];
+      if (!live(s)) return {YAHKV_ERR_INVALID, "attend_decode: not a live sequence: " + std::to_string(s)};
+      const std::int64_t n = len(s, layer);
+      if (n <= 0)
+        return {YAHKV_ERR_ORDER, "attend_decode: sequence " + std::to_string(s) + " has no keys in layer " +
+                                     std::to_string(layer) + " (append first)"};
+      key_scratch_.push_back(s);
+      key_scratch_.push_back(n);
+      total_pages += (n + kPageTokens - 1) / kPageTokens;
+    }
+    if (key_scratch_ == plan_key_) {
+      *changed = false;
+      return {};
+    }
+    // Automatic unit size: enough units to fill the machine several times over, but not so small that the partial
+    // write-back matters. 148 SMs x 2 resident CTAs x 8 units each.
+    int auto_pages = static_cast<int>((total_pages * kKvHeads + 2367) / 2368);
+    auto_pages = std::min(std::max(auto_pages, 1), 16);
+    std::vector<DecodeUnit> units;
+    std::vector<CombineItem> items(static_cast<std::size_t>(n_seqs) * kKvHeads);
+    for (int b = 0; b < n_seqs; ++b) {
+      const int s = seq_ids[b];
+      const std::int64_t n = len(s, layer);
+      const int pages = static_cast<int>((n + kPageTokens - 1) / kPageTokens);
+      int per = n_splits > 0 ? (pages + n_splits - 1) / n_splits : auto_pages;
+      per = std::max(per, (pages + max_splits - 1) / max_splits);
+      const int nu = (pages + per - 1) / per;
+      for (int h = 0; h < kKvHeads; ++h) {
+        items[static_cast<std::size_t>(b) * kKvHeads + h] = {static_cast<std::int32_t>(units.size()), nu};
+        for (int k = 0; k < nu; ++k) {
+          DecodeUnit u{};
+          u.batch = b, u.seq = s, u.kvh = h;
+          u.page_begin = k * per, u.page_end = std::min(pages, (k + 1) * per);
+          u.n_keys = static_cast<std::int32_t>(n);
+          u.partial = static_cast<std::int32_t>(units.size());
+          units.push_back(u);
+        }
+      }
+    }
+    if (static_cast<long long>(units.size()) > max_units)
+      return {YAHKV_ERR_CAPACITY, "attend_decode: split-K plan needs " + std::to_string(units.size()) +
+                                      " units, workspace holds " + std::to_string(max_units)};
+    units_ = std::move(units);
+    items_ = std::move(items);
+    plan_key_ = key_scratch_;
+    *changed = true;
+    return {};
+  }
+  void InvalidateDecodePlan() { plan_key_.clear(); }
+  const std::vector<DecodeUnit>& units() const { return units_; }
+  const std::vector<CombineItem>& items() const { return items_; }
+
+  // Tiles of one prefill call: 64 query rows x one kv head each, longest keys first within the call.
+  HostError PlanPrefill(int layer, int n_seqs, const std::int32_t* seq_ids, const std::int32_t* chunk_lens,
+                        int max_rows, std::vector<PrefillTile>* tiles, std::int64_t* total_rows) {
+    if (layer < 0 || layer >= cfg_.n_layers) return {YAHKV_ERR_INVALID, "attend_prefill: layer out of range"};
+    if (n_seqs < 0 || (n_seqs > 0 && (seq_ids == nullptr || chunk_lens == nullptr)))
+      return {YAHKV_ERR_INVALID, "attend_prefill: bad sequence list"};
+    tiles->clear();
+    std::int64_t row = 0;
+    for (int i = 0; i < n_seqs; ++i) {
+      const int s = seq_ids[i];
+      if (!live(s)) return {YAHKV_ERR_INVALID, "attend_prefill: not a live sequence: " + std::to_string(s)};
+      const std::int64_t n = len(s, layer);
+      const int c = chunk_lens[i];
+      if (c <= 0) return {YAHKV_ERR_INVALID, "attend_prefill: chunk length must be positive"};
+      if (c > n)
+        return {YAHKV_ERR_ORDER, "attend_prefill: chunk of " + std::to_string(c) + " rows but sequence " +
+                                     std::to_string(s) + " holds " + std::to_string(n) + " keys (append first)"};
+      for (int r = 0; r < c; r += 64)
+        for (int h = 0; h < kKvHeads; ++h) {
+          PrefillTile t{};
+          t.seq = s, t.kvh = h;
+          t.q_row0 = static_cast<std::int32_t>(row + r);
+          t.n_rows = std::min(64, c - r);
+          t.pos0 = static_cast<std::int32_t>(n - c + r);
+          tiles->push_back(t);
+        }
+      row += c;
+    }
+    if (row > max_rows) return {YAHKV_ERR_CAPACITY, "attend_prefill: more query rows than max_batch_tokens"};
+    // Tiles with the most keys first, so the short ones fill the tail.
+    std::stable_sort(tiles->begin(), tiles->end(),
+                     [](const PrefillTile& a, const PrefillTile& b) { return a.pos0 + a.n_rows > b.pos0 + b.n_rows; });
+    *total_rows = row;
+    return {};
+  }
+
+  // Rows of the block table changed since the last call: [lo, hi) per sequence. The caller uploads and clears.
+  template <class F>
+  void ForEachDirty(F&& fn) {
+    for (int s : dirty_list_) {
+      const std::size_t i = static_cast<std::size_t>(s);
+      if (dirty_hi_[i] > dirty_lo_[i]) fn(s, dirty_lo_[i], dirty_hi_[i]);
+      dirty_lo_[i] = dirty_hi_[i] = 0;
+    }
+    dirty_list_.clear();
+  }
+
+ private:
+  std::int32_t* mutable_row(int seq) {
+    return table_.data() + static_cast<std::size_t>(seq) * static_cast<std::size_t>(cfg_.max_pages_per_seq);
+  }
+  std::int64_t& len_ref(int seq, int layer) {
+    return len_[static_cast<std::size_t>(seq) * static_cast<std::size_t>(cfg_.n_layers) + static_cast<std::size_t>(layer)];
+  }
+  void SetLenAll(int seq, std::int64_t v) {
+    for (int l = 0; l < cfg_.n_layers; ++l) len_ref(seq, l) = v;
+  }
+  void ReleasePages(int seq) {
+    const std::int32_t* row = table_row(seq);
+    // Pushed in table order, so the most recently added page is reused first.
+    for (int i = 0; i < n_pages_[static_cast<std::size_t>(seq)]; ++i) {
+      owner_[static_cast<std::size_t>(row[i])] = -1;
+      free_pages_.push_back(row[i]);
+    }
+    n_pages_[static_cast<std::size_t>(seq)] = 0;
+  }
+  void MarkDirty(int seq, int lo, int hi) {
+    const std::size_t i = static_cast<std::size_t>(seq);
+    if (dirty_hi_[i] == dirty_lo_[i]) {
+      dirty_lo_[i] = lo, dirty_hi_[i] = hi;
+      dirty_list_.push_back(seq);
+    } else {
+      dirty_lo_[i] = std::min(dirty_lo_[i], lo), dirty_hi_[i] = std::max(dirty_hi_[i], hi);
+    }
+  }
+
+  yahkv_config cfg_;
+  std::vector<std::int32_t> table_;
+  std::vector<int> n_pages_;
+  std::vector<char> live_;
+  std::vector<std::int64_t> len_;
+  std::vector<int> dirty_lo_, dirty_hi_, dirty_list_;
+  std::vector<int> owner_;
+  std::vector<std::int32_t> free_pages_;
+  std::vector<int> free_seqs_;
+  std::vector<std::pair<int, std::int64_t>> scratch_len_;
+  std::vector<std::int64_t> key_scratch_, plan_key_;
+  std::vector<DecodeUnit> units_;
+  std::vector<CombineItem> items_;
+};
+
+}  // namespace yahkv

@@ -1,0 +1,133 @@
+// Thin wrappers over the sm_100a PTX this library uses: mbarriers, bulk-async (TMA) copies, ldmatrix and the
+// register-operand f16 MMA. Every wait is bounded: a wait that gives up returns false and the caller records an error
+// status instead of spinning forever.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace yahkv {
+
+__device__ __forceinline__ std::uint32_t SmemAddr(const void* p) {
+  return static_cast<std::uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void MbarInit(std::uint64_t* bar, std::uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(SmemAddr(bar)), "r"(count));
+}
+__device__ __forceinline__ void FenceBarrierInit() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void FenceProxyAsync() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void MbarArrive(std::uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(SmemAddr(bar)) : "memory");
+}
+__device__ __forceinline__ void MbarArriveExpectTx(std::uint64_t* bar, std::uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(SmemAddr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool MbarTryWait(std::uint64_t* bar, std::uint32_t parity) {
+  std::uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(SmemAddr(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ std::uint64_t GlobalTimerNs() {
+  std::uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Waits for the barrier's phase `parity` to complete, for at most about two seconds.
+__device__ __forceinline__ bool MbarWait(std::uint64_t* bar, std::uint32_t parity) {
+  if (MbarTryWait(bar, parity)) return true;
+  const std::uint64_t t0 = GlobalTimerNs();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (MbarTryWait(bar, parity)) return true;
+    if (GlobalTimerNs() - t0 > 2000000000ULL) return false;
+  }
+}
+
+// 2-D tiled TMA load (no multicast): box at (x, y) of the tensor map into this CTA's shared memory.
+__device__ __forceinline__ void TmaLoad2D(void* smem_dst, const CUtensorMap* map, int x, int y, std::uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          SmemAddr(smem_dst)),
+      "l"(reinterpret_cast<std::uint64_t>(map)), "r"(x), "r"(y), "r"(SmemAddr(bar))
+      : "memory");
+}
+// 1-D bulk copy global -> shared; both addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void BulkLoad(void* smem_dst, const void* gsrc, std::uint32_t bytes, std::uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   SmemAddr(smem_dst)),
+               "l"(reinterpret_cast<std::uint64_t>(gsrc)), "r"(bytes), "r"(SmemAddr(bar))
+               : "memory");
+}
+__device__ __forceinline__ void PrefetchTensorMap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<std::uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ void LdMatrixX4(std::uint32_t addr, std::uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void LdMatrixX4Trans(std::uint32_t addr, std::uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+// D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)
+__device__ __forceinline__ void MmaF16(float (&d)[4], std::uint32_t a0, std::uint32_t a1, std::uint32_t a2,
+                                       std::uint32_t a3, std::uint32_t b0, std::uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void NamedBarrierSync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Four int8 codes in a word -> two half2 of exact integers: bytes (0, 2) and bytes (1, 3).
+// 0x6400 | u is the fp16 value 1024 + u; with u = code + 128 the code is that minus 1152.
+__device__ __forceinline__ void Int8x4ToHalf2(std::uint32_t w, std::uint32_t& h02, std::uint32_t& h13) {
+  const std::uint32_t lo = (w & 0x00FF00FFU) ^ 0x64806480U;
+  const std::uint32_t hi = __byte_perm(w, 0x64646464U, 0x4341) ^ 0x00800080U;
+  const __half2 bias = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));
+  const __half2 a = __hsub2(*reinterpret_cast<const __half2*>(&lo), bias);
+  const __half2 b = __hsub2(*reinterpret_cast<const __half2*>(&hi), bias);
+  h02 = *reinterpret_cast<const std::uint32_t*>(&a);
+  h13 = *reinterpret_cast<const std::uint32_t*>(&b);
+}
+// Four packed q4_0 bytes -> low nibbles of bytes (0,2), (1,3) and high nibbles of bytes (0,2), (1,3), each minus 8.
+__device__ __forceinline__ void Nib4x4ToHalf2(std::uint32_t w, std::uint32_t& l02, std::uint32_t& l13,
+                                              std::uint32_t& h02, std::uint32_t& h13) {
+  const __half2 bias = __halves2half2(__ushort_as_half(0x6408), __ushort_as_half(0x6408));  // 1032
+  const std::uint32_t a = (w & 0x000F000FU) | 0x64006400U;
+  const std::uint32_t b = ((w >> 8) & 0x000F000FU) | 0x64006400U;
+  const std::uint32_t c = ((w >> 4) & 0x000F000FU) | 0x64006400U;
+  const std::uint32_t d = ((w >> 12) & 0x000F000FU) | 0x64006400U;
+  const __half2 ra = __hsub2(*reinterpret_cast<const __half2*>(&a), bias);
+  const __half2 rb = __hsub2(*reinterpret_cast<const __half2*>(&b), bias);
+  const __half2 rc = __hsub2(*reinterpret_cast<const __half2*>(&c), bias);
+  const __half2 rd = __hsub2(*reinterpret_cast<const __half2*>(&d), bias);
+  l02 = *reinterpret_cast<const std::uint32_t*>(&ra);
+  l13 = *reinterpret_cast<const std::uint32_t*>(&rb);
+  h02 = *reinterpret_cast<const std::uint32_t*>(&rc);
+  h13 = *reinterpret_cast<const std::uint32_t*>(&rd);
+}
+
+}  // namespace yahkv

@@ -1,0 +1,612 @@
+// The C ABI of the library (include/yahkv.h): context and device resources, stream-ordered uploads of block tables
+// and work lists, and the entry points that validate, plan and launch. There is no CPU fallback: a hot-path call on
+// a context without a GPU fails with YAHKV_ERR_NO_DEVICE.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/yahkv.h"
+#include "kernels.cuh"
+#include "kv_host.hpp"
+
+using namespace yahkv;
+
+namespace {
+
+std::mutex g_create_mu;
+std::string g_create_error;
+
+// A small set of pinned staging buffers handed out round-robin. A buffer is reused only after the copies that read it
+// have completed (its event), so host-side state can change right after a call returns.
+class Staging {
+ public:
+  static constexpr int kSlots = 8;
+  ~Staging() {
+    for (auto& s : slots_) {
+      if (s.host != nullptr) cudaFreeHost(s.host);
+      if (s.ev != nullptr) cudaEventDestroy(s.ev);
+    }
+  }
+  cudaError_t Acquire(std::size_t bytes, char** out) {
+    Slot& s = slots_[next_];
+    cur_ = next_;
+    next_ = (next_ + 1) % kSlots;
+    if (s.ev == nullptr) {
+      cudaError_t e = cudaEventCreateWithFlags(&s.ev, cudaEventDisableTiming);
+      if (e != cudaSuccess) return e;
+    }
+    if (s.in_flight) {
+      cudaError_t e = cudaEventSynchronize(s.ev);
+      if (e != cudaSuccess) return e;
+      s.in_flight = false;
+    }
+    if (s.cap < bytes) {
+      if (s.host != nullptr) cudaFreeHost(s.host);
+      s.host = nullptr, s.cap = 0;
+      const std::size_t cap = std::max<std::size_t>(bytes, 1 << 16);
+      cudaError_t e = cudaHostAlloc(reinterpret_cast<void**>(&s.host), cap, cudaHostAllocDefault);
+      if (e != cudaSuccess) return e;
+      s.cap = cap;
+    }
+    *out = s.host;
+    return cudaSuccess;
+  }
+  // Marks the buffer handed out last as busy until everything queued on `stream` so far has run.
+  cudaError_t Release(cudaStream_t stream) {
+    Slot& s = slots_[cur_];
+    s.in_flight = true;
+    return cudaEventRecord(s.ev, stream);
+  }
+
+ private:
+  struct Slot {
+    char* host = nullptr;
+    std::size_t cap = 0;
+    cudaEvent_t ev = nullptr;
+    bool in_flight = false;
+  };
+  Slot slots_[kSlots];
+  int next_ = 0, cur_ = 0;
+};
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+}  // namespace
+
+struct yahkv_ctx {
+  explicit yahkv_ctx(const yahkv_config& c) : cfg(c), host(c) {}
+  yahkv_config cfg;
+  KvHost host;
+  mutable std::string err;
+  bool has_device = false;
+  PoolView pool{};
+  CUtensorMap kmap{}, vmap{};
+  std::int32_t* tables_dev = nullptr;
+  DecodeUnit* units_dev = nullptr;
+  CombineItem* items_dev = nullptr;
+  PrefillTile* tiles_dev = nullptr;
+  int max_tiles = 0;
+  std::int64_t* slots_dev = nullptr;
+  float* partial_acc = nullptr;
+  float* partial_ml = nullptr;
+  int max_units = 0;
+  int* status_dev = nullptr;
+  cudaStream_t stream = nullptr;
+  Staging staging;
+  // device-side staging of the host-buffer entry point
+  void *hs_k = nullptr, *hs_v = nullptr, *hs_q = nullptr, *hs_out = nullptr;
+  float* hs_gate = nullptr;
+  std::int64_t launches = 0;
+  std::int64_t device_bytes = 0;
+  std::vector<std::int64_t> slot_scratch;
+  std::vector<std::int64_t> pos_scratch;
+  std::vector<PrefillTile> tile_scratch;
+  float scale_log2 = 0.0F;
+};
+
+namespace {
+
+int Fail(const yahkv_ctx* ctx, int code, std::string msg) {
+  ctx->err = std::move(msg);
+  return code;
+}
+int FailHost(const yahkv_ctx* ctx, HostError e) { return Fail(ctx, e.code, std::move(e.message)); }
+int FailCuda(const yahkv_ctx* ctx, const char* what, cudaError_t e) {
+  return Fail(ctx, YAHKV_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+#define YAHKV_CUDA(ctx, call)                                     \
+  do {                                                            \
+    const cudaError_t e_ = (call);                                \
+    if (e_ != cudaSuccess) return FailCuda((ctx), #call, e_);     \
+  } while (0)
+
+template <class T>
+cudaError_t DevAlloc(yahkv_ctx* ctx, T** p, std::size_t count, bool zero) {
+  const std::size_t bytes = std::max<std::size_t>(count * sizeof(T), 256);
+  cudaError_t e = cudaMalloc(reinterpret_cast<void**>(p), bytes);
+  if (e != cudaSuccess) return e;
+  ctx->device_bytes += static_cast<std::int64_t>(bytes);
+  if (zero) e = cudaMemset(*p, 0, bytes);
+  return e;
+}
+
+int EncodeMap(yahkv_ctx* ctx, EncodeTiledFn encode, CUtensorMap* map, void* base) {
+  const cuuint64_t row_bytes = static_cast<cuuint64_t>(CodeBytes(ctx->cfg.fmt));
+  const cuuint64_t rows = static_cast<cuuint64_t>(ctx->cfg.n_layers) * ctx->cfg.num_pages * kKvHeads * kPageTokens;
+  const cuuint64_t dims[2] = {row_bytes, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {128, kPageTokens};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, elem,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return Fail(ctx, YAHKV_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(r));
+  return YAHKV_OK;
+}
+
+int InitDevice(yahkv_ctx* ctx) {
+  const yahkv_config& c = ctx->cfg;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || c.device >= count)
+    return Fail(ctx, YAHKV_ERR_NO_DEVICE, "no CUDA device " + std::to_string(c.device));
+  YAHKV_CUDA(ctx, cudaSetDevice(c.device));
+  cudaDeviceProp prop{};
+  YAHKV_CUDA(ctx, cudaGetDeviceProperties(&prop, c.device));
+  if (prop.major != 10)
+    return Fail(ctx, YAHKV_ERR_NO_DEVICE, std::string("this library is built for sm_100a only; device is ") + prop.name);
+  YAHKV_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+
+  const std::size_t recs = static_cast<std::size_t>(c.n_layers) * c.num_pages * kKvHeads;
+  ctx->pool.fmt = c.fmt, ctx->pool.num_pages = c.num_pages, ctx->pool.n_layers = c.n_layers;
+  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.kcodes, recs * RecordCodeBytes(c.fmt), true));
+  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.vcodes, recs * RecordCodeBytes(c.fmt), true));
+  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.kscales, recs * kPageTokens * kBlocksPerRow, true));
+  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.vscales, recs * kPageTokens * kBlocksPerRow, true));
+  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->tables_dev, static_cast<std::size_t>(c.max_seqs) * c.max_pages_per_seq, true));
+  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->slots_dev, static_cast<std::size_t>(c.max_batch_tokens), false));
+  ctx->max_units = c.max_seqs * kKvHeads * c.max_splits;
+  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->units_dev, static_cast<std::size_t>(ctx->max_units), false));
+  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->items_dev, static_cast<std::size_t>(c.max_seqs) * kKvHeads, false));
+  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->partial_acc, static_cast<std::size_t>(ctx->max_units) * kPartialAccFloats, false));
+  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->partial_ml, static_cast<std::size_t>(ctx->max_units) * kPartialMlFloats, false));
+  ctx->max_tiles = (c.max_batch_tokens / 64 + c.max_seqs) * kKvHeads;
+  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->tiles_dev, static_cast<std::size_t>(ctx->max_tiles), false));
+  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->status_dev, 1, true));
+  const std::size_t ns = static_cast<std::size_t>(c.max_seqs);
+  YAHKV_CUDA(ctx, DevAlloc(ctx, reinterpret_cast<char**>(&ctx->hs_k), ns * kKvHeads * kHeadDim * 2, false));
+  YAHKV_CUDA(ctx, DevAlloc(ctx, reinterpret_cast<char**>(&ctx->hs_v), ns * kKvHeads * kHeadDim * 2, false));
+  YAHKV_CUDA(ctx, DevAlloc(ctx, reinterpret_cast<char**>(&ctx->hs_q), ns * kQHeads * kHeadDim * 2, false));
+  YAHKV_CUDA(ctx, DevAlloc(ctx, reinterpret_cast<char**>(&ctx->hs_out), ns * kQHeads * kHeadDim * 4, false));
+  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->hs_gate, ns * kQHeads * kHeadDim, false));
+
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres{};
+  YAHKV_CUDA(ctx, cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+  if (fn == nullptr || qres != cudaDriverEntryPointSuccess)
+    return Fail(ctx, YAHKV_ERR_CUDA, "the driver does not export cuTensorMapEncodeTiled");
+  const auto encode = reinterpret_cast<EncodeTiledFn>(fn);
+  if (int r = EncodeMap(ctx, encode, &ctx->kmap, ctx->pool.kcodes); r != YAHKV_OK) return r;
+  if (int r = EncodeMap(ctx, encode, &ctx->vmap, ctx->pool.vcodes); r != YAHKV_OK) return r;
+  YAHKV_CUDA(ctx, ConfigureDecodeKernels());
+  YAHKV_CUDA(ctx, ConfigurePrefillKernels());
+  YAHKV_CUDA(ctx, cudaDeviceSynchronize());
+  ctx->has_device = true;
+  return YAHKV_OK;
+}
+
+void FreeDevice(yahkv_ctx* ctx) {
+  if (ctx->cfg.device < 0) return;
+  cudaSetDevice(ctx->cfg.device);
+  if (ctx->stream != nullptr) cudaStreamSynchronize(ctx->stream);
+  void* ptrs[] = {ctx->pool.kcodes, ctx->pool.vcodes, ctx->pool.kscales, ctx->pool.vscales, ctx->tables_dev,
+                  ctx->slots_dev,   ctx->units_dev,   ctx->items_dev,    ctx->partial_acc,  ctx->partial_ml,
+                  ctx->tiles_dev,   ctx->status_dev,  ctx->hs_k,         ctx->hs_v,         ctx->hs_q,
+                  ctx->hs_out,      ctx->hs_gate};
+  for (void* p : ptrs)
+    if (p != nullptr) cudaFree(p);
+  if (ctx->stream != nullptr) cudaStreamDestroy(ctx->stream);
+}
+
+cudaStream_t StreamOf(yahkv_ctx* ctx, void* stream) {
+  return stream != nullptr ? static_cast<cudaStream_t>(stream) : ctx->stream;
+}
+
+int RequireDevice(yahkv_ctx* ctx, const char* what) {
+  if (ctx == nullptr) return YAHKV_ERR_INVALID;
+  if (!ctx->has_device)
+    return Fail(ctx, YAHKV_ERR_NO_DEVICE, std::string(what) + ": host-only context (no GPU, no CPU fallback)");
+  if (cudaSetDevice(ctx->cfg.device) != cudaSuccess) return Fail(ctx, YAHKV_ERR_CUDA, "cudaSetDevice failed");
+  return YAHKV_OK;
+}
+
+// Copies `bytes` at `src` (host) to `dst` (device) on `stream` through a pinned staging buffer.
+int StagedUpload(yahkv_ctx* ctx, void* dst, const void* src, std::size_t bytes, cudaStream_t stream) {
+  char* buf = nullptr;
+  YAHKV_CUDA(ctx, ctx->staging.Acquire(bytes, &buf));
+  std::memcpy(buf, src, bytes);
+  YAHKV_CUDA(ctx, cudaMemcpyAsync(dst, buf, bytes, cudaMemcpyHostToDevice, stream));
+  YAHKV_CUDA(ctx, ctx->staging.Release(stream));
+  return YAHKV_OK;
+}
+
+// Block-table rows changed on the host since the last hot call go to the device ahead of the kernels that read them.
+int FlushTables(yahkv_ctx* ctx, cudaStream_t stream) {
+  struct Range {
+    int seq, lo, hi;
+  };
+  std::vector<Range> ranges;
+  std::size_t total = 0;
+  ctx->host.ForEachDirty([&](int s, int lo, int hi) {
+    ranges.push_back({s, lo, hi});
+    total += static_cast<std::size_t>(hi - lo) * 4;
+  });
+  if (ranges.empty()) return YAHKV_OK;
+  char* buf = nullptr;
+  YAHKV_CUDA(ctx, ctx->staging.Acquire(total, &buf));
+  std::size_t off = 0;
+  for (const Range& r : ranges) {
+    const std::size_t bytes = static_cast<std::size_t>(r.hi - r.lo) * 4;
+    if (bytes == 0) continue;
+    std::memcpy(buf + off, ctx->host.table_row(r.seq) + r.lo, bytes);
+    YAHKV_CUDA(ctx, cudaMemcpyAsync(ctx->tables_dev + static_cast<std::size_t>(r.seq) * ctx->cfg.max_pages_per_seq + r.lo,
+                                    buf + off, bytes, cudaMemcpyHostToDevice, stream));
+    off += bytes;
+  }
+  YAHKV_CUDA(ctx, ctx->staging.Release(stream));
+  return YAHKV_OK;
+}
+
+int CheckStatus(yahkv_ctx* ctx) {
+  int st = 0;
+  YAHKV_CUDA(ctx, cudaMemcpy(&st, ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
+  if (st != 0) {
+    cudaMemset(ctx->status_dev, 0, sizeof(int));
+    return Fail(ctx, YAHKV_ERR_CUDA, "a kernel gave up a bounded wait (status " + std::to_string(st) + "); results of the call are invalid");
+  }
+  return YAHKV_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* yahkv_error_name(int code) {
+  switch (code) {
+    case YAHKV_OK: return "YAHKV_OK";
+    case YAHKV_ERR_INVALID: return "YAHKV_ERR_INVALID";
+    case YAHKV_ERR_NO_PAGES: return "YAHKV_ERR_NO_PAGES";
+    case YAHKV_ERR_CUDA: return "YAHKV_ERR_CUDA";
+    case YAHKV_ERR_NO_DEVICE: return "YAHKV_ERR_NO_DEVICE";
+    case YAHKV_ERR_ORDER: return "YAHKV_ERR_ORDER";
+    case YAHKV_ERR_CAPACITY: return "YAHKV_ERR_CAPACITY";
+    default: return "YAHKV_ERR_UNKNOWN";
+  }
+}
+
+const char* yahkv_last_error(const yahkv_ctx* ctx) {
+  if (ctx != nullptr) return ctx->err.c_str();
+  std::lock_guard<std::mutex> lock(g_create_mu);
+  static thread_local std::string copy;
+  copy = g_create_error;
+  return copy.c_str();
+}
+
+int yahkv_create(const yahkv_config* cfg, yahkv_ctx** out) {
+  auto fail = [&](int code, const std::string& msg) {
+    std::lock_guard<std::mutex> lock(g_create_mu);
+    g_create_error = msg;
+    return code;
+  };
+  if (out == nullptr) return fail(YAHKV_ERR_INVALID, "yahkv_create: null out pointer");
+  *out = nullptr;
+  if (cfg == nullptr) return fail(YAHKV_ERR_INVALID, "yahkv_create: null config");
+  yahkv_config c = *cfg;
+  if (c.max_splits == 0) c.max_splits = 64;
+  if (c.max_batch_tokens == 0) c.max_batch_tokens = 8192;
+  if (c.softmax_scale == 0.0F) c.softmax_scale = 1.0F / 16.0F;
+  std::string why;
+  if (int r = KvHost::ValidateConfig(c, &why); r != YAHKV_OK) return fail(r, "yahkv_create: " + why);
+  if (c.max_batch_tokens < c.max_seqs) c.max_batch_tokens = c.max_seqs;
+  yahkv_ctx* ctx = new (std::nothrow) yahkv_ctx(c);
+  if (ctx == nullptr) return fail(YAHKV_ERR_INVALID, "yahkv_create: out of host memory");
+  ctx->scale_log2 = c.softmax_scale * 1.4426950408889634F;
+  ctx->slot_scratch.resize(static_cast<std::size_t>(c.max_batch_tokens));
+  if (c.device >= 0) {
+    if (int r = InitDevice(ctx); r != YAHKV_OK) {
+      const std::string msg = ctx->err;
+      FreeDevice(ctx);
+      delete ctx;
+      return fail(r, "yahkv_create: " + msg);
+    }
+  }
+  *out = ctx;
+  return YAHKV_OK;
+}
+
+void yahkv_destroy(yahkv_ctx* ctx) {
+  if (ctx == nullptr) return;
+  FreeDevice(ctx);
+  delete ctx;
+}
+
+int yahkv_seq_create(yahkv_ctx* ctx, int32_t* seq) {
+  if (ctx == nullptr) return YAHKV_ERR_INVALID;
+  if (seq == nullptr) return Fail(ctx, YAHKV_ERR_INVALID, "seq_create: null out pointer");
+  HostError e = ctx->host.SeqCreate(seq);
+  return e.code == YAHKV_OK ? YAHKV_OK : FailHost(ctx, std::move(e));
+}
+
+int yahkv_seq_free(yahkv_ctx* ctx, int32_t seq) {
+  if (ctx == nullptr) return YAHKV_ERR_INVALID;
+  HostError e = ctx->host.SeqFree(seq);
+  return e.code == YAHKV_OK ? YAHKV_OK : FailHost(ctx, std::move(e));
+}
+
+int yahkv_seq_reserve(yahkv_ctx* ctx, int32_t seq, int64_t n_tokens) {
+  if (ctx == nullptr) return YAHKV_ERR_INVALID;
+  HostError e = ctx->host.SeqReserve(seq, n_tokens);
+  return e.code == YAHKV_OK ? YAHKV_OK : FailHost(ctx, std::move(e));
+}
+
+int yahkv_seq_set_table(yahkv_ctx* ctx, int32_t seq, const int32_t* pages, int32_t n) {
+  if (ctx == nullptr) return YAHKV_ERR_INVALID;
+  HostError e = ctx->host.SeqSetTable(seq, pages, n);
+  return e.code == YAHKV_OK ? YAHKV_OK : FailHost(ctx, std::move(e));
+}
+
+int yahkv_seq_table(const yahkv_ctx* ctx, int32_t seq, const int32_t** pages, int32_t* n) {
+  if (ctx == nullptr) return YAHKV_ERR_INVALID;
+  if (!ctx->host.live(seq)) return Fail(ctx, YAHKV_ERR_INVALID, "seq_table: not a live sequence: " + std::to_string(seq));
+  if (pages != nullptr) *pages = ctx->host.table_row(seq);
+  if (n != nullptr) *n = ctx->host.n_pages(seq);
+  return YAHKV_OK;
+}
+
+int yahkv_seq_len(const yahkv_ctx* ctx, int32_t seq, int32_t layer, int64_t* len) {
+  if (ctx == nullptr) return YAHKV_ERR_INVALID;
+  if (!ctx->host.live(seq)) return Fail(ctx, YAHKV_ERR_INVALID, "seq_len: not a live sequence: " + std::to_string(seq));
+  if (layer < 0 || layer >= ctx->cfg.n_layers || len == nullptr) return Fail(ctx, YAHKV_ERR_INVALID, "seq_len: bad layer or null pointer");
+  *len = ctx->host.len(seq, layer);
+  return YAHKV_OK;
+}
+
+int yahkv_seq_set_len(yahkv_ctx* ctx, int32_t seq, int32_t layer, int64_t len) {
+  if (ctx == nullptr) return YAHKV_ERR_INVALID;
+  HostError e = ctx->host.SeqSetLen(seq, layer, len);
+  return e.code == YAHKV_OK ? YAHKV_OK : FailHost(ctx, std::move(e));
+}
+
+int yahkv_pages_free(const yahkv_ctx* ctx, int32_t* n) {
+  if (ctx == nullptr || n == nullptr) return YAHKV_ERR_INVALID;
+  *n = ctx->host.pages_free();
+  return YAHKV_OK;
+}
+
+int yahkv_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int32_t* seq_ids, const int64_t* positions,
+                 const void* k_dev, const void* v_dev, void* stream) {
+  if (int r = RequireDevice(ctx, "append"); r != YAHKV_OK) return r;
+  if (n_tokens > ctx->cfg.max_batch_tokens) return Fail(ctx, YAHKV_ERR_CAPACITY, "append: more tokens than max_batch_tokens");
+  if (n_tokens > 0 && (k_dev == nullptr || v_dev == nullptr)) return Fail(ctx, YAHKV_ERR_INVALID, "append: null K or V pointer");
+  HostError e = ctx->host.PlanAppend(layer, n_tokens, seq_ids, positions, ctx->slot_scratch.data());
+  if (e.code != YAHKV_OK) return FailHost(ctx, std::move(e));
+  if (n_tokens == 0) return YAHKV_OK;
+  cudaStream_t st = StreamOf(ctx, stream);
+  if (int r = FlushTables(ctx, st); r != YAHKV_OK) return r;
+  if (int r = StagedUpload(ctx, ctx->slots_dev, ctx->slot_scratch.data(), static_cast<std::size_t>(n_tokens) * 8, st); r != YAHKV_OK)
+    return r;
+  YAHKV_CUDA(ctx, LaunchAppend(ctx->pool, layer, n_tokens, ctx->slots_dev, k_dev, v_dev, st));
+  ctx->launches += 1;
+  return YAHKV_OK;
+}
+
+int yahkv_append_slots(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int64_t* slot_mapping_dev,
+                       const void* k_dev, const void* v_dev, void* stream) {
+  if (int r = RequireDevice(ctx, "append_slots"); r != YAHKV_OK) return r;
+  if (layer < 0 || layer >= ctx->cfg.n_layers) return Fail(ctx, YAHKV_ERR_INVALID, "append_slots: layer out of range");
+  if (n_tokens < 0) return Fail(ctx, YAHKV_ERR_INVALID, "append_slots: negative token count");
+  if (n_tokens == 0) return YAHKV_OK;
+  if (slot_mapping_dev == nullptr || k_dev == nullptr || v_dev == nullptr)
+    return Fail(ctx, YAHKV_ERR_INVALID, "append_slots: null pointer");
+  cudaStream_t st = StreamOf(ctx, stream);
+  if (int r = FlushTables(ctx, st); r != YAHKV_OK) return r;
+  YAHKV_CUDA(ctx, LaunchAppend(ctx->pool, layer, n_tokens, slot_mapping_dev, k_dev, v_dev, st));
+  ctx->launches += 1;
+  return YAHKV_OK;
+}
+
+int yahkv_attend_decode(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids, const void* q_dev,
+                        const float* gate_dev, void* out_dev, int32_t out_dtype, int32_t n_splits, void* stream) {
+  if (int r = RequireDevice(ctx, "attend_decode"); r != YAHKV_OK) return r;
+  if (out_dtype != YAHKV_OUT_F16 && out_dtype != YAHKV_OUT_F32) return Fail(ctx, YAHKV_ERR_INVALID, "attend_decode: bad out_dtype");
+  if (n_seqs > 0 && (q_dev == nullptr || out_dev == nullptr)) return Fail(ctx, YAHKV_ERR_INVALID, "attend_decode: null q or out pointer");
+  bool changed = false;
+  HostError e = ctx->host.PlanDecode(layer, n_seqs, seq_ids, n_splits, ctx->cfg.max_splits, ctx->max_units, &changed);
+  if (e.code != YAHKV_OK) return FailHost(ctx, std::move(e));
+  if (n_seqs == 0) return YAHKV_OK;
+  cudaStream_t st = StreamOf(ctx, stream);
+  if (int r = FlushTables(ctx, st); r != YAHKV_OK) return r;
+  const auto& units = ctx->host.units();
+  const auto& items = ctx->host.items();
+  if (changed) {
+    // One staging buffer holds both lists so they share a completion event.
+    const std::size_t ub = units.size() * sizeof(DecodeUnit), ib = items.size() * sizeof(CombineItem);
+    char* buf = nullptr;
+    YAHKV_CUDA(ctx, ctx->staging.Acquire(ub + ib, &buf));
+    std::memcpy(buf, units.data(), ub);
+    std::memcpy(buf + ub, items.data(), ib);
+    YAHKV_CUDA(ctx, cudaMemcpyAsync(ctx->units_dev, buf, ub, cudaMemcpyHostToDevice, st));
+    YAHKV_CUDA(ctx, cudaMemcpyAsync(ctx->items_dev, buf + ub, ib, cudaMemcpyHostToDevice, st));
+    YAHKV_CUDA(ctx, ctx->staging.Release(st));
+  }
+  DecodeLaunch a{};
+  a.kmap = &ctx->kmap, a.vmap = &ctx->vmap, a.pool = ctx->pool, a.layer = layer;
+  a.tables_dev = ctx->tables_dev, a.table_stride = ctx->cfg.max_pages_per_seq;
+  a.units_dev = ctx->units_dev, a.n_units = static_cast<int>(units.size());
+  a.items_dev = ctx->items_dev, a.n_seqs = n_seqs;
+  a.q_dev = q_dev, a.gate_dev = gate_dev, a.out_dev = out_dev, a.out_f32 = out_dtype == YAHKV_OUT_F32;
+  a.scale_log2 = ctx->scale_log2;
+  a.partial_acc = ctx->partial_acc, a.partial_ml = ctx->partial_ml, a.status_dev = ctx->status_dev;
+  const cudaError_t le = LaunchDecode(a, st);
+  if (le != cudaSuccess) {
+    ctx->host.InvalidateDecodePlan();
+    return FailCuda(ctx, "decode attention launch", le);
+  }
+  ctx->launches += 2;
+  return YAHKV_OK;
+}
+
+int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids,
+                         const int32_t* chunk_lens, const void* q_dev, const float* gate_dev, void* out_dev,
+                         int32_t out_dtype, void* stream) {
+  if (int r = RequireDevice(ctx, "attend_prefill"); r != YAHKV_OK) return r;
+  if (out_dtype != YAHKV_OUT_F16 && out_dtype != YAHKV_OUT_F32) return Fail(ctx, YAHKV_ERR_INVALID, "attend_prefill: bad out_dtype");
+  if (n_seqs > 0 && (q_dev == nullptr || out_dev == nullptr)) return Fail(ctx, YAHKV_ERR_INVALID, "attend_prefill: null q or out pointer");
+  std::int64_t rows = 0;
+  HostError e = ctx->host.PlanPrefill(layer, n_seqs, seq_ids, chunk_lens, ctx->cfg.max_batch_tokens, &ctx->tile_scratch, &rows);
+  if (e.code != YAHKV_OK) return FailHost(ctx, std::move(e));
+  if (ctx->tile_scratch.empty()) return YAHKV_OK;
+  if (static_cast<int>(ctx->tile_scratch.size()) > ctx->max_tiles) return Fail(ctx, YAHKV_ERR_CAPACITY, "attend_prefill: too many tiles");
+  cudaStream_t st = StreamOf(ctx, stream);
+  if (int r = FlushTables(ctx, st); r != YAHKV_OK) return r;
+  if (int r = StagedUpload(ctx, ctx->tiles_dev, ctx->tile_scratch.data(), ctx->tile_scratch.size() * sizeof(PrefillTile), st); r != YAHKV_OK)
+    return r;
+  PrefillLaunch a{};
+  a.kmap = &ctx->kmap, a.vmap = &ctx->vmap, a.pool = ctx->pool, a.layer = layer;
+  a.tables_dev = ctx->tables_dev, a.table_stride = ctx->cfg.max_pages_per_seq;
+  a.tiles_dev = ctx->tiles_dev, a.n_tiles = static_cast<int>(ctx->tile_scratch.size());
+  a.q_dev = q_dev, a.gate_dev = gate_dev, a.out_dev = out_dev, a.out_f32 = out_dtype == YAHKV_OUT_F32;
+  a.scale_log2 = ctx->scale_log2, a.status_dev = ctx->status_dev;
+  YAHKV_CUDA(ctx, LaunchPrefill(a, st));
+  ctx->launches += 1;
+  return YAHKV_OK;
+}
+
+int yahkv_decode_step_host(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids, const void* k_host,
+                           const void* v_host, const void* q_host, const float* gate_host, void* out_host,
+                           int32_t out_dtype) {
+  if (int r = RequireDevice(ctx, "decode_step_host"); r != YAHKV_OK) return r;
+  if (n_seqs <= 0 || n_seqs > ctx->cfg.max_seqs) return Fail(ctx, YAHKV_ERR_INVALID, "decode_step_host: bad n_seqs");
+  if (seq_ids == nullptr || k_host == nullptr || v_host == nullptr || q_host == nullptr || out_host == nullptr)
+    return Fail(ctx, YAHKV_ERR_INVALID, "decode_step_host: null pointer");
+  if (layer < 0 || layer >= ctx->cfg.n_layers) return Fail(ctx, YAHKV_ERR_INVALID, "decode_step_host: layer out of range");
+  if (out_dtype != YAHKV_OUT_F16 && out_dtype != YAHKV_OUT_F32) return Fail(ctx, YAHKV_ERR_INVALID, "decode_step_host: bad out_dtype");
+  ctx->pos_scratch.resize(static_cast<std::size_t>(n_seqs));
+  for (int b = 0; b < n_seqs; ++b) {
+    if (!ctx->host.live(seq_ids[b])) return Fail(ctx, YAHKV_ERR_INVALID, "decode_step_host: not a live sequence");
+    const std::int64_t pos = ctx->host.len(seq_ids[b], layer);
+    ctx->pos_scratch[static_cast<std::size_t>(b)] = pos;
+    HostError e = ctx->host.SeqReserve(seq_ids[b], pos + 1);
+    if (e.code != YAHKV_OK) return FailHost(ctx, std::move(e));
+  }
+  cudaStream_t st = ctx->stream;
+  const std::size_t kvb = static_cast<std::size_t>(n_seqs) * kKvHeads * kHeadDim * 2;
+  const std::size_t qb = static_cast<std::size_t>(n_seqs) * kQHeads * kHeadDim * 2;
+  const std::size_t ob = static_cast<std::size_t>(n_seqs) * kQHeads * kHeadDim * (out_dtype == YAHKV_OUT_F32 ? 4 : 2);
+  YAHKV_CUDA(ctx, cudaMemcpyAsync(ctx->hs_k, k_host, kvb, cudaMemcpyHostToDevice, st));
+  YAHKV_CUDA(ctx, cudaMemcpyAsync(ctx->hs_v, v_host, kvb, cudaMemcpyHostToDevice, st));
+  YAHKV_CUDA(ctx, cudaMemcpyAsync(ctx->hs_q, q_host, qb, cudaMemcpyHostToDevice, st));
+  if (gate_host != nullptr)
+    YAHKV_CUDA(ctx, cudaMemcpyAsync(ctx->hs_gate, gate_host, static_cast<std::size_t>(n_seqs) * kQHeads * kHeadDim * 4,
+                                    cudaMemcpyHostToDevice, st));
+  if (int r = yahkv_append(ctx, layer, n_seqs, seq_ids, ctx->pos_scratch.data(), ctx->hs_k, ctx->hs_v, st); r != YAHKV_OK) return r;
+  if (int r = yahkv_attend_decode(ctx, layer, n_seqs, seq_ids, ctx->hs_q, gate_host != nullptr ? ctx->hs_gate : nullptr,
+                                  ctx->hs_out, out_dtype, 0, st);
+      r != YAHKV_OK)
+    return r;
+  YAHKV_CUDA(ctx, cudaMemcpyAsync(out_host, ctx->hs_out, ob, cudaMemcpyDeviceToHost, st));
+  YAHKV_CUDA(ctx, cudaStreamSynchronize(st));
+  return YAHKV_OK;
+}
+
+int yahkv_sync(yahkv_ctx* ctx) {
+  if (int r = RequireDevice(ctx, "sync"); r != YAHKV_OK) return r;
+  YAHKV_CUDA(ctx, cudaDeviceSynchronize());
+  return CheckStatus(ctx);
+}
+
+static int PageAccess(yahkv_ctx* ctx, int32_t layer, int32_t side, int32_t page, void* codes_host, void* scales_host,
+                      bool write) {
+  if (int r = RequireDevice(ctx, write ? "write_page" : "read_page"); r != YAHKV_OK) return r;
+  if (layer < 0 || layer >= ctx->cfg.n_layers || page < 0 || page >= ctx->cfg.num_pages ||
+      (side != YAHKV_SIDE_K && side != YAHKV_SIDE_V))
+    return Fail(ctx, YAHKV_ERR_INVALID, "page access: layer, side or page out of range");
+  YAHKV_CUDA(ctx, cudaDeviceSynchronize());
+  const std::size_t rec = (static_cast<std::size_t>(layer) * ctx->cfg.num_pages + page) * kKvHeads;
+  std::uint8_t* codes = (side == YAHKV_SIDE_K ? ctx->pool.kcodes : ctx->pool.vcodes) + rec * RecordCodeBytes(ctx->cfg.fmt);
+  std::uint16_t* scales = (side == YAHKV_SIDE_K ? ctx->pool.kscales : ctx->pool.vscales) + rec * kPageTokens * kBlocksPerRow;
+  const std::size_t cb = static_cast<std::size_t>(kKvHeads) * RecordCodeBytes(ctx->cfg.fmt);
+  const std::size_t sb = static_cast<std::size_t>(kKvHeads) * kRecordScaleBytes;
+  if (codes_host != nullptr)
+    YAHKV_CUDA(ctx, write ? cudaMemcpy(codes, codes_host, cb, cudaMemcpyHostToDevice)
+                          : cudaMemcpy(codes_host, codes, cb, cudaMemcpyDeviceToHost));
+  if (scales_host != nullptr)
+    YAHKV_CUDA(ctx, write ? cudaMemcpy(scales, scales_host, sb, cudaMemcpyHostToDevice)
+                          : cudaMemcpy(scales_host, scales, sb, cudaMemcpyDeviceToHost));
+  return YAHKV_OK;
+}
+
+int yahkv_read_page(yahkv_ctx* ctx, int32_t layer, int32_t side, int32_t page, void* codes_host, void* scales_host) {
+  return PageAccess(ctx, layer, side, page, codes_host, scales_host, false);
+}
+
+int yahkv_write_page(yahkv_ctx* ctx, int32_t layer, int32_t side, int32_t page, const void* codes_host,
+                     const void* scales_host) {
+  return PageAccess(ctx, layer, side, page, const_cast<void*>(codes_host), const_cast<void*>(scales_host), true);
+}
+
+int yahkv_export_token(yahkv_ctx* ctx, int32_t layer, int32_t seq, int64_t pos, void* k_blocks, void* v_blocks) {
+  if (int r = RequireDevice(ctx, "export_token"); r != YAHKV_OK) return r;
+  if (layer < 0 || layer >= ctx->cfg.n_layers) return Fail(ctx, YAHKV_ERR_INVALID, "export_token: layer out of range");
+  if (!ctx->host.live(seq)) return Fail(ctx, YAHKV_ERR_INVALID, "export_token: not a live sequence");
+  if (pos < 0 || pos >= static_cast<std::int64_t>(ctx->host.n_pages(seq)) * kPageTokens)
+    return Fail(ctx, YAHKV_ERR_INVALID, "export_token: position outside the reserved pages");
+  YAHKV_CUDA(ctx, cudaDeviceSynchronize());
+  const int page = ctx->host.table_row(seq)[pos / kPageTokens];
+  const int tok = static_cast<int>(pos % kPageTokens);
+  const int cbytes = CodeBytes(ctx->cfg.fmt), bcodes = cbytes / kBlocksPerRow;
+  for (int side = 0; side < 2; ++side) {
+    auto* dst = static_cast<std::uint8_t*>(side == 0 ? k_blocks : v_blocks);
+    if (dst == nullptr) continue;
+    for (int h = 0; h < kKvHeads; ++h) {
+      const std::size_t rec = (static_cast<std::size_t>(layer) * ctx->cfg.num_pages + page) * kKvHeads + h;
+      std::uint8_t codes[256];
+      std::uint16_t scales[kBlocksPerRow];
+      const std::uint8_t* cs = (side == 0 ? ctx->pool.kcodes : ctx->pool.vcodes) + rec * RecordCodeBytes(ctx->cfg.fmt) +
+                               static_cast<std::size_t>(tok) * cbytes;
+      const std::uint16_t* ss = (side == 0 ? ctx->pool.kscales : ctx->pool.vscales) + rec * kPageTokens * kBlocksPerRow +
+                                static_cast<std::size_t>(tok) * kBlocksPerRow;
+      YAHKV_CUDA(ctx, cudaMemcpy(codes, cs, static_cast<std::size_t>(cbytes), cudaMemcpyDeviceToHost));
+      YAHKV_CUDA(ctx, cudaMemcpy(scales, ss, sizeof(scales), cudaMemcpyDeviceToHost));
+      for (int b = 0; b < kBlocksPerRow; ++b) {
+        std::memcpy(dst, &scales[b], 2);
+        std::memcpy(dst + 2, codes + b * bcodes, static_cast<std::size_t>(bcodes));
+        dst += 2 + bcodes;
+      }
+    }
+  }
+  return YAHKV_OK;
+}
+
+int yahkv_device_bytes(const yahkv_ctx* ctx, int64_t* bytes) {
+  if (ctx == nullptr || bytes == nullptr) return YAHKV_ERR_INVALID;
+  *bytes = ctx->device_bytes;
+  return YAHKV_OK;
+}
+
+int yahkv_launch_count(const yahkv_ctx* ctx, int64_t* launches) {
+  if (ctx == nullptr || launches == nullptr) return YAHKV_ERR_INVALID;
+  *launches = ctx->launches;
+  return YAHKV_OK;
+}
+
+}  // extern "C"

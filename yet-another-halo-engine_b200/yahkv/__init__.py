@@ -1,0 +1,257 @@
+"""ctypes binding of libyahkv.so, the C ABI declared in include/yahkv.h.
+
+This is the Python face of the library for tests and benchmarks; the product is the shared library itself. There is
+no fallback of any kind: if libyahkv.so has not been built, importing this module raises, and hot-path calls on a
+context without a GPU return YAHKV_ERR_NO_DEVICE.
+
+`KvCache` mirrors the calls the reference engine makes on this path (engine/model/loom_decoder.hpp:254-268: append,
+then attend over keys 0..pos, then the merge with the sigmoid gate), batched over sequences.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_PKG_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB_PATH = os.path.join(_PKG_DIR, "libyahkv.so")
+INCLUDE_DIR = os.path.join(os.path.dirname(_PKG_DIR), "include")
+
+FMT_Q8_0, FMT_Q4_0 = 0, 1
+SIDE_K, SIDE_V = 0, 1
+OUT_F16, OUT_F32 = 0, 1
+OK = 0
+ERR_INVALID, ERR_NO_PAGES, ERR_CUDA, ERR_NO_DEVICE, ERR_ORDER, ERR_CAPACITY = -1, -2, -3, -4, -5, -6
+
+Q_HEADS, KV_HEADS, HEAD_DIM, PAGE_TOKENS, BLOCKS = 24, 4, 256, 64, 8
+
+
+def code_bytes(fmt):
+    return 256 if fmt == FMT_Q8_0 else 128
+
+
+def bytes_per_token(fmt):
+    """K + V bytes one cached token takes in one layer (codes + fp16 scales, all 4 kv heads)."""
+    return 2 * KV_HEADS * (code_bytes(fmt) + BLOCKS * 2)
+
+
+class Config(ctypes.Structure):
+    _fields_ = [
+        ("device", ctypes.c_int32),
+        ("n_layers", ctypes.c_int32),
+        ("n_q_heads", ctypes.c_int32),
+        ("n_kv_heads", ctypes.c_int32),
+        ("head_dim", ctypes.c_int32),
+        ("page_tokens", ctypes.c_int32),
+        ("num_pages", ctypes.c_int32),
+        ("fmt", ctypes.c_int32),
+        ("max_seqs", ctypes.c_int32),
+        ("max_pages_per_seq", ctypes.c_int32),
+        ("max_splits", ctypes.c_int32),
+        ("max_batch_tokens", ctypes.c_int32),
+        ("softmax_scale", ctypes.c_float),
+    ]
+
+
+class YahkvError(RuntimeError):
+    def __init__(self, code, message):
+        super().__init__(f"{code} ({_error_name(code)}): {message}")
+        self.code = code
+        self.message = message
+
+
+def build(verbose=False):
+    """Compile libyahkv.so for sm_100a in the package directory (nvcc cross-compiles without a GPU)."""
+    r = subprocess.run(["make", "-C", _PKG_DIR, "-j4"], capture_output=True, text=True)
+    if verbose or r.returncode:
+        print(r.stdout[-4000:], r.stderr[-4000:])
+    if r.returncode:
+        raise RuntimeError("building libyahkv.so failed")
+
+
+_c = ctypes
+_VP, _I32, _I64 = _c.c_void_p, _c.c_int32, _c.c_int64
+_PI32, _PI64 = _c.POINTER(_c.c_int32), _c.POINTER(_c.c_int64)
+
+# name -> (restype, argtypes): every entry point include/yahkv.h declares.
+SIGNATURES = {
+    "yahkv_create": (_I32, [_c.POINTER(Config), _c.POINTER(_VP)]),
+    "yahkv_destroy": (None, [_VP]),
+    "yahkv_last_error": (_c.c_char_p, [_VP]),
+    "yahkv_error_name": (_c.c_char_p, [_I32]),
+    "yahkv_seq_create": (_I32, [_VP, _PI32]),
+    "yahkv_seq_free": (_I32, [_VP, _I32]),
+    "yahkv_seq_reserve": (_I32, [_VP, _I32, _I64]),
+    "yahkv_seq_set_table": (_I32, [_VP, _I32, _VP, _I32]),
+    "yahkv_seq_table": (_I32, [_VP, _I32, _c.POINTER(_PI32), _PI32]),
+    "yahkv_seq_len": (_I32, [_VP, _I32, _I32, _PI64]),
+    "yahkv_seq_set_len": (_I32, [_VP, _I32, _I32, _I64]),
+    "yahkv_pages_free": (_I32, [_VP, _PI32]),
+    "yahkv_append": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _VP]),
+    "yahkv_append_slots": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP]),
+    "yahkv_attend_decode": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _I32, _I32, _VP]),
+    "yahkv_attend_prefill": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _VP, _I32, _VP]),
+    "yahkv_decode_step_host": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _VP, _VP, _I32]),
+    "yahkv_read_page": (_I32, [_VP, _I32, _I32, _I32, _VP, _VP]),
+    "yahkv_write_page": (_I32, [_VP, _I32, _I32, _I32, _VP, _VP]),
+    "yahkv_export_token": (_I32, [_VP, _I32, _I32, _I64, _VP, _VP]),
+    "yahkv_sync": (_I32, [_VP]),
+    "yahkv_device_bytes": (_I32, [_VP, _PI64]),
+    "yahkv_launch_count": (_I32, [_VP, _PI64]),
+}
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(f"{LIB_PATH} is missing: build it first (make -C {_PKG_DIR}); there is no fallback path")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
+    return lib
+
+
+lib = _load()
+
+
+def _error_name(code):
+    return lib.yahkv_error_name(code).decode()
+
+
+def _ptr(x):
+    """Device or host address of a tensor / array / int / None as a c_void_p."""
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return ctypes.c_void_p(x)
+    if isinstance(x, np.ndarray):
+        return x.ctypes.data_as(ctypes.c_void_p)
+    if hasattr(x, "data_ptr"):  # torch tensor
+        return ctypes.c_void_p(x.data_ptr())
+    raise TypeError(f"cannot take the address of {type(x)}")
+
+
+def _i32(a):
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+class KvCache:
+    """One context = one GPU's pools, block tables and allocator (yahkv_ctx)."""
+
+    def __init__(self, *, device=0, n_layers=1, num_pages=64, fmt=FMT_Q8_0, max_seqs=8, max_pages_per_seq=64,
+                 max_splits=0, max_batch_tokens=0, softmax_scale=0.0, n_q_heads=Q_HEADS, n_kv_heads=KV_HEADS,
+                 head_dim=HEAD_DIM, page_tokens=PAGE_TOKENS):
+        self.cfg = Config(device, n_layers, n_q_heads, n_kv_heads, head_dim, page_tokens, num_pages, fmt, max_seqs,
+                          max_pages_per_seq, max_splits, max_batch_tokens, softmax_scale)
+        self.fmt = fmt
+        self._h = ctypes.c_void_p()
+        rc = lib.yahkv_create(ctypes.byref(self.cfg), ctypes.byref(self._h))
+        if rc != OK:
+            raise YahkvError(rc, lib.yahkv_last_error(None).decode())
+
+    def close(self):
+        if self._h:
+            lib.yahkv_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc):
+        if rc != OK:
+            raise YahkvError(rc, lib.yahkv_last_error(self._h).decode())
+
+    # ---- allocator / tables ----
+    def seq_create(self):
+        s = ctypes.c_int32(-1)
+        self._check(lib.yahkv_seq_create(self._h, ctypes.byref(s)))
+        return s.value
+
+    def seq_free(self, seq):
+        self._check(lib.yahkv_seq_free(self._h, seq))
+
+    def seq_reserve(self, seq, n_tokens):
+        self._check(lib.yahkv_seq_reserve(self._h, seq, n_tokens))
+
+    def seq_set_table(self, seq, pages):
+        pages = _i32(pages)
+        self._check(lib.yahkv_seq_set_table(self._h, seq, _ptr(pages), len(pages)))
+
+    def seq_table(self, seq):
+        p, n = _PI32(), ctypes.c_int32()
+        self._check(lib.yahkv_seq_table(self._h, seq, ctypes.byref(p), ctypes.byref(n)))
+        return np.ctypeslib.as_array(p, shape=(n.value,)).copy() if n.value else np.zeros(0, np.int32)
+
+    def seq_len(self, seq, layer=0):
+        n = ctypes.c_int64()
+        self._check(lib.yahkv_seq_len(self._h, seq, layer, ctypes.byref(n)))
+        return n.value
+
+    def seq_set_len(self, seq, length, layer=-1):
+        self._check(lib.yahkv_seq_set_len(self._h, seq, layer, length))
+
+    def pages_free(self):
+        n = ctypes.c_int32()
+        self._check(lib.yahkv_pages_free(self._h, ctypes.byref(n)))
+        return n.value
+
+    # ---- hot path ----
+    def append(self, layer, seq_ids, positions, k, v, stream=None):
+        seq_ids = _i32(seq_ids)
+        positions = np.ascontiguousarray(positions, dtype=np.int64)
+        assert len(seq_ids) == len(positions)
+        self._check(lib.yahkv_append(self._h, layer, len(seq_ids), _ptr(seq_ids), _ptr(positions), _ptr(k), _ptr(v),
+                                     _ptr(stream)))
+
+    def append_slots(self, layer, n_tokens, slot_mapping, k, v, stream=None):
+        self._check(lib.yahkv_append_slots(self._h, layer, n_tokens, _ptr(slot_mapping), _ptr(k), _ptr(v),
+                                           _ptr(stream)))
+
+    def attend_decode(self, layer, seq_ids, q, out, gate=None, out_dtype=OUT_F16, n_splits=0, stream=None):
+        seq_ids = _i32(seq_ids)
+        self._check(lib.yahkv_attend_decode(self._h, layer, len(seq_ids), _ptr(seq_ids), _ptr(q), _ptr(gate),
+                                            _ptr(out), out_dtype, n_splits, _ptr(stream)))
+
+    def attend_prefill(self, layer, seq_ids, chunk_lens, q, out, gate=None, out_dtype=OUT_F16, stream=None):
+        seq_ids, chunk_lens = _i32(seq_ids), _i32(chunk_lens)
+        self._check(lib.yahkv_attend_prefill(self._h, layer, len(seq_ids), _ptr(seq_ids), _ptr(chunk_lens), _ptr(q),
+                                             _ptr(gate), _ptr(out), out_dtype, _ptr(stream)))
+
+    def decode_step_host(self, layer, seq_ids, k, v, q, out, gate=None, out_dtype=OUT_F16):
+        seq_ids = _i32(seq_ids)
+        self._check(lib.yahkv_decode_step_host(self._h, layer, len(seq_ids), _ptr(seq_ids), _ptr(k), _ptr(v), _ptr(q),
+                                               _ptr(gate), _ptr(out), out_dtype))
+
+    # ---- inspection ----
+    def read_page(self, layer, side, page):
+        codes = np.zeros((KV_HEADS, PAGE_TOKENS, code_bytes(self.fmt)), np.uint8)
+        scales = np.zeros((KV_HEADS, PAGE_TOKENS, BLOCKS), np.uint16)
+        self._check(lib.yahkv_read_page(self._h, layer, side, page, _ptr(codes), _ptr(scales)))
+        return codes, scales
+
+    def write_page(self, layer, side, page, codes, scales):
+        codes = np.ascontiguousarray(codes, dtype=np.uint8)
+        scales = np.ascontiguousarray(scales, dtype=np.uint16)
+        self._check(lib.yahkv_write_page(self._h, layer, side, page, _ptr(codes), _ptr(scales)))
+
+    def export_token(self, layer, seq, pos):
+        nb = KV_HEADS * BLOCKS * (2 + code_bytes(self.fmt) // BLOCKS)
+        k, v = np.zeros(nb, np.uint8), np.zeros(nb, np.uint8)
+        self._check(lib.yahkv_export_token(self._h, layer, seq, pos, _ptr(k), _ptr(v)))
+        return k, v
+
+    def sync(self):
+        self._check(lib.yahkv_sync(self._h))
+
+    def device_bytes(self):
+        n = ctypes.c_int64()
+        self._check(lib.yahkv_device_bytes(self._h, ctypes.byref(n)))
+        return n.value
+
+    def launch_count(self):
+        n = ctypes.c_int64()
+        self._check(lib.yahkv_launch_count(self._h, ctypes.byref(n)))
+        return n.value
