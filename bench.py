@@ -1,0 +1,324 @@
+#!/usr/bin/env python3
+"""Benchmark of the paged quantized KV-cache hot path on B200.
+
+Workload (the batch-decode configuration): 32 sequences per GPU, 16 full-attention layers, 24 query / 4 KV heads of
+dim 256, q8_0 cache in 64-token pages, per-sequence context lengths uniform in [1024, 32768] (seed 0), pages drawn from
+one shuffled pool so block tables are non-contiguous, fp16 K/V/q ~ N(0,1). One step = for each layer: append one new
+token per sequence, then decode-attend over the whole context. Data is synthetic.
+
+  value        KV GB/s: algorithmic cache bytes attended (sum of context lengths x 2176 B x layers) / device time of
+               the K timed steps, inputs resident in HBM, whole job over all GPUs (weak scaling: 32 sequences per GPU).
+  e2e          the same metric through yahkv_decode_step_host: per layer the step's K/V/q come from pinned HOST
+               memory and the attention output is read back to the host inside the timed region.
+  roofline     the split-K attention kernel alone: algorithmic bytes per launch / its mean device time, from CUDA
+               event pairs the library records around every launch inside the timed region.
+  cpu_baseline the CPU oracle (a port: the reference has no CPU attention) on a bounded sample of the same workload.
+
+`--impl reference` times the CPU arm alone: the reference project's CPU code for this path is its block codec
+(QuantizeQ8_0, compiled from its sources into oracle/_ref when available) plus, for attention, the oracle port that
+restates its numpy checker; all host threads, bounded sample.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (os.path.join(ROOT, "yet-another-halo-engine_b200"), os.path.join(ROOT, "oracle")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+LAYERS, BATCH, CTX_LO, CTX_HI = 16, 32, 1024, 32768
+METRIC, UNIT = "q8_0_paged_decode_attn_kv_gbps", "GB/s"
+
+
+def workload(rank, layers):
+    rng = np.random.default_rng(rank)          # rank 0 = seed 0, the single-GPU configuration
+    lens = rng.integers(CTX_LO, CTX_HI + 1, BATCH)
+    return {"rng": rng, "lens": lens, "layers": layers}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms",
+                                       "200", "-i", str(gpu_index)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        self.p.wait()
+        self.f.flush()
+        rows = [r.split(", ") for r in open(self.f.name).read().strip().splitlines() if r.strip()]
+        os.unlink(self.f.name)
+        sm = [float(r[1]) for r in rows if len(r) >= 9]
+        reasons = set()
+        for r in rows:
+            if len(r) < 9:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.strip().lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": float(rows[0][2]) if rows and len(rows[0]) >= 3 else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_arm(layers_sample=1, seqs_sample=8, reps=2):
+    """CPU timing of the same workload on a bounded sample: `seqs_sample` sequences of the seed-0 batch, one layer.
+    Returns (attention GB/s, append Mtok/s, threads, description)."""
+    import oracle as O
+    w = workload(0, 1)
+    rng, lens = w["rng"], w["lens"][:seqs_sample]
+    pages = [(int(n) + 64) // 64 + 1 for n in lens]
+    num_pages = sum(pages)
+    perm = rng.permutation(num_pages).astype(np.int32)
+    pool = O.PagedPool(O.FMT_Q8_0, num_pages)
+    stride = max(pages)
+    tables = np.zeros((len(lens), stride), np.int32)
+    off = 0
+    t_append, n_append = 0.0, 0
+    for i, n in enumerate(lens):
+        tables[i, :pages[i]] = perm[off:off + pages[i]]
+        off += pages[i]
+        K = rng.standard_normal((int(n), 4, 256), dtype=np.float32).astype(np.float16)
+        V = rng.standard_normal((int(n), 4, 256), dtype=np.float32).astype(np.float16)
+        t0 = time.perf_counter()
+        pool.append(tables[i, :pages[i]], 0, K, V)      # the reference's QuantizeQ8_0 arithmetic + paged scatter
+        t_append += time.perf_counter() - t0
+        n_append += int(n)
+    q = rng.standard_normal((len(lens), 24, 256), dtype=np.float32).astype(np.float16)
+    best = float("inf")
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        pool.attend_decode_f32(tables, lens.astype(np.int32), q)
+        best = min(best, time.perf_counter() - t0)
+    gbs = float(lens.sum()) * 2176 / best / 1e9
+    return gbs, n_append / t_append / 1e6, O.THREADS, (
+        f"{seqs_sample} of {BATCH} sequences ({int(lens.sum())} cached tokens), 1 of {LAYERS} layers, best of {reps}")
+
+
+def reference_arm(args, rank):
+    if rank != 0:
+        return
+    t0 = time.perf_counter()
+    vals = []
+    for _ in range(max(1, min(args.steps, 3))):
+        gbs, mtok, threads, sample = cpu_arm(reps=1)
+        vals.append(gbs)
+    gbs = float(np.median(vals))
+    import oracle as O
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u8", "data": "synthetic",
+        "config": {"workload": "batch32_decode_16layers_q8_0_ctx1024-32768_page64", "note":
+                   "CPU arm; the reference has no CPU attention, so attention is the oracle port of its numpy checker "
+                   "and append is its QuantizeQ8_0 arithmetic"},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample,
+                         "append_mtok_s": mtok, "ref_codec_built": O.have_ref()},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.perf_counter() - t0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="yahkv", choices=["yahkv", "reference"])
+    ap.add_argument("--layers", type=int, default=LAYERS, help="layers per step (16 = the configuration)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        reference_arm(args, rank)
+        return
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import torch.distributed as dist
+    import yahkv
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    w = workload(rank, args.layers)
+    rng, lens, layers = w["rng"], w["lens"].copy(), w["layers"]
+    total_steps = args.warmup + args.steps
+    e2e_steps = 0 if args.no_e2e else min(args.steps, 4) + 1
+    grow = total_steps + e2e_steps + 2
+    pages = [(int(n) + grow + 63) // 64 for n in lens]
+    num_pages = sum(pages) + 64
+    cache = yahkv.KvCache(device=local_rank, n_layers=layers, num_pages=num_pages, fmt=yahkv.FMT_Q8_0,
+                          max_seqs=BATCH, max_pages_per_seq=max(pages) + 1, max_batch_tokens=8192)
+    perm = rng.permutation(num_pages).astype(np.int32)
+    seqs, off = [], 0
+    stream = torch.cuda.current_stream()
+    sptr = stream.cuda_stream
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    for i, n in enumerate(lens):
+        s = cache.seq_create()
+        cache.seq_set_table(s, perm[off:off + pages[i]])
+        off += pages[i]
+        seqs.append(s)
+        for c0 in range(0, int(n), 8192):
+            c1 = min(int(n), c0 + 8192)
+            K = torch.randn(c1 - c0, 4, 256, device="cuda", generator=gen).half()
+            V = torch.randn(c1 - c0, 4, 256, device="cuda", generator=gen).half()
+            ids, pos = np.full(c1 - c0, s, np.int32), np.arange(c0, c1, dtype=np.int64)
+            for layer in range(layers):
+                cache.append(layer, ids, pos, K, V, stream=sptr)
+    cache.sync()
+
+    seq_ids = np.array(seqs, np.int32)
+    k_new = torch.randn(layers, BATCH, 4, 256, device="cuda", generator=gen).half()
+    v_new = torch.randn(layers, BATCH, 4, 256, device="cuda", generator=gen).half()
+    q = torch.randn(layers, BATCH, 24, 256, device="cuda", generator=gen).half()
+    out = torch.zeros(layers, BATCH, 24, 256, device="cuda", dtype=torch.float16)
+
+    def step():
+        pos = np.array([cache.seq_len(s, 0) for s in seqs], np.int64)
+        for layer in range(layers):
+            cache.append(layer, seq_ids, pos, k_new[layer], v_new[layer], stream=sptr)
+            cache.attend_decode(layer, seq_ids, q[layer], out[layer], stream=sptr)
+        return int(pos.sum()) + BATCH            # keys attended per layer in this step
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    cache.kernel_timing(True)
+    launches0 = cache.launch_count()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record(stream)
+    keys = 0
+    for _ in range(args.steps):
+        keys += step()
+    ev1.record(stream)
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop() if sampler else None
+    launches = cache.launch_count() - launches0
+    part_ms, part_n = cache.kernel_timing_read(yahkv.KERNEL_DECODE_PART)
+    comb_ms, comb_n = cache.kernel_timing_read(yahkv.KERNEL_DECODE_COMBINE)
+    app_ms, app_n = cache.kernel_timing_read(yahkv.KERNEL_APPEND)
+    cache.kernel_timing(False)
+    bytes_attended = keys * layers * yahkv.bytes_per_token(yahkv.FMT_Q8_0)
+
+    # ---- end to end through the host-buffer entry point ----
+    e2e = None
+    if not args.no_e2e:
+        hk = k_new.cpu().pin_memory()
+        hv = v_new.cpu().pin_memory()
+        hq = q.cpu().pin_memory()
+        hout = torch.zeros(layers, BATCH, 24, 256, dtype=torch.float16).pin_memory()
+
+        def host_step():
+            n = sum(cache.seq_len(s, 0) for s in seqs) + BATCH
+            for layer in range(layers):
+                cache.decode_step_host(layer, seq_ids, hk[layer], hv[layer], hq[layer], hout[layer])
+            return n
+        host_step()
+        barrier()
+        t0 = time.perf_counter()
+        e_keys = 0
+        for _ in range(e2e_steps - 1):
+            e_keys += host_step()
+        torch.cuda.synchronize()
+        e_s = time.perf_counter() - t0
+        e_bytes = e_keys * layers * yahkv.bytes_per_token(yahkv.FMT_Q8_0)
+        e2e = {"bytes": e_bytes, "s": e_s,
+               "h2d": layers * BATCH * (2 * 4 * 256 * 2 + 24 * 256 * 2), "d2h": layers * BATCH * 24 * 256 * 2}
+
+    # ---- aggregate over ranks: bytes summed, time = max ----
+    stats = torch.tensor([ms, bytes_attended, e2e["s"] if e2e else 0.0, e2e["bytes"] if e2e else 0.0,
+                          part_ms / max(part_n, 1)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms, bytes_all, e_s, e_bytes_all = mx[0].item(), sm[1].item(), mx[2].item(), sm[3].item()
+    else:
+        bytes_all, e_s, e_bytes_all = bytes_attended, stats[2].item(), stats[3].item()
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        part_bytes = bytes_attended / max(part_n, 1)
+        part_mean_ms = part_ms / max(part_n, 1)
+        achieved = part_bytes / (part_mean_ms * 1e-3) / 1e9 if part_n else 0.0
+        line = {
+            "metric": METRIC, "value": bytes_all / (ms * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+            "config": {"workload": f"batch32_decode_{layers}layers_q8_0_ctx1024-32768_page64", "seqs_per_gpu": BATCH,
+                       "layers": layers, "mean_ctx": float(lens.mean()), "pages_shuffled": True,
+                       "l2": "inputs larger than L2: each layer reads its own ~1.2 GB of cache per step",
+                       "sharding": "sequences partitioned across GPUs, no collective on the data path"},
+            "extra": {"append_mtok_s": (app_n * BATCH) / (app_ms * 1e-3) / 1e6 if app_n else None,
+                      "append_us_per_launch": app_ms / max(app_n, 1) * 1e3,
+                      "batch_decode_tok_s": world * BATCH * args.steps / (ms * 1e-3),
+                      "batch_decode_note": "attention + append of 16 layers only; the rest of the model is out of scope",
+                      "combine_us_per_launch": comb_ms / max(comb_n, 1) * 1e3,
+                      "frac_of_nominal_8000": bytes_all / (ms * 1e-3) / 1e9 / world / 8000.0,
+                      "device_bytes": cache.device_bytes()},
+            "roofline": {"kernel": "DecodePartKernel<q8_0>", "bound": "hbm", "achieved": achieved, "peak": peak,
+                         "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
+                         "launches": part_n, "mean_us": part_mean_ms * 1e3, "traffic": None},
+            "gpu_launches": launches, "clocks": clocks,
+        }
+        if e2e:
+            line["e2e"] = {"value": e_bytes_all / e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"],
+                           "d2h_bytes_per_step": e2e["d2h"], "steps": e2e_steps - 1,
+                           "api": "yahkv_decode_step_host per layer (pinned host K/V/q in, output back to host)"}
+        traffic_path = os.path.join(ROOT, "profiles", "decode_part_q8_0_traffic.json")
+        if os.path.exists(traffic_path):
+            t = json.load(open(traffic_path))
+            line["roofline"]["traffic"] = t["dram_bytes_per_algorithmic_byte"] * part_bytes
+            line["roofline"]["traffic_note"] = t["note"]
+        if world == 1 and not args.no_cpu:
+            gbs, mtok, threads, sample = cpu_arm()
+            line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample,
+                                    "append_mtok_s": mtok}
+        print(json.dumps(line))
+    cache.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

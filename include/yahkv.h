@@ -142,7 +142,17 @@ int yahkv_sync(yahkv_ctx* ctx);
 /* Bytes of device memory the context holds, and kernels it has launched since creation (for benchmarks). */
 int yahkv_device_bytes(const yahkv_ctx* ctx, int64_t* bytes);
 int yahkv_launch_count(const yahkv_ctx* ctx, int64_t* launches);
-/* Device time of the last yahkv_attend_decode's kernels is not measured here: callers time with events on `stream`. */
+
+/* Per-kernel device time for benchmarks: while enabled, every launch is bracketed by a CUDA event pair on its own
+ * stream (the reference's counterpart is its per-dispatch timer, engine/run/hal_run.cc:124-135). Enabling or
+ * disabling clears the record. _read waits for the device and sums the pairs of one kernel. */
+#define YAHKV_KERNEL_APPEND 0
+#define YAHKV_KERNEL_DECODE_PART 1
+#define YAHKV_KERNEL_DECODE_COMBINE 2
+#define YAHKV_KERNEL_PREFILL 3
+#define YAHKV_KERNEL_COUNT 4
+int yahkv_kernel_timing(yahkv_ctx* ctx, int32_t enable);
+int yahkv_kernel_timing_read(yahkv_ctx* ctx, int32_t kernel, double* total_ms, int64_t* launches);
 
 #ifdef __cplusplus
 }

@@ -448,7 +448,7 @@ cudaError_t ConfigureDecodeKernels() {
                               DecodeSmemBytes<kFmtQ4>());
 }
 
-cudaError_t LaunchDecode(const DecodeLaunch& a, cudaStream_t stream) {
+cudaError_t LaunchDecodePart(const DecodeLaunch& a, cudaStream_t stream) {
   if (a.n_units <= 0 || a.n_seqs <= 0) return cudaSuccess;
   const auto* q = static_cast<const __half*>(a.q_dev);
   if (a.pool.fmt == kFmtQ8)
@@ -459,8 +459,11 @@ cudaError_t LaunchDecode(const DecodeLaunch& a, cudaStream_t stream) {
     DecodePartKernel<kFmtQ4><<<a.n_units, kDecodeThreads, DecodeSmemBytes<kFmtQ4>(), stream>>>(
         *a.kmap, *a.vmap, a.pool, a.layer, a.tables_dev, a.table_stride, a.units_dev, q, a.scale_log2, a.partial_acc,
         a.partial_ml, a.status_dev);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
+  return cudaGetLastError();
+}
+
+cudaError_t LaunchDecodeCombine(const DecodeLaunch& a, cudaStream_t stream) {
+  if (a.n_units <= 0 || a.n_seqs <= 0) return cudaSuccess;
   DecodeCombineKernel<<<a.n_seqs * kQHeads, kHeadDim / 2, 0, stream>>>(a.items_dev, a.partial_acc, a.partial_ml,
                                                                       a.gate_dev, a.out_dev, a.out_f32);
   return cudaGetLastError();

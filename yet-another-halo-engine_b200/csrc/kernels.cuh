@@ -90,7 +90,8 @@ struct DecodeLaunch {
   float* partial_ml;
   int* status_dev;          // sticky error word, 0 = ok
 };
-cudaError_t LaunchDecode(const DecodeLaunch& a, cudaStream_t stream);
+cudaError_t LaunchDecodePart(const DecodeLaunch& a, cudaStream_t stream);
+cudaError_t LaunchDecodeCombine(const DecodeLaunch& a, cudaStream_t stream);
 // Shared-memory bytes the decode kernel asks for (for the one-time attribute set-up).
 cudaError_t ConfigureDecodeKernels();
 

@@ -107,6 +107,10 @@ struct yahkv_ctx {
   float* hs_gate = nullptr;
   std::int64_t launches = 0;
   std::int64_t device_bytes = 0;
+  // optional per-kernel timing: event pairs around each launch, summed on read
+  bool timing = false;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timing_events[YAHKV_KERNEL_COUNT];
+  std::vector<cudaEvent_t> event_pool;
   std::vector<std::int64_t> slot_scratch;
   std::vector<std::int64_t> pos_scratch;
   std::vector<PrefillTile> tile_scratch;
@@ -215,7 +219,37 @@ void FreeDevice(yahkv_ctx* ctx) {
   for (void* p : ptrs)
     if (p != nullptr) cudaFree(p);
   if (ctx->stream != nullptr) cudaStreamDestroy(ctx->stream);
+  for (auto& list : ctx->timing_events)
+    for (auto& pr : list) cudaEventDestroy(pr.first), cudaEventDestroy(pr.second);
+  for (cudaEvent_t e : ctx->event_pool) cudaEventDestroy(e);
 }
+
+// Event pair around one kernel launch while timing is on: Begin before the launch, End right after it.
+struct TimedLaunch {
+  TimedLaunch(yahkv_ctx* c, int kernel, cudaStream_t st) : ctx(c), id(kernel), stream(st) {
+    if (!ctx->timing) return;
+    a = Take(), b = Take();
+    if (a != nullptr && b != nullptr) cudaEventRecord(a, stream);
+  }
+  void End() {
+    if (!ctx->timing || a == nullptr || b == nullptr) return;
+    cudaEventRecord(b, stream);
+    ctx->timing_events[id].emplace_back(a, b);
+  }
+  cudaEvent_t Take() {
+    if (!ctx->event_pool.empty()) {
+      cudaEvent_t e = ctx->event_pool.back();
+      ctx->event_pool.pop_back();
+      return e;
+    }
+    cudaEvent_t e = nullptr;
+    return cudaEventCreate(&e) == cudaSuccess ? e : nullptr;
+  }
+  yahkv_ctx* ctx;
+  int id;
+  cudaStream_t stream;
+  cudaEvent_t a = nullptr, b = nullptr;
+};
 
 cudaStream_t StreamOf(yahkv_ctx* ctx, void* stream) {
   return stream != nullptr ? static_cast<cudaStream_t>(stream) : ctx->stream;
@@ -404,7 +438,9 @@ int yahkv_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int32_t*
   if (int r = FlushTables(ctx, st); r != YAHKV_OK) return r;
   if (int r = StagedUpload(ctx, ctx->slots_dev, ctx->slot_scratch.data(), static_cast<std::size_t>(n_tokens) * 8, st); r != YAHKV_OK)
     return r;
+  TimedLaunch tl(ctx, YAHKV_KERNEL_APPEND, st);
   YAHKV_CUDA(ctx, LaunchAppend(ctx->pool, layer, n_tokens, ctx->slots_dev, k_dev, v_dev, st));
+  tl.End();
   ctx->launches += 1;
   return YAHKV_OK;
 }
@@ -419,7 +455,9 @@ int yahkv_append_slots(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const in
     return Fail(ctx, YAHKV_ERR_INVALID, "append_slots: null pointer");
   cudaStream_t st = StreamOf(ctx, stream);
   if (int r = FlushTables(ctx, st); r != YAHKV_OK) return r;
+  TimedLaunch tl(ctx, YAHKV_KERNEL_APPEND, st);
   YAHKV_CUDA(ctx, LaunchAppend(ctx->pool, layer, n_tokens, slot_mapping_dev, k_dev, v_dev, st));
+  tl.End();
   ctx->launches += 1;
   return YAHKV_OK;
 }
@@ -456,7 +494,14 @@ int yahkv_attend_decode(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int
   a.q_dev = q_dev, a.gate_dev = gate_dev, a.out_dev = out_dev, a.out_f32 = out_dtype == YAHKV_OUT_F32;
   a.scale_log2 = ctx->scale_log2;
   a.partial_acc = ctx->partial_acc, a.partial_ml = ctx->partial_ml, a.status_dev = ctx->status_dev;
-  const cudaError_t le = LaunchDecode(a, st);
+  TimedLaunch tp(ctx, YAHKV_KERNEL_DECODE_PART, st);
+  cudaError_t le = LaunchDecodePart(a, st);
+  tp.End();
+  if (le == cudaSuccess) {
+    TimedLaunch tc(ctx, YAHKV_KERNEL_DECODE_COMBINE, st);
+    le = LaunchDecodeCombine(a, st);
+    tc.End();
+  }
   if (le != cudaSuccess) {
     ctx->host.InvalidateDecodePlan();
     return FailCuda(ctx, "decode attention launch", le);
@@ -486,7 +531,9 @@ int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const in
   a.tiles_dev = ctx->tiles_dev, a.n_tiles = static_cast<int>(ctx->tile_scratch.size());
   a.q_dev = q_dev, a.gate_dev = gate_dev, a.out_dev = out_dev, a.out_f32 = out_dtype == YAHKV_OUT_F32;
   a.scale_log2 = ctx->scale_log2, a.status_dev = ctx->status_dev;
+  TimedLaunch tl(ctx, YAHKV_KERNEL_PREFILL, st);
   YAHKV_CUDA(ctx, LaunchPrefill(a, st));
+  tl.End();
   ctx->launches += 1;
   return YAHKV_OK;
 }
@@ -594,6 +641,33 @@ int yahkv_export_token(yahkv_ctx* ctx, int32_t layer, int32_t seq, int64_t pos, 
       }
     }
   }
+  return YAHKV_OK;
+}
+
+int yahkv_kernel_timing(yahkv_ctx* ctx, int32_t enable) {
+  if (int r = RequireDevice(ctx, "kernel_timing"); r != YAHKV_OK) return r;
+  YAHKV_CUDA(ctx, cudaDeviceSynchronize());
+  for (auto& list : ctx->timing_events) {
+    for (auto& pr : list) ctx->event_pool.push_back(pr.first), ctx->event_pool.push_back(pr.second);
+    list.clear();
+  }
+  ctx->timing = enable != 0;
+  return YAHKV_OK;
+}
+
+int yahkv_kernel_timing_read(yahkv_ctx* ctx, int32_t kernel, double* total_ms, int64_t* launches) {
+  if (int r = RequireDevice(ctx, "kernel_timing_read"); r != YAHKV_OK) return r;
+  if (kernel < 0 || kernel >= YAHKV_KERNEL_COUNT || total_ms == nullptr || launches == nullptr)
+    return Fail(ctx, YAHKV_ERR_INVALID, "kernel_timing_read: bad kernel id or null pointer");
+  YAHKV_CUDA(ctx, cudaDeviceSynchronize());
+  double sum = 0;
+  for (auto& pr : ctx->timing_events[kernel]) {
+    float ms = 0;
+    YAHKV_CUDA(ctx, cudaEventElapsedTime(&ms, pr.first, pr.second));
+    sum += ms;
+  }
+  *total_ms = sum;
+  *launches = static_cast<std::int64_t>(ctx->timing_events[kernel].size());
   return YAHKV_OK;
 }
 

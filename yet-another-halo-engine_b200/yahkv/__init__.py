@@ -20,6 +20,7 @@ INCLUDE_DIR = os.path.join(os.path.dirname(_PKG_DIR), "include")
 FMT_Q8_0, FMT_Q4_0 = 0, 1
 SIDE_K, SIDE_V = 0, 1
 OUT_F16, OUT_F32 = 0, 1
+KERNEL_APPEND, KERNEL_DECODE_PART, KERNEL_DECODE_COMBINE, KERNEL_PREFILL = 0, 1, 2, 3
 OK = 0
 ERR_INVALID, ERR_NO_PAGES, ERR_CUDA, ERR_NO_DEVICE, ERR_ORDER, ERR_CAPACITY = -1, -2, -3, -4, -5, -6
 
@@ -98,6 +99,8 @@ SIGNATURES = {
     "yahkv_sync": (_I32, [_VP]),
     "yahkv_device_bytes": (_I32, [_VP, _PI64]),
     "yahkv_launch_count": (_I32, [_VP, _PI64]),
+    "yahkv_kernel_timing": (_I32, [_VP, _I32]),
+    "yahkv_kernel_timing_read": (_I32, [_VP, _I32, _c.POINTER(_c.c_double), _PI64]),
 }
 
 
@@ -250,6 +253,15 @@ class KvCache:
         n = ctypes.c_int64()
         self._check(lib.yahkv_device_bytes(self._h, ctypes.byref(n)))
         return n.value
+
+    def kernel_timing(self, enable):
+        self._check(lib.yahkv_kernel_timing(self._h, 1 if enable else 0))
+
+    def kernel_timing_read(self, kernel):
+        """(total device milliseconds, launches) of one kernel since timing was enabled."""
+        ms, n = ctypes.c_double(), ctypes.c_int64()
+        self._check(lib.yahkv_kernel_timing_read(self._h, kernel, ctypes.byref(ms), ctypes.byref(n)))
+        return ms.value, n.value
 
     def launch_count(self):
         n = ctypes.c_int64()
