@@ -154,6 +154,50 @@ int yahkv_launch_count(const yahkv_ctx* ctx, int64_t* launches);
 int yahkv_kernel_timing(yahkv_ctx* ctx, int32_t enable);
 int yahkv_kernel_timing_read(yahkv_ctx* ctx, int32_t kernel, double* total_ms, int64_t* launches);
 
+/* ---- decode attention without any allocation ---------------------------------------------------------------
+ * No counterpart in the reference (its decoder allocates its acc/ml workspace itself, loom_decoder.hpp:125-126).
+ * For hosts that may not allocate GPU memory (a server whose own allocator holds the whole device, a plugin in a
+ * process that forbids cudaMalloc after start-up, a latency-critical loop that cannot afford an allocation's
+ * implicit synchronisation). Such a host cannot even create a yahkv_ctx, so this call takes no context: the caller
+ * owns and passes every input and output, and the split-K work list, partial results and status word live in a
+ * static device array inside the library (YAHKV_NOALLOC_SCRATCH_BYTES, held by every GPU that loads the library
+ * until the process exits). It calls no cudaMalloc / cudaFree / pinned allocation / stream or event creation.
+ *
+ * Pools use the layout at the top of this file. Row b of tables_dev belongs to sequence b of the call; lens_dev[b]
+ * is its number of visible keys (clamped to [1, table_stride * 64] on the device). n_splits is the fixed number of
+ * split-K units per (sequence, kv head). Refused with YAHKV_ERR_CAPACITY beyond YAHKV_NOALLOC_MAX_SEQS sequences or
+ * YAHKV_NOALLOC_MAX_UNITS = n_seqs * 4 * n_splits units. Results equal yahkv_attend_decode's with the same n_splits.
+ *
+ * All calls on a device share the static array, which keeps the previous call's contents (each call rewrites what
+ * it reads): calls whose kernels could overlap on the GPU race, so issue them on one stream or order them yourself.
+ * The first call on each device resolves the array's device address and sets kernel attributes; make that call
+ * before starting any stream capture. err (may be NULL) receives the message of a refused call. */
+#define YAHKV_NOALLOC_MAX_SEQS 256
+#define YAHKV_NOALLOC_MAX_UNITS 1024
+#define YAHKV_NOALLOC_SCRATCH_BYTES 6381824
+typedef struct yahkv_noalloc_args {
+  int32_t fmt;          /* YAHKV_FMT_* */
+  int32_t n_layers;     /* layers in the pools */
+  int32_t num_pages;    /* pages per layer */
+  int32_t layer;
+  const void* kcodes;   /* device, 16-byte aligned */
+  const void* vcodes;
+  const void* kscales;
+  const void* vscales;
+  const int32_t* tables_dev; /* [n_seqs][table_stride] */
+  int32_t table_stride;
+  int32_t n_seqs;
+  const int32_t* lens_dev;   /* [n_seqs] */
+  const void* q_dev;         /* [n_seqs][24][256] fp16 */
+  const float* gate_dev;     /* [n_seqs][24][256] f32 or NULL */
+  void* out_dev;             /* [n_seqs][24][256] by out_dtype */
+  int32_t out_dtype;
+  int32_t n_splits;
+  float softmax_scale;       /* 0 = 1/16 */
+  void* stream;              /* cudaStream_t; NULL = the default stream */
+} yahkv_noalloc_args;
+int yahkv_attend_decode_noalloc(const yahkv_noalloc_args* args, char* err, int32_t err_cap);
+
 #ifdef __cplusplus
 }
 #endif

@@ -54,6 +54,34 @@ class Config(ctypes.Structure):
     ]
 
 
+class NoAllocArgs(ctypes.Structure):
+    """yahkv_noalloc_args: everything yahkv_attend_decode_noalloc reads; the caller owns all of it."""
+    _fields_ = [
+        ("fmt", ctypes.c_int32),
+        ("n_layers", ctypes.c_int32),
+        ("num_pages", ctypes.c_int32),
+        ("layer", ctypes.c_int32),
+        ("kcodes", ctypes.c_void_p),
+        ("vcodes", ctypes.c_void_p),
+        ("kscales", ctypes.c_void_p),
+        ("vscales", ctypes.c_void_p),
+        ("tables_dev", ctypes.c_void_p),
+        ("table_stride", ctypes.c_int32),
+        ("n_seqs", ctypes.c_int32),
+        ("lens_dev", ctypes.c_void_p),
+        ("q_dev", ctypes.c_void_p),
+        ("gate_dev", ctypes.c_void_p),
+        ("out_dev", ctypes.c_void_p),
+        ("out_dtype", ctypes.c_int32),
+        ("n_splits", ctypes.c_int32),
+        ("softmax_scale", ctypes.c_float),
+        ("stream", ctypes.c_void_p),
+    ]
+
+
+NOALLOC_MAX_SEQS, NOALLOC_MAX_UNITS = 256, 1024
+
+
 class YahkvError(RuntimeError):
     def __init__(self, code, message):
         super().__init__(f"{code} ({_error_name(code)}): {message}")
@@ -99,6 +127,7 @@ SIGNATURES = {
     "yahkv_sync": (_I32, [_VP]),
     "yahkv_device_bytes": (_I32, [_VP, _PI64]),
     "yahkv_launch_count": (_I32, [_VP, _PI64]),
+    "yahkv_attend_decode_noalloc": (_I32, [_c.POINTER(NoAllocArgs), _c.c_char_p, _I32]),
     "yahkv_kernel_timing": (_I32, [_VP, _I32]),
     "yahkv_kernel_timing_read": (_I32, [_VP, _I32, _c.POINTER(_c.c_double), _PI64]),
 }
@@ -136,6 +165,23 @@ def _ptr(x):
 
 def _i32(a):
     return np.ascontiguousarray(a, dtype=np.int32)
+
+
+def attend_decode_noalloc(*, fmt, n_layers, num_pages, layer, kcodes, vcodes, kscales, vscales, tables, table_stride,
+                          n_seqs, lens, q, out, gate=None, out_dtype=OUT_F16, n_splits=1, softmax_scale=0.0,
+                          stream=None):
+    """Context-free decode attention for hosts that may not allocate on the GPU: every buffer is the caller's, the
+    split-K scratch is a static array inside the library. Raises YahkvError when the request is refused."""
+    def addr(x):
+        p = _ptr(x)
+        return None if p is None else p.value
+    args = NoAllocArgs(fmt, n_layers, num_pages, layer, addr(kcodes), addr(vcodes), addr(kscales), addr(vscales),
+                       addr(tables), table_stride, n_seqs, addr(lens), addr(q), addr(gate), addr(out), out_dtype,
+                       n_splits, softmax_scale, addr(stream))
+    err = ctypes.create_string_buffer(256)
+    rc = lib.yahkv_attend_decode_noalloc(ctypes.byref(args), err, len(err))
+    if rc != OK:
+        raise YahkvError(rc, err.value.decode())
 
 
 class KvCache:
