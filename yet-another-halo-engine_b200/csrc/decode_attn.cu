@@ -6,11 +6,11 @@
 // fp32 softmax statistics, partials (max, sum, unnormalised acc) merged in unit order, out = A / L * sigmoid(gate).
 //
 // Shape of the work. One CTA processes one split-K unit: a run of pages of one sequence for one kv head, all six query
-// heads of the GQA group at once, so every cache byte is read from HBM exactly once per call. A producer warp walks
-// the block table and gathers each page's K and V records with non-multicast TMA: two 2-D tiled copies per side
-// (64 token rows x 128 B, 128-byte swizzle, so the ldmatrix reads below are bank-conflict free) plus one bulk copy
-// per side for the 64 x 8 fp16 scales, all completing on one mbarrier per stage. Four consumer warps take 16 keys of
-// the page each.
+// heads of the GQA group at once, so every cache byte is read from HBM exactly once per call. Each page's K and V
+// records are gathered through the block table with non-multicast TMA: two 2-D tiled copies per side (64 token rows
+// x 128 B, 128-byte swizzle, so the ldmatrix reads below are bank-conflict free) plus one bulk copy per side for the
+// 64 x 8 fp16 scales, all completing on one mbarrier per ring stage. The CTA's four warps take 16 keys of the page
+// each; there is no producer warp: whichever warp finishes a stage last refills it, so no warp waits for another.
 //
 // The path is HBM-bound (2176 B per token per layer in q8_0), but at GQA 6 it needs 5.6 multiply-adds per byte, more
 // than the fp32 pipes can give at HBM rate, so the dot products run on the warp-level f16 tensor-core MMA with
@@ -35,9 +35,19 @@
 namespace yahkv {
 namespace {
 
-constexpr int kConsumerWarps = 4;
-constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
-constexpr int kBoxBytes = 64 * 128;  // one swizzled TMA box: 64 token rows x 128 B
+// Resident CTAs per SM and ring depth per CTA (stage = one page of one kv head: 34 KB q8_0, 18 KB q4_0).
+#ifndef YAHKV_DECODE_CTAS
+#define YAHKV_DECODE_CTAS 2
+#endif
+#ifndef YAHKV_Q8_STAGES
+#define YAHKV_Q8_STAGES 3
+#endif
+#ifndef YAHKV_Q4_STAGES
+#define YAHKV_Q4_STAGES 5
+#endif
+constexpr int kWarps = 4;             // each takes 16 of a page's 64 keys
+constexpr int kDecodeThreads = kWarps * 32;
+constexpr int kBoxBytes = 64 * 128;   // one swizzled TMA box: 64 token rows x 128 B
 
 template <int kFmt>
 struct StageLayout {
@@ -47,24 +57,41 @@ struct StageLayout {
   static constexpr int kKsOff = 2 * kBoxesPerSide * kBoxBytes;
   static constexpr int kVsOff = kKsOff + kRecordScaleBytes;
   static constexpr int kBytes = kVsOff + kRecordScaleBytes;  // 34816 (q8_0) or 18432 (q4_0), a multiple of 1024
-  static constexpr int kStages = kFmt == kFmtQ8 ? 3 : 5;
+  static constexpr int kStages = kFmt == kFmtQ8 ? YAHKV_Q8_STAGES : YAHKV_Q4_STAGES;
 };
-// Cross-warp merge scratch at the end of a unit: per consumer warp acc [6][kMergeStride] f32 and (m, l) [8][2].
+// Cross-warp merge scratch at the end of a unit: per warp acc [6][kMergeStride] f32 and (m, l) [8][2].
 constexpr int kMergeStride = kHeadDim + 8;
-constexpr int kMergeBytes = kConsumerWarps * (kGroup * kMergeStride + 16) * 4;
+constexpr int kMergeWarpFloats = kGroup * kMergeStride + 16;
+constexpr int kMergeBytes = kWarps * kMergeWarpFloats * 4;
 
 // fp16 number b (0..7) of eight packed in a uint4, widened to f32. b is a compile-time constant after unrolling.
+__device__ __forceinline__ std::uint32_t WordOf(const uint4& v, int i) {
+  return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
+}
 __device__ __forceinline__ float ScaleOf(const uint4& v, int b) {
-  const std::uint32_t w = (b >> 1) == 0 ? v.x : (b >> 1) == 1 ? v.y : (b >> 1) == 2 ? v.z : v.w;
-  return __half2float(__ushort_as_half(static_cast<unsigned short>((b & 1) ? (w >> 16) : (w & 0xFFFFU))));
+  const __half2 h = *reinterpret_cast<const __half2*>(&reinterpret_cast<const std::uint32_t&>(
+      b < 2 ? v.x : b < 4 ? v.y : b < 6 ? v.z : v.w));
+  return (b & 1) ? __high2float(h) : __low2float(h);
 }
 
-// One S^T MMA step: the Q fragment of the step comes from shared memory at use (volatile, so the compiler does not
-// hoist all sixteen fragments into registers), rows 8-15 of A are zero.
+// D = A * B with a zero accumulator input, rows 8-15 of A zero (the S^T step's first MMA of a block): no register
+// has to be cleared beforehand.
+__device__ __forceinline__ void MmaQZero(float (&d)[4], std::uint32_t q_addr, std::uint32_t b0, std::uint32_t b1) {
+  std::uint32_t a0, a1, a2, a3;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(q_addr));
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%10, %10, %10, %10};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0F));
+}
+// One S^T MMA step accumulating in place: the Q fragment of the step comes from shared memory at use (volatile, so
+// the compiler does not keep all sixteen fragments in registers), stored there as the A operand's four registers
+// (rows 8-15 of A, registers 1 and 3, are zero) so one 16-byte load fills them without any register shuffling.
 __device__ __forceinline__ void MmaQ(float (&d)[4], std::uint32_t q_addr, std::uint32_t b0, std::uint32_t b1) {
-  std::uint32_t a0, a2;
-  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(a0), "=r"(a2) : "r"(q_addr));
-  MmaF16(d, a0, 0U, a2, 0U, b0, b1);
+  std::uint32_t a0, a1, a2, a3;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(q_addr));
+  MmaF16(d, a0, a1, a2, a3, b0, b1);
 }
 
 template <int kFmt>
@@ -78,7 +105,7 @@ constexpr int DecodeSmemBytes() {
 constexpr float kLazyRescale = 4.0F;
 
 template <int kFmt>
-__global__ void __launch_bounds__(kDecodeThreads, 2)
+__global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
     DecodePartKernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                      PoolView pool, int layer, const std::int32_t* __restrict__ tables, int table_stride,
                      const DecodeUnit* __restrict__ units, const __half* __restrict__ q, float scale_log2,
@@ -86,141 +113,114 @@ __global__ void __launch_bounds__(kDecodeThreads, 2)
   using L = StageLayout<kFmt>;
   extern __shared__ std::uint8_t smem_raw[];
   __shared__ __align__(8) std::uint64_t full_bar[L::kStages];
-  __shared__ __align__(8) std::uint64_t empty_bar[L::kStages];
-  __shared__ uint2 qfrag[16 * 32];
+  __shared__ int done_cnt[L::kStages];   // warps that have finished reading the stage's current page
+  __shared__ uint4 qfrag[16 * 32];
   std::uint8_t* ring = reinterpret_cast<std::uint8_t*>((reinterpret_cast<std::uintptr_t>(smem_raw) + 1023) &
                                                        ~static_cast<std::uintptr_t>(1023));
 
   const DecodeUnit u = units[blockIdx.x];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_pages = u.page_end - u.page_begin;
+  const std::int32_t* row = tables + static_cast<std::size_t>(u.seq) * table_stride + u.page_begin;
+
+  // Gather of one page into a ring stage: 2 TMA boxes per side (q8_0; 1 for q4_0) + the two scale records, all
+  // completing on the stage's mbarrier. Issued by one thread.
+  auto issue = [&](int s, std::int32_t page) {
+    page = min(max(page, 0), pool.num_pages - 1);   // never trust a table entry read from memory
+    const std::size_t rec = (static_cast<std::size_t>(layer) * pool.num_pages + page) * kKvHeads + u.kvh;
+    const int y = static_cast<int>(rec * kPageTokens);
+    std::uint8_t* st = ring + s * L::kBytes;
+    MbarArriveExpectTx(&full_bar[s], L::kBytes);
+#pragma unroll
+    for (int b = 0; b < L::kBoxesPerSide; ++b) {
+      TmaLoad2D(st + L::kKOff + b * kBoxBytes, &kmap, b * 128, y, &full_bar[s]);
+      TmaLoad2D(st + L::kVOff + b * kBoxBytes, &vmap, b * 128, y, &full_bar[s]);
+    }
+    BulkLoad(st + L::kKsOff, pool.kscales + rec * (kPageTokens * kBlocksPerRow), kRecordScaleBytes, &full_bar[s]);
+    BulkLoad(st + L::kVsOff, pool.vscales + rec * (kPageTokens * kBlocksPerRow), kRecordScaleBytes, &full_bar[s]);
+  };
 
   if (threadIdx.x == 0) {
+    PrefetchTensorMap(&kmap);
+    PrefetchTensorMap(&vmap);
     for (int s = 0; s < L::kStages; ++s) {
       MbarInit(&full_bar[s], 1);
-      MbarInit(&empty_bar[s], kConsumerWarps);
+      done_cnt[s] = 0;
     }
     FenceBarrierInit();
-  }
-  __syncthreads();
-
-  if (warp == kConsumerWarps) {
-    // ---------------- producer: block-table walk + TMA gathers ----------------
-    if (lane == 0) {
-      PrefetchTensorMap(&kmap);
-      PrefetchTensorMap(&vmap);
-    }
-    const std::int32_t* row = tables + static_cast<std::size_t>(u.seq) * table_stride + u.page_begin;
-    bool ok = true;
-    for (int base = 0; base < n_pages && ok; base += 32) {
-      const int cnt = min(32, n_pages - base);
-      std::int32_t mine = lane < cnt ? __ldg(row + base + lane) : 0;
-      mine = min(max(mine, 0), pool.num_pages - 1);
-      for (int j = 0; j < cnt; ++j) {
-        const std::int32_t page = __shfl_sync(0xFFFFFFFFU, mine, j);
-        const int i = base + j, s = i % L::kStages;
-        if (lane == 0) {
-          if (i >= L::kStages) ok = MbarWait(&empty_bar[s], ((i / L::kStages) - 1) & 1);
-          if (ok) {
-            const std::size_t rec = (static_cast<std::size_t>(layer) * pool.num_pages + page) * kKvHeads + u.kvh;
-            const int y = static_cast<int>(rec * kPageTokens);
-            std::uint8_t* st = ring + s * L::kBytes;
-            MbarArriveExpectTx(&full_bar[s], L::kBytes);
-#pragma unroll
-            for (int b = 0; b < L::kBoxesPerSide; ++b) {
-              TmaLoad2D(st + L::kKOff + b * kBoxBytes, &kmap, b * 128, y, &full_bar[s]);
-              TmaLoad2D(st + L::kVOff + b * kBoxBytes, &vmap, b * 128, y, &full_bar[s]);
-            }
-            BulkLoad(st + L::kKsOff, pool.kscales + rec * (kPageTokens * kBlocksPerRow), kRecordScaleBytes,
-                     &full_bar[s]);
-            BulkLoad(st + L::kVsOff, pool.vscales + rec * (kPageTokens * kBlocksPerRow), kRecordScaleBytes,
-                     &full_bar[s]);
-          }
-        }
-        ok = __shfl_sync(0xFFFFFFFFU, ok ? 1 : 0, 0) != 0;
-        if (!ok) break;
-      }
-    }
-    if (!ok && lane == 0) atomicExch(status, kStatusWaitTimeout);
-    // The copies this warp issued are all awaited by the consumers (or by their bounded waits) before the CTA ends:
-    // the final __syncthreads below keeps this warp resident until then.
+    for (int i = 0; i < L::kStages && i < n_pages; ++i) issue(i, __ldg(row + i));
   }
 
-  // ---------------- consumers ----------------
   const int g = lane >> 2, t = lane & 3;
+  // Q fragments through shared memory, shared by the four warps: MMA step c (16 dims) uses dims 16c + 4t + {0, 2} in
+  // k-slots (2t, 2t+1) and + {1, 3} in (2t+8, 2t+9).
+  {
+    const __half* qrow = q + (static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + g) * kHeadDim;
+#pragma unroll
+    for (int cc = 0; cc < 16 / kWarps; ++cc) {
+      const int c = warp * (16 / kWarps) + cc;
+      uint2 v = make_uint2(0, 0);
+      if (g < kGroup) v = *reinterpret_cast<const uint2*>(qrow + 16 * c + 4 * t);
+      qfrag[c * 32 + lane] = make_uint4(__byte_perm(v.x, v.y, 0x5410), 0U,   // halves (0, 2)
+                                        __byte_perm(v.x, v.y, 0x7632), 0U);  // halves (1, 3)
+    }
+  }
+  __syncthreads();   // barriers initialised, Q fragments visible
+  const std::uint32_t qa_addr = SmemAddr(qfrag + lane);
+
   float o_acc[16][4];
+#pragma unroll
+  for (int c = 0; c < 16; ++c)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o_acc[c][i] = 0.0F;
   float m_run = -INFINITY, l_run = 0.0F;
   bool alive = true;
 
-  if (warp < kConsumerWarps) {
+  // ldmatrix row addresses: lane supplies row (lane & 7) + 8 * ((lane >> 3) & 1) of the warp's 16 keys and the
+  // 16-byte chunk 2x + (lane >> 4) of its 128-byte row, swizzled: physical chunk = chunk ^ (row & 7).
+  const int lm_key = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+  std::uint32_t lm_off[4];
 #pragma unroll
-    for (int c = 0; c < 16; ++c)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) o_acc[c][i] = 0.0F;
+  for (int x = 0; x < 4; ++x) lm_off[x] = lm_key * 128 + ((((2 * x) | (lane >> 4)) ^ (lm_key & 7)) << 4);
+  // Keys whose scores this thread holds: kt * 8 + 2t + j of the warp's 16.
+  const int my_key0 = warp * 16 + 2 * t;
 
-    // Q fragments, shared by the four warps through shared memory (keeping them in registers would spill): MMA step c
-    // (16 dims) uses dims 16c + 4t + {0, 2} in k-slots (2t, 2t+1) and + {1, 3} in (2t+8, 2t+9).
-    {
-      const __half* qrow = q + (static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + g) * kHeadDim;
-#pragma unroll
-      for (int cc = 0; cc < 16 / kConsumerWarps; ++cc) {
-        const int c = warp * (16 / kConsumerWarps) + cc;
-        uint2 v = make_uint2(0, 0);
-        if (g < kGroup) v = *reinterpret_cast<const uint2*>(qrow + 16 * c + 4 * t);
-        qfrag[c * 32 + lane] = make_uint2(__byte_perm(v.x, v.y, 0x5410),   // halves (0, 2)
-                                          __byte_perm(v.x, v.y, 0x7632));  // halves (1, 3)
-      }
+  for (int i = 0; i < n_pages; ++i) {
+    const int s = i % L::kStages;
+    // Table entry of the page that will take this stage next, fetched a whole iteration before it is needed.
+    std::int32_t refill_page = 0;
+    if (lane == 0 && i + L::kStages < n_pages) refill_page = __ldg(row + i + L::kStages);
+    if (!__all_sync(0xFFFFFFFFU, MbarWait(&full_bar[s], (i / L::kStages) & 1))) {
+      alive = false;
+      break;
     }
-    NamedBarrierSync(1, kConsumerWarps * 32);
-    const std::uint32_t qa_addr = SmemAddr(qfrag + lane);
+    const std::uint8_t* st = ring + s * L::kBytes;
+    const std::uint32_t k_base = SmemAddr(st + L::kKOff), v_base = SmemAddr(st + L::kVOff);
 
-    // ldmatrix row address pieces: lane supplies row (lane & 7) + 8 * ((lane >> 3) & 1) of the warp's 16 keys and
-    // 16-byte chunk (lane >> 4) of a chunk pair.
-    const int lm_key = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-    const int lm_half = lane >> 4;
-    // Keys whose scores this thread holds: kt * 8 + 2t + j of the warp's 16.
-    const int my_key0 = warp * 16 + 2 * t;
-
-    for (int i = 0; i < n_pages; ++i) {
-      const int s = i % L::kStages;
-      if (!MbarWait(&full_bar[s], (i / L::kStages) & 1)) {
-        alive = false;
-        break;
-      }
-      const std::uint8_t* st = ring + s * L::kBytes;
-      const std::uint32_t k_base = SmemAddr(st + L::kKOff), v_base = SmemAddr(st + L::kVOff);
-
-      // scales of this thread's four keys, all eight blocks
-      uint4 ks_raw[2][2], vs_raw[2][2];
+    // ---- S^T = Q K^T: per 32-element block an fp32 partial sum of exact products, times the block's fp16 scale ----
+    float sc[2][2] = {{0.0F, 0.0F}, {0.0F, 0.0F}};
+    {
+      uint4 ks_raw[2][2];
 #pragma unroll
       for (int kt = 0; kt < 2; ++kt)
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int key = my_key0 + kt * 8 + j;
-          ks_raw[kt][j] = *reinterpret_cast<const uint4*>(st + L::kKsOff + key * 16);
-          vs_raw[kt][j] = *reinterpret_cast<const uint4*>(st + L::kVsOff + key * 16);
-        }
-
-      // ---- S^T = Q K^T ----
-      float sc[2][2] = {{0.0F, 0.0F}, {0.0F, 0.0F}};
+        for (int j = 0; j < 2; ++j)
+          ks_raw[kt][j] = *reinterpret_cast<const uint4*>(st + L::kKsOff + (my_key0 + kt * 8 + j) * 16);
       if constexpr (kFmt == kFmtQ8) {
 #pragma unroll
         for (int b = 0; b < 8; ++b) {
-          const int c = 2 * b + lm_half;  // 16-byte chunk of the 256-byte row
-          const std::uint32_t addr =
-              k_base + (c >> 3) * kBoxBytes + lm_key * 128 + (((c & 7) ^ (lm_key & 7)) << 4);
           std::uint32_t w[4];
-          LdMatrixX4(addr, w);
-          float a0[4] = {0, 0, 0, 0}, a1[4] = {0, 0, 0, 0};
+          LdMatrixX4(k_base + (b >> 2) * kBoxBytes + lm_off[b & 3], w);
+          float a0[4], a1[4];
           std::uint32_t x0, x1;
           Int8x4ToHalf2(w[0], x0, x1);
-          MmaQ(a0, qa_addr + (2 * b) * 256, x0, x1);
-          Int8x4ToHalf2(w[2], x0, x1);
-          MmaQ(a0, qa_addr + (2 * b + 1) * 256, x0, x1);
+          MmaQZero(a0, qa_addr + (2 * b) * 512, x0, x1);
           Int8x4ToHalf2(w[1], x0, x1);
-          MmaQ(a1, qa_addr + (2 * b) * 256, x0, x1);
+          MmaQZero(a1, qa_addr + (2 * b) * 512, x0, x1);
+          Int8x4ToHalf2(w[2], x0, x1);
+          MmaQ(a0, qa_addr + (2 * b + 1) * 512, x0, x1);
           Int8x4ToHalf2(w[3], x0, x1);
-          MmaQ(a1, qa_addr + (2 * b + 1) * 256, x0, x1);
+          MmaQ(a1, qa_addr + (2 * b + 1) * 512, x0, x1);
           sc[0][0] = fmaf(ScaleOf(ks_raw[0][0], b), a0[0], sc[0][0]);
           sc[0][1] = fmaf(ScaleOf(ks_raw[0][1], b), a0[1], sc[0][1]);
           sc[1][0] = fmaf(ScaleOf(ks_raw[1][0], b), a1[0], sc[1][0]);
@@ -230,21 +230,19 @@ __global__ void __launch_bounds__(kDecodeThreads, 2)
         // q4_0 rows are 128 B = 8 blocks of 16 packed bytes; one ldmatrix.x4 covers two blocks of 16 keys.
 #pragma unroll
         for (int bp = 0; bp < 4; ++bp) {
-          const int c = 2 * bp + lm_half;  // block index = 16-byte chunk
-          const std::uint32_t addr = k_base + lm_key * 128 + ((c ^ (lm_key & 7)) << 4);
           std::uint32_t w[4];
-          LdMatrixX4(addr, w);
+          LdMatrixX4(k_base + lm_off[bp], w);
 #pragma unroll
           for (int hb = 0; hb < 2; ++hb) {
             const int b = 2 * bp + hb;
-            float a0[4] = {0, 0, 0, 0}, a1[4] = {0, 0, 0, 0};
+            float a0[4], a1[4];
             std::uint32_t l0, l1, h0, h1;
             Nib4x4ToHalf2(w[2 * hb], l0, l1, h0, h1);
-            MmaQ(a0, qa_addr + (2 * b) * 256, l0, l1);
-            MmaQ(a0, qa_addr + (2 * b + 1) * 256, h0, h1);
+            MmaQZero(a0, qa_addr + (2 * b) * 512, l0, l1);
+            MmaQ(a0, qa_addr + (2 * b + 1) * 512, h0, h1);
             Nib4x4ToHalf2(w[2 * hb + 1], l0, l1, h0, h1);
-            MmaQ(a1, qa_addr + (2 * b) * 256, l0, l1);
-            MmaQ(a1, qa_addr + (2 * b + 1) * 256, h0, h1);
+            MmaQZero(a1, qa_addr + (2 * b) * 512, l0, l1);
+            MmaQ(a1, qa_addr + (2 * b + 1) * 512, h0, h1);
             sc[0][0] = fmaf(ScaleOf(ks_raw[0][0], b), a0[0], sc[0][0]);
             sc[0][1] = fmaf(ScaleOf(ks_raw[0][1], b), a0[1], sc[0][1]);
             sc[1][0] = fmaf(ScaleOf(ks_raw[1][0], b), a1[0], sc[1][0]);
@@ -252,112 +250,127 @@ __global__ void __launch_bounds__(kDecodeThreads, 2)
           }
         }
       }
+    }
 
-      // ---- softmax statistics (per head g, the 16 keys spread over the four lanes of a quad) ----
-      const int key_pos0 = (u.page_begin + i) * kPageTokens + my_key0;
-      float tmax = -INFINITY;
+    // ---- softmax statistics (per head g, the 16 keys spread over the four lanes of a quad) ----
+    const int key_pos0 = (u.page_begin + i) * kPageTokens + my_key0;
+    float tmax = -INFINITY;
 #pragma unroll
-      for (int kt = 0; kt < 2; ++kt)
+    for (int kt = 0; kt < 2; ++kt)
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const bool valid = key_pos0 + kt * 8 + j < u.n_keys;
-          sc[kt][j] = valid ? sc[kt][j] * scale_log2 : -INFINITY;
-          tmax = fmaxf(tmax, sc[kt][j]);
-        }
-      tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFU, tmax, 1));
-      tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFU, tmax, 2));
-      if (__any_sync(0xFFFFFFFFU, tmax > m_run + kLazyRescale)) {
-        const float m_new = fmaxf(m_run, tmax);
-        const float alpha = m_new == -INFINITY ? 1.0F : exp2f(m_run - m_new);  // m_run = -inf gives 0
-        m_run = m_new;
-        l_run *= alpha;
-        const float al0 = __shfl_sync(0xFFFFFFFFU, alpha, (2 * t) * 4);
-        const float al1 = __shfl_sync(0xFFFFFFFFU, alpha, (2 * t + 1) * 4);
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          o_acc[c][0] *= al0, o_acc[c][2] *= al0;
-          o_acc[c][1] *= al1, o_acc[c][3] *= al1;
-        }
+      for (int j = 0; j < 2; ++j) {
+        const bool valid = key_pos0 + kt * 8 + j < u.n_keys;
+        sc[kt][j] = valid ? sc[kt][j] * scale_log2 : -INFINITY;
+        tmax = fmaxf(tmax, sc[kt][j]);
       }
-      const float m_use = m_run == -INFINITY ? 0.0F : m_run;
-      float p[2][2];
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFU, tmax, 1));
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFU, tmax, 2));
+    if (__any_sync(0xFFFFFFFFU, tmax > m_run + kLazyRescale)) {
+      const float m_new = fmaxf(m_run, tmax);
+      const float alpha = m_new == -INFINITY ? 1.0F : exp2f(m_run - m_new);  // m_run = -inf gives 0
+      m_run = m_new;
+      l_run *= alpha;
+      const float al0 = __shfl_sync(0xFFFFFFFFU, alpha, (2 * t) * 4);
+      const float al1 = __shfl_sync(0xFFFFFFFFU, alpha, (2 * t + 1) * 4);
 #pragma unroll
-      for (int kt = 0; kt < 2; ++kt)
+      for (int c = 0; c < 16; ++c) {
+        o_acc[c][0] *= al0, o_acc[c][2] *= al0;
+        o_acc[c][1] *= al1, o_acc[c][3] *= al1;
+      }
+    }
+    const float m_use = m_run == -INFINITY ? 0.0F : m_run;
+    // Weights as an fp16 high part plus an fp16 residual (22 bits together), one half2 per key pair.
+    __half2 p_hi[2], p_lo[2];
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          p[kt][j] = exp2f(sc[kt][j] - m_use);
-          l_run += p[kt][j];
-        }
+    for (int kt = 0; kt < 2; ++kt) {
+      const float p0 = exp2f(sc[kt][0] - m_use), p1 = exp2f(sc[kt][1] - m_use);
+      l_run += p0 + p1;
+      p_hi[kt] = __floats2half2_rn(p0, p1);
+      const float2 hf = __half22float2(p_hi[kt]);
+      p_lo[kt] = __floats2half2_rn(p0 - hf.x, p1 - hf.y);
+    }
 
-      // ---- O^T += V^T P^T ----
-      auto weights = [&](int b, std::uint32_t (&hi)[2], std::uint32_t (&lo)[2]) {
+    // ---- O^T += V^T P^T, the V scale of (key, block) folded into the weights ----
+    uint4 vs_raw[2][2];
 #pragma unroll
-        for (int kt = 0; kt < 2; ++kt) {
-          const float w0 = p[kt][0] * ScaleOf(vs_raw[kt][0], b);
-          const float w1 = p[kt][1] * ScaleOf(vs_raw[kt][1], b);
-          const __half2 h = __floats2half2_rn(w0, w1);
-          const float2 hf = __half22float2(h);
-          const __half2 l = __floats2half2_rn(w0 - hf.x, w1 - hf.y);
-          hi[kt] = *reinterpret_cast<const std::uint32_t*>(&h);
-          lo[kt] = *reinterpret_cast<const std::uint32_t*>(&l);
-        }
-      };
-      if constexpr (kFmt == kFmtQ8) {
+    for (int kt = 0; kt < 2; ++kt)
 #pragma unroll
-        for (int b = 0; b < 8; ++b) {
+      for (int j = 0; j < 2; ++j)
+        vs_raw[kt][j] = *reinterpret_cast<const uint4*>(st + L::kVsOff + (my_key0 + kt * 8 + j) * 16);
+    // weight x scale without leaving fp16: hi = round(p_hi d); the rounding error of that product is recovered
+    // exactly by an fma and joins the low part: lo = p_lo d + (p_hi d - hi).
+    auto weights = [&](int b, std::uint32_t (&hi)[2], std::uint32_t (&lo)[2]) {
+#pragma unroll
+      for (int kt = 0; kt < 2; ++kt) {
+        const std::uint32_t dw = __byte_perm(WordOf(vs_raw[kt][0], b >> 1), WordOf(vs_raw[kt][1], b >> 1),
+                                             (b & 1) ? 0x7632 : 0x5410);
+        const __half2 d2 = *reinterpret_cast<const __half2*>(&dw);
+        const __half2 h = __hmul2(p_hi[kt], d2);
+        const __half2 r = __hfma2(p_hi[kt], d2, __hneg2(h));
+        const __half2 l = __hfma2(p_lo[kt], d2, r);
+        hi[kt] = *reinterpret_cast<const std::uint32_t*>(&h);
+        lo[kt] = *reinterpret_cast<const std::uint32_t*>(&l);
+      }
+    };
+    if constexpr (kFmt == kFmtQ8) {
+#pragma unroll
+      for (int b = 0; b < 8; ++b) {
+        std::uint32_t hi[2], lo[2];
+        weights(b, hi, lo);
+        std::uint32_t w[4];
+        LdMatrixX4Trans(v_base + (b >> 2) * kBoxBytes + lm_off[b & 3], w);
+        std::uint32_t a0, a1, a2, a3;
+        Int8x4ToHalf2(w[0], a0, a1);
+        Int8x4ToHalf2(w[1], a2, a3);
+        MmaF16(o_acc[2 * b], a0, a1, a2, a3, hi[0], hi[1]);
+        MmaF16(o_acc[2 * b], a0, a1, a2, a3, lo[0], lo[1]);
+        Int8x4ToHalf2(w[2], a0, a1);
+        Int8x4ToHalf2(w[3], a2, a3);
+        MmaF16(o_acc[2 * b + 1], a0, a1, a2, a3, hi[0], hi[1]);
+        MmaF16(o_acc[2 * b + 1], a0, a1, a2, a3, lo[0], lo[1]);
+      }
+    } else {
+#pragma unroll
+      for (int bp = 0; bp < 4; ++bp) {
+        std::uint32_t w[4];
+        LdMatrixX4Trans(v_base + lm_off[bp], w);
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb) {
+          const int b = 2 * bp + hb;
           std::uint32_t hi[2], lo[2];
           weights(b, hi, lo);
-          const int c = 2 * b + lm_half;
-          const std::uint32_t addr =
-              v_base + (c >> 3) * kBoxBytes + lm_key * 128 + (((c & 7) ^ (lm_key & 7)) << 4);
-          std::uint32_t w[4];
-          LdMatrixX4Trans(addr, w);
-          std::uint32_t a0, a1, a2, a3;
-          Int8x4ToHalf2(w[0], a0, a1);
-          Int8x4ToHalf2(w[1], a2, a3);
-          MmaF16(o_acc[2 * b], a0, a1, a2, a3, hi[0], hi[1]);
-          MmaF16(o_acc[2 * b], a0, a1, a2, a3, lo[0], lo[1]);
-          Int8x4ToHalf2(w[2], a0, a1);
-          Int8x4ToHalf2(w[3], a2, a3);
-          MmaF16(o_acc[2 * b + 1], a0, a1, a2, a3, hi[0], hi[1]);
-          MmaF16(o_acc[2 * b + 1], a0, a1, a2, a3, lo[0], lo[1]);
-        }
-      } else {
-#pragma unroll
-        for (int bp = 0; bp < 4; ++bp) {
-          const int c = 2 * bp + lm_half;
-          const std::uint32_t addr = v_base + lm_key * 128 + ((c ^ (lm_key & 7)) << 4);
-          std::uint32_t w[4];
-          LdMatrixX4Trans(addr, w);
-#pragma unroll
-          for (int hb = 0; hb < 2; ++hb) {
-            const int b = 2 * bp + hb;
-            std::uint32_t hi[2], lo[2];
-            weights(b, hi, lo);
-            std::uint32_t la0, la1, ha0, ha1, la2, la3, ha2, ha3;
-            Nib4x4ToHalf2(w[2 * hb], la0, la1, ha0, ha1);      // keys 0-7 of the warp's 16
-            Nib4x4ToHalf2(w[2 * hb + 1], la2, la3, ha2, ha3);  // keys 8-15
-            MmaF16(o_acc[2 * b], la0, la1, la2, la3, hi[0], hi[1]);
-            MmaF16(o_acc[2 * b], la0, la1, la2, la3, lo[0], lo[1]);
-            MmaF16(o_acc[2 * b + 1], ha0, ha1, ha2, ha3, hi[0], hi[1]);
-            MmaF16(o_acc[2 * b + 1], ha0, ha1, ha2, ha3, lo[0], lo[1]);
-          }
+          std::uint32_t la0, la1, ha0, ha1, la2, la3, ha2, ha3;
+          Nib4x4ToHalf2(w[2 * hb], la0, la1, ha0, ha1);      // keys 0-7 of the warp's 16
+          Nib4x4ToHalf2(w[2 * hb + 1], la2, la3, ha2, ha3);  // keys 8-15
+          MmaF16(o_acc[2 * b], la0, la1, la2, la3, hi[0], hi[1]);
+          MmaF16(o_acc[2 * b], la0, la1, la2, la3, lo[0], lo[1]);
+          MmaF16(o_acc[2 * b + 1], ha0, ha1, ha2, ha3, hi[0], hi[1]);
+          MmaF16(o_acc[2 * b + 1], ha0, ha1, ha2, ha3, lo[0], lo[1]);
         }
       }
-
-      __syncwarp();
-      if (lane == 0) MbarArrive(&empty_bar[s]);
     }
-    if (!alive && lane == 0) atomicExch(status, kStatusWaitTimeout);
-    l_run += __shfl_xor_sync(0xFFFFFFFFU, l_run, 1);
-    l_run += __shfl_xor_sync(0xFFFFFFFFU, l_run, 2);
+
+    // The last of the four warps to finish with the stage refills it (no warp ever waits for another one). The
+    // MMAs above consumed every ldmatrix result, so this warp's reads of the stage are complete.
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence_block();
+      if (atomicAdd(&done_cnt[s], 1) == kWarps - 1) {
+        done_cnt[s] = 0;
+        __threadfence_block();
+        if (i + L::kStages < n_pages) issue(s, refill_page);
+      }
+    }
   }
+  if (!alive && lane == 0) atomicExch(status, kStatusWaitTimeout);
+  l_run += __shfl_xor_sync(0xFFFFFFFFU, l_run, 1);
+  l_run += __shfl_xor_sync(0xFFFFFFFFU, l_run, 2);
 
   // Every stage has been consumed (or a wait gave up): the ring is free to hold the merge scratch.
   __syncthreads();
   float* merge = reinterpret_cast<float*>(ring);
-  if (warp < kConsumerWarps) {
-    float* mine = merge + warp * (kGroup * kMergeStride + 16);
+  {
+    float* mine = merge + warp * kMergeWarpFloats;
 #pragma unroll
     for (int c = 0; c < 16; ++c) {
       // o_acc[c][0..3] = (dim 16c + 2g, head 2t), (dim 16c + 2g, head 2t+1), (dim 16c + 2g + 1, head 2t), (.., 2t+1)
@@ -374,24 +387,24 @@ __global__ void __launch_bounds__(kDecodeThreads, 2)
     }
   }
   __syncthreads();
-  if (warp < kConsumerWarps) {
+  {
     const int tid = threadIdx.x;  // 0..127: two dims per thread per head
     float* acc_out = partial_acc + static_cast<std::size_t>(u.partial) * kPartialAccFloats;
     float* ml_out = partial_ml + static_cast<std::size_t>(u.partial) * kPartialMlFloats;
 #pragma unroll
     for (int h = 0; h < kGroup; ++h) {
-      float mw[kConsumerWarps], M = -INFINITY;
+      float mw[kWarps], M = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < kConsumerWarps; ++w) {
-        mw[w] = merge[w * (kGroup * kMergeStride + 16) + kGroup * kMergeStride + 2 * h];
+      for (int w = 0; w < kWarps; ++w) {
+        mw[w] = merge[w * kMergeWarpFloats + kGroup * kMergeStride + 2 * h];
         M = fmaxf(M, mw[w]);
       }
       float2 a = make_float2(0.0F, 0.0F);
       float lsum = 0.0F;
 #pragma unroll
-      for (int w = 0; w < kConsumerWarps; ++w) {
+      for (int w = 0; w < kWarps; ++w) {
         const float wgt = mw[w] == -INFINITY ? 0.0F : exp2f(mw[w] - M);
-        const float* src = merge + w * (kGroup * kMergeStride + 16);
+        const float* src = merge + w * kMergeWarpFloats;
         const float2 v = *reinterpret_cast<const float2*>(src + h * kMergeStride + 2 * tid);
         a.x = fmaf(wgt, v.x, a.x), a.y = fmaf(wgt, v.y, a.y);
         lsum = fmaf(wgt, src[kGroup * kMergeStride + 2 * h + 1], lsum);

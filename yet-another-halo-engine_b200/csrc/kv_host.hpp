@@ -9,6 +9,7 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 #include <string>
 #include <utility>
 #include <vector>
@@ -222,6 +223,7 @@ class KvHost {
     // write-back matters. 148 SMs x 2 resident CTAs x 8 units each.
     int auto_pages = static_cast<int>((total_pages * kKvHeads + 2367) / 2368);
     auto_pages = std::min(std::max(auto_pages, 1), 16);
+    if (const char* e = std::getenv("YAHKV_TUNE_UNIT_PAGES")) auto_pages = std::max(1, std::atoi(e));
     std::vector<DecodeUnit> units;
     std::vector<CombineItem> items(static_cast<std::size_t>(n_seqs) * kKvHeads);
     for (int b = 0; b < n_seqs; ++b) {
@@ -246,6 +248,10 @@ class KvHost {
     if (static_cast<long long>(units.size()) > max_units)
       return {YAHKV_ERR_CAPACITY, "attend_decode: split-K plan needs " + std::to_string(units.size()) +
                                       " units, workspace holds " + std::to_string(max_units)};
+    // Longest units first: CTAs are handed out in index order, so the short tail units fill the last wave.
+    std::stable_sort(units.begin(), units.end(), [](const DecodeUnit& a, const DecodeUnit& b) {
+      return a.page_end - a.page_begin > b.page_end - b.page_begin;
+    });
     units_ = std::move(units);
     items_ = std::move(items);
     plan_key_ = key_scratch_;

@@ -14,7 +14,8 @@ import subprocess
 import numpy as np
 
 _PKG_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LIB_PATH = os.path.join(_PKG_DIR, "libyahkv.so")
+# YAHKV_LIB points at another build of the same library (a debug or tuning build); the default is the in-tree one.
+LIB_PATH = os.environ.get("YAHKV_LIB") or os.path.join(_PKG_DIR, "libyahkv.so")
 INCLUDE_DIR = os.path.join(os.path.dirname(_PKG_DIR), "include")
 
 FMT_Q8_0, FMT_Q4_0 = 0, 1
