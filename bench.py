@@ -152,6 +152,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="yahkv", choices=["yahkv", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers per step (16 = the configuration)")
+    ap.add_argument("--fmt", default="q8_0", choices=["q8_0", "q4_0"], help="cache format (q8_0 = the configuration)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
     args = ap.parse_args()
@@ -178,7 +179,8 @@ def main():
     grow = total_steps + e2e_steps + 2
     pages = [(int(n) + grow + 63) // 64 for n in lens]
     num_pages = sum(pages) + 64
-    cache = yahkv.KvCache(device=local_rank, n_layers=layers, num_pages=num_pages, fmt=yahkv.FMT_Q8_0,
+    fmt = yahkv.FMT_Q8_0 if args.fmt == "q8_0" else yahkv.FMT_Q4_0
+    cache = yahkv.KvCache(device=local_rank, n_layers=layers, num_pages=num_pages, fmt=fmt,
                           max_seqs=BATCH, max_pages_per_seq=max(pages) + 1, max_batch_tokens=8192)
     perm = rng.permutation(num_pages).astype(np.int32)
     seqs, off = [], 0
@@ -238,7 +240,7 @@ def main():
     comb_ms, comb_n = cache.kernel_timing_read(yahkv.KERNEL_DECODE_COMBINE)
     app_ms, app_n = cache.kernel_timing_read(yahkv.KERNEL_APPEND)
     cache.kernel_timing(False)
-    bytes_attended = keys * layers * yahkv.bytes_per_token(yahkv.FMT_Q8_0)
+    bytes_attended = keys * layers * yahkv.bytes_per_token(fmt)
 
     # ---- end to end through the host-buffer entry point ----
     e2e = None
@@ -261,7 +263,7 @@ def main():
             e_keys += host_step()
         torch.cuda.synchronize()
         e_s = time.perf_counter() - t0
-        e_bytes = e_keys * layers * yahkv.bytes_per_token(yahkv.FMT_Q8_0)
+        e_bytes = e_keys * layers * yahkv.bytes_per_token(fmt)
         e2e = {"bytes": e_bytes, "s": e_s,
                "h2d": layers * BATCH * (2 * 4 * 256 * 2 + 24 * 256 * 2), "d2h": layers * BATCH * 24 * 256 * 2}
 
@@ -285,7 +287,7 @@ def main():
             "metric": METRIC, "value": bytes_all / (ms * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-            "config": {"workload": f"batch32_decode_{layers}layers_q8_0_ctx1024-32768_page64", "seqs_per_gpu": BATCH,
+            "config": {"workload": f"batch32_decode_{layers}layers_{args.fmt}_ctx1024-32768_page64", "seqs_per_gpu": BATCH,
                        "layers": layers, "mean_ctx": float(lens.mean()), "pages_shuffled": True,
                        "l2": "inputs larger than L2: each layer reads its own ~1.2 GB of cache per step",
                        "sharding": "sequences partitioned across GPUs, no collective on the data path"},
@@ -296,7 +298,7 @@ def main():
                       "combine_us_per_launch": comb_ms / max(comb_n, 1) * 1e3,
                       "frac_of_nominal_8000": bytes_all / (ms * 1e-3) / 1e9 / world / 8000.0,
                       "device_bytes": cache.device_bytes()},
-            "roofline": {"kernel": "DecodePartKernel<q8_0>", "bound": "hbm", "achieved": achieved, "peak": peak,
+            "roofline": {"kernel": f"DecodePartKernel<{args.fmt}>", "bound": "hbm", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
                          "launches": part_n, "mean_us": part_mean_ms * 1e3, "traffic": None},
             "gpu_launches": launches, "clocks": clocks,

@@ -9,8 +9,14 @@
 // heads of the GQA group at once, so every cache byte is read from HBM exactly once per call. Each page's K and V
 // records are gathered through the block table with non-multicast TMA: two 2-D tiled copies per side (64 token rows
 // x 128 B, 128-byte swizzle, so the ldmatrix reads below are bank-conflict free) plus one bulk copy per side for the
-// 64 x 8 fp16 scales, all completing on one mbarrier per ring stage. The CTA's four warps take 16 keys of the page
-// each; there is no producer warp: whichever warp finishes a stage last refills it, so no warp waits for another.
+// 64 x 8 fp16 scales, all completing on one mbarrier per ring stage. There is no producer warp: whichever warp
+// finishes a stage last refills it, so no warp waits for another.
+//
+// Eight warps share a page: four key groups of 16 keys x two halves of the head dimension. The two warps of a key
+// group each compute the scores' partial sums over their 128 dims, swap them through shared memory (one 64-thread
+// named barrier per page), run the same softmax, and accumulate their own 128 output dims. Splitting the dims halves
+// the accumulator registers per thread, which is what lets 16 warps stay resident per SM; with fewer warps the kernel
+// is bound by instruction latency, not by HBM.
 //
 // The path is HBM-bound (2176 B per token per layer in q8_0), but at GQA 6 it needs 5.6 multiply-adds per byte, more
 // than the fp32 pipes can give at HBM rate, so the dot products run on the warp-level f16 tensor-core MMA with
@@ -45,9 +51,10 @@ namespace {
 #ifndef YAHKV_Q4_STAGES
 #define YAHKV_Q4_STAGES 5
 #endif
-constexpr int kWarps = 4;             // each takes 16 of a page's 64 keys
+constexpr int kKeyGroups = 4;              // 16 keys of a page each
+constexpr int kWarps = 2 * kKeyGroups;     // x two halves of the head dimension
 constexpr int kDecodeThreads = kWarps * 32;
-constexpr int kBoxBytes = 64 * 128;   // one swizzled TMA box: 64 token rows x 128 B
+constexpr int kBoxBytes = 64 * 128;        // one swizzled TMA box: 64 token rows x 128 B
 
 template <int kFmt>
 struct StageLayout {
@@ -59,23 +66,22 @@ struct StageLayout {
   static constexpr int kBytes = kVsOff + kRecordScaleBytes;  // 34816 (q8_0) or 18432 (q4_0), a multiple of 1024
   static constexpr int kStages = kFmt == kFmtQ8 ? YAHKV_Q8_STAGES : YAHKV_Q4_STAGES;
 };
-// Cross-warp merge scratch at the end of a unit: per warp acc [6][kMergeStride] f32 and (m, l) [8][2].
+// Cross-warp merge scratch at the end of a unit: per key group acc [6][kMergeStride] f32 and (m, l) [8][2].
 constexpr int kMergeStride = kHeadDim + 8;
-constexpr int kMergeWarpFloats = kGroup * kMergeStride + 16;
-constexpr int kMergeBytes = kWarps * kMergeWarpFloats * 4;
+constexpr int kMergeGroupFloats = kGroup * kMergeStride + 16;
+constexpr int kMergeBytes = kKeyGroups * kMergeGroupFloats * 4;
 
-// fp16 number b (0..7) of eight packed in a uint4, widened to f32. b is a compile-time constant after unrolling.
-__device__ __forceinline__ std::uint32_t WordOf(const uint4& v, int i) {
-  return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
-}
-__device__ __forceinline__ float ScaleOf(const uint4& v, int b) {
-  const __half2 h = *reinterpret_cast<const __half2*>(&reinterpret_cast<const std::uint32_t&>(
-      b < 2 ? v.x : b < 4 ? v.y : b < 6 ? v.z : v.w));
-  return (b & 1) ? __high2float(h) : __low2float(h);
+// fp16 number i (0..3) of four packed in a uint2, widened to f32. i is a compile-time constant after unrolling.
+__device__ __forceinline__ float ScaleOf(const uint2& v, int i) {
+  const std::uint32_t w = i < 2 ? v.x : v.y;
+  const __half2 h = *reinterpret_cast<const __half2*>(&w);
+  return (i & 1) ? __high2float(h) : __low2float(h);
 }
 
-// D = A * B with a zero accumulator input, rows 8-15 of A zero (the S^T step's first MMA of a block): no register
-// has to be cleared beforehand.
+// One S^T MMA step with a zero accumulator input: no register has to be cleared beforehand. The Q fragment of the
+// step comes from shared memory at use (volatile, so the compiler does not keep all fragments in registers), stored
+// there as the A operand's four registers (rows 8-15 of A, registers 1 and 3, are zero) so one 16-byte load fills
+// them without any register shuffling.
 __device__ __forceinline__ void MmaQZero(float (&d)[4], std::uint32_t q_addr, std::uint32_t b0, std::uint32_t b1) {
   std::uint32_t a0, a1, a2, a3;
   asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(q_addr));
@@ -85,20 +91,35 @@ __device__ __forceinline__ void MmaQZero(float (&d)[4], std::uint32_t q_addr, st
       : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0F));
 }
-// One S^T MMA step accumulating in place: the Q fragment of the step comes from shared memory at use (volatile, so
-// the compiler does not keep all sixteen fragments in registers), stored there as the A operand's four registers
-// (rows 8-15 of A, registers 1 and 3, are zero) so one 16-byte load fills them without any register shuffling.
+// The same step accumulating in place.
 __device__ __forceinline__ void MmaQ(float (&d)[4], std::uint32_t q_addr, std::uint32_t b0, std::uint32_t b1) {
   std::uint32_t a0, a1, a2, a3;
   asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(q_addr));
   MmaF16(d, a0, a1, a2, a3, b0, b1);
 }
 
+// Shared memory of a CTA, all dynamic so that the ring starts at the window's 1024-byte aligned base (the swizzled
+// TMA boxes need that alignment): ring | Q operands | score exchange | mbarriers | stage counters. Lanes 24-31 of a
+// warp hold the two padding heads of the 8-wide MMA; they reuse the Q operands of lanes 16-23 (finite duplicates of
+// heads 4, 5 whose results are never stored), so the Q and exchange arrays are 24 lanes wide.
+constexpr int kQLanes = 24;
+constexpr int kQfragBytes = 16 * kQLanes * 16;
+constexpr int kXchgBytes = kWarps * kQLanes * 16;
+template <int kFmt>
+struct SmemLayout {
+  static constexpr int kRing = StageLayout<kFmt>::kStages * StageLayout<kFmt>::kBytes;
+  static_assert(kRing >= kMergeBytes, "the merge scratch aliases the ring");
+  static constexpr int kQfragOff = kRing;
+  static constexpr int kXchgOff = kQfragOff + kQfragBytes;
+  static constexpr int kBarOff = kXchgOff + kXchgBytes;
+  static constexpr int kCntOff = kBarOff + 8 * StageLayout<kFmt>::kStages;
+  static constexpr int kBytes = kCntOff + 4 * StageLayout<kFmt>::kStages;
+};
 template <int kFmt>
 constexpr int DecodeSmemBytes() {
-  constexpr int ring = StageLayout<kFmt>::kStages * StageLayout<kFmt>::kBytes;
-  return (ring > kMergeBytes ? ring : kMergeBytes) + 1024;  // + slack to align the ring to 1024 B
+  return (SmemLayout<kFmt>::kBytes + 127) / 128 * 128;
 }
+constexpr int kStatusSmemMisaligned = 2;
 
 // Running max may lag the true max by this much (log2 units) before the accumulators are rescaled; weights stay
 // <= 2^4, so weight x scale fits fp16 for every representable fp16 input.
@@ -111,15 +132,22 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
                      const DecodeUnit* __restrict__ units, const __half* __restrict__ q, float scale_log2,
                      float* __restrict__ partial_acc, float* __restrict__ partial_ml, int* status) {
   using L = StageLayout<kFmt>;
-  extern __shared__ std::uint8_t smem_raw[];
-  __shared__ __align__(8) std::uint64_t full_bar[L::kStages];
-  __shared__ int done_cnt[L::kStages];   // warps that have finished reading the stage's current page
-  __shared__ uint4 qfrag[16 * 32];
-  std::uint8_t* ring = reinterpret_cast<std::uint8_t*>((reinterpret_cast<std::uintptr_t>(smem_raw) + 1023) &
-                                                       ~static_cast<std::uintptr_t>(1023));
+  using S = SmemLayout<kFmt>;
+  extern __shared__ __align__(1024) std::uint8_t smem_raw[];
+  std::uint8_t* ring = smem_raw;
+  uint4* qfrag = reinterpret_cast<uint4*>(smem_raw + S::kQfragOff);     // Q as MMA A operands [16 steps][24 lanes]
+  float4* xchg = reinterpret_cast<float4*>(smem_raw + S::kXchgOff);     // partial scores [8 warps][24 lanes]
+  std::uint64_t* full_bar = reinterpret_cast<std::uint64_t*>(smem_raw + S::kBarOff);
+  int* done_cnt = reinterpret_cast<int*>(smem_raw + S::kCntOff);        // warps done reading a stage's page
+  if ((SmemAddr(smem_raw) & 1023U) != 0) {   // never seen; checked because a misaligned swizzle would corrupt results
+    if (threadIdx.x == 0) atomicExch(status, kStatusSmemMisaligned);
+    return;
+  }
 
   const DecodeUnit u = units[blockIdx.x];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kw = warp >> 1;   // key group: keys 16 kw .. 16 kw + 15 of the page
+  const int dh = warp & 1;    // dim half: dims 128 dh .. 128 dh + 127 (blocks 4 dh .. 4 dh + 3)
   const int n_pages = u.page_end - u.page_begin;
   const std::int32_t* row = tables + static_cast<std::size_t>(u.seq) * table_stride + u.page_begin;
 
@@ -152,97 +180,103 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
   }
 
   const int g = lane >> 2, t = lane & 3;
-  // Q fragments through shared memory, shared by the four warps: MMA step c (16 dims) uses dims 16c + 4t + {0, 2} in
-  // k-slots (2t, 2t+1) and + {1, 3} in (2t+8, 2t+9).
+  // Q fragments through shared memory: MMA step c (16 dims) uses dims 16c + 4t + {0, 2} in k-slots (2t, 2t+1) and
+  // + {1, 3} in (2t+8, 2t+9).
   {
     const __half* qrow = q + (static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + g) * kHeadDim;
 #pragma unroll
     for (int cc = 0; cc < 16 / kWarps; ++cc) {
       const int c = warp * (16 / kWarps) + cc;
-      uint2 v = make_uint2(0, 0);
-      if (g < kGroup) v = *reinterpret_cast<const uint2*>(qrow + 16 * c + 4 * t);
-      qfrag[c * 32 + lane] = make_uint4(__byte_perm(v.x, v.y, 0x5410), 0U,   // halves (0, 2)
-                                        __byte_perm(v.x, v.y, 0x7632), 0U);  // halves (1, 3)
+      if (g < kGroup) {
+        const uint2 v = *reinterpret_cast<const uint2*>(qrow + 16 * c + 4 * t);
+        qfrag[c * kQLanes + lane] = make_uint4(__byte_perm(v.x, v.y, 0x5410), 0U,   // halves (0, 2)
+                                               __byte_perm(v.x, v.y, 0x7632), 0U);  // halves (1, 3)
+      }
     }
   }
   __syncthreads();   // barriers initialised, Q fragments visible
-  const std::uint32_t qa_addr = SmemAddr(qfrag + lane);
+  // This warp's eight MMA steps are c = 8 dh .. 8 dh + 7.
+  const int qlane = lane < kQLanes ? lane : lane - 8;
+  const std::uint32_t qa_addr = SmemAddr(qfrag + 8 * dh * kQLanes + qlane);
 
-  float o_acc[16][4];
+  float o_acc[8][4];   // tile c2 = dims 128 dh + 16 c2 .. + 15
 #pragma unroll
-  for (int c = 0; c < 16; ++c)
+  for (int c = 0; c < 8; ++c)
 #pragma unroll
     for (int i = 0; i < 4; ++i) o_acc[c][i] = 0.0F;
   float m_run = -INFINITY, l_run = 0.0F;
   bool alive = true;
 
-  // ldmatrix row addresses: lane supplies row (lane & 7) + 8 * ((lane >> 3) & 1) of the warp's 16 keys and the
+  // ldmatrix row addresses: lane supplies row (lane & 7) + 8 * ((lane >> 3) & 1) of the key group's 16 keys and the
   // 16-byte chunk 2x + (lane >> 4) of its 128-byte row, swizzled: physical chunk = chunk ^ (row & 7).
-  const int lm_key = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+  const int lm_key = kw * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
   std::uint32_t lm_off[4];
 #pragma unroll
   for (int x = 0; x < 4; ++x) lm_off[x] = lm_key * 128 + ((((2 * x) | (lane >> 4)) ^ (lm_key & 7)) << 4);
-  // Keys whose scores this thread holds: kt * 8 + 2t + j of the warp's 16.
-  const int my_key0 = warp * 16 + 2 * t;
+  // q8_0: the warp's dim half is one TMA box and all four chunk pairs of it. q4_0: the row is one box of eight
+  // 16-byte blocks and the warp's half is chunk pairs 2 dh, 2 dh + 1.
+  const std::uint32_t half_off = kFmt == kFmtQ8 ? dh * kBoxBytes : 0;
+  // Keys whose scores this thread holds: kt * 8 + 2t + j of the group's 16.
+  const int my_key0 = kw * 16 + 2 * t;
 
   for (int i = 0; i < n_pages; ++i) {
     const int s = i % L::kStages;
     // Table entry of the page that will take this stage next, fetched a whole iteration before it is needed.
     std::int32_t refill_page = 0;
     if (lane == 0 && i + L::kStages < n_pages) refill_page = __ldg(row + i + L::kStages);
-    if (!__all_sync(0xFFFFFFFFU, MbarWait(&full_bar[s], (i / L::kStages) & 1))) {
-      alive = false;
-      break;
-    }
+    // A wait that gives up does not leave the loop (its partner warp would hang at the pair barrier): the warp stops
+    // waiting, finishes on whatever the ring holds, and the status word marks the call's results invalid.
+    if (alive && !__all_sync(0xFFFFFFFFU, MbarWait(&full_bar[s], (i / L::kStages) & 1))) alive = false;
     const std::uint8_t* st = ring + s * L::kBytes;
-    const std::uint32_t k_base = SmemAddr(st + L::kKOff), v_base = SmemAddr(st + L::kVOff);
+    const std::uint32_t k_base = SmemAddr(st + L::kKOff) + half_off, v_base = SmemAddr(st + L::kVOff) + half_off;
 
-    // ---- S^T = Q K^T: per 32-element block an fp32 partial sum of exact products, times the block's fp16 scale ----
+    // ---- S^T = Q K^T over this warp's 128 dims: per 32-element block an fp32 partial sum of exact products, times
+    // the block's fp16 scale ----
     float sc[2][2] = {{0.0F, 0.0F}, {0.0F, 0.0F}};
     {
-      uint4 ks_raw[2][2];
+      uint2 ks_raw[2][2];   // scales of blocks 4 dh .. 4 dh + 3 of this thread's four keys
 #pragma unroll
       for (int kt = 0; kt < 2; ++kt)
 #pragma unroll
         for (int j = 0; j < 2; ++j)
-          ks_raw[kt][j] = *reinterpret_cast<const uint4*>(st + L::kKsOff + (my_key0 + kt * 8 + j) * 16);
+          ks_raw[kt][j] = *reinterpret_cast<const uint2*>(st + L::kKsOff + (my_key0 + kt * 8 + j) * 16 + dh * 8);
       if constexpr (kFmt == kFmtQ8) {
 #pragma unroll
-        for (int b = 0; b < 8; ++b) {
+        for (int b = 0; b < 4; ++b) {
           std::uint32_t w[4];
-          LdMatrixX4(k_base + (b >> 2) * kBoxBytes + lm_off[b & 3], w);
+          LdMatrixX4(k_base + lm_off[b], w);
           float a0[4], a1[4];
           std::uint32_t x0, x1;
           Int8x4ToHalf2(w[0], x0, x1);
-          MmaQZero(a0, qa_addr + (2 * b) * 512, x0, x1);
+          MmaQZero(a0, qa_addr + (2 * b) * (kQLanes * 16), x0, x1);
           Int8x4ToHalf2(w[1], x0, x1);
-          MmaQZero(a1, qa_addr + (2 * b) * 512, x0, x1);
+          MmaQZero(a1, qa_addr + (2 * b) * (kQLanes * 16), x0, x1);
           Int8x4ToHalf2(w[2], x0, x1);
-          MmaQ(a0, qa_addr + (2 * b + 1) * 512, x0, x1);
+          MmaQ(a0, qa_addr + (2 * b + 1) * (kQLanes * 16), x0, x1);
           Int8x4ToHalf2(w[3], x0, x1);
-          MmaQ(a1, qa_addr + (2 * b + 1) * 512, x0, x1);
+          MmaQ(a1, qa_addr + (2 * b + 1) * (kQLanes * 16), x0, x1);
           sc[0][0] = fmaf(ScaleOf(ks_raw[0][0], b), a0[0], sc[0][0]);
           sc[0][1] = fmaf(ScaleOf(ks_raw[0][1], b), a0[1], sc[0][1]);
           sc[1][0] = fmaf(ScaleOf(ks_raw[1][0], b), a1[0], sc[1][0]);
           sc[1][1] = fmaf(ScaleOf(ks_raw[1][1], b), a1[1], sc[1][1]);
         }
       } else {
-        // q4_0 rows are 128 B = 8 blocks of 16 packed bytes; one ldmatrix.x4 covers two blocks of 16 keys.
+        // One ldmatrix.x4 covers two 16-byte blocks of 16 keys.
 #pragma unroll
-        for (int bp = 0; bp < 4; ++bp) {
+        for (int bp = 0; bp < 2; ++bp) {
           std::uint32_t w[4];
-          LdMatrixX4(k_base + lm_off[bp], w);
+          LdMatrixX4(k_base + (dh ? lm_off[2 + bp] : lm_off[bp]), w);
 #pragma unroll
           for (int hb = 0; hb < 2; ++hb) {
-            const int b = 2 * bp + hb;
+            const int b = 2 * bp + hb;   // block 4 dh + b
             float a0[4], a1[4];
             std::uint32_t l0, l1, h0, h1;
             Nib4x4ToHalf2(w[2 * hb], l0, l1, h0, h1);
-            MmaQZero(a0, qa_addr + (2 * b) * 512, l0, l1);
-            MmaQ(a0, qa_addr + (2 * b + 1) * 512, h0, h1);
+            MmaQZero(a0, qa_addr + (2 * b) * (kQLanes * 16), l0, l1);
+            MmaQ(a0, qa_addr + (2 * b + 1) * (kQLanes * 16), h0, h1);
             Nib4x4ToHalf2(w[2 * hb + 1], l0, l1, h0, h1);
-            MmaQZero(a1, qa_addr + (2 * b) * 512, l0, l1);
-            MmaQ(a1, qa_addr + (2 * b + 1) * 512, h0, h1);
+            MmaQZero(a1, qa_addr + (2 * b) * (kQLanes * 16), l0, l1);
+            MmaQ(a1, qa_addr + (2 * b + 1) * (kQLanes * 16), h0, h1);
             sc[0][0] = fmaf(ScaleOf(ks_raw[0][0], b), a0[0], sc[0][0]);
             sc[0][1] = fmaf(ScaleOf(ks_raw[0][1], b), a0[1], sc[0][1]);
             sc[1][0] = fmaf(ScaleOf(ks_raw[1][0], b), a1[0], sc[1][0]);
@@ -250,6 +284,18 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
           }
         }
       }
+    }
+    // Swap the partial sums with the warp that holds the other 128 dims: write, pair barrier, read, pair barrier
+    // (the second one keeps the next page's write behind this page's read). a + b == b + a, so both warps continue
+    // with identical scores.
+    {
+      if (lane < kQLanes) xchg[warp * kQLanes + lane] = make_float4(sc[0][0], sc[0][1], sc[1][0], sc[1][1]);
+      NamedBarrierSync(1 + kw, 64);
+      if (lane < kQLanes) {
+        const float4 o = xchg[(warp ^ 1) * kQLanes + lane];
+        sc[0][0] += o.x, sc[0][1] += o.y, sc[1][0] += o.z, sc[1][1] += o.w;
+      }
+      NamedBarrierSync(1 + kw, 64);
     }
 
     // ---- softmax statistics (per head g, the 16 keys spread over the four lanes of a quad) ----
@@ -265,7 +311,9 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
       }
     tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFU, tmax, 1));
     tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFU, tmax, 2));
-    if (__any_sync(0xFFFFFFFFU, tmax > m_run + kLazyRescale)) {
+    // Only the six real heads vote: the padding lanes hold unexchanged partial scores that differ between the two
+    // warps of a pair, and both warps must take the same decision to keep one running max per key group.
+    if (__any_sync(0xFFFFFFFFU, lane < kQLanes && tmax > m_run + kLazyRescale)) {
       const float m_new = fmaxf(m_run, tmax);
       const float alpha = m_new == -INFINITY ? 1.0F : exp2f(m_run - m_new);  // m_run = -inf gives 0
       m_run = m_new;
@@ -273,7 +321,7 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
       const float al0 = __shfl_sync(0xFFFFFFFFU, alpha, (2 * t) * 4);
       const float al1 = __shfl_sync(0xFFFFFFFFU, alpha, (2 * t + 1) * 4);
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
+      for (int c = 0; c < 8; ++c) {
         o_acc[c][0] *= al0, o_acc[c][2] *= al0;
         o_acc[c][1] *= al1, o_acc[c][3] *= al1;
       }
@@ -290,20 +338,21 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
       p_lo[kt] = __floats2half2_rn(p0 - hf.x, p1 - hf.y);
     }
 
-    // ---- O^T += V^T P^T, the V scale of (key, block) folded into the weights ----
-    uint4 vs_raw[2][2];
+    // ---- O^T += V^T P^T over this warp's 128 dims, the V scale of (key, block) folded into the weights ----
+    uint2 vs_raw[2][2];
 #pragma unroll
     for (int kt = 0; kt < 2; ++kt)
 #pragma unroll
       for (int j = 0; j < 2; ++j)
-        vs_raw[kt][j] = *reinterpret_cast<const uint4*>(st + L::kVsOff + (my_key0 + kt * 8 + j) * 16);
+        vs_raw[kt][j] = *reinterpret_cast<const uint2*>(st + L::kVsOff + (my_key0 + kt * 8 + j) * 16 + dh * 8);
     // weight x scale without leaving fp16: hi = round(p_hi d); the rounding error of that product is recovered
     // exactly by an fma and joins the low part: lo = p_lo d + (p_hi d - hi).
     auto weights = [&](int b, std::uint32_t (&hi)[2], std::uint32_t (&lo)[2]) {
 #pragma unroll
       for (int kt = 0; kt < 2; ++kt) {
-        const std::uint32_t dw = __byte_perm(WordOf(vs_raw[kt][0], b >> 1), WordOf(vs_raw[kt][1], b >> 1),
-                                             (b & 1) ? 0x7632 : 0x5410);
+        const std::uint32_t w0 = b < 2 ? vs_raw[kt][0].x : vs_raw[kt][0].y;
+        const std::uint32_t w1 = b < 2 ? vs_raw[kt][1].x : vs_raw[kt][1].y;
+        const std::uint32_t dw = __byte_perm(w0, w1, (b & 1) ? 0x7632 : 0x5410);
         const __half2 d2 = *reinterpret_cast<const __half2*>(&dw);
         const __half2 h = __hmul2(p_hi[kt], d2);
         const __half2 r = __hfma2(p_hi[kt], d2, __hneg2(h));
@@ -314,11 +363,11 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
     };
     if constexpr (kFmt == kFmtQ8) {
 #pragma unroll
-      for (int b = 0; b < 8; ++b) {
+      for (int b = 0; b < 4; ++b) {
         std::uint32_t hi[2], lo[2];
         weights(b, hi, lo);
         std::uint32_t w[4];
-        LdMatrixX4Trans(v_base + (b >> 2) * kBoxBytes + lm_off[b & 3], w);
+        LdMatrixX4Trans(v_base + lm_off[b], w);
         std::uint32_t a0, a1, a2, a3;
         Int8x4ToHalf2(w[0], a0, a1);
         Int8x4ToHalf2(w[1], a2, a3);
@@ -331,16 +380,16 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
       }
     } else {
 #pragma unroll
-      for (int bp = 0; bp < 4; ++bp) {
+      for (int bp = 0; bp < 2; ++bp) {
         std::uint32_t w[4];
-        LdMatrixX4Trans(v_base + lm_off[bp], w);
+        LdMatrixX4Trans(v_base + (dh ? lm_off[2 + bp] : lm_off[bp]), w);
 #pragma unroll
         for (int hb = 0; hb < 2; ++hb) {
           const int b = 2 * bp + hb;
           std::uint32_t hi[2], lo[2];
           weights(b, hi, lo);
           std::uint32_t la0, la1, ha0, ha1, la2, la3, ha2, ha3;
-          Nib4x4ToHalf2(w[2 * hb], la0, la1, ha0, ha1);      // keys 0-7 of the warp's 16
+          Nib4x4ToHalf2(w[2 * hb], la0, la1, ha0, ha1);      // keys 0-7 of the group's 16
           Nib4x4ToHalf2(w[2 * hb + 1], la2, la3, ha2, ha3);  // keys 8-15
           MmaF16(o_acc[2 * b], la0, la1, la2, la3, hi[0], hi[1]);
           MmaF16(o_acc[2 * b], la0, la1, la2, la3, lo[0], lo[1]);
@@ -350,7 +399,7 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
       }
     }
 
-    // The last of the four warps to finish with the stage refills it (no warp ever waits for another one). The
+    // The last of the eight warps to finish with the stage refills it (no warp ever waits for another one). The
     // MMAs above consumed every ldmatrix result, so this warp's reads of the stage are complete.
     __syncwarp();
     if (lane == 0) {
@@ -370,9 +419,9 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
   __syncthreads();
   float* merge = reinterpret_cast<float*>(ring);
   {
-    float* mine = merge + warp * kMergeWarpFloats;
+    float* mine = merge + kw * kMergeGroupFloats + 128 * dh;
 #pragma unroll
-    for (int c = 0; c < 16; ++c) {
+    for (int c = 0; c < 8; ++c) {
       // o_acc[c][0..3] = (dim 16c + 2g, head 2t), (dim 16c + 2g, head 2t+1), (dim 16c + 2g + 1, head 2t), (.., 2t+1)
       if (2 * t < kGroup) {
         *reinterpret_cast<float2*>(mine + (2 * t) * kMergeStride + 16 * c + 2 * g) =
@@ -381,35 +430,34 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
             make_float2(o_acc[c][1], o_acc[c][3]);
       }
     }
-    if (t == 0 && g < kGroup) {
-      mine[kGroup * kMergeStride + 2 * g] = m_run;
-      mine[kGroup * kMergeStride + 2 * g + 1] = l_run;
+    if (dh == 0 && t == 0 && g < kGroup) {
+      float* ml = merge + kw * kMergeGroupFloats + kGroup * kMergeStride;
+      ml[2 * g] = m_run;
+      ml[2 * g + 1] = l_run;
     }
   }
   __syncthreads();
   {
-    const int tid = threadIdx.x;  // 0..127: two dims per thread per head
+    const int tid = threadIdx.x;  // 0..255: one dim per thread per head
     float* acc_out = partial_acc + static_cast<std::size_t>(u.partial) * kPartialAccFloats;
     float* ml_out = partial_ml + static_cast<std::size_t>(u.partial) * kPartialMlFloats;
 #pragma unroll
     for (int h = 0; h < kGroup; ++h) {
-      float mw[kWarps], M = -INFINITY;
+      float mw[kKeyGroups], M = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < kWarps; ++w) {
-        mw[w] = merge[w * kMergeWarpFloats + kGroup * kMergeStride + 2 * h];
+      for (int w = 0; w < kKeyGroups; ++w) {
+        mw[w] = merge[w * kMergeGroupFloats + kGroup * kMergeStride + 2 * h];
         M = fmaxf(M, mw[w]);
       }
-      float2 a = make_float2(0.0F, 0.0F);
-      float lsum = 0.0F;
+      float a = 0.0F, lsum = 0.0F;
 #pragma unroll
-      for (int w = 0; w < kWarps; ++w) {
+      for (int w = 0; w < kKeyGroups; ++w) {
         const float wgt = mw[w] == -INFINITY ? 0.0F : exp2f(mw[w] - M);
-        const float* src = merge + w * kMergeWarpFloats;
-        const float2 v = *reinterpret_cast<const float2*>(src + h * kMergeStride + 2 * tid);
-        a.x = fmaf(wgt, v.x, a.x), a.y = fmaf(wgt, v.y, a.y);
+        const float* src = merge + w * kMergeGroupFloats;
+        a = fmaf(wgt, src[h * kMergeStride + tid], a);
         lsum = fmaf(wgt, src[kGroup * kMergeStride + 2 * h + 1], lsum);
       }
-      *reinterpret_cast<float2*>(acc_out + h * kHeadDim + 2 * tid) = a;
+      acc_out[h * kHeadDim + tid] = a;
       if (tid == 0) ml_out[2 * h] = M, ml_out[2 * h + 1] = lsum;
     }
   }
