@@ -130,7 +130,9 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
     DecodePartKernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                      PoolView pool, int layer, const std::int32_t* __restrict__ tables, int table_stride,
                      const DecodeUnit* __restrict__ units, const __half* __restrict__ q, float scale_log2,
-                     float* __restrict__ partial_acc, float* __restrict__ partial_ml, int* status) {
+                     float* __restrict__ partial_acc, float* __restrict__ partial_ml, int* status,
+                     const CombineItem* __restrict__ items, int* counters, const float* __restrict__ gate, void* out,
+                     int out_f32) {
   using L = StageLayout<kFmt>;
   using S = SmemLayout<kFmt>;
   extern __shared__ __align__(1024) std::uint8_t smem_raw[];
@@ -219,14 +221,15 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
   // Keys whose scores this thread holds: kt * 8 + 2t + j of the group's 16.
   const int my_key0 = kw * 16 + 2 * t;
 
+  int s = 0;                  // ring stage of page i, and the parity of the mbarrier phase that fills it
+  std::uint32_t phase = 0;
   for (int i = 0; i < n_pages; ++i) {
-    const int s = i % L::kStages;
     // Table entry of the page that will take this stage next, fetched a whole iteration before it is needed.
     std::int32_t refill_page = 0;
     if (lane == 0 && i + L::kStages < n_pages) refill_page = __ldg(row + i + L::kStages);
     // A wait that gives up does not leave the loop (its partner warp would hang at the pair barrier): the warp stops
     // waiting, finishes on whatever the ring holds, and the status word marks the call's results invalid.
-    if (alive && !__all_sync(0xFFFFFFFFU, MbarWait(&full_bar[s], (i / L::kStages) & 1))) alive = false;
+    if (alive && !__all_sync(0xFFFFFFFFU, MbarWait(&full_bar[s], phase))) alive = false;
     const std::uint8_t* st = ring + s * L::kBytes;
     const std::uint32_t k_base = SmemAddr(st + L::kKOff) + half_off, v_base = SmemAddr(st + L::kVOff) + half_off;
 
@@ -305,8 +308,8 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
     for (int kt = 0; kt < 2; ++kt)
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        const bool valid = key_pos0 + kt * 8 + j < u.n_keys;
-        sc[kt][j] = valid ? sc[kt][j] * scale_log2 : -INFINITY;
+        sc[kt][j] *= scale_log2;
+        if (key_pos0 + kt * 8 + j >= u.n_keys) sc[kt][j] = -INFINITY;   // only ever true on a sequence's last page
         tmax = fmaxf(tmax, sc[kt][j]);
       }
     tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFU, tmax, 1));
@@ -315,7 +318,7 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
     // warps of a pair, and both warps must take the same decision to keep one running max per key group.
     if (__any_sync(0xFFFFFFFFU, lane < kQLanes && tmax > m_run + kLazyRescale)) {
       const float m_new = fmaxf(m_run, tmax);
-      const float alpha = m_new == -INFINITY ? 1.0F : exp2f(m_run - m_new);  // m_run = -inf gives 0
+      const float alpha = m_new == -INFINITY ? 1.0F : Exp2Fast(m_run - m_new);  // m_run = -inf gives 0
       m_run = m_new;
       l_run *= alpha;
       const float al0 = __shfl_sync(0xFFFFFFFFU, alpha, (2 * t) * 4);
@@ -331,7 +334,7 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
     __half2 p_hi[2], p_lo[2];
 #pragma unroll
     for (int kt = 0; kt < 2; ++kt) {
-      const float p0 = exp2f(sc[kt][0] - m_use), p1 = exp2f(sc[kt][1] - m_use);
+      const float p0 = Exp2Fast(sc[kt][0] - m_use), p1 = Exp2Fast(sc[kt][1] - m_use);
       l_run += p0 + p1;
       p_hi[kt] = __floats2half2_rn(p0, p1);
       const float2 hf = __half22float2(p_hi[kt]);
@@ -410,6 +413,7 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
         if (i + L::kStages < n_pages) issue(s, refill_page);
       }
     }
+    if (++s == L::kStages) s = 0, phase ^= 1U;
   }
   if (!alive && lane == 0) atomicExch(status, kStatusWaitTimeout);
   l_run += __shfl_xor_sync(0xFFFFFFFFU, l_run, 1);
@@ -461,42 +465,123 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
       if (tid == 0) ml_out[2 * h] = M, ml_out[2 * h + 1] = lsum;
     }
   }
+  if (counters == nullptr) return;   // a separate combine launch follows
+
+  // ---- the unit that arrives last at its (sequence, kv head) counter merges that pair's partials ----
+  // (the reference's dattn_reduce, engine/gpu/loom/tools/gen_decode_attn.py:373-408, without a second launch: no unit
+  // waits for another; partials are merged in unit order whatever the arrival order, so results do not depend on it)
+  const int item_idx = u.batch * kKvHeads + u.kvh;
+  const CombineItem it = items[item_idx];
+  __threadfence();   // this unit's partial is visible device-wide before its arrival is counted
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const bool last = atomicAdd(&counters[item_idx], 1) == it.n_partials - 1;
+    if (last) counters[item_idx] = 0;   // re-armed for the next call
+    done_cnt[0] = last ? 1 : 0;
+  }
+  __syncthreads();
+  if (done_cnt[0] == 0) return;
+  __threadfence();
+  {
+    // Step 1: every unit's (max, sum) pairs into shared memory with independent loads (the ring is free again).
+    // Step 2: per head the overall max and each unit's weight 2^(m - M). Step 3: thread = output dim, all loads of
+    // the weighted sum independent of each other.
+    float* ml_s = reinterpret_cast<float*>(ring);                       // [n_partials][12]
+    float* w_s = ml_s + static_cast<std::size_t>(it.n_partials) * kPartialMlFloats;   // [n_partials][6]
+    float* l_s = w_s + static_cast<std::size_t>(it.n_partials) * kGroup;               // [6] overall sums
+    const float* ml_g = partial_ml + static_cast<std::size_t>(it.first_partial) * kPartialMlFloats;
+    for (int e = threadIdx.x; e < it.n_partials * kPartialMlFloats; e += kDecodeThreads) ml_s[e] = __ldcg(ml_g + e);
+    __syncthreads();
+    if (threadIdx.x < kGroup) {
+      const int h = threadIdx.x;
+      float M = -INFINITY;
+      for (int i = 0; i < it.n_partials; ++i) M = fmaxf(M, ml_s[i * kPartialMlFloats + 2 * h]);
+      float Lsum = 0.0F;
+      for (int i = 0; i < it.n_partials; ++i) {   // in unit order
+        const float m = ml_s[i * kPartialMlFloats + 2 * h];
+        const float w = m == -INFINITY ? 0.0F : Exp2Fast(m - M);
+        w_s[i * kGroup + h] = w;
+        Lsum = fmaf(w, ml_s[i * kPartialMlFloats + 2 * h + 1], Lsum);
+      }
+      l_s[h] = Lsum;
+    }
+    __syncthreads();
+    const int d = threadIdx.x;
+    const float* acc_g = partial_acc + static_cast<std::size_t>(it.first_partial) * kPartialAccFloats + d;
+    float A[kGroup];
+#pragma unroll
+    for (int h = 0; h < kGroup; ++h) A[h] = 0.0F;
+#pragma unroll 2
+    for (int i = 0; i < it.n_partials; ++i) {
+      float v[kGroup];
+#pragma unroll
+      for (int h = 0; h < kGroup; ++h) v[h] = __ldcg(acc_g + static_cast<std::size_t>(i) * kPartialAccFloats + h * kHeadDim);
+#pragma unroll
+      for (int h = 0; h < kGroup; ++h) A[h] = fmaf(w_s[i * kGroup + h], v[h], A[h]);
+    }
+#pragma unroll
+    for (int h = 0; h < kGroup; ++h) {
+      float o = A[h] * (1.0F / l_s[h]);
+      const std::size_t oi = (static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + h) * kHeadDim + d;
+      if (gate != nullptr) o *= 1.0F / (1.0F + expf(-gate[oi]));
+      if (out_f32)
+        static_cast<float*>(out)[oi] = o;
+      else
+        static_cast<__half*>(out)[oi] = __float2half_rn(o);
+    }
+  }
 }
 
-// Merge the units of one (batch row, query head): out = (sum w_i acc_i) / (sum w_i l_i) * sigmoid(gate), with
-// w_i = 2^(m_i - M), accumulated in unit order (engine/gpu/loom/tools/gen_decode_attn.py:373-408).
-__global__ void __launch_bounds__(kHeadDim / 2)
+// Merge the units of one (batch row, query head): out = (sum w_i acc_i) / (sum w_i l_i) * sigmoid(gate) with
+// w_i = 2^(m_i - M), accumulated in unit order (engine/gpu/loom/tools/gen_decode_attn.py:373-408). One CTA per head,
+// thread = output dim. The merge is latency-bound, so the weights are prepared in shared memory first and the loads
+// of the weighted sum are all independent of each other.
+constexpr int kCombineMaxUnits = 1024;
+__global__ void __launch_bounds__(kHeadDim)
     DecodeCombineKernel(const CombineItem* __restrict__ items, const float* __restrict__ partial_acc,
                         const float* __restrict__ partial_ml, const float* __restrict__ gate, void* out, int out_f32) {
+  __shared__ float m_s[kCombineMaxUnits], w_s[kCombineMaxUnits];
+  __shared__ float red_s[kHeadDim / 32];
+  __shared__ float inv_l;
   const int b = blockIdx.x / kQHeads, hh = blockIdx.x % kQHeads;
   const int kvh = hh / kGroup, j = hh % kGroup;
   const CombineItem it = items[b * kKvHeads + kvh];
-  float M = -INFINITY;
-  for (int i = 0; i < it.n_partials; ++i)
-    M = fmaxf(M, partial_ml[static_cast<std::size_t>(it.first_partial + i) * kPartialMlFloats + 2 * j]);
-  float2 A = make_float2(0.0F, 0.0F);
-  float Lsum = 0.0F;
-  const int d = 2 * threadIdx.x;
-  for (int i = 0; i < it.n_partials; ++i) {
-    const std::size_t pi = static_cast<std::size_t>(it.first_partial + i);
-    const float m = partial_ml[pi * kPartialMlFloats + 2 * j];
-    const float w = m == -INFINITY ? 0.0F : exp2f(m - M);
-    const float2 v = *reinterpret_cast<const float2*>(partial_acc + pi * kPartialAccFloats + j * kHeadDim + d);
-    A.x = fmaf(w, v.x, A.x), A.y = fmaf(w, v.y, A.y);
-    Lsum = fmaf(w, partial_ml[pi * kPartialMlFloats + 2 * j + 1], Lsum);
+  const int n = min(it.n_partials, kCombineMaxUnits);   // the planner never exceeds it
+  const float* ml_g = partial_ml + static_cast<std::size_t>(it.first_partial) * kPartialMlFloats + 2 * j;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // overall max
+  float mx = -INFINITY;
+  for (int i = tid; i < n; i += kHeadDim) {
+    const float m = ml_g[static_cast<std::size_t>(i) * kPartialMlFloats];
+    m_s[i] = m;
+    mx = fmaxf(mx, m);
   }
-  const float inv = 1.0F / Lsum;
-  float2 o = make_float2(A.x * inv, A.y * inv);
-  const std::size_t oi = (static_cast<std::size_t>(b) * kQHeads + hh) * kHeadDim + d;
-  if (gate != nullptr) {
-    const float2 gt = *reinterpret_cast<const float2*>(gate + oi);
-    o.x *= 1.0F / (1.0F + expf(-gt.x));
-    o.y *= 1.0F / (1.0F + expf(-gt.y));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFU, mx, o));
+  if (lane == 0) red_s[warp] = mx;
+  __syncthreads();
+  float M = red_s[0];
+#pragma unroll
+  for (int w = 1; w < kHeadDim / 32; ++w) M = fmaxf(M, red_s[w]);
+  for (int i = tid; i < n; i += kHeadDim) w_s[i] = m_s[i] == -INFINITY ? 0.0F : Exp2Fast(m_s[i] - M);
+  __syncthreads();
+  if (tid == 0) {   // the sum of the units' sums in unit order (few terms, kept sequential so the result is reproducible)
+    float Lsum = 0.0F;
+    for (int i = 0; i < n; ++i) Lsum = fmaf(w_s[i], ml_g[static_cast<std::size_t>(i) * kPartialMlFloats + 1], Lsum);
+    inv_l = 1.0F / Lsum;
   }
+  const float* acc_g = partial_acc + static_cast<std::size_t>(it.first_partial) * kPartialAccFloats + j * kHeadDim + tid;
+  float A = 0.0F;
+#pragma unroll 8
+  for (int i = 0; i < n; ++i) A = fmaf(w_s[i], acc_g[static_cast<std::size_t>(i) * kPartialAccFloats], A);
+  __syncthreads();
+  float o = A * inv_l;
+  const std::size_t oi = (static_cast<std::size_t>(b) * kQHeads + hh) * kHeadDim + tid;
+  if (gate != nullptr) o *= 1.0F / (1.0F + expf(-gate[oi]));
   if (out_f32)
-    *reinterpret_cast<float2*>(static_cast<float*>(out) + oi) = o;
+    static_cast<float*>(out)[oi] = o;
   else
-    *reinterpret_cast<__half2*>(static_cast<__half*>(out) + oi) = __floats2half2_rn(o.x, o.y);
+    static_cast<__half*>(out)[oi] = __float2half_rn(o);
 }
 
 }  // namespace
@@ -515,18 +600,18 @@ cudaError_t LaunchDecodePart(const DecodeLaunch& a, cudaStream_t stream) {
   if (a.pool.fmt == kFmtQ8)
     DecodePartKernel<kFmtQ8><<<a.n_units, kDecodeThreads, DecodeSmemBytes<kFmtQ8>(), stream>>>(
         *a.kmap, *a.vmap, a.pool, a.layer, a.tables_dev, a.table_stride, a.units_dev, q, a.scale_log2, a.partial_acc,
-        a.partial_ml, a.status_dev);
+        a.partial_ml, a.status_dev, a.items_dev, a.counters_dev, a.gate_dev, a.out_dev, a.out_f32);
   else
     DecodePartKernel<kFmtQ4><<<a.n_units, kDecodeThreads, DecodeSmemBytes<kFmtQ4>(), stream>>>(
         *a.kmap, *a.vmap, a.pool, a.layer, a.tables_dev, a.table_stride, a.units_dev, q, a.scale_log2, a.partial_acc,
-        a.partial_ml, a.status_dev);
+        a.partial_ml, a.status_dev, a.items_dev, a.counters_dev, a.gate_dev, a.out_dev, a.out_f32);
   return cudaGetLastError();
 }
 
 cudaError_t LaunchDecodeCombine(const DecodeLaunch& a, cudaStream_t stream) {
-  if (a.n_units <= 0 || a.n_seqs <= 0) return cudaSuccess;
-  DecodeCombineKernel<<<a.n_seqs * kQHeads, kHeadDim / 2, 0, stream>>>(a.items_dev, a.partial_acc, a.partial_ml,
-                                                                      a.gate_dev, a.out_dev, a.out_f32);
+  if (a.n_units <= 0 || a.n_seqs <= 0 || a.counters_dev != nullptr) return cudaSuccess;  // merged in the part kernel
+  DecodeCombineKernel<<<a.n_seqs * kQHeads, kHeadDim, 0, stream>>>(a.items_dev, a.partial_acc, a.partial_ml,
+                                                                  a.gate_dev, a.out_dev, a.out_f32);
   return cudaGetLastError();
 }
 

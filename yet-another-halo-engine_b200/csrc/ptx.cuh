@@ -101,11 +101,19 @@ __device__ __forceinline__ void NamedBarrierSync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// 2^x on the special-function unit, one instruction (flush-to-zero; exact powers of two for integer x, -inf -> 0).
+__device__ __forceinline__ float Exp2Fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // Four int8 codes in a word -> two half2 of exact integers: bytes (0, 2) and bytes (1, 3).
-// 0x6400 | u is the fp16 value 1024 + u; with u = code + 128 the code is that minus 1152.
+// 0x6400 | u is the fp16 value 1024 + u; with u = code + 128 (the sign bit flipped) the code is that minus 1152.
 __device__ __forceinline__ void Int8x4ToHalf2(std::uint32_t w, std::uint32_t& h02, std::uint32_t& h13) {
-  const std::uint32_t lo = (w & 0x00FF00FFU) ^ 0x64806480U;
-  const std::uint32_t hi = __byte_perm(w, 0x64646464U, 0x4341) ^ 0x00800080U;
+  const std::uint32_t u = w ^ 0x80808080U;
+  const std::uint32_t lo = __byte_perm(u, 0x64646464U, 0x4240);
+  const std::uint32_t hi = __byte_perm(u, 0x64646464U, 0x4341);
   const __half2 bias = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));
   const __half2 a = __hsub2(*reinterpret_cast<const __half2*>(&lo), bias);
   const __half2 b = __hsub2(*reinterpret_cast<const __half2*>(&hi), bias);
