@@ -52,8 +52,9 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    """nvidia-smi clocks and throttle reasons sampled every 50 ms; started ahead of the warm-up (the tool takes a
+    moment to come up) and cut to the timed region by its own timestamps."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
@@ -61,17 +62,29 @@ class ClockSampler:
         self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         try:
             self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms",
-                                       "200", "-i", str(gpu_index)], stdout=self.f, stderr=subprocess.DEVNULL)
+                                       "50", "-i", str(gpu_index)], stdout=self.f, stderr=subprocess.DEVNULL)
         except OSError:
             self.p = None
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
+        """t_begin / t_end: time.time() bounds of the timed region (None = keep every sample)."""
         if self.p is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.p.terminate()
         self.p.wait()
         self.f.flush()
-        rows = [r.split(", ") for r in open(self.f.name).read().strip().splitlines() if r.strip()]
+        import datetime
+        rows = []
+        for r in open(self.f.name).read().strip().splitlines():
+            r = r.split(", ")
+            if len(r) < 9:
+                continue
+            try:
+                ts = datetime.datetime.strptime(r[0].strip(), "%Y/%m/%d %H:%M:%S.%f").timestamp()
+            except ValueError:
+                ts = None
+            if ts is None or t_begin is None or (t_begin - 0.05 <= ts <= t_end + 0.05):
+                rows.append(r)
         os.unlink(self.f.name)
         sm = [float(r[1]) for r in rows if len(r) >= 9]
         reasons = set()
@@ -125,15 +138,18 @@ def reference_arm(args, rank):
         return
     t0 = time.perf_counter()
     vals = []
+    t_steps = []
     for _ in range(max(1, min(args.steps, 3))):
+        ts = time.perf_counter()
         gbs, mtok, threads, sample = cpu_arm(reps=1)
+        t_steps.append(time.perf_counter() - ts)
         vals.append(gbs)
     gbs = float(np.median(vals))
     import oracle as O
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "u8", "data": "synthetic",
+        "warmup": args.warmup, "ms_per_step": float(np.median(t_steps)) * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
         "config": {"workload": "batch32_decode_16layers_q8_0_ctx1024-32768_page64", "note":
                    "CPU arm; the reference has no CPU attention, so attention is the oracle port of its numpy checker "
                    "and append is its QuantizeQ8_0 arithmetic"},
@@ -148,8 +164,8 @@ def reference_arm(args, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="yahkv", choices=["yahkv", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers per step (16 = the configuration)")
     ap.add_argument("--fmt", default="q8_0", choices=["q8_0", "q4_0"], help="cache format (q8_0 = the configuration)")
@@ -219,22 +235,24 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank) if rank == 0 else None
     for _ in range(args.warmup):
         step()
     barrier()
     cache.kernel_timing(True)
     launches0 = cache.launch_count()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    t_begin = time.time()
     ev0.record(stream)
     keys = 0
     for _ in range(args.steps):
         keys += step()
     ev1.record(stream)
     barrier()
+    t_end = time.time()
     ms = ev0.elapsed_time(ev1)
-    clocks = sampler.stop() if sampler else None
+    clocks = sampler.stop(t_begin, t_end) if sampler else None
     launches = cache.launch_count() - launches0
     part_ms, part_n = cache.kernel_timing_read(yahkv.KERNEL_DECODE_PART)
     comb_ms, comb_n = cache.kernel_timing_read(yahkv.KERNEL_DECODE_COMBINE)
