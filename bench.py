@@ -35,6 +35,9 @@ for p in (os.path.join(ROOT, "yet-another-halo-engine_b200"), os.path.join(ROOT,
 
 LAYERS, BATCH, CTX_LO, CTX_HI = 16, 32, 1024, 32768
 METRIC, UNIT = "q8_0_paged_decode_attn_kv_gbps", "GB/s"
+# DRAM bytes per algorithmic byte of the split-K attention kernel, from an ncu capture of one full-size launch of this
+# workload (1.238842 GB read + 11.02 MB written for 1.236479 GB of cache): profiles/decode_part_q8_0_batch32.md.
+NCU_DRAM_PER_ALGORITHMIC_BYTE = {"q8_0": 1.0108}
 
 
 def workload(rank, layers):
@@ -325,11 +328,11 @@ def main():
             line["e2e"] = {"value": e_bytes_all / e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"],
                            "d2h_bytes_per_step": e2e["d2h"], "steps": e2e_steps - 1,
                            "api": "yahkv_decode_step_host per layer (pinned host K/V/q in, output back to host)"}
-        traffic_path = os.path.join(ROOT, "profiles", "decode_part_q8_0_traffic.json")
-        if os.path.exists(traffic_path):
-            t = json.load(open(traffic_path))
-            line["roofline"]["traffic"] = t["dram_bytes_per_algorithmic_byte"] * part_bytes
-            line["roofline"]["traffic_note"] = t["note"]
+        if args.fmt in NCU_DRAM_PER_ALGORITHMIC_BYTE:
+            line["roofline"]["traffic"] = NCU_DRAM_PER_ALGORITHMIC_BYTE[args.fmt] * part_bytes
+            line["roofline"]["traffic_note"] = ("(dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of "
+                                                "one ncu-captured launch of this workload, times this run's bytes "
+                                                "per launch")
         if world == 1 and not args.no_cpu:
             gbs, mtok, threads, sample = cpu_arm()
             line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample,
