@@ -150,7 +150,8 @@ int yahkv_launch_count(const yahkv_ctx* ctx, int64_t* launches);
 #define YAHKV_KERNEL_DECODE_PART 1
 #define YAHKV_KERNEL_DECODE_COMBINE 2
 #define YAHKV_KERNEL_PREFILL 3
-#define YAHKV_KERNEL_COUNT 4
+#define YAHKV_KERNEL_PREFILL_DEQUANT 4
+#define YAHKV_KERNEL_COUNT 5
 int yahkv_kernel_timing(yahkv_ctx* ctx, int32_t enable);
 int yahkv_kernel_timing_read(yahkv_ctx* ctx, int32_t kernel, double* total_ms, int64_t* launches);
 

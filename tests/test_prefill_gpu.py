@@ -1,0 +1,99 @@
+"""Chunked-prefill attention on the GPU (fp16 dequantize pass + tcgen05 kernel) against the float64 oracle.
+Tolerance: 2e-3 max-abs with fp32 softmax accumulation, on fp16 Q/K/V ~ N(0,1) as the benchmark configuration has."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as O
+import yahkv
+from gpu_util import dev
+
+pytestmark = pytest.mark.gpu
+ABS_TOL = 2e-3
+
+
+def build(fmt, cached, chunks, seed, n_layers=1, layer=0):
+    """Sequences with `cached[i]` tokens appended earlier and a chunk of `chunks[i]` tokens appended now."""
+    rng = np.random.default_rng(seed)
+    totals = [a + b for a, b in zip(cached, chunks)]
+    num_pages = sum((n + 63) // 64 for n in totals) + 3
+    cache = yahkv.KvCache(n_layers=n_layers, num_pages=num_pages, fmt=fmt, max_seqs=len(totals),
+                          max_pages_per_seq=max((n + 63) // 64 for n in totals), max_batch_tokens=4096)
+    pool = O.PagedPool(fmt, num_pages)
+    free = list(rng.permutation(num_pages))
+    seqs, tables = [], []
+    for n, c0 in zip(totals, cached):
+        s = cache.seq_create()
+        table = np.array([free.pop() for _ in range((n + 63) // 64)], np.int32)
+        cache.seq_set_table(s, table)
+        K = rng.standard_normal((n, 4, 256)).astype(np.float16)
+        V = rng.standard_normal((n, 4, 256)).astype(np.float16)
+        if c0:
+            cache.append(layer, np.full(c0, s, np.int32), np.arange(c0), dev(K[:c0]), dev(V[:c0]))
+        cache.append(layer, np.full(n - c0, s, np.int32), np.arange(c0, n), dev(K[c0:]), dev(V[c0:]))   # the chunk
+        pool.append(table, 0, K, V)
+        seqs.append(s); tables.append(table)
+    return cache, pool, seqs, tables, rng
+
+
+def run_prefill(cache, layer, seqs, chunks, q, gate, out_dtype):
+    rows = sum(chunks)
+    out = torch.full((rows, 24, 256), float("nan"), device="cuda",
+                     dtype=torch.float32 if out_dtype == yahkv.OUT_F32 else torch.float16)
+    cache.attend_prefill(layer, seqs, chunks, dev(q), out, gate=None if gate is None else dev(gate), out_dtype=out_dtype)
+    cache.sync()
+    return out.float().cpu().numpy().astype(np.float64)
+
+
+@pytest.mark.parametrize("fmt", [yahkv.FMT_Q8_0, yahkv.FMT_Q4_0])
+def test_one_sequence_cache_plus_chunk(fmt):
+    cached, chunk = 200, 130
+    cache, pool, seqs, tables, rng = build(fmt, [cached], [chunk], seed=41)
+    q = rng.standard_normal((chunk, 24, 256)).astype(np.float16)
+    gate = rng.standard_normal((chunk, 24, 256)).astype(np.float32)
+    want = pool.attend_prefill_f64(tables[0], cached, q, gate=gate)
+    got = run_prefill(cache, 0, seqs, [chunk], q, gate, yahkv.OUT_F32)
+    err = np.abs(got - want).reshape(chunk, -1).max(1)
+    assert err.max() <= ABS_TOL, (int(err.argmax()), err.max())
+    got16 = run_prefill(cache, 0, seqs, [chunk], q, None, yahkv.OUT_F16)
+    want_plain = pool.attend_prefill_f64(tables[0], cached, q)
+    assert np.abs(got16 - want_plain).max() <= ABS_TOL + np.abs(want_plain).max() * 2.0 ** -11
+
+
+def test_ragged_batch_of_chunks():
+    cached = [0, 63, 500, 1000, 64]
+    chunks = [100, 1, 129, 300, 128]
+    cache, pool, seqs, tables, rng = build(yahkv.FMT_Q8_0, cached, chunks, seed=42, n_layers=2, layer=1)
+    q = rng.standard_normal((sum(chunks), 24, 256)).astype(np.float16)
+    got = run_prefill(cache, 1, seqs, chunks, q, None, yahkv.OUT_F32)
+    row = 0
+    for i, c in enumerate(chunks):
+        want = pool.attend_prefill_f64(tables[i], cached[i], q[row:row + c])
+        err = np.abs(got[row:row + c] - want).max()
+        assert err <= ABS_TOL, (i, err)
+        row += c
+
+
+def test_prefill_rows_equal_decode_of_the_same_position():
+    # the last row of a chunk is exactly a decode step over the whole sequence
+    cached, chunk = 300, 70
+    cache, pool, seqs, tables, rng = build(yahkv.FMT_Q8_0, [cached], [chunk], seed=43)
+    q = rng.standard_normal((chunk, 24, 256)).astype(np.float16)
+    got = run_prefill(cache, 0, seqs, [chunk], q, None, yahkv.OUT_F32)
+    dec = torch.zeros(1, 24, 256, device="cuda")
+    cache.attend_decode(0, seqs, dev(q[-1:]), dec, out_dtype=yahkv.OUT_F32)
+    cache.sync()
+    assert np.abs(got[-1] - dec.cpu().numpy()[0]).max() <= ABS_TOL
+
+
+def test_prefill_errors_launch_nothing():
+    cache, pool, seqs, tables, rng = build(yahkv.FMT_Q8_0, [10], [5], seed=44)
+    q = torch.zeros(20, 24, 256, dtype=torch.float16, device="cuda")
+    out = torch.zeros(20, 24, 256, dtype=torch.float16, device="cuda")
+    before = cache.launch_count()
+    for seq_ids, chunks, code in (([seqs[0]], [16], yahkv.ERR_ORDER), ([seqs[0]], [0], yahkv.ERR_INVALID),
+                                  ([3], [1], yahkv.ERR_INVALID)):
+        with pytest.raises(yahkv.YahkvError) as e:
+            cache.attend_prefill(0, seq_ids, chunks, q, out)
+        assert e.value.code == code
+    assert cache.launch_count() == before

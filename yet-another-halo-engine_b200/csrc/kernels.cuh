@@ -53,13 +53,25 @@ struct CombineItem {
   std::int32_t n_partials;
 };
 
-// One tile of prefill attention: 64 query rows of one sequence for one kv head.
-struct PrefillTile {
+// Prefill attention reads a dequantized fp16 copy of the sequences' K and V (the reference's yah_kdeq / yah_vdeq
+// pre-pass, engine/gpu/loom/tools/gen_attn_fa.py:4648-4860): rows [kv_row0 + kvh * kv_rows, ...) of the scratch hold
+// kv head kvh of the sequence, token-major, 256 fp16 each, kv_rows = the length rounded up to whole pages.
+struct PrefillSeq {
   std::int32_t seq;         // block-table row
-  std::int32_t kvh;
+  std::int32_t n_pages;     // pages holding keys 0 .. kv_len - 1
+  std::int32_t kv_len;      // keys in the cache, the chunk included
+  std::int32_t kv_rows;     // n_pages * 64
+  std::int32_t kv_row0;     // first scratch row of the sequence
+  std::int32_t pad[3];
+};
+// One tile of prefill attention: 128 query rows of one sequence for one query head.
+constexpr int kPrefillTileRows = 128;
+struct PrefillTile {
+  std::int32_t kv_row0;     // first scratch row of (sequence, kv head of this query head)
+  std::int32_t head;        // query head
   std::int32_t q_row0;      // first packed query row of the tile
-  std::int32_t n_rows;      // valid query rows in the tile (<= 64)
-  std::int32_t pos0;        // position of the tile's first query row
+  std::int32_t n_rows;      // valid query rows in the tile (<= 128)
+  std::int32_t pos0;        // position of the tile's first query row; row r sees keys 0 .. pos0 + r
   std::int32_t pad[3];
 };
 
@@ -99,23 +111,32 @@ cudaError_t LaunchDecodeCombine(const DecodeLaunch& a, cudaStream_t stream);
 cudaError_t ConfigureDecodeKernels();
 
 struct PrefillLaunch {
-  const CUtensorMap* kmap;
-  const CUtensorMap* vmap;
   PoolView pool;
   int layer;
   const std::int32_t* tables_dev;
   int table_stride;
+  const PrefillSeq* seqs_dev;
+  int n_seqs;
+  int max_pages;            // largest n_pages of the call (grid of the dequantize pass)
+  void* k16_dev;            // fp16 scratch [rows][256], K and V
+  void* v16_dev;
+  const CUtensorMap* qmap;  // q as [rows][24 * 256] fp16, box 64 x 128, 128-byte swizzle
+  const CUtensorMap* k16map;  // scratch as [rows][256] fp16, box 64 x 64, 128-byte swizzle
+  const CUtensorMap* v16map;
   const PrefillTile* tiles_dev;
   int n_tiles;
-  const void* q_dev;
   const float* gate_dev;
   void* out_dev;
   int out_f32;
   float scale_log2;
   int* status_dev;
 };
+cudaError_t LaunchPrefillDequant(const PrefillLaunch& a, cudaStream_t stream);
 cudaError_t LaunchPrefill(const PrefillLaunch& a, cudaStream_t stream);
 cudaError_t ConfigurePrefillKernels();
+// Encodes a 2-D tiled tensor map (row-major, `inner` elements of `elem_bytes` per row, 128-byte swizzle). Host only.
+bool EncodeTensorMap2D(CUtensorMap* map, int elem_bytes, void* base, std::uint64_t inner, std::uint64_t rows,
+                       std::uint32_t box_inner, std::uint32_t box_rows);
 
 // Status codes the kernels write into the sticky status word.
 constexpr int kStatusWaitTimeout = 1;

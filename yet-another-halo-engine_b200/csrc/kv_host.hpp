@@ -261,14 +261,18 @@ class KvHost {
   const std::vector<DecodeUnit>& units() const { return units_; }
   const std::vector<CombineItem>& items() const { return items_; }
 
-  // Tiles of one prefill call: 64 query rows x one kv head each, longest keys first within the call.
+  // Work lists of one prefill call: per sequence the span of the fp16 scratch it is dequantized into, and tiles of
+  // 128 query rows x one query head, the ones with the most keys first so that the short ones fill the tail.
   HostError PlanPrefill(int layer, int n_seqs, const std::int32_t* seq_ids, const std::int32_t* chunk_lens,
-                        int max_rows, std::vector<PrefillTile>* tiles, std::int64_t* total_rows) {
+                        int max_rows, std::vector<PrefillSeq>* seqs, std::vector<PrefillTile>* tiles,
+                        std::int64_t* total_rows, std::int64_t* scratch_rows, int* max_pages) {
     if (layer < 0 || layer >= cfg_.n_layers) return {YAHKV_ERR_INVALID, "attend_prefill: layer out of range"};
     if (n_seqs < 0 || (n_seqs > 0 && (seq_ids == nullptr || chunk_lens == nullptr)))
       return {YAHKV_ERR_INVALID, "attend_prefill: bad sequence list"};
+    seqs->clear();
     tiles->clear();
-    std::int64_t row = 0;
+    std::int64_t row = 0, kv_row = 0;
+    *max_pages = 0;
     for (int i = 0; i < n_seqs; ++i) {
       const int s = seq_ids[i];
       if (!live(s)) return {YAHKV_ERR_INVALID, "attend_prefill: not a live sequence: " + std::to_string(s)};
@@ -278,22 +282,33 @@ class KvHost {
       if (c > n)
         return {YAHKV_ERR_ORDER, "attend_prefill: chunk of " + std::to_string(c) + " rows but sequence " +
                                      std::to_string(s) + " holds " + std::to_string(n) + " keys (append first)"};
-      for (int r = 0; r < c; r += 64)
-        for (int h = 0; h < kKvHeads; ++h) {
+      PrefillSeq ps{};
+      ps.seq = s;
+      ps.n_pages = static_cast<std::int32_t>((n + kPageTokens - 1) / kPageTokens);
+      ps.kv_len = static_cast<std::int32_t>(n);
+      ps.kv_rows = ps.n_pages * kPageTokens;
+      ps.kv_row0 = static_cast<std::int32_t>(kv_row);
+      seqs->push_back(ps);
+      *max_pages = std::max(*max_pages, static_cast<int>(ps.n_pages));
+      for (int r = 0; r < c; r += kPrefillTileRows)
+        for (int h = 0; h < kQHeads; ++h) {
           PrefillTile t{};
-          t.seq = s, t.kvh = h;
+          t.kv_row0 = static_cast<std::int32_t>(kv_row + static_cast<std::int64_t>(h / kGroup) * ps.kv_rows);
+          t.head = h;
           t.q_row0 = static_cast<std::int32_t>(row + r);
-          t.n_rows = std::min(64, c - r);
+          t.n_rows = std::min(kPrefillTileRows, c - r);
           t.pos0 = static_cast<std::int32_t>(n - c + r);
           tiles->push_back(t);
         }
       row += c;
+      kv_row += static_cast<std::int64_t>(kKvHeads) * ps.kv_rows;
+      if (kv_row >= (1LL << 31)) return {YAHKV_ERR_CAPACITY, "attend_prefill: too many cached keys in one call"};
     }
     if (row > max_rows) return {YAHKV_ERR_CAPACITY, "attend_prefill: more query rows than max_batch_tokens"};
-    // Tiles with the most keys first, so the short ones fill the tail.
     std::stable_sort(tiles->begin(), tiles->end(),
                      [](const PrefillTile& a, const PrefillTile& b) { return a.pos0 + a.n_rows > b.pos0 + b.n_rows; });
     *total_rows = row;
+    *scratch_rows = kv_row;
     return {};
   }
 

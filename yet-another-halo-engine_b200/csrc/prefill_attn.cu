@@ -1,7 +1,463 @@
-// Placeholder until the tcgen05 kernel lands: reports "not supported" so callers fail loudly.
+// Chunked-prefill attention over the quantized cache: the one dense contraction of the path, on tcgen05 tensor cores
+// with TMEM accumulators, fed by TMA.
+//
+// Stands in for the reference's yah_attn_wmma (causal FlashAttention over the paged cache, f16 MMA with f32
+// accumulate, online softmax with exp2, f16 P, o / sum * sigmoid(gate): engine/gpu/loom/tools/gen_attn_fa.py:1-22,
+// :67-71, :2897-2904, :3005-3042) together with its dequantize pre-pass yah_kdeq* / yah_vdeq* (:4648-4860), which
+// the reference measured as a win over decoding at staging (docs/results.md:206). Like the reference's kernel it is
+// not bit-identical to any ordering; the parity bar is 2e-3 max-abs against the float64 oracle.
+//
+// Pass 1, DequantPagesKernel (HBM-bound): every page of every sequence of the call, through the block table, to a
+// token-major fp16 scratch (K and V), value = fp16(code * scale). 34.8 KB read and 64 KB written per page and kv head.
+//
+// Pass 2, PrefillKernel (tensor-bound): one CTA per tile of 128 query rows of one query head; head_dim 256.
+//   S = Q K^T   tcgen05.mma kind::f16, M 128, N 64 (one 64-key tile), K 256 in 16 steps; A = Q from shared memory
+//               (K-major, 128-byte swizzle, four 64-dim TMA boxes), B = the K tile (same layout), D = S in TMEM.
+//   softmax     four warps, one thread per query row: tcgen05.ld of the row, causal mask, running max with a lazy
+//               rescale of O (threshold 2^8), P = 2^(s - m) as fp16 into shared memory in the A-operand layout.
+//   O += P V    tcgen05.mma M 128, N 256, K 64 in 4 steps; A = P from shared memory, B = the V tile as loaded
+//               (token-major = MN-major B operand, 128-byte swizzle), D = O in TMEM (256 columns).
+// TMEM columns: S double-buffered 2 x 64, O 256. Shared memory: Q 64 KB, K ring 2 x 32 KB, V ring 2 x 32 KB, P 16 KB.
+// Warp roles: 0-3 softmax / correction / epilogue, 4 TMA producer, 5 MMA issuer and TMEM owner. No multicast, no
+// cluster. Every mbarrier wait is bounded and abortable: a wait that gives up raises a CTA-wide abort flag, every
+// role leaves its loop, TMEM is freed, and the status word tells the host the call's results are invalid.
+//
+// The six query heads of a GQA group are separate CTAs here, so a K/V tile is re-read from L2 by six CTAs
+// (arithmetic intensity 128 flop per byte of shared-memory fill); pairing CTAs on one tile (cta_group::2) is the
+// next step for this kernel.
+#include <cuda_fp16.h>
+
+#include <cmath>
+
 #include "kernels.cuh"
+#include "ptx.cuh"
 
 namespace yahkv {
-cudaError_t ConfigurePrefillKernels() { return cudaSuccess; }
-cudaError_t LaunchPrefill(const PrefillLaunch&, cudaStream_t) { return cudaErrorNotSupported; }
+namespace {
+
+// ----------------------------------------------------------------------------------------------------------------
+// Pass 1: dequantize pages to fp16
+// ----------------------------------------------------------------------------------------------------------------
+constexpr int kDequantThreads = 256;
+
+template <int kFmt>
+__global__ void __launch_bounds__(kDequantThreads)
+    DequantPagesKernel(PoolView pool, int layer, const std::int32_t* __restrict__ tables, int table_stride,
+                       const PrefillSeq* __restrict__ seqs, __half* __restrict__ k16, __half* __restrict__ v16) {
+  const PrefillSeq ps = seqs[blockIdx.z];
+  const int p = blockIdx.x, kvh = blockIdx.y;
+  if (p >= ps.n_pages) return;
+  std::int32_t page = __ldg(tables + static_cast<std::size_t>(ps.seq) * table_stride + p);
+  page = min(max(page, 0), pool.num_pages - 1);
+  const std::size_t rec = (static_cast<std::size_t>(layer) * pool.num_pages + page) * kKvHeads + kvh;
+  const std::size_t out_row0 = static_cast<std::size_t>(ps.kv_row0) + static_cast<std::size_t>(kvh) * ps.kv_rows +
+                               static_cast<std::size_t>(p) * kPageTokens;
+#pragma unroll
+  for (int side = 0; side < 2; ++side) {
+    const std::uint8_t* codes = (side == 0 ? pool.kcodes : pool.vcodes) + rec * RecordCodeBytes(kFmt);
+    const std::uint16_t* scales = (side == 0 ? pool.kscales : pool.vscales) + rec * (kPageTokens * kBlocksPerRow);
+    __half* out = (side == 0 ? k16 : v16) + out_row0 * kHeadDim;
+    // thread -> 8 consecutive elements of a token row; 64 tokens x 32 groups = 2048 groups, 8 per thread
+    for (int gidx = threadIdx.x; gidx < kPageTokens * (kHeadDim / 8); gidx += kDequantThreads) {
+      const int tok = gidx >> 5, grp = gidx & 31;   // grp: elements 8 grp .. 8 grp + 7, block grp / 4
+      const float d = __half2float(__ushort_as_half(scales[tok * kBlocksPerRow + (grp >> 2)]));
+      float v[8];
+      if constexpr (kFmt == kFmtQ8) {
+        const uint2 c = *reinterpret_cast<const uint2*>(codes + tok * 256 + grp * 8);
+        const std::int8_t* cb = reinterpret_cast<const std::int8_t*>(&c);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = d * static_cast<float>(cb[i]);
+      } else {
+        // block b = grp / 4 occupies bytes 16 b .. 16 b + 15; element e of the block is the low (e < 16) or high
+        // nibble of byte e % 16. This group holds elements 8 (grp % 4) .. + 7 of its block.
+        const int e0 = (grp & 3) * 8;
+        const uint2 c = *reinterpret_cast<const uint2*>(codes + tok * 128 + (grp >> 2) * 16 + (e0 & 15));
+        const std::uint8_t* cb = reinterpret_cast<const std::uint8_t*>(&c);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = d * static_cast<float>(static_cast<int>(e0 < 16 ? (cb[i] & 0xF) : (cb[i] >> 4)) - 8);
+      }
+      uint4 o;
+      __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) oh[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+      *reinterpret_cast<uint4*>(out + static_cast<std::size_t>(tok) * kHeadDim + grp * 8) = o;
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------------------------------
+// Pass 2: tcgen05 flash attention
+// ----------------------------------------------------------------------------------------------------------------
+constexpr int kTileM = kPrefillTileRows;   // 128 query rows
+constexpr int kTileN = 64;                 // keys per KV tile
+constexpr int kPrefillThreads = 192;       // warps 0-3 softmax, 4 TMA, 5 MMA
+constexpr int kQBytes = kTileM * kHeadDim * 2;       // 65536: four [128][64] boxes
+constexpr int kKvTileBytes = kTileN * kHeadDim * 2;  // 32768: four [64][64] boxes
+constexpr int kPBytes = kTileM * kTileN * 2;         // 16384: [128][64] fp16
+constexpr int kKvStages = 2;
+constexpr int kSmemQ = 0;
+constexpr int kSmemK = kSmemQ + kQBytes;
+constexpr int kSmemV = kSmemK + kKvStages * kKvTileBytes;
+constexpr int kSmemP = kSmemV + kKvStages * kKvTileBytes;
+constexpr int kSmemBars = kSmemP + kPBytes;
+constexpr int kPrefillSmemBytes = kSmemBars + 256;
+// TMEM columns
+constexpr int kTmemCols = 512;
+constexpr int kColS = 0;      // two S buffers of 64 columns
+constexpr int kColO = 128;    // 256 columns
+constexpr float kPrefillLazyRescale = 8.0F;
+constexpr int kStatusPrefillAbort = 3;
+
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
+//   K-major operand  [rows][64 fp16]: rows 128 B apart, groups of 8 rows 1024 B apart (stride byte offset).
+//   MN-major operand [keys][64 fp16] x blocks: 8-key groups 1024 B apart (stride), 64-element blocks `lbo` apart.
+__device__ __forceinline__ std::uint64_t SmemDesc(std::uint32_t addr, std::uint32_t lbo_bytes, std::uint32_t sbo_bytes) {
+  std::uint64_t d = 0;
+  d |= static_cast<std::uint64_t>((addr >> 4) & 0x3FFFU);
+  d |= static_cast<std::uint64_t>((lbo_bytes >> 4) & 0x3FFFU) << 16;
+  d |= static_cast<std::uint64_t>((sbo_bytes >> 4) & 0x3FFFU) << 32;
+  d |= 1ULL << 46;   // version
+  d |= 2ULL << 61;   // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor of kind::f16: fp16 A and B, fp32 accumulate, A K-major.
+__host__ __device__ constexpr std::uint32_t InstrDesc(int m, int n, bool b_mn_major) {
+  return (1U << 4) | (0U << 7) | (0U << 10) | (0U << 15) | ((b_mn_major ? 1U : 0U) << 16) |
+         (static_cast<std::uint32_t>(n >> 3) << 17) | (static_cast<std::uint32_t>(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void UmmaF16(std::uint32_t d_tmem, std::uint64_t a_desc, std::uint64_t b_desc,
+                                        std::uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate ? 1U : 0U)
+      : "memory");
+}
+__device__ __forceinline__ void UmmaCommit(std::uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(SmemAddr(bar))
+               : "memory");
+}
+__device__ __forceinline__ void TcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void TcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void TmemLd32(std::uint32_t addr, std::uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(addr));
+}
+__device__ __forceinline__ void TmemSt32(std::uint32_t addr, const std::uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
+      "%15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(addr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void TmemWaitLd() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void TmemWaitSt() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Bounded, abortable wait: gives up after ~2 s or as soon as another role has raised the abort flag.
+__device__ __forceinline__ bool WaitOrAbort(std::uint64_t* bar, std::uint32_t parity, volatile int* abort_flag) {
+  if (MbarTryWait(bar, parity)) return true;
+  const std::uint64_t t0 = GlobalTimerNs();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (MbarTryWait(bar, parity)) return true;
+    if (*abort_flag != 0) return false;
+    if (GlobalTimerNs() - t0 > 2000000000ULL) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+struct PrefillBars {
+  std::uint64_t q_full;
+  std::uint64_t k_full[kKvStages], k_empty[kKvStages];
+  std::uint64_t v_full[kKvStages], v_empty[kKvStages];
+  std::uint64_t s_full[2], s_free[2];
+  std::uint64_t p_full;    // softmax -> MMA: P(j) written, O rescaled
+  std::uint64_t pv_done;   // MMA -> softmax: O += P(j) V(j) complete
+  std::uint32_t tmem_base;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(kPrefillThreads, 1)
+    PrefillKernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
+                  const __grid_constant__ CUtensorMap vmap, const PrefillTile* __restrict__ tiles,
+                  const float* __restrict__ gate, void* out, int out_f32, float scale_log2, int* status) {
+  extern __shared__ __align__(1024) std::uint8_t smem[];
+  PrefillBars* bars = reinterpret_cast<PrefillBars*>(smem + kSmemBars);
+  volatile int* abort_flag = &bars->abort_flag;
+  const PrefillTile tile = tiles[blockIdx.x];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kv_len = tile.pos0 + tile.n_rows;                 // keys any row of the tile can see
+  const int n_tiles = (kv_len + kTileN - 1) / kTileN;
+
+  if ((SmemAddr(smem) & 1023U) != 0) {   // the swizzled operands need the 1024-byte aligned base
+    if (threadIdx.x == 0) atomicExch(status, kStatusPrefillAbort);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    MbarInit(&bars->q_full, 1);
+    for (int s = 0; s < kKvStages; ++s) {
+      MbarInit(&bars->k_full[s], 1);
+      MbarInit(&bars->k_empty[s], 1);
+      MbarInit(&bars->v_full[s], 1);
+      MbarInit(&bars->v_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      MbarInit(&bars->s_full[b], 1);
+      MbarInit(&bars->s_free[b], kTileM);
+    }
+    MbarInit(&bars->p_full, kTileM);
+    MbarInit(&bars->pv_done, 1);
+    bars->abort_flag = 0;
+    FenceBarrierInit();
+  }
+  if (warp == 5) {   // TMEM: one warp allocates, the same warp frees
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(&bars->tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  TcFenceBefore();
+  __syncthreads();
+  TcFenceAfter();
+  const std::uint32_t tmem = bars->tmem_base;
+
+  if (warp == 4) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      PrefetchTensorMap(&qmap);
+      PrefetchTensorMap(&kmap);
+      PrefetchTensorMap(&vmap);
+      MbarArriveExpectTx(&bars->q_full, kQBytes);
+      for (int kb = 0; kb < 4; ++kb)
+        TmaLoad2D(smem + kSmemQ + kb * (kTileM * 128), &qmap, tile.head * kHeadDim + kb * 64, tile.q_row0, &bars->q_full);
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % kKvStages;
+        const std::uint32_t ph = static_cast<std::uint32_t>(j / kKvStages) & 1U;
+        const int y = tile.kv_row0 + j * kTileN;
+        if (j >= kKvStages) ok = WaitOrAbort(&bars->k_empty[s], ph ^ 1U, abort_flag);
+        if (!ok) break;
+        MbarArriveExpectTx(&bars->k_full[s], kKvTileBytes);
+        for (int kb = 0; kb < 4; ++kb)
+          TmaLoad2D(smem + kSmemK + s * kKvTileBytes + kb * (kTileN * 128), &kmap, kb * 64, y, &bars->k_full[s]);
+        if (j >= kKvStages) ok = WaitOrAbort(&bars->v_empty[s], ph ^ 1U, abort_flag);
+        if (!ok) break;
+        MbarArriveExpectTx(&bars->v_full[s], kKvTileBytes);
+        for (int kb = 0; kb < 4; ++kb)
+          TmaLoad2D(smem + kSmemV + s * kKvTileBytes + kb * (kTileN * 128), &vmap, kb * 64, y, &bars->v_full[s]);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr std::uint32_t idesc_s = InstrDesc(kTileM, kTileN, false);
+      constexpr std::uint32_t idesc_o = InstrDesc(kTileM, kHeadDim, true);
+      const std::uint32_t q_addr = SmemAddr(smem + kSmemQ), p_addr = SmemAddr(smem + kSmemP);
+      auto issue_pv = [&](int j) -> bool {   // O += P(j) V(j)
+        const int s = j % kKvStages;
+        if (!WaitOrAbort(&bars->v_full[s], static_cast<std::uint32_t>(j / kKvStages) & 1U, abort_flag)) return false;
+        if (!WaitOrAbort(&bars->p_full, static_cast<std::uint32_t>(j) & 1U, abort_flag)) return false;
+        TcFenceAfter();
+        const std::uint32_t v_addr = SmemAddr(smem + kSmemV + s * kKvTileBytes);
+#pragma unroll
+        for (int k16 = 0; k16 < kTileN / 16; ++k16)
+          UmmaF16(tmem + kColO, SmemDesc(p_addr + k16 * 32, 16, 1024),
+                  SmemDesc(v_addr + k16 * (16 * 128), kTileN * 128, 1024), idesc_o, j > 0 || k16 > 0);
+        UmmaCommit(&bars->v_empty[s]);
+        UmmaCommit(&bars->pv_done);
+        return true;
+      };
+      bool ok = WaitOrAbort(&bars->q_full, 0, abort_flag);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % kKvStages, b = j & 1;
+        ok = WaitOrAbort(&bars->k_full[s], static_cast<std::uint32_t>(j / kKvStages) & 1U, abort_flag);
+        if (ok && j >= 2) ok = WaitOrAbort(&bars->s_free[b], static_cast<std::uint32_t>((j >> 1) - 1) & 1U, abort_flag);
+        if (!ok) break;
+        TcFenceAfter();
+        const std::uint32_t k_addr = SmemAddr(smem + kSmemK + s * kKvTileBytes);
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb)
+#pragma unroll
+          for (int k16 = 0; k16 < 4; ++k16)
+            UmmaF16(tmem + kColS + b * kTileN, SmemDesc(q_addr + kb * (kTileM * 128) + k16 * 32, 16, 1024),
+                    SmemDesc(k_addr + kb * (kTileN * 128) + k16 * 32, 16, 1024), idesc_s, kb > 0 || k16 > 0);
+        UmmaCommit(&bars->k_empty[s]);
+        UmmaCommit(&bars->s_full[b]);
+        // the previous tile's P.V goes behind this tile's S, so the tensor pipe has work while softmax(j) runs
+        if (j >= 1) ok = issue_pv(j - 1);
+      }
+      if (ok && n_tiles > 0) issue_pv(n_tiles - 1);
+    }
+  } else {
+    // ------------------------------ softmax, correction, epilogue: thread = query row ------------------------------
+    const int r = threadIdx.x;                                   // 0..127
+    const std::uint32_t lane_addr = tmem + (static_cast<std::uint32_t>(warp * 32) << 16);
+    const int my_last_key = tile.pos0 + r;                       // row r sees keys 0 .. pos0 + r
+    float m_run = -INFINITY, l_run = 0.0F;
+    std::uint8_t* p_row = smem + kSmemP + r * 128;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int b = j & 1;
+      ok = WaitOrAbort(&bars->s_full[b], static_cast<std::uint32_t>(j >> 1) & 1U, abort_flag);
+      ok = __all_sync(0xFFFFFFFFU, ok);
+      if (!ok) break;
+      TcFenceAfter();
+      std::uint32_t sraw[2][32];
+      TmemLd32(lane_addr + kColS + b * kTileN, sraw[0]);
+      TmemLd32(lane_addr + kColS + b * kTileN + 32, sraw[1]);
+      TmemWaitLd();
+      TcFenceBefore();
+      MbarArrive(&bars->s_free[b]);
+      // scores in log2 units, causal mask on the tiles that reach past this row's position
+      const int key0 = j * kTileN;
+      float tmax = -INFINITY;
+      float sc[kTileN];
+#pragma unroll
+      for (int c = 0; c < kTileN; ++c) {
+        float v = __uint_as_float(sraw[c >> 5][c & 31]) * scale_log2;
+        if (key0 + c > my_last_key) v = -INFINITY;
+        sc[c] = v;
+        tmax = fmaxf(tmax, v);
+      }
+      // P(j-1) V(j-1) must be complete before O is rescaled or the P buffer is overwritten
+      if (j >= 1) {
+        ok = WaitOrAbort(&bars->pv_done, static_cast<std::uint32_t>(j - 1) & 1U, abort_flag);
+        ok = __all_sync(0xFFFFFFFFU, ok);
+        if (!ok) break;
+        TcFenceAfter();
+      }
+      const bool need = tmax > m_run + kPrefillLazyRescale;
+      if (__any_sync(0xFFFFFFFFU, need)) {   // warp-uniform: TMEM loads and stores are warp-wide
+        const float m_new = need ? tmax : m_run;
+        const float alpha = m_new == -INFINITY ? 1.0F : Exp2Fast(m_run - m_new);
+        m_run = m_new;
+        l_run *= alpha;
+        if (j >= 1) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
+            std::uint32_t o[32];
+            TmemLd32(lane_addr + kColO + c0, o);
+            TmemWaitLd();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+            TmemSt32(lane_addr + kColO + c0, o);
+          }
+          TmemWaitSt();
+        }
+      }
+      const float m_use = m_run == -INFINITY ? 0.0F : m_run;
+      // P row: 64 fp16 = eight 16-byte chunks, chunk c stored at c ^ (row & 7) (the 128-byte swizzle of the operand)
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        uint4 pk;
+        __half2* ph = reinterpret_cast<__half2*>(&pk);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float p0 = Exp2Fast(sc[ch * 8 + 2 * i] - m_use), p1 = Exp2Fast(sc[ch * 8 + 2 * i + 1] - m_use);
+          ph[i] = __floats2half2_rn(p0, p1);
+          // the sum uses the rounded weights, so numerator and denominator agree
+          const float2 pf = __half22float2(ph[i]);
+          l_run += pf.x + pf.y;
+        }
+        *reinterpret_cast<uint4*>(p_row + ((ch ^ (r & 7)) << 4)) = pk;
+      }
+      FenceProxyAsync();   // generic-proxy writes of P visible to the tensor core's async proxy
+      TcFenceBefore();
+      MbarArrive(&bars->p_full);
+    }
+    // ---- epilogue: O / l * sigmoid(gate) ----
+    if (ok && n_tiles > 0) {
+      ok = WaitOrAbort(&bars->pv_done, static_cast<std::uint32_t>(n_tiles - 1) & 1U, abort_flag);
+      ok = __all_sync(0xFFFFFFFFU, ok);
+    }
+    if (ok && n_tiles > 0) {
+      TcFenceAfter();
+      const float inv = 1.0F / l_run;
+      const bool valid = r < tile.n_rows;
+      const std::size_t oi = (static_cast<std::size_t>(tile.q_row0 + r) * kQHeads + tile.head) * kHeadDim;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
+        std::uint32_t o[32];
+        TmemLd32(lane_addr + kColO + c0, o);
+        TmemWaitLd();
+        if (valid) {
+          float v[32];
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            v[c] = __uint_as_float(o[c]) * inv;
+            if (gate != nullptr) v[c] *= 1.0F / (1.0F + expf(-gate[oi + c0 + c]));
+          }
+          if (out_f32) {
+            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(out) + oi + c0);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) dst[c] = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+          } else {
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(out) + oi + c0);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint4 pk;
+              __half2* ph = reinterpret_cast<__half2*>(&pk);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) ph[i] = __floats2half2_rn(v[8 * c + 2 * i], v[8 * c + 2 * i + 1]);
+              dst[c] = pk;
+            }
+          }
+        }
+      }
+    }
+  }
+  // ---- teardown: every role arrives here, also after an abort ----
+  TcFenceBefore();
+  __syncthreads();
+  if (threadIdx.x == 0 && bars->abort_flag != 0) atomicExch(status, kStatusPrefillAbort);
+  if (warp == 5) {
+    TcFenceAfter();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+}  // namespace
+
+cudaError_t ConfigurePrefillKernels() {
+  return cudaFuncSetAttribute(PrefillKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmemBytes);
+}
+
+cudaError_t LaunchPrefillDequant(const PrefillLaunch& a, cudaStream_t stream) {
+  if (a.n_seqs <= 0 || a.max_pages <= 0) return cudaSuccess;
+  const dim3 grid(static_cast<unsigned>(a.max_pages), kKvHeads, static_cast<unsigned>(a.n_seqs));
+  auto* k16 = static_cast<__half*>(a.k16_dev);
+  auto* v16 = static_cast<__half*>(a.v16_dev);
+  if (a.pool.fmt == kFmtQ8)
+    DequantPagesKernel<kFmtQ8><<<grid, kDequantThreads, 0, stream>>>(a.pool, a.layer, a.tables_dev, a.table_stride,
+                                                                     a.seqs_dev, k16, v16);
+  else
+    DequantPagesKernel<kFmtQ4><<<grid, kDequantThreads, 0, stream>>>(a.pool, a.layer, a.tables_dev, a.table_stride,
+                                                                     a.seqs_dev, k16, v16);
+  return cudaGetLastError();
+}
+
+cudaError_t LaunchPrefill(const PrefillLaunch& a, cudaStream_t stream) {
+  if (a.n_tiles <= 0) return cudaSuccess;
+  PrefillKernel<<<a.n_tiles, kPrefillThreads, kPrefillSmemBytes, stream>>>(*a.qmap, *a.k16map, *a.v16map, a.tiles_dev,
+                                                                          a.gate_dev, a.out_dev, a.out_f32,
+                                                                          a.scale_log2, a.status_dev);
+  return cudaGetLastError();
+}
+
 }  // namespace yahkv

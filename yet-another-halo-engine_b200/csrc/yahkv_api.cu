@@ -115,6 +115,11 @@ struct yahkv_ctx {
   std::vector<std::int64_t> slot_scratch;
   std::vector<std::int64_t> pos_scratch;
   std::vector<PrefillTile> tile_scratch;
+  std::vector<PrefillSeq> pseq_scratch;
+  PrefillSeq* pseqs_dev = nullptr;
+  void *k16_dev = nullptr, *v16_dev = nullptr;   // fp16 scratch of the prefill dequantize pass, grown on demand
+  std::int64_t p16_rows = 0;
+  CUtensorMap k16map{}, v16map{};
   float scale_log2 = 0.0F;
 };
 
@@ -144,6 +149,8 @@ cudaError_t DevAlloc(yahkv_ctx* ctx, T** p, std::size_t count, bool zero) {
   if (zero) e = cudaMemset(*p, 0, bytes);
   return e;
 }
+
+EncodeTiledFn g_encode = nullptr;   // cuTensorMapEncodeTiled, fetched once per process
 
 int EncodeMap(yahkv_ctx* ctx, EncodeTiledFn encode, CUtensorMap* map, void* base) {
   const cuuint64_t row_bytes = static_cast<cuuint64_t>(CodeBytes(ctx->cfg.fmt));
@@ -184,8 +191,9 @@ int InitDevice(yahkv_ctx* ctx) {
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->items_dev, static_cast<std::size_t>(c.max_seqs) * kKvHeads, false));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->partial_acc, static_cast<std::size_t>(ctx->max_units) * kPartialAccFloats, false));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->partial_ml, static_cast<std::size_t>(ctx->max_units) * kPartialMlFloats, false));
-  ctx->max_tiles = (c.max_batch_tokens / 64 + c.max_seqs) * kKvHeads;
+  ctx->max_tiles = (c.max_batch_tokens / kPrefillTileRows + c.max_seqs) * kQHeads;
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->tiles_dev, static_cast<std::size_t>(ctx->max_tiles), false));
+  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pseqs_dev, static_cast<std::size_t>(c.max_seqs), false));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->status_dev, 1, true));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->counters_dev, static_cast<std::size_t>(c.max_seqs) * kKvHeads, true));
   const std::size_t ns = static_cast<std::size_t>(c.max_seqs);
@@ -201,6 +209,7 @@ int InitDevice(yahkv_ctx* ctx) {
   if (fn == nullptr || qres != cudaDriverEntryPointSuccess)
     return Fail(ctx, YAHKV_ERR_CUDA, "the driver does not export cuTensorMapEncodeTiled");
   const auto encode = reinterpret_cast<EncodeTiledFn>(fn);
+  g_encode = encode;
   if (int r = EncodeMap(ctx, encode, &ctx->kmap, ctx->pool.kcodes); r != YAHKV_OK) return r;
   if (int r = EncodeMap(ctx, encode, &ctx->vmap, ctx->pool.vcodes); r != YAHKV_OK) return r;
   YAHKV_CUDA(ctx, ConfigureDecodeKernels());
@@ -216,7 +225,8 @@ void FreeDevice(yahkv_ctx* ctx) {
   if (ctx->stream != nullptr) cudaStreamSynchronize(ctx->stream);
   void* ptrs[] = {ctx->pool.kcodes, ctx->pool.vcodes, ctx->pool.kscales, ctx->pool.vscales, ctx->tables_dev,
                   ctx->slots_dev,   ctx->units_dev,   ctx->items_dev,    ctx->partial_acc,  ctx->partial_ml,
-                  ctx->tiles_dev,   ctx->status_dev,  ctx->counters_dev, ctx->hs_k,         ctx->hs_v,         ctx->hs_q,
+                  ctx->tiles_dev,   ctx->status_dev,  ctx->counters_dev, ctx->pseqs_dev, ctx->k16_dev, ctx->v16_dev,
+                  ctx->hs_k,         ctx->hs_v,         ctx->hs_q,
                   ctx->hs_out,      ctx->hs_gate};
   for (void* p : ptrs)
     if (p != nullptr) cudaFree(p);
@@ -313,6 +323,21 @@ int CheckStatus(yahkv_ctx* ctx) {
 }
 
 }  // namespace
+
+namespace yahkv {
+bool EncodeTensorMap2D(CUtensorMap* map, int elem_bytes, void* base, std::uint64_t inner, std::uint64_t rows,
+                       std::uint32_t box_inner, std::uint32_t box_rows) {
+  if (g_encode == nullptr || rows == 0) return false;
+  const CUtensorMapDataType type = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const cuuint64_t dims[2] = {inner, rows};
+  const cuuint64_t strides[1] = {inner * static_cast<cuuint64_t>(elem_bytes)};
+  const cuuint32_t box[2] = {box_inner, box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  return g_encode(map, type, 2, base, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+}  // namespace yahkv
 
 extern "C" {
 
@@ -521,25 +546,64 @@ int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const in
   if (int r = RequireDevice(ctx, "attend_prefill"); r != YAHKV_OK) return r;
   if (out_dtype != YAHKV_OUT_F16 && out_dtype != YAHKV_OUT_F32) return Fail(ctx, YAHKV_ERR_INVALID, "attend_prefill: bad out_dtype");
   if (n_seqs > 0 && (q_dev == nullptr || out_dev == nullptr)) return Fail(ctx, YAHKV_ERR_INVALID, "attend_prefill: null q or out pointer");
-  std::int64_t rows = 0;
-  HostError e = ctx->host.PlanPrefill(layer, n_seqs, seq_ids, chunk_lens, ctx->cfg.max_batch_tokens, &ctx->tile_scratch, &rows);
+  if ((reinterpret_cast<std::uintptr_t>(q_dev) & 15) != 0 || (reinterpret_cast<std::uintptr_t>(out_dev) & 15) != 0)
+    return Fail(ctx, YAHKV_ERR_INVALID, "attend_prefill: q and out must be 16-byte aligned");
+  std::int64_t rows = 0, scratch_rows = 0;
+  int max_pages = 0;
+  HostError e = ctx->host.PlanPrefill(layer, n_seqs, seq_ids, chunk_lens, ctx->cfg.max_batch_tokens, &ctx->pseq_scratch,
+                                      &ctx->tile_scratch, &rows, &scratch_rows, &max_pages);
   if (e.code != YAHKV_OK) return FailHost(ctx, std::move(e));
   if (ctx->tile_scratch.empty()) return YAHKV_OK;
   if (static_cast<int>(ctx->tile_scratch.size()) > ctx->max_tiles) return Fail(ctx, YAHKV_ERR_CAPACITY, "attend_prefill: too many tiles");
   cudaStream_t st = StreamOf(ctx, stream);
+  // The fp16 scratch of the dequantize pass grows to the largest call seen (a one-time cost per high-water mark).
+  if (scratch_rows > ctx->p16_rows) {
+    YAHKV_CUDA(ctx, cudaDeviceSynchronize());
+    if (ctx->k16_dev != nullptr) cudaFree(ctx->k16_dev), ctx->device_bytes -= ctx->p16_rows * kHeadDim * 2;
+    if (ctx->v16_dev != nullptr) cudaFree(ctx->v16_dev), ctx->device_bytes -= ctx->p16_rows * kHeadDim * 2;
+    ctx->k16_dev = ctx->v16_dev = nullptr, ctx->p16_rows = 0;
+    const std::size_t bytes = static_cast<std::size_t>(scratch_rows) * kHeadDim * 2;
+    YAHKV_CUDA(ctx, cudaMalloc(&ctx->k16_dev, bytes));
+    YAHKV_CUDA(ctx, cudaMalloc(&ctx->v16_dev, bytes));
+    ctx->device_bytes += 2 * static_cast<std::int64_t>(bytes);
+    ctx->p16_rows = scratch_rows;
+    if (!EncodeTensorMap2D(&ctx->k16map, 2, ctx->k16_dev, kHeadDim, static_cast<std::uint64_t>(scratch_rows), 64, 64) ||
+        !EncodeTensorMap2D(&ctx->v16map, 2, ctx->v16_dev, kHeadDim, static_cast<std::uint64_t>(scratch_rows), 64, 64))
+      return Fail(ctx, YAHKV_ERR_CUDA, "attend_prefill: tensor map encode failed for the fp16 scratch");
+  }
+  CUtensorMap qmap;
+  if (!EncodeTensorMap2D(&qmap, 2, const_cast<void*>(q_dev), static_cast<std::uint64_t>(kQHeads) * kHeadDim,
+                         static_cast<std::uint64_t>(rows), 64, kPrefillTileRows))
+    return Fail(ctx, YAHKV_ERR_CUDA, "attend_prefill: tensor map encode failed for q");
   if (int r = FlushTables(ctx, st); r != YAHKV_OK) return r;
-  if (int r = StagedUpload(ctx, ctx->tiles_dev, ctx->tile_scratch.data(), ctx->tile_scratch.size() * sizeof(PrefillTile), st); r != YAHKV_OK)
-    return r;
+  {
+    const std::size_t sb = ctx->pseq_scratch.size() * sizeof(PrefillSeq), tb = ctx->tile_scratch.size() * sizeof(PrefillTile);
+    char* buf = nullptr;
+    YAHKV_CUDA(ctx, ctx->staging.Acquire(sb + tb, &buf));
+    std::memcpy(buf, ctx->pseq_scratch.data(), sb);
+    std::memcpy(buf + sb, ctx->tile_scratch.data(), tb);
+    YAHKV_CUDA(ctx, cudaMemcpyAsync(ctx->pseqs_dev, buf, sb, cudaMemcpyHostToDevice, st));
+    YAHKV_CUDA(ctx, cudaMemcpyAsync(ctx->tiles_dev, buf + sb, tb, cudaMemcpyHostToDevice, st));
+    YAHKV_CUDA(ctx, ctx->staging.Release(st));
+  }
   PrefillLaunch a{};
-  a.kmap = &ctx->kmap, a.vmap = &ctx->vmap, a.pool = ctx->pool, a.layer = layer;
+  a.pool = ctx->pool, a.layer = layer;
   a.tables_dev = ctx->tables_dev, a.table_stride = ctx->cfg.max_pages_per_seq;
+  a.seqs_dev = ctx->pseqs_dev, a.n_seqs = n_seqs, a.max_pages = max_pages;
+  a.k16_dev = ctx->k16_dev, a.v16_dev = ctx->v16_dev;
+  a.qmap = &qmap, a.k16map = &ctx->k16map, a.v16map = &ctx->v16map;
   a.tiles_dev = ctx->tiles_dev, a.n_tiles = static_cast<int>(ctx->tile_scratch.size());
-  a.q_dev = q_dev, a.gate_dev = gate_dev, a.out_dev = out_dev, a.out_f32 = out_dtype == YAHKV_OUT_F32;
+  a.gate_dev = gate_dev, a.out_dev = out_dev, a.out_f32 = out_dtype == YAHKV_OUT_F32;
   a.scale_log2 = ctx->scale_log2, a.status_dev = ctx->status_dev;
+  {
+    TimedLaunch tl(ctx, YAHKV_KERNEL_PREFILL_DEQUANT, st);
+    YAHKV_CUDA(ctx, LaunchPrefillDequant(a, st));
+    tl.End();
+  }
   TimedLaunch tl(ctx, YAHKV_KERNEL_PREFILL, st);
   YAHKV_CUDA(ctx, LaunchPrefill(a, st));
   tl.End();
-  ctx->launches += 1;
+  ctx->launches += 2;
   return YAHKV_OK;
 }
 

@@ -21,7 +21,7 @@ INCLUDE_DIR = os.path.join(os.path.dirname(_PKG_DIR), "include")
 FMT_Q8_0, FMT_Q4_0 = 0, 1
 SIDE_K, SIDE_V = 0, 1
 OUT_F16, OUT_F32 = 0, 1
-KERNEL_APPEND, KERNEL_DECODE_PART, KERNEL_DECODE_COMBINE, KERNEL_PREFILL = 0, 1, 2, 3
+KERNEL_APPEND, KERNEL_DECODE_PART, KERNEL_DECODE_COMBINE, KERNEL_PREFILL, KERNEL_PREFILL_DEQUANT = 0, 1, 2, 3, 4
 OK = 0
 ERR_INVALID, ERR_NO_PAGES, ERR_CUDA, ERR_NO_DEVICE, ERR_ORDER, ERR_CAPACITY = -1, -2, -3, -4, -5, -6
 
