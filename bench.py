@@ -164,6 +164,90 @@ def reference_arm(args, rank):
     print(json.dumps(line))
 
 
+def prefill_arm(args, local_rank):
+    """The chunked-prefill configuration: 4 sequences with 30720 cached tokens (q8_0) each append a 2048-token chunk
+    (quantize + scatter) and run causal attention of the chunk over cache + chunk; one layer per step, single GPU."""
+    import torch
+    import yahkv
+    torch.cuda.set_device(local_rank)
+    n_seq, cached, chunk = 4, 30720, 2048
+    pages = (cached + chunk) // 64
+    rng = np.random.default_rng(0)
+    cache = yahkv.KvCache(device=local_rank, n_layers=1, num_pages=n_seq * pages + 8, fmt=yahkv.FMT_Q8_0, max_seqs=n_seq,
+                          max_pages_per_seq=pages, max_batch_tokens=n_seq * chunk)
+    perm = rng.permutation(n_seq * pages + 8).astype(np.int32)
+    # An explicit stream: the legacy default stream's handle is 0, which the library reads as "use the context's own
+    # stream", and events recorded on one stream say nothing about kernels on another.
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    sptr = stream.cuda_stream
+    assert sptr != 0
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    seqs = []
+    for i in range(n_seq):
+        s = cache.seq_create()
+        cache.seq_set_table(s, perm[i * pages:(i + 1) * pages])
+        for c0 in range(0, cached, 8192):
+            n = min(8192, cached - c0)
+            K = torch.randn(n, 4, 256, device="cuda", generator=gen).half()
+            V = torch.randn(n, 4, 256, device="cuda", generator=gen).half()
+            cache.append(0, np.full(n, s, np.int32), np.arange(c0, c0 + n), K, V, stream=sptr)
+        seqs.append(s)
+    kc = torch.randn(n_seq * chunk, 4, 256, device="cuda", generator=gen).half()
+    vc = torch.randn(n_seq * chunk, 4, 256, device="cuda", generator=gen).half()
+    q = torch.randn(n_seq * chunk, 24, 256, device="cuda", generator=gen).half()
+    out = torch.zeros(n_seq * chunk, 24, 256, device="cuda", dtype=torch.float16)
+    ids = np.repeat(np.array(seqs, np.int32), chunk)
+    pos = np.tile(np.arange(cached, cached + chunk, dtype=np.int64), n_seq)
+
+    def step():
+        for s in seqs:
+            cache.seq_set_len(s, cached)        # the same chunk is appended again each step
+        cache.append(0, ids, pos, kc, vc, stream=sptr)
+        cache.attend_prefill(0, seqs, [chunk] * n_seq, q, out, stream=sptr)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    cache.kernel_timing(True)
+    sampler = ClockSampler(local_rank)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_begin = time.time()
+    ev0.record(stream)
+    for _ in range(args.steps):
+        step()
+    ev1.record(stream)
+    torch.cuda.synchronize()
+    t_end = time.time()
+    ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop(t_begin, t_end)
+    att_ms, att_n = cache.kernel_timing_read(yahkv.KERNEL_PREFILL)
+    deq_ms, deq_n = cache.kernel_timing_read(yahkv.KERNEL_PREFILL_DEQUANT)
+    app_ms, app_n = cache.kernel_timing_read(yahkv.KERNEL_APPEND)
+    flops = n_seq * 4 * 24 * 256 * sum(cached + i + 1 for i in range(chunk))
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(
+        os.path.join(ROOT, "MEASURED_PEAKS.json")) else {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+    achieved = flops / (att_ms / max(att_n, 1) * 1e-3) / 1e12
+    line = {
+        "metric": "q8_0_chunked_prefill_attn_tflops", "value": flops * args.steps / (ms * 1e-3) / 1e12,
+        "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "chunked_prefill_4seq_30720cached_2048chunk_q8_0_1layer",
+                   "l2": "inputs larger than L2 (285 MB of cache + 537 MB fp16 scratch per step)"},
+        "extra": {"attention_ms": att_ms / max(att_n, 1), "dequant_ms": deq_ms / max(deq_n, 1),
+                  "append_ms": app_ms / max(app_n, 1),
+                  "append_mtok_s": n_seq * chunk / (app_ms / max(app_n, 1) * 1e-3) / 1e6},
+        "roofline": {"kernel": "PrefillKernel (tcgen05)", "bound": "tensor", "achieved": achieved,
+                     "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                     "frac": achieved / peaks["bf16_tflops_sustained"], "peak_kind": "of measured (sustained)",
+                     "frac_of_burst": achieved / peaks["bf16_tflops"], "traffic": None},
+        "gpu_launches": 3 * args.steps, "clocks": clocks,
+    }
+    print(json.dumps(line))
+    cache.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -172,6 +256,8 @@ def main():
     ap.add_argument("--impl", default="yahkv", choices=["yahkv", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers per step (16 = the configuration)")
     ap.add_argument("--fmt", default="q8_0", choices=["q8_0", "q4_0"], help="cache format (q8_0 = the configuration)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+                    help="decode = the batch-32 configuration (default, the headline metric); prefill = chunked prefill")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
     args = ap.parse_args()
@@ -183,6 +269,10 @@ def main():
         return
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload == "prefill":
+        if rank == 0:
+            prefill_arm(args, local_rank)
+        return
 
     import torch
     import torch.distributed as dist
@@ -203,8 +293,12 @@ def main():
                           max_seqs=BATCH, max_pages_per_seq=max(pages) + 1, max_batch_tokens=8192)
     perm = rng.permutation(num_pages).astype(np.int32)
     seqs, off = [], 0
-    stream = torch.cuda.current_stream()
+    # An explicit stream: the legacy default stream's handle is 0, which the library reads as "use the context's own
+    # stream", and events recorded on one stream say nothing about kernels on another.
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
     sptr = stream.cuda_stream
+    assert sptr != 0
     gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
     for i, n in enumerate(lens):
         s = cache.seq_create()

@@ -8,7 +8,9 @@ import yahkv
 
 def dev(a):
     """numpy array -> CUDA tensor with the same bytes (float16 arrays stay float16)."""
-    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    torch.cuda.synchronize()   # the library runs on its own stream, not on torch's
+    return t
 
 
 def pool_pages(cache, layer, num_pages):

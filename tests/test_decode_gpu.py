@@ -18,6 +18,7 @@ def run_decode(cache, layer, seqs, q, gate=None, out_dtype=yahkv.OUT_F32, n_spli
     n = len(seqs)
     out = torch.full((n, 24, 256), float("nan"), device="cuda",
                      dtype=torch.float32 if out_dtype == yahkv.OUT_F32 else torch.float16)
+    torch.cuda.synchronize()   # the fill runs on torch's stream, the library on its own
     cache.attend_decode(layer, seqs, dev(q), out, gate=None if gate is None else dev(gate), out_dtype=out_dtype,
                         n_splits=n_splits)
     cache.sync()

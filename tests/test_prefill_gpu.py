@@ -40,6 +40,7 @@ def run_prefill(cache, layer, seqs, chunks, q, gate, out_dtype):
     rows = sum(chunks)
     out = torch.full((rows, 24, 256), float("nan"), device="cuda",
                      dtype=torch.float32 if out_dtype == yahkv.OUT_F32 else torch.float16)
+    torch.cuda.synchronize()   # the fill runs on torch's stream, the library on its own
     cache.attend_prefill(layer, seqs, chunks, dev(q), out, gate=None if gate is None else dev(gate), out_dtype=out_dtype)
     cache.sync()
     return out.float().cpu().numpy().astype(np.float64)

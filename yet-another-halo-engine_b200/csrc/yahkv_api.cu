@@ -176,7 +176,9 @@ int InitDevice(yahkv_ctx* ctx) {
   YAHKV_CUDA(ctx, cudaGetDeviceProperties(&prop, c.device));
   if (prop.major != 10)
     return Fail(ctx, YAHKV_ERR_NO_DEVICE, std::string("this library is built for sm_100a only; device is ") + prop.name);
-  YAHKV_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+  // A blocking stream: it orders itself against the legacy default stream, so a caller that prepares buffers on the
+  // default stream (and passes no stream) needs no extra synchronisation.
+  YAHKV_CUDA(ctx, cudaStreamCreate(&ctx->stream));
 
   const std::size_t recs = static_cast<std::size_t>(c.n_layers) * c.num_pages * kKvHeads;
   ctx->pool.fmt = c.fmt, ctx->pool.num_pages = c.num_pages, ctx->pool.n_layers = c.n_layers;
