@@ -13,12 +13,12 @@
 // Pass 2, PrefillKernel (tensor-bound): one CTA per tile of 128 query rows of one query head; head_dim 256.
 //   S = Q K^T   tcgen05.mma kind::f16, M 128, N 64 (one 64-key tile), K 256 in 16 steps; A = Q from shared memory
 //               (K-major, 128-byte swizzle, four 64-dim TMA boxes), B = the K tile (same layout), D = S in TMEM.
-//   softmax     four warps, one thread per query row: tcgen05.ld of the row, causal mask, running max with a lazy
-//               rescale of O (threshold 2^8), P = 2^(s - m) as fp16 into shared memory in the A-operand layout.
+//   softmax     eight warps, two threads per query row (32 columns each): tcgen05.ld, causal mask, running max with a
+//               lazy rescale of O (threshold 2^8), P = 2^(s - m) as fp16 into shared memory in the A-operand layout.
 //   O += P V    tcgen05.mma M 128, N 256, K 64 in 4 steps; A = P from shared memory, B = the V tile as loaded
 //               (token-major = MN-major B operand, 128-byte swizzle), D = O in TMEM (256 columns).
-// TMEM columns: S double-buffered 2 x 64, O 256. Shared memory: Q 64 KB, K ring 2 x 32 KB, V ring 2 x 32 KB, P 16 KB.
-// Warp roles: 0-3 softmax / correction / epilogue, 4 TMA producer, 5 MMA issuer and TMEM owner. No multicast, no
+// TMEM columns: S double-buffered 2 x 64, O 256. Shared memory: Q 64 KB, K ring 2 x 32 KB, V ring 2 x 32 KB, P 2 x 16 KB.
+// Warp roles: 0-7 softmax / correction / epilogue, 8 TMA producer, 9 MMA issuer and TMEM owner. No multicast, no
 // cluster. Every mbarrier wait is bounded and abortable: a wait that gives up raises a CTA-wide abort flag, every
 // role leaves its loop, TMEM is freed, and the status word tells the host the call's results are invalid.
 //
@@ -90,7 +90,9 @@ __global__ void __launch_bounds__(kDequantThreads)
 // ----------------------------------------------------------------------------------------------------------------
 constexpr int kTileM = kPrefillTileRows;   // 128 query rows
 constexpr int kTileN = 64;                 // keys per KV tile
-constexpr int kPrefillThreads = 192;       // warps 0-3 softmax, 4 TMA, 5 MMA
+constexpr int kSoftmaxThreads = 256;       // warps 0-7: two threads per query row, 32 of a tile's 64 columns each
+constexpr int kPrefillThreads = 320;       // + warp 8 TMA producer, warp 9 MMA issuer
+constexpr int kWarpTma = 8, kWarpMma = 9;
 constexpr int kQBytes = kTileM * kHeadDim * 2;       // 65536: four [128][64] boxes
 constexpr int kKvTileBytes = kTileN * kHeadDim * 2;  // 32768: four [64][64] boxes
 constexpr int kPBytes = kTileM * kTileN * 2;         // 16384: [128][64] fp16
@@ -99,8 +101,9 @@ constexpr int kSmemQ = 0;
 constexpr int kSmemK = kSmemQ + kQBytes;
 constexpr int kSmemV = kSmemK + kKvStages * kKvTileBytes;
 constexpr int kSmemP = kSmemV + kKvStages * kKvTileBytes;
-constexpr int kSmemBars = kSmemP + kPBytes;
-constexpr int kPrefillSmemBytes = kSmemBars + 256;
+constexpr int kSmemBars = kSmemP + 2 * kPBytes;   // P is double-buffered by tile parity
+constexpr int kBarBytes = 256;
+constexpr int kPrefillSmemBytes = kSmemBars + kBarBytes + 4 * kTileM * 4;   // barriers, then the max / sum exchange
 // TMEM columns
 constexpr int kTmemCols = 512;
 constexpr int kColS = 0;      // two S buffers of 64 columns
@@ -189,9 +192,12 @@ struct PrefillBars {
   std::uint64_t s_full[2], s_free[2];
   std::uint64_t p_full;    // softmax -> MMA: P(j) written, O rescaled
   std::uint64_t pv_done;   // MMA -> softmax: O += P(j) V(j) complete
+  std::uint64_t p_free[2]; // MMA -> softmax: the P buffer of that parity has been read
   std::uint32_t tmem_base;
   int abort_flag;
 };
+
+static_assert(sizeof(PrefillBars) <= kBarBytes, "the max / sum exchange follows the barriers");
 
 __global__ void __launch_bounds__(kPrefillThreads, 1)
     PrefillKernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
@@ -219,14 +225,16 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     }
     for (int b = 0; b < 2; ++b) {
       MbarInit(&bars->s_full[b], 1);
-      MbarInit(&bars->s_free[b], kTileM);
+      MbarInit(&bars->s_free[b], kSoftmaxThreads);
     }
-    MbarInit(&bars->p_full, kTileM);
+    MbarInit(&bars->p_full, kSoftmaxThreads);
     MbarInit(&bars->pv_done, 1);
+    MbarInit(&bars->p_free[0], 1);
+    MbarInit(&bars->p_free[1], 1);
     bars->abort_flag = 0;
     FenceBarrierInit();
   }
-  if (warp == 5) {   // TMEM: one warp allocates, the same warp frees
+  if (warp == kWarpMma) {   // TMEM: one warp allocates, the same warp frees
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(&bars->tmem_base)),
                  "r"(kTmemCols)
                  : "memory");
@@ -237,7 +245,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
   TcFenceAfter();
   const std::uint32_t tmem = bars->tmem_base;
 
-  if (warp == 4) {
+  if (warp == kWarpTma) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       PrefetchTensorMap(&qmap);
@@ -263,7 +271,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
           TmaLoad2D(smem + kSmemV + s * kKvTileBytes + kb * (kTileN * 128), &vmap, kb * 64, y, &bars->v_full[s]);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kWarpMma) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
       constexpr std::uint32_t idesc_s = InstrDesc(kTileM, kTileN, false);
@@ -277,9 +285,10 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         const std::uint32_t v_addr = SmemAddr(smem + kSmemV + s * kKvTileBytes);
 #pragma unroll
         for (int k16 = 0; k16 < kTileN / 16; ++k16)
-          UmmaF16(tmem + kColO, SmemDesc(p_addr + k16 * 32, 16, 1024),
+          UmmaF16(tmem + kColO, SmemDesc(p_addr + (j & 1) * kPBytes + k16 * 32, 16, 1024),
                   SmemDesc(v_addr + k16 * (16 * 128), kTileN * 128, 1024), idesc_o, j > 0 || k16 > 0);
         UmmaCommit(&bars->v_empty[s]);
+        UmmaCommit(&bars->p_free[j & 1]);
         UmmaCommit(&bars->pv_done);
         return true;
       };
@@ -305,12 +314,17 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       if (ok && n_tiles > 0) issue_pv(n_tiles - 1);
     }
   } else {
-    // ------------------------------ softmax, correction, epilogue: thread = query row ------------------------------
-    const int r = threadIdx.x;                                   // 0..127
-    const std::uint32_t lane_addr = tmem + (static_cast<std::uint32_t>(warp * 32) << 16);
+    // ------------------ softmax, correction, epilogue: two threads per query row, half the columns each ------------------
+    // Warps 0-3 take columns 0-31 of a tile's 64 (and O columns 0-127), warps 4-7 the rest; warp w and w + 4 hold the
+    // same 32 rows (a warp reaches TMEM lanes 32 (w % 4) .. + 31). The two halves of a row swap their maxima through
+    // shared memory once per tile, so both keep the same running max; the row sums are joined in the epilogue.
+    const int r = threadIdx.x & (kTileM - 1);                    // query row 0..127
+    const int hc = threadIdx.x >> 7;                             // column half
+    const std::uint32_t lane_addr = tmem + (static_cast<std::uint32_t>((warp & 3) * 32) << 16);
     const int my_last_key = tile.pos0 + r;                       // row r sees keys 0 .. pos0 + r
     float m_run = -INFINITY, l_run = 0.0F;
     std::uint8_t* p_row = smem + kSmemP + r * 128;
+    float* xmax = reinterpret_cast<float*>(smem + kSmemBars + kBarBytes);   // [2 parities][2 halves][128 rows]
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int b = j & 1;
@@ -318,83 +332,107 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       ok = __all_sync(0xFFFFFFFFU, ok);
       if (!ok) break;
       TcFenceAfter();
-      std::uint32_t sraw[2][32];
-      TmemLd32(lane_addr + kColS + b * kTileN, sraw[0]);
-      TmemLd32(lane_addr + kColS + b * kTileN + 32, sraw[1]);
+      std::uint32_t sraw[32];
+      TmemLd32(lane_addr + kColS + b * kTileN + hc * 32, sraw);
       TmemWaitLd();
       TcFenceBefore();
       MbarArrive(&bars->s_free[b]);
-      // scores in log2 units, causal mask on the tiles that reach past this row's position
-      const int key0 = j * kTileN;
-      float tmax = -INFINITY;
-      float sc[kTileN];
+      // Row max on the raw scores (the scale is positive); the causal mask only on tiles that reach past the tile's
+      // first row (a warp-uniform test), where a masked score becomes -inf.
+      const int key0 = j * kTileN + hc * 32;
+      if (j * kTileN + kTileN - 1 > tile.pos0) {
 #pragma unroll
-      for (int c = 0; c < kTileN; ++c) {
-        float v = __uint_as_float(sraw[c >> 5][c & 31]) * scale_log2;
-        if (key0 + c > my_last_key) v = -INFINITY;
-        sc[c] = v;
-        tmax = fmaxf(tmax, v);
+        for (int c = 0; c < 32; ++c)
+          if (key0 + c > my_last_key) sraw[c] = 0xFF800000U;   // -inf
       }
-      // P(j-1) V(j-1) must be complete before O is rescaled or the P buffer is overwritten
-      if (j >= 1) {
-        ok = WaitOrAbort(&bars->pv_done, static_cast<std::uint32_t>(j - 1) & 1U, abort_flag);
-        ok = __all_sync(0xFFFFFFFFU, ok);
-        if (!ok) break;
-        TcFenceAfter();
-      }
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 32; ++c) mx[c & 3] = fmaxf(mx[c & 3], __uint_as_float(sraw[c]));
+      float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      xmax[(b * 2 + hc) * kTileM + r] = tmax;
+      NamedBarrierSync(1, kSoftmaxThreads);   // also orders this tile's exchange against the one two tiles later
+      tmax = fmaxf(tmax, xmax[(b * 2 + (hc ^ 1)) * kTileM + r]) * scale_log2;   // log2 units from here on
       const bool need = tmax > m_run + kPrefillLazyRescale;
-      if (__any_sync(0xFFFFFFFFU, need)) {   // warp-uniform: TMEM loads and stores are warp-wide
+      if (__any_sync(0xFFFFFFFFU, need)) {   // warp-uniform (TMEM accesses are warp-wide); warps w and w + 4 agree
+        // O may only be rescaled once P(j-1) V(j-1) has completed (rare path: the running max has settled after the
+        // first few tiles, so this wait is off the steady-state critical path)
+        if (j >= 1) {
+          ok = WaitOrAbort(&bars->pv_done, static_cast<std::uint32_t>(j - 1) & 1U, abort_flag);
+          ok = __all_sync(0xFFFFFFFFU, ok);
+          if (!ok) break;
+          TcFenceAfter();
+        }
         const float m_new = need ? tmax : m_run;
         const float alpha = m_new == -INFINITY ? 1.0F : Exp2Fast(m_run - m_new);
         m_run = m_new;
         l_run *= alpha;
         if (j >= 1) {
 #pragma unroll 1
-          for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
+          for (int c0 = 0; c0 < kHeadDim / 2; c0 += 32) {
             std::uint32_t o[32];
-            TmemLd32(lane_addr + kColO + c0, o);
+            TmemLd32(lane_addr + kColO + hc * (kHeadDim / 2) + c0, o);
             TmemWaitLd();
 #pragma unroll
             for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-            TmemSt32(lane_addr + kColO + c0, o);
+            TmemSt32(lane_addr + kColO + hc * (kHeadDim / 2) + c0, o);
           }
           TmemWaitSt();
         }
       }
-      const float m_use = m_run == -INFINITY ? 0.0F : m_run;
-      // P row: 64 fp16 = eight 16-byte chunks, chunk c stored at c ^ (row & 7) (the 128-byte swizzle of the operand)
+      const float neg_m = m_run == -INFINITY ? 0.0F : -m_run;
+      // p = 2^(s * scale - m): one fma + one ex2 per element. The row's 64 fp16 are eight 16-byte chunks, chunk c
+      // stored at c ^ (row & 7) (the 128-byte swizzle of the operand); this thread writes chunks 4 hc .. 4 hc + 3.
+      // The row sum is taken in fp32 before the fp16 rounding.
+      float ls[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+      uint4 pk4[4];
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
+      for (int ch = 0; ch < 4; ++ch) {
         uint4 pk;
         __half2* ph = reinterpret_cast<__half2*>(&pk);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float p0 = Exp2Fast(sc[ch * 8 + 2 * i] - m_use), p1 = Exp2Fast(sc[ch * 8 + 2 * i + 1] - m_use);
+          const int c = ch * 8 + 2 * i;
+          const float p0 = Exp2Fast(fmaf(__uint_as_float(sraw[c]), scale_log2, neg_m));
+          const float p1 = Exp2Fast(fmaf(__uint_as_float(sraw[c + 1]), scale_log2, neg_m));
+          ls[i] += p0 + p1;
           ph[i] = __floats2half2_rn(p0, p1);
-          // the sum uses the rounded weights, so numerator and denominator agree
-          const float2 pf = __half22float2(ph[i]);
-          l_run += pf.x + pf.y;
         }
-        *reinterpret_cast<uint4*>(p_row + ((ch ^ (r & 7)) << 4)) = pk;
+        pk4[ch] = pk;
       }
+      // The P buffer of this parity was last read by P(j-2) V(j-2); it has its own barrier (one phase per two tiles)
+      // because a parity wait can only tell adjacent phases apart. Not waiting for P(j-1) V(j-1) here keeps the
+      // tensor pipe one tile ahead of the softmax.
+      if (j >= 2) {
+        ok = WaitOrAbort(&bars->p_free[b], static_cast<std::uint32_t>((j >> 1) - 1) & 1U, abort_flag);
+        ok = __all_sync(0xFFFFFFFFU, ok);
+        if (!ok) break;
+      }
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch)
+        *reinterpret_cast<uint4*>(p_row + b * kPBytes + (((hc * 4 + ch) ^ (r & 7)) << 4)) = pk4[ch];
+      l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       FenceProxyAsync();   // generic-proxy writes of P visible to the tensor core's async proxy
       TcFenceBefore();
       MbarArrive(&bars->p_full);
     }
-    // ---- epilogue: O / l * sigmoid(gate) ----
+    // ---- epilogue: O / l * sigmoid(gate); the two halves of a row join their sums first ----
     if (ok && n_tiles > 0) {
       ok = WaitOrAbort(&bars->pv_done, static_cast<std::uint32_t>(n_tiles - 1) & 1U, abort_flag);
       ok = __all_sync(0xFFFFFFFFU, ok);
     }
+    float* xsum = xmax;   // [2 halves][128 rows]; the max exchange is over
+    NamedBarrierSync(1, kSoftmaxThreads);   // every thread is past its last read of the max exchange
+    xsum[hc * kTileM + r] = l_run;
+    NamedBarrierSync(1, kSoftmaxThreads);
     if (ok && n_tiles > 0) {
       TcFenceAfter();
-      const float inv = 1.0F / l_run;
+      const float inv = 1.0F / (l_run + xsum[(hc ^ 1) * kTileM + r]);
       const bool valid = r < tile.n_rows;
-      const std::size_t oi = (static_cast<std::size_t>(tile.q_row0 + r) * kQHeads + tile.head) * kHeadDim;
+      const std::size_t oi = (static_cast<std::size_t>(tile.q_row0 + r) * kQHeads + tile.head) * kHeadDim + hc * (kHeadDim / 2);
 #pragma unroll 1
-      for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
+      for (int c0 = 0; c0 < kHeadDim / 2; c0 += 32) {
         std::uint32_t o[32];
-        TmemLd32(lane_addr + kColO + c0, o);
+        TmemLd32(lane_addr + kColO + hc * (kHeadDim / 2) + c0, o);
         TmemWaitLd();
         if (valid) {
           float v[32];
@@ -426,7 +464,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
   TcFenceBefore();
   __syncthreads();
   if (threadIdx.x == 0 && bars->abort_flag != 0) atomicExch(status, kStatusPrefillAbort);
-  if (warp == 5) {
+  if (warp == kWarpMma) {
     TcFenceAfter();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
   }
