@@ -120,7 +120,7 @@ struct PrefillLaunch {
   int max_pages;            // largest n_pages of the call (grid of the dequantize pass)
   void* k16_dev;            // fp16 scratch [rows][256], K and V
   void* v16_dev;
-  const CUtensorMap* qmap;  // q as [rows][24 * 256] fp16, box 64 x 128, 128-byte swizzle
+  const void* q_dev;        // [rows][24][256] fp16
   const CUtensorMap* k16map;  // scratch as [rows][256] fp16, box 64 x 64, 128-byte swizzle
   const CUtensorMap* v16map;
   const PrefillTile* tiles_dev;

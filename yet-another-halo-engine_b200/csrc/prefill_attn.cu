@@ -11,20 +11,23 @@
 // token-major fp16 scratch (K and V), value = fp16(code * scale). 34.8 KB read and 64 KB written per page and kv head.
 //
 // Pass 2, PrefillKernel (tensor-bound): one CTA per tile of 128 query rows of one query head; head_dim 256.
-//   S = Q K^T   tcgen05.mma kind::f16, M 128, N 64 (one 64-key tile), K 256 in 16 steps; A = Q from shared memory
-//               (K-major, 128-byte swizzle, four 64-dim TMA boxes), B = the K tile (same layout), D = S in TMEM.
+//   S = Q K^T   tcgen05.mma kind::f16, M 128, N 64 (one 64-key tile), K 256 in 16 steps; A = Q held in tensor memory
+//               for the whole CTA, B = the K tile in shared memory (K-major, 128-byte swizzle, four 64-dim TMA
+//               boxes), D = S in TMEM.
 //   softmax     eight warps, two threads per query row (32 columns each): tcgen05.ld, causal mask, running max with a
-//               lazy rescale of O (threshold 2^8), P = 2^(s - m) as fp16 into shared memory in the A-operand layout.
-//   O += P V    tcgen05.mma M 128, N 256, K 64 in 4 steps; A = P from shared memory, B = the V tile as loaded
+//               lazy rescale of O (threshold 2^8), P = 2^(s - m) as fp16 written back over S with tcgen05.st.
+//   O += P V    tcgen05.mma M 128, N 256, K 64 in 4 steps; A = P from tensor memory, B = the V tile as loaded
 //               (token-major = MN-major B operand, 128-byte swizzle), D = O in TMEM (256 columns).
-// TMEM columns: S double-buffered 2 x 64, O 256. Shared memory: Q 64 KB, K ring 2 x 32 KB, V ring 2 x 32 KB, P 2 x 16 KB.
+// Both A operands live in tensor memory because with them in shared memory the kernel was bound by shared-memory
+// bandwidth (the 64 KB Q tile re-read for every key tile): measured 103 clocks per S step and 238 per P.V step
+// against 32 and 128 at the tensor rate.
+// TMEM columns (all 512): S / P double-buffered 2 x 64, O 256, Q 128. Shared memory: K ring 3 x 32 KB, V ring 3 x 32 KB.
 // Warp roles: 0-7 softmax / correction / epilogue, 8 TMA producer, 9 MMA issuer and TMEM owner. No multicast, no
 // cluster. Every mbarrier wait is bounded and abortable: a wait that gives up raises a CTA-wide abort flag, every
 // role leaves its loop, TMEM is freed, and the status word tells the host the call's results are invalid.
 //
-// The six query heads of a GQA group are separate CTAs here, so a K/V tile is re-read from L2 by six CTAs
-// (arithmetic intensity 128 flop per byte of shared-memory fill); pairing CTAs on one tile (cta_group::2) is the
-// next step for this kernel.
+// The six query heads of a GQA group are separate CTAs here, so a K/V tile is re-read from L2 by six CTAs; pairing
+// CTAs on one tile (cta_group::2) is the next step for this kernel.
 #include <cuda_fp16.h>
 
 #include <cmath>
@@ -93,21 +96,18 @@ constexpr int kTileN = 64;                 // keys per KV tile
 constexpr int kSoftmaxThreads = 256;       // warps 0-7: two threads per query row, 32 of a tile's 64 columns each
 constexpr int kPrefillThreads = 320;       // + warp 8 TMA producer, warp 9 MMA issuer
 constexpr int kWarpTma = 8, kWarpMma = 9;
-constexpr int kQBytes = kTileM * kHeadDim * 2;       // 65536: four [128][64] boxes
-constexpr int kKvTileBytes = kTileN * kHeadDim * 2;  // 32768: four [64][64] boxes
-constexpr int kPBytes = kTileM * kTileN * 2;         // 16384: [128][64] fp16
-constexpr int kKvStages = 2;
-constexpr int kSmemQ = 0;
-constexpr int kSmemK = kSmemQ + kQBytes;
+constexpr int kKvTileBytes = kTileN * kHeadDim * 2;  // 32768: four [64 keys][64 dims] boxes
+constexpr int kKvStages = 3;
+constexpr int kSmemK = 0;
 constexpr int kSmemV = kSmemK + kKvStages * kKvTileBytes;
-constexpr int kSmemP = kSmemV + kKvStages * kKvTileBytes;
-constexpr int kSmemBars = kSmemP + 2 * kPBytes;   // P is double-buffered by tile parity
+constexpr int kSmemBars = kSmemV + kKvStages * kKvTileBytes;
 constexpr int kBarBytes = 256;
 constexpr int kPrefillSmemBytes = kSmemBars + kBarBytes + 4 * kTileM * 4;   // barriers, then the max / sum exchange
-// TMEM columns
+// TMEM columns (512 in all): S / P double-buffered, O, and Q as the A operand of S = Q K^T.
 constexpr int kTmemCols = 512;
-constexpr int kColS = 0;      // two S buffers of 64 columns
-constexpr int kColO = 128;    // 256 columns
+constexpr int kColS = 0;      // two buffers of 64 fp32 columns; P (fp16 pairs) overwrites the first 32 of its buffer
+constexpr int kColO = 128;    // 256 fp32 columns
+constexpr int kColQ = 384;    // 128 columns = 256 fp16 per row
 constexpr float kPrefillLazyRescale = 8.0F;
 constexpr int kStatusPrefillAbort = 3;
 
@@ -129,15 +129,18 @@ __host__ __device__ constexpr std::uint32_t InstrDesc(int m, int n, bool b_mn_ma
          (static_cast<std::uint32_t>(n >> 3) << 17) | (static_cast<std::uint32_t>(m >> 4) << 24);
 }
 
-__device__ __forceinline__ void UmmaF16(std::uint32_t d_tmem, std::uint64_t a_desc, std::uint64_t b_desc,
-                                        std::uint32_t idesc, bool accumulate) {
+// D(tmem) (+)= A(tmem) * B(smem). The A operand sits in tensor memory (row = lane, two fp16 per 32-bit column), so an
+// MMA step reads only its B slice from shared memory: with both operands in shared memory this kernel was bound by
+// shared-memory bandwidth (the 64 KB Q tile was re-read for every 64-key tile).
+__device__ __forceinline__ void UmmaF16Ts(std::uint32_t d_tmem, std::uint32_t a_tmem, std::uint64_t b_desc,
+                                          std::uint32_t idesc, bool accumulate) {
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
       "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
       "}\n" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate ? 1U : 0U)
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate ? 1U : 0U)
       : "memory");
 }
 __device__ __forceinline__ void UmmaCommit(std::uint64_t* bar) {
@@ -166,6 +169,14 @@ __device__ __forceinline__ void TmemSt32(std::uint32_t addr, const std::uint32_t
       "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+__device__ __forceinline__ void TmemSt16(std::uint32_t addr, const std::uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
+      "%15, %16};" ::"r"(addr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 __device__ __forceinline__ void TmemWaitLd() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void TmemWaitSt() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -186,23 +197,21 @@ __device__ __forceinline__ bool WaitOrAbort(std::uint64_t* bar, std::uint32_t pa
 }
 
 struct PrefillBars {
-  std::uint64_t q_full;
+  std::uint64_t q_full;    // softmax threads -> MMA: Q is in tensor memory
   std::uint64_t k_full[kKvStages], k_empty[kKvStages];
   std::uint64_t v_full[kKvStages], v_empty[kKvStages];
-  std::uint64_t s_full[2], s_free[2];
-  std::uint64_t p_full;    // softmax -> MMA: P(j) written, O rescaled
+  std::uint64_t s_full[2]; // MMA -> softmax: S(j) is in its buffer
+  std::uint64_t p_full;    // softmax -> MMA: P(j) written over S(j), O rescaled
   std::uint64_t pv_done;   // MMA -> softmax: O += P(j) V(j) complete
-  std::uint64_t p_free[2]; // MMA -> softmax: the P buffer of that parity has been read
   std::uint32_t tmem_base;
   int abort_flag;
 };
-
 static_assert(sizeof(PrefillBars) <= kBarBytes, "the max / sum exchange follows the barriers");
 
 __global__ void __launch_bounds__(kPrefillThreads, 1)
-    PrefillKernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
-                  const __grid_constant__ CUtensorMap vmap, const PrefillTile* __restrict__ tiles,
-                  const float* __restrict__ gate, void* out, int out_f32, float scale_log2, int* status) {
+    PrefillKernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                  const PrefillTile* __restrict__ tiles, const __half* __restrict__ q, const float* __restrict__ gate,
+                  void* out, int out_f32, float scale_log2, int* status) {
   extern __shared__ __align__(1024) std::uint8_t smem[];
   PrefillBars* bars = reinterpret_cast<PrefillBars*>(smem + kSmemBars);
   volatile int* abort_flag = &bars->abort_flag;
@@ -216,21 +225,17 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     return;
   }
   if (threadIdx.x == 0) {
-    MbarInit(&bars->q_full, 1);
+    MbarInit(&bars->q_full, kSoftmaxThreads);
     for (int s = 0; s < kKvStages; ++s) {
       MbarInit(&bars->k_full[s], 1);
       MbarInit(&bars->k_empty[s], 1);
       MbarInit(&bars->v_full[s], 1);
       MbarInit(&bars->v_empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
-      MbarInit(&bars->s_full[b], 1);
-      MbarInit(&bars->s_free[b], kSoftmaxThreads);
-    }
+    MbarInit(&bars->s_full[0], 1);
+    MbarInit(&bars->s_full[1], 1);
     MbarInit(&bars->p_full, kSoftmaxThreads);
     MbarInit(&bars->pv_done, 1);
-    MbarInit(&bars->p_free[0], 1);
-    MbarInit(&bars->p_free[1], 1);
     bars->abort_flag = 0;
     FenceBarrierInit();
   }
@@ -246,14 +251,10 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
   const std::uint32_t tmem = bars->tmem_base;
 
   if (warp == kWarpTma) {
-    // ------------------------------ TMA producer ------------------------------
+    // ------------------------------ TMA producer: K and V tiles into their rings ------------------------------
     if (lane == 0) {
-      PrefetchTensorMap(&qmap);
       PrefetchTensorMap(&kmap);
       PrefetchTensorMap(&vmap);
-      MbarArriveExpectTx(&bars->q_full, kQBytes);
-      for (int kb = 0; kb < 4; ++kb)
-        TmaLoad2D(smem + kSmemQ + kb * (kTileM * 128), &qmap, tile.head * kHeadDim + kb * 64, tile.q_row0, &bars->q_full);
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j % kKvStages;
@@ -273,11 +274,12 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     }
   } else if (warp == kWarpMma) {
     // ------------------------------ MMA issuer ------------------------------
+    // The tensor pipe executes in issue order, which is what makes the buffer reuse safe without further barriers:
+    // S(j+2) is issued after P(j) V(j), the last reader of that S / P buffer.
     if (lane == 0) {
       constexpr std::uint32_t idesc_s = InstrDesc(kTileM, kTileN, false);
       constexpr std::uint32_t idesc_o = InstrDesc(kTileM, kHeadDim, true);
-      const std::uint32_t q_addr = SmemAddr(smem + kSmemQ), p_addr = SmemAddr(smem + kSmemP);
-      auto issue_pv = [&](int j) -> bool {   // O += P(j) V(j)
+      auto issue_pv = [&](int j) -> bool {   // O += P(j) V(j), A = P from its S buffer, 16 keys (8 columns) per step
         const int s = j % kKvStages;
         if (!WaitOrAbort(&bars->v_full[s], static_cast<std::uint32_t>(j / kKvStages) & 1U, abort_flag)) return false;
         if (!WaitOrAbort(&bars->p_full, static_cast<std::uint32_t>(j) & 1U, abort_flag)) return false;
@@ -285,10 +287,9 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         const std::uint32_t v_addr = SmemAddr(smem + kSmemV + s * kKvTileBytes);
 #pragma unroll
         for (int k16 = 0; k16 < kTileN / 16; ++k16)
-          UmmaF16(tmem + kColO, SmemDesc(p_addr + (j & 1) * kPBytes + k16 * 32, 16, 1024),
-                  SmemDesc(v_addr + k16 * (16 * 128), kTileN * 128, 1024), idesc_o, j > 0 || k16 > 0);
+          UmmaF16Ts(tmem + kColO, tmem + kColS + (j & 1) * kTileN + k16 * 8,
+                    SmemDesc(v_addr + k16 * (16 * 128), kTileN * 128, 1024), idesc_o, j > 0 || k16 > 0);
         UmmaCommit(&bars->v_empty[s]);
-        UmmaCommit(&bars->p_free[j & 1]);
         UmmaCommit(&bars->pv_done);
         return true;
       };
@@ -296,16 +297,15 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j % kKvStages, b = j & 1;
         ok = WaitOrAbort(&bars->k_full[s], static_cast<std::uint32_t>(j / kKvStages) & 1U, abort_flag);
-        if (ok && j >= 2) ok = WaitOrAbort(&bars->s_free[b], static_cast<std::uint32_t>((j >> 1) - 1) & 1U, abort_flag);
         if (!ok) break;
         TcFenceAfter();
         const std::uint32_t k_addr = SmemAddr(smem + kSmemK + s * kKvTileBytes);
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb)
 #pragma unroll
-          for (int k16 = 0; k16 < 4; ++k16)
-            UmmaF16(tmem + kColS + b * kTileN, SmemDesc(q_addr + kb * (kTileM * 128) + k16 * 32, 16, 1024),
-                    SmemDesc(k_addr + kb * (kTileN * 128) + k16 * 32, 16, 1024), idesc_s, kb > 0 || k16 > 0);
+          for (int k16 = 0; k16 < 4; ++k16)   // A = Q from tensor memory, 16 dims (8 columns) per step
+            UmmaF16Ts(tmem + kColS + b * kTileN, tmem + kColQ + (kb * 4 + k16) * 8,
+                      SmemDesc(k_addr + kb * (kTileN * 128) + k16 * 32, 16, 1024), idesc_s, kb > 0 || k16 > 0);
         UmmaCommit(&bars->k_empty[s]);
         UmmaCommit(&bars->s_full[b]);
         // the previous tile's P.V goes behind this tile's S, so the tensor pipe has work while softmax(j) runs
@@ -321,9 +321,27 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     const int r = threadIdx.x & (kTileM - 1);                    // query row 0..127
     const int hc = threadIdx.x >> 7;                             // column half
     const std::uint32_t lane_addr = tmem + (static_cast<std::uint32_t>((warp & 3) * 32) << 16);
+    // Q row -> tensor memory: this thread's 128 dims (256 B) as 64 columns of fp16 pairs. Rows past the chunk are zero.
+    {
+      const uint4* src = reinterpret_cast<const uint4*>(
+          q + (static_cast<std::size_t>(tile.q_row0 + r) * kQHeads + tile.head) * kHeadDim + hc * (kHeadDim / 2));
+      const bool valid = r < tile.n_rows;
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        std::uint32_t qr[32];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint4 v = valid ? __ldg(src + part * 8 + i) : make_uint4(0, 0, 0, 0);
+          qr[4 * i] = v.x, qr[4 * i + 1] = v.y, qr[4 * i + 2] = v.z, qr[4 * i + 3] = v.w;
+        }
+        TmemSt32(lane_addr + kColQ + hc * 64 + part * 32, qr);
+      }
+      TmemWaitSt();
+      TcFenceBefore();
+      MbarArrive(&bars->q_full);
+    }
     const int my_last_key = tile.pos0 + r;                       // row r sees keys 0 .. pos0 + r
     float m_run = -INFINITY, l_run = 0.0F;
-    std::uint8_t* p_row = smem + kSmemP + r * 128;
     float* xmax = reinterpret_cast<float*>(smem + kSmemBars + kBarBytes);   // [2 parities][2 halves][128 rows]
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
@@ -335,8 +353,6 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       std::uint32_t sraw[32];
       TmemLd32(lane_addr + kColS + b * kTileN + hc * 32, sraw);
       TmemWaitLd();
-      TcFenceBefore();
-      MbarArrive(&bars->s_free[b]);
       // Row max on the raw scores (the scale is positive); the causal mask only on tiles that reach past the tile's
       // first row (a warp-uniform test), where a masked score becomes -inf.
       const int key0 = j * kTileN + hc * 32;
@@ -350,11 +366,13 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       for (int c = 0; c < 32; ++c) mx[c & 3] = fmaxf(mx[c & 3], __uint_as_float(sraw[c]));
       float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       xmax[(b * 2 + hc) * kTileM + r] = tmax;
-      NamedBarrierSync(1, kSoftmaxThreads);   // also orders this tile's exchange against the one two tiles later
+      // One barrier per tile: it completes the max exchange, orders it against the exchange two tiles later, and
+      // tells every thread that all 256 have finished loading S(j), whose columns P(j) is about to overwrite.
+      NamedBarrierSync(1, kSoftmaxThreads);
       tmax = fmaxf(tmax, xmax[(b * 2 + (hc ^ 1)) * kTileM + r]) * scale_log2;   // log2 units from here on
       const bool need = tmax > m_run + kPrefillLazyRescale;
       if (__any_sync(0xFFFFFFFFU, need)) {   // warp-uniform (TMEM accesses are warp-wide); warps w and w + 4 agree
-        // O may only be rescaled once P(j-1) V(j-1) has completed (rare path: the running max has settled after the
+        // O may only be rescaled once P(j-1) V(j-1) has completed (rare path: the running max settles after the
         // first few tiles, so this wait is off the steady-state critical path)
         if (j >= 1) {
           ok = WaitOrAbort(&bars->pv_done, static_cast<std::uint32_t>(j - 1) & 1U, abort_flag);
@@ -380,38 +398,21 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         }
       }
       const float neg_m = m_run == -INFINITY ? 0.0F : -m_run;
-      // p = 2^(s * scale - m): one fma + one ex2 per element. The row's 64 fp16 are eight 16-byte chunks, chunk c
-      // stored at c ^ (row & 7) (the 128-byte swizzle of the operand); this thread writes chunks 4 hc .. 4 hc + 3.
-      // The row sum is taken in fp32 before the fp16 rounding.
+      // p = 2^(s * scale - m): one fma + one ex2 per element; the row sum in fp32 before the fp16 rounding. P goes
+      // back into tensor memory as the A operand of P.V: 32 fp16 = 16 columns, at columns 16 hc .. of this S buffer.
       float ls[4] = {0.0F, 0.0F, 0.0F, 0.0F};
-      uint4 pk4[4];
+      std::uint32_t pk[16];
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        uint4 pk;
-        __half2* ph = reinterpret_cast<__half2*>(&pk);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int c = ch * 8 + 2 * i;
-          const float p0 = Exp2Fast(fmaf(__uint_as_float(sraw[c]), scale_log2, neg_m));
-          const float p1 = Exp2Fast(fmaf(__uint_as_float(sraw[c + 1]), scale_log2, neg_m));
-          ls[i] += p0 + p1;
-          ph[i] = __floats2half2_rn(p0, p1);
-        }
-        pk4[ch] = pk;
+      for (int i = 0; i < 16; ++i) {
+        const float p0 = Exp2Fast(fmaf(__uint_as_float(sraw[2 * i]), scale_log2, neg_m));
+        const float p1 = Exp2Fast(fmaf(__uint_as_float(sraw[2 * i + 1]), scale_log2, neg_m));
+        ls[i & 3] += p0 + p1;
+        const __half2 h = __floats2half2_rn(p0, p1);
+        pk[i] = *reinterpret_cast<const std::uint32_t*>(&h);
       }
-      // The P buffer of this parity was last read by P(j-2) V(j-2); it has its own barrier (one phase per two tiles)
-      // because a parity wait can only tell adjacent phases apart. Not waiting for P(j-1) V(j-1) here keeps the
-      // tensor pipe one tile ahead of the softmax.
-      if (j >= 2) {
-        ok = WaitOrAbort(&bars->p_free[b], static_cast<std::uint32_t>((j >> 1) - 1) & 1U, abort_flag);
-        ok = __all_sync(0xFFFFFFFFU, ok);
-        if (!ok) break;
-      }
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch)
-        *reinterpret_cast<uint4*>(p_row + b * kPBytes + (((hc * 4 + ch) ^ (r & 7)) << 4)) = pk4[ch];
       l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      FenceProxyAsync();   // generic-proxy writes of P visible to the tensor core's async proxy
+      TmemSt16(lane_addr + kColS + b * kTileN + hc * 16, pk);
+      TmemWaitSt();
       TcFenceBefore();
       MbarArrive(&bars->p_full);
     }
@@ -492,9 +493,9 @@ cudaError_t LaunchPrefillDequant(const PrefillLaunch& a, cudaStream_t stream) {
 
 cudaError_t LaunchPrefill(const PrefillLaunch& a, cudaStream_t stream) {
   if (a.n_tiles <= 0) return cudaSuccess;
-  PrefillKernel<<<a.n_tiles, kPrefillThreads, kPrefillSmemBytes, stream>>>(*a.qmap, *a.k16map, *a.v16map, a.tiles_dev,
-                                                                          a.gate_dev, a.out_dev, a.out_f32,
-                                                                          a.scale_log2, a.status_dev);
+  PrefillKernel<<<a.n_tiles, kPrefillThreads, kPrefillSmemBytes, stream>>>(
+      *a.k16map, *a.v16map, a.tiles_dev, static_cast<const __half*>(a.q_dev), a.gate_dev, a.out_dev, a.out_f32,
+      a.scale_log2, a.status_dev);
   return cudaGetLastError();
 }
 

@@ -573,10 +573,6 @@ int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const in
         !EncodeTensorMap2D(&ctx->v16map, 2, ctx->v16_dev, kHeadDim, static_cast<std::uint64_t>(scratch_rows), 64, 64))
       return Fail(ctx, YAHKV_ERR_CUDA, "attend_prefill: tensor map encode failed for the fp16 scratch");
   }
-  CUtensorMap qmap;
-  if (!EncodeTensorMap2D(&qmap, 2, const_cast<void*>(q_dev), static_cast<std::uint64_t>(kQHeads) * kHeadDim,
-                         static_cast<std::uint64_t>(rows), 64, kPrefillTileRows))
-    return Fail(ctx, YAHKV_ERR_CUDA, "attend_prefill: tensor map encode failed for q");
   if (int r = FlushTables(ctx, st); r != YAHKV_OK) return r;
   {
     const std::size_t sb = ctx->pseq_scratch.size() * sizeof(PrefillSeq), tb = ctx->tile_scratch.size() * sizeof(PrefillTile);
@@ -593,7 +589,7 @@ int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const in
   a.tables_dev = ctx->tables_dev, a.table_stride = ctx->cfg.max_pages_per_seq;
   a.seqs_dev = ctx->pseqs_dev, a.n_seqs = n_seqs, a.max_pages = max_pages;
   a.k16_dev = ctx->k16_dev, a.v16_dev = ctx->v16_dev;
-  a.qmap = &qmap, a.k16map = &ctx->k16map, a.v16map = &ctx->v16map;
+  a.q_dev = q_dev, a.k16map = &ctx->k16map, a.v16map = &ctx->v16map;
   a.tiles_dev = ctx->tiles_dev, a.n_tiles = static_cast<int>(ctx->tile_scratch.size());
   a.gate_dev = gate_dev, a.out_dev = out_dev, a.out_f32 = out_dtype == YAHKV_OUT_F32;
   a.scale_log2 = ctx->scale_log2, a.status_dev = ctx->status_dev;
