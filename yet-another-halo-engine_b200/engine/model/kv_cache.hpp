@@ -1,0 +1,132 @@
+// C++ face of the yahkv C ABI for the engine's own code: the calls LoomDecoder::Step and LoomPrefill::RunAttention
+// make on this path become one-liners, and errors surface as exceptions thrown before anything is launched, the
+// engine's convention (LoomError, engine/model/loom_runtime.hpp:44-60; checks before dispatch,
+// engine/model/loom_decoder.hpp:186-209, :230-234).
+//
+//   reference                                               here
+//   LoomDecoder::OwnState() / LoomPrefill pools             KvCache::OwnState(cfg)   (one object, shared by both)
+//   LoomDecoder::Bind(LoomPrefill::DecoderState())          nothing to do: prefill and decode use the same KvCache
+//   dattn_kappend_q + dattn_vappend_q | dattn_kvappend      Append(layer, seqs, positions, k, v, stream)
+//   dattn_part(_q) + dattn_reduce                           AttendDecode(layer, seqs, q, gate, out, ...)
+//   yah_kq8 | yah_vq8 ... + yah_attn_wmma                   Append(...) then AttendPrefill(...)
+// Header-only; link with libyahkv.so. Not reentrant, like the engine (engine/model/generator.hpp:56).
+#ifndef YAH_MODEL_KV_CACHE_HPP_
+#define YAH_MODEL_KV_CACHE_HPP_
+
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "yahkv.h"
+
+namespace yah::model {
+
+class KvError : public std::runtime_error {
+ public:
+  KvError(int code, const std::string& what) : std::runtime_error(what), code_(code) {}
+  [[nodiscard]] int code() const { return code_; }
+
+ private:
+  int code_;
+};
+
+class KvCache {
+ public:
+  // The engine's geometry (engine/model/loom_decoder.hpp:55-57) with 64-token pages.
+  static yahkv_config Config(int device, int n_layers, int num_pages, int max_seqs, int max_pages_per_seq,
+                             int fmt = YAHKV_FMT_Q8_0) {
+    yahkv_config c{};
+    c.device = device, c.n_layers = n_layers, c.n_q_heads = 24, c.n_kv_heads = 4, c.head_dim = 256;
+    c.page_tokens = 64, c.num_pages = num_pages, c.fmt = fmt, c.max_seqs = max_seqs;
+    c.max_pages_per_seq = max_pages_per_seq;
+    return c;
+  }
+
+  // Allocates the pools, tables and workspaces (LoomDecoder::OwnState, engine/model/loom_decoder.hpp:159-183).
+  static KvCache OwnState(const yahkv_config& cfg) {
+    yahkv_ctx* ctx = nullptr;
+    const int rc = yahkv_create(&cfg, &ctx);
+    if (rc != YAHKV_OK) throw KvError(rc, std::string("kv cache: ") + yahkv_last_error(nullptr));
+    return KvCache(ctx);
+  }
+
+  KvCache(KvCache&& o) noexcept : ctx_(std::exchange(o.ctx_, nullptr)) {}
+  KvCache& operator=(KvCache&& o) noexcept {
+    if (this != &o) {
+      yahkv_destroy(ctx_);
+      ctx_ = std::exchange(o.ctx_, nullptr);
+    }
+    return *this;
+  }
+  KvCache(const KvCache&) = delete;
+  KvCache& operator=(const KvCache&) = delete;
+  ~KvCache() { yahkv_destroy(ctx_); }
+
+  [[nodiscard]] yahkv_ctx* handle() const { return ctx_; }
+
+  // ---- sequences and pages ----
+  [[nodiscard]] std::int32_t NewSequence() {
+    std::int32_t s = -1;
+    Check(yahkv_seq_create(ctx_, &s));
+    return s;
+  }
+  void FreeSequence(std::int32_t seq) { Check(yahkv_seq_free(ctx_, seq)); }
+  void Reserve(std::int32_t seq, std::int64_t n_tokens) { Check(yahkv_seq_reserve(ctx_, seq, n_tokens)); }
+  void SetTable(std::int32_t seq, const std::vector<std::int32_t>& pages) {
+    Check(yahkv_seq_set_table(ctx_, seq, pages.data(), static_cast<std::int32_t>(pages.size())));
+  }
+  [[nodiscard]] std::vector<std::int32_t> Table(std::int32_t seq) const {
+    const std::int32_t* p = nullptr;
+    std::int32_t n = 0;
+    Check(yahkv_seq_table(ctx_, seq, &p, &n));
+    return std::vector<std::int32_t>(p, p + n);
+  }
+  [[nodiscard]] std::int64_t Length(std::int32_t seq, std::int32_t layer) const {
+    std::int64_t n = 0;
+    Check(yahkv_seq_len(ctx_, seq, layer, &n));
+    return n;
+  }
+  void SetLength(std::int32_t seq, std::int64_t len, std::int32_t layer = -1) {
+    Check(yahkv_seq_set_len(ctx_, seq, layer, len));
+  }
+  [[nodiscard]] std::int32_t PagesFree() const {
+    std::int32_t n = 0;
+    Check(yahkv_pages_free(ctx_, &n));
+    return n;
+  }
+
+  // ---- the hot path (device pointers, asynchronous on `stream`) ----
+  void Append(std::int32_t layer, const std::vector<std::int32_t>& seqs, const std::vector<std::int64_t>& positions,
+              const void* k_dev, const void* v_dev, void* stream = nullptr) {
+    if (seqs.size() != positions.size()) throw KvError(YAHKV_ERR_INVALID, "kv cache: one position per token expected");
+    Check(yahkv_append(ctx_, layer, static_cast<std::int32_t>(seqs.size()), seqs.data(), positions.data(), k_dev, v_dev,
+                       stream));
+  }
+  void AttendDecode(std::int32_t layer, const std::vector<std::int32_t>& seqs, const void* q_dev, const float* gate_dev,
+                    void* out_dev, std::int32_t out_dtype = YAHKV_OUT_F16, std::int32_t n_splits = 0,
+                    void* stream = nullptr) {
+    Check(yahkv_attend_decode(ctx_, layer, static_cast<std::int32_t>(seqs.size()), seqs.data(), q_dev, gate_dev, out_dev,
+                              out_dtype, n_splits, stream));
+  }
+  void AttendPrefill(std::int32_t layer, const std::vector<std::int32_t>& seqs, const std::vector<std::int32_t>& chunks,
+                     const void* q_dev, const float* gate_dev, void* out_dev, std::int32_t out_dtype = YAHKV_OUT_F16,
+                     void* stream = nullptr) {
+    if (seqs.size() != chunks.size()) throw KvError(YAHKV_ERR_INVALID, "kv cache: one chunk length per sequence expected");
+    Check(yahkv_attend_prefill(ctx_, layer, static_cast<std::int32_t>(seqs.size()), seqs.data(), chunks.data(), q_dev,
+                               gate_dev, out_dev, out_dtype, stream));
+  }
+  void Synchronize() { Check(yahkv_sync(ctx_)); }
+
+ private:
+  explicit KvCache(yahkv_ctx* ctx) : ctx_(ctx) {}
+  void Check(int rc) const {
+    if (rc != YAHKV_OK) throw KvError(rc, std::string("kv cache: ") + yahkv_last_error(ctx_));
+  }
+  yahkv_ctx* ctx_ = nullptr;
+};
+
+}  // namespace yah::model
+
+#endif  // YAH_MODEL_KV_CACHE_HPP_
