@@ -34,6 +34,7 @@ for p in (os.path.join(ROOT, "yet-another-halo-engine_b200"), os.path.join(ROOT,
         sys.path.insert(0, p)
 
 LAYERS, BATCH, CTX_LO, CTX_HI = 16, 32, 1024, 32768
+N_SPLITS = 0          # split-K units per (sequence, kv head); 0 = the library's automatic choice
 METRIC, UNIT = "q8_0_paged_decode_attn_kv_gbps", "GB/s"
 # DRAM bytes per algorithmic byte of the split-K attention kernel, from an ncu capture of one full-size launch of this
 # workload (1.238842 GB read + 11.02 MB written for 1.236479 GB of cache): profiles/decode_part_q8_0_batch32.md.
@@ -248,6 +249,111 @@ def prefill_arm(args, local_rank):
     cache.close()
 
 
+def churn_arm(args, rank, local_rank, world):
+    """The whole-box serving-churn configuration, scaled with the GPU count (weak scaling): 32 sequence slots per GPU
+    (256 on 8 GPUs, the configuration), contexts uniform in [512, 65536], per step 30 decode tokens per GPU plus one
+    1024-token prefill chunk per box, a tenth of the slots finishing and being re-admitted from the recycled page
+    pool; q8_0, 64-token pages, `--layers` layers (16 = the configuration). Sequences are partitioned by slot; the only
+    communication is the barrier and the max-over-ranks of the device time."""
+    import torch
+    import torch.distributed as dist
+    import yahkv
+    from yahkv.churn import ChurnRunner, ChurnSchedule, pages_needed
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    layers = args.layers
+    sched = ChurnSchedule(n_slots=32 * world, ctx_lo=512, ctx_hi=65536, n_decode=30 * world, chunk=1024,
+                          finish_frac=0.1, seed=0)
+    cap_pages = (sched.ctx_hi + sched.chunk + 64 + 63) // 64 + 1
+    cache = yahkv.KvCache(device=local_rank, n_layers=layers, num_pages=pages_needed(sched, rank, world),
+                          fmt=yahkv.FMT_Q8_0, max_seqs=40, max_pages_per_seq=cap_pages, max_batch_tokens=2048)
+    runner = ChurnRunner(cache, sched, rank, world, n_layers=layers)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    sptr = stream.cuda_stream
+    gen = torch.Generator(device="cuda").manual_seed(99 + rank)
+    nd = 40
+    k1 = torch.randn(nd, 4, 256, device="cuda", generator=gen).half()
+    v1 = torch.randn(nd, 4, 256, device="cuda", generator=gen).half()
+    q1 = torch.randn(nd, 24, 256, device="cuda", generator=gen).half()
+    o1 = torch.zeros(nd, 24, 256, device="cuda", dtype=torch.float16)
+    kc = torch.randn(sched.chunk, 4, 256, device="cuda", generator=gen).half()
+    vc = torch.randn(sched.chunk, 4, 256, device="cuda", generator=gen).half()
+    qc = torch.randn(sched.chunk, 24, 256, device="cuda", generator=gen).half()
+    oc = torch.zeros(sched.chunk, 24, 256, device="cuda", dtype=torch.float16)
+    work = {"decode_keys": 0, "prefill_flops": 0.0}
+
+    def gpu(kind, sids, pos):
+        n = len(pos)
+        if kind == "decode":
+            for layer in range(layers):
+                cache.append(layer, sids, pos, k1[:n], v1[:n], stream=sptr)
+                cache.attend_decode(layer, sids, q1[:n], o1[:n], stream=sptr)
+            work["decode_keys"] += int(pos.sum()) + n
+        else:
+            ids = np.full(n, sids[0], np.int32)
+            for layer in range(layers):
+                cache.append(layer, ids, pos, kc, vc, stream=sptr)
+                cache.attend_prefill(layer, sids, [n], qc, oc, stream=sptr)
+            work["prefill_flops"] += 4.0 * 24 * 256 * float((pos + 1).sum())
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    step_no = 0
+    for _ in range(max(args.warmup, 3)):
+        runner.step(step_no, gpu)
+        step_no += 1
+    barrier()
+    work["decode_keys"], work["prefill_flops"] = 0, 0.0
+    launches0 = cache.launch_count()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_begin = time.time()
+    ev0.record(stream)
+    tokens = 0
+    for _ in range(args.steps):
+        tokens += runner.step(step_no, gpu)["tokens"]
+        step_no += 1
+    ev1.record(stream)
+    barrier()
+    t_end = time.time()
+    ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop(t_begin, t_end) if sampler else None
+    stats = torch.tensor([ms, tokens, work["decode_keys"], work["prefill_flops"], cache.launch_count() - launches0],
+                         dtype=torch.float64, device="cuda")
+    if world > 1:
+        mx, sm = stats.clone(), stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms, tokens, dkeys, pflops, launches = mx[0].item(), sm[1].item(), sm[2].item(), sm[3].item(), sm[4].item()
+    else:
+        tokens, dkeys, pflops, launches = stats[1].item(), stats[2].item(), stats[3].item(), stats[4].item()
+    if rank == 0:
+        line = {
+            "metric": "serving_churn_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+            "config": {"workload": f"churn_{sched.n_slots}slots_{layers}layers_q8_0_ctx512-65536_page64",
+                       "slots_per_gpu": 32, "decode_tokens_per_step": sched.n_decode, "prefill_chunk": sched.chunk,
+                       "finish_frac": 0.1, "note": "attention + append only; new sequences take recycled pages as "
+                       "their prompt cache; sequences partitioned by slot, no collective on the data path"},
+            "extra": {"decode_kv_gbps": dkeys * layers * 2176 / (ms * 1e-3) / 1e9,
+                      "prefill_tflops_averaged_over_the_run": pflops * layers / (ms * 1e-3) / 1e12,
+                      "pages_free_rank0": cache.pages_free(), "device_bytes_rank0": cache.device_bytes()},
+            "gpu_launches": int(launches), "clocks": clocks,
+        }
+        print(json.dumps(line))
+    cache.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -256,8 +362,9 @@ def main():
     ap.add_argument("--impl", default="yahkv", choices=["yahkv", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers per step (16 = the configuration)")
     ap.add_argument("--fmt", default="q8_0", choices=["q8_0", "q4_0"], help="cache format (q8_0 = the configuration)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
-                    help="decode = the batch-32 configuration (default, the headline metric); prefill = chunked prefill")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "longctx", "churn"],
+                    help="decode = the batch-32 configuration (default, the headline metric); prefill = chunked "
+                         "prefill; longctx = batch 8 x 131072 tokens, q4_0, 64 splits, one layer")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
     args = ap.parse_args()
@@ -273,6 +380,15 @@ def main():
         if rank == 0:
             prefill_arm(args, local_rank)
         return
+    if args.workload == "churn":
+        churn_arm(args, rank, local_rank, world)
+        return
+    if args.workload == "longctx":
+        global BATCH, CTX_LO, CTX_HI, N_SPLITS
+        BATCH, CTX_LO, CTX_HI, N_SPLITS = 8, 131072, 131072, 64
+        args.fmt = "q4_0"
+        if args.layers == LAYERS:
+            args.layers = 1
 
     import torch
     import torch.distributed as dist
@@ -324,7 +440,7 @@ def main():
         pos = np.array([cache.seq_len(s, 0) for s in seqs], np.int64)
         for layer in range(layers):
             cache.append(layer, seq_ids, pos, k_new[layer], v_new[layer], stream=sptr)
-            cache.attend_decode(layer, seq_ids, q[layer], out[layer], stream=sptr)
+            cache.attend_decode(layer, seq_ids, q[layer], out[layer], n_splits=N_SPLITS, stream=sptr)
         return int(pos.sum()) + BATCH            # keys attended per layer in this step
 
     def barrier():
@@ -399,10 +515,12 @@ def main():
         part_mean_ms = part_ms / max(part_n, 1)
         achieved = part_bytes / (part_mean_ms * 1e-3) / 1e9 if part_n else 0.0
         line = {
-            "metric": METRIC, "value": bytes_all / (ms * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world,
+            "metric": METRIC if args.fmt == "q8_0" else METRIC.replace("q8_0", args.fmt),
+            "value": bytes_all / (ms * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-            "config": {"workload": f"batch32_decode_{layers}layers_{args.fmt}_ctx1024-32768_page64", "seqs_per_gpu": BATCH,
+            "config": {"workload": f"batch{BATCH}_decode_{layers}layers_{args.fmt}_ctx{CTX_LO}-{CTX_HI}_page64",
+                       "seqs_per_gpu": BATCH, "n_splits": N_SPLITS,
                        "layers": layers, "mean_ctx": float(lens.mean()), "pages_shuffled": True,
                        "l2": "inputs larger than L2: each layer reads its own ~1.2 GB of cache per step",
                        "sharding": "sequences partitioned across GPUs, no collective on the data path"},
