@@ -323,6 +323,7 @@ def churn_arm(args, rank, local_rank, world):
     ev1.record(stream)
     barrier()
     t_end = time.time()
+    cache.sync()                       # raises if a kernel recorded an error status
     ms = ev0.elapsed_time(ev1)
     clocks = sampler.stop(t_begin, t_end) if sampler else None
     stats = torch.tensor([ms, tokens, work["decode_keys"], work["prefill_flops"], cache.launch_count() - launches0],
