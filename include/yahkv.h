@@ -139,6 +139,15 @@ int yahkv_write_page(yahkv_ctx* ctx, int32_t layer, int32_t side, int32_t page, 
 int yahkv_export_token(yahkv_ctx* ctx, int32_t layer, int32_t seq, int64_t pos, void* k_blocks, void* v_blocks);
 int yahkv_sync(yahkv_ctx* ctx);
 
+/* Cache snapshots (the reference's LoomPrefill::SaveState / LoadState, engine/model/loom_prefill.hpp:973-1024, for
+ * this path's state): the listed sequences with their per-layer lengths and every page they reference, stored in
+ * logical page order, so a load takes fresh pages from the free list and may land anywhere in the pool. A snapshot
+ * loads only into a context of the same format, layer count and geometry. Both calls block. On load, seq_ids_out
+ * receives the new sequence ids in the saved order; *n_inout is the array's capacity on entry, the count on return;
+ * a failed load leaves no sequence behind. */
+int yahkv_snapshot_save(yahkv_ctx* ctx, int32_t n_seqs, const int32_t* seq_ids, const char* path);
+int yahkv_snapshot_load(yahkv_ctx* ctx, const char* path, int32_t* seq_ids_out, int32_t* n_inout);
+
 /* Bytes of device memory the context holds, and kernels it has launched since creation (for benchmarks). */
 int yahkv_device_bytes(const yahkv_ctx* ctx, int64_t* bytes);
 int yahkv_launch_count(const yahkv_ctx* ctx, int64_t* launches);

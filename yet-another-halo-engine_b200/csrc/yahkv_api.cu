@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include <cmath>
+#include <cstdio>
 #include <cstring>
 #include <memory>
 #include <mutex>
@@ -735,6 +736,114 @@ int yahkv_kernel_timing_read(yahkv_ctx* ctx, int32_t kernel, double* total_ms, i
   }
   *total_ms = sum;
   *launches = static_cast<std::int64_t>(ctx->timing_events[kernel].size());
+  return YAHKV_OK;
+}
+
+// ---- snapshots: sequences with their pages, in logical page order, so a load may place them anywhere ----------
+namespace {
+struct SnapshotHeader {
+  char magic[8];            // "YAHKVSN1"
+  std::int32_t fmt, n_layers, n_q_heads, n_kv_heads, head_dim, page_tokens, n_seqs, reserved;
+};
+struct FileCloser {
+  void operator()(std::FILE* f) const {
+    if (f != nullptr) std::fclose(f);
+  }
+};
+}  // namespace
+
+int yahkv_snapshot_save(yahkv_ctx* ctx, int32_t n_seqs, const int32_t* seq_ids, const char* path) {
+  if (int r = RequireDevice(ctx, "snapshot_save"); r != YAHKV_OK) return r;
+  if (n_seqs < 0 || (n_seqs > 0 && seq_ids == nullptr) || path == nullptr)
+    return Fail(ctx, YAHKV_ERR_INVALID, "snapshot_save: bad sequence list or path");
+  for (int i = 0; i < n_seqs; ++i)
+    if (!ctx->host.live(seq_ids[i])) return Fail(ctx, YAHKV_ERR_INVALID, "snapshot_save: not a live sequence");
+  YAHKV_CUDA(ctx, cudaDeviceSynchronize());
+  std::unique_ptr<std::FILE, FileCloser> f(std::fopen(path, "wb"));
+  if (!f) return Fail(ctx, YAHKV_ERR_INVALID, std::string("snapshot_save: cannot open ") + path);
+  const yahkv_config& c = ctx->cfg;
+  SnapshotHeader h{};
+  std::memcpy(h.magic, "YAHKVSN1", 8);
+  h.fmt = c.fmt, h.n_layers = c.n_layers, h.n_q_heads = c.n_q_heads, h.n_kv_heads = c.n_kv_heads;
+  h.head_dim = c.head_dim, h.page_tokens = c.page_tokens, h.n_seqs = n_seqs;
+  bool ok = std::fwrite(&h, sizeof(h), 1, f.get()) == 1;
+  const std::size_t cb = static_cast<std::size_t>(kKvHeads) * RecordCodeBytes(c.fmt);
+  const std::size_t sb = static_cast<std::size_t>(kKvHeads) * kRecordScaleBytes;
+  std::vector<std::uint8_t> buf(2 * (cb + sb));
+  for (int i = 0; i < n_seqs && ok; ++i) {
+    const int s = seq_ids[i];
+    const std::int32_t np = ctx->host.n_pages(s);
+    ok = std::fwrite(&np, 4, 1, f.get()) == 1;
+    for (int l = 0; l < c.n_layers && ok; ++l) {
+      const std::int64_t len = ctx->host.len(s, l);
+      ok = std::fwrite(&len, 8, 1, f.get()) == 1;
+    }
+    for (int l = 0; l < c.n_layers && ok; ++l)
+      for (int p = 0; p < np && ok; ++p) {
+        const std::size_t rec = (static_cast<std::size_t>(l) * c.num_pages + ctx->host.table_row(s)[p]) * kKvHeads;
+        YAHKV_CUDA(ctx, cudaMemcpy(buf.data(), ctx->pool.kcodes + rec * RecordCodeBytes(c.fmt), cb, cudaMemcpyDeviceToHost));
+        YAHKV_CUDA(ctx, cudaMemcpy(buf.data() + cb, ctx->pool.kscales + rec * kPageTokens * kBlocksPerRow, sb, cudaMemcpyDeviceToHost));
+        YAHKV_CUDA(ctx, cudaMemcpy(buf.data() + cb + sb, ctx->pool.vcodes + rec * RecordCodeBytes(c.fmt), cb, cudaMemcpyDeviceToHost));
+        YAHKV_CUDA(ctx, cudaMemcpy(buf.data() + 2 * cb + sb, ctx->pool.vscales + rec * kPageTokens * kBlocksPerRow, sb, cudaMemcpyDeviceToHost));
+        ok = std::fwrite(buf.data(), buf.size(), 1, f.get()) == 1;
+      }
+  }
+  if (!ok) return Fail(ctx, YAHKV_ERR_INVALID, std::string("snapshot_save: write failed on ") + path);
+  return YAHKV_OK;
+}
+
+int yahkv_snapshot_load(yahkv_ctx* ctx, const char* path, int32_t* seq_ids_out, int32_t* n_inout) {
+  if (int r = RequireDevice(ctx, "snapshot_load"); r != YAHKV_OK) return r;
+  if (path == nullptr || seq_ids_out == nullptr || n_inout == nullptr)
+    return Fail(ctx, YAHKV_ERR_INVALID, "snapshot_load: null argument");
+  std::unique_ptr<std::FILE, FileCloser> f(std::fopen(path, "rb"));
+  if (!f) return Fail(ctx, YAHKV_ERR_INVALID, std::string("snapshot_load: cannot open ") + path);
+  const yahkv_config& c = ctx->cfg;
+  SnapshotHeader h{};
+  if (std::fread(&h, sizeof(h), 1, f.get()) != 1 || std::memcmp(h.magic, "YAHKVSN1", 8) != 0)
+    return Fail(ctx, YAHKV_ERR_INVALID, "snapshot_load: not a yahkv snapshot");
+  // Only into an identical set, as the reference's LoadState (engine/model/loom_prefill.hpp:973-1024).
+  if (h.fmt != c.fmt || h.n_layers != c.n_layers || h.n_q_heads != c.n_q_heads || h.n_kv_heads != c.n_kv_heads ||
+      h.head_dim != c.head_dim || h.page_tokens != c.page_tokens)
+    return Fail(ctx, YAHKV_ERR_INVALID, "snapshot_load: format, layer count or geometry differ from this context");
+  if (h.n_seqs < 0 || h.n_seqs > *n_inout) return Fail(ctx, YAHKV_ERR_CAPACITY, "snapshot_load: more sequences than the caller's array holds");
+  YAHKV_CUDA(ctx, cudaDeviceSynchronize());
+  const std::size_t cb = static_cast<std::size_t>(kKvHeads) * RecordCodeBytes(c.fmt);
+  const std::size_t sb = static_cast<std::size_t>(kKvHeads) * kRecordScaleBytes;
+  std::vector<std::uint8_t> buf(2 * (cb + sb));
+  std::vector<std::int32_t> made;
+  auto undo = [&](int code, const std::string& msg) {   // a failed load leaves no half-made sequences behind
+    for (auto it = made.rbegin(); it != made.rend(); ++it) ctx->host.SeqFree(*it);   // restores the free lists' order
+    return Fail(ctx, code, msg);
+  };
+  for (int i = 0; i < h.n_seqs; ++i) {
+    std::int32_t np = 0;
+    if (std::fread(&np, 4, 1, f.get()) != 1 || np < 0) return undo(YAHKV_ERR_INVALID, "snapshot_load: truncated file");
+    std::vector<std::int64_t> lens(static_cast<std::size_t>(c.n_layers));
+    if (std::fread(lens.data(), 8, lens.size(), f.get()) != lens.size()) return undo(YAHKV_ERR_INVALID, "snapshot_load: truncated file");
+    std::int32_t s = -1;
+    HostError e = ctx->host.SeqCreate(&s);
+    if (e.code != YAHKV_OK) return undo(e.code, e.message);
+    made.push_back(s);
+    e = ctx->host.SeqReserve(s, static_cast<std::int64_t>(np) * kPageTokens);
+    if (e.code != YAHKV_OK) return undo(e.code, e.message);
+    for (int l = 0; l < c.n_layers; ++l) {
+      e = ctx->host.SeqSetLen(s, l, lens[static_cast<std::size_t>(l)]);
+      if (e.code != YAHKV_OK) return undo(e.code, "snapshot_load: " + e.message);
+    }
+    for (int l = 0; l < c.n_layers; ++l)
+      for (int p = 0; p < np; ++p) {
+        if (std::fread(buf.data(), buf.size(), 1, f.get()) != 1) return undo(YAHKV_ERR_INVALID, "snapshot_load: truncated file");
+        const std::size_t rec = (static_cast<std::size_t>(l) * c.num_pages + ctx->host.table_row(s)[p]) * kKvHeads;
+        cudaError_t ce = cudaMemcpy(ctx->pool.kcodes + rec * RecordCodeBytes(c.fmt), buf.data(), cb, cudaMemcpyHostToDevice);
+        if (ce == cudaSuccess) ce = cudaMemcpy(ctx->pool.kscales + rec * kPageTokens * kBlocksPerRow, buf.data() + cb, sb, cudaMemcpyHostToDevice);
+        if (ce == cudaSuccess) ce = cudaMemcpy(ctx->pool.vcodes + rec * RecordCodeBytes(c.fmt), buf.data() + cb + sb, cb, cudaMemcpyHostToDevice);
+        if (ce == cudaSuccess) ce = cudaMemcpy(ctx->pool.vscales + rec * kPageTokens * kBlocksPerRow, buf.data() + 2 * cb + sb, sb, cudaMemcpyHostToDevice);
+        if (ce != cudaSuccess) return undo(YAHKV_ERR_CUDA, std::string("snapshot_load: ") + cudaGetErrorString(ce));
+      }
+    seq_ids_out[i] = s;
+  }
+  *n_inout = h.n_seqs;
   return YAHKV_OK;
 }
 

@@ -126,6 +126,8 @@ SIGNATURES = {
     "yahkv_write_page": (_I32, [_VP, _I32, _I32, _I32, _VP, _VP]),
     "yahkv_export_token": (_I32, [_VP, _I32, _I32, _I64, _VP, _VP]),
     "yahkv_sync": (_I32, [_VP]),
+    "yahkv_snapshot_save": (_I32, [_VP, _I32, _VP, _c.c_char_p]),
+    "yahkv_snapshot_load": (_I32, [_VP, _c.c_char_p, _VP, _PI32]),
     "yahkv_device_bytes": (_I32, [_VP, _PI64]),
     "yahkv_launch_count": (_I32, [_VP, _PI64]),
     "yahkv_attend_decode_noalloc": (_I32, [_c.POINTER(NoAllocArgs), _c.c_char_p, _I32]),
@@ -292,6 +294,17 @@ class KvCache:
         k, v = np.zeros(nb, np.uint8), np.zeros(nb, np.uint8)
         self._check(lib.yahkv_export_token(self._h, layer, seq, pos, _ptr(k), _ptr(v)))
         return k, v
+
+    def snapshot_save(self, seq_ids, path):
+        seq_ids = _i32(seq_ids)
+        self._check(lib.yahkv_snapshot_save(self._h, len(seq_ids), _ptr(seq_ids), str(path).encode()))
+
+    def snapshot_load(self, path, max_seqs=1024):
+        """Loads every sequence of the snapshot; returns their new ids in the saved order."""
+        ids = np.zeros(max_seqs, np.int32)
+        n = ctypes.c_int32(max_seqs)
+        self._check(lib.yahkv_snapshot_load(self._h, str(path).encode(), _ptr(ids), ctypes.byref(n)))
+        return ids[:n.value].tolist()
 
     def sync(self):
         self._check(lib.yahkv_sync(self._h))
