@@ -139,6 +139,32 @@ int yahkv_write_page(yahkv_ctx* ctx, int32_t layer, int32_t side, int32_t page, 
 int yahkv_export_token(yahkv_ctx* ctx, int32_t layer, int32_t seq, int64_t pos, void* k_blocks, void* v_blocks);
 int yahkv_sync(yahkv_ctx* ctx);
 
+/* ---- device-resident decode batches (CUDA-graph friendly) -----------------------------------------------------
+ * The reference queues decode steps back to back with no host round trip: positions come from a device array
+ * (engine/model/loom_decoder.hpp:131-133, :239; docs/architecture.md:171). A yahkv_batch is the batched analogue: the
+ * lengths of a fixed set of sequences live on the device, and small kernels derive each step's slots and split-K
+ * units from them, so plan / decode_layer / advance touch no host state and can be stream-captured into a CUDA graph
+ * once and replayed.
+ *   batch_create        the sequences must have equal lengths in all layers; allocates the batch's device arrays.
+ *   batch_prepare       NOT capturable. Reserves pages for the next horizon_steps positions, uploads block tables and
+ *                       lengths, and fixes the number of split-K units per sequence for that horizon.
+ *                       *layout_changed = 1 when that number changed, i.e. a captured graph must be captured again.
+ *   batch_plan          capturable; once per step: slots of the new tokens and the step's units from the lengths.
+ *   batch_decode_layer  capturable; per layer: append k/v [n][4][256] fp16 at the planned slots, then attend with
+ *                       q [n][24][256] over lengths + 1 keys (rows in batch_create's order).
+ *   batch_advance       capturable; once per step: lengths += 1 on the device.
+ *   batch_commit        host side: tells the context that `steps` steps have been queued (eagerly or by replaying a
+ *                       graph), so sequence lengths and later non-batch calls see them. At most the prepared horizon. */
+typedef struct yahkv_batch yahkv_batch;
+int yahkv_batch_create(yahkv_ctx* ctx, int32_t n_seqs, const int32_t* seq_ids, yahkv_batch** out);
+void yahkv_batch_destroy(yahkv_batch* batch);
+int yahkv_batch_prepare(yahkv_batch* batch, int32_t horizon_steps, int32_t* layout_changed, void* stream);
+int yahkv_batch_plan(yahkv_batch* batch, void* stream);
+int yahkv_batch_decode_layer(yahkv_batch* batch, int32_t layer, const void* k_dev, const void* v_dev, const void* q_dev,
+                             const float* gate_dev, void* out_dev, int32_t out_dtype, void* stream);
+int yahkv_batch_advance(yahkv_batch* batch, void* stream);
+int yahkv_batch_commit(yahkv_batch* batch, int32_t steps);
+
 /* Cache snapshots (the reference's LoomPrefill::SaveState / LoadState, engine/model/loom_prefill.hpp:973-1024, for
  * this path's state): the listed sequences with their per-layer lengths and every page they reference, stored in
  * logical page order, so a load takes fresh pages from the free list and may land anywhere in the pool. A snapshot

@@ -1,0 +1,150 @@
+"""Device-resident decode batches (plan / decode_layer / advance from device-side lengths), eagerly and replayed from
+a captured CUDA graph, against the ordinary host-planned calls on a twin cache with the same contents."""
+import numpy as np
+import pytest
+import torch
+
+import yahkv
+from gpu_util import assert_pools_equal, dev, pool_pages
+
+pytestmark = pytest.mark.gpu
+LAYERS = 2
+
+
+def twin_caches(lens, seed, extra_tokens):
+    rng = np.random.default_rng(seed)
+    pages = [(n + extra_tokens + 63) // 64 for n in lens]
+    num_pages = sum(pages) + 2
+    caches = [yahkv.KvCache(n_layers=LAYERS, num_pages=num_pages, max_seqs=len(lens), max_pages_per_seq=max(pages))
+              for _ in range(2)]
+    perm = rng.permutation(num_pages).astype(np.int32)
+    seqs, off = [], 0
+    for i, n in enumerate(lens):
+        K = rng.standard_normal((LAYERS, n, 4, 256)).astype(np.float16)
+        V = rng.standard_normal((LAYERS, n, 4, 256)).astype(np.float16)
+        for c in caches:
+            s = c.seq_create()
+            c.seq_set_table(s, perm[off:off + pages[i]])
+            for layer in range(LAYERS):
+                c.append(layer, np.full(n, s, np.int32), np.arange(n), dev(K[layer]), dev(V[layer]))
+        seqs.append(s)
+        off += pages[i]
+    return caches[0], caches[1], seqs, num_pages, rng
+
+
+def host_step(cache, seqs, lens, k, v, q, gate):
+    outs = []
+    for layer in range(LAYERS):
+        cache.append(layer, seqs, lens, dev(k[layer]), dev(v[layer]))
+        out = torch.zeros(len(seqs), 24, 256, device="cuda")
+        torch.cuda.synchronize()
+        cache.attend_decode(layer, seqs, dev(q[layer]), out, gate=dev(gate[layer]), out_dtype=yahkv.OUT_F32)
+        cache.sync()
+        outs.append(out.cpu().numpy())
+    return outs
+
+
+def step_inputs(rng, n):
+    return (rng.standard_normal((LAYERS, n, 4, 256)).astype(np.float16),
+            rng.standard_normal((LAYERS, n, 4, 256)).astype(np.float16),
+            rng.standard_normal((LAYERS, n, 24, 256)).astype(np.float16),
+            rng.standard_normal((LAYERS, n, 24, 256)).astype(np.float32))
+
+
+def test_eager_batch_steps_match_host_planned_steps():
+    lens = [5, 63, 64, 1535, 24 * 64 - 2, 700]          # page boundaries and a unit boundary (24 pages) get crossed
+    ref, cache, seqs, num_pages, rng = twin_caches(lens, 61, extra_tokens=8)
+    batch = yahkv.DecodeBatch(cache, seqs)
+    assert batch.prepare(6) is True
+    cur = list(lens)
+    for step in range(6):
+        k, v, q, gate = step_inputs(rng, len(seqs))
+        want = host_step(ref, seqs, cur, k, v, q, gate)
+        batch.plan()
+        for layer in range(LAYERS):
+            out = torch.zeros(len(seqs), 24, 256, device="cuda")
+            torch.cuda.synchronize()
+            batch.decode_layer(layer, dev(k[layer]), dev(v[layer]), dev(q[layer]), out, gate=dev(gate[layer]),
+                               out_dtype=yahkv.OUT_F32)
+            cache.sync()
+            assert np.abs(out.cpu().numpy() - want[layer]).max() <= 1e-4, (step, layer)
+        batch.advance()
+        batch.commit(1)
+        cur = [n + 1 for n in cur]
+        assert [cache.seq_len(s, 1) for s in seqs] == cur
+    for layer in range(LAYERS):      # the appends landed in the same places with the same bytes
+        a, b = pool_pages(ref, layer, num_pages), pool_pages(cache, layer, num_pages)
+        assert all(np.array_equal(x, y) for x, y in zip(a, b))
+    with pytest.raises(yahkv.YahkvError) as e:
+        batch.commit(1)                  # nothing prepared beyond the six steps
+    assert e.value.code == yahkv.ERR_ORDER
+    assert batch.prepare(3) is False     # same unit layout: a captured graph stays valid
+    batch.close()
+
+
+def test_replayed_cuda_graph_matches_host_planned_steps():
+    lens = [300, 64 * 24 - 3, 2000, 1]
+    ref, cache, seqs, num_pages, rng = twin_caches(lens, 62, extra_tokens=8)
+    n = len(seqs)
+    batch = yahkv.DecodeBatch(cache, seqs)
+    batch.prepare(6)
+    side = torch.cuda.Stream()
+    k_s = torch.zeros(LAYERS, n, 4, 256, device="cuda", dtype=torch.float16)
+    v_s = torch.zeros_like(k_s)
+    q_s = torch.zeros(LAYERS, n, 24, 256, device="cuda", dtype=torch.float16)
+    g_s = torch.zeros(LAYERS, n, 24, 256, device="cuda", dtype=torch.float32)
+    o_s = torch.zeros(LAYERS, n, 24, 256, device="cuda", dtype=torch.float32)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        sp = torch.cuda.current_stream().cuda_stream
+        batch.plan(stream=sp)
+        for layer in range(LAYERS):
+            batch.decode_layer(layer, k_s[layer], v_s[layer], q_s[layer], o_s[layer], gate=g_s[layer],
+                               out_dtype=yahkv.OUT_F32, stream=sp)
+        batch.advance(stream=sp)
+    cur = list(lens)
+    for step in range(5):
+        k, v, q, gate = step_inputs(rng, n)
+        want = host_step(ref, seqs, cur, k, v, q, gate)
+        k_s.copy_(torch.from_numpy(k)); v_s.copy_(torch.from_numpy(v))
+        q_s.copy_(torch.from_numpy(q)); g_s.copy_(torch.from_numpy(gate))
+        graph.replay()
+        torch.cuda.synchronize()
+        got = o_s.cpu().numpy()
+        for layer in range(LAYERS):
+            assert np.abs(got[layer] - want[layer]).max() <= 1e-4, (step, layer)
+        cur = [x + 1 for x in cur]
+    batch.commit(5)
+    cache.sync()
+    assert [cache.seq_len(s, 0) for s in seqs] == cur
+    for layer in range(LAYERS):
+        a, b = pool_pages(ref, layer, num_pages), pool_pages(cache, layer, num_pages)
+        assert all(np.array_equal(x, y) for x, y in zip(a, b))
+    # after the batch, the ordinary calls continue from the committed lengths
+    k, v, q, gate = step_inputs(rng, n)
+    want = host_step(ref, seqs, cur, k, v, q, gate)
+    got = host_step(cache, seqs, cur, k, v, q, gate)
+    assert all(np.abs(a - b).max() <= 1e-4 for a, b in zip(got, want))
+    batch.close()
+
+
+def test_batch_refuses_what_it_cannot_hold():
+    cache = yahkv.KvCache(n_layers=2, num_pages=4, max_seqs=2, max_pages_per_seq=2)
+    s = cache.seq_create()
+    cache.seq_reserve(s, 10)
+    x = torch.zeros(10, 4, 256, dtype=torch.float16, device="cuda")
+    cache.append(0, np.full(10, s, np.int32), np.arange(10), x, x)     # layer 1 stays empty
+    with pytest.raises(yahkv.YahkvError) as e:
+        yahkv.DecodeBatch(cache, [s])
+    assert e.value.code == yahkv.ERR_ORDER
+    cache.append(1, np.full(10, s, np.int32), np.arange(10), x, x)
+    batch = yahkv.DecodeBatch(cache, [s])
+    with pytest.raises(yahkv.YahkvError) as e:
+        batch.plan()                                                   # not prepared
+    assert e.value.code == yahkv.ERR_ORDER
+    with pytest.raises(yahkv.YahkvError) as e:
+        batch.prepare(64 * 2)                                          # past max_pages_per_seq
+    assert e.value.code == yahkv.ERR_CAPACITY
+    batch.prepare(5)
+    batch.close()

@@ -1,0 +1,72 @@
+// Device-resident decode stepping: the per-step bookkeeping of a fixed batch of sequences done by small kernels from
+// device-resident lengths, so that a whole multi-layer decode step (plan, then per layer append + attend, then
+// advance) touches no host state and can be captured once into a CUDA graph and replayed.
+//
+// The reference engine works the same way: positions come from a device array and steps are queued back to back
+// with no host round trip (engine/model/loom_decoder.hpp:131-133, :239; docs/architecture.md:171). Its single
+// sequence becomes a batch here, and its fixed one-workgroup-per-page grid becomes a fixed number of split-K units
+// per sequence, reserved for the growth the caller announced; units that hold no page yet exit at once.
+#include "kernels.cuh"
+
+namespace yahkv {
+namespace {
+
+// One thread per (batch row, kv head): this step appends position lens[b] and attends over lens[b] + 1 keys.
+__global__ void BatchPlanKernel(const std::int32_t* __restrict__ lens, const BatchSeq* __restrict__ seqs, int n_seqs,
+                                const std::int32_t* __restrict__ tables, int table_stride, int unit_pages,
+                                int num_pages, DecodeUnit* __restrict__ units, CombineItem* __restrict__ items,
+                                std::int64_t* __restrict__ slots) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_seqs * kKvHeads) return;
+  const int b = idx / kKvHeads, h = idx % kKvHeads;
+  const BatchSeq bs = seqs[b];
+  const int pos = max(lens[b], 0);
+  const int n = pos + 1;
+  const int pages = min((n + kPageTokens - 1) / kPageTokens, table_stride);
+  const int used = min((pages + unit_pages - 1) / unit_pages, bs.n_units);
+  const int first = bs.first_unit + h * bs.n_units;
+  items[idx] = {first, used};
+  for (int k = 0; k < bs.n_units; ++k) {
+    DecodeUnit u;
+    u.batch = b, u.seq = bs.seq_row, u.kvh = h;
+    u.page_begin = min(k * unit_pages, pages);
+    // the last reserved unit takes whatever is left, so an under-reserved batch degrades to longer units, never to
+    // missing keys
+    u.page_end = k == bs.n_units - 1 ? pages : min((k + 1) * unit_pages, pages);
+    u.n_keys = n;
+    u.partial = first + k;
+    u.pad = 0;
+    units[first + k] = u;
+  }
+  if (h == 0) {
+    std::int32_t page = tables[static_cast<std::size_t>(bs.seq_row) * table_stride + min(pos / kPageTokens, table_stride - 1)];
+    page = min(max(page, 0), num_pages - 1);
+    slots[b] = static_cast<std::int64_t>(page) * kPageTokens + pos % kPageTokens;
+  }
+}
+
+__global__ void BatchAdvanceKernel(std::int32_t* __restrict__ lens, int n_seqs, int by) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < n_seqs) lens[b] += by;
+}
+
+}  // namespace
+
+cudaError_t LaunchBatchPlan(const std::int32_t* lens_dev, const BatchSeq* seqs_dev, int n_seqs,
+                            const std::int32_t* tables_dev, int table_stride, int unit_pages, int num_pages,
+                            DecodeUnit* units_dev, CombineItem* items_dev, std::int64_t* slots_dev,
+                            cudaStream_t stream) {
+  if (n_seqs <= 0) return cudaSuccess;
+  const int threads = n_seqs * kKvHeads;
+  BatchPlanKernel<<<(threads + 127) / 128, 128, 0, stream>>>(lens_dev, seqs_dev, n_seqs, tables_dev, table_stride,
+                                                            unit_pages, num_pages, units_dev, items_dev, slots_dev);
+  return cudaGetLastError();
+}
+
+cudaError_t LaunchBatchAdvance(std::int32_t* lens_dev, int n_seqs, int by, cudaStream_t stream) {
+  if (n_seqs <= 0) return cudaSuccess;
+  BatchAdvanceKernel<<<(n_seqs + 127) / 128, 128, 0, stream>>>(lens_dev, n_seqs, by);
+  return cudaGetLastError();
+}
+
+}  // namespace yahkv

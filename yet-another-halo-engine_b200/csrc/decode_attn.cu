@@ -151,6 +151,7 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
   const int kw = warp >> 1;   // key group: keys 16 kw .. 16 kw + 15 of the page
   const int dh = warp & 1;    // dim half: dims 128 dh .. 128 dh + 127 (blocks 4 dh .. 4 dh + 3)
   const int n_pages = u.page_end - u.page_begin;
+  if (n_pages <= 0) return;   // a unit reserved for growth that holds no page yet: the merge does not count it
   const std::int32_t* row = tables + static_cast<std::size_t>(u.seq) * table_stride + u.page_begin;
 
   // Gather of one page into a ring stage: 2 TMA boxes per side (q8_0; 1 for q4_0) + the two scale records, all

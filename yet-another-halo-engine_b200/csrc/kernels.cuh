@@ -53,6 +53,20 @@ struct CombineItem {
   std::int32_t n_partials;
 };
 
+// One row of a device-resident decode batch: its block-table row and the split-K units reserved for it per kv head
+// (units [first_unit + kvh * n_units, + n_units) belong to kv head kvh).
+struct BatchSeq {
+  std::int32_t seq_row;
+  std::int32_t first_unit;
+  std::int32_t n_units;
+  std::int32_t pad;
+};
+cudaError_t LaunchBatchPlan(const std::int32_t* lens_dev, const BatchSeq* seqs_dev, int n_seqs,
+                            const std::int32_t* tables_dev, int table_stride, int unit_pages, int num_pages,
+                            DecodeUnit* units_dev, CombineItem* items_dev, std::int64_t* slots_dev,
+                            cudaStream_t stream);
+cudaError_t LaunchBatchAdvance(std::int32_t* lens_dev, int n_seqs, int by, cudaStream_t stream);
+
 // Prefill attention reads a dequantized fp16 copy of the sequences' K and V (the reference's yah_kdeq / yah_vdeq
 // pre-pass, engine/gpu/loom/tools/gen_attn_fa.py:4648-4860): rows [kv_row0 + kvh * kv_rows, ...) of the scratch hold
 // kv head kvh of the sequence, token-major, 256 fp16 each, kv_rows = the length rounded up to whole pages.

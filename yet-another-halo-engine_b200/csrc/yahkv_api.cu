@@ -4,6 +4,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -736,6 +737,193 @@ int yahkv_kernel_timing_read(yahkv_ctx* ctx, int32_t kernel, double* total_ms, i
   }
   *total_ms = sum;
   *launches = static_cast<std::int64_t>(ctx->timing_events[kernel].size());
+  return YAHKV_OK;
+}
+
+// ---- device-resident decode batches ------------------------------------------------------------------------
+struct yahkv_batch {
+  yahkv_ctx* ctx = nullptr;
+  std::vector<std::int32_t> seqs;
+  std::vector<std::int32_t> lens;       // host mirror of lens_dev (committed steps only)
+  std::vector<BatchSeq> rows;
+  int total_units = 0;
+  int horizon = 0;
+  std::int32_t* lens_dev = nullptr;
+  BatchSeq* rows_dev = nullptr;
+  DecodeUnit* units_dev = nullptr;
+  CombineItem* items_dev = nullptr;
+  std::int64_t* slots_dev = nullptr;
+  int units_cap = 0;
+};
+namespace {
+constexpr int kBatchUnitPages = 24;   // the automatic planner's unit size on large batches (kv_host.hpp)
+void BatchFree(yahkv_batch* b) {
+  for (void* p : {static_cast<void*>(b->lens_dev), static_cast<void*>(b->rows_dev), static_cast<void*>(b->units_dev),
+                  static_cast<void*>(b->items_dev), static_cast<void*>(b->slots_dev)})
+    if (p != nullptr) cudaFree(p);
+  delete b;
+}
+}  // namespace
+
+int yahkv_batch_create(yahkv_ctx* ctx, int32_t n_seqs, const int32_t* seq_ids, yahkv_batch** out) {
+  if (int r = RequireDevice(ctx, "batch_create"); r != YAHKV_OK) return r;
+  if (out == nullptr) return Fail(ctx, YAHKV_ERR_INVALID, "batch_create: null out pointer");
+  *out = nullptr;
+  if (n_seqs <= 0 || n_seqs > ctx->cfg.max_seqs || seq_ids == nullptr) return Fail(ctx, YAHKV_ERR_INVALID, "batch_create: bad sequence list");
+  auto* b = new (std::nothrow) yahkv_batch();
+  if (b == nullptr) return Fail(ctx, YAHKV_ERR_INVALID, "batch_create: out of host memory");
+  b->ctx = ctx;
+  for (int i = 0; i < n_seqs; ++i) {
+    const int s = seq_ids[i];
+    if (!ctx->host.live(s)) {
+      delete b;
+      return Fail(ctx, YAHKV_ERR_INVALID, "batch_create: not a live sequence: " + std::to_string(s));
+    }
+    const std::int64_t n = ctx->host.len(s, 0);
+    for (int l = 1; l < ctx->cfg.n_layers; ++l)
+      if (ctx->host.len(s, l) != n) {
+        delete b;
+        return Fail(ctx, YAHKV_ERR_ORDER, "batch_create: sequence " + std::to_string(s) + " has different lengths in its layers");
+      }
+    b->seqs.push_back(s);
+    b->lens.push_back(static_cast<std::int32_t>(n));
+  }
+  b->units_cap = ctx->max_units;
+  cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&b->lens_dev), sizeof(std::int32_t) * n_seqs);
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&b->rows_dev), sizeof(BatchSeq) * n_seqs);
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&b->units_dev), sizeof(DecodeUnit) * b->units_cap);
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&b->items_dev), sizeof(CombineItem) * n_seqs * kKvHeads);
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&b->slots_dev), sizeof(std::int64_t) * n_seqs);
+  if (e != cudaSuccess) {
+    BatchFree(b);
+    return FailCuda(ctx, "batch_create", e);
+  }
+  *out = b;
+  return YAHKV_OK;
+}
+
+void yahkv_batch_destroy(yahkv_batch* b) {
+  if (b == nullptr) return;
+  cudaSetDevice(b->ctx->cfg.device);
+  cudaDeviceSynchronize();
+  BatchFree(b);
+}
+
+int yahkv_batch_prepare(yahkv_batch* b, int32_t horizon_steps, int32_t* layout_changed, void* stream) {
+  if (b == nullptr) return YAHKV_ERR_INVALID;
+  yahkv_ctx* ctx = b->ctx;
+  if (int r = RequireDevice(ctx, "batch_prepare"); r != YAHKV_OK) return r;
+  if (horizon_steps < 1) return Fail(ctx, YAHKV_ERR_INVALID, "batch_prepare: horizon must be at least one step");
+  const int n = static_cast<int>(b->seqs.size());
+  // pages for every position the next `horizon_steps` steps will append; nothing changes if any reservation fails
+  for (int i = 0; i < n; ++i) {
+    if (!ctx->host.live(b->seqs[i]) || ctx->host.len(b->seqs[i], 0) != b->lens[i])
+      return Fail(ctx, YAHKV_ERR_ORDER, "batch_prepare: a sequence of the batch was freed or changed outside the batch");
+    const std::int64_t need = (static_cast<std::int64_t>(b->lens[i]) + horizon_steps + kPageTokens - 1) / kPageTokens;
+    if (need > ctx->cfg.max_pages_per_seq) return Fail(ctx, YAHKV_ERR_CAPACITY, "batch_prepare: horizon exceeds max_pages_per_seq");
+  }
+  for (int i = 0; i < n; ++i) {
+    HostError e = ctx->host.SeqReserve(b->seqs[i], static_cast<std::int64_t>(b->lens[i]) + horizon_steps);
+    if (e.code != YAHKV_OK) return FailHost(ctx, std::move(e));
+  }
+  // units reserved per sequence, the longest sequences first (CTAs are handed out in index order)
+  std::vector<int> order(static_cast<std::size_t>(n));
+  for (int i = 0; i < n; ++i) order[static_cast<std::size_t>(i)] = i;
+  std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return b->lens[x] > b->lens[y]; });
+  std::vector<BatchSeq> rows(static_cast<std::size_t>(n));
+  int total = 0;
+  for (int i : order) {
+    const int pages = (b->lens[i] + horizon_steps + kPageTokens - 1) / kPageTokens;
+    BatchSeq r{};
+    r.seq_row = b->seqs[i];
+    r.n_units = std::min(std::max((pages + kBatchUnitPages - 1) / kBatchUnitPages, 1), ctx->cfg.max_splits);
+    r.first_unit = total;
+    total += r.n_units * kKvHeads;
+    rows[static_cast<std::size_t>(i)] = r;
+  }
+  if (total > b->units_cap) return Fail(ctx, YAHKV_ERR_CAPACITY, "batch_prepare: more split-K units than the workspace holds");
+  bool changed = rows.size() != b->rows.size() || total != b->total_units;
+  for (std::size_t i = 0; !changed && i < rows.size(); ++i)
+    changed = rows[i].n_units != b->rows[i].n_units || rows[i].first_unit != b->rows[i].first_unit;
+  if (layout_changed != nullptr) *layout_changed = changed ? 1 : 0;
+  cudaStream_t st = StreamOf(ctx, stream);
+  if (int r = FlushTables(ctx, st); r != YAHKV_OK) return r;
+  {
+    const std::size_t lb = sizeof(std::int32_t) * static_cast<std::size_t>(n), rb = sizeof(BatchSeq) * static_cast<std::size_t>(n);
+    char* buf = nullptr;
+    YAHKV_CUDA(ctx, ctx->staging.Acquire(lb + rb, &buf));
+    std::memcpy(buf, b->lens.data(), lb);
+    std::memcpy(buf + lb, rows.data(), rb);
+    YAHKV_CUDA(ctx, cudaMemcpyAsync(b->lens_dev, buf, lb, cudaMemcpyHostToDevice, st));
+    YAHKV_CUDA(ctx, cudaMemcpyAsync(b->rows_dev, buf + lb, rb, cudaMemcpyHostToDevice, st));
+    YAHKV_CUDA(ctx, ctx->staging.Release(st));
+  }
+  b->rows = std::move(rows);
+  b->total_units = total;
+  b->horizon = horizon_steps;
+  return YAHKV_OK;
+}
+
+int yahkv_batch_plan(yahkv_batch* b, void* stream) {
+  if (b == nullptr) return YAHKV_ERR_INVALID;
+  yahkv_ctx* ctx = b->ctx;
+  if (int r = RequireDevice(ctx, "batch_plan"); r != YAHKV_OK) return r;
+  if (b->total_units == 0) return Fail(ctx, YAHKV_ERR_ORDER, "batch_plan: call batch_prepare first");
+  YAHKV_CUDA(ctx, LaunchBatchPlan(b->lens_dev, b->rows_dev, static_cast<int>(b->seqs.size()), ctx->tables_dev,
+                                  ctx->cfg.max_pages_per_seq, kBatchUnitPages, ctx->cfg.num_pages, b->units_dev,
+                                  b->items_dev, b->slots_dev, StreamOf(ctx, stream)));
+  ctx->launches += 1;
+  return YAHKV_OK;
+}
+
+int yahkv_batch_decode_layer(yahkv_batch* b, int32_t layer, const void* k_dev, const void* v_dev, const void* q_dev,
+                             const float* gate_dev, void* out_dev, int32_t out_dtype, void* stream) {
+  if (b == nullptr) return YAHKV_ERR_INVALID;
+  yahkv_ctx* ctx = b->ctx;
+  if (int r = RequireDevice(ctx, "batch_decode_layer"); r != YAHKV_OK) return r;
+  if (layer < 0 || layer >= ctx->cfg.n_layers) return Fail(ctx, YAHKV_ERR_INVALID, "batch_decode_layer: layer out of range");
+  if (out_dtype != YAHKV_OUT_F16 && out_dtype != YAHKV_OUT_F32) return Fail(ctx, YAHKV_ERR_INVALID, "batch_decode_layer: bad out_dtype");
+  if (k_dev == nullptr || v_dev == nullptr || q_dev == nullptr || out_dev == nullptr)
+    return Fail(ctx, YAHKV_ERR_INVALID, "batch_decode_layer: null device pointer");
+  if (b->total_units == 0) return Fail(ctx, YAHKV_ERR_ORDER, "batch_decode_layer: call batch_prepare first");
+  cudaStream_t st = StreamOf(ctx, stream);
+  const int n = static_cast<int>(b->seqs.size());
+  YAHKV_CUDA(ctx, LaunchAppend(ctx->pool, layer, n, b->slots_dev, k_dev, v_dev, st));
+  DecodeLaunch a{};
+  a.kmap = &ctx->kmap, a.vmap = &ctx->vmap, a.pool = ctx->pool, a.layer = layer;
+  a.tables_dev = ctx->tables_dev, a.table_stride = ctx->cfg.max_pages_per_seq;
+  a.units_dev = b->units_dev, a.n_units = b->total_units;
+  a.items_dev = b->items_dev, a.n_seqs = n;
+  a.q_dev = q_dev, a.gate_dev = gate_dev, a.out_dev = out_dev, a.out_f32 = out_dtype == YAHKV_OUT_F32;
+  a.scale_log2 = ctx->scale_log2;
+  a.partial_acc = ctx->partial_acc, a.partial_ml = ctx->partial_ml, a.status_dev = ctx->status_dev;
+  a.counters_dev = nullptr;
+  YAHKV_CUDA(ctx, LaunchDecodePart(a, st));
+  YAHKV_CUDA(ctx, LaunchDecodeCombine(a, st));
+  ctx->launches += 3;
+  return YAHKV_OK;
+}
+
+int yahkv_batch_advance(yahkv_batch* b, void* stream) {
+  if (b == nullptr) return YAHKV_ERR_INVALID;
+  yahkv_ctx* ctx = b->ctx;
+  if (int r = RequireDevice(ctx, "batch_advance"); r != YAHKV_OK) return r;
+  YAHKV_CUDA(ctx, LaunchBatchAdvance(b->lens_dev, static_cast<int>(b->seqs.size()), 1, StreamOf(ctx, stream)));
+  ctx->launches += 1;
+  return YAHKV_OK;
+}
+
+int yahkv_batch_commit(yahkv_batch* b, int32_t steps) {
+  if (b == nullptr) return YAHKV_ERR_INVALID;
+  yahkv_ctx* ctx = b->ctx;
+  if (steps < 0 || steps > b->horizon) return Fail(ctx, YAHKV_ERR_ORDER, "batch_commit: more steps than the prepared horizon");
+  for (std::size_t i = 0; i < b->seqs.size(); ++i) {
+    HostError e = ctx->host.SeqSetLen(b->seqs[i], -1, static_cast<std::int64_t>(b->lens[i]) + steps);
+    if (e.code != YAHKV_OK) return FailHost(ctx, std::move(e));
+  }
+  for (auto& n : b->lens) n += steps;
+  b->horizon -= steps;
+  ctx->host.InvalidateDecodePlan();
   return YAHKV_OK;
 }
 

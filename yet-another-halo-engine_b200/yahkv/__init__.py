@@ -126,6 +126,13 @@ SIGNATURES = {
     "yahkv_write_page": (_I32, [_VP, _I32, _I32, _I32, _VP, _VP]),
     "yahkv_export_token": (_I32, [_VP, _I32, _I32, _I64, _VP, _VP]),
     "yahkv_sync": (_I32, [_VP]),
+    "yahkv_batch_create": (_I32, [_VP, _I32, _VP, _c.POINTER(_VP)]),
+    "yahkv_batch_destroy": (None, [_VP]),
+    "yahkv_batch_prepare": (_I32, [_VP, _I32, _PI32, _VP]),
+    "yahkv_batch_plan": (_I32, [_VP, _VP]),
+    "yahkv_batch_decode_layer": (_I32, [_VP, _I32, _VP, _VP, _VP, _VP, _VP, _I32, _VP]),
+    "yahkv_batch_advance": (_I32, [_VP, _VP]),
+    "yahkv_batch_commit": (_I32, [_VP, _I32]),
     "yahkv_snapshot_save": (_I32, [_VP, _I32, _VP, _c.c_char_p]),
     "yahkv_snapshot_load": (_I32, [_VP, _c.c_char_p, _VP, _PI32]),
     "yahkv_device_bytes": (_I32, [_VP, _PI64]),
@@ -185,6 +192,42 @@ def attend_decode_noalloc(*, fmt, n_layers, num_pages, layer, kcodes, vcodes, ks
     rc = lib.yahkv_attend_decode_noalloc(ctypes.byref(args), err, len(err))
     if rc != OK:
         raise YahkvError(rc, err.value.decode())
+
+
+class DecodeBatch:
+    """Device-resident decode stepping over a fixed set of sequences (yahkv_batch): plan / decode_layer / advance
+    touch no host state and may be captured into a CUDA graph; prepare and commit are the host-side bookends."""
+
+    def __init__(self, cache, seq_ids):
+        self.cache = cache
+        seq_ids = _i32(seq_ids)
+        self.n = len(seq_ids)
+        self._h = ctypes.c_void_p()
+        cache._check(lib.yahkv_batch_create(cache._h, self.n, _ptr(seq_ids), ctypes.byref(self._h)))
+
+    def close(self):
+        if self._h:
+            lib.yahkv_batch_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def prepare(self, horizon_steps, stream=None):
+        """Returns True when the unit layout changed (a captured graph must then be captured again)."""
+        changed = ctypes.c_int32()
+        self.cache._check(lib.yahkv_batch_prepare(self._h, horizon_steps, ctypes.byref(changed), _ptr(stream)))
+        return bool(changed.value)
+
+    def plan(self, stream=None):
+        self.cache._check(lib.yahkv_batch_plan(self._h, _ptr(stream)))
+
+    def decode_layer(self, layer, k, v, q, out, gate=None, out_dtype=OUT_F16, stream=None):
+        self.cache._check(lib.yahkv_batch_decode_layer(self._h, layer, _ptr(k), _ptr(v), _ptr(q), _ptr(gate), _ptr(out),
+                                                       out_dtype, _ptr(stream)))
+
+    def advance(self, stream=None):
+        self.cache._check(lib.yahkv_batch_advance(self._h, _ptr(stream)))
+
+    def commit(self, steps):
+        self.cache._check(lib.yahkv_batch_commit(self._h, steps))
 
 
 class KvCache:
