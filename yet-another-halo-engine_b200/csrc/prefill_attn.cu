@@ -132,15 +132,17 @@ __host__ __device__ constexpr std::uint32_t InstrDesc(int m, int n, bool b_mn_ma
 // D(tmem) (+)= A(tmem) * B(smem). The A operand sits in tensor memory (row = lane, two fp16 per 32-bit column), so an
 // MMA step reads only its B slice from shared memory: with both operands in shared memory this kernel was bound by
 // shared-memory bandwidth (the 64 KB Q tile was re-read for every 64-key tile).
-__device__ __forceinline__ void UmmaF16Ts(std::uint32_t d_tmem, std::uint32_t a_tmem, std::uint64_t b_desc,
-                                          std::uint32_t idesc, bool accumulate) {
+__device__ __forceinline__ void UmmaF16Ts(std::uint32_t d_tmem, std::uint32_t a_tmem, std::uint32_t b_desc_lo,
+                                          std::uint32_t b_desc_hi, std::uint32_t idesc, bool accumulate) {
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      ".reg .b64 bd;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "mov.b64 bd, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %4, p;\n"
       "}\n" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate ? 1U : 0U)
+      "r"(a_tmem), "r"(b_desc_lo), "r"(b_desc_hi), "r"(idesc), "r"(accumulate ? 1U : 0U)
       : "memory");
 }
 __device__ __forceinline__ void UmmaCommit(std::uint64_t* bar) {
@@ -276,38 +278,57 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     // ------------------------------ MMA issuer ------------------------------
     // The tensor pipe executes in issue order, which is what makes the buffer reuse safe without further barriers:
     // S(j+2) is issued after P(j) V(j), the last reader of that S / P buffer.
+    // The issuing thread is a single lane running dependent scalar code, so everything per MMA is kept to a couple of
+    // instructions: descriptors are split into a constant high word and a low word = (stage base + compile-time
+    // offset), ring positions are running counters. With descriptors rebuilt per MMA the issue path itself took ~100
+    // clocks per instruction and bound the kernel.
     if (lane == 0) {
       constexpr std::uint32_t idesc_s = InstrDesc(kTileM, kTileN, false);
       constexpr std::uint32_t idesc_o = InstrDesc(kTileM, kHeadDim, true);
+      // descriptor words (see SmemDesc): K-major operand lbo 16 B, sbo 1024 B; MN-major V lbo = 64-dim block pitch
+      constexpr std::uint32_t desc_hi = (1024U >> 4) | (1U << 14) | (2U << 29);
+      std::uint32_t k_lo[kKvStages], v_lo[kKvStages];
+#pragma unroll
+      for (int s = 0; s < kKvStages; ++s) {
+        k_lo[s] = ((SmemAddr(smem + kSmemK + s * kKvTileBytes) >> 4) & 0x3FFFU) | ((16U >> 4) << 16);
+        v_lo[s] = ((SmemAddr(smem + kSmemV + s * kKvTileBytes) >> 4) & 0x3FFFU) |
+                  ((static_cast<std::uint32_t>(kTileN * 128) >> 4) << 16);
+      }
+      const std::uint32_t q_col = tmem + kColQ, o_col = tmem + kColO;
+      int pv_s = 0;                      // ring stage and barrier parity of the next P.V tile
+      std::uint32_t pv_ph = 0;
       auto issue_pv = [&](int j) -> bool {   // O += P(j) V(j), A = P from its S buffer, 16 keys (8 columns) per step
-        const int s = j % kKvStages;
-        if (!WaitOrAbort(&bars->v_full[s], static_cast<std::uint32_t>(j / kKvStages) & 1U, abort_flag)) return false;
+        if (!WaitOrAbort(&bars->v_full[pv_s], pv_ph, abort_flag)) return false;
         if (!WaitOrAbort(&bars->p_full, static_cast<std::uint32_t>(j) & 1U, abort_flag)) return false;
         TcFenceAfter();
-        const std::uint32_t v_addr = SmemAddr(smem + kSmemV + s * kKvTileBytes);
+        const std::uint32_t p_col = tmem + kColS + (j & 1) * kTileN;
+        const std::uint32_t lo = pv_s == 0 ? v_lo[0] : pv_s == 1 ? v_lo[1] : v_lo[2];
+        UmmaF16Ts(o_col, p_col, lo, desc_hi, idesc_o, j > 0);
 #pragma unroll
-        for (int k16 = 0; k16 < kTileN / 16; ++k16)
-          UmmaF16Ts(tmem + kColO, tmem + kColS + (j & 1) * kTileN + k16 * 8,
-                    SmemDesc(v_addr + k16 * (16 * 128), kTileN * 128, 1024), idesc_o, j > 0 || k16 > 0);
-        UmmaCommit(&bars->v_empty[s]);
+        for (int k16 = 1; k16 < kTileN / 16; ++k16)
+          UmmaF16Ts(o_col, p_col + k16 * 8, lo + k16 * ((16 * 128) >> 4), desc_hi, idesc_o, true);
+        UmmaCommit(&bars->v_empty[pv_s]);
         UmmaCommit(&bars->pv_done);
+        if (++pv_s == kKvStages) pv_s = 0, pv_ph ^= 1U;
         return true;
       };
+      static_assert(kKvStages == 3, "the stage selects above are written for three stages");
       bool ok = WaitOrAbort(&bars->q_full, 0, abort_flag);
+      int s = 0;
+      std::uint32_t ph = 0;
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j % kKvStages, b = j & 1;
-        ok = WaitOrAbort(&bars->k_full[s], static_cast<std::uint32_t>(j / kKvStages) & 1U, abort_flag);
+        const int b = j & 1;
+        ok = WaitOrAbort(&bars->k_full[s], ph, abort_flag);
         if (!ok) break;
         TcFenceAfter();
-        const std::uint32_t k_addr = SmemAddr(smem + kSmemK + s * kKvTileBytes);
+        const std::uint32_t lo = s == 0 ? k_lo[0] : s == 1 ? k_lo[1] : k_lo[2];
+        const std::uint32_t s_col = tmem + kColS + b * kTileN;
 #pragma unroll
-        for (int kb = 0; kb < 4; ++kb)
-#pragma unroll
-          for (int k16 = 0; k16 < 4; ++k16)   // A = Q from tensor memory, 16 dims (8 columns) per step
-            UmmaF16Ts(tmem + kColS + b * kTileN, tmem + kColQ + (kb * 4 + k16) * 8,
-                      SmemDesc(k_addr + kb * (kTileN * 128) + k16 * 32, 16, 1024), idesc_s, kb > 0 || k16 > 0);
+        for (int i = 0; i < 16; ++i)   // A = Q from tensor memory, 16 dims (8 columns) per step; 64-dim blocks 8 KB apart
+          UmmaF16Ts(s_col, q_col + i * 8, lo + (((i >> 2) * (kTileN * 128) + (i & 3) * 32) >> 4), desc_hi, idesc_s, i > 0);
         UmmaCommit(&bars->k_empty[s]);
         UmmaCommit(&bars->s_full[b]);
+        if (++s == kKvStages) s = 0, ph ^= 1U;
         // the previous tile's P.V goes behind this tile's S, so the tensor pipe has work while softmax(j) runs
         if (j >= 1) ok = issue_pv(j - 1);
       }
