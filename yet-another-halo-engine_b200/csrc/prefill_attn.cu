@@ -149,6 +149,11 @@ __device__ __forceinline__ void UmmaCommit(std::uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(SmemAddr(bar))
                : "memory");
 }
+__device__ __forceinline__ bool ElectOne() {   // one lane of a converged warp
+  std::uint32_t e;
+  asm volatile("{ .reg .pred P; elect.sync _|P, 0xffffffff; selp.u32 %0, 1, 0, P; }" : "=r"(e));
+  return e != 0;
+}
 __device__ __forceinline__ void TcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void TcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void TmemLd32(std::uint32_t addr, std::uint32_t (&r)[32]) {
@@ -254,35 +259,47 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
 
   if (warp == kWarpTma) {
     // ------------------------------ TMA producer: K and V tiles into their rings ------------------------------
-    if (lane == 0) {
-      PrefetchTensorMap(&kmap);
-      PrefetchTensorMap(&vmap);
+    {   // the warp stays converged; one elected lane issues the copies
+      const bool elected = ElectOne();
+      if (elected) {
+        PrefetchTensorMap(&kmap);
+        PrefetchTensorMap(&vmap);
+      }
       bool ok = true;
+      int s = 0;
+      std::uint32_t ph = 1;   // parity of the "empty" phase to wait for: 0 on the ring's second round, then alternating
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j % kKvStages;
-        const std::uint32_t ph = static_cast<std::uint32_t>(j / kKvStages) & 1U;
         const int y = tile.kv_row0 + j * kTileN;
-        if (j >= kKvStages) ok = WaitOrAbort(&bars->k_empty[s], ph ^ 1U, abort_flag);
+        if (j >= kKvStages) ok = WaitOrAbort(&bars->k_empty[s], ph, abort_flag);
         if (!ok) break;
-        MbarArriveExpectTx(&bars->k_full[s], kKvTileBytes);
-        for (int kb = 0; kb < 4; ++kb)
-          TmaLoad2D(smem + kSmemK + s * kKvTileBytes + kb * (kTileN * 128), &kmap, kb * 64, y, &bars->k_full[s]);
-        if (j >= kKvStages) ok = WaitOrAbort(&bars->v_empty[s], ph ^ 1U, abort_flag);
+        if (elected) {
+          MbarArriveExpectTx(&bars->k_full[s], kKvTileBytes);
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb)
+            TmaLoad2D(smem + kSmemK + s * kKvTileBytes + kb * (kTileN * 128), &kmap, kb * 64, y, &bars->k_full[s]);
+        }
+        if (j >= kKvStages) ok = WaitOrAbort(&bars->v_empty[s], ph, abort_flag);
         if (!ok) break;
-        MbarArriveExpectTx(&bars->v_full[s], kKvTileBytes);
-        for (int kb = 0; kb < 4; ++kb)
-          TmaLoad2D(smem + kSmemV + s * kKvTileBytes + kb * (kTileN * 128), &vmap, kb * 64, y, &bars->v_full[s]);
+        if (elected) {
+          MbarArriveExpectTx(&bars->v_full[s], kKvTileBytes);
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb)
+            TmaLoad2D(smem + kSmemV + s * kKvTileBytes + kb * (kTileN * 128), &vmap, kb * 64, y, &bars->v_full[s]);
+        }
+        if (++s == kKvStages) s = 0, ph ^= 1U;
       }
     }
   } else if (warp == kWarpMma) {
     // ------------------------------ MMA issuer ------------------------------
     // The tensor pipe executes in issue order, which is what makes the buffer reuse safe without further barriers:
     // S(j+2) is issued after P(j) V(j), the last reader of that S / P buffer.
-    // The issuing thread is a single lane running dependent scalar code, so everything per MMA is kept to a couple of
-    // instructions: descriptors are split into a constant high word and a low word = (stage base + compile-time
-    // offset), ring positions are running counters. With descriptors rebuilt per MMA the issue path itself took ~100
-    // clocks per instruction and bound the kernel.
-    if (lane == 0) {
+    // Issue cost is what bounds this kernel, so the whole warp runs the loop converged and only the tcgen05.mma /
+    // tcgen05.commit instructions are predicated on the elected lane: operands that are uniform across a converged
+    // warp reach the instruction without per-lane register traffic (measured: ~67 clocks per MMA issued from inside
+    // a lane-0 branch, under 40 from a converged warp). Descriptors are a constant high word and a low word = stage
+    // base + compile-time offset; ring positions are running counters.
+    {
+      const bool elected = ElectOne();
       constexpr std::uint32_t idesc_s = InstrDesc(kTileM, kTileN, false);
       constexpr std::uint32_t idesc_o = InstrDesc(kTileM, kHeadDim, true);
       // descriptor words (see SmemDesc): K-major operand lbo 16 B, sbo 1024 B; MN-major V lbo = 64-dim block pitch
@@ -303,12 +320,12 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         TcFenceAfter();
         const std::uint32_t p_col = tmem + kColS + (j & 1) * kTileN;
         const std::uint32_t lo = pv_s == 0 ? v_lo[0] : pv_s == 1 ? v_lo[1] : v_lo[2];
-        UmmaF16Ts(o_col, p_col, lo, desc_hi, idesc_o, j > 0);
+        if (elected) UmmaF16Ts(o_col, p_col, lo, desc_hi, idesc_o, j > 0);
 #pragma unroll
         for (int k16 = 1; k16 < kTileN / 16; ++k16)
-          UmmaF16Ts(o_col, p_col + k16 * 8, lo + k16 * ((16 * 128) >> 4), desc_hi, idesc_o, true);
-        UmmaCommit(&bars->v_empty[pv_s]);
-        UmmaCommit(&bars->pv_done);
+          if (elected) UmmaF16Ts(o_col, p_col + k16 * 8, lo + k16 * ((16 * 128) >> 4), desc_hi, idesc_o, true);
+        if (elected) UmmaCommit(&bars->v_empty[pv_s]);
+        if (elected) UmmaCommit(&bars->pv_done);
         if (++pv_s == kKvStages) pv_s = 0, pv_ph ^= 1U;
         return true;
       };
@@ -325,9 +342,9 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         const std::uint32_t s_col = tmem + kColS + b * kTileN;
 #pragma unroll
         for (int i = 0; i < 16; ++i)   // A = Q from tensor memory, 16 dims (8 columns) per step; 64-dim blocks 8 KB apart
-          UmmaF16Ts(s_col, q_col + i * 8, lo + (((i >> 2) * (kTileN * 128) + (i & 3) * 32) >> 4), desc_hi, idesc_s, i > 0);
-        UmmaCommit(&bars->k_empty[s]);
-        UmmaCommit(&bars->s_full[b]);
+          if (elected) UmmaF16Ts(s_col, q_col + i * 8, lo + (((i >> 2) * (kTileN * 128) + (i & 3) * 32) >> 4), desc_hi, idesc_s, i > 0);
+        if (elected) UmmaCommit(&bars->k_empty[s]);
+        if (elected) UmmaCommit(&bars->s_full[b]);
         if (++s == kKvStages) s = 0, ph ^= 1U;
         // the previous tile's P.V goes behind this tile's S, so the tensor pipe has work while softmax(j) runs
         if (j >= 1) ok = issue_pv(j - 1);
