@@ -208,8 +208,11 @@ struct PrefillBars {
   std::uint64_t k_full[kKvStages], k_empty[kKvStages];
   std::uint64_t v_full[kKvStages], v_empty[kKvStages];
   std::uint64_t s_full[2]; // MMA -> softmax: S(j) is in its buffer
-  std::uint64_t p_full;    // softmax -> MMA: P(j) written over S(j), O rescaled
+  std::uint64_t p_full[2]; // softmax -> MMA: P(j) written over S(j), O rescaled; one per tile parity
+  std::uint64_t m_posted[2];   // softmax group of tile j -> group of tile j + 1: m(j) is in shared memory
   std::uint64_t pv_done;   // MMA -> softmax: O += P(j) V(j) complete
+  std::uint64_t o_done;    // MMA -> softmax: the last P.V is complete (a parity wait on pv_done may lag at most one phase,
+                           // which the epilogue cannot guarantee)
   std::uint32_t tmem_base;
   int abort_flag;
 };
@@ -232,7 +235,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     return;
   }
   if (threadIdx.x == 0) {
-    MbarInit(&bars->q_full, kSoftmaxThreads);
+    MbarInit(&bars->q_full, kSoftmaxThreads / 32);   // one arrival per softmax warp
     for (int s = 0; s < kKvStages; ++s) {
       MbarInit(&bars->k_full[s], 1);
       MbarInit(&bars->k_empty[s], 1);
@@ -241,8 +244,12 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     }
     MbarInit(&bars->s_full[0], 1);
     MbarInit(&bars->s_full[1], 1);
-    MbarInit(&bars->p_full, kSoftmaxThreads);
+    for (int g = 0; g < 2; ++g) {
+      MbarInit(&bars->p_full[g], kSoftmaxThreads / 64);   // one arrival per warp of the tile's group
+      MbarInit(&bars->m_posted[g], kSoftmaxThreads / 64);
+    }
     MbarInit(&bars->pv_done, 1);
+    MbarInit(&bars->o_done, 1);
     bars->abort_flag = 0;
     FenceBarrierInit();
   }
@@ -316,7 +323,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       std::uint32_t pv_ph = 0;
       auto issue_pv = [&](int j) -> bool {   // O += P(j) V(j), A = P from its S buffer, 16 keys (8 columns) per step
         if (!WaitOrAbort(&bars->v_full[pv_s], pv_ph, abort_flag)) return false;
-        if (!WaitOrAbort(&bars->p_full, static_cast<std::uint32_t>(j) & 1U, abort_flag)) return false;
+        if (!WaitOrAbort(&bars->p_full[j & 1], static_cast<std::uint32_t>(j >> 1) & 1U, abort_flag)) return false;
         TcFenceAfter();
         const std::uint32_t p_col = tmem + kColS + (j & 1) * kTileN;
         const std::uint32_t lo = pv_s == 0 ? v_lo[0] : pv_s == 1 ? v_lo[1] : v_lo[2];
@@ -349,15 +356,15 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         // the previous tile's P.V goes behind this tile's S, so the tensor pipe has work while softmax(j) runs
         if (j >= 1) ok = issue_pv(j - 1);
       }
-      if (ok && n_tiles > 0) issue_pv(n_tiles - 1);
+      if (ok && n_tiles > 0) ok = issue_pv(n_tiles - 1);
+      if (ok && elected) UmmaCommit(&bars->o_done);
     }
   } else {
-    // ------------------ softmax, correction, epilogue: two threads per query row, half the columns each ------------------
-    // Warps 0-3 take columns 0-31 of a tile's 64 (and O columns 0-127), warps 4-7 the rest; warp w and w + 4 hold the
-    // same 32 rows (a warp reaches TMEM lanes 32 (w % 4) .. + 31). The two halves of a row swap their maxima through
-    // shared memory once per tile, so both keep the same running max; the row sums are joined in the epilogue.
+    // ------------------ softmax, correction, epilogue: two warpgroups of one thread per query row ------------------
+    // Warp w and w + 4 hold the same 32 rows (a warp reaches TMEM lanes 32 (w % 4) .. + 31). Group hc = 0 is warps
+    // 0-3, group 1 warps 4-7; for the Q load and the epilogue a group takes half of the head dimension.
     const int r = threadIdx.x & (kTileM - 1);                    // query row 0..127
-    const int hc = threadIdx.x >> 7;                             // column half
+    const int hc = threadIdx.x >> 7;                             // warpgroup
     const std::uint32_t lane_addr = tmem + (static_cast<std::uint32_t>((warp & 3) * 32) << 16);
     // Q row -> tensor memory: this thread's 128 dims (256 B) as 64 columns of fp16 pairs. Rows past the chunk are zero.
     {
@@ -376,96 +383,116 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       }
       TmemWaitSt();
       TcFenceBefore();
-      MbarArrive(&bars->q_full);
+      __syncwarp();
+      if (lane == 0) MbarArrive(&bars->q_full);
     }
+    // Tiles alternate between the two warpgroups: group g = hc runs the softmax of tiles j = g, g + 2, ..., one
+    // thread per query row with all 64 columns, so a tile's softmax may take up to two tile periods before it holds
+    // the tensor pipe back. The rows' reference maximum travels between the groups through shared memory: the
+    // group of tile j posts m(j) as soon as it has decided it (before its exponentials), the group of tile j + 1
+    // picks it up. Each group keeps its own partial row sum, relative to the reference it last saw.
     const int my_last_key = tile.pos0 + r;                       // row r sees keys 0 .. pos0 + r
-    float m_run = -INFINITY, l_run = 0.0F;
-    float* xmax = reinterpret_cast<float*>(smem + kSmemBars + kBarBytes);   // [2 parities][2 halves][128 rows]
+    float m_mine = -INFINITY, l_mine = 0.0F;
+    float* mref = reinterpret_cast<float*>(smem + kSmemBars + kBarBytes);   // [128 rows]
     bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      const int b = j & 1;
-      ok = WaitOrAbort(&bars->s_full[b], static_cast<std::uint32_t>(j >> 1) & 1U, abort_flag);
+    for (int j = hc; j < n_tiles; j += 2) {
+      const std::uint32_t ph = static_cast<std::uint32_t>(j >> 1) & 1U;
+      ok = WaitOrAbort(&bars->s_full[hc], ph, abort_flag);
       ok = __all_sync(0xFFFFFFFFU, ok);
       if (!ok) break;
       TcFenceAfter();
-      std::uint32_t sraw[32];
-      TmemLd32(lane_addr + kColS + b * kTileN + hc * 32, sraw);
+      std::uint32_t sraw[64];
+      TmemLd32(lane_addr + kColS + hc * kTileN, *reinterpret_cast<std::uint32_t(*)[32]>(&sraw[0]));
+      TmemLd32(lane_addr + kColS + hc * kTileN + 32, *reinterpret_cast<std::uint32_t(*)[32]>(&sraw[32]));
       TmemWaitLd();
       // Row max on the raw scores (the scale is positive); the causal mask only on tiles that reach past the tile's
       // first row (a warp-uniform test), where a masked score becomes -inf.
-      const int key0 = j * kTileN + hc * 32;
       if (j * kTileN + kTileN - 1 > tile.pos0) {
 #pragma unroll
-        for (int c = 0; c < 32; ++c)
-          if (key0 + c > my_last_key) sraw[c] = 0xFF800000U;   // -inf
+        for (int c = 0; c < kTileN; ++c)
+          if (j * kTileN + c > my_last_key) sraw[c] = 0xFF800000U;   // -inf
       }
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < 32; ++c) mx[c & 3] = fmaxf(mx[c & 3], __uint_as_float(sraw[c]));
-      float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      xmax[(b * 2 + hc) * kTileM + r] = tmax;
-      // One barrier per tile: it completes the max exchange, orders it against the exchange two tiles later, and
-      // tells every thread that all 256 have finished loading S(j), whose columns P(j) is about to overwrite.
-      NamedBarrierSync(1, kSoftmaxThreads);
-      tmax = fmaxf(tmax, xmax[(b * 2 + (hc ^ 1)) * kTileM + r]) * scale_log2;   // log2 units from here on
-      const bool need = tmax > m_run + kPrefillLazyRescale;
-      if (__any_sync(0xFFFFFFFFU, need)) {   // warp-uniform (TMEM accesses are warp-wide); warps w and w + 4 agree
-        // O may only be rescaled once P(j-1) V(j-1) has completed (rare path: the running max settles after the
-        // first few tiles, so this wait is off the steady-state critical path)
+      for (int c = 0; c < kTileN; ++c) mx[c & 3] = fmaxf(mx[c & 3], __uint_as_float(sraw[c]));
+      const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;   // log2 units from here on
+      float m_ref = -INFINITY;
+      if (j >= 1) {   // m(j-1), posted by the other group
+        ok = WaitOrAbort(&bars->m_posted[hc ^ 1], static_cast<std::uint32_t>((j - 1) >> 1) & 1U, abort_flag);
+        ok = __all_sync(0xFFFFFFFFU, ok);
+        if (!ok) break;
+        m_ref = mref[r];
+      }
+      if (m_mine != m_ref) {   // the other group moved the reference: bring this group's partial sum along
+        l_mine *= Exp2Fast(m_mine - m_ref);   // m_mine = -inf only while l_mine = 0
+        m_mine = m_ref;
+      }
+      const bool need = tmax > m_ref + kPrefillLazyRescale;
+      if (__any_sync(0xFFFFFFFFU, need)) {   // warp-uniform (TMEM accesses are warp-wide)
+        // O may only be rescaled once P(j-1) V(j-1) has completed, which also means the other group has finished
+        // tile j - 1 (rare path: the reference settles after the first few tiles)
         if (j >= 1) {
           ok = WaitOrAbort(&bars->pv_done, static_cast<std::uint32_t>(j - 1) & 1U, abort_flag);
           ok = __all_sync(0xFFFFFFFFU, ok);
           if (!ok) break;
           TcFenceAfter();
         }
-        const float m_new = need ? tmax : m_run;
-        const float alpha = m_new == -INFINITY ? 1.0F : Exp2Fast(m_run - m_new);
-        m_run = m_new;
-        l_run *= alpha;
+        const float m_new = need ? tmax : m_ref;
+        const float alpha = m_new == -INFINITY ? 1.0F : Exp2Fast(m_ref - m_new);
+        m_mine = m_ref = m_new;
+        l_mine *= alpha;
         if (j >= 1) {
 #pragma unroll 1
-          for (int c0 = 0; c0 < kHeadDim / 2; c0 += 32) {
+          for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
             std::uint32_t o[32];
-            TmemLd32(lane_addr + kColO + hc * (kHeadDim / 2) + c0, o);
+            TmemLd32(lane_addr + kColO + c0, o);
             TmemWaitLd();
 #pragma unroll
             for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-            TmemSt32(lane_addr + kColO + hc * (kHeadDim / 2) + c0, o);
+            TmemSt32(lane_addr + kColO + c0, o);
           }
           TmemWaitSt();
         }
       }
-      const float neg_m = m_run == -INFINITY ? 0.0F : -m_run;
+      mref[r] = m_ref;
+      __syncwarp();
+      if (lane == 0) MbarArrive(&bars->m_posted[hc]);   // release: the warp's 32 rows of m(j) are posted
+      const float neg_m = m_ref == -INFINITY ? 0.0F : -m_ref;
       // p = 2^(s * scale - m): one fma + one ex2 per element; the row sum in fp32 before the fp16 rounding. P goes
-      // back into tensor memory as the A operand of P.V: 32 fp16 = 16 columns, at columns 16 hc .. of this S buffer.
+      // back into tensor memory as the A operand of P.V: 64 fp16 = the first 32 columns of this S buffer.
       float ls[4] = {0.0F, 0.0F, 0.0F, 0.0F};
-      std::uint32_t pk[16];
+      std::uint32_t pk[32];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
+      for (int i = 0; i < 32; ++i) {
         const float p0 = Exp2Fast(fmaf(__uint_as_float(sraw[2 * i]), scale_log2, neg_m));
         const float p1 = Exp2Fast(fmaf(__uint_as_float(sraw[2 * i + 1]), scale_log2, neg_m));
         ls[i & 3] += p0 + p1;
         const __half2 h = __floats2half2_rn(p0, p1);
         pk[i] = *reinterpret_cast<const std::uint32_t*>(&h);
       }
-      l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      TmemSt16(lane_addr + kColS + b * kTileN + hc * 16, pk);
+      l_mine += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+      TmemSt32(lane_addr + kColS + hc * kTileN, pk);
       TmemWaitSt();
       TcFenceBefore();
-      MbarArrive(&bars->p_full);
+      __syncwarp();   // every lane's P columns are in tensor memory: one arrival stands for the warp
+      if (lane == 0) MbarArrive(&bars->p_full[hc]);
     }
-    // ---- epilogue: O / l * sigmoid(gate); the two halves of a row join their sums first ----
+    // ---- epilogue: O / l * sigmoid(gate); the two groups bring their partial sums to the final reference ----
     if (ok && n_tiles > 0) {
-      ok = WaitOrAbort(&bars->pv_done, static_cast<std::uint32_t>(n_tiles - 1) & 1U, abort_flag);
+      ok = WaitOrAbort(&bars->o_done, 0, abort_flag);
       ok = __all_sync(0xFFFFFFFFU, ok);
     }
-    float* xsum = xmax;   // [2 halves][128 rows]; the max exchange is over
-    NamedBarrierSync(1, kSoftmaxThreads);   // every thread is past its last read of the max exchange
-    xsum[hc * kTileM + r] = l_run;
+    float* xsum = mref + kTileM;   // [2 groups][128 rows]
+    NamedBarrierSync(1, kSoftmaxThreads);   // the last m posted is visible to both groups
+    if (n_tiles > 0) {
+      const float m_fin = mref[r];
+      if (m_mine != m_fin) l_mine *= Exp2Fast(m_mine - m_fin);
+    }
+    xsum[hc * kTileM + r] = l_mine;
     NamedBarrierSync(1, kSoftmaxThreads);
     if (ok && n_tiles > 0) {
       TcFenceAfter();
-      const float inv = 1.0F / (l_run + xsum[(hc ^ 1) * kTileM + r]);
+      const float inv = 1.0F / (l_mine + xsum[(hc ^ 1) * kTileM + r]);
       const bool valid = r < tile.n_rows;
       const std::size_t oi = (static_cast<std::size_t>(tile.q_row0 + r) * kQHeads + tile.head) * kHeadDim + hc * (kHeadDim / 2);
 #pragma unroll 1
