@@ -205,8 +205,8 @@ __device__ __forceinline__ bool WaitOrAbort(std::uint64_t* bar, std::uint32_t pa
 
 struct PrefillBars {
   std::uint64_t q_full;    // softmax threads -> MMA: Q is in tensor memory
-  std::uint64_t k_full[kKvStages], k_empty[kKvStages];
-  std::uint64_t v_full[kKvStages], v_empty[kKvStages];
+  std::uint64_t kv_full[kKvStages];    // TMA -> MMA: K(j) and V(j) have landed (one wait per tile for both)
+  std::uint64_t kv_empty[kKvStages];   // MMA -> TMA: P(j) V(j), the last reader of the stage, is complete
   std::uint64_t s_full[2]; // MMA -> softmax: S(j) is in its buffer
   std::uint64_t p_full[2]; // softmax -> MMA: P(j) written over S(j), O rescaled; one per tile parity
   std::uint64_t m_posted[2];   // softmax group of tile j -> group of tile j + 1: m(j) is in shared memory
@@ -237,10 +237,8 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
   if (threadIdx.x == 0) {
     MbarInit(&bars->q_full, kSoftmaxThreads / 32);   // one arrival per softmax warp
     for (int s = 0; s < kKvStages; ++s) {
-      MbarInit(&bars->k_full[s], 1);
-      MbarInit(&bars->k_empty[s], 1);
-      MbarInit(&bars->v_full[s], 1);
-      MbarInit(&bars->v_empty[s], 1);
+      MbarInit(&bars->kv_full[s], 1);
+      MbarInit(&bars->kv_empty[s], 1);
     }
     MbarInit(&bars->s_full[0], 1);
     MbarInit(&bars->s_full[1], 1);
@@ -277,21 +275,16 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       std::uint32_t ph = 1;   // parity of the "empty" phase to wait for: 0 on the ring's second round, then alternating
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int y = tile.kv_row0 + j * kTileN;
-        if (j >= kKvStages) ok = WaitOrAbort(&bars->k_empty[s], ph, abort_flag);
+        if (j >= kKvStages) ok = WaitOrAbort(&bars->kv_empty[s], ph, abort_flag);
         if (!ok) break;
         if (elected) {
-          MbarArriveExpectTx(&bars->k_full[s], kKvTileBytes);
+          MbarArriveExpectTx(&bars->kv_full[s], 2 * kKvTileBytes);
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb)
-            TmaLoad2D(smem + kSmemK + s * kKvTileBytes + kb * (kTileN * 128), &kmap, kb * 64, y, &bars->k_full[s]);
-        }
-        if (j >= kKvStages) ok = WaitOrAbort(&bars->v_empty[s], ph, abort_flag);
-        if (!ok) break;
-        if (elected) {
-          MbarArriveExpectTx(&bars->v_full[s], kKvTileBytes);
+            TmaLoad2D(smem + kSmemK + s * kKvTileBytes + kb * (kTileN * 128), &kmap, kb * 64, y, &bars->kv_full[s]);
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb)
-            TmaLoad2D(smem + kSmemV + s * kKvTileBytes + kb * (kTileN * 128), &vmap, kb * 64, y, &bars->v_full[s]);
+            TmaLoad2D(smem + kSmemV + s * kKvTileBytes + kb * (kTileN * 128), &vmap, kb * 64, y, &bars->kv_full[s]);
         }
         if (++s == kKvStages) s = 0, ph ^= 1U;
       }
@@ -319,10 +312,8 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
                   ((static_cast<std::uint32_t>(kTileN * 128) >> 4) << 16);
       }
       const std::uint32_t q_col = tmem + kColQ, o_col = tmem + kColO;
-      int pv_s = 0;                      // ring stage and barrier parity of the next P.V tile
-      std::uint32_t pv_ph = 0;
+      int pv_s = 0;                      // ring stage of the next P.V tile (its V arrived with the K of S(j))
       auto issue_pv = [&](int j) -> bool {   // O += P(j) V(j), A = P from its S buffer, 16 keys (8 columns) per step
-        if (!WaitOrAbort(&bars->v_full[pv_s], pv_ph, abort_flag)) return false;
         if (!WaitOrAbort(&bars->p_full[j & 1], static_cast<std::uint32_t>(j >> 1) & 1U, abort_flag)) return false;
         TcFenceAfter();
         const std::uint32_t p_col = tmem + kColS + (j & 1) * kTileN;
@@ -331,9 +322,9 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
 #pragma unroll
         for (int k16 = 1; k16 < kTileN / 16; ++k16)
           if (elected) UmmaF16Ts(o_col, p_col + k16 * 8, lo + k16 * ((16 * 128) >> 4), desc_hi, idesc_o, true);
-        if (elected) UmmaCommit(&bars->v_empty[pv_s]);
+        if (elected) UmmaCommit(&bars->kv_empty[pv_s]);
         if (elected) UmmaCommit(&bars->pv_done);
-        if (++pv_s == kKvStages) pv_s = 0, pv_ph ^= 1U;
+        if (++pv_s == kKvStages) pv_s = 0;
         return true;
       };
       static_assert(kKvStages == 3, "the stage selects above are written for three stages");
@@ -342,7 +333,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       std::uint32_t ph = 0;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int b = j & 1;
-        ok = WaitOrAbort(&bars->k_full[s], ph, abort_flag);
+        ok = WaitOrAbort(&bars->kv_full[s], ph, abort_flag);
         if (!ok) break;
         TcFenceAfter();
         const std::uint32_t lo = s == 0 ? k_lo[0] : s == 1 ? k_lo[1] : k_lo[2];
@@ -350,7 +341,6 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
 #pragma unroll
         for (int i = 0; i < 16; ++i)   // A = Q from tensor memory, 16 dims (8 columns) per step; 64-dim blocks 8 KB apart
           if (elected) UmmaF16Ts(s_col, q_col + i * 8, lo + (((i >> 2) * (kTileN * 128) + (i & 3) * 32) >> 4), desc_hi, idesc_s, i > 0);
-        if (elected) UmmaCommit(&bars->k_empty[s]);
         if (elected) UmmaCommit(&bars->s_full[b]);
         if (++s == kKvStages) s = 0, ph ^= 1U;
         // the previous tile's P.V goes behind this tile's S, so the tensor pipe has work while softmax(j) runs
