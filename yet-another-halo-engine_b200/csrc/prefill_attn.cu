@@ -14,20 +14,28 @@
 //   S = Q K^T   tcgen05.mma kind::f16, M 128, N 64 (one 64-key tile), K 256 in 16 steps; A = Q held in tensor memory
 //               for the whole CTA, B = the K tile in shared memory (K-major, 128-byte swizzle, four 64-dim TMA
 //               boxes), D = S in TMEM.
-//   softmax     eight warps, two threads per query row (32 columns each): tcgen05.ld, causal mask, running max with a
-//               lazy rescale of O (threshold 2^8), P = 2^(s - m) as fp16 written back over S with tcgen05.st.
+//   softmax     two warpgroups of one thread per query row; tiles alternate between them. tcgen05.ld of the 64
+//               scores, causal mask, reference max with a lazy rescale of O (threshold 2^8) handed from the group of
+//               tile j to the group of tile j + 1 through shared memory, P = 2^(s - m) as fp16 written back over S
+//               with tcgen05.st. Each group keeps a partial row sum; the epilogue joins them.
 //   O += P V    tcgen05.mma M 128, N 256, K 64 in 4 steps; A = P from tensor memory, B = the V tile as loaded
 //               (token-major = MN-major B operand, 128-byte swizzle), D = O in TMEM (256 columns).
 // Both A operands live in tensor memory because with them in shared memory the kernel was bound by shared-memory
-// bandwidth (the 64 KB Q tile re-read for every key tile): measured 103 clocks per S step and 238 per P.V step
-// against 32 and 128 at the tensor rate.
-// TMEM columns (all 512): S / P double-buffered 2 x 64, O 256, Q 128. Shared memory: K ring 3 x 32 KB, V ring 3 x 32 KB.
-// Warp roles: 0-7 softmax / correction / epilogue, 8 TMA producer, 9 MMA issuer and TMEM owner. No multicast, no
-// cluster. Every mbarrier wait is bounded and abortable: a wait that gives up raises a CTA-wide abort flag, every
-// role leaves its loop, TMEM is freed, and the status word tells the host the call's results are invalid.
+// bandwidth (the 64 KB Q tile re-read for every key tile).
+// TMEM columns (all 512): S / P double-buffered 2 x 64, O 256, Q 128. Shared memory: three stages of K tile + V tile
+// (64 KB each), one full / empty barrier pair per stage.
+// Warp roles: 0-7 softmax / correction / epilogue, 8 TMA producer, 9 MMA issuer and TMEM owner; the producer and the
+// issuer run their loops as converged warps and predicate only the asynchronous instructions on an elected lane
+// (issued from inside a lane-0 branch a tcgen05.mma cost ~67 clocks of issue, from a converged warp ~27). No
+// multicast, no cluster. Every mbarrier wait is bounded and abortable: a wait that gives up raises a CTA-wide abort
+// flag, every role leaves its loop, TMEM is freed, and the status word tells the host the call's results are invalid.
 //
-// The six query heads of a GQA group are separate CTAs here, so a K/V tile is re-read from L2 by six CTAs; pairing
-// CTAs on one tile (cta_group::2) is the next step for this kernel.
+// What bounds it: the tensor pipe needs 1,024 clocks per 64-key tile (16 x 32 + 4 x 128) and the measured steady
+// state is ~1,430. The six query heads of a GQA group times the query tiles are separate CTAs, so every CTA pulls
+// its own 64 KB per tile from L2: 45 B/clock/SM, about 10.5 TB/s over the chip, which is where the MMA warp's waits
+// for loads come from (~125 clocks per tile). A CTA pair per two heads (cta_group::2, half of each B operand per
+// CTA) removes those waits but puts two cross-CTA signals into the S -> softmax -> P.V chain, and with only two S
+// buffers in TMEM that chain then bounds the tile at ~1,700 clocks; it needs a third S buffer (Q out of TMEM) to pay.
 #include <cuda_fp16.h>
 
 #include <cmath>
@@ -111,18 +119,10 @@ constexpr int kColQ = 384;    // 128 columns = 256 fp16 per row
 constexpr float kPrefillLazyRescale = 8.0F;
 constexpr int kStatusPrefillAbort = 3;
 
-// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
+// Shared-memory matrix descriptors, 128-byte swizzle (layout type 2), descriptor version 1: bits 0-13 start address
+// >> 4, 16-29 leading byte offset >> 4, 32-45 stride byte offset >> 4, bit 46 version, 61-63 layout.
 //   K-major operand  [rows][64 fp16]: rows 128 B apart, groups of 8 rows 1024 B apart (stride byte offset).
 //   MN-major operand [keys][64 fp16] x blocks: 8-key groups 1024 B apart (stride), 64-element blocks `lbo` apart.
-__device__ __forceinline__ std::uint64_t SmemDesc(std::uint32_t addr, std::uint32_t lbo_bytes, std::uint32_t sbo_bytes) {
-  std::uint64_t d = 0;
-  d |= static_cast<std::uint64_t>((addr >> 4) & 0x3FFFU);
-  d |= static_cast<std::uint64_t>((lbo_bytes >> 4) & 0x3FFFU) << 16;
-  d |= static_cast<std::uint64_t>((sbo_bytes >> 4) & 0x3FFFU) << 32;
-  d |= 1ULL << 46;   // version
-  d |= 2ULL << 61;   // SWIZZLE_128B
-  return d;
-}
 // Instruction descriptor of kind::f16: fp16 A and B, fp32 accumulate, A K-major.
 __host__ __device__ constexpr std::uint32_t InstrDesc(int m, int n, bool b_mn_major) {
   return (1U << 4) | (0U << 7) | (0U << 10) | (0U << 15) | ((b_mn_major ? 1U : 0U) << 16) |
@@ -174,14 +174,6 @@ __device__ __forceinline__ void TmemSt32(std::uint32_t addr, const std::uint32_t
       "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
       "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
       "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-__device__ __forceinline__ void TmemSt16(std::uint32_t addr, const std::uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
-      "%15, %16};" ::"r"(addr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
 __device__ __forceinline__ void TmemWaitLd() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -302,7 +294,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       const bool elected = ElectOne();
       constexpr std::uint32_t idesc_s = InstrDesc(kTileM, kTileN, false);
       constexpr std::uint32_t idesc_o = InstrDesc(kTileM, kHeadDim, true);
-      // descriptor words (see SmemDesc): K-major operand lbo 16 B, sbo 1024 B; MN-major V lbo = 64-dim block pitch
+      // descriptor words: K-major operand lbo 16 B, sbo 1024 B; MN-major V lbo = 64-dim block pitch
       constexpr std::uint32_t desc_hi = (1024U >> 4) | (1U << 14) | (2U << 29);
       std::uint32_t k_lo[kKvStages], v_lo[kKvStages];
 #pragma unroll
