@@ -155,30 +155,36 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
   const std::int32_t* row = tables + static_cast<std::size_t>(u.seq) * table_stride + u.page_begin;
 
   // Gather of one page into a ring stage: 2 TMA boxes per side (q8_0; 1 for q4_0) + the two scale records, all
-  // completing on the stage's mbarrier. Issued by one thread.
+  // completing on the stage's mbarrier. Called by a whole converged warp with warp-uniform arguments; one elected
+  // lane issues (asynchronous copies issued from inside a single-lane branch cost several times more issue time).
   auto issue = [&](int s, std::int32_t page) {
     page = min(max(page, 0), pool.num_pages - 1);   // never trust a table entry read from memory
     const std::size_t rec = (static_cast<std::size_t>(layer) * pool.num_pages + page) * kKvHeads + u.kvh;
     const int y = static_cast<int>(rec * kPageTokens);
     std::uint8_t* st = ring + s * L::kBytes;
-    MbarArriveExpectTx(&full_bar[s], L::kBytes);
+    if (ElectOne()) {
+      MbarArriveExpectTx(&full_bar[s], L::kBytes);
 #pragma unroll
-    for (int b = 0; b < L::kBoxesPerSide; ++b) {
-      TmaLoad2D(st + L::kKOff + b * kBoxBytes, &kmap, b * 128, y, &full_bar[s]);
-      TmaLoad2D(st + L::kVOff + b * kBoxBytes, &vmap, b * 128, y, &full_bar[s]);
+      for (int b = 0; b < L::kBoxesPerSide; ++b) {
+        TmaLoad2D(st + L::kKOff + b * kBoxBytes, &kmap, b * 128, y, &full_bar[s]);
+        TmaLoad2D(st + L::kVOff + b * kBoxBytes, &vmap, b * 128, y, &full_bar[s]);
+      }
+      BulkLoad(st + L::kKsOff, pool.kscales + rec * (kPageTokens * kBlocksPerRow), kRecordScaleBytes, &full_bar[s]);
+      BulkLoad(st + L::kVsOff, pool.vscales + rec * (kPageTokens * kBlocksPerRow), kRecordScaleBytes, &full_bar[s]);
     }
-    BulkLoad(st + L::kKsOff, pool.kscales + rec * (kPageTokens * kBlocksPerRow), kRecordScaleBytes, &full_bar[s]);
-    BulkLoad(st + L::kVsOff, pool.vscales + rec * (kPageTokens * kBlocksPerRow), kRecordScaleBytes, &full_bar[s]);
   };
 
-  if (threadIdx.x == 0) {
-    PrefetchTensorMap(&kmap);
-    PrefetchTensorMap(&vmap);
-    for (int s = 0; s < L::kStages; ++s) {
-      MbarInit(&full_bar[s], 1);
-      done_cnt[s] = 0;
+  if (warp == 0) {
+    if (lane == 0) {
+      PrefetchTensorMap(&kmap);
+      PrefetchTensorMap(&vmap);
+      for (int s = 0; s < L::kStages; ++s) {
+        MbarInit(&full_bar[s], 1);
+        done_cnt[s] = 0;
+      }
+      FenceBarrierInit();
     }
-    FenceBarrierInit();
+    __syncwarp();
     for (int i = 0; i < L::kStages && i < n_pages; ++i) issue(i, __ldg(row + i));
   }
 
@@ -406,14 +412,17 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
     // The last of the eight warps to finish with the stage refills it (no warp ever waits for another one). The
     // MMAs above consumed every ldmatrix result, so this warp's reads of the stage are complete.
     __syncwarp();
+    int last = 0;
     if (lane == 0) {
       __threadfence_block();
-      if (atomicAdd(&done_cnt[s], 1) == kWarps - 1) {
+      last = atomicAdd(&done_cnt[s], 1) == kWarps - 1;
+      if (last) {
         done_cnt[s] = 0;
         __threadfence_block();
-        if (i + L::kStages < n_pages) issue(s, refill_page);
       }
     }
+    last = __shfl_sync(0xFFFFFFFFU, last, 0);
+    if (last != 0 && i + L::kStages < n_pages) issue(s, __shfl_sync(0xFFFFFFFFU, refill_page, 0));
     if (++s == L::kStages) s = 0, phase ^= 1U;
   }
   if (!alive && lane == 0) atomicExch(status, kStatusWaitTimeout);

@@ -149,11 +149,6 @@ __device__ __forceinline__ void UmmaCommit(std::uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(SmemAddr(bar))
                : "memory");
 }
-__device__ __forceinline__ bool ElectOne() {   // one lane of a converged warp
-  std::uint32_t e;
-  asm volatile("{ .reg .pred P; elect.sync _|P, 0xffffffff; selp.u32 %0, 1, 0, P; }" : "=r"(e));
-  return e != 0;
-}
 __device__ __forceinline__ void TcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void TcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void TmemLd32(std::uint32_t addr, std::uint32_t (&r)[32]) {

@@ -57,6 +57,13 @@ __device__ __forceinline__ bool MbarWait(std::uint64_t* bar, std::uint32_t parit
   }
 }
 
+// True in exactly one lane of a fully converged warp (all 32 lanes must execute it).
+__device__ __forceinline__ bool ElectOne() {
+  std::uint32_t e;
+  asm volatile("{ .reg .pred P; elect.sync _|P, 0xffffffff; selp.u32 %0, 1, 0, P; }" : "=r"(e));
+  return e != 0;
+}
+
 // 2-D tiled TMA load (no multicast): box at (x, y) of the tensor map into this CTA's shared memory.
 __device__ __forceinline__ void TmaLoad2D(void* smem_dst, const CUtensorMap* map, int x, int y, std::uint64_t* bar) {
   asm volatile(
