@@ -8,8 +8,9 @@ token per sequence, then decode-attend over the whole context. Data is synthetic
 
   value        KV GB/s: algorithmic cache bytes attended (sum of context lengths x 2176 B x layers) / device time of
                the K timed steps, inputs resident in HBM, whole job over all GPUs (weak scaling: 32 sequences per GPU).
-  e2e          the same metric through yahkv_decode_step_host: per layer the step's K/V/q come from pinned HOST
-               memory and the attention output is read back to the host inside the timed region.
+  e2e          the same metric through yahkv_decode_step_host_async / _wait: per layer the step's K/V/q come from
+               pinned HOST memory and every layer's attention output is back in host memory before the step ends,
+               all inside the timed region.
   roofline     the split-K attention kernel alone: algorithmic bytes per launch / its mean device time, from CUDA
                event pairs the library records around every launch inside the timed region.
   cpu_baseline the CPU oracle (a port: the reference has no CPU attention) on a bounded sample of the same workload.
@@ -516,8 +517,9 @@ def main():
 
         def host_step():
             n = sum(cache.seq_len(s, 0) for s in seqs) + BATCH
-            for layer in range(layers):
-                cache.decode_step_host(layer, seq_ids, hk[layer], hv[layer], hq[layer], hout[layer])
+            for layer in range(layers):   # queued back to back; the copies overlap the previous layer's kernels
+                cache.decode_step_host_async(layer, seq_ids, hk[layer], hv[layer], hq[layer], hout[layer])
+            cache.decode_step_host_wait()   # the step's outputs are in host memory
             return n
         host_step()
         barrier()
@@ -582,7 +584,7 @@ def main():
         if e2e:
             line["e2e"] = {"value": e_bytes_all / e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"],
                            "d2h_bytes_per_step": e2e["d2h"], "steps": e2e_steps - 1,
-                           "api": "yahkv_decode_step_host per layer (pinned host K/V/q in, output back to host)"}
+                           "api": "yahkv_decode_step_host_async per layer + yahkv_decode_step_host_wait per step (pinned host K/V/q in, outputs back in host memory before the step ends)"}
         if args.fmt in NCU_DRAM_PER_ALGORITHMIC_BYTE:
             line["roofline"]["traffic"] = NCU_DRAM_PER_ALGORITHMIC_BYTE[args.fmt] * part_bytes
             line["roofline"]["traffic_note"] = ("(dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of "

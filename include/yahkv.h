@@ -125,6 +125,15 @@ int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const in
 int yahkv_decode_step_host(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids, const void* k_host,
                            const void* v_host, const void* q_host, const float* gate_host, void* out_host,
                            int32_t out_dtype);
+/* The same step queued without waiting, so that a host which already holds the next layer's (or step's) inputs can
+ * queue it while this one runs: the copies go on the context's own copy-in and copy-out streams around the kernels,
+ * over two sets of staging buffers used in turn (the engine queues work the same way and waits only on the events it
+ * needs, engine/model/engine.hpp:210-225). The host buffers must be page-locked and stay untouched until
+ * yahkv_decode_step_host_wait returns, which waits for every queued read-back and reports a kernel that gave up. */
+int yahkv_decode_step_host_async(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids,
+                                 const void* k_host, const void* v_host, const void* q_host, const float* gate_host,
+                                 void* out_host, int32_t out_dtype);
+int yahkv_decode_step_host_wait(yahkv_ctx* ctx);
 
 /* ---- inspection (parity tests, checkpoints); these block until the context's queued work is done ------------- */
 

@@ -167,6 +167,40 @@ def test_host_buffer_step_matches_device_calls():
             assert np.abs(out[i] - want).max() <= ABS_TOL
 
 
+def test_pipelined_host_steps_match_the_blocking_ones():
+    """Six layer-steps queued back to back with page-locked host buffers (two staging sets in turn, copies on their own
+    streams) give bit-identical outputs to the same steps made one at a time on a second cache."""
+    rng = np.random.default_rng(77)
+    lens, n_layers = [70, 200, 129], 3
+    caches = [yahkv.KvCache(n_layers=n_layers, num_pages=16, fmt=yahkv.FMT_Q8_0, max_seqs=3, max_pages_per_seq=5)
+              for _ in range(2)]
+    seqs = [[c.seq_create() for _ in lens] for c in caches]
+    for i, n in enumerate(lens):
+        K = rng.standard_normal((n, 4, 256)).astype(np.float16)
+        V = rng.standard_normal((n, 4, 256)).astype(np.float16)
+        for c, ss in zip(caches, seqs):
+            c.seq_reserve(ss[i], n + 2)
+            for layer in range(n_layers):
+                c.append(layer, np.full(n, ss[i], np.int32), np.arange(n), dev(K), dev(V))
+    pin = lambda shape, dt: torch.empty(shape, dtype=dt).pin_memory()
+    steps = [(step, layer) for step in range(2) for layer in range(n_layers)]
+    k = [pin((3, 4, 256), torch.float16).copy_(torch.from_numpy(rng.standard_normal((3, 4, 256)).astype(np.float16))) for _ in steps]
+    v = [pin((3, 4, 256), torch.float16).copy_(torch.from_numpy(rng.standard_normal((3, 4, 256)).astype(np.float16))) for _ in steps]
+    q = [pin((3, 24, 256), torch.float16).copy_(torch.from_numpy(rng.standard_normal((3, 24, 256)).astype(np.float16))) for _ in steps]
+    out_a = [pin((3, 24, 256), torch.float32).zero_() for _ in steps]
+    out_b = [pin((3, 24, 256), torch.float32).zero_() for _ in steps]
+    for i, (_, layer) in enumerate(steps):
+        caches[0].decode_step_host_async(layer, seqs[0], k[i], v[i], q[i], out_a[i], out_dtype=yahkv.OUT_F32)
+    caches[0].decode_step_host_wait()
+    for i, (_, layer) in enumerate(steps):
+        caches[1].decode_step_host(layer, seqs[1], k[i], v[i], q[i], out_b[i], out_dtype=yahkv.OUT_F32)
+    for a, b in zip(out_a, out_b):
+        assert torch.equal(a, b) and float(a.abs().max()) > 0
+    assert [caches[0].seq_len(s, 0) for s in seqs[0]] == [n + 2 for n in lens]
+    for c in caches:
+        c.close()
+
+
 @pytest.mark.parametrize("fmt,ctx_len,batch", [(yahkv.FMT_Q8_0, 32768, 4), (yahkv.FMT_Q4_0, 131072, 1)])
 def test_full_length_properties(fmt, ctx_len, batch):
     """At the benchmark's context lengths, where the float64 oracle would take minutes: size-independent properties.

@@ -105,9 +105,17 @@ struct yahkv_ctx {
   int* counters_dev = nullptr;
   cudaStream_t stream = nullptr;
   Staging staging;
-  // device-side staging of the host-buffer entry point
-  void *hs_k = nullptr, *hs_v = nullptr, *hs_q = nullptr, *hs_out = nullptr;
-  float* hs_gate = nullptr;
+  // Device-side staging of the host-buffer entry points: two sets used in turn, so the copies of one layer-step (on
+  // their own streams) overlap the kernels of the previous one (on the context's stream).
+  struct HostStage {
+    void *k = nullptr, *v = nullptr, *q = nullptr, *out = nullptr;
+    float* gate = nullptr;
+    cudaEvent_t in_ready = nullptr, compute_done = nullptr, out_done = nullptr;
+    bool used = false;
+  };
+  HostStage hst[2];
+  int hst_next = 0;
+  cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
   std::int64_t launches = 0;
   std::int64_t device_bytes = 0;
   // optional per-kernel timing: event pairs around each launch, summed on read
@@ -201,11 +209,18 @@ int InitDevice(yahkv_ctx* ctx) {
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->status_dev, 1, true));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->counters_dev, static_cast<std::size_t>(c.max_seqs) * kKvHeads, true));
   const std::size_t ns = static_cast<std::size_t>(c.max_seqs);
-  YAHKV_CUDA(ctx, DevAlloc(ctx, reinterpret_cast<char**>(&ctx->hs_k), ns * kKvHeads * kHeadDim * 2, false));
-  YAHKV_CUDA(ctx, DevAlloc(ctx, reinterpret_cast<char**>(&ctx->hs_v), ns * kKvHeads * kHeadDim * 2, false));
-  YAHKV_CUDA(ctx, DevAlloc(ctx, reinterpret_cast<char**>(&ctx->hs_q), ns * kQHeads * kHeadDim * 2, false));
-  YAHKV_CUDA(ctx, DevAlloc(ctx, reinterpret_cast<char**>(&ctx->hs_out), ns * kQHeads * kHeadDim * 4, false));
-  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->hs_gate, ns * kQHeads * kHeadDim, false));
+  for (auto& h : ctx->hst) {
+    YAHKV_CUDA(ctx, DevAlloc(ctx, reinterpret_cast<char**>(&h.k), ns * kKvHeads * kHeadDim * 2, false));
+    YAHKV_CUDA(ctx, DevAlloc(ctx, reinterpret_cast<char**>(&h.v), ns * kKvHeads * kHeadDim * 2, false));
+    YAHKV_CUDA(ctx, DevAlloc(ctx, reinterpret_cast<char**>(&h.q), ns * kQHeads * kHeadDim * 2, false));
+    YAHKV_CUDA(ctx, DevAlloc(ctx, reinterpret_cast<char**>(&h.out), ns * kQHeads * kHeadDim * 4, false));
+    YAHKV_CUDA(ctx, DevAlloc(ctx, &h.gate, ns * kQHeads * kHeadDim, false));
+    YAHKV_CUDA(ctx, cudaEventCreateWithFlags(&h.in_ready, cudaEventDisableTiming));
+    YAHKV_CUDA(ctx, cudaEventCreateWithFlags(&h.compute_done, cudaEventDisableTiming));
+    YAHKV_CUDA(ctx, cudaEventCreateWithFlags(&h.out_done, cudaEventDisableTiming));
+  }
+  YAHKV_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->h2d_stream, cudaStreamNonBlocking));
+  YAHKV_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->d2h_stream, cudaStreamNonBlocking));
 
   void* fn = nullptr;
   cudaDriverEntryPointQueryResult qres{};
@@ -229,11 +244,17 @@ void FreeDevice(yahkv_ctx* ctx) {
   if (ctx->stream != nullptr) cudaStreamSynchronize(ctx->stream);
   void* ptrs[] = {ctx->pool.kcodes, ctx->pool.vcodes, ctx->pool.kscales, ctx->pool.vscales, ctx->tables_dev,
                   ctx->slots_dev,   ctx->units_dev,   ctx->items_dev,    ctx->partial_acc,  ctx->partial_ml,
-                  ctx->tiles_dev,   ctx->status_dev,  ctx->counters_dev, ctx->pseqs_dev, ctx->k16_dev, ctx->v16_dev,
-                  ctx->hs_k,         ctx->hs_v,         ctx->hs_q,
-                  ctx->hs_out,      ctx->hs_gate};
+                  ctx->tiles_dev,   ctx->status_dev,  ctx->counters_dev, ctx->pseqs_dev, ctx->k16_dev, ctx->v16_dev};
   for (void* p : ptrs)
     if (p != nullptr) cudaFree(p);
+  for (cudaStream_t st : {ctx->h2d_stream, ctx->d2h_stream})
+    if (st != nullptr) cudaStreamSynchronize(st), cudaStreamDestroy(st);
+  for (auto& h : ctx->hst) {
+    for (void* p : {h.k, h.v, h.q, h.out, static_cast<void*>(h.gate)})
+      if (p != nullptr) cudaFree(p);
+    for (cudaEvent_t e : {h.in_ready, h.compute_done, h.out_done})
+      if (e != nullptr) cudaEventDestroy(e);
+  }
   if (ctx->stream != nullptr) cudaStreamDestroy(ctx->stream);
   for (auto& list : ctx->timing_events)
     for (auto& pr : list) cudaEventDestroy(pr.first), cudaEventDestroy(pr.second);
@@ -607,9 +628,9 @@ int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const in
   return YAHKV_OK;
 }
 
-int yahkv_decode_step_host(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids, const void* k_host,
-                           const void* v_host, const void* q_host, const float* gate_host, void* out_host,
-                           int32_t out_dtype) {
+int yahkv_decode_step_host_async(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids,
+                                 const void* k_host, const void* v_host, const void* q_host, const float* gate_host,
+                                 void* out_host, int32_t out_dtype) {
   if (int r = RequireDevice(ctx, "decode_step_host"); r != YAHKV_OK) return r;
   if (n_seqs <= 0 || n_seqs > ctx->cfg.max_seqs) return Fail(ctx, YAHKV_ERR_INVALID, "decode_step_host: bad n_seqs");
   if (seq_ids == nullptr || k_host == nullptr || v_host == nullptr || q_host == nullptr || out_host == nullptr)
@@ -624,23 +645,52 @@ int yahkv_decode_step_host(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const 
     HostError e = ctx->host.SeqReserve(seq_ids[b], pos + 1);
     if (e.code != YAHKV_OK) return FailHost(ctx, std::move(e));
   }
-  cudaStream_t st = ctx->stream;
+  yahkv_ctx::HostStage& h = ctx->hst[ctx->hst_next];
+  cudaStream_t st = ctx->stream, in = ctx->h2d_stream, back = ctx->d2h_stream;
   const std::size_t kvb = static_cast<std::size_t>(n_seqs) * kKvHeads * kHeadDim * 2;
   const std::size_t qb = static_cast<std::size_t>(n_seqs) * kQHeads * kHeadDim * 2;
   const std::size_t ob = static_cast<std::size_t>(n_seqs) * kQHeads * kHeadDim * (out_dtype == YAHKV_OUT_F32 ? 4 : 2);
-  YAHKV_CUDA(ctx, cudaMemcpyAsync(ctx->hs_k, k_host, kvb, cudaMemcpyHostToDevice, st));
-  YAHKV_CUDA(ctx, cudaMemcpyAsync(ctx->hs_v, v_host, kvb, cudaMemcpyHostToDevice, st));
-  YAHKV_CUDA(ctx, cudaMemcpyAsync(ctx->hs_q, q_host, qb, cudaMemcpyHostToDevice, st));
+  // inputs: behind the kernels that last read this set, on the copy-in stream
+  if (h.used) YAHKV_CUDA(ctx, cudaStreamWaitEvent(in, h.compute_done, 0));
+  YAHKV_CUDA(ctx, cudaMemcpyAsync(h.k, k_host, kvb, cudaMemcpyHostToDevice, in));
+  YAHKV_CUDA(ctx, cudaMemcpyAsync(h.v, v_host, kvb, cudaMemcpyHostToDevice, in));
+  YAHKV_CUDA(ctx, cudaMemcpyAsync(h.q, q_host, qb, cudaMemcpyHostToDevice, in));
   if (gate_host != nullptr)
-    YAHKV_CUDA(ctx, cudaMemcpyAsync(ctx->hs_gate, gate_host, static_cast<std::size_t>(n_seqs) * kQHeads * kHeadDim * 4,
-                                    cudaMemcpyHostToDevice, st));
-  if (int r = yahkv_append(ctx, layer, n_seqs, seq_ids, ctx->pos_scratch.data(), ctx->hs_k, ctx->hs_v, st); r != YAHKV_OK) return r;
-  if (int r = yahkv_attend_decode(ctx, layer, n_seqs, seq_ids, ctx->hs_q, gate_host != nullptr ? ctx->hs_gate : nullptr,
-                                  ctx->hs_out, out_dtype, 0, st);
+    YAHKV_CUDA(ctx, cudaMemcpyAsync(h.gate, gate_host, static_cast<std::size_t>(n_seqs) * kQHeads * kHeadDim * 4,
+                                    cudaMemcpyHostToDevice, in));
+  YAHKV_CUDA(ctx, cudaEventRecord(h.in_ready, in));
+  // kernels: behind the inputs and behind the read-back that last used this set's output buffer
+  YAHKV_CUDA(ctx, cudaStreamWaitEvent(st, h.in_ready, 0));
+  if (h.used) YAHKV_CUDA(ctx, cudaStreamWaitEvent(st, h.out_done, 0));
+  h.used = true;
+  ctx->hst_next ^= 1;
+  if (int r = yahkv_append(ctx, layer, n_seqs, seq_ids, ctx->pos_scratch.data(), h.k, h.v, st); r != YAHKV_OK) return r;
+  if (int r = yahkv_attend_decode(ctx, layer, n_seqs, seq_ids, h.q, gate_host != nullptr ? h.gate : nullptr, h.out,
+                                  out_dtype, 0, st);
       r != YAHKV_OK)
     return r;
-  YAHKV_CUDA(ctx, cudaMemcpyAsync(out_host, ctx->hs_out, ob, cudaMemcpyDeviceToHost, st));
-  YAHKV_CUDA(ctx, cudaStreamSynchronize(st));
+  YAHKV_CUDA(ctx, cudaEventRecord(h.compute_done, st));
+  // output: behind the kernels, on the copy-out stream
+  YAHKV_CUDA(ctx, cudaStreamWaitEvent(back, h.compute_done, 0));
+  YAHKV_CUDA(ctx, cudaMemcpyAsync(out_host, h.out, ob, cudaMemcpyDeviceToHost, back));
+  YAHKV_CUDA(ctx, cudaEventRecord(h.out_done, back));
+  return YAHKV_OK;
+}
+
+int yahkv_decode_step_host_wait(yahkv_ctx* ctx) {
+  if (int r = RequireDevice(ctx, "decode_step_host_wait"); r != YAHKV_OK) return r;
+  YAHKV_CUDA(ctx, cudaStreamSynchronize(ctx->d2h_stream));   // every read-back follows its kernels
+  return CheckStatus(ctx);
+}
+
+int yahkv_decode_step_host(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids, const void* k_host,
+                           const void* v_host, const void* q_host, const float* gate_host, void* out_host,
+                           int32_t out_dtype) {
+  if (int r = yahkv_decode_step_host_async(ctx, layer, n_seqs, seq_ids, k_host, v_host, q_host, gate_host, out_host,
+                                           out_dtype);
+      r != YAHKV_OK)
+    return r;
+  YAHKV_CUDA(ctx, cudaStreamSynchronize(ctx->d2h_stream));
   return YAHKV_OK;
 }
 

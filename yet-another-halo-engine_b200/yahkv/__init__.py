@@ -122,6 +122,8 @@ SIGNATURES = {
     "yahkv_attend_decode": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _I32, _I32, _VP]),
     "yahkv_attend_prefill": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _VP, _I32, _VP]),
     "yahkv_decode_step_host": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _VP, _VP, _I32]),
+    "yahkv_decode_step_host_async": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _VP, _VP, _I32]),
+    "yahkv_decode_step_host_wait": (_I32, [_VP]),
     "yahkv_read_page": (_I32, [_VP, _I32, _I32, _I32, _VP, _VP]),
     "yahkv_write_page": (_I32, [_VP, _I32, _I32, _I32, _VP, _VP]),
     "yahkv_export_token": (_I32, [_VP, _I32, _I32, _I64, _VP, _VP]),
@@ -319,6 +321,15 @@ class KvCache:
         seq_ids = _i32(seq_ids)
         self._check(lib.yahkv_decode_step_host(self._h, layer, len(seq_ids), _ptr(seq_ids), _ptr(k), _ptr(v), _ptr(q),
                                                _ptr(gate), _ptr(out), out_dtype))
+
+    def decode_step_host_async(self, layer, seq_ids, k, v, q, out, gate=None, out_dtype=OUT_F16):
+        """Queues the step; the (page-locked) buffers must stay alive and untouched until decode_step_host_wait()."""
+        seq_ids = _i32(seq_ids)
+        self._check(lib.yahkv_decode_step_host_async(self._h, layer, len(seq_ids), _ptr(seq_ids), _ptr(k), _ptr(v),
+                                                     _ptr(q), _ptr(gate), _ptr(out), out_dtype))
+
+    def decode_step_host_wait(self):
+        self._check(lib.yahkv_decode_step_host_wait(self._h))
 
     # ---- inspection ----
     def read_page(self, layer, side, page):
