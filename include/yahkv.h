@@ -99,6 +99,17 @@ int yahkv_pages_free(const yahkv_ctx* ctx, int32_t* n);
  * engine/model/loom_decoder.hpp:233-234) and be covered by yahkv_seq_reserve. */
 int yahkv_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int32_t* seq_ids, const int64_t* positions,
                  const void* k_dev, const void* v_dev, void* stream);
+/* Replaces the reference's "rope" kernel together with the appends that follow it (QK RMSNorm + NeoX RoPE on 64 of
+ * 256 dims, theta 1e7, then dattn_kappend_q / dattn_vappend_q: engine/gpu/loom/yah_fused_qk_rope_f32.loom:1-9, :32,
+ * engine/model/loom_decoder.hpp:250-261) in one launch. q_dev [n][24][256], k_dev, v_dev [n][4][256] f32 as the
+ * projections produce them; q_weight_dev, k_weight_dev [256] f32 norm weights; eps the norm epsilon.
+ *   K: normed, rotated, rounded to fp16, quantized and scattered exactly as yahkv_append would store that fp16 row;
+ *   V: rounded to fp16, quantized and scattered;  q_out_dev [n][24][256] fp16: normed, rotated q for yahkv_attend_*.
+ * seq_ids / positions and the order rule as in yahkv_append. */
+int yahkv_rope_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int32_t* seq_ids, const int64_t* positions,
+                      const float* q_dev, const float* k_dev, const float* v_dev, const float* q_weight_dev,
+                      const float* k_weight_dev, float eps, void* q_out_dev, void* stream);
+
 /* The same with a device-resident slot mapping (slot = page * 64 + token in page; negative = skip the token).
  * Lengths are not tracked by this call: declare them with yahkv_seq_set_len. */
 int yahkv_append_slots(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int64_t* slot_mapping_dev,

@@ -88,6 +88,17 @@ def ref_dequantize(blocks, fmt):
     return y
 
 
+def rope_rows(x, weight, eps, pos):
+    """Head rows [rows][256] f32 -> RMSNorm + NeoX RoPE (64 of 256 dims, theta 1e7) -> fp16; pos: one per row."""
+    x = np.ascontiguousarray(x, np.float32).reshape(-1, 256)
+    weight = np.ascontiguousarray(weight, np.float32)
+    pos = np.ascontiguousarray(pos, np.int32)
+    assert weight.size == 256 and pos.size == x.shape[0]
+    out = np.zeros(x.shape, np.uint16)
+    _o.yahkv_oracle_rope_rows(_p(x), ctypes.c_int64(x.shape[0]), _p(weight), ctypes.c_float(eps), _p(pos), _p(out))
+    return out.view(np.float16)
+
+
 def validate_table(table, num_pages):
     table = np.ascontiguousarray(table, np.int32)
     return _o.yahkv_oracle_validate_table(_p(table), len(table), num_pages)

@@ -174,6 +174,49 @@ void yahkv_oracle_dequantize_q4_0(const std::uint8_t* src, std::uint64_t n, floa
 }
 
 // Every table entry must name a page of the pool. Returns the index of the first bad entry, or -1.
+// Head-row RMSNorm + NeoX RoPE as the reference's "rope" kernel states it
+// (engine/gpu/loom/yah_fused_qk_rope_f32.loom:4-6: inv_rms = rsqrt(sum x^2 / head_dim + eps), normed = (x * inv_rms) *
+// weight, out[p] = normed[p] cos - normed[p + half] sin, out[p + half] = normed[p] sin + normed[p + half] cos,
+// angle = pos / theta^(2 p / rotary_dim); :32 theta = 1e7; rotary_dim 64 of head_dim 256 at the engine's geometry),
+// with the operation order pinned so that a GPU kernel can reproduce the bits: the sum of squares is 32 chains of
+// eight fused multiply-adds (elements 8 l .. 8 l + 7) joined by a butterfly over distances 16, 8, 4, 2, 1; every
+// other operation is one IEEE f32 operation; cos and sin are evaluated in double precision and rounded to f32.
+// Rows are [256] f32; the result is rounded to fp16 (the append's input format). The reference has no CPU model of
+// this kernel, so this restatement is pinned by the formula only.
+void yahkv_oracle_rope_rows(const float* x, std::int64_t rows, const float* weight, float eps, const std::int32_t* pos,
+                            std::uint16_t* out_half) {
+  for (std::int64_t r = 0; r < rows; ++r) {
+    const float* xr = x + r * 256;
+    float part[32];
+    for (int l = 0; l < 32; ++l) {
+      float acc = 0.0F;
+      for (int j = 0; j < 8; ++j) acc = std::fmaf(xr[8 * l + j], xr[8 * l + j], acc);
+      part[l] = acc;
+    }
+    for (int m = 16; m >= 1; m >>= 1) {
+      float next[32];
+      for (int l = 0; l < 32; ++l) next[l] = part[l] + part[l ^ m];
+      for (int l = 0; l < 32; ++l) part[l] = next[l];
+    }
+    const float mean = part[0] * (1.0F / 256.0F);
+    const float inv = 1.0F / std::sqrt(mean + eps);
+    float n[256];
+    for (int i = 0; i < 256; ++i) {
+      const float t = xr[i] * inv;
+      n[i] = t * weight[i];
+    }
+    for (int p = 0; p < 32; ++p) {
+      const double angle = static_cast<double>(pos[r]) * std::pow(1.0e7, -2.0 * p / 64.0);
+      const float c = static_cast<float>(std::cos(angle)), sn = static_cast<float>(std::sin(angle));
+      const float a = n[p], b = n[p + 32];
+      const float ac = a * c, bs = b * sn, as = a * sn, bc = b * c;
+      n[p] = ac - bs;
+      n[p + 32] = as + bc;
+    }
+    for (int i = 0; i < 256; ++i) out_half[r * 256 + i] = FloatToHalfBits(n[i]);
+  }
+}
+
 int yahkv_oracle_validate_table(const std::int32_t* table, int n, int num_pages) {
   for (int i = 0; i < n; ++i)
     if (table[i] < 0 || table[i] >= num_pages) return i;

@@ -122,3 +122,43 @@ def test_order_and_range_errors_launch_nothing():
         cache.append(0, [s], [64], x, x)      # past the reserved pages
     assert e.value.code == yahkv.ERR_INVALID
     assert cache.launch_count() == before + 1
+
+
+@pytest.mark.parametrize("fmt", [yahkv.FMT_Q8_0, yahkv.FMT_Q4_0])
+def test_fused_rope_append_is_rope_then_append(fmt):
+    """yahkv_rope_append == the oracle's RMSNorm + RoPE (rounded to fp16) followed by the plain append, bit for bit:
+    q_out halves, pool codes, scales and placement. Two sequences, a chunk then single tokens, positions up to 4999."""
+    rng = np.random.default_rng(11)
+    num_pages, eps = 96, 1e-6
+    cache = yahkv.KvCache(n_layers=2, num_pages=num_pages, fmt=fmt, max_seqs=2, max_pages_per_seq=80, max_batch_tokens=512)
+    pool = O.PagedPool(fmt, num_pages)
+    qw = (1.0 + 0.2 * rng.standard_normal(256)).astype(np.float32)
+    kw = (1.0 + 0.2 * rng.standard_normal(256)).astype(np.float32)
+    seqs = [cache.seq_create(), cache.seq_create()]
+    starts = [0, 4700]
+    for s, n0 in zip(seqs, starts):
+        cache.seq_reserve(s, n0 + 300)
+        cache.seq_set_len(s, n0)          # earlier positions stand in as already cached
+    calls = [(np.array([seqs[0]] * 130 + [seqs[1]] * 129, np.int32),
+              np.concatenate([np.arange(130), 4700 + np.arange(129)]))]
+    calls += [(np.array(seqs, np.int32), np.array([130 + i, 4829 + i])) for i in range(3)]
+    for ids, pos in calls:
+        n = len(ids)
+        q = (rng.standard_normal((n, 24, 256)) * 2).astype(np.float32)
+        k = (rng.standard_normal((n, 4, 256)) * 3).astype(np.float32)
+        k[:, :, 5] *= 20.0                                             # an outlier channel inside the rotated dims
+        v = rng.standard_normal((n, 4, 256)).astype(np.float32)
+        q_out = torch.zeros((n, 24, 256), dtype=torch.float16, device="cuda")
+        torch.cuda.synchronize()
+        cache.rope_append(1, ids, pos, dev(q), dev(k), dev(v), dev(qw), dev(kw), eps, q_out)
+        cache.sync()
+        want_q = O.rope_rows(q, qw, eps, np.repeat(pos, 24))
+        assert np.array_equal(q_out.cpu().numpy().view(np.uint16).reshape(-1, 256), want_q.view(np.uint16))
+        k16 = O.rope_rows(k, kw, eps, np.repeat(pos, 4)).reshape(n, 4, 256)
+        v16 = v.astype(np.float16)
+        for s in seqs:
+            m = ids == s
+            pool.append(cache.seq_table(s), int(pos[m][0]), k16[m], v16[m])
+    assert_pools_equal(cache, 1, pool)
+    assert [cache.seq_len(s, 1) for s in seqs] == [133, 4832]
+    cache.close()

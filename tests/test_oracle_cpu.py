@@ -122,3 +122,21 @@ def test_prefill_oracle_agrees_with_decode_oracle():
         assert np.abs(out[i] - want).max() < 1e-12
     part = pool.attend_prefill_f64(table, start, q, q_begin=30, q_end=40, gate=gate)
     assert np.array_equal(part, out[30:40])
+
+
+def test_rope_rows_follow_the_formula():
+    # inv_rms = 1/sqrt(mean(x^2) + eps); normed = x * inv_rms * w; NeoX rotation of dims (p, p + 32), p < 32, by
+    # pos / 1e7^(2p/64); dims 64.. pass through (yah_fused_qk_rope_f32.loom:4-6, :32). Result rounded to fp16.
+    rng = np.random.default_rng(3)
+    x = (rng.standard_normal((6, 256)) * 2).astype(np.float32)
+    w = (1 + 0.1 * rng.standard_normal(256)).astype(np.float32)
+    pos = np.array([0, 1, 63, 64, 4095, 131071], np.int32)
+    got = O.rope_rows(x, w, 1e-6, pos).astype(np.float64)
+    for i, p0 in enumerate(pos):
+        xd, wd = x[i].astype(np.float64), w.astype(np.float64)
+        n = xd / np.sqrt((xd ** 2).mean() + 1e-6) * wd
+        ang = p0 / 1e7 ** (2 * np.arange(32) / 64)
+        want = n.copy()
+        want[:32] = n[:32] * np.cos(ang) - n[32:64] * np.sin(ang)
+        want[32:64] = n[:32] * np.sin(ang) + n[32:64] * np.cos(ang)
+        assert np.abs(got[i] - want).max() <= np.abs(want).max() * 2.0 ** -11 + 1e-6

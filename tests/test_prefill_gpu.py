@@ -87,6 +87,45 @@ def test_prefill_rows_equal_decode_of_the_same_position():
     assert np.abs(got[-1] - dec.cpu().numpy()[0]).max() <= ABS_TOL
 
 
+def test_full_size_chunk_properties():
+    """At the benchmark configuration's size (30,720 cached + a 2,048-token chunk, 512 key tiles per query tile), where
+    the float64 oracle would take minutes: size-independent properties.
+    (1) the softmax weights sum to one: with every cached V row equal, every output row is that row dequantized;
+    (2) a chunk row is the decode step of the same position (two different kernels, split-K vs tensor-core tiles)."""
+    cached, chunk, n = 30720, 2048, 32768
+    rng = np.random.default_rng(45)
+    cache = yahkv.KvCache(n_layers=1, num_pages=n // 64 + 2, fmt=yahkv.FMT_Q8_0, max_seqs=1, max_pages_per_seq=n // 64,
+                          max_batch_tokens=4096)
+    s = cache.seq_create()
+    cache.seq_set_table(s, rng.permutation(n // 64 + 2)[: n // 64].astype(np.int32))
+    vrow = rng.standard_normal((1, 4, 256)).astype(np.float16)
+    for p0 in range(0, n, 4096):
+        K = torch.randn((4096, 4, 256), device="cuda", dtype=torch.float16)
+        V = dev(np.broadcast_to(vrow, (4096, 4, 256)).copy())
+        torch.cuda.synchronize()
+        cache.append(0, np.full(4096, s, np.int32), np.arange(p0, p0 + 4096), K, V)
+    cache.sync()
+    q = rng.standard_normal((chunk, 24, 256)).astype(np.float16)
+    got = run_prefill(cache, 0, [s], [chunk], q, None, yahkv.OUT_F32)
+    _, vb = cache.export_token(0, s, 0)
+    want = O.dequantize(vb, yahkv.FMT_Q8_0).reshape(4, 256).astype(np.float64)
+    assert np.abs(got - np.repeat(want, 6, axis=0)[None]).max() <= ABS_TOL   # fp16(code x scale) rounds V by <= 2^-11
+    # (2): random V in the last 70 positions breaks the symmetry, then compare rows with decode steps
+    K2 = rng.standard_normal((70, 4, 256)).astype(np.float16)
+    V2 = rng.standard_normal((70, 4, 256)).astype(np.float16)
+    cache.seq_set_len(s, n - 70)
+    cache.append(0, np.full(70, s, np.int32), np.arange(n - 70, n), dev(K2), dev(V2))
+    got = run_prefill(cache, 0, [s], [chunk], q, None, yahkv.OUT_F32)
+    for row in (chunk - 1, chunk - 40):
+        cache.seq_set_len(s, n - (chunk - 1 - row))
+        dec = torch.zeros(1, 24, 256, device="cuda")
+        torch.cuda.synchronize()
+        cache.attend_decode(0, [s], dev(q[row:row + 1]), dec, out_dtype=yahkv.OUT_F32)
+        cache.sync()
+        assert np.abs(got[row] - dec.cpu().numpy()[0]).max() <= ABS_TOL
+    cache.close()
+
+
 def test_prefill_errors_launch_nothing():
     cache, pool, seqs, tables, rng = build(yahkv.FMT_Q8_0, [10], [5], seed=44)
     q = torch.zeros(20, 24, 256, dtype=torch.float16, device="cuda")

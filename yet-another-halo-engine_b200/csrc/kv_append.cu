@@ -23,31 +23,11 @@ namespace {
 
 constexpr int kAppendThreads = 256;  // 8 warps = 2 sides x 4 kv heads of one token
 
+// Quantizes one (token, side, kv head) row held by a warp (lane l: elements 8l .. 8l+7, already exact fp16 values
+// widened to f32) and stores codes and scales at the token's place in its page record.
 template <int kFmt>
-__global__ void __launch_bounds__(kAppendThreads) AppendKernel(PoolView pool, int layer,
-                                                               const std::int64_t* __restrict__ slots,
-                                                               const __half* __restrict__ k_in,
-                                                               const __half* __restrict__ v_in) {
-  const int token = blockIdx.x;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int side = warp >> 2, h = warp & 3;
-  const std::int64_t slot = slots[token];
-  if (slot < 0) return;  // padding token
-  // Writers clamp the page into the pool instead of trusting the mapping (gen_decode_attn.py:59-69).
-  std::int64_t page = slot / kPageTokens;
-  const int tok = static_cast<int>(slot % kPageTokens);
-  page = min(max(page, static_cast<std::int64_t>(0)), static_cast<std::int64_t>(pool.num_pages - 1));
-
-  const __half* src = (side == 0 ? k_in : v_in) + (static_cast<std::size_t>(token) * kKvHeads + h) * kHeadDim;
-  const uint4 raw = *reinterpret_cast<const uint4*>(src + lane * 8);
-  const __half2* hp = reinterpret_cast<const __half2*>(&raw);
-  float x[8];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 f = __half22float2(hp[i]);
-    x[2 * i] = f.x, x[2 * i + 1] = f.y;
-  }
-
+__device__ __forceinline__ void QuantizeStoreRow(const PoolView& pool, int layer, std::int64_t page, int tok, int side,
+                                                 int h, int lane, const float (&x)[8]) {
   const std::size_t rec = (static_cast<std::size_t>(layer) * pool.num_pages + static_cast<std::size_t>(page)) * kKvHeads + h;
   std::uint8_t* codes = (side == 0 ? pool.kcodes : pool.vcodes) + rec * RecordCodeBytes(kFmt) +
                         static_cast<std::size_t>(tok) * CodeBytes(kFmt);
@@ -110,6 +90,115 @@ __global__ void __launch_bounds__(kAppendThreads) AppendKernel(PoolView pool, in
   }
 }
 
+template <int kFmt>
+__global__ void __launch_bounds__(kAppendThreads) AppendKernel(PoolView pool, int layer,
+                                                               const std::int64_t* __restrict__ slots,
+                                                               const __half* __restrict__ k_in,
+                                                               const __half* __restrict__ v_in) {
+  const int token = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int side = warp >> 2, h = warp & 3;
+  const std::int64_t slot = slots[token];
+  if (slot < 0) return;  // padding token
+  // Writers clamp the page into the pool instead of trusting the mapping (gen_decode_attn.py:59-69).
+  std::int64_t page = slot / kPageTokens;
+  const int tok = static_cast<int>(slot % kPageTokens);
+  page = min(max(page, static_cast<std::int64_t>(0)), static_cast<std::int64_t>(pool.num_pages - 1));
+
+  const __half* src = (side == 0 ? k_in : v_in) + (static_cast<std::size_t>(token) * kKvHeads + h) * kHeadDim;
+  const uint4 raw = *reinterpret_cast<const uint4*>(src + lane * 8);
+  const __half2* hp = reinterpret_cast<const __half2*>(&raw);
+  float x[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(hp[i]);
+    x[2 * i] = f.x, x[2 * i + 1] = f.y;
+  }
+
+  QuantizeStoreRow<kFmt>(pool, layer, page, tok, side, h, lane, x);
+}
+
+
+// ----------------------------------------------------------------------------------------------------------------
+// Fused QK RMSNorm + NeoX RoPE + append: the reference's "rope" kernel followed by its K and V appends
+// (engine/gpu/loom/yah_fused_qk_rope_f32.loom:1-9, engine/model/loom_decoder.hpp:250-261) in one launch.
+//   inv_rms = 1 / sqrt(sum_i x[i]^2 / 256 + eps);  normed[i] = (x[i] * inv_rms) * weight[i]
+//   p < 32: out[p] = normed[p] cos - normed[p + 32] sin;  out[p + 32] = normed[p] sin + normed[p + 32] cos
+//   with angle = pos / theta^(2 p / 64), theta = 1e7; dims 64 .. 255 pass through.
+// One warp per head of one token: 24 query heads (written as fp16 for the attention), 4 K heads (normed, rotated,
+// rounded to fp16, quantized, scattered) and 4 V heads (rounded to fp16, quantized, scattered). Every f32 operation
+// is a single IEEE operation in a fixed order (no contraction, sum of squares as a per-lane fma chain followed by a
+// butterfly), and cos / sin come from a table computed on the host in double precision, so the CPU restatement
+// reproduces the bits.
+// ----------------------------------------------------------------------------------------------------------------
+constexpr int kRopeThreads = 32 * (kQHeads + 2 * kKvHeads);
+constexpr int kHalfRot = 32;   // rotary_dim 64
+
+template <int kFmt>
+__global__ void __launch_bounds__(kRopeThreads)
+    RopeAppendKernel(PoolView pool, int layer, const std::int64_t* __restrict__ slots,
+                     const std::int32_t* __restrict__ positions, const float* __restrict__ q_in,
+                     const float* __restrict__ k_in, const float* __restrict__ v_in, const float* __restrict__ q_weight,
+                     const float* __restrict__ k_weight, float eps, const float2* __restrict__ rope_tab, int rope_rows,
+                     __half* __restrict__ q_out) {
+  const int token = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool is_q = warp < kQHeads, is_v = warp >= kQHeads + kKvHeads;
+  const int h = is_q ? warp : (warp - kQHeads) & (kKvHeads - 1);
+  const float* src = is_q ? q_in + (static_cast<std::size_t>(token) * kQHeads + h) * kHeadDim
+                          : (is_v ? v_in : k_in) + (static_cast<std::size_t>(token) * kKvHeads + h) * kHeadDim;
+  float x[8];
+  {
+    const float4 a = *reinterpret_cast<const float4*>(src + lane * 8);
+    const float4 b = *reinterpret_cast<const float4*>(src + lane * 8 + 4);
+    x[0] = a.x, x[1] = a.y, x[2] = a.z, x[3] = a.w, x[4] = b.x, x[5] = b.y, x[6] = b.z, x[7] = b.w;
+  }
+  if (!is_v) {
+    float acc = 0.0F;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc = fmaf(x[j], x[j], acc);
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFU, acc, m));
+    const float inv = __fdiv_rn(1.0F, __fsqrt_rn(__fadd_rn(__fmul_rn(acc, 1.0F / kHeadDim), eps)));
+    const float* wp = (is_q ? q_weight : k_weight) + lane * 8;
+    const float4 wa = *reinterpret_cast<const float4*>(wp), wb = *reinterpret_cast<const float4*>(wp + 4);
+    const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = __fmul_rn(__fmul_rn(x[j], inv), w[j]);
+    // dims 0 .. 63 sit in lanes 0 .. 7; dim p pairs with p + 32, i.e. lane l with lane l ^ 4, same j
+    const int pos = min(max(positions[token], 0), rope_rows - 1);
+    const float2* cs_row = rope_tab + static_cast<std::size_t>(pos) * kHalfRot + (lane & 3) * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float other = __shfl_xor_sync(0xFFFFFFFFU, x[j], 4);
+      if (lane < 8) {
+        const float2 cs = cs_row[j];
+        x[j] = lane < 4 ? __fsub_rn(__fmul_rn(x[j], cs.x), __fmul_rn(other, cs.y))
+                        : __fadd_rn(__fmul_rn(other, cs.y), __fmul_rn(x[j], cs.x));
+      }
+    }
+  }
+  __half2 hx[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) hx[i] = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
+  if (is_q) {
+    *reinterpret_cast<uint4*>(q_out + (static_cast<std::size_t>(token) * kQHeads + h) * kHeadDim + lane * 8) =
+        *reinterpret_cast<const uint4*>(hx);
+    return;
+  }
+  const std::int64_t slot = slots[token];
+  if (slot < 0) return;  // padding token
+  std::int64_t page = slot / kPageTokens;
+  const int tok = static_cast<int>(slot % kPageTokens);
+  page = min(max(page, static_cast<std::int64_t>(0)), static_cast<std::int64_t>(pool.num_pages - 1));
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(hx[i]);
+    x[2 * i] = f.x, x[2 * i + 1] = f.y;
+  }
+  QuantizeStoreRow<kFmt>(pool, layer, page, tok, is_v ? 1 : 0, h, lane, x);
+}
+
 }  // namespace
 
 cudaError_t LaunchAppend(const PoolView& pool, int layer, int n_tokens, const std::int64_t* slots_dev,
@@ -121,6 +210,23 @@ cudaError_t LaunchAppend(const PoolView& pool, int layer, int n_tokens, const st
     AppendKernel<kFmtQ8><<<n_tokens, kAppendThreads, 0, stream>>>(pool, layer, slots_dev, k, v);
   else
     AppendKernel<kFmtQ4><<<n_tokens, kAppendThreads, 0, stream>>>(pool, layer, slots_dev, k, v);
+  return cudaGetLastError();
+}
+
+cudaError_t LaunchRopeAppend(const PoolView& pool, int layer, int n_tokens, const std::int64_t* slots_dev,
+                             const std::int32_t* positions_dev, const float* q_dev, const float* k_dev,
+                             const float* v_dev, const float* q_weight_dev, const float* k_weight_dev, float eps,
+                             const float2* rope_tab_dev, int rope_rows, void* q_out_dev, cudaStream_t stream) {
+  if (n_tokens <= 0) return cudaSuccess;
+  auto* qo = static_cast<__half*>(q_out_dev);
+  if (pool.fmt == kFmtQ8)
+    RopeAppendKernel<kFmtQ8><<<n_tokens, kRopeThreads, 0, stream>>>(pool, layer, slots_dev, positions_dev, q_dev, k_dev,
+                                                                    v_dev, q_weight_dev, k_weight_dev, eps, rope_tab_dev,
+                                                                    rope_rows, qo);
+  else
+    RopeAppendKernel<kFmtQ4><<<n_tokens, kRopeThreads, 0, stream>>>(pool, layer, slots_dev, positions_dev, q_dev, k_dev,
+                                                                    v_dev, q_weight_dev, k_weight_dev, eps, rope_tab_dev,
+                                                                    rope_rows, qo);
   return cudaGetLastError();
 }
 

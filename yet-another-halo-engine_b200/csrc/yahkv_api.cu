@@ -114,6 +114,11 @@ struct yahkv_ctx {
     bool used = false;
   };
   HostStage hst[2];
+  // fused RoPE + append: cos / sin of every position the block tables can hold, and the call's positions
+  float2* rope_tab_dev = nullptr;
+  int rope_rows = 0;
+  std::int32_t* rope_pos_dev = nullptr;
+  std::vector<std::int32_t> rope_pos_scratch;
   int hst_next = 0;
   cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
   std::int64_t launches = 0;
@@ -244,7 +249,8 @@ void FreeDevice(yahkv_ctx* ctx) {
   if (ctx->stream != nullptr) cudaStreamSynchronize(ctx->stream);
   void* ptrs[] = {ctx->pool.kcodes, ctx->pool.vcodes, ctx->pool.kscales, ctx->pool.vscales, ctx->tables_dev,
                   ctx->slots_dev,   ctx->units_dev,   ctx->items_dev,    ctx->partial_acc,  ctx->partial_ml,
-                  ctx->tiles_dev,   ctx->status_dev,  ctx->counters_dev, ctx->pseqs_dev, ctx->k16_dev, ctx->v16_dev};
+                  ctx->tiles_dev,   ctx->status_dev,  ctx->counters_dev, ctx->pseqs_dev, ctx->k16_dev, ctx->v16_dev,
+                  ctx->rope_tab_dev, ctx->rope_pos_dev};
   for (void* p : ptrs)
     if (p != nullptr) cudaFree(p);
   for (cudaStream_t st : {ctx->h2d_stream, ctx->d2h_stream})
@@ -492,6 +498,56 @@ int yahkv_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int32_t*
     return r;
   TimedLaunch tl(ctx, YAHKV_KERNEL_APPEND, st);
   YAHKV_CUDA(ctx, LaunchAppend(ctx->pool, layer, n_tokens, ctx->slots_dev, k_dev, v_dev, st));
+  tl.End();
+  ctx->launches += 1;
+  return YAHKV_OK;
+}
+
+// cos / sin table of the fused RoPE: angle = pos / theta^(2 p / 64), p < 32, evaluated in double precision on the
+// host and rounded to f32 once (engine/gpu/loom/yah_fused_qk_rope_f32.loom:5, :32 for the formula and theta).
+static int EnsureRopeTable(yahkv_ctx* ctx) {
+  if (ctx->rope_tab_dev != nullptr) return YAHKV_OK;
+  const int rows = ctx->cfg.max_pages_per_seq * kPageTokens;
+  std::vector<float2> tab(static_cast<std::size_t>(rows) * 32);
+  double inv_freq[32];
+  for (int p = 0; p < 32; ++p) inv_freq[p] = std::pow(1.0e7, -2.0 * p / 64.0);
+  for (int pos = 0; pos < rows; ++pos)
+    for (int p = 0; p < 32; ++p) {
+      const double a = static_cast<double>(pos) * inv_freq[p];
+      tab[static_cast<std::size_t>(pos) * 32 + p] = make_float2(static_cast<float>(std::cos(a)), static_cast<float>(std::sin(a)));
+    }
+  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->rope_tab_dev, tab.size(), false));
+  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->rope_pos_dev, static_cast<std::size_t>(ctx->cfg.max_batch_tokens), false));
+  YAHKV_CUDA(ctx, cudaMemcpy(ctx->rope_tab_dev, tab.data(), tab.size() * sizeof(float2), cudaMemcpyHostToDevice));
+  ctx->rope_rows = rows;
+  return YAHKV_OK;
+}
+
+int yahkv_rope_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int32_t* seq_ids, const int64_t* positions,
+                      const float* q_dev, const float* k_dev, const float* v_dev, const float* q_weight_dev,
+                      const float* k_weight_dev, float eps, void* q_out_dev, void* stream) {
+  if (int r = RequireDevice(ctx, "rope_append"); r != YAHKV_OK) return r;
+  if (n_tokens > ctx->cfg.max_batch_tokens) return Fail(ctx, YAHKV_ERR_CAPACITY, "rope_append: more tokens than max_batch_tokens");
+  if (n_tokens > 0 && (q_dev == nullptr || k_dev == nullptr || v_dev == nullptr || q_weight_dev == nullptr ||
+                       k_weight_dev == nullptr || q_out_dev == nullptr))
+    return Fail(ctx, YAHKV_ERR_INVALID, "rope_append: null pointer");
+  if (!(eps >= 0.0F)) return Fail(ctx, YAHKV_ERR_INVALID, "rope_append: eps must be non-negative");
+  if (int r = EnsureRopeTable(ctx); r != YAHKV_OK) return r;   // before the plan: a failure here changes no state
+  HostError e = ctx->host.PlanAppend(layer, n_tokens, seq_ids, positions, ctx->slot_scratch.data());
+  if (e.code != YAHKV_OK) return FailHost(ctx, std::move(e));
+  if (n_tokens == 0) return YAHKV_OK;
+  ctx->rope_pos_scratch.resize(static_cast<std::size_t>(n_tokens));
+  for (int i = 0; i < n_tokens; ++i) ctx->rope_pos_scratch[static_cast<std::size_t>(i)] = static_cast<std::int32_t>(positions[i]);
+  cudaStream_t st = StreamOf(ctx, stream);
+  if (int r = FlushTables(ctx, st); r != YAHKV_OK) return r;
+  if (int r = StagedUpload(ctx, ctx->slots_dev, ctx->slot_scratch.data(), static_cast<std::size_t>(n_tokens) * 8, st); r != YAHKV_OK)
+    return r;
+  if (int r = StagedUpload(ctx, ctx->rope_pos_dev, ctx->rope_pos_scratch.data(), static_cast<std::size_t>(n_tokens) * 4, st);
+      r != YAHKV_OK)
+    return r;
+  TimedLaunch tl(ctx, YAHKV_KERNEL_APPEND, st);
+  YAHKV_CUDA(ctx, LaunchRopeAppend(ctx->pool, layer, n_tokens, ctx->slots_dev, ctx->rope_pos_dev, q_dev, k_dev, v_dev,
+                                   q_weight_dev, k_weight_dev, eps, ctx->rope_tab_dev, ctx->rope_rows, q_out_dev, st));
   tl.End();
   ctx->launches += 1;
   return YAHKV_OK;

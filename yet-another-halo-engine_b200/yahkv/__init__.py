@@ -118,6 +118,7 @@ SIGNATURES = {
     "yahkv_seq_set_len": (_I32, [_VP, _I32, _I32, _I64]),
     "yahkv_pages_free": (_I32, [_VP, _PI32]),
     "yahkv_append": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _VP]),
+    "yahkv_rope_append": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _VP, _VP, _VP, ctypes.c_float, _VP, _VP]),
     "yahkv_append_slots": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP]),
     "yahkv_attend_decode": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _I32, _I32, _VP]),
     "yahkv_attend_prefill": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _VP, _I32, _VP]),
@@ -302,6 +303,14 @@ class KvCache:
         assert len(seq_ids) == len(positions)
         self._check(lib.yahkv_append(self._h, layer, len(seq_ids), _ptr(seq_ids), _ptr(positions), _ptr(k), _ptr(v),
                                      _ptr(stream)))
+
+    def rope_append(self, layer, seq_ids, positions, q, k, v, q_weight, k_weight, eps, q_out, stream=None):
+        """Fused QK RMSNorm + RoPE + append: f32 device q [n][24][256], k, v [n][4][256]; q_out fp16 [n][24][256]."""
+        seq_ids = _i32(seq_ids)
+        positions = np.ascontiguousarray(positions, dtype=np.int64)
+        assert len(seq_ids) == len(positions)
+        self._check(lib.yahkv_rope_append(self._h, layer, len(seq_ids), _ptr(seq_ids), _ptr(positions), _ptr(q), _ptr(k),
+                                          _ptr(v), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(q_out), _ptr(stream)))
 
     def append_slots(self, layer, n_tokens, slot_mapping, k, v, stream=None):
         self._check(lib.yahkv_append_slots(self._h, layer, n_tokens, _ptr(slot_mapping), _ptr(k), _ptr(v),
