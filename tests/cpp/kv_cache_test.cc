@@ -51,6 +51,10 @@ int main() {
   char dummy[16] = {};
   EXPECT(CodeOf([&] { kv.Append(0, seqs, pos, dummy, dummy); }) == YAHKV_ERR_NO_DEVICE);
   EXPECT(CodeOf([&] { kv.AttendDecode(0, seqs, dummy, nullptr, dummy); }) == YAHKV_ERR_NO_DEVICE);
+  const float* fdummy = reinterpret_cast<const float*>(dummy);
+  EXPECT(CodeOf([&] { kv.RopeAppend(0, seqs, pos, fdummy, fdummy, fdummy, fdummy, fdummy, 1e-6F, dummy); }) == YAHKV_ERR_NO_DEVICE);
+  EXPECT(CodeOf([&] { kv.DecodeStepHostAsync(0, seqs, dummy, dummy, dummy, nullptr, dummy); }) == YAHKV_ERR_NO_DEVICE);
+  EXPECT(CodeOf([&] { kv.WaitHostSteps(); }) == YAHKV_ERR_NO_DEVICE);
   EXPECT(CodeOf([&] { kv.AttendPrefill(0, seqs, {1}, dummy, nullptr, dummy); }) == YAHKV_ERR_NO_DEVICE);
   EXPECT(kv.Length(b, 0) == 0);
   // a bad geometry is refused at creation

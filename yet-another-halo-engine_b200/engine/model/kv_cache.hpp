@@ -104,6 +104,15 @@ class KvCache {
     Check(yahkv_append(ctx_, layer, static_cast<std::int32_t>(seqs.size()), seqs.data(), positions.data(), k_dev, v_dev,
                        stream));
   }
+  // The reference's "rope" dispatch and the appends behind it (loom_decoder.hpp:250-261) as one call: f32 q / k / v as
+  // the projections leave them, fp16 q for the attention out.
+  void RopeAppend(std::int32_t layer, const std::vector<std::int32_t>& seqs, const std::vector<std::int64_t>& positions,
+                  const float* q_dev, const float* k_dev, const float* v_dev, const float* q_weight_dev,
+                  const float* k_weight_dev, float eps, void* q_out_dev, void* stream = nullptr) {
+    if (seqs.size() != positions.size()) throw KvError(YAHKV_ERR_INVALID, "kv cache: one position per token expected");
+    Check(yahkv_rope_append(ctx_, layer, static_cast<std::int32_t>(seqs.size()), seqs.data(), positions.data(), q_dev,
+                            k_dev, v_dev, q_weight_dev, k_weight_dev, eps, q_out_dev, stream));
+  }
   void AttendDecode(std::int32_t layer, const std::vector<std::int32_t>& seqs, const void* q_dev, const float* gate_dev,
                     void* out_dev, std::int32_t out_dtype = YAHKV_OUT_F16, std::int32_t n_splits = 0,
                     void* stream = nullptr) {
@@ -117,6 +126,14 @@ class KvCache {
     Check(yahkv_attend_prefill(ctx_, layer, static_cast<std::int32_t>(seqs.size()), seqs.data(), chunks.data(), q_dev,
                                gate_dev, out_dev, out_dtype, stream));
   }
+  // One layer of a decode step with page-locked HOST buffers, queued without waiting; WaitHostSteps() collects them.
+  void DecodeStepHostAsync(std::int32_t layer, const std::vector<std::int32_t>& seqs, const void* k_host,
+                           const void* v_host, const void* q_host, const float* gate_host, void* out_host,
+                           std::int32_t out_dtype = YAHKV_OUT_F16) {
+    Check(yahkv_decode_step_host_async(ctx_, layer, static_cast<std::int32_t>(seqs.size()), seqs.data(), k_host, v_host,
+                                       q_host, gate_host, out_host, out_dtype));
+  }
+  void WaitHostSteps() { Check(yahkv_decode_step_host_wait(ctx_)); }
   void Synchronize() { Check(yahkv_sync(ctx_)); }
 
  private:
