@@ -1,7 +1,8 @@
 #!/usr/bin/env python3
 """Generates tests/golden/*.npz: known answers for the KV path made with the REFERENCE's own code, not with ours.
 
-Run it in a container that has the reference checkout (default /root/reference) and the `gguf` package:
+Run it where the reference checkout is present (the REF variable of oracle/Makefile points at it) and the `gguf`
+package is installed:
     python tests/golden/make_golden.py
 What produces each answer:
   * q8_0 blocks: the reference's QuantizeQ8_0 (engine/core/gguf_quant.cpp:310-320), compiled unchanged from its
