@@ -14,6 +14,10 @@
  * Pool layout (per layer, per side K|V; all layers of a side live in one allocation):
  *   codes  [num_pages][4 kv heads][64 tokens][256 B (q8_0) | 128 B (q4_0)]
  *   scales [num_pages][4 kv heads][64 tokens][8] fp16
+ * In device memory a q8_0 code byte is held with its sign bit flipped (u = code + 128), which saves the attention
+ * kernels an instruction per four codes; yahkv_read_page / yahkv_write_page / yahkv_export_token and the snapshot
+ * files translate, so everything outside the device sees GGUF's int8 codes. Only yahkv_attend_decode_noalloc, which
+ * is handed device pools directly, sees the device form. q4_0 bytes are GGUF's as they are.
  * slot(pos) = table[pos / 64] * 64 + pos % 64 (the reference's rule with 256 -> 64,
  * engine/gpu/loom/tools/gen_decode_attn.py:5, :64-72). One block table per sequence is shared by all layers
  * (docs/architecture.md:212).
@@ -219,7 +223,7 @@ int yahkv_kernel_timing_read(yahkv_ctx* ctx, int32_t kernel, double* total_ms, i
  * static device array inside the library (YAHKV_NOALLOC_SCRATCH_BYTES, held by every GPU that loads the library
  * until the process exits). It calls no cudaMalloc / cudaFree / pinned allocation / stream or event creation.
  *
- * Pools use the layout at the top of this file. Row b of tables_dev belongs to sequence b of the call; lens_dev[b]
+ * Pools use the layout at the top of this file, q8_0 codes in their device form. Row b of tables_dev belongs to sequence b of the call; lens_dev[b]
  * is its number of visible keys (clamped to [1, table_stride * 64] on the device). n_splits is the fixed number of
  * split-K units per (sequence, kv head). Refused with YAHKV_ERR_CAPACITY beyond YAHKV_NOALLOC_MAX_SEQS sequences or
  * YAHKV_NOALLOC_MAX_UNITS = n_seqs * 4 * n_splits units. Results equal yahkv_attend_decode's with the same n_splits.

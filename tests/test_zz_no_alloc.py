@@ -24,7 +24,8 @@ def _pools_as_tensors(cache, num_pages):
     sides = []
     for side in (yahkv.SIDE_K, yahkv.SIDE_V):
         pages = [cache.read_page(0, side, p) for p in range(num_pages)]
-        sides.append(torch.from_numpy(np.stack([c for c, _ in pages])).cuda())
+        # read_page hands out GGUF codes; the call under test takes device pools, whose q8_0 bytes are sign-flipped
+        sides.append(torch.from_numpy(yahkv.device_codes(cache.fmt, np.stack([c for c, _ in pages]))).cuda())
         sides.append(torch.from_numpy(np.stack([s for _, s in pages]).view(np.int16)).cuda())
     return sides   # kcodes, kscales, vcodes, vscales
 

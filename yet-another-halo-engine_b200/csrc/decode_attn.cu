@@ -257,13 +257,13 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
           LdMatrixX4(k_base + lm_off[b], w);
           float a0[4], a1[4];
           std::uint32_t x0, x1;
-          Int8x4ToHalf2(w[0], x0, x1);
+          Offset8x4ToHalf2(w[0], x0, x1);
           MmaQZero(a0, qa_addr + (2 * b) * (kQLanes * 16), x0, x1);
-          Int8x4ToHalf2(w[1], x0, x1);
+          Offset8x4ToHalf2(w[1], x0, x1);
           MmaQZero(a1, qa_addr + (2 * b) * (kQLanes * 16), x0, x1);
-          Int8x4ToHalf2(w[2], x0, x1);
+          Offset8x4ToHalf2(w[2], x0, x1);
           MmaQ(a0, qa_addr + (2 * b + 1) * (kQLanes * 16), x0, x1);
-          Int8x4ToHalf2(w[3], x0, x1);
+          Offset8x4ToHalf2(w[3], x0, x1);
           MmaQ(a1, qa_addr + (2 * b + 1) * (kQLanes * 16), x0, x1);
           sc[0][0] = fmaf(ScaleOf(ks_raw[0][0], b), a0[0], sc[0][0]);
           sc[0][1] = fmaf(ScaleOf(ks_raw[0][1], b), a0[1], sc[0][1]);
@@ -379,12 +379,12 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
         std::uint32_t w[4];
         LdMatrixX4Trans(v_base + lm_off[b], w);
         std::uint32_t a0, a1, a2, a3;
-        Int8x4ToHalf2(w[0], a0, a1);
-        Int8x4ToHalf2(w[1], a2, a3);
+        Offset8x4ToHalf2(w[0], a0, a1);
+        Offset8x4ToHalf2(w[1], a2, a3);
         MmaF16(o_acc[2 * b], a0, a1, a2, a3, hi[0], hi[1]);
         MmaF16(o_acc[2 * b], a0, a1, a2, a3, lo[0], lo[1]);
-        Int8x4ToHalf2(w[2], a0, a1);
-        Int8x4ToHalf2(w[3], a2, a3);
+        Offset8x4ToHalf2(w[2], a0, a1);
+        Offset8x4ToHalf2(w[3], a2, a3);
         MmaF16(o_acc[2 * b + 1], a0, a1, a2, a3, hi[0], hi[1]);
         MmaF16(o_acc[2 * b + 1], a0, a1, a2, a3, lo[0], lo[1]);
       }

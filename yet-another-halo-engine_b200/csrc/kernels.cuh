@@ -26,6 +26,14 @@ constexpr int kRecordScaleBytes = kPageTokens * kBlocksPerRow * 2;
 
 // The pools of one context. Codes are addressed both by pointer (append, inspection) and through 2-D tensor maps
 // whose rows are token rows of CodeBytes(fmt) bytes (attention's gathers).
+// Device representation of q8_0 codes: every code byte is stored with its sign bit flipped, u = code + 128
+// (offset binary), so that the attention kernels turn a byte into the fp16 integer with one byte-permute and one
+// subtract instead of three instructions. Everything that leaves the device (yahkv_read_page, yahkv_export_token,
+// snapshots) or enters it (yahkv_write_page, snapshot load) flips the bit back, so hosts and files see GGUF's int8
+// codes. q4_0 nibbles are unsigned already and are stored as GGUF has them.
+constexpr std::uint32_t kQ8FlipWord = 0x80808080U;
+constexpr int kQ8FlipByte = 0x80;
+
 struct PoolView {
   std::uint8_t* kcodes;
   std::uint8_t* vcodes;

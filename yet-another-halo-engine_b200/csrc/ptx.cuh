@@ -115,10 +115,9 @@ __device__ __forceinline__ float Exp2Fast(float x) {
   return y;
 }
 
-// Four int8 codes in a word -> two half2 of exact integers: bytes (0, 2) and bytes (1, 3).
-// 0x6400 | u is the fp16 value 1024 + u; with u = code + 128 (the sign bit flipped) the code is that minus 1152.
-__device__ __forceinline__ void Int8x4ToHalf2(std::uint32_t w, std::uint32_t& h02, std::uint32_t& h13) {
-  const std::uint32_t u = w ^ 0x80808080U;
+// Four q8_0 codes as the pools hold them (u = code + 128 per byte) -> two half2 of exact integers: bytes (0, 2) and
+// bytes (1, 3). 0x6400 | u is the fp16 value 1024 + u, so the code is that minus 1152.
+__device__ __forceinline__ void Offset8x4ToHalf2(std::uint32_t u, std::uint32_t& h02, std::uint32_t& h13) {
   const std::uint32_t lo = __byte_perm(u, 0x64646464U, 0x4240);
   const std::uint32_t hi = __byte_perm(u, 0x64646464U, 0x4341);
   const __half2 bias = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));

@@ -199,6 +199,10 @@ int InitDevice(yahkv_ctx* ctx) {
   ctx->pool.fmt = c.fmt, ctx->pool.num_pages = c.num_pages, ctx->pool.n_layers = c.n_layers;
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.kcodes, recs * RecordCodeBytes(c.fmt), true));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.vcodes, recs * RecordCodeBytes(c.fmt), true));
+  if (c.fmt == YAHKV_FMT_Q8_0) {   // code 0 in the device representation (sign bit flipped)
+    YAHKV_CUDA(ctx, cudaMemset(ctx->pool.kcodes, kQ8FlipByte, recs * RecordCodeBytes(c.fmt)));
+    YAHKV_CUDA(ctx, cudaMemset(ctx->pool.vcodes, kQ8FlipByte, recs * RecordCodeBytes(c.fmt)));
+  }
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.kscales, recs * kPageTokens * kBlocksPerRow, true));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.vscales, recs * kPageTokens * kBlocksPerRow, true));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->tables_dev, static_cast<std::size_t>(c.max_seqs) * c.max_pages_per_seq, true));
@@ -756,6 +760,12 @@ int yahkv_sync(yahkv_ctx* ctx) {
   return CheckStatus(ctx);
 }
 
+// GGUF int8 codes <-> the pools' device representation (kernels.cuh): the same flip both ways; q4_0 is untouched.
+static void FlipQ8(int fmt, std::uint8_t* codes, std::size_t n) {
+  if (fmt != YAHKV_FMT_Q8_0) return;
+  for (std::size_t i = 0; i < n; ++i) codes[i] ^= static_cast<std::uint8_t>(kQ8FlipByte);
+}
+
 static int PageAccess(yahkv_ctx* ctx, int32_t layer, int32_t side, int32_t page, void* codes_host, void* scales_host,
                       bool write) {
   if (int r = RequireDevice(ctx, write ? "write_page" : "read_page"); r != YAHKV_OK) return r;
@@ -768,9 +778,16 @@ static int PageAccess(yahkv_ctx* ctx, int32_t layer, int32_t side, int32_t page,
   std::uint16_t* scales = (side == YAHKV_SIDE_K ? ctx->pool.kscales : ctx->pool.vscales) + rec * kPageTokens * kBlocksPerRow;
   const std::size_t cb = static_cast<std::size_t>(kKvHeads) * RecordCodeBytes(ctx->cfg.fmt);
   const std::size_t sb = static_cast<std::size_t>(kKvHeads) * kRecordScaleBytes;
-  if (codes_host != nullptr)
-    YAHKV_CUDA(ctx, write ? cudaMemcpy(codes, codes_host, cb, cudaMemcpyHostToDevice)
-                          : cudaMemcpy(codes_host, codes, cb, cudaMemcpyDeviceToHost));
+  if (codes_host != nullptr) {   // q8_0 codes cross the boundary as GGUF int8, the pools hold them sign-flipped
+    if (write) {
+      std::vector<std::uint8_t> tmp(static_cast<const std::uint8_t*>(codes_host), static_cast<const std::uint8_t*>(codes_host) + cb);
+      FlipQ8(ctx->cfg.fmt, tmp.data(), cb);
+      YAHKV_CUDA(ctx, cudaMemcpy(codes, tmp.data(), cb, cudaMemcpyHostToDevice));
+    } else {
+      YAHKV_CUDA(ctx, cudaMemcpy(codes_host, codes, cb, cudaMemcpyDeviceToHost));
+      FlipQ8(ctx->cfg.fmt, static_cast<std::uint8_t*>(codes_host), cb);
+    }
+  }
   if (scales_host != nullptr)
     YAHKV_CUDA(ctx, write ? cudaMemcpy(scales, scales_host, sb, cudaMemcpyHostToDevice)
                           : cudaMemcpy(scales_host, scales, sb, cudaMemcpyDeviceToHost));
@@ -808,6 +825,7 @@ int yahkv_export_token(yahkv_ctx* ctx, int32_t layer, int32_t seq, int64_t pos, 
       const std::uint16_t* ss = (side == 0 ? ctx->pool.kscales : ctx->pool.vscales) + rec * kPageTokens * kBlocksPerRow +
                                 static_cast<std::size_t>(tok) * kBlocksPerRow;
       YAHKV_CUDA(ctx, cudaMemcpy(codes, cs, static_cast<std::size_t>(cbytes), cudaMemcpyDeviceToHost));
+      FlipQ8(ctx->cfg.fmt, codes, static_cast<std::size_t>(cbytes));
       YAHKV_CUDA(ctx, cudaMemcpy(scales, ss, sizeof(scales), cudaMemcpyDeviceToHost));
       for (int b = 0; b < kBlocksPerRow; ++b) {
         std::memcpy(dst, &scales[b], 2);
@@ -1079,6 +1097,8 @@ int yahkv_snapshot_save(yahkv_ctx* ctx, int32_t n_seqs, const int32_t* seq_ids, 
         YAHKV_CUDA(ctx, cudaMemcpy(buf.data() + cb, ctx->pool.kscales + rec * kPageTokens * kBlocksPerRow, sb, cudaMemcpyDeviceToHost));
         YAHKV_CUDA(ctx, cudaMemcpy(buf.data() + cb + sb, ctx->pool.vcodes + rec * RecordCodeBytes(c.fmt), cb, cudaMemcpyDeviceToHost));
         YAHKV_CUDA(ctx, cudaMemcpy(buf.data() + 2 * cb + sb, ctx->pool.vscales + rec * kPageTokens * kBlocksPerRow, sb, cudaMemcpyDeviceToHost));
+        FlipQ8(c.fmt, buf.data(), cb);                 // the file holds GGUF int8 codes
+        FlipQ8(c.fmt, buf.data() + cb + sb, cb);
         ok = std::fwrite(buf.data(), buf.size(), 1, f.get()) == 1;
       }
   }
@@ -1128,6 +1148,8 @@ int yahkv_snapshot_load(yahkv_ctx* ctx, const char* path, int32_t* seq_ids_out, 
     for (int l = 0; l < c.n_layers; ++l)
       for (int p = 0; p < np; ++p) {
         if (std::fread(buf.data(), buf.size(), 1, f.get()) != 1) return undo(YAHKV_ERR_INVALID, "snapshot_load: truncated file");
+        FlipQ8(c.fmt, buf.data(), cb);
+        FlipQ8(c.fmt, buf.data() + cb + sb, cb);
         const std::size_t rec = (static_cast<std::size_t>(l) * c.num_pages + ctx->host.table_row(s)[p]) * kKvHeads;
         cudaError_t ce = cudaMemcpy(ctx->pool.kcodes + rec * RecordCodeBytes(c.fmt), buf.data(), cb, cudaMemcpyHostToDevice);
         if (ce == cudaSuccess) ce = cudaMemcpy(ctx->pool.kscales + rec * kPageTokens * kBlocksPerRow, buf.data() + cb, sb, cudaMemcpyHostToDevice);

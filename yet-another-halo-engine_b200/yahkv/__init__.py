@@ -180,6 +180,14 @@ def _i32(a):
     return np.ascontiguousarray(a, dtype=np.int32)
 
 
+def device_codes(fmt, codes):
+    """GGUF code bytes (as read_page returns them) -> the form the device pools hold: q8_0 bytes with the sign bit
+    flipped (u = code + 128), q4_0 unchanged. The same call converts back. For callers that build device pools
+    themselves (attend_decode_noalloc)."""
+    codes = np.ascontiguousarray(codes, np.uint8)
+    return codes ^ np.uint8(0x80) if fmt == FMT_Q8_0 else codes
+
+
 def attend_decode_noalloc(*, fmt, n_layers, num_pages, layer, kcodes, vcodes, kscales, vscales, tables, table_stride,
                           n_seqs, lens, q, out, gate=None, out_dtype=OUT_F16, n_splits=1, softmax_scale=0.0,
                           stream=None):
