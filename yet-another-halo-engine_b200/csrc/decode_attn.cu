@@ -91,6 +91,16 @@ __device__ __forceinline__ void MmaQZero(float (&d)[4], std::uint32_t q_addr, st
       : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0F));
 }
+// The same step starting from a constant: rows 0-7 (the heads) start at c, the padding rows at zero.
+__device__ __forceinline__ void MmaQConst(float (&d)[4], std::uint32_t q_addr, std::uint32_t b0, std::uint32_t b1, float c) {
+  std::uint32_t a0, a1, a2, a3;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(q_addr));
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%10, %10, %11, %11};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c), "f"(0.0F));
+}
 // The same step accumulating in place.
 __device__ __forceinline__ void MmaQ(float (&d)[4], std::uint32_t q_addr, std::uint32_t b0, std::uint32_t b1) {
   std::uint32_t a0, a1, a2, a3;
@@ -113,7 +123,8 @@ struct SmemLayout {
   static constexpr int kXchgOff = kQfragOff + kQfragBytes;
   static constexpr int kBarOff = kXchgOff + kXchgBytes;
   static constexpr int kCntOff = kBarOff + 8 * StageLayout<kFmt>::kStages;
-  static constexpr int kBytes = kCntOff + 4 * StageLayout<kFmt>::kStages;
+  static constexpr int kCorrOff = (kCntOff + 4 * StageLayout<kFmt>::kStages + 15) / 16 * 16;
+  static constexpr int kBytes = kCorrOff + 2 * 8 * 16;   // [dim half][head lane g] x 4 blocks of f32
 };
 template <int kFmt>
 constexpr int DecodeSmemBytes() {
@@ -141,6 +152,7 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
   float4* xchg = reinterpret_cast<float4*>(smem_raw + S::kXchgOff);     // partial scores [8 warps][24 lanes]
   std::uint64_t* full_bar = reinterpret_cast<std::uint64_t*>(smem_raw + S::kBarOff);
   int* done_cnt = reinterpret_cast<int*>(smem_raw + S::kCntOff);        // warps done reading a stage's page
+  float* qcorr = reinterpret_cast<float*>(smem_raw + S::kCorrOff);      // [dim half][head lane][block]: -1152 sum(q)
   if ((SmemAddr(smem_raw) & 1023U) != 0) {   // never seen; checked because a misaligned swizzle would corrupt results
     if (threadIdx.x == 0) atomicExch(status, kStatusSmemMisaligned);
     return;
@@ -193,6 +205,8 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
   // + {1, 3} in (2t+8, 2t+9).
   {
     const __half* qrow = q + (static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + g) * kHeadDim;
+    static_assert(16 / kWarps == 2, "a warp loads the two MMA steps of one 32-dim block");
+    float qsum = 0.0F;   // this thread's 8 of the 32 values of block `warp` of head g
 #pragma unroll
     for (int cc = 0; cc < 16 / kWarps; ++cc) {
       const int c = warp * (16 / kWarps) + cc;
@@ -200,8 +214,16 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
         const uint2 v = *reinterpret_cast<const uint2*>(qrow + 16 * c + 4 * t);
         qfrag[c * kQLanes + lane] = make_uint4(__byte_perm(v.x, v.y, 0x5410), 0U,   // halves (0, 2)
                                                __byte_perm(v.x, v.y, 0x7632), 0U);  // halves (1, 3)
+        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+        const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+        qsum += (f0.x + f0.y) + (f1.x + f1.y);
       }
     }
+    // q8_0 scores are taken on the biased codes (fp16 1152 + code, straight from the byte permute): the bias times
+    // the block's sum of q is what the MMA accumulator starts from, so the subtract per code pair is never executed.
+    qsum += __shfl_xor_sync(0xFFFFFFFFU, qsum, 1);
+    qsum += __shfl_xor_sync(0xFFFFFFFFU, qsum, 2);
+    if (t == 0) qcorr[((warp >> 2) * 8 + g) * 4 + (warp & 3)] = g < kGroup ? -1152.0F * qsum : 0.0F;
   }
   __syncthreads();   // barriers initialised, Q fragments visible
   // This warp's eight MMA steps are c = 8 dh .. 8 dh + 7.
@@ -251,19 +273,21 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
         for (int j = 0; j < 2; ++j)
           ks_raw[kt][j] = *reinterpret_cast<const uint2*>(st + L::kKsOff + (my_key0 + kt * 8 + j) * 16 + dh * 8);
       if constexpr (kFmt == kFmtQ8) {
+        const float4 corr = *reinterpret_cast<const float4*>(qcorr + (dh * 8 + g) * 4);
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
           std::uint32_t w[4];
           LdMatrixX4(k_base + lm_off[b], w);
           float a0[4], a1[4];
           std::uint32_t x0, x1;
-          Offset8x4ToHalf2(w[0], x0, x1);
-          MmaQZero(a0, qa_addr + (2 * b) * (kQLanes * 16), x0, x1);
-          Offset8x4ToHalf2(w[1], x0, x1);
-          MmaQZero(a1, qa_addr + (2 * b) * (kQLanes * 16), x0, x1);
-          Offset8x4ToHalf2(w[2], x0, x1);
+          const float cb = b == 0 ? corr.x : b == 1 ? corr.y : b == 2 ? corr.z : corr.w;
+          Offset8x4ToBiasedHalf2(w[0], x0, x1);
+          MmaQConst(a0, qa_addr + (2 * b) * (kQLanes * 16), x0, x1, cb);
+          Offset8x4ToBiasedHalf2(w[1], x0, x1);
+          MmaQConst(a1, qa_addr + (2 * b) * (kQLanes * 16), x0, x1, cb);
+          Offset8x4ToBiasedHalf2(w[2], x0, x1);
           MmaQ(a0, qa_addr + (2 * b + 1) * (kQLanes * 16), x0, x1);
-          Offset8x4ToHalf2(w[3], x0, x1);
+          Offset8x4ToBiasedHalf2(w[3], x0, x1);
           MmaQ(a1, qa_addr + (2 * b + 1) * (kQLanes * 16), x0, x1);
           sc[0][0] = fmaf(ScaleOf(ks_raw[0][0], b), a0[0], sc[0][0]);
           sc[0][1] = fmaf(ScaleOf(ks_raw[0][1], b), a0[1], sc[0][1]);
