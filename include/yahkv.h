@@ -64,6 +64,13 @@ typedef struct yahkv_config {
   int32_t max_splits;        /* split-K units per (sequence, kv head); 0 = 64 */
   int32_t max_batch_tokens;  /* tokens per append call and query rows per prefill call; 0 = 8192 */
   float softmax_scale;       /* 0 = 1/16 */
+  /* Head-sharded layout (benchmark only): the context serves KV heads [kv_head_begin, kv_head_begin + kv_head_count)
+   * and their query heads (6 per KV head); count 0 = all four. Appends skip the other heads' K/V, decode and prefill
+   * attention write only the owned query heads' rows of `out` and leave the rest untouched, so ranks holding
+   * disjoint head ranges of the same sequences produce disjoint slices of one output. Decode batches
+   * (yahkv_batch_*) need all four heads. */
+  int32_t kv_head_begin;
+  int32_t kv_head_count;
 } yahkv_config;
 
 /* Replaces LoomDecoder::OwnState / LoomPrefill's pool allocation (engine/model/loom_decoder.hpp:159-183,

@@ -234,3 +234,40 @@ def test_full_length_properties(fmt, ctx_len, batch):
     # The tensor-core MMA truncates its fp32 accumulate, so one unit summing all 512+ pages drifts by up to
     # ~1e-4 relative against 64 short units; still far inside the tolerance.
     assert np.abs(outs[1] - outs[64]).max() <= 5e-4 and np.abs(outs[0] - outs[64]).max() <= 5e-4
+
+
+def test_head_sharded_contexts_produce_disjoint_slices_of_the_same_output():
+    """Contexts that hold KV heads {0,1} and {2,3} of the same sequences (the head-sharded layout) write exactly the
+    rows of their own query heads, bit-identical to a context that holds all four, and leave the other rows alone;
+    the same for chunked prefill."""
+    rng = np.random.default_rng(91)
+    n, chunk = 333, 70
+    K = rng.standard_normal((n, 4, 256)).astype(np.float16)
+    V = rng.standard_normal((n, 4, 256)).astype(np.float16)
+    q = rng.standard_normal((1, 24, 256)).astype(np.float16)
+    qc = rng.standard_normal((chunk, 24, 256)).astype(np.float16)
+    table = rng.permutation(8)[:6].astype(np.int32)
+    outs = []
+    for begin, count in ((0, 0), (0, 2), (2, 2)):
+        c = yahkv.KvCache(n_layers=1, num_pages=8, fmt=yahkv.FMT_Q8_0, max_seqs=1, max_pages_per_seq=6,
+                          kv_head_begin=begin, kv_head_count=count)
+        s = c.seq_create()
+        c.seq_set_table(s, table)
+        c.append(0, np.full(n, s, np.int32), np.arange(n), dev(K), dev(V))
+        dec = torch.full((1, 24, 256), float("nan"), device="cuda")
+        pre = torch.full((chunk, 24, 256), float("nan"), device="cuda")
+        torch.cuda.synchronize()
+        c.attend_decode(0, [s], dev(q), dec, out_dtype=yahkv.OUT_F32, n_splits=3)
+        c.attend_prefill(0, [s], [chunk], dev(qc), pre, out_dtype=yahkv.OUT_F32)
+        c.sync()
+        outs.append((dec.cpu().numpy(), pre.cpu().numpy()))
+        if count:
+            with pytest.raises(yahkv.YahkvError):
+                yahkv.DecodeBatch(c, [s])
+        c.close()
+    (dec_all, pre_all), lo, hi = outs
+    assert not np.isnan(dec_all).any() and not np.isnan(pre_all).any()
+    for (dec, pre), heads in ((lo, slice(0, 12)), (hi, slice(12, 24))):
+        other = slice(12, 24) if heads.start == 0 else slice(0, 12)
+        assert np.array_equal(dec[:, heads], dec_all[:, heads]) and np.isnan(dec[:, other]).all()
+        assert np.array_equal(pre[:, heads], pre_all[:, heads]) and np.isnan(pre[:, other]).all()

@@ -141,3 +141,11 @@ def test_create_without_a_gpu_fails_loudly():
     with pytest.raises(yahkv.YahkvError) as e:
         yahkv.KvCache(device=0)
     assert e.value.code in (yahkv.ERR_NO_DEVICE, yahkv.ERR_CUDA)
+
+
+def test_kv_head_range_is_validated():
+    ok = dict(device=-1, n_layers=1, num_pages=4, max_seqs=1, max_pages_per_seq=4)
+    yahkv.KvCache(**ok, kv_head_begin=2, kv_head_count=2).close()
+    for begin, count in ((3, 2), (-1, 1), (1, 0), (0, 5)):
+        with pytest.raises(yahkv.YahkvError):
+            yahkv.KvCache(**ok, kv_head_begin=begin, kv_head_count=count)

@@ -206,24 +206,35 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
   {
     const __half* qrow = q + (static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + g) * kHeadDim;
     static_assert(16 / kWarps == 2, "a warp loads the two MMA steps of one 32-dim block");
-    float qsum = 0.0F;   // this thread's 8 of the 32 values of block `warp` of head g
+    // Scores are taken on biased codes, straight from the bit tricks, and the bias times the block's sum of q is what
+    // the MMA accumulator starts from, so the subtract per code pair is never executed:
+    //   q8_0: the operand is the fp16 1152 + code; the accumulator starts at -1152 sum(q).
+    //   q4_0: elements 0-15 of a block (low nibbles) come as 1024 + n, elements 16-31 (high nibbles, left in place)
+    //         as 1024 + 16 n against q / 16 (exact in fp16), so the products sum to q n + 1024 sum_lo(q) +
+    //         64 sum_hi(q); with the -8 of the format the accumulator starts at -1032 sum_lo(q) - 72 sum_hi(q).
+    float qsum[2] = {0.0F, 0.0F};   // this thread's 4 + 4 of the 16 + 16 values of block `warp` of head g
 #pragma unroll
     for (int cc = 0; cc < 16 / kWarps; ++cc) {
       const int c = warp * (16 / kWarps) + cc;
       if (g < kGroup) {
-        const uint2 v = *reinterpret_cast<const uint2*>(qrow + 16 * c + 4 * t);
-        qfrag[c * kQLanes + lane] = make_uint4(__byte_perm(v.x, v.y, 0x5410), 0U,   // halves (0, 2)
-                                               __byte_perm(v.x, v.y, 0x7632), 0U);  // halves (1, 3)
+        uint2 v = *reinterpret_cast<const uint2*>(qrow + 16 * c + 4 * t);
         const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
         const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
-        qsum += (f0.x + f0.y) + (f1.x + f1.y);
+        qsum[cc] = (f0.x + f0.y) + (f1.x + f1.y);
+        if (kFmt == kFmtQ4 && cc == 1) {   // the MMA step of a block's high nibbles
+          const __half2 sixteenth = __halves2half2(__ushort_as_half(0x2C00), __ushort_as_half(0x2C00));
+          const __half2 a = __hmul2(*reinterpret_cast<const __half2*>(&v.x), sixteenth);
+          const __half2 b = __hmul2(*reinterpret_cast<const __half2*>(&v.y), sixteenth);
+          v.x = *reinterpret_cast<const std::uint32_t*>(&a), v.y = *reinterpret_cast<const std::uint32_t*>(&b);
+        }
+        qfrag[c * kQLanes + lane] = make_uint4(__byte_perm(v.x, v.y, 0x5410), 0U,   // halves (0, 2)
+                                               __byte_perm(v.x, v.y, 0x7632), 0U);  // halves (1, 3)
       }
     }
-    // q8_0 scores are taken on the biased codes (fp16 1152 + code, straight from the byte permute): the bias times
-    // the block's sum of q is what the MMA accumulator starts from, so the subtract per code pair is never executed.
-    qsum += __shfl_xor_sync(0xFFFFFFFFU, qsum, 1);
-    qsum += __shfl_xor_sync(0xFFFFFFFFU, qsum, 2);
-    if (t == 0) qcorr[((warp >> 2) * 8 + g) * 4 + (warp & 3)] = g < kGroup ? -1152.0F * qsum : 0.0F;
+    float corr = kFmt == kFmtQ8 ? -1152.0F * (qsum[0] + qsum[1]) : -1032.0F * qsum[0] - 72.0F * qsum[1];
+    corr += __shfl_xor_sync(0xFFFFFFFFU, corr, 1);
+    corr += __shfl_xor_sync(0xFFFFFFFFU, corr, 2);
+    if (t == 0) qcorr[((warp >> 2) * 8 + g) * 4 + (warp & 3)] = g < kGroup ? corr : 0.0F;
   }
   __syncthreads();   // barriers initialised, Q fragments visible
   // This warp's eight MMA steps are c = 8 dh .. 8 dh + 7.
@@ -272,8 +283,8 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
 #pragma unroll
         for (int j = 0; j < 2; ++j)
           ks_raw[kt][j] = *reinterpret_cast<const uint2*>(st + L::kKsOff + (my_key0 + kt * 8 + j) * 16 + dh * 8);
+      const float4 corr = *reinterpret_cast<const float4*>(qcorr + (dh * 8 + g) * 4);
       if constexpr (kFmt == kFmtQ8) {
-        const float4 corr = *reinterpret_cast<const float4*>(qcorr + (dh * 8 + g) * 4);
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
           std::uint32_t w[4];
@@ -305,11 +316,12 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
             const int b = 2 * bp + hb;   // block 4 dh + b
             float a0[4], a1[4];
             std::uint32_t l0, l1, h0, h1;
-            Nib4x4ToHalf2(w[2 * hb], l0, l1, h0, h1);
-            MmaQZero(a0, qa_addr + (2 * b) * (kQLanes * 16), l0, l1);
+            const float cb = b == 0 ? corr.x : b == 1 ? corr.y : b == 2 ? corr.z : corr.w;
+            Nib4x4ToBiasedHalf2(w[2 * hb], l0, l1, h0, h1);
+            MmaQConst(a0, qa_addr + (2 * b) * (kQLanes * 16), l0, l1, cb);
             MmaQ(a0, qa_addr + (2 * b + 1) * (kQLanes * 16), h0, h1);
-            Nib4x4ToHalf2(w[2 * hb + 1], l0, l1, h0, h1);
-            MmaQZero(a1, qa_addr + (2 * b) * (kQLanes * 16), l0, l1);
+            Nib4x4ToBiasedHalf2(w[2 * hb + 1], l0, l1, h0, h1);
+            MmaQConst(a1, qa_addr + (2 * b) * (kQLanes * 16), l0, l1, cb);
             MmaQ(a1, qa_addr + (2 * b + 1) * (kQLanes * 16), h0, h1);
             sc[0][0] = fmaf(ScaleOf(ks_raw[0][0], b), a0[0], sc[0][0]);
             sc[0][1] = fmaf(ScaleOf(ks_raw[0][1], b), a0[1], sc[0][1]);
@@ -581,6 +593,7 @@ __global__ void __launch_bounds__(kHeadDim)
   const int kvh = hh / kGroup, j = hh % kGroup;
   const CombineItem it = items[b * kKvHeads + kvh];
   const int n = min(it.n_partials, kCombineMaxUnits);   // the planner never exceeds it
+  if (n <= 0) return;   // a kv head outside the context's range: its query heads' rows belong to another context
   const float* ml_g = partial_ml + static_cast<std::size_t>(it.first_partial) * kPartialMlFloats + 2 * j;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   // overall max

@@ -185,6 +185,7 @@ extern "C" int yahkv_attend_decode_noalloc(const yahkv_noalloc_args* a, char* er
   l.pool.kscales = static_cast<std::uint16_t*>(const_cast<void*>(a->kscales));
   l.pool.vscales = static_cast<std::uint16_t*>(const_cast<void*>(a->vscales));
   l.pool.fmt = a->fmt, l.pool.num_pages = a->num_pages, l.pool.n_layers = a->n_layers;
+  l.pool.kv_head_begin = 0, l.pool.kv_head_count = kKvHeads;
   l.layer = a->layer;
   l.tables_dev = a->tables_dev, l.table_stride = a->table_stride;
   l.units_dev = reinterpret_cast<const DecodeUnit*>(scratch + kUnitsOff);

@@ -42,6 +42,9 @@ struct PoolView {
   int fmt;
   int num_pages;
   int n_layers;
+  int kv_head_begin;   // the context's KV heads: [kv_head_begin, kv_head_begin + kv_head_count)
+  int kv_head_count;
+  __host__ __device__ bool OwnsKvHead(int h) const { return h >= kv_head_begin && h < kv_head_begin + kv_head_count; }
 };
 
 // One split-K unit of decode attention: pages [page_begin, page_end) of one sequence for one kv head.

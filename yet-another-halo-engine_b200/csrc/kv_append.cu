@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(kAppendThreads) AppendKernel(PoolView pool, in
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int side = warp >> 2, h = warp & 3;
   const std::int64_t slot = slots[token];
-  if (slot < 0) return;  // padding token
+  if (slot < 0 || !pool.OwnsKvHead(h)) return;  // padding token, or a head another context holds
   // Writers clamp the page into the pool instead of trusting the mapping (gen_decode_attn.py:59-69).
   std::int64_t page = slot / kPageTokens;
   const int tok = static_cast<int>(slot % kPageTokens);
@@ -183,12 +183,13 @@ __global__ void __launch_bounds__(kRopeThreads)
 #pragma unroll
   for (int i = 0; i < 4; ++i) hx[i] = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
   if (is_q) {
+    if (!pool.OwnsKvHead(h / kGroup)) return;   // q rows of heads another context holds stay untouched
     *reinterpret_cast<uint4*>(q_out + (static_cast<std::size_t>(token) * kQHeads + h) * kHeadDim + lane * 8) =
         *reinterpret_cast<const uint4*>(hx);
     return;
   }
   const std::int64_t slot = slots[token];
-  if (slot < 0) return;  // padding token
+  if (slot < 0 || !pool.OwnsKvHead(h)) return;  // padding token, or a head another context holds
   std::int64_t page = slot / kPageTokens;
   const int tok = static_cast<int>(slot % kPageTokens);
   page = min(max(page, static_cast<std::int64_t>(0)), static_cast<std::int64_t>(pool.num_pages - 1));

@@ -54,6 +54,9 @@ class KvHost {
     if (c.num_pages < 1) return bad("num_pages must be positive");
     if (c.max_seqs < 1 || c.max_pages_per_seq < 1) return bad("max_seqs and max_pages_per_seq must be positive");
     if (c.max_splits < 0 || c.max_batch_tokens < 0) return bad("max_splits and max_batch_tokens must not be negative");
+    if (c.kv_head_begin < 0 || c.kv_head_count < 0 || c.kv_head_begin + c.kv_head_count > kKvHeads ||
+        (c.kv_head_count == 0 && c.kv_head_begin != 0))
+      return bad("kv_head_begin / kv_head_count must describe a range inside the 4 kv heads (count 0 = all)");
     // Token rows of all layers are addressed by a signed 32-bit tensor-map coordinate.
     const long long rows = 1LL * c.n_layers * c.num_pages * kKvHeads * kPageTokens;
     if (rows >= (1LL << 31)) return bad("n_layers * num_pages too large for the pool's row index");
@@ -61,6 +64,8 @@ class KvHost {
   }
 
   const yahkv_config& cfg() const { return cfg_; }
+  int kv_head_begin() const { return cfg_.kv_head_begin; }
+  int kv_head_count() const { return cfg_.kv_head_count == 0 ? kKvHeads : cfg_.kv_head_count; }
   int pages_free() const { return static_cast<int>(free_pages_.size()); }
   bool live(int seq) const { return seq >= 0 && seq < cfg_.max_seqs && live_[static_cast<std::size_t>(seq)] != 0; }
   int n_pages(int seq) const { return n_pages_[static_cast<std::size_t>(seq)]; }
@@ -221,7 +226,8 @@ class KvHost {
     // Automatic unit size: about five units per resident CTA slot (148 SMs x 2), at most 24 pages each. Measured on
     // the batch-32 benchmark: 10 pages 237 us, 16: 226, 24: 222, 32: 224, 48: 227 per layer; smaller units pay the
     // per-CTA prologue and partial write-back more often, larger ones leave a longer tail.
-    int auto_pages = static_cast<int>((total_pages * kKvHeads + 1479) / 1480);
+    const int hb = kv_head_begin(), hc = kv_head_count();
+    int auto_pages = static_cast<int>((total_pages * hc + 1479) / 1480);
     auto_pages = std::min(std::max(auto_pages, 1), 24);
     std::vector<DecodeUnit> units;
     std::vector<CombineItem> items(static_cast<std::size_t>(n_seqs) * kKvHeads);
@@ -232,7 +238,7 @@ class KvHost {
       int per = n_splits > 0 ? (pages + n_splits - 1) / n_splits : auto_pages;
       per = std::max(per, (pages + max_splits - 1) / max_splits);
       const int nu = (pages + per - 1) / per;
-      for (int h = 0; h < kKvHeads; ++h) {
+      for (int h = hb; h < hb + hc; ++h) {   // heads outside the context's range keep n_partials = 0
         items[static_cast<std::size_t>(b) * kKvHeads + h] = {static_cast<std::int32_t>(units.size()), nu};
         for (int k = 0; k < nu; ++k) {
           DecodeUnit u{};
@@ -291,7 +297,7 @@ class KvHost {
       seqs->push_back(ps);
       *max_pages = std::max(*max_pages, static_cast<int>(ps.n_pages));
       for (int r = 0; r < c; r += kPrefillTileRows)
-        for (int h = 0; h < kQHeads; ++h) {
+        for (int h = kv_head_begin() * kGroup; h < (kv_head_begin() + kv_head_count()) * kGroup; ++h) {
           PrefillTile t{};
           t.kv_row0 = static_cast<std::int32_t>(kv_row + static_cast<std::int64_t>(h / kGroup) * ps.kv_rows);
           t.head = h;

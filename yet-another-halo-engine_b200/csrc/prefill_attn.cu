@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(kDequantThreads)
                        const PrefillSeq* __restrict__ seqs, __half* __restrict__ k16, __half* __restrict__ v16) {
   const PrefillSeq ps = seqs[blockIdx.z];
   const int p = blockIdx.x, kvh = blockIdx.y;
-  if (p >= ps.n_pages) return;
+  if (p >= ps.n_pages || !pool.OwnsKvHead(kvh)) return;
   std::int32_t page = __ldg(tables + static_cast<std::size_t>(ps.seq) * table_stride + p);
   page = min(max(page, 0), pool.num_pages - 1);
   const std::size_t rec = (static_cast<std::size_t>(layer) * pool.num_pages + page) * kKvHeads + kvh;

@@ -155,4 +155,15 @@ __device__ __forceinline__ void Nib4x4ToHalf2(std::uint32_t w, std::uint32_t& l0
   h13 = *reinterpret_cast<const std::uint32_t*>(&rd);
 }
 
+// The same bit tricks without the arithmetic: low nibbles as fp16 1024 + n, high nibbles as 1024 + 16 n (bytes (0, 2)
+// and (1, 3) each). For dot products that fold the scale and the biases into the other operand and the accumulator.
+__device__ __forceinline__ void Nib4x4ToBiasedHalf2(std::uint32_t w, std::uint32_t& l02, std::uint32_t& l13,
+                                                    std::uint32_t& h02, std::uint32_t& h13) {
+  const std::uint32_t w8 = w >> 8;
+  l02 = (w & 0x000F000FU) | 0x64006400U;
+  l13 = (w8 & 0x000F000FU) | 0x64006400U;
+  h02 = (w & 0x00F000F0U) | 0x64006400U;
+  h13 = (w8 & 0x00F000F0U) | 0x64006400U;
+}
+
 }  // namespace yahkv

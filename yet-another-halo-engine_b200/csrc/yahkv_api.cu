@@ -197,6 +197,7 @@ int InitDevice(yahkv_ctx* ctx) {
 
   const std::size_t recs = static_cast<std::size_t>(c.n_layers) * c.num_pages * kKvHeads;
   ctx->pool.fmt = c.fmt, ctx->pool.num_pages = c.num_pages, ctx->pool.n_layers = c.n_layers;
+  ctx->pool.kv_head_begin = ctx->host.kv_head_begin(), ctx->pool.kv_head_count = ctx->host.kv_head_count();
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.kcodes, recs * RecordCodeBytes(c.fmt), true));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.vcodes, recs * RecordCodeBytes(c.fmt), true));
   if (c.fmt == YAHKV_FMT_Q8_0) {   // code 0 in the device representation (sign bit flipped)
@@ -894,6 +895,7 @@ int yahkv_batch_create(yahkv_ctx* ctx, int32_t n_seqs, const int32_t* seq_ids, y
   if (out == nullptr) return Fail(ctx, YAHKV_ERR_INVALID, "batch_create: null out pointer");
   *out = nullptr;
   if (n_seqs <= 0 || n_seqs > ctx->cfg.max_seqs || seq_ids == nullptr) return Fail(ctx, YAHKV_ERR_INVALID, "batch_create: bad sequence list");
+  if (ctx->host.kv_head_count() != kKvHeads) return Fail(ctx, YAHKV_ERR_INVALID, "batch_create: decode batches need a context that holds all four kv heads");
   auto* b = new (std::nothrow) yahkv_batch();
   if (b == nullptr) return Fail(ctx, YAHKV_ERR_INVALID, "batch_create: out of host memory");
   b->ctx = ctx;
