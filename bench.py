@@ -356,6 +356,107 @@ def churn_arm(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+def headshard_arm(args, rank, local_rank, world):
+    """The head-sharded layout (benchmark only): every GPU holds all 32 sequences but only 4 / world of the KV heads
+    (and their query heads); after each layer's attention the ranks' output slices are joined by one NCCL all-gather.
+    Strong scaling: the total work is one batch-32 step whatever the number of GPUs (1, 2 or 4)."""
+    import torch
+    import torch.distributed as dist
+    import yahkv
+
+    if world not in (1, 2, 4):
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "workload": "head_sharded", "n_gpus": world,
+                              "unavailable": "4 KV heads shard at most 4 ways"}))
+        return
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    w = workload(0, args.layers)                      # the same sequences on every rank
+    rng, lens, layers = w["rng"], w["lens"].copy(), w["layers"]
+    hc = 4 // world
+    grow = 2 * (args.warmup + args.steps) + 2
+    pages = [(int(n) + grow + 63) // 64 for n in lens]
+    num_pages = sum(pages) + 64
+    cache = yahkv.KvCache(device=local_rank, n_layers=layers, num_pages=num_pages, fmt=yahkv.FMT_Q8_0, max_seqs=BATCH,
+                          max_pages_per_seq=max(pages) + 1, max_batch_tokens=8192, kv_head_begin=rank * hc,
+                          kv_head_count=hc)
+    perm = rng.permutation(num_pages).astype(np.int32)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    sptr = stream.cuda_stream
+    gen = torch.Generator(device="cuda").manual_seed(1234)
+    seqs, off = [], 0
+    for i, n in enumerate(lens):
+        s = cache.seq_create()
+        cache.seq_set_table(s, perm[off:off + pages[i]])
+        off += pages[i]
+        seqs.append(s)
+        for c0 in range(0, int(n), 8192):
+            c1 = min(int(n), c0 + 8192)
+            K = torch.randn(c1 - c0, 4, 256, device="cuda", generator=gen).half()
+            V = torch.randn(c1 - c0, 4, 256, device="cuda", generator=gen).half()
+            ids, pos = np.full(c1 - c0, s, np.int32), np.arange(c0, c1, dtype=np.int64)
+            for layer in range(layers):
+                cache.append(layer, ids, pos, K, V, stream=sptr)
+    cache.sync()
+    seq_ids = np.array(seqs, np.int32)
+    k_new = torch.randn(layers, BATCH, 4, 256, device="cuda", generator=gen).half()
+    v_new = torch.randn(layers, BATCH, 4, 256, device="cuda", generator=gen).half()
+    q = torch.randn(layers, BATCH, 24, 256, device="cuda", generator=gen).half()
+    out = torch.zeros(layers, BATCH, 24, 256, device="cuda", dtype=torch.float16)
+    mine = slice(rank * hc * 6, (rank + 1) * hc * 6)
+    joined = torch.zeros(world, BATCH, hc * 6, 256, device="cuda", dtype=torch.float16)
+
+    def step(gather):
+        pos = np.array([cache.seq_len(s, 0) for s in seqs], np.int64)
+        for layer in range(layers):
+            cache.append(layer, seq_ids, pos, k_new[layer], v_new[layer], stream=sptr)
+            cache.attend_decode(layer, seq_ids, q[layer], out[layer], stream=sptr)
+            if gather and world > 1:
+                dist.all_gather_into_tensor(joined, out[layer][:, mine].contiguous())
+        return int(pos.sum()) + BATCH
+
+    def timed(gather):
+        for _ in range(args.warmup):
+            step(gather)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        keys = sum(step(gather) for _ in range(args.steps))
+        e1.record(stream)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1), keys
+
+    ms_c, _ = timed(False)
+    ms_g, keys = timed(True)
+    stats = torch.tensor([ms_c, ms_g], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    ms_c, ms_g = stats[0].item(), stats[1].item()
+    if rank == 0:
+        bytes_all = keys * layers * yahkv.bytes_per_token(yahkv.FMT_Q8_0)     # all four KV heads, once
+        peak, peak_kind = measured_peaks()
+        print(json.dumps({
+            "metric": METRIC, "value": bytes_all / (ms_g * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_g / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+            "config": {"workload": "batch32_decode_%dlayers_q8_0_head_sharded" % layers, "kv_heads_per_gpu": hc,
+                       "sharding": "KV heads partitioned across GPUs; one NCCL all-gather of the output slices per layer"},
+            "extra": {"ms_per_step_without_gather": ms_c / args.steps,
+                      "gather_ms_per_step": (ms_g - ms_c) / args.steps,
+                      "gathered_bytes_per_step": layers * BATCH * 24 * 256 * 2,
+                      "frac_of_measured_hbm_per_gpu": bytes_all / (ms_g * 1e-3) / 1e9 / world / peak},
+            "gpu_launches": 2 * 3 * layers * args.steps}))
+    cache.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -364,7 +465,7 @@ def main():
     ap.add_argument("--impl", default="yahkv", choices=["yahkv", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers per step (16 = the configuration)")
     ap.add_argument("--fmt", default="q8_0", choices=["q8_0", "q4_0"], help="cache format (q8_0 = the configuration)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "longctx", "churn"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "longctx", "churn", "headshard"],
                     help="decode = the batch-32 configuration (default, the headline metric); prefill = chunked "
                          "prefill; longctx = batch 8 x 131072 tokens, q4_0, 64 splits, one layer")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -385,6 +486,9 @@ def main():
         return
     if args.workload == "churn":
         churn_arm(args, rank, local_rank, world)
+        return
+    if args.workload == "headshard":
+        headshard_arm(args, rank, local_rank, world)
         return
     if args.workload == "longctx":
         global BATCH, CTX_LO, CTX_HI, N_SPLITS
