@@ -91,16 +91,6 @@ __device__ __forceinline__ void MmaQZero(float (&d)[4], std::uint32_t q_addr, st
       : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0F));
 }
-// The same step starting from a constant: rows 0-7 (the heads) start at c, the padding rows at zero.
-__device__ __forceinline__ void MmaQConst(float (&d)[4], std::uint32_t q_addr, std::uint32_t b0, std::uint32_t b1, float c) {
-  std::uint32_t a0, a1, a2, a3;
-  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(q_addr));
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-      "{%10, %10, %11, %11};"
-      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c), "f"(0.0F));
-}
 // The same step accumulating in place.
 __device__ __forceinline__ void MmaQ(float (&d)[4], std::uint32_t q_addr, std::uint32_t b0, std::uint32_t b1) {
   std::uint32_t a0, a1, a2, a3;
@@ -123,8 +113,7 @@ struct SmemLayout {
   static constexpr int kXchgOff = kQfragOff + kQfragBytes;
   static constexpr int kBarOff = kXchgOff + kXchgBytes;
   static constexpr int kCntOff = kBarOff + 8 * StageLayout<kFmt>::kStages;
-  static constexpr int kCorrOff = (kCntOff + 4 * StageLayout<kFmt>::kStages + 15) / 16 * 16;
-  static constexpr int kBytes = kCorrOff + 2 * 8 * 16;   // [dim half][head lane g] x 4 blocks of f32
+  static constexpr int kBytes = kCntOff + 4 * StageLayout<kFmt>::kStages;
 };
 template <int kFmt>
 constexpr int DecodeSmemBytes() {
@@ -141,9 +130,7 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
     DecodePartKernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                      PoolView pool, int layer, const std::int32_t* __restrict__ tables, int table_stride,
                      const DecodeUnit* __restrict__ units, const __half* __restrict__ q, float scale_log2,
-                     float* __restrict__ partial_acc, float* __restrict__ partial_ml, int* status,
-                     const CombineItem* __restrict__ items, int* counters, const float* __restrict__ gate, void* out,
-                     int out_f32) {
+                     float* __restrict__ partial_acc, float* __restrict__ partial_ml, int* status) {
   using L = StageLayout<kFmt>;
   using S = SmemLayout<kFmt>;
   extern __shared__ __align__(1024) std::uint8_t smem_raw[];
@@ -152,7 +139,6 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
   float4* xchg = reinterpret_cast<float4*>(smem_raw + S::kXchgOff);     // partial scores [8 warps][24 lanes]
   std::uint64_t* full_bar = reinterpret_cast<std::uint64_t*>(smem_raw + S::kBarOff);
   int* done_cnt = reinterpret_cast<int*>(smem_raw + S::kCntOff);        // warps done reading a stage's page
-  float* qcorr = reinterpret_cast<float*>(smem_raw + S::kCorrOff);      // [dim half][head lane][block]: -1152 sum(q)
   if ((SmemAddr(smem_raw) & 1023U) != 0) {   // never seen; checked because a misaligned swizzle would corrupt results
     if (threadIdx.x == 0) atomicExch(status, kStatusSmemMisaligned);
     return;
@@ -205,36 +191,15 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
   // + {1, 3} in (2t+8, 2t+9).
   {
     const __half* qrow = q + (static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + g) * kHeadDim;
-    static_assert(16 / kWarps == 2, "a warp loads the two MMA steps of one 32-dim block");
-    // Scores are taken on biased codes, straight from the bit tricks, and the bias times the block's sum of q is what
-    // the MMA accumulator starts from, so the subtract per code pair is never executed:
-    //   q8_0: the operand is the fp16 1152 + code; the accumulator starts at -1152 sum(q).
-    //   q4_0: elements 0-15 of a block (low nibbles) come as 1024 + n, elements 16-31 (high nibbles, left in place)
-    //         as 1024 + 16 n against q / 16 (exact in fp16), so the products sum to q n + 1024 sum_lo(q) +
-    //         64 sum_hi(q); with the -8 of the format the accumulator starts at -1032 sum_lo(q) - 72 sum_hi(q).
-    float qsum[2] = {0.0F, 0.0F};   // this thread's 4 + 4 of the 16 + 16 values of block `warp` of head g
 #pragma unroll
     for (int cc = 0; cc < 16 / kWarps; ++cc) {
       const int c = warp * (16 / kWarps) + cc;
       if (g < kGroup) {
-        uint2 v = *reinterpret_cast<const uint2*>(qrow + 16 * c + 4 * t);
-        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
-        const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
-        qsum[cc] = (f0.x + f0.y) + (f1.x + f1.y);
-        if (kFmt == kFmtQ4 && cc == 1) {   // the MMA step of a block's high nibbles
-          const __half2 sixteenth = __halves2half2(__ushort_as_half(0x2C00), __ushort_as_half(0x2C00));
-          const __half2 a = __hmul2(*reinterpret_cast<const __half2*>(&v.x), sixteenth);
-          const __half2 b = __hmul2(*reinterpret_cast<const __half2*>(&v.y), sixteenth);
-          v.x = *reinterpret_cast<const std::uint32_t*>(&a), v.y = *reinterpret_cast<const std::uint32_t*>(&b);
-        }
+        const uint2 v = *reinterpret_cast<const uint2*>(qrow + 16 * c + 4 * t);
         qfrag[c * kQLanes + lane] = make_uint4(__byte_perm(v.x, v.y, 0x5410), 0U,   // halves (0, 2)
                                                __byte_perm(v.x, v.y, 0x7632), 0U);  // halves (1, 3)
       }
     }
-    float corr = kFmt == kFmtQ8 ? -1152.0F * (qsum[0] + qsum[1]) : -1032.0F * qsum[0] - 72.0F * qsum[1];
-    corr += __shfl_xor_sync(0xFFFFFFFFU, corr, 1);
-    corr += __shfl_xor_sync(0xFFFFFFFFU, corr, 2);
-    if (t == 0) qcorr[((warp >> 2) * 8 + g) * 4 + (warp & 3)] = g < kGroup ? corr : 0.0F;
   }
   __syncthreads();   // barriers initialised, Q fragments visible
   // This warp's eight MMA steps are c = 8 dh .. 8 dh + 7.
@@ -283,7 +248,6 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
 #pragma unroll
         for (int j = 0; j < 2; ++j)
           ks_raw[kt][j] = *reinterpret_cast<const uint2*>(st + L::kKsOff + (my_key0 + kt * 8 + j) * 16 + dh * 8);
-      const float4 corr = *reinterpret_cast<const float4*>(qcorr + (dh * 8 + g) * 4);
       if constexpr (kFmt == kFmtQ8) {
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
@@ -291,14 +255,13 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
           LdMatrixX4(k_base + lm_off[b], w);
           float a0[4], a1[4];
           std::uint32_t x0, x1;
-          const float cb = b == 0 ? corr.x : b == 1 ? corr.y : b == 2 ? corr.z : corr.w;
-          Offset8x4ToBiasedHalf2(w[0], x0, x1);
-          MmaQConst(a0, qa_addr + (2 * b) * (kQLanes * 16), x0, x1, cb);
-          Offset8x4ToBiasedHalf2(w[1], x0, x1);
-          MmaQConst(a1, qa_addr + (2 * b) * (kQLanes * 16), x0, x1, cb);
-          Offset8x4ToBiasedHalf2(w[2], x0, x1);
+          Offset8x4ToHalf2(w[0], x0, x1);
+          MmaQZero(a0, qa_addr + (2 * b) * (kQLanes * 16), x0, x1);
+          Offset8x4ToHalf2(w[1], x0, x1);
+          MmaQZero(a1, qa_addr + (2 * b) * (kQLanes * 16), x0, x1);
+          Offset8x4ToHalf2(w[2], x0, x1);
           MmaQ(a0, qa_addr + (2 * b + 1) * (kQLanes * 16), x0, x1);
-          Offset8x4ToBiasedHalf2(w[3], x0, x1);
+          Offset8x4ToHalf2(w[3], x0, x1);
           MmaQ(a1, qa_addr + (2 * b + 1) * (kQLanes * 16), x0, x1);
           sc[0][0] = fmaf(ScaleOf(ks_raw[0][0], b), a0[0], sc[0][0]);
           sc[0][1] = fmaf(ScaleOf(ks_raw[0][1], b), a0[1], sc[0][1]);
@@ -316,12 +279,11 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
             const int b = 2 * bp + hb;   // block 4 dh + b
             float a0[4], a1[4];
             std::uint32_t l0, l1, h0, h1;
-            const float cb = b == 0 ? corr.x : b == 1 ? corr.y : b == 2 ? corr.z : corr.w;
-            Nib4x4ToBiasedHalf2(w[2 * hb], l0, l1, h0, h1);
-            MmaQConst(a0, qa_addr + (2 * b) * (kQLanes * 16), l0, l1, cb);
+            Nib4x4ToHalf2(w[2 * hb], l0, l1, h0, h1);
+            MmaQZero(a0, qa_addr + (2 * b) * (kQLanes * 16), l0, l1);
             MmaQ(a0, qa_addr + (2 * b + 1) * (kQLanes * 16), h0, h1);
-            Nib4x4ToBiasedHalf2(w[2 * hb + 1], l0, l1, h0, h1);
-            MmaQConst(a1, qa_addr + (2 * b) * (kQLanes * 16), l0, l1, cb);
+            Nib4x4ToHalf2(w[2 * hb + 1], l0, l1, h0, h1);
+            MmaQZero(a1, qa_addr + (2 * b) * (kQLanes * 16), l0, l1);
             MmaQ(a1, qa_addr + (2 * b + 1) * (kQLanes * 16), h0, h1);
             sc[0][0] = fmaf(ScaleOf(ks_raw[0][0], b), a0[0], sc[0][0]);
             sc[0][1] = fmaf(ScaleOf(ks_raw[0][1], b), a0[1], sc[0][1]);
@@ -511,71 +473,6 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
       if (tid == 0) ml_out[2 * h] = M, ml_out[2 * h + 1] = lsum;
     }
   }
-  if (counters == nullptr) return;   // a separate combine launch follows
-
-  // ---- the unit that arrives last at its (sequence, kv head) counter merges that pair's partials ----
-  // (the reference's dattn_reduce, engine/gpu/loom/tools/gen_decode_attn.py:373-408, without a second launch: no unit
-  // waits for another; partials are merged in unit order whatever the arrival order, so results do not depend on it)
-  const int item_idx = u.batch * kKvHeads + u.kvh;
-  const CombineItem it = items[item_idx];
-  __threadfence();   // this unit's partial is visible device-wide before its arrival is counted
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const bool last = atomicAdd(&counters[item_idx], 1) == it.n_partials - 1;
-    if (last) counters[item_idx] = 0;   // re-armed for the next call
-    done_cnt[0] = last ? 1 : 0;
-  }
-  __syncthreads();
-  if (done_cnt[0] == 0) return;
-  __threadfence();
-  {
-    // Step 1: every unit's (max, sum) pairs into shared memory with independent loads (the ring is free again).
-    // Step 2: per head the overall max and each unit's weight 2^(m - M). Step 3: thread = output dim, all loads of
-    // the weighted sum independent of each other.
-    float* ml_s = reinterpret_cast<float*>(ring);                       // [n_partials][12]
-    float* w_s = ml_s + static_cast<std::size_t>(it.n_partials) * kPartialMlFloats;   // [n_partials][6]
-    float* l_s = w_s + static_cast<std::size_t>(it.n_partials) * kGroup;               // [6] overall sums
-    const float* ml_g = partial_ml + static_cast<std::size_t>(it.first_partial) * kPartialMlFloats;
-    for (int e = threadIdx.x; e < it.n_partials * kPartialMlFloats; e += kDecodeThreads) ml_s[e] = __ldcg(ml_g + e);
-    __syncthreads();
-    if (threadIdx.x < kGroup) {
-      const int h = threadIdx.x;
-      float M = -INFINITY;
-      for (int i = 0; i < it.n_partials; ++i) M = fmaxf(M, ml_s[i * kPartialMlFloats + 2 * h]);
-      float Lsum = 0.0F;
-      for (int i = 0; i < it.n_partials; ++i) {   // in unit order
-        const float m = ml_s[i * kPartialMlFloats + 2 * h];
-        const float w = m == -INFINITY ? 0.0F : Exp2Fast(m - M);
-        w_s[i * kGroup + h] = w;
-        Lsum = fmaf(w, ml_s[i * kPartialMlFloats + 2 * h + 1], Lsum);
-      }
-      l_s[h] = Lsum;
-    }
-    __syncthreads();
-    const int d = threadIdx.x;
-    const float* acc_g = partial_acc + static_cast<std::size_t>(it.first_partial) * kPartialAccFloats + d;
-    float A[kGroup];
-#pragma unroll
-    for (int h = 0; h < kGroup; ++h) A[h] = 0.0F;
-#pragma unroll 2
-    for (int i = 0; i < it.n_partials; ++i) {
-      float v[kGroup];
-#pragma unroll
-      for (int h = 0; h < kGroup; ++h) v[h] = __ldcg(acc_g + static_cast<std::size_t>(i) * kPartialAccFloats + h * kHeadDim);
-#pragma unroll
-      for (int h = 0; h < kGroup; ++h) A[h] = fmaf(w_s[i * kGroup + h], v[h], A[h]);
-    }
-#pragma unroll
-    for (int h = 0; h < kGroup; ++h) {
-      float o = A[h] * (1.0F / l_s[h]);
-      const std::size_t oi = (static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + h) * kHeadDim + d;
-      if (gate != nullptr) o *= 1.0F / (1.0F + expf(-gate[oi]));
-      if (out_f32)
-        static_cast<float*>(out)[oi] = o;
-      else
-        static_cast<__half*>(out)[oi] = __float2half_rn(o);
-    }
-  }
 }
 
 // Merge the units of one (batch row, query head): out = (sum w_i acc_i) / (sum w_i l_i) * sigmoid(gate) with
@@ -647,16 +544,16 @@ cudaError_t LaunchDecodePart(const DecodeLaunch& a, cudaStream_t stream) {
   if (a.pool.fmt == kFmtQ8)
     DecodePartKernel<kFmtQ8><<<a.n_units, kDecodeThreads, DecodeSmemBytes<kFmtQ8>(), stream>>>(
         *a.kmap, *a.vmap, a.pool, a.layer, a.tables_dev, a.table_stride, a.units_dev, q, a.scale_log2, a.partial_acc,
-        a.partial_ml, a.status_dev, a.items_dev, a.counters_dev, a.gate_dev, a.out_dev, a.out_f32);
+        a.partial_ml, a.status_dev);
   else
     DecodePartKernel<kFmtQ4><<<a.n_units, kDecodeThreads, DecodeSmemBytes<kFmtQ4>(), stream>>>(
         *a.kmap, *a.vmap, a.pool, a.layer, a.tables_dev, a.table_stride, a.units_dev, q, a.scale_log2, a.partial_acc,
-        a.partial_ml, a.status_dev, a.items_dev, a.counters_dev, a.gate_dev, a.out_dev, a.out_f32);
+        a.partial_ml, a.status_dev);
   return cudaGetLastError();
 }
 
 cudaError_t LaunchDecodeCombine(const DecodeLaunch& a, cudaStream_t stream) {
-  if (a.n_units <= 0 || a.n_seqs <= 0 || a.counters_dev != nullptr) return cudaSuccess;  // merged in the part kernel
+  if (a.n_units <= 0 || a.n_seqs <= 0) return cudaSuccess;
   DecodeCombineKernel<<<a.n_seqs * kQHeads, kHeadDim, 0, stream>>>(a.items_dev, a.partial_acc, a.partial_ml,
                                                                   a.gate_dev, a.out_dev, a.out_f32);
   return cudaGetLastError();

@@ -130,9 +130,6 @@ struct DecodeLaunch {
   float* partial_acc;
   float* partial_ml;
   int* status_dev;          // sticky error word, 0 = ok
-  // Arrival counters, one per (batch row, kv head), all zero between calls. When given, the unit that arrives last
-  // at its counter merges that pair's partials and writes the output itself, and no combine launch is needed.
-  int* counters_dev;
 };
 cudaError_t LaunchDecodePart(const DecodeLaunch& a, cudaStream_t stream);
 cudaError_t LaunchDecodeCombine(const DecodeLaunch& a, cudaStream_t stream);

@@ -126,12 +126,6 @@ __device__ __forceinline__ void Offset8x4ToHalf2(std::uint32_t u, std::uint32_t&
   h02 = *reinterpret_cast<const std::uint32_t*>(&a);
   h13 = *reinterpret_cast<const std::uint32_t*>(&b);
 }
-// The same without the subtract: two half2 holding 1152 + code (exact: at most 1279). For dot products whose
-// accumulator starts at -1152 times the sum of the other operand.
-__device__ __forceinline__ void Offset8x4ToBiasedHalf2(std::uint32_t u, std::uint32_t& h02, std::uint32_t& h13) {
-  h02 = __byte_perm(u, 0x64646464U, 0x4240);
-  h13 = __byte_perm(u, 0x64646464U, 0x4341);
-}
 // Four packed q4_0 bytes -> low nibbles of bytes (0,2), (1,3) and high nibbles of bytes (0,2), (1,3), each minus 8.
 __device__ __forceinline__ void Nib4x4ToHalf2(std::uint32_t w, std::uint32_t& l02, std::uint32_t& l13,
                                               std::uint32_t& h02, std::uint32_t& h13) {
@@ -153,17 +147,6 @@ __device__ __forceinline__ void Nib4x4ToHalf2(std::uint32_t w, std::uint32_t& l0
   l13 = *reinterpret_cast<const std::uint32_t*>(&rb);
   h02 = *reinterpret_cast<const std::uint32_t*>(&rc);
   h13 = *reinterpret_cast<const std::uint32_t*>(&rd);
-}
-
-// The same bit tricks without the arithmetic: low nibbles as fp16 1024 + n, high nibbles as 1024 + 16 n (bytes (0, 2)
-// and (1, 3) each). For dot products that fold the scale and the biases into the other operand and the accumulator.
-__device__ __forceinline__ void Nib4x4ToBiasedHalf2(std::uint32_t w, std::uint32_t& l02, std::uint32_t& l13,
-                                                    std::uint32_t& h02, std::uint32_t& h13) {
-  const std::uint32_t w8 = w >> 8;
-  l02 = (w & 0x000F000FU) | 0x64006400U;
-  l13 = (w8 & 0x000F000FU) | 0x64006400U;
-  h02 = (w & 0x00F000F0U) | 0x64006400U;
-  h13 = (w8 & 0x00F000F0U) | 0x64006400U;
 }
 
 }  // namespace yahkv

@@ -102,7 +102,6 @@ struct yahkv_ctx {
   float* partial_ml = nullptr;
   int max_units = 0;
   int* status_dev = nullptr;
-  int* counters_dev = nullptr;
   cudaStream_t stream = nullptr;
   Staging staging;
   // Device-side staging of the host-buffer entry points: two sets used in turn, so the copies of one layer-step (on
@@ -217,7 +216,6 @@ int InitDevice(yahkv_ctx* ctx) {
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->tiles_dev, static_cast<std::size_t>(ctx->max_tiles), false));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pseqs_dev, static_cast<std::size_t>(c.max_seqs), false));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->status_dev, 1, true));
-  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->counters_dev, static_cast<std::size_t>(c.max_seqs) * kKvHeads, true));
   const std::size_t ns = static_cast<std::size_t>(c.max_seqs);
   for (auto& h : ctx->hst) {
     YAHKV_CUDA(ctx, DevAlloc(ctx, reinterpret_cast<char**>(&h.k), ns * kKvHeads * kHeadDim * 2, false));
@@ -254,7 +252,7 @@ void FreeDevice(yahkv_ctx* ctx) {
   if (ctx->stream != nullptr) cudaStreamSynchronize(ctx->stream);
   void* ptrs[] = {ctx->pool.kcodes, ctx->pool.vcodes, ctx->pool.kscales, ctx->pool.vscales, ctx->tables_dev,
                   ctx->slots_dev,   ctx->units_dev,   ctx->items_dev,    ctx->partial_acc,  ctx->partial_ml,
-                  ctx->tiles_dev,   ctx->status_dev,  ctx->counters_dev, ctx->pseqs_dev, ctx->k16_dev, ctx->v16_dev,
+                  ctx->tiles_dev,   ctx->status_dev,  ctx->pseqs_dev, ctx->k16_dev, ctx->v16_dev,
                   ctx->rope_tab_dev, ctx->rope_pos_dev};
   for (void* p : ptrs)
     if (p != nullptr) cudaFree(p);
@@ -607,13 +605,12 @@ int yahkv_attend_decode(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int
   a.q_dev = q_dev, a.gate_dev = gate_dev, a.out_dev = out_dev, a.out_f32 = out_dtype == YAHKV_OUT_F32;
   a.scale_log2 = ctx->scale_log2;
   a.partial_acc = ctx->partial_acc, a.partial_ml = ctx->partial_ml, a.status_dev = ctx->status_dev;
-  // The merge runs as its own small launch. Letting the last-arriving unit merge inside the part kernel (pass
-  // ctx->counters_dev here) was measured 1% slower end to end: every CTA then pays a fence and an atomic on exit.
-  a.counters_dev = nullptr;
+  // The merge runs as its own small launch: letting the last-arriving unit merge inside the part kernel was measured
+  // 1% slower end to end (every CTA then pays a fence and an atomic on exit).
   TimedLaunch tp(ctx, YAHKV_KERNEL_DECODE_PART, st);
   cudaError_t le = LaunchDecodePart(a, st);
   tp.End();
-  if (le == cudaSuccess && a.counters_dev == nullptr) {
+  if (le == cudaSuccess) {
     TimedLaunch tc(ctx, YAHKV_KERNEL_DECODE_COMBINE, st);
     le = LaunchDecodeCombine(a, st);
     tc.End();
@@ -622,7 +619,7 @@ int yahkv_attend_decode(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int
     ctx->host.InvalidateDecodePlan();
     return FailCuda(ctx, "decode attention launch", le);
   }
-  ctx->launches += a.counters_dev == nullptr ? 2 : 1;
+  ctx->launches += 2;
   return YAHKV_OK;
 }
 
@@ -1023,7 +1020,6 @@ int yahkv_batch_decode_layer(yahkv_batch* b, int32_t layer, const void* k_dev, c
   a.q_dev = q_dev, a.gate_dev = gate_dev, a.out_dev = out_dev, a.out_f32 = out_dtype == YAHKV_OUT_F32;
   a.scale_log2 = ctx->scale_log2;
   a.partial_acc = ctx->partial_acc, a.partial_ml = ctx->partial_ml, a.status_dev = ctx->status_dev;
-  a.counters_dev = nullptr;
   YAHKV_CUDA(ctx, LaunchDecodePart(a, st));
   YAHKV_CUDA(ctx, LaunchDecodeCombine(a, st));
   ctx->launches += 3;
