@@ -126,6 +126,31 @@ def test_full_size_chunk_properties():
     cache.close()
 
 
+def test_tail_tiles_split_along_the_keys(monkeypatch):
+    """With 20 SMs to fill, the 48 tiles of this call leave a last wave of 8: those are split into two key ranges each
+    and joined by the merge kernel (three launches instead of two). Results against the oracle, gate and fp16 output
+    included, and against the unsplit run."""
+    cached, chunk = 500, 129
+    runs = []
+    for sms in ("0", "20"):
+        monkeypatch.setenv("YAHKV_PREFILL_SMS", sms)
+        cache, pool, seqs, tables, rng = build(yahkv.FMT_Q8_0, [cached], [chunk], seed=46)
+        q = rng.standard_normal((chunk, 24, 256)).astype(np.float16)
+        gate = rng.standard_normal((chunk, 24, 256)).astype(np.float32)
+        before = cache.launch_count()
+        got = run_prefill(cache, 0, seqs, [chunk], q, gate, yahkv.OUT_F32)
+        launches = cache.launch_count() - before
+        got16 = run_prefill(cache, 0, seqs, [chunk], q, None, yahkv.OUT_F16)
+        want = pool.attend_prefill_f64(tables[0], cached, q, gate=gate)
+        want_plain = pool.attend_prefill_f64(tables[0], cached, q)
+        assert np.abs(got - want).max() <= ABS_TOL
+        assert np.abs(got16 - want_plain).max() <= ABS_TOL + np.abs(want_plain).max() * 2.0 ** -11
+        runs.append((got, launches))
+        cache.close()
+    assert runs[0][1] == 2 and runs[1][1] == 3
+    assert np.abs(runs[0][0] - runs[1][0]).max() <= 5e-4
+
+
 def test_prefill_errors_launch_nothing():
     cache, pool, seqs, tables, rng = build(yahkv.FMT_Q8_0, [10], [5], seed=44)
     q = torch.zeros(20, 24, 256, dtype=torch.float16, device="cuda")

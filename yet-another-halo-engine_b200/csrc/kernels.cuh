@@ -97,8 +97,21 @@ struct PrefillTile {
   std::int32_t q_row0;      // first packed query row of the tile
   std::int32_t n_rows;      // valid query rows in the tile (<= 128)
   std::int32_t pos0;        // position of the tile's first query row; row r sees keys 0 .. pos0 + r
-  std::int32_t pad[3];
+  std::int32_t jt_begin;    // 64-key tiles [jt_begin, jt_end) of the keys the rows can see: all of them for a whole
+  std::int32_t jt_end;      // tile, a slice of them for a part of a split tile
+  std::int32_t part;        // -1: the CTA finishes the rows itself; >= 0: slot of its unnormalised partial result
 };
+static_assert(sizeof(PrefillTile) == 32, "uploaded as an array");
+
+// A tile of the call's last, partly filled wave that was split along the keys into n_parts CTAs (consecutive entries
+// of the tile list from tile_index on, consecutive part slots): the merge kernel joins their partial results.
+struct PrefillMerge {
+  std::int32_t tile_index;
+  std::int32_t n_parts;
+};
+// Partial result of one part: O [128 rows][256] f32 unnormalised, then (max in log2 units, sum) per row.
+constexpr int kPrefillPartAccFloats = kPrefillTileRows * kHeadDim;
+constexpr int kPrefillPartMlFloats = kPrefillTileRows * 2;
 
 // Partial workspace per unit: acc [6][256] f32 (unnormalised), then ml [6][2] f32 (max in log2 units, sum).
 constexpr int kPartialAccFloats = kGroup * kHeadDim;
@@ -151,6 +164,10 @@ struct PrefillLaunch {
   const CUtensorMap* v16map;
   const PrefillTile* tiles_dev;
   int n_tiles;
+  const PrefillMerge* merges_dev;   // split tiles of this call (may be empty)
+  int n_merges;
+  float* part_acc;                  // [parts][128][256] f32
+  float* part_ml;                   // [parts][128][2] f32
   const float* gate_dev;
   void* out_dev;
   int out_f32;

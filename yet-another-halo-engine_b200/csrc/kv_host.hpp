@@ -269,9 +269,12 @@ class KvHost {
 
   // Work lists of one prefill call: per sequence the span of the fp16 scratch it is dequantized into, and tiles of
   // 128 query rows x one query head, the ones with the most keys first so that the short ones fill the tail.
+  // n_sm > 0: the tiles of the last, partly filled wave (one CTA per SM and wave, all tiles cost about the same) are
+  // split along their keys into parts that fill the wave's idle SMs; `merges` lists them for the merge kernel.
   HostError PlanPrefill(int layer, int n_seqs, const std::int32_t* seq_ids, const std::int32_t* chunk_lens,
-                        int max_rows, std::vector<PrefillSeq>* seqs, std::vector<PrefillTile>* tiles,
-                        std::int64_t* total_rows, std::int64_t* scratch_rows, int* max_pages) {
+                        int max_rows, int n_sm, std::vector<PrefillSeq>* seqs, std::vector<PrefillTile>* tiles,
+                        std::vector<PrefillMerge>* merges, int* n_parts, std::int64_t* total_rows,
+                        std::int64_t* scratch_rows, int* max_pages) {
     if (layer < 0 || layer >= cfg_.n_layers) return {YAHKV_ERR_INVALID, "attend_prefill: layer out of range"};
     if (n_seqs < 0 || (n_seqs > 0 && (seq_ids == nullptr || chunk_lens == nullptr)))
       return {YAHKV_ERR_INVALID, "attend_prefill: bad sequence list"};
@@ -304,6 +307,7 @@ class KvHost {
           t.q_row0 = static_cast<std::int32_t>(row + r);
           t.n_rows = std::min(kPrefillTileRows, c - r);
           t.pos0 = static_cast<std::int32_t>(n - c + r);
+          t.jt_begin = 0, t.jt_end = (t.pos0 + t.n_rows + 63) / 64, t.part = -1;
           tiles->push_back(t);
         }
       row += c;
@@ -313,6 +317,28 @@ class KvHost {
     if (row > max_rows) return {YAHKV_ERR_CAPACITY, "attend_prefill: more query rows than max_batch_tokens"};
     std::stable_sort(tiles->begin(), tiles->end(),
                      [](const PrefillTile& a, const PrefillTile& b) { return a.pos0 + a.n_rows > b.pos0 + b.n_rows; });
+    merges->clear();
+    *n_parts = 0;
+    const int n_tiles = static_cast<int>(tiles->size());
+    const int tail = n_sm > 0 && n_tiles > n_sm ? n_tiles % n_sm : 0;
+    if (tail > 0 && 2 * tail <= n_sm) {
+      const int f = std::min(4, n_sm / tail);
+      const std::vector<PrefillTile> last(tiles->end() - tail, tiles->end());
+      tiles->resize(static_cast<std::size_t>(n_tiles - tail));
+      for (const PrefillTile& t : last) {
+        const int ff = std::min(f, t.jt_end / 2);   // a part covers at least two key tiles
+        if (ff < 2) {
+          tiles->push_back(t);
+          continue;
+        }
+        merges->push_back({static_cast<std::int32_t>(tiles->size()), ff});
+        for (int k = 0; k < ff; ++k) {
+          PrefillTile p = t;
+          p.jt_begin = t.jt_end * k / ff, p.jt_end = t.jt_end * (k + 1) / ff, p.part = (*n_parts)++;
+          tiles->push_back(p);
+        }
+      }
+    }
     *total_rows = row;
     *scratch_rows = kv_row;
     return {};

@@ -30,6 +30,10 @@
 // multicast, no cluster. Every mbarrier wait is bounded and abortable: a wait that gives up raises a CTA-wide abort
 // flag, every role leaves its loop, TMEM is freed, and the status word tells the host the call's results are invalid.
 //
+// Tiles of a call's last, partly filled wave arrive split along the keys (PrefillTile::jt_begin / jt_end / part): such
+// a CTA leaves its unnormalised accumulator and the rows' (max, sum) in a workspace and PrefillMergeKernel joins the
+// parts.
+//
 // What bounds it: the tensor pipe needs 1,024 clocks per 64-key tile (16 x 32 + 4 x 128) and the measured steady
 // state is ~1,430. The six query heads of a GQA group times the query tiles are separate CTAs, so every CTA pulls
 // its own 64 KB per tile from L2: 45 B/clock/SM, about 10.5 TB/s over the chip, which is where the MMA warp's waits
@@ -208,14 +212,18 @@ static_assert(sizeof(PrefillBars) <= kBarBytes, "the max / sum exchange follows 
 __global__ void __launch_bounds__(kPrefillThreads, 1)
     PrefillKernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                   const PrefillTile* __restrict__ tiles, const __half* __restrict__ q, const float* __restrict__ gate,
-                  void* out, int out_f32, float scale_log2, int* status) {
+                  void* out, int out_f32, float scale_log2, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                  int* status) {
   extern __shared__ __align__(1024) std::uint8_t smem[];
   PrefillBars* bars = reinterpret_cast<PrefillBars*>(smem + kSmemBars);
   volatile int* abort_flag = &bars->abort_flag;
   const PrefillTile tile = tiles[blockIdx.x];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kv_len = tile.pos0 + tile.n_rows;                 // keys any row of the tile can see
-  const int n_tiles = (kv_len + kTileN - 1) / kTileN;
+  // Key tiles jt0 .. jt0 + n_tiles - 1 of the keys the tile's rows can see: all of them, or one slice of a tile
+  // that the planner split along the keys. Every loop below runs on the local index j; only the load coordinate and
+  // the causal mask use the absolute tile jt0 + j.
+  const int jt0 = tile.jt_begin;
+  const int n_tiles = tile.jt_end - tile.jt_begin;
 
   if ((SmemAddr(smem) & 1023U) != 0) {   // the swizzled operands need the 1024-byte aligned base
     if (threadIdx.x == 0) atomicExch(status, kStatusPrefillAbort);
@@ -261,7 +269,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       int s = 0;
       std::uint32_t ph = 1;   // parity of the "empty" phase to wait for: 0 on the ring's second round, then alternating
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int y = tile.kv_row0 + j * kTileN;
+        const int y = tile.kv_row0 + (jt0 + j) * kTileN;
         if (j >= kKvStages) ok = WaitOrAbort(&bars->kv_empty[s], ph, abort_flag);
         if (!ok) break;
         if (elected) {
@@ -384,10 +392,11 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       TmemWaitLd();
       // Row max on the raw scores (the scale is positive); the causal mask only on tiles that reach past the tile's
       // first row (a warp-uniform test), where a masked score becomes -inf.
-      if (j * kTileN + kTileN - 1 > tile.pos0) {
+      const int key0 = (jt0 + j) * kTileN;
+      if (key0 + kTileN - 1 > tile.pos0) {
 #pragma unroll
         for (int c = 0; c < kTileN; ++c)
-          if (j * kTileN + c > my_last_key) sraw[c] = 0xFF800000U;   // -inf
+          if (key0 + c > my_last_key) sraw[c] = 0xFF800000U;   // -inf
       }
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -467,7 +476,26 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     }
     xsum[hc * kTileM + r] = l_mine;
     NamedBarrierSync(1, kSoftmaxThreads);
-    if (ok && n_tiles > 0) {
+    if (ok && n_tiles > 0 && tile.part >= 0) {
+      // A part of a split tile: the unnormalised accumulator and the row's (reference max, sum) go to the part's slot
+      // of the workspace; the merge kernel joins the parts.
+      TcFenceAfter();
+      float* acc = part_acc + (static_cast<std::size_t>(tile.part) * kTileM + r) * kHeadDim + hc * (kHeadDim / 2);
+      if (hc == 0) {
+        float* ml = part_ml + (static_cast<std::size_t>(tile.part) * kTileM + r) * 2;
+        ml[0] = mref[r];
+        ml[1] = l_mine + xsum[kTileM + r];
+      }
+#pragma unroll 1
+      for (int c0 = 0; c0 < kHeadDim / 2; c0 += 32) {
+        std::uint32_t o[32];
+        TmemLd32(lane_addr + kColO + hc * (kHeadDim / 2) + c0, o);
+        TmemWaitLd();
+        uint4* dst = reinterpret_cast<uint4*>(acc + c0);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) dst[c] = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+      }
+    } else if (ok && n_tiles > 0) {
       TcFenceAfter();
       const float inv = 1.0F / (l_mine + xsum[(hc ^ 1) * kTileM + r]);
       const bool valid = r < tile.n_rows;
@@ -513,6 +541,37 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
   }
 }
 
+// Joins the parts of a split tile: out = (sum_i 2^(m_i - M) O_i) / (sum_i 2^(m_i - M) l_i) * sigmoid(gate), parts in
+// order. One CTA per split tile, thread = output dim, looping over the tile's rows.
+__global__ void __launch_bounds__(kHeadDim)
+    PrefillMergeKernel(const PrefillMerge* __restrict__ merges, const PrefillTile* __restrict__ tiles,
+                       const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                       const float* __restrict__ gate, void* out, int out_f32) {
+  const PrefillMerge mg = merges[blockIdx.x];
+  const PrefillTile t = tiles[mg.tile_index];
+  const int d = threadIdx.x;
+  for (int r = 0; r < t.n_rows; ++r) {
+    float M = -INFINITY;
+    for (int i = 0; i < mg.n_parts; ++i)
+      M = fmaxf(M, part_ml[(static_cast<std::size_t>(t.part + i) * kTileM + r) * 2]);
+    float a = 0.0F, l = 0.0F;
+    for (int i = 0; i < mg.n_parts; ++i) {
+      const std::size_t row = static_cast<std::size_t>(t.part + i) * kTileM + r;
+      const float m = part_ml[row * 2];
+      const float w = m == -INFINITY ? 0.0F : Exp2Fast(m - M);
+      a = fmaf(w, part_acc[row * kHeadDim + d], a);
+      l = fmaf(w, part_ml[row * 2 + 1], l);
+    }
+    float o = a / l;
+    const std::size_t oi = (static_cast<std::size_t>(t.q_row0 + r) * kQHeads + t.head) * kHeadDim + d;
+    if (gate != nullptr) o *= 1.0F / (1.0F + expf(-gate[oi]));
+    if (out_f32)
+      static_cast<float*>(out)[oi] = o;
+    else
+      static_cast<__half*>(out)[oi] = __float2half_rn(o);
+  }
+}
+
 }  // namespace
 
 cudaError_t ConfigurePrefillKernels() {
@@ -537,7 +596,10 @@ cudaError_t LaunchPrefill(const PrefillLaunch& a, cudaStream_t stream) {
   if (a.n_tiles <= 0) return cudaSuccess;
   PrefillKernel<<<a.n_tiles, kPrefillThreads, kPrefillSmemBytes, stream>>>(
       *a.k16map, *a.v16map, a.tiles_dev, static_cast<const __half*>(a.q_dev), a.gate_dev, a.out_dev, a.out_f32,
-      a.scale_log2, a.status_dev);
+      a.scale_log2, a.part_acc, a.part_ml, a.status_dev);
+  if (a.n_merges > 0)
+    PrefillMergeKernel<<<a.n_merges, kHeadDim, 0, stream>>>(a.merges_dev, a.tiles_dev, a.part_acc, a.part_ml, a.gate_dev,
+                                                          a.out_dev, a.out_f32);
   return cudaGetLastError();
 }
 

@@ -6,6 +6,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstdio>
 #include <cstring>
 #include <memory>
@@ -129,6 +130,11 @@ struct yahkv_ctx {
   std::vector<std::int64_t> slot_scratch;
   std::vector<std::int64_t> pos_scratch;
   std::vector<PrefillTile> tile_scratch;
+  std::vector<PrefillMerge> merge_scratch;
+  PrefillMerge* merges_dev = nullptr;
+  float* part_acc_dev = nullptr;   // partial results of split prefill tiles: one slot per SM at most
+  float* part_ml_dev = nullptr;
+  int n_sm = 0;                    // SMs the prefill planner fills waves of
   std::vector<PrefillSeq> pseq_scratch;
   PrefillSeq* pseqs_dev = nullptr;
   void *k16_dev = nullptr, *v16_dev = nullptr;   // fp16 scratch of the prefill dequantize pass, grown on demand
@@ -212,8 +218,16 @@ int InitDevice(yahkv_ctx* ctx) {
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->items_dev, static_cast<std::size_t>(c.max_seqs) * kKvHeads, false));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->partial_acc, static_cast<std::size_t>(ctx->max_units) * kPartialAccFloats, false));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->partial_ml, static_cast<std::size_t>(ctx->max_units) * kPartialMlFloats, false));
-  ctx->max_tiles = (c.max_batch_tokens / kPrefillTileRows + c.max_seqs) * kQHeads;
+  YAHKV_CUDA(ctx, cudaDeviceGetAttribute(&ctx->n_sm, cudaDevAttrMultiProcessorCount, c.device));
+  if (const char* env = std::getenv("YAHKV_PREFILL_SMS"); env != nullptr)   // tests: split small calls too
+    ctx->n_sm = std::min(std::max(std::atoi(env), 0), ctx->n_sm);
+  ctx->max_tiles = (c.max_batch_tokens / kPrefillTileRows + c.max_seqs) * kQHeads + ctx->n_sm;
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->tiles_dev, static_cast<std::size_t>(ctx->max_tiles), false));
+  if (ctx->n_sm > 0) {
+    YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->merges_dev, static_cast<std::size_t>(ctx->n_sm), false));
+    YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->part_acc_dev, static_cast<std::size_t>(ctx->n_sm) * kPrefillPartAccFloats, false));
+    YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->part_ml_dev, static_cast<std::size_t>(ctx->n_sm) * kPrefillPartMlFloats, false));
+  }
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pseqs_dev, static_cast<std::size_t>(c.max_seqs), false));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->status_dev, 1, true));
   const std::size_t ns = static_cast<std::size_t>(c.max_seqs);
@@ -253,6 +267,7 @@ void FreeDevice(yahkv_ctx* ctx) {
   void* ptrs[] = {ctx->pool.kcodes, ctx->pool.vcodes, ctx->pool.kscales, ctx->pool.vscales, ctx->tables_dev,
                   ctx->slots_dev,   ctx->units_dev,   ctx->items_dev,    ctx->partial_acc,  ctx->partial_ml,
                   ctx->tiles_dev,   ctx->status_dev,  ctx->pseqs_dev, ctx->k16_dev, ctx->v16_dev,
+                  ctx->merges_dev, ctx->part_acc_dev, ctx->part_ml_dev,
                   ctx->rope_tab_dev, ctx->rope_pos_dev};
   for (void* p : ptrs)
     if (p != nullptr) cudaFree(p);
@@ -633,8 +648,10 @@ int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const in
     return Fail(ctx, YAHKV_ERR_INVALID, "attend_prefill: q and out must be 16-byte aligned");
   std::int64_t rows = 0, scratch_rows = 0;
   int max_pages = 0;
-  HostError e = ctx->host.PlanPrefill(layer, n_seqs, seq_ids, chunk_lens, ctx->cfg.max_batch_tokens, &ctx->pseq_scratch,
-                                      &ctx->tile_scratch, &rows, &scratch_rows, &max_pages);
+  int n_parts = 0;
+  HostError e = ctx->host.PlanPrefill(layer, n_seqs, seq_ids, chunk_lens, ctx->cfg.max_batch_tokens, ctx->n_sm,
+                                      &ctx->pseq_scratch, &ctx->tile_scratch, &ctx->merge_scratch, &n_parts, &rows,
+                                      &scratch_rows, &max_pages);
   if (e.code != YAHKV_OK) return FailHost(ctx, std::move(e));
   if (ctx->tile_scratch.empty()) return YAHKV_OK;
   if (static_cast<int>(ctx->tile_scratch.size()) > ctx->max_tiles) return Fail(ctx, YAHKV_ERR_CAPACITY, "attend_prefill: too many tiles");
@@ -657,12 +674,15 @@ int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const in
   if (int r = FlushTables(ctx, st); r != YAHKV_OK) return r;
   {
     const std::size_t sb = ctx->pseq_scratch.size() * sizeof(PrefillSeq), tb = ctx->tile_scratch.size() * sizeof(PrefillTile);
+    const std::size_t mb = ctx->merge_scratch.size() * sizeof(PrefillMerge);
     char* buf = nullptr;
-    YAHKV_CUDA(ctx, ctx->staging.Acquire(sb + tb, &buf));
+    YAHKV_CUDA(ctx, ctx->staging.Acquire(sb + tb + mb, &buf));
     std::memcpy(buf, ctx->pseq_scratch.data(), sb);
     std::memcpy(buf + sb, ctx->tile_scratch.data(), tb);
+    if (mb > 0) std::memcpy(buf + sb + tb, ctx->merge_scratch.data(), mb);
     YAHKV_CUDA(ctx, cudaMemcpyAsync(ctx->pseqs_dev, buf, sb, cudaMemcpyHostToDevice, st));
     YAHKV_CUDA(ctx, cudaMemcpyAsync(ctx->tiles_dev, buf + sb, tb, cudaMemcpyHostToDevice, st));
+    if (mb > 0) YAHKV_CUDA(ctx, cudaMemcpyAsync(ctx->merges_dev, buf + sb + tb, mb, cudaMemcpyHostToDevice, st));
     YAHKV_CUDA(ctx, ctx->staging.Release(st));
   }
   PrefillLaunch a{};
@@ -672,6 +692,8 @@ int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const in
   a.k16_dev = ctx->k16_dev, a.v16_dev = ctx->v16_dev;
   a.q_dev = q_dev, a.k16map = &ctx->k16map, a.v16map = &ctx->v16map;
   a.tiles_dev = ctx->tiles_dev, a.n_tiles = static_cast<int>(ctx->tile_scratch.size());
+  a.merges_dev = ctx->merges_dev, a.n_merges = static_cast<int>(ctx->merge_scratch.size());
+  a.part_acc = ctx->part_acc_dev, a.part_ml = ctx->part_ml_dev;
   a.gate_dev = gate_dev, a.out_dev = out_dev, a.out_f32 = out_dtype == YAHKV_OUT_F32;
   a.scale_log2 = ctx->scale_log2, a.status_dev = ctx->status_dev;
   {
@@ -682,7 +704,7 @@ int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const in
   TimedLaunch tl(ctx, YAHKV_KERNEL_PREFILL, st);
   YAHKV_CUDA(ctx, LaunchPrefill(a, st));
   tl.End();
-  ctx->launches += 2;
+  ctx->launches += a.n_merges > 0 ? 3 : 2;
   return YAHKV_OK;
 }
 
