@@ -7,6 +7,7 @@
 // sequence becomes a batch here, and its fixed one-workgroup-per-page grid becomes a fixed number of split-K units
 // per sequence, reserved for the growth the caller announced; units that hold no page yet exit at once.
 #include "kernels.cuh"
+#include "ptx.cuh"
 
 namespace yahkv {
 namespace {
@@ -16,6 +17,7 @@ __global__ void BatchPlanKernel(const std::int32_t* __restrict__ lens, const Bat
                                 const std::int32_t* __restrict__ tables, int table_stride, int unit_pages,
                                 int num_pages, DecodeUnit* __restrict__ units, CombineItem* __restrict__ items,
                                 std::int64_t* __restrict__ slots) {
+  ChainedKernelEntry();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n_seqs * kKvHeads) return;
   const int b = idx / kKvHeads, h = idx % kKvHeads;
@@ -46,6 +48,7 @@ __global__ void BatchPlanKernel(const std::int32_t* __restrict__ lens, const Bat
 }
 
 __global__ void BatchAdvanceKernel(std::int32_t* __restrict__ lens, int n_seqs, int by) {
+  ChainedKernelEntry();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b < n_seqs) lens[b] += by;
 }
@@ -58,15 +61,13 @@ cudaError_t LaunchBatchPlan(const std::int32_t* lens_dev, const BatchSeq* seqs_d
                             cudaStream_t stream) {
   if (n_seqs <= 0) return cudaSuccess;
   const int threads = n_seqs * kKvHeads;
-  BatchPlanKernel<<<(threads + 127) / 128, 128, 0, stream>>>(lens_dev, seqs_dev, n_seqs, tables_dev, table_stride,
-                                                            unit_pages, num_pages, units_dev, items_dev, slots_dev);
-  return cudaGetLastError();
+  return LaunchChained(BatchPlanKernel, (threads + 127) / 128, 128, 0, stream, lens_dev, seqs_dev, n_seqs, tables_dev,
+                       table_stride, unit_pages, num_pages, units_dev, items_dev, slots_dev);
 }
 
 cudaError_t LaunchBatchAdvance(std::int32_t* lens_dev, int n_seqs, int by, cudaStream_t stream) {
   if (n_seqs <= 0) return cudaSuccess;
-  BatchAdvanceKernel<<<(n_seqs + 127) / 128, 128, 0, stream>>>(lens_dev, n_seqs, by);
-  return cudaGetLastError();
+  return LaunchChained(BatchAdvanceKernel, (n_seqs + 127) / 128, 128, 0, stream, lens_dev, n_seqs, by);
 }
 
 }  // namespace yahkv

@@ -131,6 +131,7 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
                      PoolView pool, int layer, const std::int32_t* __restrict__ tables, int table_stride,
                      const DecodeUnit* __restrict__ units, const __half* __restrict__ q, float scale_log2,
                      float* __restrict__ partial_acc, float* __restrict__ partial_ml, int* status) {
+  ChainedKernelEntry();
   using L = StageLayout<kFmt>;
   using S = SmemLayout<kFmt>;
   extern __shared__ __align__(1024) std::uint8_t smem_raw[];
@@ -486,6 +487,7 @@ __global__ void __launch_bounds__(kHeadDim)
   __shared__ float m_s[kCombineMaxUnits], w_s[kCombineMaxUnits];
   __shared__ float red_s[kHeadDim / 32];
   __shared__ float inv_l;
+  ChainedKernelEntry();
   const int b = blockIdx.x / kQHeads, hh = blockIdx.x % kQHeads;
   const int kvh = hh / kGroup, j = hh % kGroup;
   const CombineItem it = items[b * kKvHeads + kvh];
@@ -542,21 +544,18 @@ cudaError_t LaunchDecodePart(const DecodeLaunch& a, cudaStream_t stream) {
   if (a.n_units <= 0 || a.n_seqs <= 0) return cudaSuccess;
   const auto* q = static_cast<const __half*>(a.q_dev);
   if (a.pool.fmt == kFmtQ8)
-    DecodePartKernel<kFmtQ8><<<a.n_units, kDecodeThreads, DecodeSmemBytes<kFmtQ8>(), stream>>>(
-        *a.kmap, *a.vmap, a.pool, a.layer, a.tables_dev, a.table_stride, a.units_dev, q, a.scale_log2, a.partial_acc,
-        a.partial_ml, a.status_dev);
-  else
-    DecodePartKernel<kFmtQ4><<<a.n_units, kDecodeThreads, DecodeSmemBytes<kFmtQ4>(), stream>>>(
-        *a.kmap, *a.vmap, a.pool, a.layer, a.tables_dev, a.table_stride, a.units_dev, q, a.scale_log2, a.partial_acc,
-        a.partial_ml, a.status_dev);
-  return cudaGetLastError();
+    return LaunchChained(DecodePartKernel<kFmtQ8>, a.n_units, kDecodeThreads, DecodeSmemBytes<kFmtQ8>(), stream, *a.kmap,
+                         *a.vmap, a.pool, a.layer, a.tables_dev, a.table_stride, a.units_dev, q, a.scale_log2,
+                         a.partial_acc, a.partial_ml, a.status_dev);
+  return LaunchChained(DecodePartKernel<kFmtQ4>, a.n_units, kDecodeThreads, DecodeSmemBytes<kFmtQ4>(), stream, *a.kmap,
+                       *a.vmap, a.pool, a.layer, a.tables_dev, a.table_stride, a.units_dev, q, a.scale_log2,
+                       a.partial_acc, a.partial_ml, a.status_dev);
 }
 
 cudaError_t LaunchDecodeCombine(const DecodeLaunch& a, cudaStream_t stream) {
   if (a.n_units <= 0 || a.n_seqs <= 0) return cudaSuccess;
-  DecodeCombineKernel<<<a.n_seqs * kQHeads, kHeadDim, 0, stream>>>(a.items_dev, a.partial_acc, a.partial_ml,
-                                                                  a.gate_dev, a.out_dev, a.out_f32);
-  return cudaGetLastError();
+  return LaunchChained(DecodeCombineKernel, a.n_seqs * kQHeads, kHeadDim, 0, stream, a.items_dev, a.partial_acc,
+                       a.partial_ml, a.gate_dev, a.out_dev, a.out_f32);
 }
 
 }  // namespace yahkv

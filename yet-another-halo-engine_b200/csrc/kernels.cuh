@@ -117,6 +117,19 @@ constexpr int kPrefillPartMlFloats = kPrefillTileRows * 2;
 constexpr int kPartialAccFloats = kGroup * kHeadDim;
 constexpr int kPartialMlFloats = kGroup * 2;
 
+// Launch with programmatic stream serialization allowed: see ChainedKernelEntry in ptx.cuh.
+template <class... Params, class... Args>
+cudaError_t LaunchChained(void (*kernel)(Params...), dim3 grid, dim3 block, std::size_t smem, cudaStream_t stream,
+                          Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr, cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
 cudaError_t LaunchAppend(const PoolView& pool, int layer, int n_tokens, const std::int64_t* slots_dev,
                          const void* k_dev, const void* v_dev, cudaStream_t stream);
 cudaError_t LaunchRopeAppend(const PoolView& pool, int layer, int n_tokens, const std::int64_t* slots_dev,

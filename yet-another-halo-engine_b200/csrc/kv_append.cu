@@ -17,6 +17,7 @@
 #include <cuda_fp16.h>
 
 #include "kernels.cuh"
+#include "ptx.cuh"
 
 namespace yahkv {
 namespace {
@@ -96,6 +97,7 @@ __global__ void __launch_bounds__(kAppendThreads) AppendKernel(PoolView pool, in
                                                                const std::int64_t* __restrict__ slots,
                                                                const __half* __restrict__ k_in,
                                                                const __half* __restrict__ v_in) {
+  ChainedKernelEntry();
   const int token = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int side = warp >> 2, h = warp & 3;
@@ -209,10 +211,8 @@ cudaError_t LaunchAppend(const PoolView& pool, int layer, int n_tokens, const st
   const auto* k = static_cast<const __half*>(k_dev);
   const auto* v = static_cast<const __half*>(v_dev);
   if (pool.fmt == kFmtQ8)
-    AppendKernel<kFmtQ8><<<n_tokens, kAppendThreads, 0, stream>>>(pool, layer, slots_dev, k, v);
-  else
-    AppendKernel<kFmtQ4><<<n_tokens, kAppendThreads, 0, stream>>>(pool, layer, slots_dev, k, v);
-  return cudaGetLastError();
+    return LaunchChained(AppendKernel<kFmtQ8>, n_tokens, kAppendThreads, 0, stream, pool, layer, slots_dev, k, v);
+  return LaunchChained(AppendKernel<kFmtQ4>, n_tokens, kAppendThreads, 0, stream, pool, layer, slots_dev, k, v);
 }
 
 cudaError_t LaunchRopeAppend(const PoolView& pool, int layer, int n_tokens, const std::int64_t* slots_dev,

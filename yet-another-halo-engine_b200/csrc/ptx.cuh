@@ -57,6 +57,16 @@ __device__ __forceinline__ bool MbarWait(std::uint64_t* bar, std::uint32_t parit
   }
 }
 
+// Programmatic dependent launch. A kernel launched with LaunchChained (kernels.cuh) may start while the kernel before
+// it in the stream is still running; ChainedKernelEntry, first thing in the kernel, lets the NEXT kernel be scheduled
+// as soon as every CTA of this one has started, then waits until the kernels before have completed and their writes
+// are visible. Nothing is read or written before it, so the result is that of a plain stream; what overlaps is the
+// launch latency and block scheduling of consecutive small kernels. After a plain launch both are no-ops.
+__device__ __forceinline__ void ChainedKernelEntry() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // True in exactly one lane of a fully converged warp (all 32 lanes must execute it).
 __device__ __forceinline__ bool ElectOne() {
   std::uint32_t e;
