@@ -481,10 +481,11 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
 // thread = output dim. The merge is latency-bound, so the weights are prepared in shared memory first and the loads
 // of the weighted sum are all independent of each other.
 constexpr int kCombineMaxUnits = 1024;
+constexpr int kCombineEarly = 32;   // partial rows fetched before their weights are known
 __global__ void __launch_bounds__(kHeadDim)
     DecodeCombineKernel(const CombineItem* __restrict__ items, const float* __restrict__ partial_acc,
                         const float* __restrict__ partial_ml, const float* __restrict__ gate, void* out, int out_f32) {
-  __shared__ float m_s[kCombineMaxUnits], w_s[kCombineMaxUnits];
+  __shared__ float m_s[kCombineMaxUnits], w_s[kCombineMaxUnits], l_s[kCombineMaxUnits];
   __shared__ float red_s[kHeadDim / 32];
   __shared__ float inv_l;
   ChainedKernelEntry();
@@ -494,13 +495,19 @@ __global__ void __launch_bounds__(kHeadDim)
   const int n = min(it.n_partials, kCombineMaxUnits);   // the planner never exceeds it
   if (n <= 0) return;   // a kv head outside the context's range: its query heads' rows belong to another context
   const float* ml_g = partial_ml + static_cast<std::size_t>(it.first_partial) * kPartialMlFloats + 2 * j;
+  const float* acc_g = partial_acc + static_cast<std::size_t>(it.first_partial) * kPartialAccFloats + j * kHeadDim + threadIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  // overall max
+  // The merge is a chain of dependent global loads (max, weights, weighted sum), so the first rows of the weighted
+  // sum are fetched up front, together with the (max, sum) pairs, and only multiplied once the weights exist.
+  float early[kCombineEarly];
+#pragma unroll
+  for (int i = 0; i < kCombineEarly; ++i)
+    early[i] = i < n ? acc_g[static_cast<std::size_t>(i) * kPartialAccFloats] : 0.0F;
   float mx = -INFINITY;
   for (int i = tid; i < n; i += kHeadDim) {
-    const float m = ml_g[static_cast<std::size_t>(i) * kPartialMlFloats];
-    m_s[i] = m;
-    mx = fmaxf(mx, m);
+    const float2 ml = *reinterpret_cast<const float2*>(ml_g + static_cast<std::size_t>(i) * kPartialMlFloats);
+    m_s[i] = ml.x, l_s[i] = ml.y;
+    mx = fmaxf(mx, ml.x);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFU, mx, o));
@@ -513,13 +520,14 @@ __global__ void __launch_bounds__(kHeadDim)
   __syncthreads();
   if (tid == 0) {   // the sum of the units' sums in unit order (few terms, kept sequential so the result is reproducible)
     float Lsum = 0.0F;
-    for (int i = 0; i < n; ++i) Lsum = fmaf(w_s[i], ml_g[static_cast<std::size_t>(i) * kPartialMlFloats + 1], Lsum);
+    for (int i = 0; i < n; ++i) Lsum = fmaf(w_s[i], l_s[i], Lsum);
     inv_l = 1.0F / Lsum;
   }
-  const float* acc_g = partial_acc + static_cast<std::size_t>(it.first_partial) * kPartialAccFloats + j * kHeadDim + tid;
   float A = 0.0F;
+#pragma unroll
+  for (int i = 0; i < kCombineEarly; ++i) A = fmaf(i < n ? w_s[i] : 0.0F, early[i], A);   // unit order
 #pragma unroll 8
-  for (int i = 0; i < n; ++i) A = fmaf(w_s[i], acc_g[static_cast<std::size_t>(i) * kPartialAccFloats], A);
+  for (int i = kCombineEarly; i < n; ++i) A = fmaf(w_s[i], acc_g[static_cast<std::size_t>(i) * kPartialAccFloats], A);
   __syncthreads();
   float o = A * inv_l;
   const std::size_t oi = (static_cast<std::size_t>(b) * kQHeads + hh) * kHeadDim + tid;
