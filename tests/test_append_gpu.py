@@ -162,3 +162,27 @@ def test_fused_rope_append_is_rope_then_append(fmt):
     assert_pools_equal(cache, 1, pool)
     assert [cache.seq_len(s, 1) for s in seqs] == [133, 4832]
     cache.close()
+
+
+def test_empty_calls_are_accepted_and_launch_nothing():
+    """Zero tokens / zero sequences: every hot call returns success without a launch (the engine queues whatever a
+    scheduling step produced, which may be nothing)."""
+    cache = yahkv.KvCache(n_layers=1, num_pages=4, fmt=yahkv.FMT_Q8_0, max_seqs=2, max_pages_per_seq=2)
+    s = cache.seq_create()
+    cache.seq_reserve(s, 10)
+    x = torch.zeros((1, 24, 256), dtype=torch.float16, device="cuda")
+    xf = torch.zeros((1, 24, 256), dtype=torch.float32, device="cuda")
+    empty_i32, empty_i64 = np.zeros(0, np.int32), np.zeros(0, np.int64)
+    before = cache.launch_count()
+    cache.append(0, empty_i32, empty_i64, x, x)
+    cache.rope_append(0, empty_i32, empty_i64, xf, xf, xf, xf, xf, 1e-6, x)
+    cache.append_slots(0, 0, torch.zeros(1, dtype=torch.int64, device="cuda"), x, x)
+    cache.attend_decode(0, empty_i32, x, x)
+    cache.attend_prefill(0, empty_i32, empty_i32, x, x)
+    cache.sync()
+    assert cache.launch_count() == before and cache.seq_len(s, 0) == 0
+    # and a sequence with no keys yet cannot be attended
+    with pytest.raises(yahkv.YahkvError) as e:
+        cache.attend_decode(0, [s], x, x)
+    assert e.value.code == yahkv.ERR_ORDER
+    cache.close()
