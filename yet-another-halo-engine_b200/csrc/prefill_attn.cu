@@ -542,7 +542,10 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
 }
 
 // Joins the parts of a split tile: out = (sum_i 2^(m_i - M) O_i) / (sum_i 2^(m_i - M) l_i) * sigmoid(gate), parts in
-// order. One CTA per split tile, thread = output dim, looping over the tile's rows.
+// order. One CTA per (split tile, group of 4 rows), thread = output dim; the rows of a group are independent, so their
+// loads overlap (one CTA walking all 128 rows one after the other spent ~2 us of load latency per row).
+constexpr int kMergeRows = 4;
+constexpr int kMergeMaxParts = 4;   // the planner splits a tile into at most four
 __global__ void __launch_bounds__(kHeadDim)
     PrefillMergeKernel(const PrefillMerge* __restrict__ merges, const PrefillTile* __restrict__ tiles,
                        const float* __restrict__ part_acc, const float* __restrict__ part_ml,
@@ -550,19 +553,35 @@ __global__ void __launch_bounds__(kHeadDim)
   const PrefillMerge mg = merges[blockIdx.x];
   const PrefillTile t = tiles[mg.tile_index];
   const int d = threadIdx.x;
-  for (int r = 0; r < t.n_rows; ++r) {
-    float M = -INFINITY;
-    for (int i = 0; i < mg.n_parts; ++i)
-      M = fmaxf(M, part_ml[(static_cast<std::size_t>(t.part + i) * kTileM + r) * 2]);
-    float a = 0.0F, l = 0.0F;
-    for (int i = 0; i < mg.n_parts; ++i) {
-      const std::size_t row = static_cast<std::size_t>(t.part + i) * kTileM + r;
-      const float m = part_ml[row * 2];
-      const float w = m == -INFINITY ? 0.0F : Exp2Fast(m - M);
-      a = fmaf(w, part_acc[row * kHeadDim + d], a);
-      l = fmaf(w, part_ml[row * 2 + 1], l);
+  const int np = min(mg.n_parts, kMergeMaxParts);
+  float acc[kMergeRows][kMergeMaxParts], m[kMergeRows][kMergeMaxParts], l[kMergeRows][kMergeMaxParts];
+#pragma unroll
+  for (int rr = 0; rr < kMergeRows; ++rr) {
+    const int r = blockIdx.y * kMergeRows + rr;
+#pragma unroll
+    for (int i = 0; i < kMergeMaxParts; ++i) {
+      const bool on = i < np && r < t.n_rows;
+      const std::size_t row = static_cast<std::size_t>(t.part + (on ? i : 0)) * kTileM + (on ? r : 0);
+      acc[rr][i] = on ? part_acc[row * kHeadDim + d] : 0.0F;
+      m[rr][i] = on ? part_ml[row * 2] : -INFINITY;
+      l[rr][i] = on ? part_ml[row * 2 + 1] : 0.0F;
     }
-    float o = a / l;
+  }
+#pragma unroll
+  for (int rr = 0; rr < kMergeRows; ++rr) {
+    const int r = blockIdx.y * kMergeRows + rr;
+    if (r >= t.n_rows) break;
+    float M = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kMergeMaxParts; ++i) M = fmaxf(M, m[rr][i]);
+    float a = 0.0F, ls = 0.0F;
+#pragma unroll
+    for (int i = 0; i < kMergeMaxParts; ++i) {
+      const float w = m[rr][i] == -INFINITY ? 0.0F : Exp2Fast(m[rr][i] - M);
+      a = fmaf(w, acc[rr][i], a);
+      ls = fmaf(w, l[rr][i], ls);
+    }
+    float o = a / ls;
     const std::size_t oi = (static_cast<std::size_t>(t.q_row0 + r) * kQHeads + t.head) * kHeadDim + d;
     if (gate != nullptr) o *= 1.0F / (1.0F + expf(-gate[oi]));
     if (out_f32)
@@ -598,7 +617,7 @@ cudaError_t LaunchPrefill(const PrefillLaunch& a, cudaStream_t stream) {
       *a.k16map, *a.v16map, a.tiles_dev, static_cast<const __half*>(a.q_dev), a.gate_dev, a.out_dev, a.out_f32,
       a.scale_log2, a.part_acc, a.part_ml, a.status_dev);
   if (a.n_merges > 0)
-    PrefillMergeKernel<<<a.n_merges, kHeadDim, 0, stream>>>(a.merges_dev, a.tiles_dev, a.part_acc, a.part_ml, a.gate_dev,
+    PrefillMergeKernel<<<dim3(a.n_merges, kTileM / kMergeRows), kHeadDim, 0, stream>>>(a.merges_dev, a.tiles_dev, a.part_acc, a.part_ml, a.gate_dev,
                                                           a.out_dev, a.out_f32);
   return cudaGetLastError();
 }
