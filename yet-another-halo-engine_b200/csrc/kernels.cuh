@@ -109,6 +109,7 @@ struct PrefillMerge {
   std::int32_t tile_index;
   std::int32_t n_parts;
 };
+constexpr int kPrefillMaxParts = 4;   // key ranges a tile is split into at most
 // Partial result of one part: O [128 rows][256] f32 unnormalised, then (max in log2 units, sum) per row.
 constexpr int kPrefillPartAccFloats = kPrefillTileRows * kHeadDim;
 constexpr int kPrefillPartMlFloats = kPrefillTileRows * 2;

@@ -320,9 +320,15 @@ class KvHost {
     merges->clear();
     *n_parts = 0;
     const int n_tiles = static_cast<int>(tiles->size());
-    const int tail = n_sm > 0 && n_tiles > n_sm ? n_tiles % n_sm : 0;
-    if (tail > 0 && 2 * tail <= n_sm) {
-      const int f = std::min(4, n_sm / tail);
+    const int tail = n_sm > 0 ? n_tiles % n_sm : 0;   // a call of fewer tiles than SMs is all tail
+    // Split factor: the tail's tiles cut into f key ranges take ceil(tail f / n_sm) waves of 1 / f tile time each.
+    int f = 1;
+    double best = 1.0;
+    for (int c = 2; c <= kPrefillMaxParts && tail > 0; ++c) {
+      const double cost = static_cast<double>((tail * c + n_sm - 1) / n_sm) / c;
+      if (cost < best - 1e-9) best = cost, f = c;
+    }
+    if (f > 1) {
       const std::vector<PrefillTile> last(tiles->end() - tail, tiles->end());
       tiles->resize(static_cast<std::size_t>(n_tiles - tail));
       for (const PrefillTile& t : last) {

@@ -545,7 +545,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
 // order. One CTA per (split tile, group of 4 rows), thread = output dim; the rows of a group are independent, so their
 // loads overlap (one CTA walking all 128 rows one after the other spent ~2 us of load latency per row).
 constexpr int kMergeRows = 4;
-constexpr int kMergeMaxParts = 4;   // the planner splits a tile into at most four
+constexpr int kMergeMaxParts = kPrefillMaxParts;
 __global__ void __launch_bounds__(kHeadDim)
     PrefillMergeKernel(const PrefillMerge* __restrict__ merges, const PrefillTile* __restrict__ tiles,
                        const float* __restrict__ part_acc, const float* __restrict__ part_ml,

@@ -132,7 +132,7 @@ struct yahkv_ctx {
   std::vector<PrefillTile> tile_scratch;
   std::vector<PrefillMerge> merge_scratch;
   PrefillMerge* merges_dev = nullptr;
-  float* part_acc_dev = nullptr;   // partial results of split prefill tiles: one slot per SM at most
+  float* part_acc_dev = nullptr;   // partial results of split prefill tiles
   float* part_ml_dev = nullptr;
   int n_sm = 0;                    // SMs the prefill planner fills waves of
   std::vector<PrefillSeq> pseq_scratch;
@@ -221,12 +221,14 @@ int InitDevice(yahkv_ctx* ctx) {
   YAHKV_CUDA(ctx, cudaDeviceGetAttribute(&ctx->n_sm, cudaDevAttrMultiProcessorCount, c.device));
   if (const char* env = std::getenv("YAHKV_PREFILL_SMS"); env != nullptr)   // tests: split small calls too
     ctx->n_sm = std::min(std::max(std::atoi(env), 0), ctx->n_sm);
-  ctx->max_tiles = (c.max_batch_tokens / kPrefillTileRows + c.max_seqs) * kQHeads + ctx->n_sm;
+  ctx->max_tiles = (c.max_batch_tokens / kPrefillTileRows + c.max_seqs) * kQHeads + kPrefillMaxParts * ctx->n_sm;
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->tiles_dev, static_cast<std::size_t>(ctx->max_tiles), false));
   if (ctx->n_sm > 0) {
     YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->merges_dev, static_cast<std::size_t>(ctx->n_sm), false));
-    YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->part_acc_dev, static_cast<std::size_t>(ctx->n_sm) * kPrefillPartAccFloats, false));
-    YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->part_ml_dev, static_cast<std::size_t>(ctx->n_sm) * kPrefillPartMlFloats, false));
+    // a tail of up to n_sm - 1 tiles, each in up to kPrefillMaxParts parts (78 MB on 148 SMs)
+    const std::size_t parts = static_cast<std::size_t>(ctx->n_sm) * kPrefillMaxParts;
+    YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->part_acc_dev, parts * kPrefillPartAccFloats, false));
+    YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->part_ml_dev, parts * kPrefillPartMlFloats, false));
   }
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pseqs_dev, static_cast<std::size_t>(c.max_seqs), false));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->status_dev, 1, true));
