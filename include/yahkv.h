@@ -14,10 +14,12 @@
  * Pool layout (per layer, per side K|V; all layers of a side live in one allocation):
  *   codes  [num_pages][4 kv heads][64 tokens][256 B (q8_0) | 128 B (q4_0)]
  *   scales [num_pages][4 kv heads][64 tokens][8] fp16
- * In device memory a q8_0 code byte is held with its sign bit flipped (u = code + 128), which saves the attention
- * kernels an instruction per four codes; yahkv_read_page / yahkv_write_page / yahkv_export_token and the snapshot
- * files translate, so everything outside the device sees GGUF's int8 codes. Only yahkv_attend_decode_noalloc, which
- * is handed device pools directly, sees the device form. q4_0 bytes are GGUF's as they are.
+ * In device memory the q8_0 K codes are GGUF's int8 bytes as they are (the attention kernel feeds them to the integer
+ * tensor-core MMA untouched); a q8_0 V code byte is held with its sign bit flipped (u = code + 128), which saves the
+ * attention kernels an instruction per four codes. yahkv_read_page / yahkv_write_page / yahkv_export_token and the
+ * snapshot files translate, so everything outside the device sees GGUF's int8 codes. Only
+ * yahkv_attend_decode_noalloc, which is handed device pools directly, sees the device form. q4_0 bytes are GGUF's as
+ * they are.
  * slot(pos) = table[pos / 64] * 64 + pos % 64 (the reference's rule with 256 -> 64,
  * engine/gpu/loom/tools/gen_decode_attn.py:5, :64-72). One block table per sequence is shared by all layers
  * (docs/architecture.md:212).
@@ -209,6 +211,18 @@ int yahkv_snapshot_load(yahkv_ctx* ctx, const char* path, int32_t* seq_ids_out, 
 int yahkv_device_bytes(const yahkv_ctx* ctx, int64_t* bytes);
 int yahkv_launch_count(const yahkv_ctx* ctx, int64_t* launches);
 
+/* ---- test hooks ------------------------------------------------------------------------------------------------
+ * yahkv_debug_wait_timeout runs the give-up path of the library's bounded device waits on purpose: one small kernel
+ * waits at most limit_us microseconds (1 .. 1,000,000) on a barrier nobody arrives at, stops waiting, records the
+ * sticky status word and returns, so the next yahkv_sync fails with YAHKV_ERR_CUDA and clears it. The reference bounds
+ * its device-side polls the same way and leaves a sticky status (engine/gpu/loom/tools/gen_chain.py:12-19). Nothing
+ * traps or faults, the context stays usable.
+ * yahkv_debug_set_prefill_sms sets the number of SMs whose last partly filled wave the prefill planner splits along
+ * the keys (0 = never split, at most the device's count, which is the default), so a small test reaches the split
+ * and merge path. */
+int yahkv_debug_wait_timeout(yahkv_ctx* ctx, int64_t limit_us, void* stream);
+int yahkv_debug_set_prefill_sms(yahkv_ctx* ctx, int32_t n_sm);
+
 /* Per-kernel device time for benchmarks: while enabled, every launch is bracketed by a CUDA event pair on its own
  * stream (the reference's counterpart is its per-dispatch timer, engine/run/hal_run.cc:124-135). Enabling or
  * disabling clears the record. _read waits for the device and sums the pairs of one kernel. */
@@ -264,6 +278,13 @@ typedef struct yahkv_noalloc_args {
   void* stream;              /* cudaStream_t; NULL = the default stream */
 } yahkv_noalloc_args;
 int yahkv_attend_decode_noalloc(const yahkv_noalloc_args* args, char* err, int32_t err_cap);
+/* The error channel of the call above, equally allocation-free (no counterpart in the reference): queues on `stream`
+ * an asynchronous copy of the static array's status word into *status_host, which the caller owns (page-locked memory
+ * if the copy is to be truly asynchronous). Once the stream has reached the copy, 0 means every yahkv_attend_decode_noalloc
+ * ordered before it on this device ran to completion; non-zero means a kernel gave up a bounded wait and the outputs
+ * of the last call are invalid. The next call clears the word. Fails with YAHKV_ERR_ORDER before the first
+ * yahkv_attend_decode_noalloc on the device (the array's address is resolved there). */
+int yahkv_noalloc_status(int32_t* status_host, void* stream);
 
 #ifdef __cplusplus
 }

@@ -28,10 +28,11 @@ def test_library_exports_every_declared_symbol():
 
 def test_config_is_validated():
     for bad in (dict(n_q_heads=32), dict(head_dim=128), dict(page_tokens=256), dict(fmt=7), dict(num_pages=0),
-                dict(n_layers=0), dict(max_seqs=0), dict(num_pages=1 << 24, n_layers=64)):
+                dict(n_layers=0), dict(max_seqs=0), dict(num_pages=1 << 24, n_layers=64), dict(max_splits=1025)):
         with pytest.raises(yahkv.YahkvError) as e:
             host_ctx(**bad)
         assert e.value.code == yahkv.ERR_INVALID
+    host_ctx(max_splits=1024).close()        # the combine kernel's limit itself is accepted
 
 
 def test_allocator_is_lifo_and_recycles():

@@ -126,15 +126,15 @@ def test_full_size_chunk_properties():
     cache.close()
 
 
-def test_tail_tiles_split_along_the_keys(monkeypatch):
+def test_tail_tiles_split_along_the_keys():
     """With 20 SMs to fill, the 48 tiles of this call leave a last wave of 8: those are split into two key ranges each
     and joined by the merge kernel (three launches instead of two). Results against the oracle, gate and fp16 output
     included, and against the unsplit run."""
     cached, chunk = 500, 129
     runs = []
-    for sms in ("0", "20"):
-        monkeypatch.setenv("YAHKV_PREFILL_SMS", sms)
+    for sms in (0, 20):
         cache, pool, seqs, tables, rng = build(yahkv.FMT_Q8_0, [cached], [chunk], seed=46)
+        cache.debug_set_prefill_sms(sms)
         q = rng.standard_normal((chunk, 24, 256)).astype(np.float16)
         gate = rng.standard_normal((chunk, 24, 256)).astype(np.float32)
         before = cache.launch_count()

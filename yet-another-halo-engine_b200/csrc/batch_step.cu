@@ -53,7 +53,25 @@ __global__ void BatchAdvanceKernel(std::int32_t* __restrict__ lens, int n_seqs, 
   if (b < n_seqs) lens[b] += by;
 }
 
+// A wait that cannot succeed: the barrier expects one arrival and nobody arrives. The kernel leaves by the same path
+// a real kernel takes when a copy never lands: it stops waiting at the limit, sets the sticky status word, returns.
+__global__ void WaitProbeKernel(int* status, std::uint64_t limit_ns) {
+  __shared__ std::uint64_t bar;
+  if (threadIdx.x == 0) {
+    MbarInit(&bar, 1);
+    FenceBarrierInit();
+  }
+  __syncthreads();
+  const bool ok = MbarWait(&bar, 0, limit_ns);
+  if (!ok && threadIdx.x == 0) atomicExch(status, kStatusWaitTimeout);
+}
+
 }  // namespace
+
+cudaError_t LaunchWaitProbe(int* status_dev, std::uint64_t limit_ns, cudaStream_t stream) {
+  WaitProbeKernel<<<1, 32, 0, stream>>>(status_dev, limit_ns);
+  return cudaGetLastError();
+}
 
 cudaError_t LaunchBatchPlan(const std::int32_t* lens_dev, const BatchSeq* seqs_dev, int n_seqs,
                             const std::int32_t* tables_dev, int table_stride, int unit_pages, int num_pages,

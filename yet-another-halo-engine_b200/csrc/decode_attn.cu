@@ -19,18 +19,26 @@
 // is bound by instruction latency, not by HBM.
 //
 // The path is HBM-bound (2176 B per token per layer in q8_0), but at GQA 6 it needs 5.6 multiply-adds per byte, more
-// than the fp32 pipes can give at HBM rate, so the dot products run on the warp-level f16 tensor-core MMA with
-// register operands (dequantization stays in registers): codes become exact f16 integers by a byte permute and a
-// magic-number subtract, the products accumulate in fp32 per 32-element block, and the block's fp16 scale multiplies
-// the block sum in fp32. For P.V the per-(key, block) V scale is folded into the weights, which are split into an
-// f16 high and low part (two MMAs) so the weights keep ~22 bits: a single f16 weight would cost up to 3e-3 absolute
-// error on outlier channels.
+// than the fp32 pipes can give at HBM rate, so the dot products run on the warp-level tensor-core MMA with register
+// operands, and what limits the kernel next is the number of instructions issued per byte. The two products are
+// treated differently for that reason:
+//   Q.K^T runs on the integer MMA (m16n8k32, s8 x s8 -> s32) straight on the cached codes: a 32-element block is
+//   exactly one k-step, ldmatrix delivers the code bytes in the B operand's register layout, and nothing is converted
+//   (q4_0: three logic instructions turn eight nibbles into the int8 values 16 (n - 8)). The query row is quantized
+//   once per CTA to 16 bits against its head's largest magnitude and split into two int8 planes, hi and lo
+//   (q = s (256 hi + lo), |error| <= s / 2 = amax / 64000 per element, far below the fp16 query's own spacing).
+//   Both planes ride in one MMA as rows 0-5 and 8-13 of the 16-row A operand, so one instruction gives the exact
+//   block sums of both; they are joined in integers, converted once, and multiplied by the block's fp16 scale in
+//   fp32.
+//   P.V stays on the f16 MMA: V codes become exact f16 integers by a byte permute and a magic-number subtract, and
+//   the per-(key, block) V scale is folded into the weights, which are split into an f16 high and low part (two
+//   MMAs) so the weights keep ~22 bits: a single f16 weight would cost up to 3e-3 absolute error on outlier channels.
 //
-// MMA orientation. S^T[head][key] = Q[head][dim] . K[key][dim]: A = Q (rows 0-5 real heads, the rest zero), B = K^T
+// MMA orientation. S^T[head][key] = Q[head][dim] . K[key][dim]: A = Q (hi and lo planes of the six heads), B = K^T
 // read with ldmatrix straight from the token-major page. O^T[dim][head] = V^T[dim][key] . P^T[key][head]: A = V^T read
 // with ldmatrix.trans from the same token-major layout, B = the weights, which the first MMA left in exactly the
-// register layout the second one wants. The dims inside a 16-wide MMA step are a fixed permutation of the page's
-// dims; Q is loaded with the same permutation, so the dot products are unchanged.
+// register layout the second one wants. The dims inside a 16-wide step of the second MMA are a fixed permutation of
+// the page's dims, undone when the accumulators are written out.
 #include <cuda_fp16.h>
 
 #include <cmath>
@@ -78,32 +86,31 @@ __device__ __forceinline__ float ScaleOf(const uint2& v, int i) {
   return (i & 1) ? __high2float(h) : __low2float(h);
 }
 
-// One S^T MMA step with a zero accumulator input: no register has to be cleared beforehand. The Q fragment of the
-// step comes from shared memory at use (volatile, so the compiler does not keep all fragments in registers), stored
-// there as the A operand's four registers (rows 8-15 of A, registers 1 and 3, are zero) so one 16-byte load fills
-// them without any register shuffling.
-__device__ __forceinline__ void MmaQZero(float (&d)[4], std::uint32_t q_addr, std::uint32_t b0, std::uint32_t b1) {
+// One S^T step on the integer tensor pipe: D(16 x 8, s32) = A(16 x 32, s8) . B(32 x 8, s8), accumulator input zero.
+// A = the query planes of one 32-element block, fetched from shared memory at use as the operand's four registers
+// (one 16-byte load, no shuffling); B = the code bytes of eight keys as ldmatrix left them.
+__device__ __forceinline__ void MmaQK(int (&d)[4], std::uint32_t q_addr, std::uint32_t b0, std::uint32_t b1) {
   std::uint32_t a0, a1, a2, a3;
   asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(q_addr));
   asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
       "{%10, %10, %10, %10};"
-      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0F));
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
-// The same step accumulating in place.
-__device__ __forceinline__ void MmaQ(float (&d)[4], std::uint32_t q_addr, std::uint32_t b0, std::uint32_t b1) {
-  std::uint32_t a0, a1, a2, a3;
-  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(q_addr));
-  MmaF16(d, a0, a1, a2, a3, b0, b1);
-}
+// The block sum of one (head, key): the hi plane's sum times 256 plus the lo plane's, exact in 32 bits
+// (|sum| <= 32 x 128 x 32768), as a float.
+__device__ __forceinline__ float JoinPlanes(int hi, int lo) { return static_cast<float>(hi * 256 + lo); }
+
+// Query quantization: 16 bits against the head's largest magnitude. 32000 keeps the hi plane inside [-125, 125].
+constexpr float kQSteps = 32000.0F;
 
 // Shared memory of a CTA, all dynamic so that the ring starts at the window's 1024-byte aligned base (the swizzled
-// TMA boxes need that alignment): ring | Q operands | score exchange | mbarriers | stage counters. Lanes 24-31 of a
-// warp hold the two padding heads of the 8-wide MMA; they reuse the Q operands of lanes 16-23 (finite duplicates of
-// heads 4, 5 whose results are never stored), so the Q and exchange arrays are 24 lanes wide.
+// TMA boxes need that alignment): ring | Q operands | score exchange | mbarriers | stage counters | query scales |
+// abort flag. Lanes 24-31 of a warp hold the two padding heads of the 8-wide MMA; they reuse the Q operands of lanes
+// 16-23 (duplicates of heads 4, 5 whose results are never stored), so the Q and exchange arrays are 24 lanes wide.
 constexpr int kQLanes = 24;
-constexpr int kQfragBytes = 16 * kQLanes * 16;
+constexpr int kQfragBytes = kBlocksPerRow * kQLanes * 16;   // per 32-element block the A operand's four registers
 constexpr int kXchgBytes = kWarps * kQLanes * 16;
 template <int kFmt>
 struct SmemLayout {
@@ -113,7 +120,10 @@ struct SmemLayout {
   static constexpr int kXchgOff = kQfragOff + kQfragBytes;
   static constexpr int kBarOff = kXchgOff + kXchgBytes;
   static constexpr int kCntOff = kBarOff + 8 * StageLayout<kFmt>::kStages;
-  static constexpr int kBytes = kCntOff + 4 * StageLayout<kFmt>::kStages;
+  static constexpr int kFillOff = kCntOff + 4 * StageLayout<kFmt>::kStages;     // fills issued per stage
+  static constexpr int kQScaleOff = kFillOff + 4 * StageLayout<kFmt>::kStages;  // [8] f32, one per head (6 used)
+  static constexpr int kAbortOff = kQScaleOff + 4 * 8;
+  static constexpr int kBytes = kAbortOff + 4;
 };
 template <int kFmt>
 constexpr int DecodeSmemBytes() {
@@ -136,10 +146,13 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
   using S = SmemLayout<kFmt>;
   extern __shared__ __align__(1024) std::uint8_t smem_raw[];
   std::uint8_t* ring = smem_raw;
-  uint4* qfrag = reinterpret_cast<uint4*>(smem_raw + S::kQfragOff);     // Q as MMA A operands [16 steps][24 lanes]
+  std::uint32_t* qfrag = reinterpret_cast<std::uint32_t*>(smem_raw + S::kQfragOff);   // [8 blocks][24 lanes][4]
   float4* xchg = reinterpret_cast<float4*>(smem_raw + S::kXchgOff);     // partial scores [8 warps][24 lanes]
   std::uint64_t* full_bar = reinterpret_cast<std::uint64_t*>(smem_raw + S::kBarOff);
   int* done_cnt = reinterpret_cast<int*>(smem_raw + S::kCntOff);        // warps done reading a stage's page
+  int* fill_cnt = reinterpret_cast<int*>(smem_raw + S::kFillOff);       // fills issued to a stage so far
+  float* q_scale = reinterpret_cast<float*>(smem_raw + S::kQScaleOff);  // query quantization step per head
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + S::kAbortOff);   // a wait gave up
   if ((SmemAddr(smem_raw) & 1023U) != 0) {   // never seen; checked because a misaligned swizzle would corrupt results
     if (threadIdx.x == 0) atomicExch(status, kStatusSmemMisaligned);
     return;
@@ -156,12 +169,16 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
   // Gather of one page into a ring stage: 2 TMA boxes per side (q8_0; 1 for q4_0) + the two scale records, all
   // completing on the stage's mbarrier. Called by a whole converged warp with warp-uniform arguments; one elected
   // lane issues (asynchronous copies issued from inside a single-lane branch cost several times more issue time).
+  // Once any warp has given up a wait nothing more is fetched: the CTA is on its way out and must not leave copies
+  // in flight behind it.
   auto issue = [&](int s, std::int32_t page) {
+    if (*abort_flag != 0) return;
     page = min(max(page, 0), pool.num_pages - 1);   // never trust a table entry read from memory
     const std::size_t rec = (static_cast<std::size_t>(layer) * pool.num_pages + page) * kKvHeads + u.kvh;
     const int y = static_cast<int>(rec * kPageTokens);
     std::uint8_t* st = ring + s * L::kBytes;
     if (ElectOne()) {
+      fill_cnt[s] += 1;
       MbarArriveExpectTx(&full_bar[s], L::kBytes);
 #pragma unroll
       for (int b = 0; b < L::kBoxesPerSide; ++b) {
@@ -180,7 +197,9 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
       for (int s = 0; s < L::kStages; ++s) {
         MbarInit(&full_bar[s], 1);
         done_cnt[s] = 0;
+        fill_cnt[s] = 0;
       }
+      *abort_flag = 0;
       FenceBarrierInit();
     }
     __syncwarp();
@@ -188,24 +207,51 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
   }
 
   const int g = lane >> 2, t = lane & 3;
-  // Q fragments through shared memory: MMA step c (16 dims) uses dims 16c + 4t + {0, 2} in k-slots (2t, 2t+1) and
-  // + {1, 3} in (2t+8, 2t+9).
-  {
-    const __half* qrow = q + (static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + g) * kHeadDim;
+  // Query planes through shared memory. Warp h < 6 quantizes head h of the group: lane l holds dims 8 l .. 8 l + 7
+  // (block l / 4, elements 8 (l % 4) .. + 7 of it). q16 = rint(q * 32000 / amax), hi = (q16 + 128) >> 8,
+  // lo = q16 - 256 hi in [-128, 127]. The A operand of block b for lane (g = head, t) is four registers:
+  //   a0 = hi of elements 4t .. 4t+3, a1 = lo of the same, a2 = hi of elements 16+4t .. 16+4t+3, a3 = lo of those,
+  // so that rows 0-5 of the MMA are the hi plane and rows 8-13 the lo plane of the six heads.
+  if (warp < kGroup) {
+    const __half* qrow = q + (static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + warp) * kHeadDim;
+    const uint4 raw = *reinterpret_cast<const uint4*>(qrow + 8 * lane);
+    const __half2* hp = reinterpret_cast<const __half2*>(&raw);
+    float x[8];
+    float amax = 0.0F;
 #pragma unroll
-    for (int cc = 0; cc < 16 / kWarps; ++cc) {
-      const int c = warp * (16 / kWarps) + cc;
-      if (g < kGroup) {
-        const uint2 v = *reinterpret_cast<const uint2*>(qrow + 16 * c + 4 * t);
-        qfrag[c * kQLanes + lane] = make_uint4(__byte_perm(v.x, v.y, 0x5410), 0U,   // halves (0, 2)
-                                               __byte_perm(v.x, v.y, 0x7632), 0U);  // halves (1, 3)
-      }
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(hp[i]);
+      x[2 * i] = f.x, x[2 * i + 1] = f.y;
+      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFU, amax, o));
+    const float inv = amax > 0.0F ? kQSteps / amax : 0.0F;
+    std::uint32_t hi_w[2] = {0, 0}, lo_w[2] = {0, 0};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int q16 = __float2int_rn(x[i] * inv);
+      const int hi = (q16 + 128) >> 8;
+      const int lo = q16 - hi * 256;
+      hi_w[i >> 2] |= (static_cast<std::uint32_t>(hi) & 0xFFU) << (8 * (i & 3));
+      lo_w[i >> 2] |= (static_cast<std::uint32_t>(lo) & 0xFFU) << (8 * (i & 3));
+    }
+    const int blk = lane >> 2, e0 = (lane & 3) * 8;
+    const int reg = e0 < 16 ? 0 : 2, t0 = (e0 & 15) >> 2;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      std::uint32_t* dst = qfrag + ((blk * kQLanes + warp * 4 + t0 + j) << 2) + reg;
+      dst[0] = hi_w[j];
+      dst[1] = lo_w[j];
+    }
+    // q = step (256 hi + lo); q4_0 codes enter the MMA as 16 (n - 8), which the step absorbs
+    if (lane == 0) q_scale[warp] = (amax / kQSteps) * (kFmt == kFmtQ8 ? 1.0F : 0.0625F);
   }
-  __syncthreads();   // barriers initialised, Q fragments visible
-  // This warp's eight MMA steps are c = 8 dh .. 8 dh + 7.
+  __syncthreads();   // barriers initialised, query planes visible
+  // This warp's four blocks are 4 dh .. 4 dh + 3.
   const int qlane = lane < kQLanes ? lane : lane - 8;
-  const std::uint32_t qa_addr = SmemAddr(qfrag + 8 * dh * kQLanes + qlane);
+  const std::uint32_t qa_addr = SmemAddr(qfrag + ((4 * dh * kQLanes + qlane) << 2));
+  const float score_scale = scale_log2 * q_scale[qlane >> 2];   // softmax scale x log2(e) x the head's query step
 
   float o_acc[8][4];   // tile c2 = dims 128 dh + 16 c2 .. + 15
 #pragma unroll
@@ -234,13 +280,17 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
     std::int32_t refill_page = 0;
     if (lane == 0 && i + L::kStages < n_pages) refill_page = __ldg(row + i + L::kStages);
     // A wait that gives up does not leave the loop (its partner warp would hang at the pair barrier): the warp stops
-    // waiting, finishes on whatever the ring holds, and the status word marks the call's results invalid.
-    if (alive && !__all_sync(0xFFFFFFFFU, MbarWait(&full_bar[s], phase))) alive = false;
+    // waiting, raises the CTA's abort flag so that nothing more is fetched, finishes on whatever the ring holds, and
+    // the status word marks the call's results invalid.
+    if (alive && (*abort_flag != 0 || !__all_sync(0xFFFFFFFFU, MbarWait(&full_bar[s], phase)))) {
+      alive = false;
+      *abort_flag = 1;
+    }
     const std::uint8_t* st = ring + s * L::kBytes;
     const std::uint32_t k_base = SmemAddr(st + L::kKOff) + half_off, v_base = SmemAddr(st + L::kVOff) + half_off;
 
-    // ---- S^T = Q K^T over this warp's 128 dims: per 32-element block an fp32 partial sum of exact products, times
-    // the block's fp16 scale ----
+    // ---- S^T = Q K^T over this warp's 128 dims: per 32-element block the exact integer sums of the two query
+    // planes, joined, converted once, times the block's fp16 scale ----
     float sc[2][2] = {{0.0F, 0.0F}, {0.0F, 0.0F}};
     {
       uint2 ks_raw[2][2];   // scales of blocks 4 dh .. 4 dh + 3 of this thread's four keys
@@ -250,27 +300,23 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
         for (int j = 0; j < 2; ++j)
           ks_raw[kt][j] = *reinterpret_cast<const uint2*>(st + L::kKsOff + (my_key0 + kt * 8 + j) * 16 + dh * 8);
       if constexpr (kFmt == kFmtQ8) {
+        // One ldmatrix.x4 = one block of 16 keys: registers 0 / 2 are the two 16-byte halves of keys 0-7 (the B
+        // operand's k 0-15 and 16-31), registers 1 / 3 those of keys 8-15.
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
           std::uint32_t w[4];
           LdMatrixX4(k_base + lm_off[b], w);
-          float a0[4], a1[4];
-          std::uint32_t x0, x1;
-          Offset8x4ToHalf2(w[0], x0, x1);
-          MmaQZero(a0, qa_addr + (2 * b) * (kQLanes * 16), x0, x1);
-          Offset8x4ToHalf2(w[1], x0, x1);
-          MmaQZero(a1, qa_addr + (2 * b) * (kQLanes * 16), x0, x1);
-          Offset8x4ToHalf2(w[2], x0, x1);
-          MmaQ(a0, qa_addr + (2 * b + 1) * (kQLanes * 16), x0, x1);
-          Offset8x4ToHalf2(w[3], x0, x1);
-          MmaQ(a1, qa_addr + (2 * b + 1) * (kQLanes * 16), x0, x1);
-          sc[0][0] = fmaf(ScaleOf(ks_raw[0][0], b), a0[0], sc[0][0]);
-          sc[0][1] = fmaf(ScaleOf(ks_raw[0][1], b), a0[1], sc[0][1]);
-          sc[1][0] = fmaf(ScaleOf(ks_raw[1][0], b), a1[0], sc[1][0]);
-          sc[1][1] = fmaf(ScaleOf(ks_raw[1][1], b), a1[1], sc[1][1]);
+          int a0[4], a1[4];
+          MmaQK(a0, qa_addr + b * (kQLanes * 16), w[0], w[2]);
+          MmaQK(a1, qa_addr + b * (kQLanes * 16), w[1], w[3]);
+          sc[0][0] = fmaf(ScaleOf(ks_raw[0][0], b), JoinPlanes(a0[0], a0[2]), sc[0][0]);
+          sc[0][1] = fmaf(ScaleOf(ks_raw[0][1], b), JoinPlanes(a0[1], a0[3]), sc[0][1]);
+          sc[1][0] = fmaf(ScaleOf(ks_raw[1][0], b), JoinPlanes(a1[0], a1[2]), sc[1][0]);
+          sc[1][1] = fmaf(ScaleOf(ks_raw[1][1], b), JoinPlanes(a1[1], a1[3]), sc[1][1]);
         }
       } else {
-        // One ldmatrix.x4 covers two 16-byte blocks of 16 keys.
+        // One ldmatrix.x4 covers two 16-byte blocks of 16 keys; a thread's word is bytes 4t .. 4t+3 of a block, i.e.
+        // elements 4t .. 4t+3 in the low nibbles (k 4t ..) and 16+4t .. in the high ones (k 16+4t ..).
 #pragma unroll
         for (int bp = 0; bp < 2; ++bp) {
           std::uint32_t w[4];
@@ -278,18 +324,16 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
 #pragma unroll
           for (int hb = 0; hb < 2; ++hb) {
             const int b = 2 * bp + hb;   // block 4 dh + b
-            float a0[4], a1[4];
-            std::uint32_t l0, l1, h0, h1;
-            Nib4x4ToHalf2(w[2 * hb], l0, l1, h0, h1);
-            MmaQZero(a0, qa_addr + (2 * b) * (kQLanes * 16), l0, l1);
-            MmaQ(a0, qa_addr + (2 * b + 1) * (kQLanes * 16), h0, h1);
-            Nib4x4ToHalf2(w[2 * hb + 1], l0, l1, h0, h1);
-            MmaQZero(a1, qa_addr + (2 * b) * (kQLanes * 16), l0, l1);
-            MmaQ(a1, qa_addr + (2 * b + 1) * (kQLanes * 16), h0, h1);
-            sc[0][0] = fmaf(ScaleOf(ks_raw[0][0], b), a0[0], sc[0][0]);
-            sc[0][1] = fmaf(ScaleOf(ks_raw[0][1], b), a0[1], sc[0][1]);
-            sc[1][0] = fmaf(ScaleOf(ks_raw[1][0], b), a1[0], sc[1][0]);
-            sc[1][1] = fmaf(ScaleOf(ks_raw[1][1], b), a1[1], sc[1][1]);
+            int a0[4], a1[4];
+            std::uint32_t lo, hi;
+            Nib8ToInt8(w[2 * hb], lo, hi);
+            MmaQK(a0, qa_addr + b * (kQLanes * 16), lo, hi);
+            Nib8ToInt8(w[2 * hb + 1], lo, hi);
+            MmaQK(a1, qa_addr + b * (kQLanes * 16), lo, hi);
+            sc[0][0] = fmaf(ScaleOf(ks_raw[0][0], b), JoinPlanes(a0[0], a0[2]), sc[0][0]);
+            sc[0][1] = fmaf(ScaleOf(ks_raw[0][1], b), JoinPlanes(a0[1], a0[3]), sc[0][1]);
+            sc[1][0] = fmaf(ScaleOf(ks_raw[1][0], b), JoinPlanes(a1[0], a1[2]), sc[1][0]);
+            sc[1][1] = fmaf(ScaleOf(ks_raw[1][1], b), JoinPlanes(a1[1], a1[3]), sc[1][1]);
           }
         }
       }
@@ -314,7 +358,7 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
     for (int kt = 0; kt < 2; ++kt)
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        sc[kt][j] *= scale_log2;
+        sc[kt][j] *= score_scale;
         if (key_pos0 + kt * 8 + j >= u.n_keys) sc[kt][j] = -INFINITY;   // only ever true on a sequence's last page
         tmax = fmaxf(tmax, sc[kt][j]);
       }
@@ -430,6 +474,15 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
 
   // Every stage has been consumed (or a wait gave up): the ring is free to hold the merge scratch.
   __syncthreads();
+  if (*abort_flag != 0) {   // the same value in every thread now
+    // On the way out after a wait gave up: the copies this CTA still has in flight get one more bounded wait each
+    // (the fill counters say which phase of which stage is outstanding), so that none lands in shared memory that
+    // is being reused. The unit's partial is still written; the status word invalidates the call.
+    if (threadIdx.x == 0)
+      for (int x = 0; x < L::kStages; ++x)
+        if (fill_cnt[x] > 0) MbarWait(&full_bar[x], static_cast<std::uint32_t>(fill_cnt[x] - 1) & 1U, 20000000ULL);
+    __syncthreads();
+  }
   float* merge = reinterpret_cast<float*>(ring);
   {
     float* mine = merge + kw * kMergeGroupFloats + 128 * dh;
@@ -480,7 +533,6 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
 // w_i = 2^(m_i - M), accumulated in unit order (engine/gpu/loom/tools/gen_decode_attn.py:373-408). One CTA per head,
 // thread = output dim. The merge is latency-bound, so the weights are prepared in shared memory first and the loads
 // of the weighted sum are all independent of each other.
-constexpr int kCombineMaxUnits = 1024;
 constexpr int kCombineEarly = 32;   // partial rows fetched before their weights are known
 __global__ void __launch_bounds__(kHeadDim)
     DecodeCombineKernel(const CombineItem* __restrict__ items, const float* __restrict__ partial_acc,

@@ -20,6 +20,9 @@
 // call's contents; everything a call reads it first rewrites (the planner rewrites the units and combine items, each
 // unit rewrites its partial), and the status word is cleared by the planner.
 //
+// Errors. A kernel that gives up a bounded wait records it in the array's status word; yahkv_noalloc_status copies
+// that word into the caller's host memory with one asynchronous copy on the caller's stream (no allocation either).
+//
 // First call on a device. The array's name in host code is only a handle, not a device address, so the first call on
 // each device resolves its address with cudaGetSymbolAddress (and raises the kernels' shared-memory limit). That
 // set-up call should happen before any stream capture begins.
@@ -71,7 +74,8 @@ __global__ void NoAllocPlanKernel(unsigned char* scratch, const std::int32_t* __
     DecodeUnit u;
     u.batch = b, u.seq = b, u.kvh = h;
     u.page_begin = min(k * per, pages);
-    u.page_end = min((k + 1) * per, pages);          // empty past nu: such a unit writes (max -inf, sum 0, acc 0)
+    u.page_end = min((k + 1) * per, pages);          // empty past nu: such a unit exits without writing anything,
+                                                     // and the combine item above (n_partials = nu) never reads it
     u.n_keys = n;
     u.partial = first + k;
     u.pad = 0;
@@ -201,4 +205,19 @@ extern "C" int yahkv_attend_decode_noalloc(const yahkv_noalloc_args* a, char* er
   if (e == cudaSuccess) e = LaunchDecodeCombine(l, stream);
   if (e != cudaSuccess) return Refuse(err, err_cap, YAHKV_ERR_CUDA, cudaGetErrorString(e));
   return YAHKV_OK;
+}
+
+extern "C" int yahkv_noalloc_status(int32_t* status_host, void* stream) {
+  if (status_host == nullptr) return YAHKV_ERR_INVALID;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return YAHKV_ERR_NO_DEVICE;
+  unsigned char* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (!g_setup[dev].done) return YAHKV_ERR_ORDER;   // the address is resolved by the first attend call
+    scratch = g_setup[dev].scratch;
+  }
+  const cudaError_t e = cudaMemcpyAsync(status_host, scratch + kStatusOff, sizeof(int32_t), cudaMemcpyDeviceToHost,
+                                        static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? YAHKV_OK : YAHKV_ERR_CUDA;
 }

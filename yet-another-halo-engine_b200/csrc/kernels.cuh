@@ -26,13 +26,17 @@ constexpr int kRecordScaleBytes = kPageTokens * kBlocksPerRow * 2;
 
 // The pools of one context. Codes are addressed both by pointer (append, inspection) and through 2-D tensor maps
 // whose rows are token rows of CodeBytes(fmt) bytes (attention's gathers).
-// Device representation of q8_0 codes: every code byte is stored with its sign bit flipped, u = code + 128
-// (offset binary), so that the attention kernels turn a byte into the fp16 integer with one byte-permute and one
-// subtract instead of three instructions. Everything that leaves the device (yahkv_read_page, yahkv_export_token,
-// snapshots) or enters it (yahkv_write_page, snapshot load) flips the bit back, so hosts and files see GGUF's int8
-// codes. q4_0 nibbles are unsigned already and are stored as GGUF has them.
+// Device representation of q8_0 codes. K codes are GGUF's int8 bytes as they are: the attention kernel feeds them
+// to the integer MMA without touching them. V codes are stored with the sign bit flipped, u = code + 128 (offset
+// binary), so that the attention kernel turns a byte into the fp16 integer with one byte-permute and one subtract
+// instead of three instructions. Everything that leaves the device (yahkv_read_page, yahkv_export_token,
+// snapshots) or enters it (yahkv_write_page, snapshot load) flips the V bytes back, so hosts and files see GGUF's
+// int8 codes on both sides. q4_0 nibbles are unsigned already and are stored as GGUF has them.
 constexpr std::uint32_t kQ8FlipWord = 0x80808080U;
 constexpr int kQ8FlipByte = 0x80;
+// The flip of one side (0 = K, 1 = V) of a q8_0 pool, as a byte and as a word of four codes.
+__host__ __device__ constexpr int Q8FlipByte(int side) { return side == 0 ? 0 : kQ8FlipByte; }
+__host__ __device__ constexpr std::uint32_t Q8FlipWord(int side) { return side == 0 ? 0U : kQ8FlipWord; }
 
 struct PoolView {
   std::uint8_t* kcodes;
@@ -117,6 +121,9 @@ constexpr int kPrefillPartMlFloats = kPrefillTileRows * 2;
 // Partial workspace per unit: acc [6][256] f32 (unnormalised), then ml [6][2] f32 (max in log2 units, sum).
 constexpr int kPartialAccFloats = kGroup * kHeadDim;
 constexpr int kPartialMlFloats = kGroup * 2;
+// Split-K units one (batch row, kv head) may have: the combine kernel keeps one weight per unit in shared memory.
+// Every planner stays below it (yahkv_config.max_splits is refused above it).
+constexpr int kCombineMaxUnits = 1024;
 
 // Launch with programmatic stream serialization allowed: see ChainedKernelEntry in ptx.cuh.
 template <class... Params, class... Args>
@@ -197,5 +204,8 @@ bool EncodeTensorMap2D(CUtensorMap* map, int elem_bytes, void* base, std::uint64
 
 // Status codes the kernels write into the sticky status word.
 constexpr int kStatusWaitTimeout = 1;
+// One CTA waits at most limit_ns on an mbarrier nobody arrives at, gives up, records kStatusWaitTimeout and returns:
+// the give-up path of every bounded wait in this library, run on purpose (yahkv_debug_wait_timeout).
+cudaError_t LaunchWaitProbe(int* status_dev, std::uint64_t limit_ns, cudaStream_t stream);
 
 }  // namespace yahkv

@@ -50,8 +50,9 @@ __device__ __forceinline__ void QuantizeStoreRow(const PoolView& pool, int layer
       const int q = static_cast<int>(roundf(__fmul_rn(x[i], inv)));  // roundf: halfway cases away from zero = lround
       w[i >> 2] |= (static_cast<std::uint32_t>(q) & 0xFFU) << (8 * (i & 3));
     }
-    // stored with the sign bits flipped: the pools' device representation of q8_0 codes
-    *reinterpret_cast<uint2*>(codes + lane * 8) = make_uint2(w[0] ^ kQ8FlipWord, w[1] ^ kQ8FlipWord);
+    // the pools' device representation of q8_0 codes: K as it is, V with the sign bits flipped
+    const std::uint32_t flip = Q8FlipWord(side);
+    *reinterpret_cast<uint2*>(codes + lane * 8) = make_uint2(w[0] ^ flip, w[1] ^ flip);
     if (sub == 0) scales[blk] = __half_as_ushort(__float2half_rn(d));
   } else {
     // Largest magnitude of the block with its sign, first occurrence on ties.

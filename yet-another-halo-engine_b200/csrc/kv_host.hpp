@@ -54,6 +54,8 @@ class KvHost {
     if (c.num_pages < 1) return bad("num_pages must be positive");
     if (c.max_seqs < 1 || c.max_pages_per_seq < 1) return bad("max_seqs and max_pages_per_seq must be positive");
     if (c.max_splits < 0 || c.max_batch_tokens < 0) return bad("max_splits and max_batch_tokens must not be negative");
+    static_assert(kCombineMaxUnits == 1024, "the message below names the limit");
+    if (c.max_splits > kCombineMaxUnits) return bad("max_splits must not exceed 1024 (the combine kernel's unit limit)");
     if (c.kv_head_begin < 0 || c.kv_head_count < 0 || c.kv_head_begin + c.kv_head_count > kKvHeads ||
         (c.kv_head_count == 0 && c.kv_head_begin != 0))
       return bad("kv_head_begin / kv_head_count must describe a range inside the 4 kv heads (count 0 = all)");
@@ -349,6 +351,9 @@ class KvHost {
     *scratch_rows = kv_row;
     return {};
   }
+
+  // Puts a range back that ForEachDirty handed out but the caller could not upload.
+  void MarkDirtyAgain(int seq, int lo, int hi) { MarkDirty(seq, lo, hi); }
 
   // Rows of the block table changed since the last call: [lo, hi) per sequence. The caller uploads and clears.
   template <class F>

@@ -79,9 +79,11 @@ __global__ void __launch_bounds__(kDequantThreads)
       float v[8];
       if constexpr (kFmt == kFmtQ8) {
         const uint2 c = *reinterpret_cast<const uint2*>(codes + tok * 256 + grp * 8);
-        const std::uint8_t* cb = reinterpret_cast<const std::uint8_t*>(&c);   // u = code + 128 on the device
+        const std::uint8_t* cb = reinterpret_cast<const std::uint8_t*>(&c);   // K: int8; V: u = code + 128
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = d * static_cast<float>(static_cast<int>(cb[i]) - kQ8FlipByte);
+        for (int i = 0; i < 8; ++i)
+          v[i] = d * static_cast<float>(side == 0 ? static_cast<int>(static_cast<std::int8_t>(cb[i]))
+                                                  : static_cast<int>(cb[i]) - kQ8FlipByte);
       } else {
         // block b = grp / 4 occupies bytes 16 b .. 16 b + 15; element e of the block is the low (e < 16) or high
         // nibble of byte e % 16. This group holds elements 8 (grp % 4) .. + 7 of its block.

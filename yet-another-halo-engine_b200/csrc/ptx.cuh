@@ -45,15 +45,19 @@ __device__ __forceinline__ std::uint64_t GlobalTimerNs() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Waits for the barrier's phase `parity` to complete, for at most about two seconds.
-__device__ __forceinline__ bool MbarWait(std::uint64_t* bar, std::uint32_t parity) {
+// Waits for the barrier's phase `parity` to complete, for at most `limit_ns` (about two seconds unless the caller
+// says otherwise). The reference bounds its device-side polls the same way and leaves a sticky status behind
+// (engine/gpu/loom/tools/gen_chain.py:12-19).
+constexpr std::uint64_t kWaitLimitNs = 2000000000ULL;
+__device__ __forceinline__ bool MbarWait(std::uint64_t* bar, std::uint32_t parity,
+                                         std::uint64_t limit_ns = kWaitLimitNs) {
   if (MbarTryWait(bar, parity)) return true;
   const std::uint64_t t0 = GlobalTimerNs();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 256; ++i)
       if (MbarTryWait(bar, parity)) return true;
-    if (GlobalTimerNs() - t0 > 2000000000ULL) return false;
+    if (GlobalTimerNs() - t0 > limit_ns) return false;
   }
 }
 
@@ -135,6 +139,13 @@ __device__ __forceinline__ void Offset8x4ToHalf2(std::uint32_t u, std::uint32_t&
   const __half2 b = __hsub2(*reinterpret_cast<const __half2*>(&hi), bias);
   h02 = *reinterpret_cast<const std::uint32_t*>(&a);
   h13 = *reinterpret_cast<const std::uint32_t*>(&b);
+}
+// Four packed q4_0 bytes -> the int8 values 16 (n - 8) of their low nibbles (byte order kept) and of their high
+// nibbles: a nibble moved to the top of its byte is 16 n as an unsigned byte, and flipping the byte's sign bit
+// subtracts 128.
+__device__ __forceinline__ void Nib8ToInt8(std::uint32_t w, std::uint32_t& lo, std::uint32_t& hi) {
+  lo = ((w << 4) & 0xF0F0F0F0U) ^ 0x80808080U;
+  hi = (w & 0xF0F0F0F0U) ^ 0x80808080U;
 }
 // Four packed q4_0 bytes -> low nibbles of bytes (0,2), (1,3) and high nibbles of bytes (0,2), (1,3), each minus 8.
 __device__ __forceinline__ void Nib4x4ToHalf2(std::uint32_t w, std::uint32_t& l02, std::uint32_t& l13,

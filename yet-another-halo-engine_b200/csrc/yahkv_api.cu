@@ -135,6 +135,7 @@ struct yahkv_ctx {
   float* part_acc_dev = nullptr;   // partial results of split prefill tiles
   float* part_ml_dev = nullptr;
   int n_sm = 0;                    // SMs the prefill planner fills waves of
+  int n_sm_device = 0;             // SMs of the device (the planner's default and upper bound)
   std::vector<PrefillSeq> pseq_scratch;
   PrefillSeq* pseqs_dev = nullptr;
   void *k16_dev = nullptr, *v16_dev = nullptr;   // fp16 scratch of the prefill dequantize pass, grown on demand
@@ -205,10 +206,8 @@ int InitDevice(yahkv_ctx* ctx) {
   ctx->pool.kv_head_begin = ctx->host.kv_head_begin(), ctx->pool.kv_head_count = ctx->host.kv_head_count();
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.kcodes, recs * RecordCodeBytes(c.fmt), true));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.vcodes, recs * RecordCodeBytes(c.fmt), true));
-  if (c.fmt == YAHKV_FMT_Q8_0) {   // code 0 in the device representation (sign bit flipped)
-    YAHKV_CUDA(ctx, cudaMemset(ctx->pool.kcodes, kQ8FlipByte, recs * RecordCodeBytes(c.fmt)));
+  if (c.fmt == YAHKV_FMT_Q8_0)   // code 0 in the V side's device representation (sign bit flipped)
     YAHKV_CUDA(ctx, cudaMemset(ctx->pool.vcodes, kQ8FlipByte, recs * RecordCodeBytes(c.fmt)));
-  }
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.kscales, recs * kPageTokens * kBlocksPerRow, true));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.vscales, recs * kPageTokens * kBlocksPerRow, true));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->tables_dev, static_cast<std::size_t>(c.max_seqs) * c.max_pages_per_seq, true));
@@ -219,8 +218,7 @@ int InitDevice(yahkv_ctx* ctx) {
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->partial_acc, static_cast<std::size_t>(ctx->max_units) * kPartialAccFloats, false));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->partial_ml, static_cast<std::size_t>(ctx->max_units) * kPartialMlFloats, false));
   YAHKV_CUDA(ctx, cudaDeviceGetAttribute(&ctx->n_sm, cudaDevAttrMultiProcessorCount, c.device));
-  if (const char* env = std::getenv("YAHKV_PREFILL_SMS"); env != nullptr)   // tests: split small calls too
-    ctx->n_sm = std::min(std::max(std::atoi(env), 0), ctx->n_sm);
+  ctx->n_sm_device = ctx->n_sm;
   ctx->max_tiles = (c.max_batch_tokens / kPrefillTileRows + c.max_seqs) * kQHeads + kPrefillMaxParts * ctx->n_sm;
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->tiles_dev, static_cast<std::size_t>(ctx->max_tiles), false));
   if (ctx->n_sm > 0) {
@@ -348,18 +346,26 @@ int FlushTables(yahkv_ctx* ctx, cudaStream_t stream) {
     total += static_cast<std::size_t>(hi - lo) * 4;
   });
   if (ranges.empty()) return YAHKV_OK;
+  // A flush that fails part-way marks every range dirty again, so the rows go up with the next hot call instead of
+  // being lost.
+  auto fail = [&](const char* what, cudaError_t e) {
+    for (const Range& r : ranges) ctx->host.MarkDirtyAgain(r.seq, r.lo, r.hi);
+    return FailCuda(ctx, what, e);
+  };
   char* buf = nullptr;
-  YAHKV_CUDA(ctx, ctx->staging.Acquire(total, &buf));
+  if (cudaError_t e = ctx->staging.Acquire(total, &buf); e != cudaSuccess) return fail("table staging", e);
   std::size_t off = 0;
   for (const Range& r : ranges) {
     const std::size_t bytes = static_cast<std::size_t>(r.hi - r.lo) * 4;
     if (bytes == 0) continue;
     std::memcpy(buf + off, ctx->host.table_row(r.seq) + r.lo, bytes);
-    YAHKV_CUDA(ctx, cudaMemcpyAsync(ctx->tables_dev + static_cast<std::size_t>(r.seq) * ctx->cfg.max_pages_per_seq + r.lo,
-                                    buf + off, bytes, cudaMemcpyHostToDevice, stream));
+    if (cudaError_t e = cudaMemcpyAsync(ctx->tables_dev + static_cast<std::size_t>(r.seq) * ctx->cfg.max_pages_per_seq + r.lo,
+                                        buf + off, bytes, cudaMemcpyHostToDevice, stream);
+        e != cudaSuccess)
+      return fail("table upload", e);
     off += bytes;
   }
-  YAHKV_CUDA(ctx, ctx->staging.Release(stream));
+  if (cudaError_t e = ctx->staging.Release(stream); e != cudaSuccess) return fail("table staging event", e);
   return YAHKV_OK;
 }
 
@@ -599,6 +605,15 @@ int yahkv_attend_decode(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int
   HostError e = ctx->host.PlanDecode(layer, n_seqs, seq_ids, n_splits, ctx->cfg.max_splits, ctx->max_units, &changed);
   if (e.code != YAHKV_OK) return FailHost(ctx, std::move(e));
   if (n_seqs == 0) return YAHKV_OK;
+  // The plan is cached on the host from here on; anything that fails before both kernels are queued drops it, so the
+  // next identical call plans and uploads again instead of launching on a unit list that never reached the device.
+  struct PlanGuard {
+    KvHost* host;
+    bool keep = false;
+    ~PlanGuard() {
+      if (!keep) host->InvalidateDecodePlan();
+    }
+  } guard{&ctx->host};
   cudaStream_t st = StreamOf(ctx, stream);
   if (int r = FlushTables(ctx, st); r != YAHKV_OK) return r;
   const auto& units = ctx->host.units();
@@ -632,10 +647,8 @@ int yahkv_attend_decode(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int
     le = LaunchDecodeCombine(a, st);
     tc.End();
   }
-  if (le != cudaSuccess) {
-    ctx->host.InvalidateDecodePlan();
-    return FailCuda(ctx, "decode attention launch", le);
-  }
+  if (le != cudaSuccess) return FailCuda(ctx, "decode attention launch", le);
+  guard.keep = true;
   ctx->launches += 2;
   return YAHKV_OK;
 }
@@ -773,7 +786,7 @@ int yahkv_decode_step_host(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const 
       r != YAHKV_OK)
     return r;
   YAHKV_CUDA(ctx, cudaStreamSynchronize(ctx->d2h_stream));
-  return YAHKV_OK;
+  return CheckStatus(ctx);
 }
 
 int yahkv_sync(yahkv_ctx* ctx) {
@@ -782,10 +795,11 @@ int yahkv_sync(yahkv_ctx* ctx) {
   return CheckStatus(ctx);
 }
 
-// GGUF int8 codes <-> the pools' device representation (kernels.cuh): the same flip both ways; q4_0 is untouched.
-static void FlipQ8(int fmt, std::uint8_t* codes, std::size_t n) {
-  if (fmt != YAHKV_FMT_Q8_0) return;
-  for (std::size_t i = 0; i < n; ++i) codes[i] ^= static_cast<std::uint8_t>(kQ8FlipByte);
+// GGUF int8 codes <-> the pools' device representation (kernels.cuh): V bytes flip, the same way in both
+// directions; K bytes and q4_0 are untouched.
+static void FlipQ8(int fmt, int side, std::uint8_t* codes, std::size_t n) {
+  if (fmt != YAHKV_FMT_Q8_0 || Q8FlipByte(side) == 0) return;
+  for (std::size_t i = 0; i < n; ++i) codes[i] ^= static_cast<std::uint8_t>(Q8FlipByte(side));
 }
 
 static int PageAccess(yahkv_ctx* ctx, int32_t layer, int32_t side, int32_t page, void* codes_host, void* scales_host,
@@ -800,14 +814,14 @@ static int PageAccess(yahkv_ctx* ctx, int32_t layer, int32_t side, int32_t page,
   std::uint16_t* scales = (side == YAHKV_SIDE_K ? ctx->pool.kscales : ctx->pool.vscales) + rec * kPageTokens * kBlocksPerRow;
   const std::size_t cb = static_cast<std::size_t>(kKvHeads) * RecordCodeBytes(ctx->cfg.fmt);
   const std::size_t sb = static_cast<std::size_t>(kKvHeads) * kRecordScaleBytes;
-  if (codes_host != nullptr) {   // q8_0 codes cross the boundary as GGUF int8, the pools hold them sign-flipped
+  if (codes_host != nullptr) {   // q8_0 codes cross the boundary as GGUF int8, the V pool holds them sign-flipped
     if (write) {
       std::vector<std::uint8_t> tmp(static_cast<const std::uint8_t*>(codes_host), static_cast<const std::uint8_t*>(codes_host) + cb);
-      FlipQ8(ctx->cfg.fmt, tmp.data(), cb);
+      FlipQ8(ctx->cfg.fmt, side, tmp.data(), cb);
       YAHKV_CUDA(ctx, cudaMemcpy(codes, tmp.data(), cb, cudaMemcpyHostToDevice));
     } else {
       YAHKV_CUDA(ctx, cudaMemcpy(codes_host, codes, cb, cudaMemcpyDeviceToHost));
-      FlipQ8(ctx->cfg.fmt, static_cast<std::uint8_t*>(codes_host), cb);
+      FlipQ8(ctx->cfg.fmt, side, static_cast<std::uint8_t*>(codes_host), cb);
     }
   }
   if (scales_host != nullptr)
@@ -847,7 +861,7 @@ int yahkv_export_token(yahkv_ctx* ctx, int32_t layer, int32_t seq, int64_t pos, 
       const std::uint16_t* ss = (side == 0 ? ctx->pool.kscales : ctx->pool.vscales) + rec * kPageTokens * kBlocksPerRow +
                                 static_cast<std::size_t>(tok) * kBlocksPerRow;
       YAHKV_CUDA(ctx, cudaMemcpy(codes, cs, static_cast<std::size_t>(cbytes), cudaMemcpyDeviceToHost));
-      FlipQ8(ctx->cfg.fmt, codes, static_cast<std::size_t>(cbytes));
+      FlipQ8(ctx->cfg.fmt, side, codes, static_cast<std::size_t>(cbytes));
       YAHKV_CUDA(ctx, cudaMemcpy(scales, ss, sizeof(scales), cudaMemcpyDeviceToHost));
       for (int b = 0; b < kBlocksPerRow; ++b) {
         std::memcpy(dst, &scales[b], 2);
@@ -962,13 +976,19 @@ int yahkv_batch_prepare(yahkv_batch* b, int32_t horizon_steps, int32_t* layout_c
   if (int r = RequireDevice(ctx, "batch_prepare"); r != YAHKV_OK) return r;
   if (horizon_steps < 1) return Fail(ctx, YAHKV_ERR_INVALID, "batch_prepare: horizon must be at least one step");
   const int n = static_cast<int>(b->seqs.size());
-  // pages for every position the next `horizon_steps` steps will append; nothing changes if any reservation fails
+  // pages for every position the next `horizon_steps` steps will append: the table widths and the pool's free pages
+  // are checked for the whole batch first, so a refusal changes nothing
+  std::int64_t new_pages = 0;
   for (int i = 0; i < n; ++i) {
     if (!ctx->host.live(b->seqs[i]) || ctx->host.len(b->seqs[i], 0) != b->lens[i])
       return Fail(ctx, YAHKV_ERR_ORDER, "batch_prepare: a sequence of the batch was freed or changed outside the batch");
     const std::int64_t need = (static_cast<std::int64_t>(b->lens[i]) + horizon_steps + kPageTokens - 1) / kPageTokens;
     if (need > ctx->cfg.max_pages_per_seq) return Fail(ctx, YAHKV_ERR_CAPACITY, "batch_prepare: horizon exceeds max_pages_per_seq");
+    new_pages += std::max<std::int64_t>(need - ctx->host.n_pages(b->seqs[i]), 0);
   }
+  if (new_pages > ctx->host.pages_free())
+    return Fail(ctx, YAHKV_ERR_NO_PAGES, "batch_prepare: the horizon needs " + std::to_string(new_pages) +
+                                             " new pages, " + std::to_string(ctx->host.pages_free()) + " are free");
   for (int i = 0; i < n; ++i) {
     HostError e = ctx->host.SeqReserve(b->seqs[i], static_cast<std::int64_t>(b->lens[i]) + horizon_steps);
     if (e.code != YAHKV_OK) return FailHost(ctx, std::move(e));
@@ -1119,8 +1139,8 @@ int yahkv_snapshot_save(yahkv_ctx* ctx, int32_t n_seqs, const int32_t* seq_ids, 
         YAHKV_CUDA(ctx, cudaMemcpy(buf.data() + cb, ctx->pool.kscales + rec * kPageTokens * kBlocksPerRow, sb, cudaMemcpyDeviceToHost));
         YAHKV_CUDA(ctx, cudaMemcpy(buf.data() + cb + sb, ctx->pool.vcodes + rec * RecordCodeBytes(c.fmt), cb, cudaMemcpyDeviceToHost));
         YAHKV_CUDA(ctx, cudaMemcpy(buf.data() + 2 * cb + sb, ctx->pool.vscales + rec * kPageTokens * kBlocksPerRow, sb, cudaMemcpyDeviceToHost));
-        FlipQ8(c.fmt, buf.data(), cb);                 // the file holds GGUF int8 codes
-        FlipQ8(c.fmt, buf.data() + cb + sb, cb);
+        FlipQ8(c.fmt, YAHKV_SIDE_K, buf.data(), cb);                 // the file holds GGUF int8 codes
+        FlipQ8(c.fmt, YAHKV_SIDE_V, buf.data() + cb + sb, cb);
         ok = std::fwrite(buf.data(), buf.size(), 1, f.get()) == 1;
       }
   }
@@ -1170,8 +1190,8 @@ int yahkv_snapshot_load(yahkv_ctx* ctx, const char* path, int32_t* seq_ids_out, 
     for (int l = 0; l < c.n_layers; ++l)
       for (int p = 0; p < np; ++p) {
         if (std::fread(buf.data(), buf.size(), 1, f.get()) != 1) return undo(YAHKV_ERR_INVALID, "snapshot_load: truncated file");
-        FlipQ8(c.fmt, buf.data(), cb);
-        FlipQ8(c.fmt, buf.data() + cb + sb, cb);
+        FlipQ8(c.fmt, YAHKV_SIDE_K, buf.data(), cb);
+        FlipQ8(c.fmt, YAHKV_SIDE_V, buf.data() + cb + sb, cb);
         const std::size_t rec = (static_cast<std::size_t>(l) * c.num_pages + ctx->host.table_row(s)[p]) * kKvHeads;
         cudaError_t ce = cudaMemcpy(ctx->pool.kcodes + rec * RecordCodeBytes(c.fmt), buf.data(), cb, cudaMemcpyHostToDevice);
         if (ce == cudaSuccess) ce = cudaMemcpy(ctx->pool.kscales + rec * kPageTokens * kBlocksPerRow, buf.data() + cb, sb, cudaMemcpyHostToDevice);
@@ -1182,6 +1202,21 @@ int yahkv_snapshot_load(yahkv_ctx* ctx, const char* path, int32_t* seq_ids_out, 
     seq_ids_out[i] = s;
   }
   *n_inout = h.n_seqs;
+  return YAHKV_OK;
+}
+
+int yahkv_debug_wait_timeout(yahkv_ctx* ctx, int64_t limit_us, void* stream) {
+  if (int r = RequireDevice(ctx, "debug_wait_timeout"); r != YAHKV_OK) return r;
+  if (limit_us < 1 || limit_us > 1000000) return Fail(ctx, YAHKV_ERR_INVALID, "debug_wait_timeout: limit must be 1 us .. 1 s");
+  YAHKV_CUDA(ctx, LaunchWaitProbe(ctx->status_dev, static_cast<std::uint64_t>(limit_us) * 1000ULL, StreamOf(ctx, stream)));
+  ctx->launches += 1;
+  return YAHKV_OK;
+}
+
+int yahkv_debug_set_prefill_sms(yahkv_ctx* ctx, int32_t n_sm) {
+  if (int r = RequireDevice(ctx, "debug_set_prefill_sms"); r != YAHKV_OK) return r;
+  if (n_sm < 0 || n_sm > ctx->n_sm_device) return Fail(ctx, YAHKV_ERR_INVALID, "debug_set_prefill_sms: 0 .. the device's SM count");
+  ctx->n_sm = n_sm;
   return YAHKV_OK;
 }
 

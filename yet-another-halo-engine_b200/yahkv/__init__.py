@@ -14,8 +14,7 @@ import subprocess
 import numpy as np
 
 _PKG_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-# YAHKV_LIB points at another build of the same library (a debug or tuning build); the default is the in-tree one.
-LIB_PATH = os.environ.get("YAHKV_LIB") or os.path.join(_PKG_DIR, "libyahkv.so")
+LIB_PATH = os.path.join(_PKG_DIR, "libyahkv.so")
 INCLUDE_DIR = os.path.join(os.path.dirname(_PKG_DIR), "include")
 
 FMT_Q8_0, FMT_Q4_0 = 0, 1
@@ -143,6 +142,9 @@ SIGNATURES = {
     "yahkv_device_bytes": (_I32, [_VP, _PI64]),
     "yahkv_launch_count": (_I32, [_VP, _PI64]),
     "yahkv_attend_decode_noalloc": (_I32, [_c.POINTER(NoAllocArgs), _c.c_char_p, _I32]),
+    "yahkv_noalloc_status": (_I32, [_PI32, _VP]),
+    "yahkv_debug_wait_timeout": (_I32, [_VP, _I64, _VP]),
+    "yahkv_debug_set_prefill_sms": (_I32, [_VP, _I32]),
     "yahkv_kernel_timing": (_I32, [_VP, _I32]),
     "yahkv_kernel_timing_read": (_I32, [_VP, _I32, _c.POINTER(_c.c_double), _PI64]),
 }
@@ -182,12 +184,12 @@ def _i32(a):
     return np.ascontiguousarray(a, dtype=np.int32)
 
 
-def device_codes(fmt, codes):
-    """GGUF code bytes (as read_page returns them) -> the form the device pools hold: q8_0 bytes with the sign bit
-    flipped (u = code + 128), q4_0 unchanged. The same call converts back. For callers that build device pools
-    themselves (attend_decode_noalloc)."""
+def device_codes(fmt, codes, side):
+    """GGUF code bytes (as read_page returns them) -> the form the device pools hold: q8_0 V bytes with the sign bit
+    flipped (u = code + 128); q8_0 K bytes and q4_0 unchanged. The same call converts back. For callers that build
+    device pools themselves (attend_decode_noalloc)."""
     codes = np.ascontiguousarray(codes, np.uint8)
-    return codes ^ np.uint8(0x80) if fmt == FMT_Q8_0 else codes
+    return codes ^ np.uint8(0x80) if fmt == FMT_Q8_0 and side == SIDE_V else codes
 
 
 def attend_decode_noalloc(*, fmt, n_layers, num_pages, layer, kcodes, vcodes, kscales, vscales, tables, table_stride,
@@ -205,6 +207,14 @@ def attend_decode_noalloc(*, fmt, n_layers, num_pages, layer, kcodes, vcodes, ks
     rc = lib.yahkv_attend_decode_noalloc(ctypes.byref(args), err, len(err))
     if rc != OK:
         raise YahkvError(rc, err.value.decode())
+
+
+def noalloc_status(status_host, stream=None):
+    """Queues the copy of the no-allocation path's status word into `status_host` (an int32 array or pinned tensor of
+    one element) on `stream`; read it after synchronising the stream."""
+    rc = lib.yahkv_noalloc_status(ctypes.cast(_ptr(status_host), _PI32), _ptr(stream))
+    if rc != OK:
+        raise YahkvError(rc, "noalloc_status: no yahkv_attend_decode_noalloc call has run on this device yet")
 
 
 class DecodeBatch:
@@ -395,6 +405,13 @@ class KvCache:
         ms, n = ctypes.c_double(), ctypes.c_int64()
         self._check(lib.yahkv_kernel_timing_read(self._h, kernel, ctypes.byref(ms), ctypes.byref(n)))
         return ms.value, n.value
+
+    def debug_wait_timeout(self, limit_us, stream=None):
+        """Runs a device wait that cannot succeed for at most limit_us; the next sync() then reports it."""
+        self._check(lib.yahkv_debug_wait_timeout(self._h, int(limit_us), _ptr(stream)))
+
+    def debug_set_prefill_sms(self, n_sm):
+        self._check(lib.yahkv_debug_set_prefill_sms(self._h, int(n_sm)))
 
     def launch_count(self):
         n = ctypes.c_int64()
