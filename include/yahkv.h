@@ -73,6 +73,12 @@ typedef struct yahkv_config {
    * (yahkv_batch_*) need all four heads. */
   int32_t kv_head_begin;
   int32_t kv_head_count;
+  /* Cached keys (chunk included, summed over the sequences of one call, each rounded up to whole pages) that one
+   * yahkv_attend_prefill call may cover. > 0: the fp16 scratch of the prefill dequantize pass (4 KB per key) is
+   * allocated once at yahkv_create and a larger call is refused with YAHKV_ERR_CAPACITY, so the call never
+   * allocates or synchronises. 0: the scratch grows to the largest call seen, which costs a device synchronisation
+   * and a reallocation whenever the high-water mark rises. */
+  int32_t max_prefill_keys;
 } yahkv_config;
 
 /* Replaces LoomDecoder::OwnState / LoomPrefill's pool allocation (engine/model/loom_decoder.hpp:159-183,

@@ -12,11 +12,12 @@
 // 64 x 8 fp16 scales, all completing on one mbarrier per ring stage. There is no producer warp: whichever warp
 // finishes a stage last refills it, so no warp waits for another.
 //
-// Eight warps share a page: four key groups of 16 keys x two halves of the head dimension. The two warps of a key
-// group each compute the scores' partial sums over their 128 dims, swap them through shared memory (one 64-thread
-// named barrier per page), run the same softmax, and accumulate their own 128 output dims. Splitting the dims halves
-// the accumulator registers per thread, which is what lets 16 warps stay resident per SM; with fewer warps the kernel
-// is bound by instruction latency, not by HBM.
+// Eight warps work on two pages at a time: warp w owns key group w % 4 (16 keys) of the pages whose index in the unit
+// has parity w / 4, and for those keys it does everything: scores over all 256 dims, softmax, and all 256 output
+// dims (64 accumulator registers). No warp ever exchanges anything with another one inside the page loop: per page
+// there is one wait, one softmax per key group and no barrier, which is what keeps the number of instructions issued
+// per cached byte low enough for q4_0 as well (an earlier layout split the head dimension over warp pairs: half the
+// accumulators per thread, but two barriers, an exchange through shared memory and a duplicated softmax per page).
 //
 // The path is HBM-bound (2176 B per token per layer in q8_0), but at GQA 6 it needs 5.6 multiply-adds per byte, more
 // than the fp32 pipes can give at HBM rate, so the dot products run on the warp-level tensor-core MMA with register
@@ -24,7 +25,8 @@
 // treated differently for that reason:
 //   Q.K^T runs on the integer MMA (m16n8k32, s8 x s8 -> s32) straight on the cached codes: a 32-element block is
 //   exactly one k-step, ldmatrix delivers the code bytes in the B operand's register layout, and nothing is converted
-//   (q4_0: three logic instructions turn eight nibbles into the int8 values 16 (n - 8)). The query row is quantized
+//   (q4_0: three logic instructions turn eight nibbles into the bytes 16 n, and the accumulator starts at -128 times
+//   the block sum of the query plane, which supplies the - 8). The query row is quantized
 //   once per CTA to 16 bits against its head's largest magnitude and split into two int8 planes, hi and lo
 //   (q = s (256 hi + lo), |error| <= s / 2 = amax / 64000 per element, far below the fp16 query's own spacing).
 //   Both planes ride in one MMA as rows 0-5 and 8-13 of the 16-row A operand, so one instruction gives the exact
@@ -60,7 +62,8 @@ namespace {
 #define YAHKV_Q4_STAGES 5
 #endif
 constexpr int kKeyGroups = 4;              // 16 keys of a page each
-constexpr int kWarps = 2 * kKeyGroups;     // x two halves of the head dimension
+constexpr int kPageSets = 2;               // pages in work at a time: warp w takes the pages of parity w / 4
+constexpr int kWarps = kPageSets * kKeyGroups;
 constexpr int kDecodeThreads = kWarps * 32;
 constexpr int kBoxBytes = 64 * 128;        // one swizzled TMA box: 64 token rows x 128 B
 
@@ -74,10 +77,10 @@ struct StageLayout {
   static constexpr int kBytes = kVsOff + kRecordScaleBytes;  // 34816 (q8_0) or 18432 (q4_0), a multiple of 1024
   static constexpr int kStages = kFmt == kFmtQ8 ? YAHKV_Q8_STAGES : YAHKV_Q4_STAGES;
 };
-// Cross-warp merge scratch at the end of a unit: per key group acc [6][kMergeStride] f32 and (m, l) [8][2].
+// Cross-warp merge scratch at the end of a unit: per warp acc [6][kMergeStride] f32 and (m, l) [8][2].
 constexpr int kMergeStride = kHeadDim + 8;
 constexpr int kMergeGroupFloats = kGroup * kMergeStride + 16;
-constexpr int kMergeBytes = kKeyGroups * kMergeGroupFloats * 4;
+constexpr int kMergeBytes = kWarps * kMergeGroupFloats * 4;
 
 // fp16 number i (0..3) of four packed in a uint2, widened to f32. i is a compile-time constant after unrolling.
 __device__ __forceinline__ float ScaleOf(const uint2& v, int i) {
@@ -87,16 +90,28 @@ __device__ __forceinline__ float ScaleOf(const uint2& v, int i) {
 }
 
 // One S^T step on the integer tensor pipe: D(16 x 8, s32) = A(16 x 32, s8) . B(32 x 8, s8), accumulator input zero.
-// A = the query planes of one 32-element block, fetched from shared memory at use as the operand's four registers
-// (one 16-byte load, no shuffling); B = the code bytes of eight keys as ldmatrix left them.
-__device__ __forceinline__ void MmaQK(int (&d)[4], std::uint32_t q_addr, std::uint32_t b0, std::uint32_t b1) {
-  std::uint32_t a0, a1, a2, a3;
-  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(q_addr));
+// A = the query planes of one 32-element block (LoadQ: one 16-byte load from shared memory at use, shared by the two
+// key tiles of the block); B = the code bytes of eight keys as ldmatrix left them.
+__device__ __forceinline__ void LoadQ(std::uint32_t (&a)[4], std::uint32_t q_addr) {
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(q_addr));
+}
+__device__ __forceinline__ void MmaQK(int (&d)[4], const std::uint32_t (&a)[4], std::uint32_t b0, std::uint32_t b1) {
   asm volatile(
       "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
       "{%10, %10, %10, %10};"
       : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
+}
+// The q4_0 form: B holds the unsigned bytes 16 n (a nibble moved to the top of its byte), so the sum comes out as
+// 16 sum(q n); the accumulator starts at -128 sum(q) of the block (c_hi for the hi plane's rows, c_lo for the lo
+// plane's), which makes it 16 sum(q (n - 8)) without touching the codes again.
+__device__ __forceinline__ void MmaQKU8(int (&d)[4], const std::uint32_t (&a)[4], std::uint32_t b0, std::uint32_t b1,
+                                        int c_hi, int c_lo) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%10, %10, %11, %11};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c_hi), "r"(c_lo));
 }
 // The block sum of one (head, key): the hi plane's sum times 256 plus the lo plane's, exact in 32 bits
 // (|sum| <= 32 x 128 x 32768), as a float.
@@ -106,23 +121,22 @@ __device__ __forceinline__ float JoinPlanes(int hi, int lo) { return static_cast
 constexpr float kQSteps = 32000.0F;
 
 // Shared memory of a CTA, all dynamic so that the ring starts at the window's 1024-byte aligned base (the swizzled
-// TMA boxes need that alignment): ring | Q operands | score exchange | mbarriers | stage counters | query scales |
-// abort flag. Lanes 24-31 of a warp hold the two padding heads of the 8-wide MMA; they reuse the Q operands of lanes
-// 16-23 (duplicates of heads 4, 5 whose results are never stored), so the Q and exchange arrays are 24 lanes wide.
+// TMA boxes need that alignment): ring | Q operands | mbarriers | stage counters | query scales | abort flag.
+// Lanes 24-31 of a warp hold the two padding heads of the 8-wide MMA; they reuse the Q operands of lanes 16-23
+// (duplicates of heads 4, 5 whose results are never stored), so the Q array is 24 lanes wide.
 constexpr int kQLanes = 24;
 constexpr int kQfragBytes = kBlocksPerRow * kQLanes * 16;   // per 32-element block the A operand's four registers
-constexpr int kXchgBytes = kWarps * kQLanes * 16;
 template <int kFmt>
 struct SmemLayout {
   static constexpr int kRing = StageLayout<kFmt>::kStages * StageLayout<kFmt>::kBytes;
   static_assert(kRing >= kMergeBytes, "the merge scratch aliases the ring");
   static constexpr int kQfragOff = kRing;
-  static constexpr int kXchgOff = kQfragOff + kQfragBytes;
-  static constexpr int kBarOff = kXchgOff + kXchgBytes;
+  static constexpr int kBarOff = kQfragOff + kQfragBytes;
   static constexpr int kCntOff = kBarOff + 8 * StageLayout<kFmt>::kStages;
   static constexpr int kFillOff = kCntOff + 4 * StageLayout<kFmt>::kStages;     // fills issued per stage
   static constexpr int kQScaleOff = kFillOff + 4 * StageLayout<kFmt>::kStages;  // [8] f32, one per head (6 used)
-  static constexpr int kAbortOff = kQScaleOff + 4 * 8;
+  static constexpr int kQCorrOff = (kQScaleOff + 4 * 8 + 7) / 8 * 8;            // [8 blocks][8 heads] int2 (q4_0)
+  static constexpr int kAbortOff = kQCorrOff + kBlocksPerRow * 8 * 8;
   static constexpr int kBytes = kAbortOff + 4;
 };
 template <int kFmt>
@@ -147,11 +161,11 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
   extern __shared__ __align__(1024) std::uint8_t smem_raw[];
   std::uint8_t* ring = smem_raw;
   std::uint32_t* qfrag = reinterpret_cast<std::uint32_t*>(smem_raw + S::kQfragOff);   // [8 blocks][24 lanes][4]
-  float4* xchg = reinterpret_cast<float4*>(smem_raw + S::kXchgOff);     // partial scores [8 warps][24 lanes]
   std::uint64_t* full_bar = reinterpret_cast<std::uint64_t*>(smem_raw + S::kBarOff);
   int* done_cnt = reinterpret_cast<int*>(smem_raw + S::kCntOff);        // warps done reading a stage's page
   int* fill_cnt = reinterpret_cast<int*>(smem_raw + S::kFillOff);       // fills issued to a stage so far
   float* q_scale = reinterpret_cast<float*>(smem_raw + S::kQScaleOff);  // query quantization step per head
+  int2* q_corr = reinterpret_cast<int2*>(smem_raw + S::kQCorrOff);      // -128 x block sums of the query planes
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + S::kAbortOff);   // a wait gave up
   if ((SmemAddr(smem_raw) & 1023U) != 0) {   // never seen; checked because a misaligned swizzle would corrupt results
     if (threadIdx.x == 0) atomicExch(status, kStatusSmemMisaligned);
@@ -160,8 +174,8 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
 
   const DecodeUnit u = units[blockIdx.x];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kw = warp >> 1;   // key group: keys 16 kw .. 16 kw + 15 of the page
-  const int dh = warp & 1;    // dim half: dims 128 dh .. 128 dh + 127 (blocks 4 dh .. 4 dh + 3)
+  const int kw = warp & (kKeyGroups - 1);   // key group: keys 16 kw .. 16 kw + 15 of a page
+  const int par = warp / kKeyGroups;        // this warp's pages: index par, par + 2, ... of the unit
   const int n_pages = u.page_end - u.page_begin;
   if (n_pages <= 0) return;   // a unit reserved for growth that holds no page yet: the merge does not count it
   const std::int32_t* row = tables + static_cast<std::size_t>(u.seq) * table_stride + u.page_begin;
@@ -228,15 +242,22 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFU, amax, o));
     const float inv = amax > 0.0F ? kQSteps / amax : 0.0F;
     std::uint32_t hi_w[2] = {0, 0}, lo_w[2] = {0, 0};
+    int sum_hi = 0, sum_lo = 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int q16 = __float2int_rn(x[i] * inv);
       const int hi = (q16 + 128) >> 8;
       const int lo = q16 - hi * 256;
+      sum_hi += hi, sum_lo += lo;
       hi_w[i >> 2] |= (static_cast<std::uint32_t>(hi) & 0xFFU) << (8 * (i & 3));
       lo_w[i >> 2] |= (static_cast<std::uint32_t>(lo) & 0xFFU) << (8 * (i & 3));
     }
     const int blk = lane >> 2, e0 = (lane & 3) * 8;
+    if constexpr (kFmt == kFmtQ4) {   // the block's plane sums (a block is four lanes), for the unsigned-code MMA
+      sum_hi += __shfl_xor_sync(0xFFFFFFFFU, sum_hi, 1), sum_lo += __shfl_xor_sync(0xFFFFFFFFU, sum_lo, 1);
+      sum_hi += __shfl_xor_sync(0xFFFFFFFFU, sum_hi, 2), sum_lo += __shfl_xor_sync(0xFFFFFFFFU, sum_lo, 2);
+      if ((lane & 3) == 0) q_corr[blk * 8 + warp] = make_int2(-128 * sum_hi, -128 * sum_lo);
+    }
     const int reg = e0 < 16 ? 0 : 2, t0 = (e0 & 15) >> 2;
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
@@ -248,14 +269,13 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
     if (lane == 0) q_scale[warp] = (amax / kQSteps) * (kFmt == kFmtQ8 ? 1.0F : 0.0625F);
   }
   __syncthreads();   // barriers initialised, query planes visible
-  // This warp's four blocks are 4 dh .. 4 dh + 3.
   const int qlane = lane < kQLanes ? lane : lane - 8;
-  const std::uint32_t qa_addr = SmemAddr(qfrag + ((4 * dh * kQLanes + qlane) << 2));
-  const float score_scale = scale_log2 * q_scale[qlane >> 2];   // softmax scale x log2(e) x the head's query step
+  const std::uint32_t qa_addr = SmemAddr(qfrag + (qlane << 2));   // block b: + b * kQLanes * 16 bytes
+  const float score_scale = scale_log2 * q_scale[qlane >> 2];     // softmax scale x log2(e) x the head's query step
 
-  float o_acc[8][4];   // tile c2 = dims 128 dh + 16 c2 .. + 15
+  float o_acc[16][4];   // tile c = dims 16 c .. 16 c + 15 (in the MMA's permuted order)
 #pragma unroll
-  for (int c = 0; c < 8; ++c)
+  for (int c = 0; c < 16; ++c)
 #pragma unroll
     for (int i = 0; i < 4; ++i) o_acc[c][i] = 0.0F;
   float m_run = -INFINITY, l_run = 0.0F;
@@ -263,37 +283,69 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
 
   // ldmatrix row addresses: lane supplies row (lane & 7) + 8 * ((lane >> 3) & 1) of the key group's 16 keys and the
   // 16-byte chunk 2x + (lane >> 4) of its 128-byte row, swizzled: physical chunk = chunk ^ (row & 7).
+  // Chunk pair x differs from pair 0 in address bits 5-6 only, and the swizzle is an xor, so pair x's offset is pair
+  // 0's xor (x << 5). q8_0 keeps one register and pays the xor at each use; q4_0, whose page loop has no slack on the
+  // logic pipe or on the address path of its ldmatrix reads, keeps the four offsets in registers (measured: 391 us per
+  // launch of the long-context workload with the xor, 323 us with the registers; q8_0 201 against 204 us).
   const int lm_key = kw * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-  std::uint32_t lm_off[4];
+  const std::uint32_t lm0 = lm_key * 128 + (((lane >> 4) ^ (lm_key & 7)) << 4);
+  std::uint32_t lm_arr[4];
 #pragma unroll
-  for (int x = 0; x < 4; ++x) lm_off[x] = lm_key * 128 + ((((2 * x) | (lane >> 4)) ^ (lm_key & 7)) << 4);
-  // q8_0: the warp's dim half is one TMA box and all four chunk pairs of it. q4_0: the row is one box of eight
-  // 16-byte blocks and the warp's half is chunk pairs 2 dh, 2 dh + 1.
-  const std::uint32_t half_off = kFmt == kFmtQ8 ? dh * kBoxBytes : 0;
+  for (int x = 0; x < 4; ++x) lm_arr[x] = lm_key * 128 + ((((2 * x) | (lane >> 4)) ^ (lm_key & 7)) << 4);
+  auto lm_off = [&](int x) -> std::uint32_t {
+    if constexpr (kFmt == kFmtQ4) {
+      return lm_arr[x];
+    } else {
+      return lm0 ^ (static_cast<std::uint32_t>(x) << 5);
+    }
+  };
   // Keys whose scores this thread holds: kt * 8 + 2t + j of the group's 16.
   const int my_key0 = kw * 16 + 2 * t;
 
-  int s = 0;                  // ring stage of page i, and the parity of the mbarrier phase that fills it
-  std::uint32_t phase = 0;
-  for (int i = 0; i < n_pages; ++i) {
+  NibConsts nib{};
+  if constexpr (kFmt == kFmtQ4) nib.Load();
+  static_assert(kPageSets <= L::kStages, "the stage counter below wraps at most once per step");
+  for (int i = par; i < n_pages; i += kPageSets) {
+    const int s = i % L::kStages;    // ring stage of page i
+    const int gen = i / L::kStages;  // fills of that stage before this page's
+    const std::uint32_t phase = static_cast<std::uint32_t>(gen) & 1U;   // parity of the mbarrier phase that fills it
     // Table entry of the page that will take this stage next, fetched a whole iteration before it is needed.
     std::int32_t refill_page = 0;
     if (lane == 0 && i + L::kStages < n_pages) refill_page = __ldg(row + i + L::kStages);
-    // A wait that gives up does not leave the loop (its partner warp would hang at the pair barrier): the warp stops
-    // waiting, raises the CTA's abort flag so that nothing more is fetched, finishes on whatever the ring holds, and
-    // the status word marks the call's results invalid.
-    if (alive && (*abort_flag != 0 || !__all_sync(0xFFFFFFFFU, MbarWait(&full_bar[s], phase)))) {
-      alive = false;
-      *abort_flag = 1;
+    // A wait that gives up does not stop the warp half-way through a unit: it stops waiting, raises the CTA's abort
+    // flag so that nothing more is fetched, finishes on whatever the ring holds, and the status word marks the call's
+    // results invalid.
+    // The mbarrier wait names its phase by parity only, so it is safe only for a warp that is not a whole phase ahead
+    // of the barrier. A page's stage is refilled by the OTHER page set, whose progress this warp does not otherwise
+    // depend on, so the warp first makes sure (a bounded poll of the stage's fill counter, almost always true at
+    // once) that the fill it wants has at least been issued; from then on the parity is unambiguous.
+    if (alive) {
+      const int need = gen + 1;
+      volatile int* fills = fill_cnt + s;
+      bool ok = *abort_flag == 0;
+      if (ok && *fills < need) {
+        const std::uint64_t t0 = GlobalTimerNs();
+        while (*fills < need) {
+          if (*abort_flag != 0 || GlobalTimerNs() - t0 > kWaitLimitNs) {
+            ok = false;
+            break;
+          }
+        }
+      }
+      if (!ok || !__all_sync(0xFFFFFFFFU, MbarWait(&full_bar[s], phase))) {
+        alive = false;
+        *abort_flag = 1;
+      }
     }
     const std::uint8_t* st = ring + s * L::kBytes;
-    const std::uint32_t k_base = SmemAddr(st + L::kKOff) + half_off, v_base = SmemAddr(st + L::kVOff) + half_off;
+    const std::uint32_t k_base = SmemAddr(st + L::kKOff), v_base = SmemAddr(st + L::kVOff);
 
-    // ---- S^T = Q K^T over this warp's 128 dims: per 32-element block the exact integer sums of the two query
-    // planes, joined, converted once, times the block's fp16 scale ----
+    // ---- S^T = Q K^T: per 32-element block the exact integer sums of the two query planes, joined, converted once,
+    // times the block's fp16 scale ----
     float sc[2][2] = {{0.0F, 0.0F}, {0.0F, 0.0F}};
-    {
-      uint2 ks_raw[2][2];   // scales of blocks 4 dh .. 4 dh + 3 of this thread's four keys
+#pragma unroll
+    for (int dh = 0; dh < 2; ++dh) {   // blocks 4 dh .. 4 dh + 3 (scales fetched per half to keep registers low)
+      uint2 ks_raw[2][2];
 #pragma unroll
       for (int kt = 0; kt < 2; ++kt)
 #pragma unroll
@@ -301,14 +353,15 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
           ks_raw[kt][j] = *reinterpret_cast<const uint2*>(st + L::kKsOff + (my_key0 + kt * 8 + j) * 16 + dh * 8);
       if constexpr (kFmt == kFmtQ8) {
         // One ldmatrix.x4 = one block of 16 keys: registers 0 / 2 are the two 16-byte halves of keys 0-7 (the B
-        // operand's k 0-15 and 16-31), registers 1 / 3 those of keys 8-15.
+        // operand's k 0-15 and 16-31), registers 1 / 3 those of keys 8-15. Dim half dh is TMA box dh.
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-          std::uint32_t w[4];
-          LdMatrixX4(k_base + lm_off[b], w);
+          std::uint32_t w[4], qa[4];
+          LdMatrixX4(k_base + dh * kBoxBytes + lm_off(b), w);
+          LoadQ(qa, qa_addr + (4 * dh + b) * (kQLanes * 16));
           int a0[4], a1[4];
-          MmaQK(a0, qa_addr + b * (kQLanes * 16), w[0], w[2]);
-          MmaQK(a1, qa_addr + b * (kQLanes * 16), w[1], w[3]);
+          MmaQK(a0, qa, w[0], w[2]);
+          MmaQK(a1, qa, w[1], w[3]);
           sc[0][0] = fmaf(ScaleOf(ks_raw[0][0], b), JoinPlanes(a0[0], a0[2]), sc[0][0]);
           sc[0][1] = fmaf(ScaleOf(ks_raw[0][1], b), JoinPlanes(a0[1], a0[3]), sc[0][1]);
           sc[1][0] = fmaf(ScaleOf(ks_raw[1][0], b), JoinPlanes(a1[0], a1[2]), sc[1][0]);
@@ -320,16 +373,19 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
 #pragma unroll
         for (int bp = 0; bp < 2; ++bp) {
           std::uint32_t w[4];
-          LdMatrixX4(k_base + (dh ? lm_off[2 + bp] : lm_off[bp]), w);
+          LdMatrixX4(k_base + lm_off(2 * dh + bp), w);
 #pragma unroll
           for (int hb = 0; hb < 2; ++hb) {
             const int b = 2 * bp + hb;   // block 4 dh + b
+            std::uint32_t qa[4];
+            LoadQ(qa, qa_addr + (4 * dh + b) * (kQLanes * 16));
+            const int2 corr = q_corr[(4 * dh + b) * 8 + (qlane >> 2)];
             int a0[4], a1[4];
             std::uint32_t lo, hi;
-            Nib8ToInt8(w[2 * hb], lo, hi);
-            MmaQK(a0, qa_addr + b * (kQLanes * 16), lo, hi);
-            Nib8ToInt8(w[2 * hb + 1], lo, hi);
-            MmaQK(a1, qa_addr + b * (kQLanes * 16), lo, hi);
+            Nib8ToU8(w[2 * hb], lo, hi);
+            MmaQKU8(a0, qa, lo, hi, corr.x, corr.y);
+            Nib8ToU8(w[2 * hb + 1], lo, hi);
+            MmaQKU8(a1, qa, lo, hi, corr.x, corr.y);
             sc[0][0] = fmaf(ScaleOf(ks_raw[0][0], b), JoinPlanes(a0[0], a0[2]), sc[0][0]);
             sc[0][1] = fmaf(ScaleOf(ks_raw[0][1], b), JoinPlanes(a0[1], a0[3]), sc[0][1]);
             sc[1][0] = fmaf(ScaleOf(ks_raw[1][0], b), JoinPlanes(a1[0], a1[2]), sc[1][0]);
@@ -338,34 +394,25 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
         }
       }
     }
-    // Swap the partial sums with the warp that holds the other 128 dims: write, pair barrier, read, pair barrier
-    // (the second one keeps the next page's write behind this page's read). a + b == b + a, so both warps continue
-    // with identical scores.
-    {
-      if (lane < kQLanes) xchg[warp * kQLanes + lane] = make_float4(sc[0][0], sc[0][1], sc[1][0], sc[1][1]);
-      NamedBarrierSync(1 + kw, 64);
-      if (lane < kQLanes) {
-        const float4 o = xchg[(warp ^ 1) * kQLanes + lane];
-        sc[0][0] += o.x, sc[0][1] += o.y, sc[1][0] += o.z, sc[1][1] += o.w;
-      }
-      NamedBarrierSync(1 + kw, 64);
-    }
 
     // ---- softmax statistics (per head g, the 16 keys spread over the four lanes of a quad) ----
-    const int key_pos0 = (u.page_begin + i) * kPageTokens + my_key0;
     float tmax = -INFINITY;
 #pragma unroll
     for (int kt = 0; kt < 2; ++kt)
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        sc[kt][j] *= score_scale;
-        if (key_pos0 + kt * 8 + j >= u.n_keys) sc[kt][j] = -INFINITY;   // only ever true on a sequence's last page
-        tmax = fmaxf(tmax, sc[kt][j]);
-      }
+      for (int j = 0; j < 2; ++j) sc[kt][j] *= score_scale;
+    if ((u.page_begin + i + 1) * kPageTokens > u.n_keys) {   // only ever true on a sequence's last page
+      const int key_pos0 = (u.page_begin + i) * kPageTokens + my_key0;
+#pragma unroll
+      for (int kt = 0; kt < 2; ++kt)
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+          if (key_pos0 + kt * 8 + j >= u.n_keys) sc[kt][j] = -INFINITY;
+    }
+    tmax = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
     tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFU, tmax, 1));
     tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFU, tmax, 2));
-    // Only the six real heads vote: the padding lanes hold unexchanged partial scores that differ between the two
-    // warps of a pair, and both warps must take the same decision to keep one running max per key group.
+    // Only the six real heads vote: the padding lanes hold duplicates.
     if (__any_sync(0xFFFFFFFFU, lane < kQLanes && tmax > m_run + kLazyRescale)) {
       const float m_new = fmaxf(m_run, tmax);
       const float alpha = m_new == -INFINITY ? 1.0F : Exp2Fast(m_run - m_new);  // m_run = -inf gives 0
@@ -374,7 +421,7 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
       const float al0 = __shfl_sync(0xFFFFFFFFU, alpha, (2 * t) * 4);
       const float al1 = __shfl_sync(0xFFFFFFFFU, alpha, (2 * t + 1) * 4);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 16; ++c) {
         o_acc[c][0] *= al0, o_acc[c][2] *= al0;
         o_acc[c][1] *= al1, o_acc[c][3] *= al1;
       }
@@ -391,74 +438,77 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
       p_lo[kt] = __floats2half2_rn(p0 - hf.x, p1 - hf.y);
     }
 
-    // ---- O^T += V^T P^T over this warp's 128 dims, the V scale of (key, block) folded into the weights ----
-    uint2 vs_raw[2][2];
+    // ---- O^T += V^T P^T, the V scale of (key, block) folded into the weights ----
 #pragma unroll
-    for (int kt = 0; kt < 2; ++kt)
+    for (int dh = 0; dh < 2; ++dh) {
+      uint2 vs_raw[2][2];
 #pragma unroll
-      for (int j = 0; j < 2; ++j)
-        vs_raw[kt][j] = *reinterpret_cast<const uint2*>(st + L::kVsOff + (my_key0 + kt * 8 + j) * 16 + dh * 8);
-    // weight x scale without leaving fp16: hi = round(p_hi d); the rounding error of that product is recovered
-    // exactly by an fma and joins the low part: lo = p_lo d + (p_hi d - hi).
-    auto weights = [&](int b, std::uint32_t (&hi)[2], std::uint32_t (&lo)[2]) {
+      for (int kt = 0; kt < 2; ++kt)
 #pragma unroll
-      for (int kt = 0; kt < 2; ++kt) {
-        const std::uint32_t w0 = b < 2 ? vs_raw[kt][0].x : vs_raw[kt][0].y;
-        const std::uint32_t w1 = b < 2 ? vs_raw[kt][1].x : vs_raw[kt][1].y;
-        const std::uint32_t dw = __byte_perm(w0, w1, (b & 1) ? 0x7632 : 0x5410);
-        const __half2 d2 = *reinterpret_cast<const __half2*>(&dw);
-        const __half2 h = __hmul2(p_hi[kt], d2);
-        const __half2 r = __hfma2(p_hi[kt], d2, __hneg2(h));
-        const __half2 l = __hfma2(p_lo[kt], d2, r);
-        hi[kt] = *reinterpret_cast<const std::uint32_t*>(&h);
-        lo[kt] = *reinterpret_cast<const std::uint32_t*>(&l);
-      }
-    };
-    if constexpr (kFmt == kFmtQ8) {
+        for (int j = 0; j < 2; ++j)
+          vs_raw[kt][j] = *reinterpret_cast<const uint2*>(st + L::kVsOff + (my_key0 + kt * 8 + j) * 16 + dh * 8);
+      // weight x scale without leaving fp16: hi = round(p_hi d); the rounding error of that product is recovered
+      // exactly by an fma and joins the low part: lo = p_lo d + (p_hi d - hi).
+      auto weights = [&](int b, std::uint32_t (&hi)[2], std::uint32_t (&lo)[2]) {
 #pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        std::uint32_t hi[2], lo[2];
-        weights(b, hi, lo);
-        std::uint32_t w[4];
-        LdMatrixX4Trans(v_base + lm_off[b], w);
-        std::uint32_t a0, a1, a2, a3;
-        Offset8x4ToHalf2(w[0], a0, a1);
-        Offset8x4ToHalf2(w[1], a2, a3);
-        MmaF16(o_acc[2 * b], a0, a1, a2, a3, hi[0], hi[1]);
-        MmaF16(o_acc[2 * b], a0, a1, a2, a3, lo[0], lo[1]);
-        Offset8x4ToHalf2(w[2], a0, a1);
-        Offset8x4ToHalf2(w[3], a2, a3);
-        MmaF16(o_acc[2 * b + 1], a0, a1, a2, a3, hi[0], hi[1]);
-        MmaF16(o_acc[2 * b + 1], a0, a1, a2, a3, lo[0], lo[1]);
-      }
-    } else {
+        for (int kt = 0; kt < 2; ++kt) {
+          const std::uint32_t w0 = b < 2 ? vs_raw[kt][0].x : vs_raw[kt][0].y;
+          const std::uint32_t w1 = b < 2 ? vs_raw[kt][1].x : vs_raw[kt][1].y;
+          const std::uint32_t dw = __byte_perm(w0, w1, (b & 1) ? 0x7632 : 0x5410);
+          const __half2 d2 = *reinterpret_cast<const __half2*>(&dw);
+          const __half2 h = __hmul2(p_hi[kt], d2);
+          const __half2 r = __hfma2(p_hi[kt], d2, __hneg2(h));
+          const __half2 l = __hfma2(p_lo[kt], d2, r);
+          hi[kt] = *reinterpret_cast<const std::uint32_t*>(&h);
+          lo[kt] = *reinterpret_cast<const std::uint32_t*>(&l);
+        }
+      };
+      if constexpr (kFmt == kFmtQ8) {
 #pragma unroll
-      for (int bp = 0; bp < 2; ++bp) {
-        std::uint32_t w[4];
-        LdMatrixX4Trans(v_base + (dh ? lm_off[2 + bp] : lm_off[bp]), w);
-#pragma unroll
-        for (int hb = 0; hb < 2; ++hb) {
-          const int b = 2 * bp + hb;
+        for (int b = 0; b < 4; ++b) {
           std::uint32_t hi[2], lo[2];
           weights(b, hi, lo);
-          std::uint32_t la0, la1, ha0, ha1, la2, la3, ha2, ha3;
-          Nib4x4ToHalf2(w[2 * hb], la0, la1, ha0, ha1);      // keys 0-7 of the group's 16
-          Nib4x4ToHalf2(w[2 * hb + 1], la2, la3, ha2, ha3);  // keys 8-15
-          MmaF16(o_acc[2 * b], la0, la1, la2, la3, hi[0], hi[1]);
-          MmaF16(o_acc[2 * b], la0, la1, la2, la3, lo[0], lo[1]);
-          MmaF16(o_acc[2 * b + 1], ha0, ha1, ha2, ha3, hi[0], hi[1]);
-          MmaF16(o_acc[2 * b + 1], ha0, ha1, ha2, ha3, lo[0], lo[1]);
+          std::uint32_t w[4];
+          LdMatrixX4Trans(v_base + dh * kBoxBytes + lm_off(b), w);
+          std::uint32_t a0, a1, a2, a3;
+          Offset8x4ToHalf2(w[0], a0, a1);
+          Offset8x4ToHalf2(w[1], a2, a3);
+          MmaF16(o_acc[8 * dh + 2 * b], a0, a1, a2, a3, hi[0], hi[1]);
+          MmaF16(o_acc[8 * dh + 2 * b], a0, a1, a2, a3, lo[0], lo[1]);
+          Offset8x4ToHalf2(w[2], a0, a1);
+          Offset8x4ToHalf2(w[3], a2, a3);
+          MmaF16(o_acc[8 * dh + 2 * b + 1], a0, a1, a2, a3, hi[0], hi[1]);
+          MmaF16(o_acc[8 * dh + 2 * b + 1], a0, a1, a2, a3, lo[0], lo[1]);
+        }
+      } else {
+#pragma unroll
+        for (int bp = 0; bp < 2; ++bp) {
+          std::uint32_t w[4];
+          LdMatrixX4Trans(v_base + lm_off(2 * dh + bp), w);
+#pragma unroll
+          for (int hb = 0; hb < 2; ++hb) {
+            const int b = 2 * bp + hb;
+            std::uint32_t hi[2], lo[2];
+            weights(b, hi, lo);
+            std::uint32_t la0, la1, ha0, ha1, la2, la3, ha2, ha3;
+            Nib4x4ToHalf2(nib, w[2 * hb], la0, la1, ha0, ha1);      // keys 0-7 of the group's 16
+            Nib4x4ToHalf2(nib, w[2 * hb + 1], la2, la3, ha2, ha3);  // keys 8-15
+            MmaF16(o_acc[8 * dh + 2 * b], la0, la1, la2, la3, hi[0], hi[1]);
+            MmaF16(o_acc[8 * dh + 2 * b], la0, la1, la2, la3, lo[0], lo[1]);
+            MmaF16(o_acc[8 * dh + 2 * b + 1], ha0, ha1, ha2, ha3, hi[0], hi[1]);
+            MmaF16(o_acc[8 * dh + 2 * b + 1], ha0, ha1, ha2, ha3, lo[0], lo[1]);
+          }
         }
       }
     }
 
-    // The last of the eight warps to finish with the stage refills it (no warp ever waits for another one). The
-    // MMAs above consumed every ldmatrix result, so this warp's reads of the stage are complete.
+    // The last of the page's four warps to finish with the stage refills it (no warp ever waits for another one).
+    // The MMAs above consumed every ldmatrix result, so this warp's reads of the stage are complete.
     __syncwarp();
     int last = 0;
     if (lane == 0) {
       __threadfence_block();
-      last = atomicAdd(&done_cnt[s], 1) == kWarps - 1;
+      last = atomicAdd(&done_cnt[s], 1) == kKeyGroups - 1;
       if (last) {
         done_cnt[s] = 0;
         __threadfence_block();
@@ -466,7 +516,6 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
     }
     last = __shfl_sync(0xFFFFFFFFU, last, 0);
     if (last != 0 && i + L::kStages < n_pages) issue(s, __shfl_sync(0xFFFFFFFFU, refill_page, 0));
-    if (++s == L::kStages) s = 0, phase ^= 1U;
   }
   if (!alive && lane == 0) atomicExch(status, kStatusWaitTimeout);
   l_run += __shfl_xor_sync(0xFFFFFFFFU, l_run, 1);
@@ -485,9 +534,9 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
   }
   float* merge = reinterpret_cast<float*>(ring);
   {
-    float* mine = merge + kw * kMergeGroupFloats + 128 * dh;
+    float* mine = merge + warp * kMergeGroupFloats;
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
+    for (int c = 0; c < 16; ++c) {
       // o_acc[c][0..3] = (dim 16c + 2g, head 2t), (dim 16c + 2g, head 2t+1), (dim 16c + 2g + 1, head 2t), (.., 2t+1)
       if (2 * t < kGroup) {
         *reinterpret_cast<float2*>(mine + (2 * t) * kMergeStride + 16 * c + 2 * g) =
@@ -496,8 +545,8 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
             make_float2(o_acc[c][1], o_acc[c][3]);
       }
     }
-    if (dh == 0 && t == 0 && g < kGroup) {
-      float* ml = merge + kw * kMergeGroupFloats + kGroup * kMergeStride;
+    if (t == 0 && g < kGroup) {
+      float* ml = mine + kGroup * kMergeStride;
       ml[2 * g] = m_run;
       ml[2 * g + 1] = l_run;
     }
@@ -509,15 +558,15 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
     float* ml_out = partial_ml + static_cast<std::size_t>(u.partial) * kPartialMlFloats;
 #pragma unroll
     for (int h = 0; h < kGroup; ++h) {
-      float mw[kKeyGroups], M = -INFINITY;
+      float mw[kWarps], M = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < kKeyGroups; ++w) {
+      for (int w = 0; w < kWarps; ++w) {
         mw[w] = merge[w * kMergeGroupFloats + kGroup * kMergeStride + 2 * h];
         M = fmaxf(M, mw[w]);
       }
       float a = 0.0F, lsum = 0.0F;
 #pragma unroll
-      for (int w = 0; w < kKeyGroups; ++w) {
+      for (int w = 0; w < kWarps; ++w) {   // a warp that saw no page has max -inf and weight 0
         const float wgt = mw[w] == -INFINITY ? 0.0F : exp2f(mw[w] - M);
         const float* src = merge + w * kMergeGroupFloats;
         a = fmaf(wgt, src[h * kMergeStride + tid], a);

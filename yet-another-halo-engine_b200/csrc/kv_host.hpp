@@ -55,6 +55,8 @@ class KvHost {
     if (c.max_seqs < 1 || c.max_pages_per_seq < 1) return bad("max_seqs and max_pages_per_seq must be positive");
     if (c.max_splits < 0 || c.max_batch_tokens < 0) return bad("max_splits and max_batch_tokens must not be negative");
     static_assert(kCombineMaxUnits == 1024, "the message below names the limit");
+    if (c.max_prefill_keys < 0 || 1LL * c.max_prefill_keys * kKvHeads >= (1LL << 31))
+      return bad("max_prefill_keys out of range");
     if (c.max_splits > kCombineMaxUnits) return bad("max_splits must not exceed 1024 (the combine kernel's unit limit)");
     if (c.kv_head_begin < 0 || c.kv_head_count < 0 || c.kv_head_begin + c.kv_head_count > kKvHeads ||
         (c.kv_head_count == 0 && c.kv_head_begin != 0))

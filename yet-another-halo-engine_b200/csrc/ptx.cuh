@@ -140,26 +140,41 @@ __device__ __forceinline__ void Offset8x4ToHalf2(std::uint32_t u, std::uint32_t&
   h02 = *reinterpret_cast<const std::uint32_t*>(&a);
   h13 = *reinterpret_cast<const std::uint32_t*>(&b);
 }
-// Four packed q4_0 bytes -> the int8 values 16 (n - 8) of their low nibbles (byte order kept) and of their high
-// nibbles: a nibble moved to the top of its byte is 16 n as an unsigned byte, and flipping the byte's sign bit
-// subtracts 128.
-__device__ __forceinline__ void Nib8ToInt8(std::uint32_t w, std::uint32_t& lo, std::uint32_t& hi) {
-  lo = ((w << 4) & 0xF0F0F0F0U) ^ 0x80808080U;
-  hi = (w & 0xF0F0F0F0U) ^ 0x80808080U;
+// Four packed q4_0 bytes -> the unsigned bytes 16 n of their low nibbles (byte order kept) and of their high
+// nibbles: a nibble moved to the top of its byte. Three instructions, each with one immediate.
+__device__ __forceinline__ void Nib8ToU8(std::uint32_t w, std::uint32_t& lo, std::uint32_t& hi) {
+  lo = (w << 4) & 0xF0F0F0F0U;
+  hi = w & 0xF0F0F0F0U;
 }
+// d = (a & b) | c as ONE logic instruction with all three inputs in registers. Written as a & imm | imm the compiler
+// must split it (an instruction carries one immediate), which doubles the cost of every nibble conversion.
+__device__ __forceinline__ std::uint32_t AndOr(std::uint32_t a, std::uint32_t b, std::uint32_t c) {
+  std::uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+// The three constants of the nibble conversion, held in registers the compiler cannot turn back into immediates.
+struct NibConsts {
+  std::uint32_t lo_mask, hi_mask, magic;
+  __device__ __forceinline__ void Load() {
+    asm volatile("mov.u32 %0, 0x000F000F;" : "=r"(lo_mask));
+    asm volatile("mov.u32 %0, 0x00F000F0;" : "=r"(hi_mask));
+    asm volatile("mov.u32 %0, 0x64006400;" : "=r"(magic));
+  }
+};
 // Four packed q4_0 bytes -> low nibbles of bytes (0,2), (1,3) and high nibbles of bytes (0,2), (1,3), each minus 8.
-__device__ __forceinline__ void Nib4x4ToHalf2(std::uint32_t w, std::uint32_t& l02, std::uint32_t& l13,
-                                              std::uint32_t& h02, std::uint32_t& h13) {
+__device__ __forceinline__ void Nib4x4ToHalf2(const NibConsts& k, std::uint32_t w, std::uint32_t& l02,
+                                              std::uint32_t& l13, std::uint32_t& h02, std::uint32_t& h13) {
   // Low nibbles: 0x6400 | n is the fp16 1024 + n, minus 1032. High nibbles stay where they are: 0x6400 | (n << 4) is
   // 1024 + 16 n, and (1024 + 16 n) / 16 - 72 = n - 8 in one exact fma, which saves the two shifts by 4.
   const __half2 bias = __halves2half2(__ushort_as_half(0x6408), __ushort_as_half(0x6408));  // 1032
   const __half2 sixteenth = __halves2half2(__ushort_as_half(0x2C00), __ushort_as_half(0x2C00));  // 1 / 16
   const __half2 bias_hi = __halves2half2(__ushort_as_half(0xD480), __ushort_as_half(0xD480));    // -72
   const std::uint32_t w8 = w >> 8;
-  const std::uint32_t a = (w & 0x000F000FU) | 0x64006400U;
-  const std::uint32_t b = (w8 & 0x000F000FU) | 0x64006400U;
-  const std::uint32_t c = (w & 0x00F000F0U) | 0x64006400U;
-  const std::uint32_t d = (w8 & 0x00F000F0U) | 0x64006400U;
+  const std::uint32_t a = AndOr(w, k.lo_mask, k.magic);
+  const std::uint32_t b = AndOr(w8, k.lo_mask, k.magic);
+  const std::uint32_t c = AndOr(w, k.hi_mask, k.magic);
+  const std::uint32_t d = AndOr(w8, k.hi_mask, k.magic);
   const __half2 ra = __hsub2(*reinterpret_cast<const __half2*>(&a), bias);
   const __half2 rb = __hsub2(*reinterpret_cast<const __half2*>(&b), bias);
   const __half2 rc = __hfma2(*reinterpret_cast<const __half2*>(&c), sixteenth, bias_hi);

@@ -172,6 +172,7 @@ cudaError_t DevAlloc(yahkv_ctx* ctx, T** p, std::size_t count, bool zero) {
 }
 
 EncodeTiledFn g_encode = nullptr;   // cuTensorMapEncodeTiled, fetched once per process
+int ResizePrefillScratch(yahkv_ctx* ctx, std::int64_t rows);
 
 int EncodeMap(yahkv_ctx* ctx, EncodeTiledFn encode, CUtensorMap* map, void* base) {
   const cuuint64_t row_bytes = static_cast<cuuint64_t>(CodeBytes(ctx->cfg.fmt));
@@ -253,6 +254,8 @@ int InitDevice(yahkv_ctx* ctx) {
   g_encode = encode;
   if (int r = EncodeMap(ctx, encode, &ctx->kmap, ctx->pool.kcodes); r != YAHKV_OK) return r;
   if (int r = EncodeMap(ctx, encode, &ctx->vmap, ctx->pool.vcodes); r != YAHKV_OK) return r;
+  if (c.max_prefill_keys > 0)
+    if (int r = ResizePrefillScratch(ctx, static_cast<std::int64_t>(c.max_prefill_keys) * kKvHeads); r != YAHKV_OK) return r;
   YAHKV_CUDA(ctx, ConfigureDecodeKernels());
   YAHKV_CUDA(ctx, ConfigurePrefillKernels());
   YAHKV_CUDA(ctx, cudaDeviceSynchronize());
@@ -366,6 +369,22 @@ int FlushTables(yahkv_ctx* ctx, cudaStream_t stream) {
     off += bytes;
   }
   if (cudaError_t e = ctx->staging.Release(stream); e != cudaSuccess) return fail("table staging event", e);
+  return YAHKV_OK;
+}
+
+// (Re)allocates the fp16 K and V scratch of the prefill dequantize pass for `rows` token rows and encodes its maps.
+int ResizePrefillScratch(yahkv_ctx* ctx, std::int64_t rows) {
+  if (ctx->k16_dev != nullptr) cudaFree(ctx->k16_dev), ctx->device_bytes -= ctx->p16_rows * kHeadDim * 2;
+  if (ctx->v16_dev != nullptr) cudaFree(ctx->v16_dev), ctx->device_bytes -= ctx->p16_rows * kHeadDim * 2;
+  ctx->k16_dev = ctx->v16_dev = nullptr, ctx->p16_rows = 0;
+  const std::size_t bytes = static_cast<std::size_t>(rows) * kHeadDim * 2;
+  YAHKV_CUDA(ctx, cudaMalloc(&ctx->k16_dev, bytes));
+  YAHKV_CUDA(ctx, cudaMalloc(&ctx->v16_dev, bytes));
+  ctx->device_bytes += 2 * static_cast<std::int64_t>(bytes);
+  ctx->p16_rows = rows;
+  if (!EncodeTensorMap2D(&ctx->k16map, 2, ctx->k16_dev, kHeadDim, static_cast<std::uint64_t>(rows), 64, 64) ||
+      !EncodeTensorMap2D(&ctx->v16map, 2, ctx->v16_dev, kHeadDim, static_cast<std::uint64_t>(rows), 64, 64))
+    return Fail(ctx, YAHKV_ERR_CUDA, "tensor map encode failed for the prefill scratch");
   return YAHKV_OK;
 }
 
@@ -671,20 +690,14 @@ int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const in
   if (ctx->tile_scratch.empty()) return YAHKV_OK;
   if (static_cast<int>(ctx->tile_scratch.size()) > ctx->max_tiles) return Fail(ctx, YAHKV_ERR_CAPACITY, "attend_prefill: too many tiles");
   cudaStream_t st = StreamOf(ctx, stream);
-  // The fp16 scratch of the dequantize pass grows to the largest call seen (a one-time cost per high-water mark).
+  // The fp16 scratch of the dequantize pass: fixed at create when the configuration sizes it, else grown to the
+  // largest call seen (a one-time cost per high-water mark, with a device synchronisation).
   if (scratch_rows > ctx->p16_rows) {
+    if (ctx->cfg.max_prefill_keys > 0)
+      return Fail(ctx, YAHKV_ERR_CAPACITY, "attend_prefill: the call covers " + std::to_string(scratch_rows / kKvHeads) +
+                                               " cached keys, max_prefill_keys is " + std::to_string(ctx->cfg.max_prefill_keys));
     YAHKV_CUDA(ctx, cudaDeviceSynchronize());
-    if (ctx->k16_dev != nullptr) cudaFree(ctx->k16_dev), ctx->device_bytes -= ctx->p16_rows * kHeadDim * 2;
-    if (ctx->v16_dev != nullptr) cudaFree(ctx->v16_dev), ctx->device_bytes -= ctx->p16_rows * kHeadDim * 2;
-    ctx->k16_dev = ctx->v16_dev = nullptr, ctx->p16_rows = 0;
-    const std::size_t bytes = static_cast<std::size_t>(scratch_rows) * kHeadDim * 2;
-    YAHKV_CUDA(ctx, cudaMalloc(&ctx->k16_dev, bytes));
-    YAHKV_CUDA(ctx, cudaMalloc(&ctx->v16_dev, bytes));
-    ctx->device_bytes += 2 * static_cast<std::int64_t>(bytes);
-    ctx->p16_rows = scratch_rows;
-    if (!EncodeTensorMap2D(&ctx->k16map, 2, ctx->k16_dev, kHeadDim, static_cast<std::uint64_t>(scratch_rows), 64, 64) ||
-        !EncodeTensorMap2D(&ctx->v16map, 2, ctx->v16_dev, kHeadDim, static_cast<std::uint64_t>(scratch_rows), 64, 64))
-      return Fail(ctx, YAHKV_ERR_CUDA, "attend_prefill: tensor map encode failed for the fp16 scratch");
+    if (int r = ResizePrefillScratch(ctx, scratch_rows); r != YAHKV_OK) return r;
   }
   if (int r = FlushTables(ctx, st); r != YAHKV_OK) return r;
   {

@@ -53,6 +53,7 @@ class Config(ctypes.Structure):
         ("softmax_scale", ctypes.c_float),
         ("kv_head_begin", ctypes.c_int32),
         ("kv_head_count", ctypes.c_int32),
+        ("max_prefill_keys", ctypes.c_int32),
     ]
 
 
@@ -258,9 +259,10 @@ class KvCache:
 
     def __init__(self, *, device=0, n_layers=1, num_pages=64, fmt=FMT_Q8_0, max_seqs=8, max_pages_per_seq=64,
                  max_splits=0, max_batch_tokens=0, softmax_scale=0.0, n_q_heads=Q_HEADS, n_kv_heads=KV_HEADS,
-                 head_dim=HEAD_DIM, page_tokens=PAGE_TOKENS, kv_head_begin=0, kv_head_count=0):
+                 head_dim=HEAD_DIM, page_tokens=PAGE_TOKENS, kv_head_begin=0, kv_head_count=0, max_prefill_keys=0):
         self.cfg = Config(device, n_layers, n_q_heads, n_kv_heads, head_dim, page_tokens, num_pages, fmt, max_seqs,
-                          max_pages_per_seq, max_splits, max_batch_tokens, softmax_scale, kv_head_begin, kv_head_count)
+                          max_pages_per_seq, max_splits, max_batch_tokens, softmax_scale, kv_head_begin, kv_head_count,
+                          max_prefill_keys)
         self.fmt = fmt
         self._h = ctypes.c_void_p()
         rc = lib.yahkv_create(ctypes.byref(self.cfg), ctypes.byref(self._h))
