@@ -35,6 +35,21 @@ extern "C" {
 
 #define YAHKV_FMT_Q8_0 0
 #define YAHKV_FMT_Q4_0 1
+/* The reference's own kv8a16 cache format (engine/gpu/loom/tools/gen_kvq.py:166-285, :474-660;
+ * docs/architecture.md:210-230), on 64-token pages of four 16-key tiles (the reference uses 256-token pages):
+ *   K  per token, minus a per-channel mean fixed per (sequence, layer): per (head, 128-dim half) an int8 scale,
+ *      codes u = roundeven((k - mean) / s) + 128, dwords of four dims in byte slots (d0, d2, d1, d3), fp16 pair
+ *      (256 s, -384 s);  pools: codes [page][4][64][256 B], pairs [page][4][64][2][2] fp16.
+ *   V  per (16-key tile, channel): centre and scale over the tile's keys, codes in four dwords per channel
+ *      (dword w byte p = key 4w + (0, 2, 1, 3)[p]), fp16 pair (256 sf, cf - 384 sf);
+ *      pools: codes [page][4][4 tiles][256][16 B], pairs [page][4][4][256][2] fp16.
+ *   The tile of a sequence's newest key stays in fp16 (the "open tile", engine/gpu/loom/tools/gen_decode_attn.py:426-427)
+ *   and attention reads it from there; a tile is quantized when its 16th key arrives.
+ * 2336 B per token per layer. Supported with this format: yahkv_append, yahkv_attend_decode, the host-buffer decode
+ * steps, yahkv_read_page / yahkv_write_page, yahkv_seq_set_kmean, yahkv_read_open_tile. Not supported (refused with
+ * YAHKV_ERR_INVALID): prefill attention, the fused RoPE append, decode batches, snapshots, yahkv_export_token,
+ * head-sharded contexts, and yahkv_seq_set_len to anything but 0. */
+#define YAHKV_FMT_KV8A16 2
 
 #define YAHKV_SIDE_K 0
 #define YAHKV_SIDE_V 1
@@ -108,6 +123,15 @@ int yahkv_seq_len(const yahkv_ctx* ctx, int32_t seq, int32_t layer, int64_t* len
 /* Declare the length (after yahkv_append_slots, or to roll a sequence back to a prefix). layer -1 = all layers. */
 int yahkv_seq_set_len(yahkv_ctx* ctx, int32_t seq, int32_t layer, int64_t len);
 int yahkv_pages_free(const yahkv_ctx* ctx, int32_t* n);
+/* YAHKV_FMT_KV8A16 only. Sets the per-channel K mean of a sequence in one layer (layer -1 = all): mean_host [4][256]
+ * f32, subtracted from every K row before it is quantized. Replaces the reference's yah_kmean dispatch
+ * (engine/gpu/loom/tools/gen_kvq.py:99-163, computed there from the first prefill chunk; zeros when the decoder owns
+ * the state, engine/model/loom_decoder.hpp:46): here the caller supplies it, before the sequence's first append;
+ * a fresh sequence has mean 0. Blocks. */
+int yahkv_seq_set_kmean(yahkv_ctx* ctx, int32_t seq, int32_t layer, const float* mean_host);
+/* YAHKV_FMT_KV8A16 only (inspection): the current open tile of (seq, layer) as [4][256][16] fp16; key j of the tile
+ * that holds the newest position is column j, columns past the sequence's length are stale. Blocks. */
+int yahkv_read_open_tile(yahkv_ctx* ctx, int32_t seq, int32_t layer, void* tile_host);
 
 /* ---- hot path (asynchronous on `stream`, a cudaStream_t; NULL = the context's own stream) -------------------- */
 
@@ -168,7 +192,8 @@ int yahkv_decode_step_host_wait(yahkv_ctx* ctx);
 /* ---- inspection (parity tests, checkpoints); these block until the context's queued work is done ------------- */
 
 /* One page record of one layer and side: codes [4][64][256|128] bytes to codes_host, scales [4][64][8] fp16 to
- * scales_host (either may be NULL). The reference's checkers read whole pools back the same way
+ * scales_host (either may be NULL). YAHKV_FMT_KV8A16: K codes [4][64][256], K pairs [4][64][2][2] fp16; V codes
+ * [4][4][256][16], V pairs [4][4][256][2] fp16. The reference's checkers read whole pools back the same way
  * (engine/gpu/loom/tools/dattn_q_check.py:219-220). */
 int yahkv_read_page(yahkv_ctx* ctx, int32_t layer, int32_t side, int32_t page, void* codes_host, void* scales_host);
 int yahkv_write_page(yahkv_ctx* ctx, int32_t layer, int32_t side, int32_t page, const void* codes_host,

@@ -17,7 +17,7 @@ ORACLE_SO = os.path.join(_HERE, "libyahkv_oracle.so")
 REF_SO = os.path.join(_HERE, "_ref", "libyah_ref_codec.so")
 
 Q_HEADS, KV_HEADS, HEAD_DIM, PAGE_TOKENS, BLOCKS = 24, 4, 256, 64, 8
-FMT_Q8_0, FMT_Q4_0 = 0, 1
+FMT_Q8_0, FMT_Q4_0, FMT_KV8A16 = 0, 1, 2
 GGML_Q4_0, GGML_Q8_0 = 2, 8  # ggml type ids the reference's Dequantize takes
 
 
@@ -181,4 +181,72 @@ class PagedPool:
                                            _p(self.vcodes), _p(self.vscales), _p(table), len(table),
                                            ctypes.c_int64(start), n_q, q_begin, q_end, _p(q.view(np.uint16)),
                                            _p(gate), ctypes.c_double(scale), _p(out), threads)
+        return out
+
+
+# ---- the reference's own kv8a16 format (oracle/kv8a16_oracle.cpp) ------------------------------------------------
+def kv8_quant_k(k_row, mean):
+    """One token's K [4][256] fp16 and the channel mean [4][256] f32 -> (codes [4][256] u8, scale pairs [4][2][2] u16)."""
+    k_row = np.ascontiguousarray(k_row, np.float16).reshape(KV_HEADS, HEAD_DIM)
+    mean = np.ascontiguousarray(mean, np.float32).reshape(KV_HEADS, HEAD_DIM)
+    codes, scales = np.zeros((KV_HEADS, HEAD_DIM), np.uint8), np.zeros((KV_HEADS, 2, 2), np.uint16)
+    _o.yahkv_oracle_kv8_quant_k(_p(k_row.view(np.uint16)), _p(mean), _p(codes), _p(scales))
+    return codes, scales
+
+
+def kv8_deq_k(codes, scales):
+    out = np.zeros((KV_HEADS, HEAD_DIM), np.float32)
+    _o.yahkv_oracle_kv8_deq_k(_p(np.ascontiguousarray(codes, np.uint8)), _p(np.ascontiguousarray(scales, np.uint16)), _p(out))
+    return out
+
+
+def kv8_quant_vtile(v_tile):
+    """v [16 keys][4][256] fp16 -> (codes [4][256][16] u8, stat pairs [4][256][2] u16)."""
+    v_tile = np.ascontiguousarray(v_tile, np.float16).reshape(16, KV_HEADS, HEAD_DIM)
+    codes, stats = np.zeros((KV_HEADS, HEAD_DIM, 16), np.uint8), np.zeros((KV_HEADS, HEAD_DIM, 2), np.uint16)
+    _o.yahkv_oracle_kv8_quant_vtile(_p(v_tile.view(np.uint16)), _p(codes), _p(stats))
+    return codes, stats
+
+
+def kv8_deq_vtile(codes, stats):
+    out = np.zeros((16, KV_HEADS, HEAD_DIM), np.float32)
+    _o.yahkv_oracle_kv8_deq_vtile(_p(np.ascontiguousarray(codes, np.uint8)), _p(np.ascontiguousarray(stats, np.uint16)), _p(out))
+    return out
+
+
+class Kv8Pool:
+    """One layer's kv8a16 pools on the host in the library's layout (64-token pages of four 16-key tiles). Sequence
+    state that the format needs beyond the pools (the open fp16 V tile, the K channel mean) is the caller's: see
+    `new_sequence`."""
+
+    def __init__(self, num_pages):
+        self.num_pages = num_pages
+        self.kcodes = np.zeros((num_pages, KV_HEADS, PAGE_TOKENS, HEAD_DIM), np.uint8)
+        self.kscales = np.zeros((num_pages, KV_HEADS, PAGE_TOKENS, 2, 2), np.uint16)
+        self.vcodes = np.zeros((num_pages, KV_HEADS, PAGE_TOKENS // 16, HEAD_DIM, 16), np.uint8)
+        self.vstats = np.zeros((num_pages, KV_HEADS, PAGE_TOKENS // 16, HEAD_DIM, 2), np.uint16)
+
+    @staticmethod
+    def new_sequence(mean=None):
+        """(open tile [4][256][16] fp16 as u16, mean [4][256] f32) of a fresh sequence."""
+        m = np.zeros((KV_HEADS, HEAD_DIM), np.float32) if mean is None else np.ascontiguousarray(mean, np.float32).reshape(KV_HEADS, HEAD_DIM).copy()
+        return np.zeros((KV_HEADS, HEAD_DIM, 16), np.uint16), m
+
+    def append(self, table, pos0, k, v, open_tile, mean):
+        table = np.ascontiguousarray(table, np.int32)
+        k = np.ascontiguousarray(k, np.float16)
+        v = np.ascontiguousarray(v, np.float16)
+        _o.yahkv_oracle_kv8_append_seq(PAGE_TOKENS, self.num_pages, _p(self.kcodes), _p(self.kscales), _p(self.vcodes),
+                                       _p(self.vstats), _p(open_tile), _p(mean), _p(table), len(table),
+                                       ctypes.c_int64(pos0), k.shape[0], _p(k.view(np.uint16)), _p(v.view(np.uint16)))
+
+    def attend_decode_f64(self, table, n_keys, q, open_tile, gate=None, scale=1.0 / 16.0, threads=THREADS):
+        table = np.ascontiguousarray(table, np.int32)
+        q = np.ascontiguousarray(q, np.float16)
+        gate = None if gate is None else np.ascontiguousarray(gate, np.float32)
+        out = np.zeros((Q_HEADS, HEAD_DIM), np.float64)
+        _o.yahkv_oracle_kv8_attend_decode_f64(PAGE_TOKENS, self.num_pages, _p(self.kcodes), _p(self.kscales),
+                                              _p(self.vcodes), _p(self.vstats), _p(open_tile), _p(table), len(table),
+                                              ctypes.c_int64(n_keys), _p(q.view(np.uint16)), _p(gate),
+                                              ctypes.c_double(scale), _p(out), threads)
         return out

@@ -37,3 +37,16 @@ def outlier_kv(n_tokens, seed=0, n_outliers=4, factor=20.0):
         K[:, h, ch[h]] *= factor
         V[:, h, ch[4 + h]] *= factor
     return K.astype(np.float16), V.astype(np.float16), rng
+
+
+def kv8a16_recipe(T=320, seed=5):
+    """Data recipe of the reference's quantized-decode checker for its own cache formats
+    (engine/gpu/loom/tools/dattn_q_check.py:147-157): a per-channel K mean m = 0.5 N(0,1), K = N(0,1) + m and
+    V = N(0,1) as fp16 [T][1024], q = 0.3 N(0,1) f32 rounded to fp16, gate ~ N(0,1)."""
+    rng = np.random.default_rng(seed)
+    m = (0.5 * rng.standard_normal(1024)).astype(np.float32)
+    K = (rng.standard_normal((T, 1024)) + m).astype(np.float16)
+    V = rng.standard_normal((T, 1024)).astype(np.float16)
+    q = (0.3 * rng.standard_normal((24, 256))).astype(np.float16)
+    gate = rng.standard_normal((24, 256)).astype(np.float32)
+    return {"T": T, "m": m, "K": K, "V": V, "q": q, "gate": gate}

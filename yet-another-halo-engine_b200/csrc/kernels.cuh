@@ -18,11 +18,22 @@ constexpr int kBlocksPerRow = 8; // 32-element blocks per head row
 
 constexpr int kFmtQ8 = 0;
 constexpr int kFmtQ4 = 1;
+// The reference's own kv8a16 format (engine/gpu/loom/tools/gen_kvq.py:166-285, :474-660): K codes per token with a
+// scale pair per 128-dim half; V codes per (16-key tile, channel) with a statistic pair per channel, four tiles to a
+// page; the tile of the newest key stays open in fp16 (kv8a16.cu).
+constexpr int kFmtKv8 = 2;
+constexpr int kTileKeys = 16;
+constexpr int kTilesPerPage = kPageTokens / kTileKeys;
 
-__host__ __device__ constexpr int CodeBytes(int fmt) { return fmt == kFmtQ8 ? 256 : 128; }
+__host__ __device__ constexpr int CodeBytes(int fmt) { return fmt == kFmtQ4 ? 128 : 256; }
 // One page record of one kv head: codes then (in a separate pool) scales.
 __host__ __device__ constexpr int RecordCodeBytes(int fmt) { return kPageTokens * CodeBytes(fmt); }
-constexpr int kRecordScaleBytes = kPageTokens * kBlocksPerRow * 2;
+constexpr int kRecordScaleBytes = kPageTokens * kBlocksPerRow * 2;   // q8_0 / q4_0: 8 fp16 block scales per token
+// Scale (q8_0, q4_0) or statistic (kv8a16) bytes of one page record of one kv head, by side (0 = K, 1 = V):
+// kv8a16 K holds 2 halves x an fp16 pair per token, kv8a16 V holds an fp16 pair per (tile, channel).
+__host__ __device__ constexpr int RecordScaleBytes(int fmt, int side) {
+  return fmt != kFmtKv8 ? kRecordScaleBytes : (side == 0 ? kPageTokens * 2 * 2 * 2 : kTilesPerPage * kHeadDim * 2 * 2);
+}
 
 // The pools of one context. Codes are addressed both by pointer (append, inspection) and through 2-D tensor maps
 // whose rows are token rows of CodeBytes(fmt) bytes (attention's gathers).
@@ -166,6 +177,33 @@ struct DecodeLaunch {
   int* status_dev;          // sticky error word, 0 = ok
 };
 cudaError_t LaunchDecodePart(const DecodeLaunch& a, cudaStream_t stream);
+
+// ---- kv8a16 (kv8a16.cu) ----
+// Per-sequence state of the format beyond the pools, per layer: two open-tile buffers [2][4 heads][256][16] fp16 (the
+// tile of the newest key in fp16; which of the two is current is host state) and the K channel mean [4][256] f32.
+constexpr int kOpenTileHalfs = kKvHeads * kHeadDim * kTileKeys;   // one buffer, in fp16 elements
+// One 16-key V tile touched by an append call.
+struct VTileWork {
+  std::int32_t state_row;   // (sequence * n_layers + layer): index of the open-tile pair
+  std::int32_t phys_tile;   // page * 4 + tile in page: the pool slot of the tile
+  std::int32_t n_old;       // keys 0 .. n_old - 1 were appended earlier and come from open buffer read_buf
+  std::int32_t n_keys;      // keys of the tile after this call
+  std::int32_t read_buf;    // 0 | 1
+  std::int32_t write_buf;   // open buffer that receives the tile's keys (-1: the tile is not the newest, keep none)
+  std::int32_t complete;    // n_keys == 16: quantize and store the tile
+  std::int32_t pad;
+  std::int32_t src[kTileKeys];   // input token index of key j for j >= n_old
+};
+static_assert(sizeof(VTileWork) == 96, "uploaded as an array");
+cudaError_t LaunchKv8AppendK(const PoolView& pool, int layer, int n_tokens, const std::int64_t* slots_dev,
+                             const std::int32_t* state_rows_dev, const float* kmean_dev, const void* k_dev,
+                             cudaStream_t stream);
+cudaError_t LaunchKv8AppendV(const PoolView& pool, int layer, int n_work, const VTileWork* work_dev, void* open_tiles_dev,
+                             const void* v_dev, cudaStream_t stream);
+// Decode attention over kv8a16 pools. DecodeUnit::pad carries the sequence's current open buffer (0 | 1);
+// state_stride = n_layers (the open-tile pair of (sequence, layer) is row seq * n_layers + layer).
+cudaError_t LaunchKv8DecodePart(const DecodeLaunch& a, const void* open_tiles_dev, int n_layers, cudaStream_t stream);
+cudaError_t ConfigureKv8Kernels();
 cudaError_t LaunchDecodeCombine(const DecodeLaunch& a, cudaStream_t stream);
 // Shared-memory bytes the decode kernel asks for (for the one-time attribute set-up).
 cudaError_t ConfigureDecodeKernels();

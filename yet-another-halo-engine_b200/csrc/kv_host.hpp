@@ -49,7 +49,10 @@ class KvHost {
     if (c.n_q_heads != kQHeads || c.n_kv_heads != kKvHeads || c.head_dim != kHeadDim)
       return bad("geometry must be 24 query heads, 4 kv heads, head_dim 256");
     if (c.page_tokens != kPageTokens) return bad("page_tokens must be 64");
-    if (c.fmt != YAHKV_FMT_Q8_0 && c.fmt != YAHKV_FMT_Q4_0) return bad("fmt must be YAHKV_FMT_Q8_0 or YAHKV_FMT_Q4_0");
+    if (c.fmt != YAHKV_FMT_Q8_0 && c.fmt != YAHKV_FMT_Q4_0 && c.fmt != YAHKV_FMT_KV8A16)
+      return bad("fmt must be YAHKV_FMT_Q8_0, YAHKV_FMT_Q4_0 or YAHKV_FMT_KV8A16");
+    if (c.fmt == YAHKV_FMT_KV8A16 && c.kv_head_count != 0 && c.kv_head_count != kKvHeads)
+      return bad("YAHKV_FMT_KV8A16 contexts hold all four kv heads");
     if (c.n_layers < 1 || c.n_layers > 1024) return bad("n_layers out of range");
     if (c.num_pages < 1) return bad("num_pages must be positive");
     if (c.max_seqs < 1 || c.max_pages_per_seq < 1) return bad("max_seqs and max_pages_per_seq must be positive");
@@ -268,6 +271,65 @@ class KvHost {
     return {};
   }
   void InvalidateDecodePlan() { plan_key_.clear(); }
+
+  // ---- kv8a16: which of a (sequence, layer)'s two open-tile buffers is current, and the V tile work of an append --
+  int open_cur(int seq, int layer) const {
+    return open_cur_.empty() ? 0 : open_cur_[static_cast<std::size_t>(seq) * static_cast<std::size_t>(cfg_.n_layers) + static_cast<std::size_t>(layer)];
+  }
+  // Called after a successful PlanAppend of the same call: the tokens of every sequence are consecutive positions
+  // starting at its previous length, so the first position seen is that length. Builds one work item per 16-key tile
+  // the call touches and flips the open buffer of sequences whose newest tile changed.
+  void PlanKv8Tiles(int layer, int n_tokens, const std::int32_t* seq_ids, const std::int64_t* positions,
+                    std::vector<VTileWork>* work) {
+    if (open_cur_.empty()) open_cur_.assign(static_cast<std::size_t>(cfg_.max_seqs) * static_cast<std::size_t>(cfg_.n_layers), 0);
+    work->clear();
+    struct Span {
+      int seq;
+      std::int64_t p0, p1;
+    };
+    std::vector<Span> spans;
+    for (int t = 0; t < n_tokens; ++t) {
+      bool found = false;
+      for (auto& sp : spans)
+        if (sp.seq == seq_ids[t]) sp.p1 = positions[t] + 1, found = true;
+      if (!found) spans.push_back({seq_ids[t], positions[t], positions[t] + 1});
+    }
+    for (const Span& sp : spans) {
+      const std::size_t si = static_cast<std::size_t>(sp.seq) * static_cast<std::size_t>(cfg_.n_layers) + static_cast<std::size_t>(layer);
+      const int cur = open_cur_[si];
+      const std::int64_t t0 = sp.p0 / kTileKeys, t1 = (sp.p1 - 1) / kTileKeys;
+      for (std::int64_t tile = t0; tile <= t1; ++tile) {
+        VTileWork w{};
+        w.state_row = static_cast<std::int32_t>(si);
+        w.phys_tile = table_row(sp.seq)[tile * kTileKeys / kPageTokens] * kTilesPerPage + static_cast<std::int32_t>(tile % kTilesPerPage);
+        w.n_old = tile == t0 ? static_cast<std::int32_t>(sp.p0 - tile * kTileKeys) : 0;
+        w.n_keys = static_cast<std::int32_t>(std::min<std::int64_t>(kTileKeys, sp.p1 - tile * kTileKeys));
+        w.read_buf = cur;
+        w.write_buf = tile != t1 ? -1 : (t0 == t1 ? cur : cur ^ 1);
+        w.complete = w.n_keys == kTileKeys ? 1 : 0;
+        for (int j = 0; j < kTileKeys; ++j) w.src[j] = -1;
+        work->push_back(w);
+      }
+      if (t0 != t1) open_cur_[si] = cur ^ 1;
+    }
+    // input token index of every new key
+    for (int t = 0; t < n_tokens; ++t) {
+      const std::int64_t tile = positions[t] / kTileKeys;
+      std::size_t base = 0;
+      for (const Span& sp : spans) {
+        const std::int64_t t0 = sp.p0 / kTileKeys, t1 = (sp.p1 - 1) / kTileKeys;
+        if (sp.seq == seq_ids[t]) {
+          (*work)[base + static_cast<std::size_t>(tile - t0)].src[positions[t] % kTileKeys] = t;
+          break;
+        }
+        base += static_cast<std::size_t>(t1 - t0 + 1);
+      }
+    }
+  }
+  void ResetOpenState(int seq) {
+    if (open_cur_.empty()) return;
+    for (int l = 0; l < cfg_.n_layers; ++l) open_cur_[static_cast<std::size_t>(seq) * static_cast<std::size_t>(cfg_.n_layers) + static_cast<std::size_t>(l)] = 0;
+  }
   const std::vector<DecodeUnit>& units() const { return units_; }
   const std::vector<CombineItem>& items() const { return items_; }
 
@@ -410,6 +472,7 @@ class KvHost {
   std::vector<std::int64_t> key_scratch_, plan_key_;
   std::vector<DecodeUnit> units_;
   std::vector<CombineItem> items_;
+  std::vector<int> open_cur_;   // kv8a16: current open-tile buffer per (sequence, layer)
 };
 
 }  // namespace yahkv

@@ -142,6 +142,14 @@ struct yahkv_ctx {
   std::int64_t p16_rows = 0;
   CUtensorMap k16map{}, v16map{};
   float scale_log2 = 0.0F;
+  // kv8a16: per (sequence, layer) two open fp16 V tiles and the K channel mean; per-call work lists
+  void* open_tiles_dev = nullptr;
+  float* kmean_dev = nullptr;
+  std::int32_t* state_rows_dev = nullptr;
+  VTileWork* vwork_dev = nullptr;
+  std::vector<VTileWork> vwork_scratch;
+  std::vector<std::int32_t> state_row_scratch;
+  std::vector<DecodeUnit> unit_scratch;
 };
 
 namespace {
@@ -209,8 +217,16 @@ int InitDevice(yahkv_ctx* ctx) {
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.vcodes, recs * RecordCodeBytes(c.fmt), true));
   if (c.fmt == YAHKV_FMT_Q8_0)   // code 0 in the V side's device representation (sign bit flipped)
     YAHKV_CUDA(ctx, cudaMemset(ctx->pool.vcodes, kQ8FlipByte, recs * RecordCodeBytes(c.fmt)));
-  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.kscales, recs * kPageTokens * kBlocksPerRow, true));
-  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.vscales, recs * kPageTokens * kBlocksPerRow, true));
+  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.kscales, recs * (RecordScaleBytes(c.fmt, 0) / 2), true));
+  YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.vscales, recs * (RecordScaleBytes(c.fmt, 1) / 2), true));
+  if (c.fmt == YAHKV_FMT_KV8A16) {
+    const std::size_t states = static_cast<std::size_t>(c.max_seqs) * c.n_layers;
+    YAHKV_CUDA(ctx, DevAlloc(ctx, reinterpret_cast<std::uint16_t**>(&ctx->open_tiles_dev), states * 2 * kOpenTileHalfs, true));
+    YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->kmean_dev, states * kKvHeads * kHeadDim, true));
+    YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->state_rows_dev, static_cast<std::size_t>(c.max_batch_tokens), false));
+    YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->vwork_dev, static_cast<std::size_t>(c.max_batch_tokens) + 2 * c.max_seqs, false));
+    YAHKV_CUDA(ctx, ConfigureKv8Kernels());
+  }
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->tables_dev, static_cast<std::size_t>(c.max_seqs) * c.max_pages_per_seq, true));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->slots_dev, static_cast<std::size_t>(c.max_batch_tokens), false));
   ctx->max_units = c.max_seqs * kKvHeads * c.max_splits;
@@ -271,7 +287,8 @@ void FreeDevice(yahkv_ctx* ctx) {
                   ctx->slots_dev,   ctx->units_dev,   ctx->items_dev,    ctx->partial_acc,  ctx->partial_ml,
                   ctx->tiles_dev,   ctx->status_dev,  ctx->pseqs_dev, ctx->k16_dev, ctx->v16_dev,
                   ctx->merges_dev, ctx->part_acc_dev, ctx->part_ml_dev,
-                  ctx->rope_tab_dev, ctx->rope_pos_dev};
+                  ctx->rope_tab_dev, ctx->rope_pos_dev, ctx->open_tiles_dev, ctx->kmean_dev, ctx->state_rows_dev,
+                  ctx->vwork_dev};
   for (void* p : ptrs)
     if (p != nullptr) cudaFree(p);
   for (cudaStream_t st : {ctx->h2d_stream, ctx->d2h_stream})
@@ -480,7 +497,15 @@ int yahkv_seq_create(yahkv_ctx* ctx, int32_t* seq) {
   if (ctx == nullptr) return YAHKV_ERR_INVALID;
   if (seq == nullptr) return Fail(ctx, YAHKV_ERR_INVALID, "seq_create: null out pointer");
   HostError e = ctx->host.SeqCreate(seq);
-  return e.code == YAHKV_OK ? YAHKV_OK : FailHost(ctx, std::move(e));
+  if (e.code != YAHKV_OK) return FailHost(ctx, std::move(e));
+  if (ctx->has_device && ctx->cfg.fmt == YAHKV_FMT_KV8A16) {   // a fresh sequence: mean 0, first open buffer
+    ctx->host.ResetOpenState(*seq);
+    if (cudaSetDevice(ctx->cfg.device) != cudaSuccess) return Fail(ctx, YAHKV_ERR_CUDA, "cudaSetDevice failed");
+    YAHKV_CUDA(ctx, cudaDeviceSynchronize());
+    YAHKV_CUDA(ctx, cudaMemset(ctx->kmean_dev + static_cast<std::size_t>(*seq) * ctx->cfg.n_layers * kKvHeads * kHeadDim, 0,
+                               static_cast<std::size_t>(ctx->cfg.n_layers) * kKvHeads * kHeadDim * sizeof(float)));
+  }
+  return YAHKV_OK;
 }
 
 int yahkv_seq_free(yahkv_ctx* ctx, int32_t seq) {
@@ -519,8 +544,40 @@ int yahkv_seq_len(const yahkv_ctx* ctx, int32_t seq, int32_t layer, int64_t* len
 
 int yahkv_seq_set_len(yahkv_ctx* ctx, int32_t seq, int32_t layer, int64_t len) {
   if (ctx == nullptr) return YAHKV_ERR_INVALID;
+  if (ctx->cfg.fmt == YAHKV_FMT_KV8A16 && len != 0)
+    return Fail(ctx, YAHKV_ERR_INVALID, "seq_set_len: a YAHKV_FMT_KV8A16 sequence can only be reset to length 0 (its open tile holds the newest keys)");
   HostError e = ctx->host.SeqSetLen(seq, layer, len);
-  return e.code == YAHKV_OK ? YAHKV_OK : FailHost(ctx, std::move(e));
+  if (e.code != YAHKV_OK) return FailHost(ctx, std::move(e));
+  if (ctx->cfg.fmt == YAHKV_FMT_KV8A16 && layer == -1) ctx->host.ResetOpenState(seq);
+  return YAHKV_OK;
+}
+
+int yahkv_seq_set_kmean(yahkv_ctx* ctx, int32_t seq, int32_t layer, const float* mean_host) {
+  if (int r = RequireDevice(ctx, "seq_set_kmean"); r != YAHKV_OK) return r;
+  if (ctx->cfg.fmt != YAHKV_FMT_KV8A16) return Fail(ctx, YAHKV_ERR_INVALID, "seq_set_kmean: only for YAHKV_FMT_KV8A16");
+  if (!ctx->host.live(seq) || mean_host == nullptr || layer < -1 || layer >= ctx->cfg.n_layers)
+    return Fail(ctx, YAHKV_ERR_INVALID, "seq_set_kmean: bad sequence, layer or null pointer");
+  for (int l = 0; l < ctx->cfg.n_layers; ++l)
+    if ((layer == -1 || layer == l) && ctx->host.len(seq, l) != 0)
+      return Fail(ctx, YAHKV_ERR_ORDER, "seq_set_kmean: the mean is fixed once a key has been appended");
+  YAHKV_CUDA(ctx, cudaDeviceSynchronize());
+  for (int l = 0; l < ctx->cfg.n_layers; ++l)
+    if (layer == -1 || layer == l)
+      YAHKV_CUDA(ctx, cudaMemcpy(ctx->kmean_dev + (static_cast<std::size_t>(seq) * ctx->cfg.n_layers + l) * kKvHeads * kHeadDim,
+                                 mean_host, static_cast<std::size_t>(kKvHeads) * kHeadDim * sizeof(float), cudaMemcpyHostToDevice));
+  return YAHKV_OK;
+}
+
+int yahkv_read_open_tile(yahkv_ctx* ctx, int32_t seq, int32_t layer, void* tile_host) {
+  if (int r = RequireDevice(ctx, "read_open_tile"); r != YAHKV_OK) return r;
+  if (ctx->cfg.fmt != YAHKV_FMT_KV8A16) return Fail(ctx, YAHKV_ERR_INVALID, "read_open_tile: only for YAHKV_FMT_KV8A16");
+  if (!ctx->host.live(seq) || tile_host == nullptr || layer < 0 || layer >= ctx->cfg.n_layers)
+    return Fail(ctx, YAHKV_ERR_INVALID, "read_open_tile: bad sequence, layer or null pointer");
+  YAHKV_CUDA(ctx, cudaDeviceSynchronize());
+  const std::size_t row = (static_cast<std::size_t>(seq) * ctx->cfg.n_layers + layer) * 2 + ctx->host.open_cur(seq, layer);
+  YAHKV_CUDA(ctx, cudaMemcpy(tile_host, static_cast<const std::uint16_t*>(ctx->open_tiles_dev) + row * kOpenTileHalfs,
+                             static_cast<std::size_t>(kOpenTileHalfs) * 2, cudaMemcpyDeviceToHost));
+  return YAHKV_OK;
 }
 
 int yahkv_pages_free(const yahkv_ctx* ctx, int32_t* n) {
@@ -541,6 +598,26 @@ int yahkv_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int32_t*
   if (int r = FlushTables(ctx, st); r != YAHKV_OK) return r;
   if (int r = StagedUpload(ctx, ctx->slots_dev, ctx->slot_scratch.data(), static_cast<std::size_t>(n_tokens) * 8, st); r != YAHKV_OK)
     return r;
+  if (ctx->cfg.fmt == YAHKV_FMT_KV8A16) {
+    // K: one row per token against its sequence's mean. V: one work item per 16-key tile the call touches; the tile
+    // of each sequence's newest key also stays in fp16 (engine/gpu/loom/tools/gen_decode_attn.py:436-573).
+    ctx->host.PlanKv8Tiles(layer, n_tokens, seq_ids, positions, &ctx->vwork_scratch);
+    ctx->state_row_scratch.resize(static_cast<std::size_t>(n_tokens));
+    for (int i = 0; i < n_tokens; ++i)
+      ctx->state_row_scratch[static_cast<std::size_t>(i)] = seq_ids[i] * ctx->cfg.n_layers + layer;
+    if (int r = StagedUpload(ctx, ctx->state_rows_dev, ctx->state_row_scratch.data(), static_cast<std::size_t>(n_tokens) * 4, st); r != YAHKV_OK)
+      return r;
+    if (int r = StagedUpload(ctx, ctx->vwork_dev, ctx->vwork_scratch.data(), ctx->vwork_scratch.size() * sizeof(VTileWork), st);
+        r != YAHKV_OK)
+      return r;
+    TimedLaunch tl(ctx, YAHKV_KERNEL_APPEND, st);
+    YAHKV_CUDA(ctx, LaunchKv8AppendK(ctx->pool, layer, n_tokens, ctx->slots_dev, ctx->state_rows_dev, ctx->kmean_dev, k_dev, st));
+    YAHKV_CUDA(ctx, LaunchKv8AppendV(ctx->pool, layer, static_cast<int>(ctx->vwork_scratch.size()), ctx->vwork_dev,
+                                     ctx->open_tiles_dev, v_dev, st));
+    tl.End();
+    ctx->launches += 2;
+    return YAHKV_OK;
+  }
   TimedLaunch tl(ctx, YAHKV_KERNEL_APPEND, st);
   YAHKV_CUDA(ctx, LaunchAppend(ctx->pool, layer, n_tokens, ctx->slots_dev, k_dev, v_dev, st));
   tl.End();
@@ -572,6 +649,7 @@ int yahkv_rope_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int
                       const float* q_dev, const float* k_dev, const float* v_dev, const float* q_weight_dev,
                       const float* k_weight_dev, float eps, void* q_out_dev, void* stream) {
   if (int r = RequireDevice(ctx, "rope_append"); r != YAHKV_OK) return r;
+  if (ctx->cfg.fmt == YAHKV_FMT_KV8A16) return Fail(ctx, YAHKV_ERR_INVALID, "rope_append: not available for YAHKV_FMT_KV8A16");
   if (n_tokens > ctx->cfg.max_batch_tokens) return Fail(ctx, YAHKV_ERR_CAPACITY, "rope_append: more tokens than max_batch_tokens");
   if (n_tokens > 0 && (q_dev == nullptr || k_dev == nullptr || v_dev == nullptr || q_weight_dev == nullptr ||
                        k_weight_dev == nullptr || q_out_dev == nullptr))
@@ -601,6 +679,8 @@ int yahkv_rope_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int
 int yahkv_append_slots(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int64_t* slot_mapping_dev,
                        const void* k_dev, const void* v_dev, void* stream) {
   if (int r = RequireDevice(ctx, "append_slots"); r != YAHKV_OK) return r;
+  if (ctx->cfg.fmt == YAHKV_FMT_KV8A16)
+    return Fail(ctx, YAHKV_ERR_INVALID, "append_slots: YAHKV_FMT_KV8A16 needs the sequence of every token (use yahkv_append)");
   if (layer < 0 || layer >= ctx->cfg.n_layers) return Fail(ctx, YAHKV_ERR_INVALID, "append_slots: layer out of range");
   if (n_tokens < 0) return Fail(ctx, YAHKV_ERR_INVALID, "append_slots: negative token count");
   if (n_tokens == 0) return YAHKV_OK;
@@ -635,7 +715,13 @@ int yahkv_attend_decode(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int
   } guard{&ctx->host};
   cudaStream_t st = StreamOf(ctx, stream);
   if (int r = FlushTables(ctx, st); r != YAHKV_OK) return r;
-  const auto& units = ctx->host.units();
+  const bool kv8 = ctx->cfg.fmt == YAHKV_FMT_KV8A16;
+  if (kv8) {   // every unit carries its sequence's current open-tile buffer of THIS layer: uploaded on every call
+    ctx->unit_scratch = ctx->host.units();
+    for (DecodeUnit& u : ctx->unit_scratch) u.pad = ctx->host.open_cur(u.seq, layer);
+    changed = true;
+  }
+  const auto& units = kv8 ? ctx->unit_scratch : ctx->host.units();
   const auto& items = ctx->host.items();
   if (changed) {
     // One staging buffer holds both lists so they share a completion event.
@@ -659,7 +745,7 @@ int yahkv_attend_decode(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int
   // The merge runs as its own small launch: letting the last-arriving unit merge inside the part kernel was measured
   // 1% slower end to end (every CTA then pays a fence and an atomic on exit).
   TimedLaunch tp(ctx, YAHKV_KERNEL_DECODE_PART, st);
-  cudaError_t le = LaunchDecodePart(a, st);
+  cudaError_t le = kv8 ? LaunchKv8DecodePart(a, ctx->open_tiles_dev, ctx->cfg.n_layers, st) : LaunchDecodePart(a, st);
   tp.End();
   if (le == cudaSuccess) {
     TimedLaunch tc(ctx, YAHKV_KERNEL_DECODE_COMBINE, st);
@@ -676,6 +762,7 @@ int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const in
                          const int32_t* chunk_lens, const void* q_dev, const float* gate_dev, void* out_dev,
                          int32_t out_dtype, void* stream) {
   if (int r = RequireDevice(ctx, "attend_prefill"); r != YAHKV_OK) return r;
+  if (ctx->cfg.fmt == YAHKV_FMT_KV8A16) return Fail(ctx, YAHKV_ERR_INVALID, "attend_prefill: not available for YAHKV_FMT_KV8A16");
   if (out_dtype != YAHKV_OUT_F16 && out_dtype != YAHKV_OUT_F32) return Fail(ctx, YAHKV_ERR_INVALID, "attend_prefill: bad out_dtype");
   if (n_seqs > 0 && (q_dev == nullptr || out_dev == nullptr)) return Fail(ctx, YAHKV_ERR_INVALID, "attend_prefill: null q or out pointer");
   if ((reinterpret_cast<std::uintptr_t>(q_dev) & 15) != 0 || (reinterpret_cast<std::uintptr_t>(out_dev) & 15) != 0)
@@ -824,9 +911,10 @@ static int PageAccess(yahkv_ctx* ctx, int32_t layer, int32_t side, int32_t page,
   YAHKV_CUDA(ctx, cudaDeviceSynchronize());
   const std::size_t rec = (static_cast<std::size_t>(layer) * ctx->cfg.num_pages + page) * kKvHeads;
   std::uint8_t* codes = (side == YAHKV_SIDE_K ? ctx->pool.kcodes : ctx->pool.vcodes) + rec * RecordCodeBytes(ctx->cfg.fmt);
-  std::uint16_t* scales = (side == YAHKV_SIDE_K ? ctx->pool.kscales : ctx->pool.vscales) + rec * kPageTokens * kBlocksPerRow;
+  const std::size_t rsb = static_cast<std::size_t>(RecordScaleBytes(ctx->cfg.fmt, side));
+  std::uint16_t* scales = (side == YAHKV_SIDE_K ? ctx->pool.kscales : ctx->pool.vscales) + rec * (rsb / 2);
   const std::size_t cb = static_cast<std::size_t>(kKvHeads) * RecordCodeBytes(ctx->cfg.fmt);
-  const std::size_t sb = static_cast<std::size_t>(kKvHeads) * kRecordScaleBytes;
+  const std::size_t sb = static_cast<std::size_t>(kKvHeads) * rsb;
   if (codes_host != nullptr) {   // q8_0 codes cross the boundary as GGUF int8, the V pool holds them sign-flipped
     if (write) {
       std::vector<std::uint8_t> tmp(static_cast<const std::uint8_t*>(codes_host), static_cast<const std::uint8_t*>(codes_host) + cb);
@@ -854,6 +942,7 @@ int yahkv_write_page(yahkv_ctx* ctx, int32_t layer, int32_t side, int32_t page, 
 
 int yahkv_export_token(yahkv_ctx* ctx, int32_t layer, int32_t seq, int64_t pos, void* k_blocks, void* v_blocks) {
   if (int r = RequireDevice(ctx, "export_token"); r != YAHKV_OK) return r;
+  if (ctx->cfg.fmt == YAHKV_FMT_KV8A16) return Fail(ctx, YAHKV_ERR_INVALID, "export_token: YAHKV_FMT_KV8A16 has no GGUF block form (use yahkv_read_page)");
   if (layer < 0 || layer >= ctx->cfg.n_layers) return Fail(ctx, YAHKV_ERR_INVALID, "export_token: layer out of range");
   if (!ctx->host.live(seq)) return Fail(ctx, YAHKV_ERR_INVALID, "export_token: not a live sequence");
   if (pos < 0 || pos >= static_cast<std::int64_t>(ctx->host.n_pages(seq)) * kPageTokens)
@@ -940,6 +1029,7 @@ void BatchFree(yahkv_batch* b) {
 
 int yahkv_batch_create(yahkv_ctx* ctx, int32_t n_seqs, const int32_t* seq_ids, yahkv_batch** out) {
   if (int r = RequireDevice(ctx, "batch_create"); r != YAHKV_OK) return r;
+  if (ctx->cfg.fmt == YAHKV_FMT_KV8A16) return Fail(ctx, YAHKV_ERR_INVALID, "batch_create: not available for YAHKV_FMT_KV8A16");
   if (out == nullptr) return Fail(ctx, YAHKV_ERR_INVALID, "batch_create: null out pointer");
   *out = nullptr;
   if (n_seqs <= 0 || n_seqs > ctx->cfg.max_seqs || seq_ids == nullptr) return Fail(ctx, YAHKV_ERR_INVALID, "batch_create: bad sequence list");
@@ -1121,6 +1211,7 @@ struct FileCloser {
 
 int yahkv_snapshot_save(yahkv_ctx* ctx, int32_t n_seqs, const int32_t* seq_ids, const char* path) {
   if (int r = RequireDevice(ctx, "snapshot_save"); r != YAHKV_OK) return r;
+  if (ctx->cfg.fmt == YAHKV_FMT_KV8A16) return Fail(ctx, YAHKV_ERR_INVALID, "snapshot_save: not available for YAHKV_FMT_KV8A16");
   if (n_seqs < 0 || (n_seqs > 0 && seq_ids == nullptr) || path == nullptr)
     return Fail(ctx, YAHKV_ERR_INVALID, "snapshot_save: bad sequence list or path");
   for (int i = 0; i < n_seqs; ++i)
@@ -1163,6 +1254,7 @@ int yahkv_snapshot_save(yahkv_ctx* ctx, int32_t n_seqs, const int32_t* seq_ids, 
 
 int yahkv_snapshot_load(yahkv_ctx* ctx, const char* path, int32_t* seq_ids_out, int32_t* n_inout) {
   if (int r = RequireDevice(ctx, "snapshot_load"); r != YAHKV_OK) return r;
+  if (ctx->cfg.fmt == YAHKV_FMT_KV8A16) return Fail(ctx, YAHKV_ERR_INVALID, "snapshot_load: not available for YAHKV_FMT_KV8A16");
   if (path == nullptr || seq_ids_out == nullptr || n_inout == nullptr)
     return Fail(ctx, YAHKV_ERR_INVALID, "snapshot_load: null argument");
   std::unique_ptr<std::FILE, FileCloser> f(std::fopen(path, "rb"));

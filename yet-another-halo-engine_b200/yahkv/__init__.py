@@ -17,7 +17,7 @@ _PKG_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB_PATH = os.path.join(_PKG_DIR, "libyahkv.so")
 INCLUDE_DIR = os.path.join(os.path.dirname(_PKG_DIR), "include")
 
-FMT_Q8_0, FMT_Q4_0 = 0, 1
+FMT_Q8_0, FMT_Q4_0, FMT_KV8A16 = 0, 1, 2
 SIDE_K, SIDE_V = 0, 1
 OUT_F16, OUT_F32 = 0, 1
 KERNEL_APPEND, KERNEL_DECODE_PART, KERNEL_DECODE_COMBINE, KERNEL_PREFILL, KERNEL_PREFILL_DEQUANT = 0, 1, 2, 3, 4
@@ -28,12 +28,23 @@ Q_HEADS, KV_HEADS, HEAD_DIM, PAGE_TOKENS, BLOCKS = 24, 4, 256, 64, 8
 
 
 def code_bytes(fmt):
-    return 256 if fmt == FMT_Q8_0 else 128
+    return 128 if fmt == FMT_Q4_0 else 256
 
 
 def bytes_per_token(fmt):
     """K + V bytes one cached token takes in one layer (codes + fp16 scales, all 4 kv heads)."""
+    if fmt == FMT_KV8A16:     # K: 256 B + 2 pairs per head; V: 256 B + a sixteenth of 256 pairs per head
+        return KV_HEADS * (256 + 8) + KV_HEADS * (256 + 64)
     return 2 * KV_HEADS * (code_bytes(fmt) + BLOCKS * 2)
+
+
+def page_shapes(fmt, side):
+    """(codes shape, scales shape) of one page record as yahkv_read_page returns it."""
+    if fmt != FMT_KV8A16:
+        return (KV_HEADS, PAGE_TOKENS, code_bytes(fmt)), (KV_HEADS, PAGE_TOKENS, BLOCKS)
+    if side == SIDE_K:
+        return (KV_HEADS, PAGE_TOKENS, 256), (KV_HEADS, PAGE_TOKENS, 2, 2)
+    return (KV_HEADS, PAGE_TOKENS // 16, HEAD_DIM, 16), (KV_HEADS, PAGE_TOKENS // 16, HEAD_DIM, 2)
 
 
 class Config(ctypes.Structure):
@@ -119,6 +130,8 @@ SIGNATURES = {
     "yahkv_seq_len": (_I32, [_VP, _I32, _I32, _PI64]),
     "yahkv_seq_set_len": (_I32, [_VP, _I32, _I32, _I64]),
     "yahkv_pages_free": (_I32, [_VP, _PI32]),
+    "yahkv_seq_set_kmean": (_I32, [_VP, _I32, _I32, _VP]),
+    "yahkv_read_open_tile": (_I32, [_VP, _I32, _I32, _VP]),
     "yahkv_append": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _VP]),
     "yahkv_rope_append": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _VP, _VP, _VP, ctypes.c_float, _VP, _VP]),
     "yahkv_append_slots": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP]),
@@ -363,9 +376,21 @@ class KvCache:
         self._check(lib.yahkv_decode_step_host_wait(self._h))
 
     # ---- inspection ----
+    def seq_set_kmean(self, seq, mean, layer=-1):
+        """kv8a16: the per-channel K mean [4][256] f32 of a sequence (before its first append)."""
+        mean = np.ascontiguousarray(mean, np.float32).reshape(KV_HEADS, HEAD_DIM)
+        self._check(lib.yahkv_seq_set_kmean(self._h, seq, layer, _ptr(mean)))
+
+    def read_open_tile(self, seq, layer):
+        """kv8a16: the current open V tile [4][256][16] as float16."""
+        tile = np.zeros((KV_HEADS, HEAD_DIM, 16), np.float16)
+        self._check(lib.yahkv_read_open_tile(self._h, seq, layer, _ptr(tile)))
+        return tile
+
     def read_page(self, layer, side, page):
-        codes = np.zeros((KV_HEADS, PAGE_TOKENS, code_bytes(self.fmt)), np.uint8)
-        scales = np.zeros((KV_HEADS, PAGE_TOKENS, BLOCKS), np.uint16)
+        cs, ss = page_shapes(self.fmt, side)
+        codes = np.zeros(cs, np.uint8)
+        scales = np.zeros(ss, np.uint16)
         self._check(lib.yahkv_read_page(self._h, layer, side, page, _ptr(codes), _ptr(scales)))
         return codes, scales
 
