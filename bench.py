@@ -250,7 +250,7 @@ def prefill_arm(args, local_rank):
     pages = (cached + chunk) // 64
     rng = np.random.default_rng(0)
     cache = yahkv.KvCache(device=local_rank, n_layers=1, num_pages=n_seq * pages + 8, fmt=yahkv.FMT_Q8_0, max_seqs=n_seq,
-                          max_pages_per_seq=pages, max_batch_tokens=n_seq * chunk)
+                          max_pages_per_seq=pages, max_batch_tokens=n_seq * chunk, max_prefill_keys=n_seq * pages * 64)
     perm = rng.permutation(n_seq * pages + 8).astype(np.int32)
     # An explicit stream: the legacy default stream's handle is 0, which the library reads as "use the context's own
     # stream", and events recorded on one stream say nothing about kernels on another.
@@ -407,7 +407,8 @@ def churn_arm(args, rank, local_rank, world):
                           finish_frac=0.1, seed=0)
     cap_pages = (sched.ctx_hi + sched.chunk + 64 + 63) // 64 + 1
     cache = yahkv.KvCache(device=local_rank, n_layers=layers, num_pages=pages_needed(sched, rank, world),
-                          fmt=yahkv.FMT_Q8_0, max_seqs=40, max_pages_per_seq=cap_pages, max_batch_tokens=2048)
+                          fmt=yahkv.FMT_Q8_0, max_seqs=40, max_pages_per_seq=cap_pages, max_batch_tokens=2048,
+                          max_prefill_keys=cap_pages * 64)      # the prefill scratch is allocated once, up front
     runner = ChurnRunner(cache, sched, rank, world, n_layers=layers)
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
