@@ -25,8 +25,8 @@
 // treated differently for that reason:
 //   Q.K^T runs on the integer MMA (m16n8k32, s8 x s8 -> s32) straight on the cached codes: a 32-element block is
 //   exactly one k-step, ldmatrix delivers the code bytes in the B operand's register layout, and nothing is converted
-//   (q4_0: three logic instructions turn eight nibbles into the bytes 16 n, and the accumulator starts at -128 times
-//   the block sum of the query plane, which supplies the - 8). The query row is quantized
+//   (q4_0: three logic instructions turn eight nibbles into the signed bytes 16 (n - 8): the nibble moved to the top of
+//   its byte and the byte's sign bit flipped, so the format's offset costs nothing). The query row is quantized
 //   once per CTA to 16 bits against its head's largest magnitude and split into two int8 planes, hi and lo
 //   (q = s (256 hi + lo), |error| <= s / 2 = amax / 64000 per element, far below the fp16 query's own spacing).
 //   Both planes ride in one MMA as rows 0-5 and 8-13 of the 16-row A operand, so one instruction gives the exact
@@ -102,17 +102,6 @@ __device__ __forceinline__ void MmaQK(int (&d)[4], const std::uint32_t (&a)[4], 
       : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
 }
-// The q4_0 form: B holds the unsigned bytes 16 n (a nibble moved to the top of its byte), so the sum comes out as
-// 16 sum(q n); the accumulator starts at -128 sum(q) of the block (c_hi for the hi plane's rows, c_lo for the lo
-// plane's), which makes it 16 sum(q (n - 8)) without touching the codes again.
-__device__ __forceinline__ void MmaQKU8(int (&d)[4], const std::uint32_t (&a)[4], std::uint32_t b0, std::uint32_t b1,
-                                        int c_hi, int c_lo) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-      "{%10, %10, %11, %11};"
-      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c_hi), "r"(c_lo));
-}
 // The block sum of one (head, key): the hi plane's sum times 256 plus the lo plane's, exact in 32 bits
 // (|sum| <= 32 x 128 x 32768), as a float.
 __device__ __forceinline__ float JoinPlanes(int hi, int lo) { return static_cast<float>(hi * 256 + lo); }
@@ -121,7 +110,7 @@ __device__ __forceinline__ float JoinPlanes(int hi, int lo) { return static_cast
 constexpr float kQSteps = 32000.0F;
 
 // Shared memory of a CTA, all dynamic so that the ring starts at the window's 1024-byte aligned base (the swizzled
-// TMA boxes need that alignment): ring | Q operands | mbarriers | stage counters | query scales | abort flag.
+// TMA boxes need that alignment): ring | Q operands | mbarriers | stage counters | query steps | abort flag.
 // Lanes 24-31 of a warp hold the two padding heads of the 8-wide MMA; they reuse the Q operands of lanes 16-23
 // (duplicates of heads 4, 5 whose results are never stored), so the Q array is 24 lanes wide.
 constexpr int kQLanes = 24;
@@ -135,8 +124,7 @@ struct SmemLayout {
   static constexpr int kCntOff = kBarOff + 8 * StageLayout<kFmt>::kStages;
   static constexpr int kFillOff = kCntOff + 4 * StageLayout<kFmt>::kStages;     // fills issued per stage
   static constexpr int kQScaleOff = kFillOff + 4 * StageLayout<kFmt>::kStages;  // [8] f32, one per head (6 used)
-  static constexpr int kQCorrOff = (kQScaleOff + 4 * 8 + 7) / 8 * 8;            // [8 blocks][8 heads] int2 (q4_0)
-  static constexpr int kAbortOff = kQCorrOff + kBlocksPerRow * 8 * 8;
+  static constexpr int kAbortOff = kQScaleOff + 4 * 8;
   static constexpr int kBytes = kAbortOff + 4;
 };
 template <int kFmt>
@@ -165,7 +153,6 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
   int* done_cnt = reinterpret_cast<int*>(smem_raw + S::kCntOff);        // warps done reading a stage's page
   int* fill_cnt = reinterpret_cast<int*>(smem_raw + S::kFillOff);       // fills issued to a stage so far
   float* q_scale = reinterpret_cast<float*>(smem_raw + S::kQScaleOff);  // query quantization step per head
-  int2* q_corr = reinterpret_cast<int2*>(smem_raw + S::kQCorrOff);      // -128 x block sums of the query planes
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + S::kAbortOff);   // a wait gave up
   if ((SmemAddr(smem_raw) & 1023U) != 0) {   // never seen; checked because a misaligned swizzle would corrupt results
     if (threadIdx.x == 0) atomicExch(status, kStatusSmemMisaligned);
@@ -242,22 +229,15 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFU, amax, o));
     const float inv = amax > 0.0F ? kQSteps / amax : 0.0F;
     std::uint32_t hi_w[2] = {0, 0}, lo_w[2] = {0, 0};
-    int sum_hi = 0, sum_lo = 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int q16 = __float2int_rn(x[i] * inv);
       const int hi = (q16 + 128) >> 8;
       const int lo = q16 - hi * 256;
-      sum_hi += hi, sum_lo += lo;
       hi_w[i >> 2] |= (static_cast<std::uint32_t>(hi) & 0xFFU) << (8 * (i & 3));
       lo_w[i >> 2] |= (static_cast<std::uint32_t>(lo) & 0xFFU) << (8 * (i & 3));
     }
     const int blk = lane >> 2, e0 = (lane & 3) * 8;
-    if constexpr (kFmt == kFmtQ4) {   // the block's plane sums (a block is four lanes), for the unsigned-code MMA
-      sum_hi += __shfl_xor_sync(0xFFFFFFFFU, sum_hi, 1), sum_lo += __shfl_xor_sync(0xFFFFFFFFU, sum_lo, 1);
-      sum_hi += __shfl_xor_sync(0xFFFFFFFFU, sum_hi, 2), sum_lo += __shfl_xor_sync(0xFFFFFFFFU, sum_lo, 2);
-      if ((lane & 3) == 0) q_corr[blk * 8 + warp] = make_int2(-128 * sum_hi, -128 * sum_lo);
-    }
     const int reg = e0 < 16 ? 0 : 2, t0 = (e0 & 15) >> 2;
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
@@ -379,13 +359,12 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
             const int b = 2 * bp + hb;   // block 4 dh + b
             std::uint32_t qa[4];
             LoadQ(qa, qa_addr + (4 * dh + b) * (kQLanes * 16));
-            const int2 corr = q_corr[(4 * dh + b) * 8 + (qlane >> 2)];
             int a0[4], a1[4];
             std::uint32_t lo, hi;
-            Nib8ToU8(w[2 * hb], lo, hi);
-            MmaQKU8(a0, qa, lo, hi, corr.x, corr.y);
-            Nib8ToU8(w[2 * hb + 1], lo, hi);
-            MmaQKU8(a1, qa, lo, hi, corr.x, corr.y);
+            Nib8ToS8(nib.top_mask, nib.sign_flip, w[2 * hb], lo, hi);
+            MmaQK(a0, qa, lo, hi);
+            Nib8ToS8(nib.top_mask, nib.sign_flip, w[2 * hb + 1], lo, hi);
+            MmaQK(a1, qa, lo, hi);
             sc[0][0] = fmaf(ScaleOf(ks_raw[0][0], b), JoinPlanes(a0[0], a0[2]), sc[0][0]);
             sc[0][1] = fmaf(ScaleOf(ks_raw[0][1], b), JoinPlanes(a0[1], a0[3]), sc[0][1]);
             sc[1][0] = fmaf(ScaleOf(ks_raw[1][0], b), JoinPlanes(a1[0], a1[2]), sc[1][0]);

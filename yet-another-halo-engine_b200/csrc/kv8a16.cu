@@ -22,9 +22,8 @@
 // a new tile writes that tile into the OTHER buffer, so the kernel's blocks never write what another block still
 // reads; which buffer is current is host state, handed to the kernels per call.
 //
-// Decode attention here uses plain global loads (every warp takes whole 16-key tiles: K rows as 16-byte loads that
-// land in the integer MMA's operand layout, V tiles a dword per (channel, lane)); it is the straightforward form, not
-// yet the TMA-ring form of the q8_0 / q4_0 kernel.
+// Decode attention has the shape of the q8_0 / q4_0 kernel (a TMA-filled ring of page stages, whole-tile warps); see
+// the comment above it.
 #include <cuda_fp16.h>
 
 #include <cmath>
@@ -151,22 +150,68 @@ __global__ void __launch_bounds__(kHeadDim) Kv8AppendVKernel(PoolView pool, int 
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Decode attention: one CTA per split-K unit, a warp per 16-key tile (round robin), all 256 dims per warp.
+// Decode attention: one CTA per split-K unit (a run of pages of one sequence for one kv head, all six query heads).
+//
+// The same shape as the q8_0 / q4_0 kernel: a ring of page-sized stages filled by non-multicast TMA on one mbarrier
+// per stage, eight warps on two pages at a time (warp w owns 16-key tile w % 4 of the pages of parity w / 4 and does
+// everything for it: scores over 256 dims, softmax, 256 output channels), the last of a page's four warps refills its
+// stage, no barrier and no exchange inside the page loop. A stage holds the page's K codes as two swizzled 64 x 128 B
+// boxes (box = one 128-dim half), its four V tiles as stored (one linear 16 KB copy), the V statistic pairs (4 KB) and
+// the K scale pairs (512 B): 37,376 B, three stages per CTA, two CTAs per SM.
+//
+// Scores: the integer MMA on the unsigned codes, the four 32-byte blocks of a half accumulating in the instruction's
+// accumulator, which starts at -128 x the plane sums of the query half (u = value + 128). The ldmatrix rows are given
+// in the order the V tile packs its keys, so that score column c of key tile kt is key 4 (c / 2) + 2 kt + c % 2 and
+// the weights land in the second MMA's operand layout with no shuffle; a thread's four scores are then four
+// consecutive keys, and their scale pairs two 16-byte loads.
+// Values: v = a (u - 128) + b per (tile, channel), a = S / 256, b = 1.5 S + C'. u - 128 enters the f16 MMA as exact
+// integers against the weights' hi and lo parts (both into one fresh accumulator); a and b are applied in fp32 to
+// the tile's sums: o += a d + b sum(p). The tile that holds the newest key is read in fp16 from the sequence's open
+// buffer (in the same key order), by plain loads: one tile per sequence and kv head.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int kKv8Warps = 8;
+constexpr int kKv8Stages = 3;
+constexpr int kKv8KeyGroups = 4;
+constexpr int kKv8PageSets = 2;
+constexpr int kKv8Warps = kKv8KeyGroups * kKv8PageSets;
 constexpr int kKv8Threads = kKv8Warps * 32;
+constexpr int kKv8BoxBytes = 64 * 128;
+constexpr int kKv8KBytes = 2 * kKv8BoxBytes;                          // K codes of a page of one kv head
+constexpr int kKv8VBytes = kTilesPerPage * kHeadDim * kTileKeys;      // V codes
+constexpr int kKv8VsBytes = kTilesPerPage * kHeadDim * 4;             // V statistic pairs
+constexpr int kKv8KsBytes = kPageTokens * 2 * 4;                      // K scale pairs
+static_assert(kKv8KBytes == RecordCodeBytes(kFmtKv8) && kKv8VBytes == RecordCodeBytes(kFmtKv8), "record sizes");
+static_assert(kKv8KsBytes == RecordScaleBytes(kFmtKv8, 0) && kKv8VsBytes == RecordScaleBytes(kFmtKv8, 1), "record sizes");
+constexpr int kKv8TxBytes = kKv8KBytes + kKv8VBytes + kKv8VsBytes + kKv8KsBytes;
+// Shared memory (dynamic, 1024-byte aligned base): the four parts of the ring each as [stage][...] so that every K box
+// starts on a 1024-byte boundary without padding; then the query operands and the bookkeeping words. Two CTAs and
+// their 1 KB reservations fill an SM's 228 KB to within 512 bytes.
+constexpr int kKv8KOff = 0;
+constexpr int kKv8VOff = kKv8KOff + kKv8Stages * kKv8KBytes;
+constexpr int kKv8VsOff = kKv8VOff + kKv8Stages * kKv8VBytes;
+constexpr int kKv8KsOff = kKv8VsOff + kKv8Stages * kKv8VsBytes;
+constexpr int kKv8RingBytes = kKv8KsOff + kKv8Stages * kKv8KsBytes;
+constexpr int kKv8QLanes = 24;
+constexpr int kKv8QfragOff = kKv8RingBytes;                           // [8 blocks][24 lanes][4] u32
+constexpr int kKv8BarOff = kKv8QfragOff + kBlocksPerRow * kKv8QLanes * 16;
+constexpr int kKv8DoneOff = kKv8BarOff + 8 * kKv8Stages;
+constexpr int kKv8FillOff = kKv8DoneOff + 4 * kKv8Stages;
+constexpr int kKv8QStepOff = kKv8FillOff + 4 * kKv8Stages;            // [8] f32
+constexpr int kKv8QCorrOff = (kKv8QStepOff + 32 + 7) / 8 * 8;         // [2 halves][8 heads] int2
+constexpr int kKv8AbortOff = kKv8QCorrOff + 2 * 8 * 8;
+constexpr int kKv8SmemBytes = (kKv8AbortOff + 4 + 127) / 128 * 128;
+static_assert(2 * (kKv8SmemBytes + 1024) <= 228 * 1024, "two CTAs per SM");
 constexpr int kMergeStride = kHeadDim + 8;
 constexpr int kMergeWarpFloats = kGroup * kMergeStride + 16;
-constexpr int kKv8SmemBytes = kKv8Warps * kMergeWarpFloats * 4;   // merge scratch; the query planes alias its start
+static_assert(kKv8Warps * kMergeWarpFloats * 4 <= kKv8RingBytes, "the merge scratch aliases the ring");
 constexpr float kLazyRescale = 4.0F;
 constexpr float kQSteps = 32000.0F;
+constexpr int kStatusSmemMisaligned = 2;
 
-__device__ __forceinline__ void MmaS8U8Acc(int (&d)[4], std::uint32_t a0, std::uint32_t a1, std::uint32_t a2,
-                                           std::uint32_t a3, std::uint32_t b0, std::uint32_t b1) {
+__device__ __forceinline__ void MmaS8U8Acc(int (&d)[4], const std::uint32_t (&a)[4], std::uint32_t b0, std::uint32_t b1) {
   asm volatile(
       "mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
       : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void MmaF16Zero(float (&d)[4], std::uint32_t a0, std::uint32_t a1, std::uint32_t a2,
                                            std::uint32_t a3, std::uint32_t b0, std::uint32_t b1) {
@@ -176,27 +221,76 @@ __device__ __forceinline__ void MmaF16Zero(float (&d)[4], std::uint32_t a0, std:
       : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0F));
 }
+__device__ __forceinline__ void LoadQ4(std::uint32_t (&a)[4], std::uint32_t addr) {
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(addr));
+}
 
 __global__ void __launch_bounds__(kKv8Threads, 2)
-    Kv8DecodePartKernel(PoolView pool, int layer, const std::int32_t* __restrict__ tables, int table_stride,
-                        const DecodeUnit* __restrict__ units, const __half* __restrict__ q, float scale_log2,
-                        const __half* __restrict__ open_tiles, int n_layers, float* __restrict__ partial_acc,
-                        float* __restrict__ partial_ml) {
+    Kv8DecodePartKernel(const __grid_constant__ CUtensorMap kmap, PoolView pool, int layer,
+                        const std::int32_t* __restrict__ tables, int table_stride, const DecodeUnit* __restrict__ units,
+                        const __half* __restrict__ q, float scale_log2, const __half* __restrict__ open_tiles,
+                        int n_layers, float* __restrict__ partial_acc, float* __restrict__ partial_ml, int* status) {
   ChainedKernelEntry();
-  extern __shared__ __align__(16) std::uint8_t smem[];
-  // Query planes in the pool's byte order: [6 heads][hi | lo][256 B], then per (head, half) -128 x the plane sums and
-  // the head's quantization step. They live at the start of the merge scratch, which is only used after the loop.
-  std::uint8_t* planes = smem;                                        // 6 * 2 * 256
-  int* corr = reinterpret_cast<int*>(smem + 6 * 2 * 256);             // [6][2 halves][2 planes]
-  float* q_step = reinterpret_cast<float*>(smem + 6 * 2 * 256 + 96);  // [8]
+  extern __shared__ __align__(1024) std::uint8_t smem[];
+  std::uint32_t* qfrag = reinterpret_cast<std::uint32_t*>(smem + kKv8QfragOff);
+  std::uint64_t* full_bar = reinterpret_cast<std::uint64_t*>(smem + kKv8BarOff);
+  int* done_cnt = reinterpret_cast<int*>(smem + kKv8DoneOff);     // warps done reading a stage's page
+  int* fill_cnt = reinterpret_cast<int*>(smem + kKv8FillOff);     // fills issued to a stage so far
+  float* q_step = reinterpret_cast<float*>(smem + kKv8QStepOff);
+  int2* q_corr = reinterpret_cast<int2*>(smem + kKv8QCorrOff);    // -128 x the plane sums of each query half
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kKv8AbortOff);
+  if ((SmemAddr(smem) & 1023U) != 0) {   // never seen; a misaligned swizzle would corrupt results
+    if (threadIdx.x == 0) atomicExch(status, kStatusSmemMisaligned);
+    return;
+  }
 
   const DecodeUnit u = units[blockIdx.x];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kw = warp & (kKv8KeyGroups - 1);   // tile kw of a page
+  const int par = warp / kKv8KeyGroups;        // this warp's pages: index par, par + 2, ... of the unit
   const int g = lane >> 2, t = lane & 3;
   const int n_pages = u.page_end - u.page_begin;
   if (n_pages <= 0) return;
+  const std::int32_t* row = tables + static_cast<std::size_t>(u.seq) * table_stride + u.page_begin;
 
-  if (warp < kGroup) {   // quantize head `warp` to two int8 planes, bytes in the order the K pool holds a dword
+  // Gather of one page into a ring stage; a whole converged warp calls it, one elected lane issues. Once a wait has
+  // given up nothing more is fetched: the CTA is on its way out and must not leave copies in flight behind it.
+  auto issue = [&](int s, std::int32_t page) {
+    if (*abort_flag != 0) return;
+    page = min(max(page, 0), pool.num_pages - 1);   // never trust a table entry read from memory
+    const std::size_t rec = (static_cast<std::size_t>(layer) * pool.num_pages + page) * kKvHeads + u.kvh;
+    const int y = static_cast<int>(rec * kPageTokens);
+    if (ElectOne()) {
+      fill_cnt[s] += 1;
+      MbarArriveExpectTx(&full_bar[s], kKv8TxBytes);
+      TmaLoad2D(smem + kKv8KOff + s * kKv8KBytes, &kmap, 0, y, &full_bar[s]);
+      TmaLoad2D(smem + kKv8KOff + s * kKv8KBytes + kKv8BoxBytes, &kmap, 128, y, &full_bar[s]);
+      BulkLoad(smem + kKv8VOff + s * kKv8VBytes, pool.vcodes + rec * kKv8VBytes, kKv8VBytes, &full_bar[s]);
+      BulkLoad(smem + kKv8VsOff + s * kKv8VsBytes, pool.vscales + rec * (kKv8VsBytes / 2), kKv8VsBytes, &full_bar[s]);
+      BulkLoad(smem + kKv8KsOff + s * kKv8KsBytes, pool.kscales + rec * (kKv8KsBytes / 2), kKv8KsBytes, &full_bar[s]);
+    }
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      PrefetchTensorMap(&kmap);
+      for (int s = 0; s < kKv8Stages; ++s) {
+        MbarInit(&full_bar[s], 1);
+        done_cnt[s] = 0;
+        fill_cnt[s] = 0;
+      }
+      *abort_flag = 0;
+      FenceBarrierInit();
+    }
+    __syncwarp();
+    for (int i = 0; i < kKv8Stages && i < n_pages; ++i) issue(i, __ldg(row + i));
+  }
+
+  // Query planes through shared memory. Warp h < 6 quantizes head h: lane l holds dims 8 l .. 8 l + 7, bytes in the
+  // pool's order (a dword's dims in slots d0, d2, d1, d3). q16 = rint(q * 32000 / amax), hi = (q16 + 128) >> 8,
+  // lo = q16 - 256 hi. The A operand of 32-byte block b for lane (g = head, t): a0 = hi bytes 4t .. 4t+3, a1 = lo of the
+  // same, a2 = hi bytes 16+4t .., a3 = lo of those: rows 0-5 of the MMA are the hi plane, rows 8-13 the lo plane.
+  if (warp < kGroup) {
     const __half* qrow = q + (static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + warp) * kHeadDim;
     const uint4 raw = *reinterpret_cast<const uint4*>(qrow + 8 * lane);
     const __half2* hp = reinterpret_cast<const __half2*>(&raw);
@@ -210,184 +304,241 @@ __global__ void __launch_bounds__(kKv8Threads, 2)
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFU, amax, o));
     const float inv = amax > 0.0F ? kQSteps / amax : 0.0F;
-    int hi[8], lo[8], sum_hi = 0, sum_lo = 0;
+    std::uint32_t hi_w[2] = {0, 0}, lo_w[2] = {0, 0};
+    int sum_hi = 0, sum_lo = 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int q16 = __float2int_rn(x[i] * inv);
-      hi[i] = (q16 + 128) >> 8;
-      lo[i] = q16 - hi[i] * 256;
-      sum_hi += hi[i], sum_lo += lo[i];
+      const int hi = (q16 + 128) >> 8;
+      const int lo = q16 - hi * 256;
+      sum_hi += hi, sum_lo += lo;
+      const int slot = (i & 3) == 1 ? 2 : (i & 3) == 2 ? 1 : (i & 3);
+      hi_w[i >> 2] |= (static_cast<std::uint32_t>(hi) & 0xFFU) << (8 * slot);
+      lo_w[i >> 2] |= (static_cast<std::uint32_t>(lo) & 0xFFU) << (8 * slot);
     }
-    auto pack = [](const int* v) {   // byte slots (d0, d2, d1, d3)
-      return (static_cast<std::uint32_t>(v[0]) & 255U) | ((static_cast<std::uint32_t>(v[2]) & 255U) << 8) |
-             ((static_cast<std::uint32_t>(v[1]) & 255U) << 16) | ((static_cast<std::uint32_t>(v[3]) & 255U) << 24);
-    };
-    *reinterpret_cast<uint2*>(planes + (warp * 2 + 0) * 256 + lane * 8) = make_uint2(pack(hi), pack(hi + 4));
-    *reinterpret_cast<uint2*>(planes + (warp * 2 + 1) * 256 + lane * 8) = make_uint2(pack(lo), pack(lo + 4));
 #pragma unroll
     for (int o = 1; o <= 8; o <<= 1) {   // plane sums over the 128-dim half (16 lanes)
       sum_hi += __shfl_xor_sync(0xFFFFFFFFU, sum_hi, o);
       sum_lo += __shfl_xor_sync(0xFFFFFFFFU, sum_lo, o);
     }
-    if ((lane & 15) == 0) {
-      corr[(warp * 2 + (lane >> 4)) * 2 + 0] = -128 * sum_hi;
-      corr[(warp * 2 + (lane >> 4)) * 2 + 1] = -128 * sum_lo;
+    if ((lane & 15) == 0) q_corr[(lane >> 4) * 8 + warp] = make_int2(-128 * sum_hi, -128 * sum_lo);
+    const int blk = lane >> 2, e0 = (lane & 3) * 8;
+    const int reg = e0 < 16 ? 0 : 2, t0 = (e0 & 15) >> 2;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      std::uint32_t* dst = qfrag + ((blk * kKv8QLanes + warp * 4 + t0 + j) << 2) + reg;
+      dst[0] = hi_w[j];
+      dst[1] = lo_w[j];
     }
     if (lane == 0) q_step[warp] = amax / kQSteps;
   }
-  __syncthreads();
-  const int gq = g < kGroup ? g : g - 2;   // the two padding rows of the MMA reuse heads 4, 5
-  const std::uint8_t* my_hi = planes + (gq * 2 + 0) * 256 + 32 * t;
-  const std::uint8_t* my_lo = planes + (gq * 2 + 1) * 256 + 32 * t;
-  int c_hi[2], c_lo[2];
-#pragma unroll
-  for (int hf = 0; hf < 2; ++hf) c_hi[hf] = corr[(gq * 2 + hf) * 2], c_lo[hf] = corr[(gq * 2 + hf) * 2 + 1];
-  const float score_scale = scale_log2 * q_step[gq];
+  __syncthreads();   // barriers initialised, query planes visible
+  const int qlane = lane < kKv8QLanes ? lane : lane - 8;   // the two padding rows of the MMA reuse heads 4, 5
+  const std::uint32_t qa_addr = SmemAddr(qfrag + (qlane << 2));
+  // softmax scale x log2(e) x the head's query step x 1 / 256 (the K pair's first value is 256 s)
+  const float score_scale = scale_log2 * q_step[qlane >> 2] * (1.0F / 256.0F);
+  const int2 corr0 = q_corr[qlane >> 2], corr1 = q_corr[8 + (qlane >> 2)];
 
-  float o_acc[16][4];
+  float o_acc[16][4];   // [c][0..3] = (channel 16c + g, head 2t), (16c + g, 2t+1), (16c + g + 8, 2t), (16c + g + 8, 2t+1)
 #pragma unroll
   for (int c = 0; c < 16; ++c)
 #pragma unroll
     for (int i = 0; i < 4; ++i) o_acc[c][i] = 0.0F;
   float m_run = -INFINITY, l_run = 0.0F;
+  bool alive = true;
 
-  const std::int32_t* row = tables + static_cast<std::size_t>(u.seq) * table_stride;
+  // ldmatrix row of this lane in a K box: matrix (lane >> 3) & 1 is key tile kt, row lane & 7 its column c, which is
+  // key 4 (c / 2) + 2 kt + c % 2 of the 16; 16-byte chunk 2x + (lane >> 4) of the 128-byte row, swizzled.
+  const int lm_key = kw * kTileKeys + 4 * ((lane & 7) >> 1) + 2 * ((lane >> 3) & 1) + (lane & 1);
+  const std::uint32_t lm0 = lm_key * 128 + (((lane >> 4) ^ (lm_key & 7)) << 4);
   const int cur_tile = (u.n_keys - 1) / kTileKeys;
-  const int tile_begin = u.page_begin * kTilesPerPage;
-  const int tile_end = min(u.page_end * kTilesPerPage, cur_tile + 1);
   const __half* open_buf = open_tiles + ((static_cast<std::size_t>(u.seq) * n_layers + layer) * 2 + (u.pad & 1)) * kOpenTileHalfs +
                            static_cast<std::size_t>(u.kvh) * kHeadDim * kTileKeys;
 
-  for (int tile = tile_begin + warp; tile < tile_end; tile += kKv8Warps) {
-    const bool open = tile == cur_tile;
-    std::int32_t page = __ldg(row + tile / kTilesPerPage);
-    page = min(max(page, 0), pool.num_pages - 1);
-    const std::size_t rec = (static_cast<std::size_t>(layer) * pool.num_pages + page) * kKvHeads + u.kvh;
-    const int t_in_page = tile % kTilesPerPage;
-    // Which key of the tile sits in column c of key tile kt: quantized tiles pack keys so that the V dwords unpack
-    // straight into the second MMA's operand (column 2t, 2t+1 of tile 0 = keys 4t, 4t+1; of tile 1 = keys 4t+2, 4t+3);
-    // the open tile is in natural order.
-    auto key_of = [&](int kt, int c) { return open ? kt * 8 + c : 4 * (c >> 1) + 2 * kt + (c & 1); };
-    const std::uint8_t* kbase = pool.kcodes + rec * RecordCodeBytes(kFmtKv8) + static_cast<std::size_t>(t_in_page) * kTileKeys * 256;
-    const std::uint16_t* ksc = pool.kscales + rec * (RecordScaleBytes(kFmtKv8, 0) / 2) + static_cast<std::size_t>(t_in_page) * kTileKeys * 4;
+  for (int i = par; i < n_pages; i += kKv8PageSets) {
+    const int s = i % kKv8Stages;
+    const int gen = i / kKv8Stages;
+    const std::uint32_t phase = static_cast<std::uint32_t>(gen) & 1U;
+    std::int32_t refill_page = 0;
+    if (lane == 0 && i + kKv8Stages < n_pages) refill_page = __ldg(row + i + kKv8Stages);
+    // The mbarrier wait names its phase by parity only; the stage is refilled by the other page set, so the warp first
+    // makes sure (a bounded poll, almost always true at once) that the fill it wants has been issued. A wait that
+    // gives up raises the CTA's abort flag, the warp finishes on whatever the ring holds and the status word marks the
+    // call's results invalid.
+    if (alive) {
+      const int need = gen + 1;
+      volatile int* fills = fill_cnt + s;
+      bool ok = *abort_flag == 0;
+      if (ok && *fills < need) {
+        const std::uint64_t t0 = GlobalTimerNs();
+        while (*fills < need) {
+          if (*abort_flag != 0 || GlobalTimerNs() - t0 > kWaitLimitNs) {
+            ok = false;
+            break;
+          }
+        }
+      }
+      if (!ok || !__all_sync(0xFFFFFFFFU, MbarWait(&full_bar[s], phase))) {
+        alive = false;
+        *abort_flag = 1;
+      }
+    }
+    const int tile = (u.page_begin + i) * kTilesPerPage + kw;
+    if (tile <= cur_tile) {   // warp-uniform: tiles past the newest key hold nothing
+      const std::uint32_t k_base = SmemAddr(smem + kKv8KOff + s * kKv8KBytes);
 
-    // ---- scores: per 128-dim half the integer sums of the two query planes over the unsigned codes ----
-    float sc[2][2];
-#pragma unroll
-    for (int kt = 0; kt < 2; ++kt) {
-      const std::uint8_t* krow = kbase + key_of(kt, g) * 256 + 32 * t;   // this lane's 32 bytes of each half
-      float part[2] = {0.0F, 0.0F};
+      // ---- scores ----
+      int acc[2][2][4];   // [key tile][half][hi col 2t, hi col 2t+1, lo col 2t, lo col 2t+1]
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
-        const uint4 ka = *reinterpret_cast<const uint4*>(krow + hf * 128), kb = *reinterpret_cast<const uint4*>(krow + hf * 128 + 16);
-        const std::uint32_t kw[8] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w};
-        int acc[4] = {c_hi[hf], c_hi[hf], c_lo[hf], c_lo[hf]};
+        const int2 cr = hf == 0 ? corr0 : corr1;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {   // k-step j: this lane's bytes 8j .. 8j+7 of the half, query bytes likewise
-          const uint2 qh = *reinterpret_cast<const uint2*>(my_hi + hf * 128 + 8 * j);
-          const uint2 ql = *reinterpret_cast<const uint2*>(my_lo + hf * 128 + 8 * j);
-          MmaS8U8Acc(acc, qh.x, ql.x, qh.y, ql.y, kw[2 * j], kw[2 * j + 1]);
-        }
-        // columns 2t, 2t+1 of this key tile: scale pair of their keys, first value = 256 s
+        for (int kt = 0; kt < 2; ++kt) acc[kt][hf][0] = cr.x, acc[kt][hf][1] = cr.x, acc[kt][hf][2] = cr.y, acc[kt][hf][3] = cr.y;
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const std::uint16_t sbits = __ldg(ksc + key_of(kt, 2 * t + j) * 4 + hf * 2);
-          const float sdeq = __half2float(__ushort_as_half(sbits)) * (1.0F / 256.0F);
-          part[j] = fmaf(sdeq, static_cast<float>(acc[j] * 256 + acc[2 + j]), part[j]);
+        for (int b = 0; b < 4; ++b) {
+          std::uint32_t w[4], qa[4];
+          LdMatrixX4(k_base + hf * kKv8BoxBytes + (lm0 ^ (static_cast<std::uint32_t>(b) << 5)), w);
+          LoadQ4(qa, qa_addr + (4 * hf + b) * (kKv8QLanes * 16));
+          MmaS8U8Acc(acc[0][hf], qa, w[0], w[2]);
+          MmaS8U8Acc(acc[1][hf], qa, w[1], w[3]);
         }
       }
-      sc[kt][0] = part[0] * score_scale, sc[kt][1] = part[1] * score_scale;
-    }
-    // keys past the sequence's length (only in its newest tile)
-    if ((tile + 1) * kTileKeys > u.n_keys) {
+      // This thread's four columns are keys 4t .. 4t+3 of the tile (key 4t + 2 kt + j): their scale pairs are 32
+      // consecutive bytes, per key (half 0: 256 s, -384 s; half 1: the same).
+      float sc[2][2];
+      {
+        const uint4* ks = reinterpret_cast<const uint4*>(smem + kKv8KsOff + s * kKv8KsBytes + (kw * kTileKeys + 4 * t) * 8);
+        const uint4 ka = ks[0], kb = ks[1];
+        const std::uint32_t pr[4][2] = {{ka.x, ka.y}, {ka.z, ka.w}, {kb.x, kb.y}, {kb.z, kb.w}};
 #pragma unroll
-      for (int kt = 0; kt < 2; ++kt)
+        for (int kt = 0; kt < 2; ++kt)
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
-          if (tile * kTileKeys + key_of(kt, 2 * t + j) >= u.n_keys) sc[kt][j] = -INFINITY;
-    }
-    float tmax = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
-    tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFU, tmax, 1));
-    tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFU, tmax, 2));
-    if (__any_sync(0xFFFFFFFFU, g < kGroup && tmax > m_run + kLazyRescale)) {
-      const float m_new = fmaxf(m_run, tmax);
-      const float alpha = m_new == -INFINITY ? 1.0F : Exp2Fast(m_run - m_new);
-      m_run = m_new;
-      l_run *= alpha;
-      const float al0 = __shfl_sync(0xFFFFFFFFU, alpha, (2 * t) * 4);
-      const float al1 = __shfl_sync(0xFFFFFFFFU, alpha, (2 * t + 1) * 4);
-#pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        o_acc[c][0] *= al0, o_acc[c][2] *= al0;
-        o_acc[c][1] *= al1, o_acc[c][3] *= al1;
+          for (int j = 0; j < 2; ++j) {
+            const float s0 = __low2float(*reinterpret_cast<const __half2*>(&pr[2 * kt + j][0]));
+            const float s1 = __low2float(*reinterpret_cast<const __half2*>(&pr[2 * kt + j][1]));
+            const float v0 = static_cast<float>(acc[kt][0][j] * 256 + acc[kt][0][2 + j]);
+            const float v1 = static_cast<float>(acc[kt][1][j] * 256 + acc[kt][1][2 + j]);
+            sc[kt][j] = fmaf(s0, v0, s1 * v1) * score_scale;
+          }
       }
-    }
-    const float m_use = m_run == -INFINITY ? 0.0F : m_run;
-    std::uint32_t p_hi[2], p_lo[2];
-    float psum = 0.0F;
+      if (tile == cur_tile) {   // keys past the sequence's length
 #pragma unroll
-    for (int kt = 0; kt < 2; ++kt) {
-      const float p0 = Exp2Fast(sc[kt][0] - m_use), p1 = Exp2Fast(sc[kt][1] - m_use);
-      psum += p0 + p1;
-      const __half2 h2 = __floats2half2_rn(p0, p1);
-      const float2 hf = __half22float2(h2);
-      const __half2 l2 = __floats2half2_rn(p0 - hf.x, p1 - hf.y);
-      p_hi[kt] = *reinterpret_cast<const std::uint32_t*>(&h2);
-      p_lo[kt] = *reinterpret_cast<const std::uint32_t*>(&l2);
-    }
-    l_run += psum;
-    psum += __shfl_xor_sync(0xFFFFFFFFU, psum, 1);
-    psum += __shfl_xor_sync(0xFFFFFFFFU, psum, 2);   // the tile's sum of weights of head g
-    const float ps0 = __shfl_sync(0xFFFFFFFFU, psum, (2 * t) * 4), ps1 = __shfl_sync(0xFFFFFFFFU, psum, (2 * t + 1) * 4);
+        for (int kt = 0; kt < 2; ++kt)
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+            if (tile * kTileKeys + 4 * t + 2 * kt + j >= u.n_keys) sc[kt][j] = -INFINITY;
+      }
 
-    // ---- O^T += V^T P^T ----
-    if (open) {   // fp16 keys in natural order: k-slots (2t, 2t+1) = keys 2t, 2t+1; (2t+8, 2t+9) = keys 2t+8, 2t+9
+      // ---- softmax statistics (per head g, the 16 keys spread over the four lanes of a quad) ----
+      float tmax = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
+      tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFU, tmax, 1));
+      tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFU, tmax, 2));
+      if (__any_sync(0xFFFFFFFFU, lane < kKv8QLanes && tmax > m_run + kLazyRescale)) {
+        const float m_new = fmaxf(m_run, tmax);
+        const float alpha = m_new == -INFINITY ? 1.0F : Exp2Fast(m_run - m_new);
+        m_run = m_new;
+        l_run *= alpha;
+        const float al0 = __shfl_sync(0xFFFFFFFFU, alpha, (2 * t) * 4);
+        const float al1 = __shfl_sync(0xFFFFFFFFU, alpha, (2 * t + 1) * 4);
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        const __half* r0 = open_buf + (16 * c + g) * kTileKeys + 2 * t;
-        const __half* r1 = r0 + 8 * kTileKeys;
-        const std::uint32_t a0 = *reinterpret_cast<const std::uint32_t*>(r0), a1 = *reinterpret_cast<const std::uint32_t*>(r1);
-        const std::uint32_t a2 = *reinterpret_cast<const std::uint32_t*>(r0 + 8), a3 = *reinterpret_cast<const std::uint32_t*>(r1 + 8);
-        MmaF16(o_acc[c], a0, a1, a2, a3, p_hi[0], p_hi[1]);
-        MmaF16(o_acc[c], a0, a1, a2, a3, p_lo[0], p_lo[1]);
+        for (int c = 0; c < 16; ++c) {
+          o_acc[c][0] *= al0, o_acc[c][2] *= al0;
+          o_acc[c][1] *= al1, o_acc[c][3] *= al1;
+        }
       }
-    } else {      // v = (u - 128) a + b with a = S / 256, b = 1.5 S + C' (= the tile's centre), per channel
-      const std::uint8_t* vbase = pool.vcodes + rec * RecordCodeBytes(kFmtKv8) + static_cast<std::size_t>(t_in_page) * kHeadDim * 16;
-      const std::uint16_t* vst = pool.vscales + rec * (RecordScaleBytes(kFmtKv8, 1) / 2) + static_cast<std::size_t>(t_in_page) * kHeadDim * 2;
+      const float m_use = m_run == -INFINITY ? 0.0F : m_run;
+      std::uint32_t p_hi[2], p_lo[2];
+      float psum = 0.0F;
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        const int ch0 = 16 * c + g, ch1 = ch0 + 8;
-        const std::uint32_t w0 = __ldg(reinterpret_cast<const std::uint32_t*>(vbase + ch0 * 16 + 4 * t));
-        const std::uint32_t w1 = __ldg(reinterpret_cast<const std::uint32_t*>(vbase + ch1 * 16 + 4 * t));
-        const std::uint32_t s0 = __ldg(reinterpret_cast<const std::uint32_t*>(vst + ch0 * 2));
-        const std::uint32_t s1 = __ldg(reinterpret_cast<const std::uint32_t*>(vst + ch1 * 2));
-        std::uint32_t a0, a1, a2, a3;
-        Offset8x4ToHalf2(w0, a0, a2);   // bytes (0, 2) = keys 4t, 4t+1;  bytes (1, 3) = keys 4t+2, 4t+3
-        Offset8x4ToHalf2(w1, a1, a3);
-        float d[4], e[4];
-        MmaF16Zero(d, a0, a1, a2, a3, p_hi[0], p_hi[1]);
-        MmaF16Zero(e, a0, a1, a2, a3, p_lo[0], p_lo[1]);
-        const float2 st0 = __half22float2(*reinterpret_cast<const __half2*>(&s0));
-        const float2 st1 = __half22float2(*reinterpret_cast<const __half2*>(&s1));
-        const float sa0 = st0.x * (1.0F / 256.0F), sb0 = fmaf(1.5F, st0.x, st0.y);
-        const float sa1 = st1.x * (1.0F / 256.0F), sb1 = fmaf(1.5F, st1.x, st1.y);
-        o_acc[c][0] = fmaf(sa0, d[0] + e[0], fmaf(sb0, ps0, o_acc[c][0]));
-        o_acc[c][1] = fmaf(sa0, d[1] + e[1], fmaf(sb0, ps1, o_acc[c][1]));
-        o_acc[c][2] = fmaf(sa1, d[2] + e[2], fmaf(sb1, ps0, o_acc[c][2]));
-        o_acc[c][3] = fmaf(sa1, d[3] + e[3], fmaf(sb1, ps1, o_acc[c][3]));
+      for (int kt = 0; kt < 2; ++kt) {
+        const float p0 = Exp2Fast(sc[kt][0] - m_use), p1 = Exp2Fast(sc[kt][1] - m_use);
+        psum += p0 + p1;
+        const __half2 h2 = __floats2half2_rn(p0, p1);
+        const float2 hf = __half22float2(h2);
+        const __half2 l2 = __floats2half2_rn(p0 - hf.x, p1 - hf.y);
+        p_hi[kt] = *reinterpret_cast<const std::uint32_t*>(&h2);
+        p_lo[kt] = *reinterpret_cast<const std::uint32_t*>(&l2);
+      }
+      l_run += psum;
+
+      // ---- O^T += V^T P^T: k-slots (2t, 2t+1) = keys 4t, 4t+1 and (2t+8, 2t+9) = keys 4t+2, 4t+3 ----
+      if (tile == cur_tile) {   // the open tile, fp16 [channel][16 keys]
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const uint2 r0 = *reinterpret_cast<const uint2*>(open_buf + (16 * c + g) * kTileKeys + 4 * t);
+          const uint2 r1 = *reinterpret_cast<const uint2*>(open_buf + (16 * c + g + 8) * kTileKeys + 4 * t);
+          MmaF16(o_acc[c], r0.x, r1.x, r0.y, r1.y, p_hi[0], p_hi[1]);
+          MmaF16(o_acc[c], r0.x, r1.x, r0.y, r1.y, p_lo[0], p_lo[1]);
+        }
+      } else {
+        psum += __shfl_xor_sync(0xFFFFFFFFU, psum, 1);
+        psum += __shfl_xor_sync(0xFFFFFFFFU, psum, 2);   // the tile's sum of weights of head g
+        const float ps0 = __shfl_sync(0xFFFFFFFFU, psum, (2 * t) * 4), ps1 = __shfl_sync(0xFFFFFFFFU, psum, (2 * t + 1) * 4);
+        // One ldmatrix.x4 = the dwords of 32 channels (row = a channel's 16 bytes): matrices 0 / 1 are channels
+        // 16c + r and 16c + 8 + r of c = 2 cp, matrices 2 / 3 those of c = 2 cp + 1; the thread's word is keys 4t .. 4t+3
+        // in byte slots (0, 2, 1, 3).
+        const std::uint32_t v_addr = SmemAddr(smem + kKv8VOff + s * kKv8VBytes + kw * (kHeadDim * kTileKeys)) + lane * 16;
+        const std::uint32_t* vs = reinterpret_cast<const std::uint32_t*>(smem + kKv8VsOff + s * kKv8VsBytes + kw * (kHeadDim * 4)) + g;
+#pragma unroll
+        for (int cp = 0; cp < 8; ++cp) {
+          std::uint32_t w[4];
+          LdMatrixX4(v_addr + cp * 512, w);
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            const int c = 2 * cp + x;
+            std::uint32_t a0, a1, a2, a3;
+            Offset8x4ToHalf2(w[2 * x], a0, a2);       // bytes (0, 2) = keys 4t, 4t+1;  bytes (1, 3) = keys 4t+2, 4t+3
+            Offset8x4ToHalf2(w[2 * x + 1], a1, a3);
+            float d[4];
+            MmaF16Zero(d, a0, a1, a2, a3, p_hi[0], p_hi[1]);
+            MmaF16(d, a0, a1, a2, a3, p_lo[0], p_lo[1]);
+            const std::uint32_t s0 = vs[16 * c], s1 = vs[16 * c + 8];
+            const float2 st0 = __half22float2(*reinterpret_cast<const __half2*>(&s0));
+            const float2 st1 = __half22float2(*reinterpret_cast<const __half2*>(&s1));
+            const float sa0 = st0.x * (1.0F / 256.0F), sb0 = fmaf(1.5F, st0.x, st0.y);
+            const float sa1 = st1.x * (1.0F / 256.0F), sb1 = fmaf(1.5F, st1.x, st1.y);
+            o_acc[c][0] = fmaf(sa0, d[0], fmaf(sb0, ps0, o_acc[c][0]));
+            o_acc[c][1] = fmaf(sa0, d[1], fmaf(sb0, ps1, o_acc[c][1]));
+            o_acc[c][2] = fmaf(sa1, d[2], fmaf(sb1, ps0, o_acc[c][2]));
+            o_acc[c][3] = fmaf(sa1, d[3], fmaf(sb1, ps1, o_acc[c][3]));
+          }
+        }
       }
     }
+
+    // The last of the page's four warps to finish with the stage refills it. The MMAs above consumed every shared
+    // memory read of the stage, so this warp's reads are complete.
+    __syncwarp();
+    int last = 0;
+    if (lane == 0) {
+      __threadfence_block();
+      last = atomicAdd(&done_cnt[s], 1) == kKv8KeyGroups - 1;
+      if (last) {
+        done_cnt[s] = 0;
+        __threadfence_block();
+      }
+    }
+    last = __shfl_sync(0xFFFFFFFFU, last, 0);
+    if (last != 0 && i + kKv8Stages < n_pages) issue(s, __shfl_sync(0xFFFFFFFFU, refill_page, 0));
   }
+  if (!alive && lane == 0) atomicExch(status, kStatusWaitTimeout);
   l_run += __shfl_xor_sync(0xFFFFFFFFU, l_run, 1);
   l_run += __shfl_xor_sync(0xFFFFFFFFU, l_run, 2);
 
-  __syncthreads();   // the query planes are dead: the scratch now holds the warps' results
+  // Every stage has been consumed (or a wait gave up): the ring is free to hold the merge scratch.
+  __syncthreads();
+  if (*abort_flag != 0) {   // the same value in every thread now
+    // Copies still in flight get one more bounded wait each, so that none lands in shared memory that is being reused.
+    if (threadIdx.x == 0)
+      for (int x = 0; x < kKv8Stages; ++x)
+        if (fill_cnt[x] > 0) MbarWait(&full_bar[x], static_cast<std::uint32_t>(fill_cnt[x] - 1) & 1U, 20000000ULL);
+    __syncthreads();
+  }
   float* merge = reinterpret_cast<float*>(smem);
   {
     float* mine = merge + warp * kMergeWarpFloats;
 #pragma unroll
     for (int c = 0; c < 16; ++c) {
-      // o_acc[c][0..3] = (channel 16c + g, head 2t), (16c + g, 2t+1), (16c + g + 8, 2t), (16c + g + 8, 2t+1)
       if (2 * t < kGroup) {
         mine[(2 * t) * kMergeStride + 16 * c + g] = o_acc[c][0];
         mine[(2 * t + 1) * kMergeStride + 16 * c + g] = o_acc[c][1];
@@ -416,7 +567,7 @@ __global__ void __launch_bounds__(kKv8Threads, 2)
       }
       float a = 0.0F, lsum = 0.0F;
 #pragma unroll
-      for (int w = 0; w < kKv8Warps; ++w) {
+      for (int w = 0; w < kKv8Warps; ++w) {   // a warp that saw no tile has max -inf and weight 0
         const float wgt = mw[w] == -INFINITY ? 0.0F : exp2f(mw[w] - M);
         const float* src = merge + w * kMergeWarpFloats;
         a = fmaf(wgt, src[h * kMergeStride + tid], a);
@@ -451,9 +602,9 @@ cudaError_t LaunchKv8AppendV(const PoolView& pool, int layer, int n_work, const 
 
 cudaError_t LaunchKv8DecodePart(const DecodeLaunch& a, const void* open_tiles_dev, int n_layers, cudaStream_t stream) {
   if (a.n_units <= 0 || a.n_seqs <= 0) return cudaSuccess;
-  return LaunchChained(Kv8DecodePartKernel, a.n_units, kKv8Threads, kKv8SmemBytes, stream, a.pool, a.layer, a.tables_dev,
-                       a.table_stride, a.units_dev, static_cast<const __half*>(a.q_dev), a.scale_log2,
-                       static_cast<const __half*>(open_tiles_dev), n_layers, a.partial_acc, a.partial_ml);
+  return LaunchChained(Kv8DecodePartKernel, a.n_units, kKv8Threads, kKv8SmemBytes, stream, *a.kmap, a.pool, a.layer,
+                       a.tables_dev, a.table_stride, a.units_dev, static_cast<const __half*>(a.q_dev), a.scale_log2,
+                       static_cast<const __half*>(open_tiles_dev), n_layers, a.partial_acc, a.partial_ml, a.status_dev);
 }
 
 }  // namespace yahkv

@@ -146,6 +146,20 @@ __device__ __forceinline__ void Nib8ToU8(std::uint32_t w, std::uint32_t& lo, std
   lo = (w << 4) & 0xF0F0F0F0U;
   hi = w & 0xF0F0F0F0U;
 }
+// d = (a & b) ^ c as one logic instruction with all three inputs in registers.
+__device__ __forceinline__ std::uint32_t AndXor(std::uint32_t a, std::uint32_t b, std::uint32_t c) {
+  std::uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+// The same nibbles as the SIGNED bytes 16 (n - 8): the nibble at the top of its byte with the byte's sign bit
+// flipped, so that the q4_0 offset costs nothing and the codes enter the s8 x s8 MMA with a zero accumulator.
+// Three instructions (a shift and two and-xor) given the mask 0xF0F0F0F0 and the flip 0x80808080 in registers.
+__device__ __forceinline__ void Nib8ToS8(std::uint32_t mask, std::uint32_t flip, std::uint32_t w, std::uint32_t& lo,
+                                         std::uint32_t& hi) {
+  lo = AndXor(w << 4, mask, flip);
+  hi = AndXor(w, mask, flip);
+}
 // d = (a & b) | c as ONE logic instruction with all three inputs in registers. Written as a & imm | imm the compiler
 // must split it (an instruction carries one immediate), which doubles the cost of every nibble conversion.
 __device__ __forceinline__ std::uint32_t AndOr(std::uint32_t a, std::uint32_t b, std::uint32_t c) {
@@ -155,11 +169,13 @@ __device__ __forceinline__ std::uint32_t AndOr(std::uint32_t a, std::uint32_t b,
 }
 // The three constants of the nibble conversion, held in registers the compiler cannot turn back into immediates.
 struct NibConsts {
-  std::uint32_t lo_mask, hi_mask, magic;
+  std::uint32_t lo_mask, hi_mask, magic, top_mask, sign_flip;
   __device__ __forceinline__ void Load() {
     asm volatile("mov.u32 %0, 0x000F000F;" : "=r"(lo_mask));
     asm volatile("mov.u32 %0, 0x00F000F0;" : "=r"(hi_mask));
     asm volatile("mov.u32 %0, 0x64006400;" : "=r"(magic));
+    asm volatile("mov.u32 %0, 0xF0F0F0F0;" : "=r"(top_mask));
+    asm volatile("mov.u32 %0, 0x80808080;" : "=r"(sign_flip));
   }
 };
 // Four packed q4_0 bytes -> low nibbles of bytes (0,2), (1,3) and high nibbles of bytes (0,2), (1,3), each minus 8.
