@@ -244,6 +244,9 @@ class KvHost {
       const int pages = static_cast<int>((n + kPageTokens - 1) / kPageTokens);
       int per = n_splits > 0 ? (pages + n_splits - 1) / n_splits : auto_pages;
       per = std::max(per, (pages + max_splits - 1) / max_splits);
+      // The part kernel's two page sets take alternate pages of a unit: an odd count leaves one set idle for a page,
+      // so a unit costs as much as the next even count. Rounding up never raises the number of units.
+      if (per > 1) per += per & 1;
       const int nu = (pages + per - 1) / per;
       for (int h = hb; h < hb + hc; ++h) {   // heads outside the context's range keep n_partials = 0
         items[static_cast<std::size_t>(b) * kKvHeads + h] = {static_cast<std::int32_t>(units.size()), nu};
