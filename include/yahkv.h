@@ -45,9 +45,10 @@ extern "C" {
  *      pools: codes [page][4][4 tiles][256][16 B], pairs [page][4][4][256][2] fp16.
  *   The tile of a sequence's newest key stays in fp16 (the "open tile", engine/gpu/loom/tools/gen_decode_attn.py:426-427)
  *   and attention reads it from there; a tile is quantized when its 16th key arrives.
- * 2336 B per token per layer. Supported with this format: yahkv_append, yahkv_attend_decode, the host-buffer decode
- * steps, yahkv_read_page / yahkv_write_page, yahkv_seq_set_kmean, yahkv_read_open_tile. Not supported (refused with
- * YAHKV_ERR_INVALID): prefill attention, the fused RoPE append, decode batches, snapshots, yahkv_export_token,
+ * 2336 B per token per layer. Supported with this format: yahkv_append, yahkv_attend_decode, yahkv_attend_prefill
+ * (its dequantize pass reads the tile of each sequence's newest key from the open buffer, the others from the pools),
+ * the host-buffer decode steps, yahkv_read_page / yahkv_write_page, yahkv_seq_set_kmean, yahkv_read_open_tile. Not
+ * supported (refused with YAHKV_ERR_INVALID): the fused RoPE append, decode batches, snapshots, yahkv_export_token,
  * head-sharded contexts, and yahkv_seq_set_len to anything but 0. */
 #define YAHKV_FMT_KV8A16 2
 

@@ -250,3 +250,48 @@ class Kv8Pool:
                                               ctypes.c_int64(n_keys), _p(q.view(np.uint16)), _p(gate),
                                               ctypes.c_double(scale), _p(out), threads)
         return out
+
+    def dequantized(self, table, n_keys, open_tile):
+        """(K, V) [n_keys][4][256] f32 of one sequence as attention sees them: K = (u - 128) s (mean not added back),
+        V tiles dequantized except the tile of the newest key, which is the open fp16 tile."""
+        table = np.ascontiguousarray(table, np.int32)
+        validate_table(table, self.num_pages)
+        K = np.zeros((n_keys, KV_HEADS, HEAD_DIM), np.float32)
+        V = np.zeros((n_keys, KV_HEADS, HEAD_DIM), np.float32)
+        for pos in range(n_keys):
+            pg, tok = table[pos // PAGE_TOKENS], pos % PAGE_TOKENS
+            K[pos] = kv8_deq_k(self.kcodes[pg, :, tok], self.kscales[pg, :, tok])
+        newest = (n_keys - 1) // 16
+        for t in range(newest + 1):
+            k0, k1 = 16 * t, min(n_keys, 16 * t + 16)
+            if t == newest:
+                tile = np.ascontiguousarray(open_tile).view(np.float16).astype(np.float32)      # [4][256][16]
+                V[k0:k1] = np.transpose(tile, (2, 0, 1))[:k1 - k0]
+            else:
+                pg, tl = table[k0 // PAGE_TOKENS], (k0 % PAGE_TOKENS) // 16
+                V[k0:k1] = kv8_deq_vtile(self.vcodes[pg, :, tl], self.vstats[pg, :, tl])[:k1 - k0]
+        return K, V
+
+    def attend_prefill_f64(self, table, start, q, open_tile, q_begin=0, q_end=None, gate=None, scale=1.0 / 16.0):
+        """Causal attention of chunk rows [q_begin, q_end) (row i sits at position start + i) over the cache as it is
+        after the chunk's append, in float64: q [rows][24][256] fp16 -> out [q_end - q_begin][24][256]. The
+        dequantize-then-attend form of the reference's prefill (gen_attn_fa.py:4648-4860, :3005-3042)."""
+        q = np.ascontiguousarray(q, np.float16)
+        q_end = q.shape[0] if q_end is None else q_end
+        n_keys = start + q.shape[0]
+        K, V = self.dequantized(table, n_keys, open_tile)
+        K, V = K.astype(np.float64), V.astype(np.float64)
+        out = np.zeros((q_end - q_begin, Q_HEADS, HEAD_DIM), np.float64)
+        group = Q_HEADS // KV_HEADS
+        for i in range(q_begin, q_end):
+            vis = start + i + 1
+            for h in range(Q_HEADS):
+                kvh = h // group
+                s_ = (K[:vis, kvh] @ q[i, h].astype(np.float64)) * scale
+                w = np.exp(s_ - s_.max())
+                o = (w @ V[:vis, kvh]) / w.sum()
+                if gate is not None:
+                    o = o / (1.0 + np.exp(-np.asarray(gate[i, h], np.float64)))
+                out[i - q_begin, h] = o
+        return out
+

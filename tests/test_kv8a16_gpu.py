@@ -134,9 +134,62 @@ def test_ragged_batch_with_means_and_decode_steps():
     assert_pools(cache, 0, pool)
     # what the format does not support is refused before anything is launched
     x = torch.zeros(4, 24, 256, dtype=torch.float16, device="cuda")
-    for call in (lambda: cache.attend_prefill(0, [seqs[0]], [1], x, x), lambda: cache.export_token(0, seqs[0], 0),
+    for call in (lambda: cache.export_token(0, seqs[0], 0),
                  lambda: yahkv.DecodeBatch(cache, seqs), lambda: cache.seq_set_len(seqs[0], 1),
                  lambda: cache.seq_set_kmean(seqs[0], np.zeros((4, 256), np.float32))):
         with pytest.raises(yahkv.YahkvError):
             call()
     cache.close()
+
+
+def test_chunked_prefill_attention():
+    """A prompt goes in as chunks (append, then attend_prefill over the cache, the chunk included), with lengths that
+    end inside a tile, on a tile edge and on a page edge; sampled rows of every chunk against the float64 model over the
+    dequantized cache. The operands are fp16 on the tensor cores: 2e-3 absolute, 1e-3 of the largest output."""
+    rng = np.random.default_rng(23)
+    chunks = [300, 212, 128, 1, 391]           # ends: inside a tile, 512 (page edge), 640, 641, 1032
+    total = sum(chunks)
+    pages = (total + 63) // 64
+    num_pages = pages + 4
+    cache = yahkv.KvCache(n_layers=2, num_pages=num_pages, fmt=yahkv.FMT_KV8A16, max_seqs=2, max_pages_per_seq=pages,
+                          max_batch_tokens=512, max_prefill_keys=pages * 64)
+    pool = O.Kv8Pool(num_pages)
+    table = rng.permutation(num_pages)[:pages].astype(np.int32)
+    m = (0.5 * rng.standard_normal((4, 256))).astype(np.float32)
+    seq = cache.seq_create()
+    cache.seq_set_table(seq, table)
+    cache.seq_set_kmean(seq, m)
+    open_tile, mean = pool.new_sequence(m)
+    K = (rng.standard_normal((total, 4, 256)) + m).astype(np.float16)
+    V = rng.standard_normal((total, 4, 256)).astype(np.float16)
+    start = 0
+    for c in chunks:
+        q = (0.5 * rng.standard_normal((c, 24, 256))).astype(np.float16)
+        gate = rng.standard_normal((c, 24, 256)).astype(np.float32)
+        cache.append(1, np.full(c, seq, np.int32), np.arange(start, start + c, dtype=np.int64), dev(K[start:start + c]),
+                     dev(V[start:start + c]))
+        pool.append(table, start, K[start:start + c], V[start:start + c], open_tile, mean)
+        out = torch.full((c, 24, 256), float("nan"), device="cuda")
+        cache.attend_prefill(1, [seq], [c], dev(q), out, gate=dev(gate), out_dtype=yahkv.OUT_F32)
+        cache.sync()
+        got = out.cpu().numpy().astype(np.float64)
+        assert np.isfinite(got).all()
+        rows = sorted({0, c - 1, c // 2, min(c - 1, 127), min(c - 1, 128)})
+        for r in rows:
+            want = pool.attend_prefill_f64(table, start, q, open_tile, r, r + 1, gate)[0]
+            err = np.abs(got[r] - want).max()
+            assert err <= 2e-3 and err <= 1e-3 * np.abs(want).max(), (start, c, r, err, np.abs(want).max())
+        start += c
+    assert_pools(cache, 1, pool)
+    # decode continues from the prefilled cache
+    k1 = rng.standard_normal((1, 4, 256)).astype(np.float16)
+    v1 = rng.standard_normal((1, 4, 256)).astype(np.float16)
+    q1 = (0.5 * rng.standard_normal((1, 24, 256))).astype(np.float16)
+    cache.append(1, [seq], [start], dev(k1), dev(v1))
+    pool.append(table, start, k1, v1, open_tile, mean)
+    got = run_decode(cache, 1, [seq], q1)[0]
+    want = pool.attend_decode_f64(table, start + 1, q1[0], open_tile)
+    err = np.abs(got - want).max()
+    assert err <= 2e-3 and err / np.abs(want).max() < 1e-4, err
+    cache.close()
+

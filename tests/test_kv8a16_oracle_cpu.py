@@ -81,3 +81,15 @@ def test_paged_append_and_attention_with_an_open_tile(g8):
     for name, gate in (("gated", r["gate"]), ("plain", None)):
         got = pool.attend_decode_f64(table, n, r["q"], open_tile, gate)
         assert np.abs(got - g8[f"attn_{name}"]).max() < 1e-12, name
+    # the prefill model (numpy over the same dequantizers): its last row is the decode model's answer, and an earlier
+    # row sees only the keys up to its own position
+    for gate in (r["gate"], None):
+        want = pool.attend_decode_f64(table, n, r["q"], open_tile, gate)
+        got = pool.attend_prefill_f64(table, n - 1, r["q"][None], open_tile, gate=None if gate is None else gate[None])[0]
+        assert np.abs(got - want).max() < 1e-12
+    q2 = np.stack([r["q"], r["q"]])
+    two = pool.attend_prefill_f64(table, n - 2, q2, open_tile)
+    Kd, Vd = pool.dequantized(table, n, open_tile)
+    s = (Kd[:n - 1, 0].astype(np.float64) @ q2[0, 0].astype(np.float64)) / 16.0
+    w = np.exp(s - s.max())
+    assert np.abs(two[0, 0] - (w @ Vd[:n - 1, 0].astype(np.float64)) / w.sum()).max() < 1e-12

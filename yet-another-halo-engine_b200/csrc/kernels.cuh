@@ -102,7 +102,7 @@ struct PrefillSeq {
   std::int32_t kv_len;      // keys in the cache, the chunk included
   std::int32_t kv_rows;     // n_pages * 64
   std::int32_t kv_row0;     // first scratch row of the sequence
-  std::int32_t pad[3];
+  std::int32_t pad[3];      // pad[0]: kv8a16 only, which of the sequence's two open-tile buffers is current
 };
 // One tile of prefill attention: 128 query rows of one sequence for one query head.
 constexpr int kPrefillTileRows = 128;
@@ -234,6 +234,8 @@ struct PrefillLaunch {
   int* status_dev;
 };
 cudaError_t LaunchPrefillDequant(const PrefillLaunch& a, cudaStream_t stream);
+// kv8a16: the same pass for that format (kv8a16.cu); PrefillSeq::pad[0] names each sequence's current open buffer.
+cudaError_t LaunchKv8PrefillDequant(const PrefillLaunch& a, const void* open_tiles_dev, int n_layers, cudaStream_t stream);
 cudaError_t LaunchPrefill(const PrefillLaunch& a, cudaStream_t stream);
 cudaError_t ConfigurePrefillKernels();
 // Encodes a 2-D tiled tensor map (row-major, `inner` elements of `elem_bytes` per row, 128-byte swizzle). Host only.

@@ -23,7 +23,8 @@
 // reads; which buffer is current is host state, handed to the kernels per call.
 //
 // Decode attention has the shape of the q8_0 / q4_0 kernel (a TMA-filled ring of page stages, whole-tile warps); see
-// the comment above it.
+// the comment above it. Prefill attention uses the tensor-core kernel of the other formats behind a dequantize pass of
+// its own (Kv8DequantPagesKernel).
 #include <cuda_fp16.h>
 
 #include <cmath>
@@ -579,6 +580,101 @@ __global__ void __launch_bounds__(kKv8Threads, 2)
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Prefill attention's dequantize pass for this format: every page of every sequence of the call, through the block
+// table, to the token-major fp16 scratch the tensor-core kernel reads (the reference's yah_kdeq* / yah_vdeq* pre-pass,
+// engine/gpu/loom/tools/gen_attn_fa.py:4648-4860). K = fp16((u - 128) s) per 128-dim half, bytes back in dim order;
+// the mean stays out (it moves every score of a head by the same amount). V = fp16((u - 128) a + b) per (tile,
+// channel), transposed from [channel][16 keys] to [key][channel]; the tile that holds the sequence's newest key comes
+// from the open fp16 buffer, as in decode attention.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kKv8DequantThreads = 256;
+__global__ void __launch_bounds__(kKv8DequantThreads)
+    Kv8DequantPagesKernel(PoolView pool, int layer, int n_layers, const std::int32_t* __restrict__ tables,
+                          int table_stride, const PrefillSeq* __restrict__ seqs, const __half* __restrict__ open_tiles,
+                          __half* __restrict__ k16, __half* __restrict__ v16) {
+  const PrefillSeq ps = seqs[blockIdx.z];
+  const int p = blockIdx.x, kvh = blockIdx.y;
+  if (p >= ps.n_pages || !pool.OwnsKvHead(kvh)) return;
+  std::int32_t page = __ldg(tables + static_cast<std::size_t>(ps.seq) * table_stride + p);
+  page = min(max(page, 0), pool.num_pages - 1);
+  const std::size_t rec = (static_cast<std::size_t>(layer) * pool.num_pages + page) * kKvHeads + kvh;
+  const std::size_t out_row0 = static_cast<std::size_t>(ps.kv_row0) + static_cast<std::size_t>(kvh) * ps.kv_rows +
+                               static_cast<std::size_t>(p) * kPageTokens;
+  {   // K: thread -> 8 bytes of a token row = dims 8 grp .. 8 grp + 7 with the middle two of each dword swapped
+    const std::uint8_t* codes = pool.kcodes + rec * RecordCodeBytes(kFmtKv8);
+    const std::uint16_t* scales = pool.kscales + rec * (RecordScaleBytes(kFmtKv8, 0) / 2);
+    __half* out = k16 + out_row0 * kHeadDim;
+    for (int gidx = threadIdx.x; gidx < kPageTokens * (kHeadDim / 8); gidx += kKv8DequantThreads) {
+      const int tok = gidx >> 5, grp = gidx & 31;
+      const float s = __half2float(__ushort_as_half(scales[tok * 4 + (grp >> 4) * 2])) * (1.0F / 256.0F);
+      const uint2 c = *reinterpret_cast<const uint2*>(codes + tok * 256 + grp * 8);
+      const std::uint8_t* cb = reinterpret_cast<const std::uint8_t*>(&c);
+      float v[8];
+#pragma unroll
+      for (int d = 0; d < 2; ++d) {
+        v[4 * d + 0] = s * static_cast<float>(static_cast<int>(cb[4 * d + 0]) - 128);
+        v[4 * d + 1] = s * static_cast<float>(static_cast<int>(cb[4 * d + 2]) - 128);
+        v[4 * d + 2] = s * static_cast<float>(static_cast<int>(cb[4 * d + 1]) - 128);
+        v[4 * d + 3] = s * static_cast<float>(static_cast<int>(cb[4 * d + 3]) - 128);
+      }
+      uint4 o;
+      __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) oh[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+      *reinterpret_cast<uint4*>(out + static_cast<std::size_t>(tok) * kHeadDim + grp * 8) = o;
+    }
+  }
+  {   // V: thread -> two neighbouring channels of one tile (16 keys each), written as one half2 per key
+    const std::uint8_t* codes = pool.vcodes + rec * RecordCodeBytes(kFmtKv8);
+    const std::uint16_t* stats = pool.vscales + rec * (RecordScaleBytes(kFmtKv8, 1) / 2);
+    const int open_tile = (ps.kv_len - 1) / kTileKeys;
+    const __half* open_buf = open_tiles + ((static_cast<std::size_t>(ps.seq) * n_layers + layer) * 2 + (ps.pad[0] & 1)) * kOpenTileHalfs +
+                             static_cast<std::size_t>(kvh) * kHeadDim * kTileKeys;
+    __half* out = v16 + out_row0 * kHeadDim;
+    for (int w = threadIdx.x; w < kTilesPerPage * (kHeadDim / 2); w += kKv8DequantThreads) {
+      const int tl = w / (kHeadDim / 2), ch = (w % (kHeadDim / 2)) * 2;
+      const int tile = p * kTilesPerPage + tl;
+      float val[2][kTileKeys];
+      if (tile == open_tile) {
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          const uint4* src = reinterpret_cast<const uint4*>(open_buf + (ch + x) * kTileKeys);
+          const uint4 a = src[0], b = src[1];
+          const __half2* ha = reinterpret_cast<const __half2*>(&a);
+          const __half2* hb = reinterpret_cast<const __half2*>(&b);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 fa = __half22float2(ha[i]), fb = __half22float2(hb[i]);
+            val[x][2 * i] = fa.x, val[x][2 * i + 1] = fa.y;
+            val[x][8 + 2 * i] = fb.x, val[x][8 + 2 * i + 1] = fb.y;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          const uint4 c = *reinterpret_cast<const uint4*>(codes + (static_cast<std::size_t>(tl) * kHeadDim + ch + x) * 16);
+          const std::uint32_t st = *reinterpret_cast<const std::uint32_t*>(stats + (static_cast<std::size_t>(tl) * kHeadDim + ch + x) * 2);
+          const float2 pr = __half22float2(*reinterpret_cast<const __half2*>(&st));
+          const float a = pr.x * (1.0F / 256.0F), b = fmaf(1.5F, pr.x, pr.y);
+          const std::uint32_t cw[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+          for (int d = 0; d < 4; ++d) {   // dword d byte slot (0, 1, 2, 3) = key 4d + (0, 2, 1, 3)
+            val[x][4 * d + 0] = fmaf(a, static_cast<float>(static_cast<int>(cw[d] & 255U) - 128), b);
+            val[x][4 * d + 2] = fmaf(a, static_cast<float>(static_cast<int>((cw[d] >> 8) & 255U) - 128), b);
+            val[x][4 * d + 1] = fmaf(a, static_cast<float>(static_cast<int>((cw[d] >> 16) & 255U) - 128), b);
+            val[x][4 * d + 3] = fmaf(a, static_cast<float>(static_cast<int>(cw[d] >> 24) - 128), b);
+          }
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < kTileKeys; ++k)
+        *reinterpret_cast<__half2*>(out + static_cast<std::size_t>(tl * kTileKeys + k) * kHeadDim + ch) =
+            __floats2half2_rn(val[0][k], val[1][k]);
+    }
+  }
+}
+
 }  // namespace
 
 cudaError_t ConfigureKv8Kernels() {
@@ -605,6 +701,15 @@ cudaError_t LaunchKv8DecodePart(const DecodeLaunch& a, const void* open_tiles_de
   return LaunchChained(Kv8DecodePartKernel, a.n_units, kKv8Threads, kKv8SmemBytes, stream, *a.kmap, a.pool, a.layer,
                        a.tables_dev, a.table_stride, a.units_dev, static_cast<const __half*>(a.q_dev), a.scale_log2,
                        static_cast<const __half*>(open_tiles_dev), n_layers, a.partial_acc, a.partial_ml, a.status_dev);
+}
+
+cudaError_t LaunchKv8PrefillDequant(const PrefillLaunch& a, const void* open_tiles_dev, int n_layers, cudaStream_t stream) {
+  if (a.n_seqs <= 0 || a.max_pages <= 0) return cudaSuccess;
+  const dim3 grid(static_cast<unsigned>(a.max_pages), kKvHeads, static_cast<unsigned>(a.n_seqs));
+  Kv8DequantPagesKernel<<<grid, kKv8DequantThreads, 0, stream>>>(a.pool, a.layer, n_layers, a.tables_dev, a.table_stride,
+                                                                a.seqs_dev, static_cast<const __half*>(open_tiles_dev),
+                                                                static_cast<__half*>(a.k16_dev), static_cast<__half*>(a.v16_dev));
+  return cudaGetLastError();
 }
 
 }  // namespace yahkv

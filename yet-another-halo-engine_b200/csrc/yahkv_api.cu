@@ -762,7 +762,6 @@ int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const in
                          const int32_t* chunk_lens, const void* q_dev, const float* gate_dev, void* out_dev,
                          int32_t out_dtype, void* stream) {
   if (int r = RequireDevice(ctx, "attend_prefill"); r != YAHKV_OK) return r;
-  if (ctx->cfg.fmt == YAHKV_FMT_KV8A16) return Fail(ctx, YAHKV_ERR_INVALID, "attend_prefill: not available for YAHKV_FMT_KV8A16");
   if (out_dtype != YAHKV_OUT_F16 && out_dtype != YAHKV_OUT_F32) return Fail(ctx, YAHKV_ERR_INVALID, "attend_prefill: bad out_dtype");
   if (n_seqs > 0 && (q_dev == nullptr || out_dev == nullptr)) return Fail(ctx, YAHKV_ERR_INVALID, "attend_prefill: null q or out pointer");
   if ((reinterpret_cast<std::uintptr_t>(q_dev) & 15) != 0 || (reinterpret_cast<std::uintptr_t>(out_dev) & 15) != 0)
@@ -776,6 +775,9 @@ int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const in
   if (e.code != YAHKV_OK) return FailHost(ctx, std::move(e));
   if (ctx->tile_scratch.empty()) return YAHKV_OK;
   if (static_cast<int>(ctx->tile_scratch.size()) > ctx->max_tiles) return Fail(ctx, YAHKV_ERR_CAPACITY, "attend_prefill: too many tiles");
+  const bool kv8 = ctx->cfg.fmt == YAHKV_FMT_KV8A16;
+  if (kv8)   // the tile of each sequence's newest key is read from its current open buffer
+    for (PrefillSeq& ps : ctx->pseq_scratch) ps.pad[0] = ctx->host.open_cur(ps.seq, layer);
   cudaStream_t st = StreamOf(ctx, stream);
   // The fp16 scratch of the dequantize pass: fixed at create when the configuration sizes it, else grown to the
   // largest call seen (a one-time cost per high-water mark, with a device synchronisation).
@@ -813,7 +815,7 @@ int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const in
   a.scale_log2 = ctx->scale_log2, a.status_dev = ctx->status_dev;
   {
     TimedLaunch tl(ctx, YAHKV_KERNEL_PREFILL_DEQUANT, st);
-    YAHKV_CUDA(ctx, LaunchPrefillDequant(a, st));
+    YAHKV_CUDA(ctx, kv8 ? LaunchKv8PrefillDequant(a, ctx->open_tiles_dev, ctx->cfg.n_layers, st) : LaunchPrefillDequant(a, st));
     tl.End();
   }
   TimedLaunch tl(ctx, YAHKV_KERNEL_PREFILL, st);
