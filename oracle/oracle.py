@@ -17,7 +17,7 @@ ORACLE_SO = os.path.join(_HERE, "libyahkv_oracle.so")
 REF_SO = os.path.join(_HERE, "_ref", "libyah_ref_codec.so")
 
 Q_HEADS, KV_HEADS, HEAD_DIM, PAGE_TOKENS, BLOCKS = 24, 4, 256, 64, 8
-FMT_Q8_0, FMT_Q4_0, FMT_KV8A16 = 0, 1, 2
+FMT_Q8_0, FMT_Q4_0, FMT_KV8A16, FMT_KV4A16 = 0, 1, 2, 3
 GGML_Q4_0, GGML_Q8_0 = 2, 8  # ggml type ids the reference's Dequantize takes
 
 
@@ -288,6 +288,110 @@ class Kv8Pool:
             for h in range(Q_HEADS):
                 kvh = h // group
                 s_ = (K[:vis, kvh] @ q[i, h].astype(np.float64)) * scale
+                w = np.exp(s_ - s_.max())
+                o = (w @ V[:vis, kvh]) / w.sum()
+                if gate is not None:
+                    o = o / (1.0 + np.exp(-np.asarray(gate[i, h], np.float64)))
+                out[i - q_begin, h] = o
+        return out
+
+
+# ---- the reference's own kv4a16 format (oracle/kv4a16_oracle.cpp) ------------------------------------------------
+def hadamard256_f64(x):
+    """H256 x / 16 over the last axis (length 256), float64; self-inverse."""
+    x = np.ascontiguousarray(x, np.float64).copy()
+    _o.yahkv_oracle_hadamard256_f64(_p(x), x.size // HEAD_DIM)
+    return x
+
+
+def kv4_quant_k(k_row, mean):
+    """One token's K [4][256] fp16 and the channel mean [4][256] f32 -> (codes [4][128] u8, scale pairs [4][8][2] u16)."""
+    k_row = np.ascontiguousarray(k_row, np.float16).reshape(KV_HEADS, HEAD_DIM)
+    mean = np.ascontiguousarray(mean, np.float32).reshape(KV_HEADS, HEAD_DIM)
+    codes, scales = np.zeros((KV_HEADS, 128), np.uint8), np.zeros((KV_HEADS, 8, 2), np.uint16)
+    _o.yahkv_oracle_kv4_quant_k(_p(k_row.view(np.uint16)), _p(mean), _p(codes), _p(scales))
+    return codes, scales
+
+
+def kv4_deq_k(codes, scales):
+    """-> the rotated (k - mean) [4][256] f32."""
+    out = np.zeros((KV_HEADS, HEAD_DIM), np.float32)
+    _o.yahkv_oracle_kv4_deq_k(_p(np.ascontiguousarray(codes, np.uint8)), _p(np.ascontiguousarray(scales, np.uint16)), _p(out))
+    return out
+
+
+def kv4_quant_vtile(v_tile):
+    """v [16 keys][4][256] fp16 -> (codes [4][256][8] u8, stat pairs [4][256][2] u16)."""
+    v_tile = np.ascontiguousarray(v_tile, np.float16).reshape(16, KV_HEADS, HEAD_DIM)
+    codes, stats = np.zeros((KV_HEADS, HEAD_DIM, 8), np.uint8), np.zeros((KV_HEADS, HEAD_DIM, 2), np.uint16)
+    _o.yahkv_oracle_kv4_quant_vtile(_p(v_tile.view(np.uint16)), _p(codes), _p(stats))
+    return codes, stats
+
+
+def kv4_deq_vtile(codes, stats):
+    out = np.zeros((16, KV_HEADS, HEAD_DIM), np.float32)
+    _o.yahkv_oracle_kv4_deq_vtile(_p(np.ascontiguousarray(codes, np.uint8)), _p(np.ascontiguousarray(stats, np.uint16)), _p(out))
+    return out
+
+
+class Kv4Pool:
+    """One layer's kv4a16 pools on the host in the library's layout (64-token pages of four 16-key tiles); the
+    counterpart of Kv8Pool."""
+
+    def __init__(self, num_pages):
+        self.num_pages = num_pages
+        self.kcodes = np.zeros((num_pages, KV_HEADS, PAGE_TOKENS, 128), np.uint8)
+        self.kscales = np.zeros((num_pages, KV_HEADS, PAGE_TOKENS, 8, 2), np.uint16)
+        self.vcodes = np.zeros((num_pages, KV_HEADS, PAGE_TOKENS // 16, HEAD_DIM, 8), np.uint8)
+        self.vstats = np.zeros((num_pages, KV_HEADS, PAGE_TOKENS // 16, HEAD_DIM, 2), np.uint16)
+
+    new_sequence = staticmethod(Kv8Pool.new_sequence)
+
+    def append(self, table, pos0, k, v, open_tile, mean):
+        table = np.ascontiguousarray(table, np.int32)
+        k = np.ascontiguousarray(k, np.float16)
+        v = np.ascontiguousarray(v, np.float16)
+        _o.yahkv_oracle_kv4_append_seq(PAGE_TOKENS, self.num_pages, _p(self.kcodes), _p(self.kscales), _p(self.vcodes),
+                                       _p(self.vstats), _p(open_tile), _p(mean), _p(table), len(table),
+                                       ctypes.c_int64(pos0), k.shape[0], _p(k.view(np.uint16)), _p(v.view(np.uint16)))
+
+    def attend_decode_f64(self, table, n_keys, q, open_tile, gate=None, scale=1.0 / 16.0, threads=THREADS):
+        table = np.ascontiguousarray(table, np.int32)
+        q = np.ascontiguousarray(q, np.float16)
+        gate = None if gate is None else np.ascontiguousarray(gate, np.float32)
+        out = np.zeros((Q_HEADS, HEAD_DIM), np.float64)
+        _o.yahkv_oracle_kv4_attend_decode_f64(PAGE_TOKENS, self.num_pages, _p(self.kcodes), _p(self.kscales),
+                                              _p(self.vcodes), _p(self.vstats), _p(open_tile), _p(table), len(table),
+                                              ctypes.c_int64(n_keys), _p(q.view(np.uint16)), _p(gate),
+                                              ctypes.c_double(scale), _p(out), threads)
+        return out
+
+    def dequantized(self, table, n_keys, open_tile, threads=THREADS):
+        """(K rotated by H256 / 16, V) [n_keys][4][256] f32 of one sequence as attention sees them."""
+        table = np.ascontiguousarray(table, np.int32)
+        validate_table(table, self.num_pages)
+        K = np.zeros((n_keys, KV_HEADS, HEAD_DIM), np.float32)
+        V = np.zeros((n_keys, KV_HEADS, HEAD_DIM), np.float32)
+        _o.yahkv_oracle_kv4_dequantize(PAGE_TOKENS, self.num_pages, _p(self.kcodes), _p(self.kscales), _p(self.vcodes),
+                                       _p(self.vstats), _p(open_tile), _p(table), len(table), ctypes.c_int64(n_keys),
+                                       _p(K), _p(V), threads)
+        return K, V
+
+    def attend_prefill_f64(self, table, start, q, open_tile, q_begin=0, q_end=None, gate=None, scale=1.0 / 16.0):
+        """Causal attention of chunk rows [q_begin, q_end) over the cache after the chunk's append, in float64, with q
+        rotated like the cached K (dattn_q_check.py:203): the same numbers as attending over un-rotated rows."""
+        q = np.ascontiguousarray(q, np.float16)
+        q_end = q.shape[0] if q_end is None else q_end
+        K, V = self.dequantized(table, start + q.shape[0], open_tile)
+        K, V = K.astype(np.float64), V.astype(np.float64)
+        out = np.zeros((q_end - q_begin, Q_HEADS, HEAD_DIM), np.float64)
+        group = Q_HEADS // KV_HEADS
+        for i in range(q_begin, q_end):
+            vis = start + i + 1
+            qr = hadamard256_f64(q[i].astype(np.float64))
+            for h in range(Q_HEADS):
+                kvh = h // group
+                s_ = (K[:vis, kvh] @ qr[h]) * scale
                 w = np.exp(s_ - s_.max())
                 o = (w @ V[:vis, kvh]) / w.sum()
                 if gate is not None:
