@@ -46,7 +46,9 @@ N_SPLITS = 0          # split-K units per (sequence, kv head); 0 = the library's
 METRIC, UNIT = "q8_0_paged_decode_attn_kv_gbps", "GB/s"
 # DRAM bytes per algorithmic byte of the split-K attention kernel, from an ncu capture of one full-size launch of this
 # workload (1.238827 GB read + 11.76 MB written for 1.236479 GB of cache): profiles/decode_part_q8_0_batch32.md.
-NCU_DRAM_PER_ALGORITHMIC_BYTE = {"q8_0": 1.0114}
+# q4_0: the long-context launch (1.2094 GB + 22.8 MB for 1.2080 GB), profiles/decode_longctx_q4_0.md; kv8a16: the
+# batch-32 launch (1.3311 GB + 14.8 MB for 1.3271 GB), profiles/decode_part_kv8a16_batch32.md.
+NCU_DRAM_PER_ALGORITHMIC_BYTE = {"q8_0": 1.0114, "q4_0": 1.0200, "kv8a16": 1.0142}
 
 
 def workload(rank, world, layers):
@@ -713,8 +715,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="yahkv", choices=["yahkv", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers per step (16 = the configuration)")
-    ap.add_argument("--fmt", default="q8_0", choices=["q8_0", "q4_0", "kv8a16"],
-                    help="cache format (q8_0 = the configuration; kv8a16 = the reference's own format, eager calls only)")
+    ap.add_argument("--fmt", default="q8_0", choices=["q8_0", "q4_0", "kv8a16", "kv4a16"],
+                    help="cache format (q8_0 = the configuration; kv8a16 / kv4a16 = the reference's own formats, eager calls only)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "longctx", "churn", "headshard"],
                     help="decode = the batch-32 configuration (default, the headline metric); prefill = chunked "
                          "prefill; longctx = batch 8 x 131072 tokens, q4_0, 64 splits, one layer")
@@ -759,11 +761,11 @@ def main():
     rng, lens, layers = w["rng"], w["lens"].copy(), w["layers"]
     total_steps = args.warmup + args.steps
     e2e_steps = 0 if args.no_e2e else args.steps + 1
-    graph_steps = 0 if (args.no_graph or N_SPLITS or args.fmt == "kv8a16") else args.steps + 3
+    graph_steps = 0 if (args.no_graph or N_SPLITS or args.fmt in ("kv8a16", "kv4a16")) else args.steps + 3
     grow = total_steps + graph_steps + e2e_steps + 2
     pages = [(int(n) + grow + 63) // 64 for n in lens]
     num_pages = sum(pages) + 64
-    fmt = {"q8_0": yahkv.FMT_Q8_0, "q4_0": yahkv.FMT_Q4_0, "kv8a16": yahkv.FMT_KV8A16}[args.fmt]
+    fmt = {"q8_0": yahkv.FMT_Q8_0, "q4_0": yahkv.FMT_Q4_0, "kv8a16": yahkv.FMT_KV8A16, "kv4a16": yahkv.FMT_KV4A16}[args.fmt]
     cache = yahkv.KvCache(device=local_rank, n_layers=layers, num_pages=num_pages, fmt=fmt,
                           max_seqs=BATCH, max_pages_per_seq=max(pages) + 1, max_batch_tokens=8192)
     perm = rng.permutation(num_pages).astype(np.int32)
@@ -983,7 +985,7 @@ def main():
             line["roofline"]["traffic_note"] = ("(dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of "
                                                 "one ncu-captured launch of this workload, times this run's bytes "
                                                 "per launch")
-        if world == 1 and not args.no_cpu and args.fmt != "kv8a16":
+        if world == 1 and not args.no_cpu and args.fmt not in ("kv8a16", "kv4a16"):
             res = cpu_arm(args.fmt, lens=None if args.workload == "decode" else lens[:1])
             line["cpu_baseline"] = {"value": res["gbs"], "unit": UNIT, "cores": res["threads"], "kind": "port",
                                     "sample": res["sample"], "append_mtok_s": res["append_mtok_s_port"],

@@ -51,6 +51,18 @@ extern "C" {
  * supported (refused with YAHKV_ERR_INVALID): the fused RoPE append, decode batches, snapshots, yahkv_export_token,
  * head-sharded contexts, and yahkv_seq_set_len to anything but 0. */
 #define YAHKV_FMT_KV8A16 2
+/* Its 4-bit sibling kv4a16 (engine/gpu/loom/tools/gen_kvq.py:288-463, :474-660 with 4-bit V), same pages, tiles, open
+ * tile, mean and supported calls as YAHKV_FMT_KV8A16:
+ *   K  (k - mean) per head through the orthonormal Walsh-Hadamard transform H256 / 16 (in f32: butterflies 1, 2, 4 dims
+ *      apart, then 8 .. 128), per 32-dim group of the rotated row lo = min, s = (max - lo) / 15,
+ *      u = clamp(roundeven((r - lo) / s), 0, 15); a dword holds 8 dims, dim 2j at bits 4j, dim 2j + 1 at bits 16 + 4j;
+ *      fp16 pair (16 s, lo - 16 s);  pools: codes [page][4][64][128 B], pairs [page][4][64][8][2] fp16. Attention rotates
+ *      the query the same way (prefill attention rotates the cached rows back instead), so q.k is unchanged.
+ *   V  per (16-key tile, channel) 15 levels: u = clamp(roundeven((v - cf) / sf) + 7, 0, 14), two dwords per channel
+ *      (nibble p of dword w = key 8w + 2p for p < 4, 8w + 2(p - 4) + 1 otherwise), fp16 pair (16 sf, cf - 23 sf);
+ *      pools: codes [page][4][4 tiles][256][8 B], pairs [page][4][4][256][2] fp16.
+ * 1408 B per token per layer. */
+#define YAHKV_FMT_KV4A16 3
 
 #define YAHKV_SIDE_K 0
 #define YAHKV_SIDE_V 1

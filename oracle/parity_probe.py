@@ -21,8 +21,8 @@ def compact_pool(cache, layer, seq, n_tokens=None):
     table = cache.seq_table(seq)
     if n_tokens is not None:
         table = table[: (int(n_tokens) + O.PAGE_TOKENS - 1) // O.PAGE_TOKENS]
-    if cache.fmt == O.FMT_KV8A16:
-        pool = O.Kv8Pool(max(len(table), 1))
+    if cache.fmt in (O.FMT_KV8A16, O.FMT_KV4A16):
+        pool = (O.Kv8Pool if cache.fmt == O.FMT_KV8A16 else O.Kv4Pool)(max(len(table), 1))
         for i, p in enumerate(table):
             pool.kcodes[i], pool.kscales[i] = cache.read_page(layer, 0, int(p))
             pool.vcodes[i], pool.vstats[i] = cache.read_page(layer, 1, int(p))
@@ -43,7 +43,7 @@ def check_decode_row(cache, layer, seq, n_keys, q_row, out_row, gate_row=None, o
     """Max-abs and relative error of one decode output row [24][256] against float64 attention over the cache's own
     bytes. fp16 outputs carry their rounding (2^-11 relative) on top."""
     pool, table = compact_pool(cache, layer, seq, n_keys)
-    if cache.fmt == O.FMT_KV8A16:     # the newest tile is read from the sequence's open fp16 tile
+    if cache.fmt in (O.FMT_KV8A16, O.FMT_KV4A16):     # the newest tile is read from the sequence's open fp16 tile
         open_tile = cache.read_open_tile(seq, layer).view(np.uint16)
         want = pool.attend_decode_f64(table, int(n_keys), np.asarray(q_row, np.float16), open_tile, gate_row)
     else:
@@ -70,10 +70,11 @@ def check_prefill_rows(cache, layer, seq, start, q_chunk, out_chunk, rows, gate_
 
 def check_appended_token(cache, layer, seq, pos, k_row, v_row):
     """True when the blocks the cache holds for one position are the oracle's quantization of the fp16 rows."""
-    if cache.fmt == O.FMT_KV8A16:     # K row against the oracle's quantizer (zero mean); V tiles are covered by the tests
+    if cache.fmt in (O.FMT_KV8A16, O.FMT_KV4A16):   # K row against the oracle's quantizer (zero mean); V tiles are covered by the tests
         page = int(cache.seq_table(seq)[int(pos) // O.PAGE_TOKENS])
         codes, scales = cache.read_page(layer, 0, page)
-        want_c, want_s = O.kv8_quant_k(np.asarray(k_row, np.float16), np.zeros((4, 256), np.float32))
+        quant = O.kv8_quant_k if cache.fmt == O.FMT_KV8A16 else O.kv4_quant_k
+        want_c, want_s = quant(np.asarray(k_row, np.float16), np.zeros((4, 256), np.float32))
         tok = int(pos) % O.PAGE_TOKENS
         return bool(np.array_equal(codes[:, tok], want_c) and np.array_equal(scales[:, tok], want_s))
     kb, vb = cache.export_token(layer, seq, int(pos))

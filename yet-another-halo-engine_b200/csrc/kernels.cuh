@@ -22,17 +22,28 @@ constexpr int kFmtQ4 = 1;
 // scale pair per 128-dim half; V codes per (16-key tile, channel) with a statistic pair per channel, four tiles to a
 // page; the tile of the newest key stays open in fp16 (kv8a16.cu).
 constexpr int kFmtKv8 = 2;
+// Its 4-bit sibling kv4a16 (gen_kvq.py:288-463): K rotated by the Walsh-Hadamard transform H256 / 16, 16 levels per
+// 32-dim group with an (16 s, lo - 16 s) pair; V 15 levels per (tile, channel) with a (16 sf, cf - 23 sf) pair
+// (kv4a16.cu).
+constexpr int kFmtKv4 = 3;
 constexpr int kTileKeys = 16;
 constexpr int kTilesPerPage = kPageTokens / kTileKeys;
+// The reference's own formats: V in 16-key tiles, an open fp16 tile and a K mean per (sequence, layer).
+__host__ __device__ constexpr bool IsTileFmt(int fmt) { return fmt == kFmtKv8 || fmt == kFmtKv4; }
 
-__host__ __device__ constexpr int CodeBytes(int fmt) { return fmt == kFmtQ4 ? 128 : 256; }
+// Bytes of one token row of one kv head on the K side (the rows of the K tensor map). The V side of a page record has
+// the same total size in every format (a tile format stores it as [tile][channel][16 or 8 bytes]).
+__host__ __device__ constexpr int CodeBytes(int fmt) { return fmt == kFmtQ4 || fmt == kFmtKv4 ? 128 : 256; }
 // One page record of one kv head: codes then (in a separate pool) scales.
 __host__ __device__ constexpr int RecordCodeBytes(int fmt) { return kPageTokens * CodeBytes(fmt); }
 constexpr int kRecordScaleBytes = kPageTokens * kBlocksPerRow * 2;   // q8_0 / q4_0: 8 fp16 block scales per token
-// Scale (q8_0, q4_0) or statistic (kv8a16) bytes of one page record of one kv head, by side (0 = K, 1 = V):
-// kv8a16 K holds 2 halves x an fp16 pair per token, kv8a16 V holds an fp16 pair per (tile, channel).
+// Scale (q8_0, q4_0) or statistic (tile formats) bytes of one page record of one kv head, by side (0 = K, 1 = V):
+// kv8a16 K holds 2 halves x an fp16 pair per token, kv4a16 K 8 groups x a pair; the V side of both holds an fp16 pair
+// per (tile, channel).
 __host__ __device__ constexpr int RecordScaleBytes(int fmt, int side) {
-  return fmt != kFmtKv8 ? kRecordScaleBytes : (side == 0 ? kPageTokens * 2 * 2 * 2 : kTilesPerPage * kHeadDim * 2 * 2);
+  return !IsTileFmt(fmt) ? kRecordScaleBytes
+         : side == 1     ? kTilesPerPage * kHeadDim * 2 * 2
+                         : kPageTokens * (fmt == kFmtKv8 ? 2 : 8) * 2 * 2;
 }
 
 // The pools of one context. Codes are addressed both by pointer (append, inspection) and through 2-D tensor maps
@@ -204,6 +215,13 @@ cudaError_t LaunchKv8AppendV(const PoolView& pool, int layer, int n_work, const 
 // state_stride = n_layers (the open-tile pair of (sequence, layer) is row seq * n_layers + layer).
 cudaError_t LaunchKv8DecodePart(const DecodeLaunch& a, const void* open_tiles_dev, int n_layers, cudaStream_t stream);
 cudaError_t ConfigureKv8Kernels();
+// kv4a16 (kv4a16.cu): the K append (rotation + 4-bit groups) and decode attention; the V append and the prefill
+// dequantize pass are the kv8a16 launchers above and below, which switch on pool.fmt.
+cudaError_t LaunchKv4AppendK(const PoolView& pool, int layer, int n_tokens, const std::int64_t* slots_dev,
+                             const std::int32_t* state_rows_dev, const float* kmean_dev, const void* k_dev,
+                             cudaStream_t stream);
+cudaError_t LaunchKv4DecodePart(const DecodeLaunch& a, const void* open_tiles_dev, int n_layers, cudaStream_t stream);
+cudaError_t ConfigureKv4Kernels();
 cudaError_t LaunchDecodeCombine(const DecodeLaunch& a, cudaStream_t stream);
 // Shared-memory bytes the decode kernel asks for (for the one-time attribute set-up).
 cudaError_t ConfigureDecodeKernels();
@@ -236,6 +254,8 @@ struct PrefillLaunch {
 cudaError_t LaunchPrefillDequant(const PrefillLaunch& a, cudaStream_t stream);
 // kv8a16: the same pass for that format (kv8a16.cu); PrefillSeq::pad[0] names each sequence's current open buffer.
 cudaError_t LaunchKv8PrefillDequant(const PrefillLaunch& a, const void* open_tiles_dev, int n_layers, cudaStream_t stream);
+// kv4a16 (kv4a16.cu): K rows are rotated back (the transform is its own inverse) so the chunk's q needs no rotation.
+cudaError_t LaunchKv4PrefillDequant(const PrefillLaunch& a, const void* open_tiles_dev, int n_layers, cudaStream_t stream);
 cudaError_t LaunchPrefill(const PrefillLaunch& a, cudaStream_t stream);
 cudaError_t ConfigurePrefillKernels();
 // Encodes a 2-D tiled tensor map (row-major, `inner` elements of `elem_bytes` per row, 128-byte swizzle). Host only.

@@ -90,6 +90,10 @@ __global__ void __launch_bounds__(128) Kv8AppendKKernel(PoolView pool, int layer
 // ---------------------------------------------------------------------------------------------------------------
 // Append, V side: one CTA per (tile touched by the call, kv head), thread = channel.
 // ---------------------------------------------------------------------------------------------------------------
+// kBits = 8: 255 levels around the centre, four dwords per channel. kBits = 4 (kv4a16, dattn_q_check.py:101-122 with
+// bits = 4): 15 levels, u = clamp(roundeven((v - cf) / sf) + 7, 0, 14), two dwords per channel with nibble p of dword w =
+// key 8w + 2p (p < 4) or 8w + 2(p - 4) + 1, pair (16 sf, cf - 23 sf).
+template <int kBits>
 __global__ void __launch_bounds__(kHeadDim) Kv8AppendVKernel(PoolView pool, int layer, const VTileWork* __restrict__ work,
                                                              __half* __restrict__ open_tiles,
                                                              const __half* __restrict__ v_in) {
@@ -122,32 +126,44 @@ __global__ void __launch_bounds__(kHeadDim) Kv8AppendVKernel(PoolView pool, int 
     x[j] = __half2float(v[j]);
     mx = fmaxf(mx, x[j]), mn = fminf(mn, x[j]);
   }
+  constexpr float kLevels = kBits == 8 ? 254.0F : 14.0F, kOff = kBits == 8 ? 128.0F : 7.0F, kMax = kBits == 8 ? 255.0F : 14.0F;
+  constexpr float kSMul = kBits == 8 ? 256.0F : 16.0F, kCMul = kBits == 8 ? -384.0F : -23.0F;
   const float cen = __fmul_rn(__fadd_rn(mx, mn), 0.5F);
-  const float s0 = __fdiv_rn(__fsub_rn(mx, mn), 254.0F);
+  const float s0 = __fdiv_rn(__fsub_rn(mx, mn), kLevels);
   const float s = s0 > 0.0F ? s0 : 1.0F;
   const float sf = __half2float(__float2half_rn(s)), cf = __half2float(__float2half_rn(cen));
   const float inv = __fdiv_rn(1.0F, sf);
-  std::uint32_t w[4];
+  std::uint32_t u[kTileKeys];
 #pragma unroll
-  for (int d = 0; d < 4; ++d) {   // dword d byte p = key 4d + (0, 2, 1, 3)[p]
-    std::uint32_t u[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      float q = __fadd_rn(rintf(__fmul_rn(__fsub_rn(x[4 * d + k], cf), inv)), 128.0F);
-      q = fminf(fmaxf(q, 0.0F), 255.0F);
-      u[k] = static_cast<std::uint32_t>(q);
-    }
-    w[d] = u[0] | (u[2] << 8) | (u[1] << 16) | (u[3] << 24);
+  for (int k = 0; k < kTileKeys; ++k) {
+    float q = __fadd_rn(rintf(__fmul_rn(__fsub_rn(x[k], cf), inv)), kOff);
+    q = fminf(fmaxf(q, 0.0F), kMax);
+    u[k] = static_cast<std::uint32_t>(q);
   }
   std::int64_t page = wk.phys_tile / kTilesPerPage;
   page = min(max(page, static_cast<std::int64_t>(0)), static_cast<std::int64_t>(pool.num_pages - 1));
   const int t_in_page = wk.phys_tile % kTilesPerPage;
   const std::size_t rec = (static_cast<std::size_t>(layer) * pool.num_pages + static_cast<std::size_t>(page)) * kKvHeads + h;
-  std::uint8_t* codes = pool.vcodes + rec * RecordCodeBytes(kFmtKv8) + (static_cast<std::size_t>(t_in_page) * kHeadDim + ch) * 16;
-  *reinterpret_cast<uint4*>(codes) = make_uint4(w[0], w[1], w[2], w[3]);
+  constexpr int kChBytes = kBits * 2;   // 16 codes of a channel
+  std::uint8_t* codes = pool.vcodes + rec * RecordCodeBytes(kBits == 8 ? kFmtKv8 : kFmtKv4) + (static_cast<std::size_t>(t_in_page) * kHeadDim + ch) * kChBytes;
+  if constexpr (kBits == 8) {   // dword d byte p = key 4d + (0, 2, 1, 3)[p]
+    std::uint32_t w[4];
+#pragma unroll
+    for (int d = 0; d < 4; ++d) w[d] = u[4 * d] | (u[4 * d + 2] << 8) | (u[4 * d + 1] << 16) | (u[4 * d + 3] << 24);
+    *reinterpret_cast<uint4*>(codes) = make_uint4(w[0], w[1], w[2], w[3]);
+  } else {                      // dword d: keys 8d + (0, 2, 4, 6) in the low 16 bits, 8d + (1, 3, 5, 7) in the high ones
+    std::uint32_t w[2];
+#pragma unroll
+    for (int d = 0; d < 2; ++d) {
+      w[d] = 0;
+#pragma unroll
+      for (int p = 0; p < 8; ++p) w[d] |= u[8 * d + (p < 4 ? 2 * p : 2 * (p - 4) + 1)] << (4 * p);
+    }
+    *reinterpret_cast<uint2*>(codes) = make_uint2(w[0], w[1]);
+  }
   std::uint16_t* st = pool.vscales + rec * (RecordScaleBytes(kFmtKv8, 1) / 2) + (static_cast<std::size_t>(t_in_page) * kHeadDim + ch) * 2;
   *reinterpret_cast<__half2*>(st) =
-      __halves2half2(__float2half_rn(__fmul_rn(sf, 256.0F)), __float2half_rn(__fadd_rn(cf, __fmul_rn(sf, -384.0F))));
+      __halves2half2(__float2half_rn(__fmul_rn(sf, kSMul)), __float2half_rn(__fadd_rn(cf, __fmul_rn(sf, kCMul))));
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -692,7 +708,10 @@ cudaError_t LaunchKv8AppendK(const PoolView& pool, int layer, int n_tokens, cons
 cudaError_t LaunchKv8AppendV(const PoolView& pool, int layer, int n_work, const VTileWork* work_dev, void* open_tiles_dev,
                              const void* v_dev, cudaStream_t stream) {
   if (n_work <= 0) return cudaSuccess;
-  return LaunchChained(Kv8AppendVKernel, dim3(n_work, kKvHeads), kHeadDim, 0, stream, pool, layer, work_dev,
+  if (pool.fmt == kFmtKv4)
+    return LaunchChained(Kv8AppendVKernel<4>, dim3(n_work, kKvHeads), kHeadDim, 0, stream, pool, layer, work_dev,
+                         static_cast<__half*>(open_tiles_dev), static_cast<const __half*>(v_dev));
+  return LaunchChained(Kv8AppendVKernel<8>, dim3(n_work, kKvHeads), kHeadDim, 0, stream, pool, layer, work_dev,
                        static_cast<__half*>(open_tiles_dev), static_cast<const __half*>(v_dev));
 }
 

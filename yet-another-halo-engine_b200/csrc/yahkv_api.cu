@@ -219,13 +219,14 @@ int InitDevice(yahkv_ctx* ctx) {
     YAHKV_CUDA(ctx, cudaMemset(ctx->pool.vcodes, kQ8FlipByte, recs * RecordCodeBytes(c.fmt)));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.kscales, recs * (RecordScaleBytes(c.fmt, 0) / 2), true));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->pool.vscales, recs * (RecordScaleBytes(c.fmt, 1) / 2), true));
-  if (c.fmt == YAHKV_FMT_KV8A16) {
+  if (IsTileFmt(c.fmt)) {
     const std::size_t states = static_cast<std::size_t>(c.max_seqs) * c.n_layers;
     YAHKV_CUDA(ctx, DevAlloc(ctx, reinterpret_cast<std::uint16_t**>(&ctx->open_tiles_dev), states * 2 * kOpenTileHalfs, true));
     YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->kmean_dev, states * kKvHeads * kHeadDim, true));
     YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->state_rows_dev, static_cast<std::size_t>(c.max_batch_tokens), false));
     YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->vwork_dev, static_cast<std::size_t>(c.max_batch_tokens) + 2 * c.max_seqs, false));
     YAHKV_CUDA(ctx, ConfigureKv8Kernels());
+    YAHKV_CUDA(ctx, ConfigureKv4Kernels());
   }
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->tables_dev, static_cast<std::size_t>(c.max_seqs) * c.max_pages_per_seq, true));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->slots_dev, static_cast<std::size_t>(c.max_batch_tokens), false));
@@ -498,7 +499,7 @@ int yahkv_seq_create(yahkv_ctx* ctx, int32_t* seq) {
   if (seq == nullptr) return Fail(ctx, YAHKV_ERR_INVALID, "seq_create: null out pointer");
   HostError e = ctx->host.SeqCreate(seq);
   if (e.code != YAHKV_OK) return FailHost(ctx, std::move(e));
-  if (ctx->has_device && ctx->cfg.fmt == YAHKV_FMT_KV8A16) {   // a fresh sequence: mean 0, first open buffer
+  if (ctx->has_device && IsTileFmt(ctx->cfg.fmt)) {   // a fresh sequence: mean 0, first open buffer
     ctx->host.ResetOpenState(*seq);
     if (cudaSetDevice(ctx->cfg.device) != cudaSuccess) return Fail(ctx, YAHKV_ERR_CUDA, "cudaSetDevice failed");
     YAHKV_CUDA(ctx, cudaDeviceSynchronize());
@@ -544,17 +545,17 @@ int yahkv_seq_len(const yahkv_ctx* ctx, int32_t seq, int32_t layer, int64_t* len
 
 int yahkv_seq_set_len(yahkv_ctx* ctx, int32_t seq, int32_t layer, int64_t len) {
   if (ctx == nullptr) return YAHKV_ERR_INVALID;
-  if (ctx->cfg.fmt == YAHKV_FMT_KV8A16 && len != 0)
-    return Fail(ctx, YAHKV_ERR_INVALID, "seq_set_len: a YAHKV_FMT_KV8A16 sequence can only be reset to length 0 (its open tile holds the newest keys)");
+  if (IsTileFmt(ctx->cfg.fmt) && len != 0)
+    return Fail(ctx, YAHKV_ERR_INVALID, "seq_set_len: a YAHKV_FMT_KV8A16 / YAHKV_FMT_KV4A16 sequence can only be reset to length 0 (its open tile holds the newest keys)");
   HostError e = ctx->host.SeqSetLen(seq, layer, len);
   if (e.code != YAHKV_OK) return FailHost(ctx, std::move(e));
-  if (ctx->cfg.fmt == YAHKV_FMT_KV8A16 && layer == -1) ctx->host.ResetOpenState(seq);
+  if (IsTileFmt(ctx->cfg.fmt) && layer == -1) ctx->host.ResetOpenState(seq);
   return YAHKV_OK;
 }
 
 int yahkv_seq_set_kmean(yahkv_ctx* ctx, int32_t seq, int32_t layer, const float* mean_host) {
   if (int r = RequireDevice(ctx, "seq_set_kmean"); r != YAHKV_OK) return r;
-  if (ctx->cfg.fmt != YAHKV_FMT_KV8A16) return Fail(ctx, YAHKV_ERR_INVALID, "seq_set_kmean: only for YAHKV_FMT_KV8A16");
+  if (!IsTileFmt(ctx->cfg.fmt)) return Fail(ctx, YAHKV_ERR_INVALID, "seq_set_kmean: only for YAHKV_FMT_KV8A16 / YAHKV_FMT_KV4A16");
   if (!ctx->host.live(seq) || mean_host == nullptr || layer < -1 || layer >= ctx->cfg.n_layers)
     return Fail(ctx, YAHKV_ERR_INVALID, "seq_set_kmean: bad sequence, layer or null pointer");
   for (int l = 0; l < ctx->cfg.n_layers; ++l)
@@ -570,7 +571,7 @@ int yahkv_seq_set_kmean(yahkv_ctx* ctx, int32_t seq, int32_t layer, const float*
 
 int yahkv_read_open_tile(yahkv_ctx* ctx, int32_t seq, int32_t layer, void* tile_host) {
   if (int r = RequireDevice(ctx, "read_open_tile"); r != YAHKV_OK) return r;
-  if (ctx->cfg.fmt != YAHKV_FMT_KV8A16) return Fail(ctx, YAHKV_ERR_INVALID, "read_open_tile: only for YAHKV_FMT_KV8A16");
+  if (!IsTileFmt(ctx->cfg.fmt)) return Fail(ctx, YAHKV_ERR_INVALID, "read_open_tile: only for YAHKV_FMT_KV8A16 / YAHKV_FMT_KV4A16");
   if (!ctx->host.live(seq) || tile_host == nullptr || layer < 0 || layer >= ctx->cfg.n_layers)
     return Fail(ctx, YAHKV_ERR_INVALID, "read_open_tile: bad sequence, layer or null pointer");
   YAHKV_CUDA(ctx, cudaDeviceSynchronize());
@@ -598,7 +599,7 @@ int yahkv_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int32_t*
   if (int r = FlushTables(ctx, st); r != YAHKV_OK) return r;
   if (int r = StagedUpload(ctx, ctx->slots_dev, ctx->slot_scratch.data(), static_cast<std::size_t>(n_tokens) * 8, st); r != YAHKV_OK)
     return r;
-  if (ctx->cfg.fmt == YAHKV_FMT_KV8A16) {
+  if (IsTileFmt(ctx->cfg.fmt)) {
     // K: one row per token against its sequence's mean. V: one work item per 16-key tile the call touches; the tile
     // of each sequence's newest key also stays in fp16 (engine/gpu/loom/tools/gen_decode_attn.py:436-573).
     ctx->host.PlanKv8Tiles(layer, n_tokens, seq_ids, positions, &ctx->vwork_scratch);
@@ -611,7 +612,8 @@ int yahkv_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int32_t*
         r != YAHKV_OK)
       return r;
     TimedLaunch tl(ctx, YAHKV_KERNEL_APPEND, st);
-    YAHKV_CUDA(ctx, LaunchKv8AppendK(ctx->pool, layer, n_tokens, ctx->slots_dev, ctx->state_rows_dev, ctx->kmean_dev, k_dev, st));
+    YAHKV_CUDA(ctx, (ctx->cfg.fmt == YAHKV_FMT_KV4A16 ? LaunchKv4AppendK : LaunchKv8AppendK)(
+                        ctx->pool, layer, n_tokens, ctx->slots_dev, ctx->state_rows_dev, ctx->kmean_dev, k_dev, st));
     YAHKV_CUDA(ctx, LaunchKv8AppendV(ctx->pool, layer, static_cast<int>(ctx->vwork_scratch.size()), ctx->vwork_dev,
                                      ctx->open_tiles_dev, v_dev, st));
     tl.End();
@@ -649,7 +651,7 @@ int yahkv_rope_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int
                       const float* q_dev, const float* k_dev, const float* v_dev, const float* q_weight_dev,
                       const float* k_weight_dev, float eps, void* q_out_dev, void* stream) {
   if (int r = RequireDevice(ctx, "rope_append"); r != YAHKV_OK) return r;
-  if (ctx->cfg.fmt == YAHKV_FMT_KV8A16) return Fail(ctx, YAHKV_ERR_INVALID, "rope_append: not available for YAHKV_FMT_KV8A16");
+  if (IsTileFmt(ctx->cfg.fmt)) return Fail(ctx, YAHKV_ERR_INVALID, "rope_append: not available for YAHKV_FMT_KV8A16 / YAHKV_FMT_KV4A16");
   if (n_tokens > ctx->cfg.max_batch_tokens) return Fail(ctx, YAHKV_ERR_CAPACITY, "rope_append: more tokens than max_batch_tokens");
   if (n_tokens > 0 && (q_dev == nullptr || k_dev == nullptr || v_dev == nullptr || q_weight_dev == nullptr ||
                        k_weight_dev == nullptr || q_out_dev == nullptr))
@@ -679,8 +681,8 @@ int yahkv_rope_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int
 int yahkv_append_slots(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int64_t* slot_mapping_dev,
                        const void* k_dev, const void* v_dev, void* stream) {
   if (int r = RequireDevice(ctx, "append_slots"); r != YAHKV_OK) return r;
-  if (ctx->cfg.fmt == YAHKV_FMT_KV8A16)
-    return Fail(ctx, YAHKV_ERR_INVALID, "append_slots: YAHKV_FMT_KV8A16 needs the sequence of every token (use yahkv_append)");
+  if (IsTileFmt(ctx->cfg.fmt))
+    return Fail(ctx, YAHKV_ERR_INVALID, "append_slots: YAHKV_FMT_KV8A16 / YAHKV_FMT_KV4A16 need the sequence of every token (use yahkv_append)");
   if (layer < 0 || layer >= ctx->cfg.n_layers) return Fail(ctx, YAHKV_ERR_INVALID, "append_slots: layer out of range");
   if (n_tokens < 0) return Fail(ctx, YAHKV_ERR_INVALID, "append_slots: negative token count");
   if (n_tokens == 0) return YAHKV_OK;
@@ -715,7 +717,7 @@ int yahkv_attend_decode(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int
   } guard{&ctx->host};
   cudaStream_t st = StreamOf(ctx, stream);
   if (int r = FlushTables(ctx, st); r != YAHKV_OK) return r;
-  const bool kv8 = ctx->cfg.fmt == YAHKV_FMT_KV8A16;
+  const bool kv8 = IsTileFmt(ctx->cfg.fmt);
   if (kv8) {   // every unit carries its sequence's current open-tile buffer of THIS layer: uploaded on every call
     ctx->unit_scratch = ctx->host.units();
     for (DecodeUnit& u : ctx->unit_scratch) u.pad = ctx->host.open_cur(u.seq, layer);
@@ -745,7 +747,9 @@ int yahkv_attend_decode(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int
   // The merge runs as its own small launch: letting the last-arriving unit merge inside the part kernel was measured
   // 1% slower end to end (every CTA then pays a fence and an atomic on exit).
   TimedLaunch tp(ctx, YAHKV_KERNEL_DECODE_PART, st);
-  cudaError_t le = kv8 ? LaunchKv8DecodePart(a, ctx->open_tiles_dev, ctx->cfg.n_layers, st) : LaunchDecodePart(a, st);
+  cudaError_t le = ctx->cfg.fmt == YAHKV_FMT_KV4A16 ? LaunchKv4DecodePart(a, ctx->open_tiles_dev, ctx->cfg.n_layers, st)
+                   : kv8                            ? LaunchKv8DecodePart(a, ctx->open_tiles_dev, ctx->cfg.n_layers, st)
+                                                    : LaunchDecodePart(a, st);
   tp.End();
   if (le == cudaSuccess) {
     TimedLaunch tc(ctx, YAHKV_KERNEL_DECODE_COMBINE, st);
@@ -775,7 +779,7 @@ int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const in
   if (e.code != YAHKV_OK) return FailHost(ctx, std::move(e));
   if (ctx->tile_scratch.empty()) return YAHKV_OK;
   if (static_cast<int>(ctx->tile_scratch.size()) > ctx->max_tiles) return Fail(ctx, YAHKV_ERR_CAPACITY, "attend_prefill: too many tiles");
-  const bool kv8 = ctx->cfg.fmt == YAHKV_FMT_KV8A16;
+  const bool kv8 = IsTileFmt(ctx->cfg.fmt);
   if (kv8)   // the tile of each sequence's newest key is read from its current open buffer
     for (PrefillSeq& ps : ctx->pseq_scratch) ps.pad[0] = ctx->host.open_cur(ps.seq, layer);
   cudaStream_t st = StreamOf(ctx, stream);
@@ -815,7 +819,9 @@ int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const in
   a.scale_log2 = ctx->scale_log2, a.status_dev = ctx->status_dev;
   {
     TimedLaunch tl(ctx, YAHKV_KERNEL_PREFILL_DEQUANT, st);
-    YAHKV_CUDA(ctx, kv8 ? LaunchKv8PrefillDequant(a, ctx->open_tiles_dev, ctx->cfg.n_layers, st) : LaunchPrefillDequant(a, st));
+    YAHKV_CUDA(ctx, ctx->cfg.fmt == YAHKV_FMT_KV4A16 ? LaunchKv4PrefillDequant(a, ctx->open_tiles_dev, ctx->cfg.n_layers, st)
+                    : kv8                            ? LaunchKv8PrefillDequant(a, ctx->open_tiles_dev, ctx->cfg.n_layers, st)
+                                                     : LaunchPrefillDequant(a, st));
     tl.End();
   }
   TimedLaunch tl(ctx, YAHKV_KERNEL_PREFILL, st);
@@ -944,7 +950,7 @@ int yahkv_write_page(yahkv_ctx* ctx, int32_t layer, int32_t side, int32_t page, 
 
 int yahkv_export_token(yahkv_ctx* ctx, int32_t layer, int32_t seq, int64_t pos, void* k_blocks, void* v_blocks) {
   if (int r = RequireDevice(ctx, "export_token"); r != YAHKV_OK) return r;
-  if (ctx->cfg.fmt == YAHKV_FMT_KV8A16) return Fail(ctx, YAHKV_ERR_INVALID, "export_token: YAHKV_FMT_KV8A16 has no GGUF block form (use yahkv_read_page)");
+  if (IsTileFmt(ctx->cfg.fmt)) return Fail(ctx, YAHKV_ERR_INVALID, "export_token: YAHKV_FMT_KV8A16 / YAHKV_FMT_KV4A16 have no GGUF block form (use yahkv_read_page)");
   if (layer < 0 || layer >= ctx->cfg.n_layers) return Fail(ctx, YAHKV_ERR_INVALID, "export_token: layer out of range");
   if (!ctx->host.live(seq)) return Fail(ctx, YAHKV_ERR_INVALID, "export_token: not a live sequence");
   if (pos < 0 || pos >= static_cast<std::int64_t>(ctx->host.n_pages(seq)) * kPageTokens)
@@ -1031,7 +1037,7 @@ void BatchFree(yahkv_batch* b) {
 
 int yahkv_batch_create(yahkv_ctx* ctx, int32_t n_seqs, const int32_t* seq_ids, yahkv_batch** out) {
   if (int r = RequireDevice(ctx, "batch_create"); r != YAHKV_OK) return r;
-  if (ctx->cfg.fmt == YAHKV_FMT_KV8A16) return Fail(ctx, YAHKV_ERR_INVALID, "batch_create: not available for YAHKV_FMT_KV8A16");
+  if (IsTileFmt(ctx->cfg.fmt)) return Fail(ctx, YAHKV_ERR_INVALID, "batch_create: not available for YAHKV_FMT_KV8A16 / YAHKV_FMT_KV4A16");
   if (out == nullptr) return Fail(ctx, YAHKV_ERR_INVALID, "batch_create: null out pointer");
   *out = nullptr;
   if (n_seqs <= 0 || n_seqs > ctx->cfg.max_seqs || seq_ids == nullptr) return Fail(ctx, YAHKV_ERR_INVALID, "batch_create: bad sequence list");
@@ -1213,7 +1219,7 @@ struct FileCloser {
 
 int yahkv_snapshot_save(yahkv_ctx* ctx, int32_t n_seqs, const int32_t* seq_ids, const char* path) {
   if (int r = RequireDevice(ctx, "snapshot_save"); r != YAHKV_OK) return r;
-  if (ctx->cfg.fmt == YAHKV_FMT_KV8A16) return Fail(ctx, YAHKV_ERR_INVALID, "snapshot_save: not available for YAHKV_FMT_KV8A16");
+  if (IsTileFmt(ctx->cfg.fmt)) return Fail(ctx, YAHKV_ERR_INVALID, "snapshot_save: not available for YAHKV_FMT_KV8A16 / YAHKV_FMT_KV4A16");
   if (n_seqs < 0 || (n_seqs > 0 && seq_ids == nullptr) || path == nullptr)
     return Fail(ctx, YAHKV_ERR_INVALID, "snapshot_save: bad sequence list or path");
   for (int i = 0; i < n_seqs; ++i)
@@ -1256,7 +1262,7 @@ int yahkv_snapshot_save(yahkv_ctx* ctx, int32_t n_seqs, const int32_t* seq_ids, 
 
 int yahkv_snapshot_load(yahkv_ctx* ctx, const char* path, int32_t* seq_ids_out, int32_t* n_inout) {
   if (int r = RequireDevice(ctx, "snapshot_load"); r != YAHKV_OK) return r;
-  if (ctx->cfg.fmt == YAHKV_FMT_KV8A16) return Fail(ctx, YAHKV_ERR_INVALID, "snapshot_load: not available for YAHKV_FMT_KV8A16");
+  if (IsTileFmt(ctx->cfg.fmt)) return Fail(ctx, YAHKV_ERR_INVALID, "snapshot_load: not available for YAHKV_FMT_KV8A16 / YAHKV_FMT_KV4A16");
   if (path == nullptr || seq_ids_out == nullptr || n_inout == nullptr)
     return Fail(ctx, YAHKV_ERR_INVALID, "snapshot_load: null argument");
   std::unique_ptr<std::FILE, FileCloser> f(std::fopen(path, "rb"));

@@ -17,7 +17,7 @@ _PKG_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB_PATH = os.path.join(_PKG_DIR, "libyahkv.so")
 INCLUDE_DIR = os.path.join(os.path.dirname(_PKG_DIR), "include")
 
-FMT_Q8_0, FMT_Q4_0, FMT_KV8A16 = 0, 1, 2
+FMT_Q8_0, FMT_Q4_0, FMT_KV8A16, FMT_KV4A16 = 0, 1, 2, 3
 SIDE_K, SIDE_V = 0, 1
 OUT_F16, OUT_F32 = 0, 1
 KERNEL_APPEND, KERNEL_DECODE_PART, KERNEL_DECODE_COMBINE, KERNEL_PREFILL, KERNEL_PREFILL_DEQUANT = 0, 1, 2, 3, 4
@@ -28,23 +28,26 @@ Q_HEADS, KV_HEADS, HEAD_DIM, PAGE_TOKENS, BLOCKS = 24, 4, 256, 64, 8
 
 
 def code_bytes(fmt):
-    return 128 if fmt == FMT_Q4_0 else 256
+    return 128 if fmt in (FMT_Q4_0, FMT_KV4A16) else 256
 
 
 def bytes_per_token(fmt):
     """K + V bytes one cached token takes in one layer (codes + fp16 scales, all 4 kv heads)."""
     if fmt == FMT_KV8A16:     # K: 256 B + 2 pairs per head; V: 256 B + a sixteenth of 256 pairs per head
         return KV_HEADS * (256 + 8) + KV_HEADS * (256 + 64)
+    if fmt == FMT_KV4A16:     # K: 128 B + 8 pairs per head; V: 128 B + a sixteenth of 256 pairs per head
+        return KV_HEADS * (128 + 32) + KV_HEADS * (128 + 64)
     return 2 * KV_HEADS * (code_bytes(fmt) + BLOCKS * 2)
 
 
 def page_shapes(fmt, side):
     """(codes shape, scales shape) of one page record as yahkv_read_page returns it."""
-    if fmt != FMT_KV8A16:
+    if fmt not in (FMT_KV8A16, FMT_KV4A16):
         return (KV_HEADS, PAGE_TOKENS, code_bytes(fmt)), (KV_HEADS, PAGE_TOKENS, BLOCKS)
+    wide = fmt == FMT_KV8A16
     if side == SIDE_K:
-        return (KV_HEADS, PAGE_TOKENS, 256), (KV_HEADS, PAGE_TOKENS, 2, 2)
-    return (KV_HEADS, PAGE_TOKENS // 16, HEAD_DIM, 16), (KV_HEADS, PAGE_TOKENS // 16, HEAD_DIM, 2)
+        return (KV_HEADS, PAGE_TOKENS, 256 if wide else 128), (KV_HEADS, PAGE_TOKENS, 2 if wide else 8, 2)
+    return (KV_HEADS, PAGE_TOKENS // 16, HEAD_DIM, 16 if wide else 8), (KV_HEADS, PAGE_TOKENS // 16, HEAD_DIM, 2)
 
 
 class Config(ctypes.Structure):
@@ -377,12 +380,12 @@ class KvCache:
 
     # ---- inspection ----
     def seq_set_kmean(self, seq, mean, layer=-1):
-        """kv8a16: the per-channel K mean [4][256] f32 of a sequence (before its first append)."""
+        """kv8a16 / kv4a16: the per-channel K mean [4][256] f32 of a sequence (before its first append)."""
         mean = np.ascontiguousarray(mean, np.float32).reshape(KV_HEADS, HEAD_DIM)
         self._check(lib.yahkv_seq_set_kmean(self._h, seq, layer, _ptr(mean)))
 
     def read_open_tile(self, seq, layer):
-        """kv8a16: the current open V tile [4][256][16] as float16."""
+        """kv8a16 / kv4a16: the current open V tile [4][256][16] as float16."""
         tile = np.zeros((KV_HEADS, HEAD_DIM, 16), np.float16)
         self._check(lib.yahkv_read_open_tile(self._h, seq, layer, _ptr(tile)))
         return tile
