@@ -18,15 +18,18 @@ def attend(cache, layer, seqs, q):
     return out.cpu().numpy()
 
 
-@pytest.mark.parametrize("fmt", [yahkv.FMT_Q8_0, yahkv.FMT_Q4_0])
+@pytest.mark.parametrize("fmt", [yahkv.FMT_Q8_0, yahkv.FMT_Q4_0, yahkv.FMT_KV8A16, yahkv.FMT_KV4A16])
 def test_snapshot_round_trip_onto_other_pages(tmp_path, fmt):
     rng = np.random.default_rng(51)
     a = yahkv.KvCache(n_layers=2, num_pages=12, fmt=fmt, max_seqs=3, max_pages_per_seq=6)
     lens = [130, 64]
     seqs = []
+    tile_fmt = fmt in (yahkv.FMT_KV8A16, yahkv.FMT_KV4A16)
     for n in lens:
         s = a.seq_create()
-        a.seq_reserve(s, n)
+        a.seq_reserve(s, n + 1)
+        if tile_fmt:                    # these formats carry a K mean and an open fp16 tile per (sequence, layer)
+            a.seq_set_kmean(s, (0.5 * rng.standard_normal((4, 256))).astype(np.float32))
         for layer in range(2):
             K = rng.standard_normal((n, 4, 256)).astype(np.float16)
             V = rng.standard_normal((n, 4, 256)).astype(np.float16)
@@ -36,6 +39,11 @@ def test_snapshot_round_trip_onto_other_pages(tmp_path, fmt):
     want = [attend(a, layer, seqs, q) for layer in range(2)]
     path = tmp_path / "kv.snap"
     a.snapshot_save(seqs, path)
+    # one more decode step in the original context: the loaded copy must continue the same way
+    k1 = rng.standard_normal((2, 4, 256)).astype(np.float16)
+    v1 = rng.standard_normal((2, 4, 256)).astype(np.float16)
+    a.append(1, seqs, lens, dev(k1), dev(v1))
+    want_next = attend(a, 1, seqs, q)
     a.close()
 
     b = yahkv.KvCache(n_layers=2, num_pages=20, fmt=fmt, max_seqs=4, max_pages_per_seq=6)
@@ -44,12 +52,14 @@ def test_snapshot_round_trip_onto_other_pages(tmp_path, fmt):
     loaded = b.snapshot_load(path)
     assert len(loaded) == 2 and other not in loaded
     assert [b.seq_len(s, 1) for s in loaded] == lens
-    assert b.seq_table(loaded[0]).tolist() == [3, 4, 5] and b.pages_free() == 20 - 3 - 3 - 1
+    assert b.seq_table(loaded[0]).tolist() == [3, 4, 5] and b.pages_free() == 20 - 3 - 3 - 2
     for layer in range(2):
         assert np.array_equal(attend(b, layer, loaded, q), want[layer])     # same bytes, same kernel: identical
+    b.append(1, loaded, lens, dev(k1), dev(v1))
+    assert np.array_equal(attend(b, 1, loaded, q), want_next)
 
     # a context of another format or layer count refuses the file and stays untouched
-    other_fmt = yahkv.FMT_Q4_0 if fmt == yahkv.FMT_Q8_0 else yahkv.FMT_Q8_0
+    other_fmt = yahkv.FMT_Q4_0 if fmt != yahkv.FMT_Q4_0 else yahkv.FMT_Q8_0
     for kw in (dict(n_layers=2, fmt=other_fmt), dict(n_layers=3, fmt=fmt)):
         c = yahkv.KvCache(num_pages=20, max_seqs=4, max_pages_per_seq=6, **kw)
         with pytest.raises(yahkv.YahkvError) as e:
@@ -66,4 +76,4 @@ def test_snapshot_round_trip_onto_other_pages(tmp_path, fmt):
     (tmp_path / "cut.snap").write_bytes(raw[: len(raw) // 2])
     with pytest.raises(yahkv.YahkvError):
         b.snapshot_load(tmp_path / "cut.snap")
-    assert b.pages_free() == 20 - 3 - 3 - 1
+    assert b.pages_free() == 20 - 3 - 3 - 2

@@ -119,9 +119,9 @@ __global__ void __launch_bounds__(128) Kv4AppendKKernel(PoolView pool, int layer
 // per-group query sums (f16 hi part in rows 0-5, residual in rows 8-13, each value in both the S and the C' slot).
 // The ldmatrix rows follow the key order of the V tile's dwords (as in the kv8a16 kernel), so the weights need no
 // shuffle before the second product.
-// Values. v = u S / 16 + (S + C') per (tile, channel). A thread's dword holds eight keys of a channel; shifted by
-// 8 (t & 1) bits its nibbles at bits 4-7 / 20-23 (and, shifted left by 4, those at bits 0-3 / 16-19) or-ed into
-// 0x5400 are the f16 pairs 64 + u of its four keys, so o += (S / 16) sum p (64 + u) + (C' - 3 S) sum p.
+// Values. v = u S / 16 + (S + C') per (tile, channel). A thread's dword holds eight keys of a channel; rotated so that
+// a key pair's nibbles sit at bits 4-7 / 20-23 and or-ed into 0x5400 they are the f16 pair 64 + u (a rotate and one
+// logic instruction per MMA register, no subtract), so o += (S / 16) sum p (64 + u) + (C' - 3 S) sum p.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kStages = 4;
 constexpr int kKeyGroups = 4;
@@ -313,7 +313,9 @@ __global__ void __launch_bounds__(kThreads, 2)
                            static_cast<std::size_t>(u.kvh) * kHeadDim * kTileKeys;
   NibConsts nib{};
   nib.Load();
-  const int v_shift = 8 * (t & 1);
+  // Rotations that bring this thread's four keys of a V dword to bits 4-7 / 20-23: the pair (4t, 4t+1) sits at bits
+  // 8 (t & 1) + (0, 16), the pair (4t+2, 4t+3) four bits higher; what else rotates in is masked away.
+  const int v_rot_lo = (8 * (t & 1) + 28) & 31, v_rot_hi = 8 * (t & 1);
 
   for (int i = par; i < n_pages; i += kPageSets) {
     const int s = i % kStages;
@@ -447,9 +449,11 @@ __global__ void __launch_bounds__(kThreads, 2)
         constexpr std::uint32_t kMagic64 = 0x54005400U;   // f16 64.0 twice: a nibble at bits 4-7 adds its value
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
-          const std::uint32_t x0 = vc[32 * c] >> v_shift, x1 = vc[32 * c + 16] >> v_shift;
-          const std::uint32_t a0 = AndOr(x0 << 4, nib.hi_mask, kMagic64), a2 = AndOr(x0, nib.hi_mask, kMagic64);
-          const std::uint32_t a1 = AndOr(x1 << 4, nib.hi_mask, kMagic64), a3 = AndOr(x1, nib.hi_mask, kMagic64);
+          const std::uint32_t x0 = vc[32 * c], x1 = vc[32 * c + 16];
+          const std::uint32_t a0 = AndOr(__funnelshift_r(x0, x0, v_rot_lo), nib.hi_mask, kMagic64);
+          const std::uint32_t a2 = AndOr(__funnelshift_r(x0, x0, v_rot_hi), nib.hi_mask, kMagic64);
+          const std::uint32_t a1 = AndOr(__funnelshift_r(x1, x1, v_rot_lo), nib.hi_mask, kMagic64);
+          const std::uint32_t a3 = AndOr(__funnelshift_r(x1, x1, v_rot_hi), nib.hi_mask, kMagic64);
           float d[4];
           MmaF16Zero(d, a0, a1, a2, a3, p_hi[0], p_hi[1]);
           MmaF16(d, a0, a1, a2, a3, p_lo[0], p_lo[1]);

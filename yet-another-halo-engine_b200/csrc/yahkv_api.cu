@@ -1219,7 +1219,6 @@ struct FileCloser {
 
 int yahkv_snapshot_save(yahkv_ctx* ctx, int32_t n_seqs, const int32_t* seq_ids, const char* path) {
   if (int r = RequireDevice(ctx, "snapshot_save"); r != YAHKV_OK) return r;
-  if (IsTileFmt(ctx->cfg.fmt)) return Fail(ctx, YAHKV_ERR_INVALID, "snapshot_save: not available for YAHKV_FMT_KV8A16 / YAHKV_FMT_KV4A16");
   if (n_seqs < 0 || (n_seqs > 0 && seq_ids == nullptr) || path == nullptr)
     return Fail(ctx, YAHKV_ERR_INVALID, "snapshot_save: bad sequence list or path");
   for (int i = 0; i < n_seqs; ++i)
@@ -1233,9 +1232,12 @@ int yahkv_snapshot_save(yahkv_ctx* ctx, int32_t n_seqs, const int32_t* seq_ids, 
   h.fmt = c.fmt, h.n_layers = c.n_layers, h.n_q_heads = c.n_q_heads, h.n_kv_heads = c.n_kv_heads;
   h.head_dim = c.head_dim, h.page_tokens = c.page_tokens, h.n_seqs = n_seqs;
   bool ok = std::fwrite(&h, sizeof(h), 1, f.get()) == 1;
+  // Per page record: K codes, K scales (or pairs), V codes, V scales (or statistic pairs), each for the four kv heads.
   const std::size_t cb = static_cast<std::size_t>(kKvHeads) * RecordCodeBytes(c.fmt);
-  const std::size_t sb = static_cast<std::size_t>(kKvHeads) * kRecordScaleBytes;
-  std::vector<std::uint8_t> buf(2 * (cb + sb));
+  const std::size_t sbk = static_cast<std::size_t>(kKvHeads) * RecordScaleBytes(c.fmt, 0);
+  const std::size_t sbv = static_cast<std::size_t>(kKvHeads) * RecordScaleBytes(c.fmt, 1);
+  std::vector<std::uint8_t> buf(2 * cb + sbk + sbv);
+  std::vector<std::uint8_t> state(static_cast<std::size_t>(kKvHeads) * kHeadDim * 4 + static_cast<std::size_t>(kOpenTileHalfs) * 2);
   for (int i = 0; i < n_seqs && ok; ++i) {
     const int s = seq_ids[i];
     const std::int32_t np = ctx->host.n_pages(s);
@@ -1248,13 +1250,23 @@ int yahkv_snapshot_save(yahkv_ctx* ctx, int32_t n_seqs, const int32_t* seq_ids, 
       for (int p = 0; p < np && ok; ++p) {
         const std::size_t rec = (static_cast<std::size_t>(l) * c.num_pages + ctx->host.table_row(s)[p]) * kKvHeads;
         YAHKV_CUDA(ctx, cudaMemcpy(buf.data(), ctx->pool.kcodes + rec * RecordCodeBytes(c.fmt), cb, cudaMemcpyDeviceToHost));
-        YAHKV_CUDA(ctx, cudaMemcpy(buf.data() + cb, ctx->pool.kscales + rec * kPageTokens * kBlocksPerRow, sb, cudaMemcpyDeviceToHost));
-        YAHKV_CUDA(ctx, cudaMemcpy(buf.data() + cb + sb, ctx->pool.vcodes + rec * RecordCodeBytes(c.fmt), cb, cudaMemcpyDeviceToHost));
-        YAHKV_CUDA(ctx, cudaMemcpy(buf.data() + 2 * cb + sb, ctx->pool.vscales + rec * kPageTokens * kBlocksPerRow, sb, cudaMemcpyDeviceToHost));
+        YAHKV_CUDA(ctx, cudaMemcpy(buf.data() + cb, ctx->pool.kscales + rec * (RecordScaleBytes(c.fmt, 0) / 2), sbk, cudaMemcpyDeviceToHost));
+        YAHKV_CUDA(ctx, cudaMemcpy(buf.data() + cb + sbk, ctx->pool.vcodes + rec * RecordCodeBytes(c.fmt), cb, cudaMemcpyDeviceToHost));
+        YAHKV_CUDA(ctx, cudaMemcpy(buf.data() + 2 * cb + sbk, ctx->pool.vscales + rec * (RecordScaleBytes(c.fmt, 1) / 2), sbv, cudaMemcpyDeviceToHost));
         FlipQ8(c.fmt, YAHKV_SIDE_K, buf.data(), cb);                 // the file holds GGUF int8 codes
-        FlipQ8(c.fmt, YAHKV_SIDE_V, buf.data() + cb + sb, cb);
+        FlipQ8(c.fmt, YAHKV_SIDE_V, buf.data() + cb + sbk, cb);
         ok = std::fwrite(buf.data(), buf.size(), 1, f.get()) == 1;
       }
+    // The tile formats keep state beyond the pages: per layer the K channel mean and the open fp16 tile.
+    for (int l = 0; IsTileFmt(c.fmt) && l < c.n_layers && ok; ++l) {
+      const std::size_t srow = static_cast<std::size_t>(s) * c.n_layers + l;
+      YAHKV_CUDA(ctx, cudaMemcpy(state.data(), ctx->kmean_dev + srow * kKvHeads * kHeadDim,
+                                 static_cast<std::size_t>(kKvHeads) * kHeadDim * 4, cudaMemcpyDeviceToHost));
+      YAHKV_CUDA(ctx, cudaMemcpy(state.data() + static_cast<std::size_t>(kKvHeads) * kHeadDim * 4,
+                                 static_cast<const std::uint16_t*>(ctx->open_tiles_dev) + (srow * 2 + ctx->host.open_cur(s, l)) * kOpenTileHalfs,
+                                 static_cast<std::size_t>(kOpenTileHalfs) * 2, cudaMemcpyDeviceToHost));
+      ok = std::fwrite(state.data(), state.size(), 1, f.get()) == 1;
+    }
   }
   if (!ok) return Fail(ctx, YAHKV_ERR_INVALID, std::string("snapshot_save: write failed on ") + path);
   return YAHKV_OK;
@@ -1262,7 +1274,6 @@ int yahkv_snapshot_save(yahkv_ctx* ctx, int32_t n_seqs, const int32_t* seq_ids, 
 
 int yahkv_snapshot_load(yahkv_ctx* ctx, const char* path, int32_t* seq_ids_out, int32_t* n_inout) {
   if (int r = RequireDevice(ctx, "snapshot_load"); r != YAHKV_OK) return r;
-  if (IsTileFmt(ctx->cfg.fmt)) return Fail(ctx, YAHKV_ERR_INVALID, "snapshot_load: not available for YAHKV_FMT_KV8A16 / YAHKV_FMT_KV4A16");
   if (path == nullptr || seq_ids_out == nullptr || n_inout == nullptr)
     return Fail(ctx, YAHKV_ERR_INVALID, "snapshot_load: null argument");
   std::unique_ptr<std::FILE, FileCloser> f(std::fopen(path, "rb"));
@@ -1278,8 +1289,10 @@ int yahkv_snapshot_load(yahkv_ctx* ctx, const char* path, int32_t* seq_ids_out, 
   if (h.n_seqs < 0 || h.n_seqs > *n_inout) return Fail(ctx, YAHKV_ERR_CAPACITY, "snapshot_load: more sequences than the caller's array holds");
   YAHKV_CUDA(ctx, cudaDeviceSynchronize());
   const std::size_t cb = static_cast<std::size_t>(kKvHeads) * RecordCodeBytes(c.fmt);
-  const std::size_t sb = static_cast<std::size_t>(kKvHeads) * kRecordScaleBytes;
-  std::vector<std::uint8_t> buf(2 * (cb + sb));
+  const std::size_t sbk = static_cast<std::size_t>(kKvHeads) * RecordScaleBytes(c.fmt, 0);
+  const std::size_t sbv = static_cast<std::size_t>(kKvHeads) * RecordScaleBytes(c.fmt, 1);
+  std::vector<std::uint8_t> buf(2 * cb + sbk + sbv);
+  std::vector<std::uint8_t> state(static_cast<std::size_t>(kKvHeads) * kHeadDim * 4 + static_cast<std::size_t>(kOpenTileHalfs) * 2);
   std::vector<std::int32_t> made;
   auto undo = [&](int code, const std::string& msg) {   // a failed load leaves no half-made sequences behind
     for (auto it = made.rbegin(); it != made.rend(); ++it) ctx->host.SeqFree(*it);   // restores the free lists' order
@@ -1304,14 +1317,28 @@ int yahkv_snapshot_load(yahkv_ctx* ctx, const char* path, int32_t* seq_ids_out, 
       for (int p = 0; p < np; ++p) {
         if (std::fread(buf.data(), buf.size(), 1, f.get()) != 1) return undo(YAHKV_ERR_INVALID, "snapshot_load: truncated file");
         FlipQ8(c.fmt, YAHKV_SIDE_K, buf.data(), cb);
-        FlipQ8(c.fmt, YAHKV_SIDE_V, buf.data() + cb + sb, cb);
+        FlipQ8(c.fmt, YAHKV_SIDE_V, buf.data() + cb + sbk, cb);
         const std::size_t rec = (static_cast<std::size_t>(l) * c.num_pages + ctx->host.table_row(s)[p]) * kKvHeads;
         cudaError_t ce = cudaMemcpy(ctx->pool.kcodes + rec * RecordCodeBytes(c.fmt), buf.data(), cb, cudaMemcpyHostToDevice);
-        if (ce == cudaSuccess) ce = cudaMemcpy(ctx->pool.kscales + rec * kPageTokens * kBlocksPerRow, buf.data() + cb, sb, cudaMemcpyHostToDevice);
-        if (ce == cudaSuccess) ce = cudaMemcpy(ctx->pool.vcodes + rec * RecordCodeBytes(c.fmt), buf.data() + cb + sb, cb, cudaMemcpyHostToDevice);
-        if (ce == cudaSuccess) ce = cudaMemcpy(ctx->pool.vscales + rec * kPageTokens * kBlocksPerRow, buf.data() + 2 * cb + sb, sb, cudaMemcpyHostToDevice);
+        if (ce == cudaSuccess) ce = cudaMemcpy(ctx->pool.kscales + rec * (RecordScaleBytes(c.fmt, 0) / 2), buf.data() + cb, sbk, cudaMemcpyHostToDevice);
+        if (ce == cudaSuccess) ce = cudaMemcpy(ctx->pool.vcodes + rec * RecordCodeBytes(c.fmt), buf.data() + cb + sbk, cb, cudaMemcpyHostToDevice);
+        if (ce == cudaSuccess) ce = cudaMemcpy(ctx->pool.vscales + rec * (RecordScaleBytes(c.fmt, 1) / 2), buf.data() + 2 * cb + sbk, sbv, cudaMemcpyHostToDevice);
         if (ce != cudaSuccess) return undo(YAHKV_ERR_CUDA, std::string("snapshot_load: ") + cudaGetErrorString(ce));
       }
+    if (IsTileFmt(c.fmt)) {   // the mean and the open tile of every layer; the tile lands in the first buffer
+      ctx->host.ResetOpenState(s);
+      for (int l = 0; l < c.n_layers; ++l) {
+        if (std::fread(state.data(), state.size(), 1, f.get()) != 1) return undo(YAHKV_ERR_INVALID, "snapshot_load: truncated file");
+        const std::size_t srow = static_cast<std::size_t>(s) * c.n_layers + l;
+        cudaError_t ce = cudaMemcpy(ctx->kmean_dev + srow * kKvHeads * kHeadDim, state.data(),
+                                    static_cast<std::size_t>(kKvHeads) * kHeadDim * 4, cudaMemcpyHostToDevice);
+        if (ce == cudaSuccess)
+          ce = cudaMemcpy(static_cast<std::uint16_t*>(ctx->open_tiles_dev) + srow * 2 * kOpenTileHalfs,
+                          state.data() + static_cast<std::size_t>(kKvHeads) * kHeadDim * 4,
+                          static_cast<std::size_t>(kOpenTileHalfs) * 2, cudaMemcpyHostToDevice);
+        if (ce != cudaSuccess) return undo(YAHKV_ERR_CUDA, std::string("snapshot_load: ") + cudaGetErrorString(ce));
+      }
+    }
     seq_ids_out[i] = s;
   }
   *n_inout = h.n_seqs;
