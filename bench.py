@@ -716,7 +716,7 @@ def main():
     ap.add_argument("--impl", default="yahkv", choices=["yahkv", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers per step (16 = the configuration)")
     ap.add_argument("--fmt", default="q8_0", choices=["q8_0", "q4_0", "kv8a16", "kv4a16"],
-                    help="cache format (q8_0 = the configuration; kv8a16 / kv4a16 = the reference's own formats, eager calls only)")
+                    help="cache format (q8_0 = the configuration; kv8a16 / kv4a16 = the reference's own formats)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "longctx", "churn", "headshard"],
                     help="decode = the batch-32 configuration (default, the headline metric); prefill = chunked "
                          "prefill; longctx = batch 8 x 131072 tokens, q4_0, 64 splits, one layer")
@@ -761,7 +761,7 @@ def main():
     rng, lens, layers = w["rng"], w["lens"].copy(), w["layers"]
     total_steps = args.warmup + args.steps
     e2e_steps = 0 if args.no_e2e else args.steps + 1
-    graph_steps = 0 if (args.no_graph or N_SPLITS or args.fmt in ("kv8a16", "kv4a16")) else args.steps + 3
+    graph_steps = 0 if (args.no_graph or N_SPLITS) else args.steps + 3
     grow = total_steps + graph_steps + e2e_steps + 2
     pages = [(int(n) + grow + 63) // 64 for n in lens]
     num_pages = sum(pages) + 64

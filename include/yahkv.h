@@ -48,9 +48,10 @@ extern "C" {
  * 2336 B per token per layer. Supported with this format: yahkv_append, yahkv_attend_decode, yahkv_attend_prefill
  * (its dequantize pass reads the tile of each sequence's newest key from the open buffer, the others from the pools),
  * the host-buffer decode steps, yahkv_read_page / yahkv_write_page, yahkv_seq_set_kmean, yahkv_read_open_tile,
- * yahkv_snapshot_save / yahkv_snapshot_load (pages plus, per layer, the mean and the open tile). Not supported (refused
- * with YAHKV_ERR_INVALID): the fused RoPE append, decode batches, yahkv_export_token, head-sharded contexts, and
- * yahkv_seq_set_len to anything but 0. */
+ * yahkv_snapshot_save / yahkv_snapshot_load (pages plus, per layer, the mean and the open tile), decode batches
+ * (yahkv_batch_*; the layers of a sequence must have been appended with the same calls). Not supported (refused with
+ * YAHKV_ERR_INVALID): the fused RoPE append, yahkv_export_token, head-sharded contexts, and yahkv_seq_set_len to
+ * anything but 0. */
 #define YAHKV_FMT_KV8A16 2
 /* Its 4-bit sibling kv4a16 (engine/gpu/loom/tools/gen_kvq.py:288-463, :474-660 with 4-bit V), same pages, tiles, open
  * tile, mean and supported calls as YAHKV_FMT_KV8A16:

@@ -11,11 +11,14 @@ pytestmark = pytest.mark.gpu
 LAYERS = 2
 
 
-def twin_caches(lens, seed, extra_tokens):
+FORMATS = [yahkv.FMT_Q8_0, yahkv.FMT_KV8A16, yahkv.FMT_KV4A16]
+
+
+def twin_caches(lens, seed, extra_tokens, fmt=yahkv.FMT_Q8_0):
     rng = np.random.default_rng(seed)
     pages = [(n + extra_tokens + 63) // 64 for n in lens]
     num_pages = sum(pages) + 2
-    caches = [yahkv.KvCache(n_layers=LAYERS, num_pages=num_pages, max_seqs=len(lens), max_pages_per_seq=max(pages))
+    caches = [yahkv.KvCache(n_layers=LAYERS, num_pages=num_pages, max_seqs=len(lens), max_pages_per_seq=max(pages), fmt=fmt)
               for _ in range(2)]
     perm = rng.permutation(num_pages).astype(np.int32)
     seqs, off = [], 0
@@ -51,9 +54,11 @@ def step_inputs(rng, n):
             rng.standard_normal((LAYERS, n, 24, 256)).astype(np.float32))
 
 
-def test_eager_batch_steps_match_host_planned_steps():
-    lens = [5, 63, 64, 1535, 24 * 64 - 2, 700]          # page boundaries and a unit boundary (24 pages) get crossed
-    ref, cache, seqs, num_pages, rng = twin_caches(lens, 61, extra_tokens=8)
+@pytest.mark.parametrize("fmt", FORMATS)
+def test_eager_batch_steps_match_host_planned_steps(fmt):
+    # page boundaries, a unit boundary (24 pages) and, for the tile formats, 16-key tile boundaries get crossed
+    lens = [5, 63, 64, 1535, 24 * 64 - 2, 700, 13]
+    ref, cache, seqs, num_pages, rng = twin_caches(lens, 61, extra_tokens=8, fmt=fmt)
     batch = yahkv.DecodeBatch(cache, seqs)
     assert batch.prepare(6) is True
     cur = list(lens)
@@ -82,9 +87,10 @@ def test_eager_batch_steps_match_host_planned_steps():
     batch.close()
 
 
-def test_replayed_cuda_graph_matches_host_planned_steps():
-    lens = [300, 64 * 24 - 3, 2000, 1]
-    ref, cache, seqs, num_pages, rng = twin_caches(lens, 62, extra_tokens=8)
+@pytest.mark.parametrize("fmt", FORMATS)
+def test_replayed_cuda_graph_matches_host_planned_steps(fmt):
+    lens = [300, 64 * 24 - 3, 2000, 1, 30]
+    ref, cache, seqs, num_pages, rng = twin_caches(lens, 62, extra_tokens=8, fmt=fmt)
     n = len(seqs)
     batch = yahkv.DecodeBatch(cache, seqs)
     batch.prepare(6)

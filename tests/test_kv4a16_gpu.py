@@ -135,7 +135,7 @@ def test_ragged_batch_with_means_and_decode_steps():
             assert err.max() <= 2e-3 and err.max() / np.abs(want).max() < 1e-4, (step, n_splits, err)
     assert_pools(cache, 0, pool)
     x = torch.zeros(4, 24, 256, dtype=torch.float16, device="cuda")
-    for call in (lambda: cache.export_token(0, seqs[0], 0), lambda: yahkv.DecodeBatch(cache, seqs),
+    for call in (lambda: cache.export_token(0, seqs[0], 0),
                  lambda: cache.seq_set_len(seqs[0], 1), lambda: cache.seq_set_kmean(seqs[0], np.zeros((4, 256), np.float32))):
         with pytest.raises(yahkv.YahkvError):
             call()

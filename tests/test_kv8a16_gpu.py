@@ -135,7 +135,7 @@ def test_ragged_batch_with_means_and_decode_steps():
     # what the format does not support is refused before anything is launched
     x = torch.zeros(4, 24, 256, dtype=torch.float16, device="cuda")
     for call in (lambda: cache.export_token(0, seqs[0], 0),
-                 lambda: yahkv.DecodeBatch(cache, seqs), lambda: cache.seq_set_len(seqs[0], 1),
+                 lambda: cache.seq_set_len(seqs[0], 1),
                  lambda: cache.seq_set_kmean(seqs[0], np.zeros((4, 256), np.float32))):
         with pytest.raises(yahkv.YahkvError):
             call()

@@ -16,7 +16,8 @@ namespace {
 __global__ void BatchPlanKernel(const std::int32_t* __restrict__ lens, const BatchSeq* __restrict__ seqs, int n_seqs,
                                 const std::int32_t* __restrict__ tables, int table_stride, int unit_pages,
                                 int num_pages, DecodeUnit* __restrict__ units, CombineItem* __restrict__ items,
-                                std::int64_t* __restrict__ slots) {
+                                std::int64_t* __restrict__ slots, VTileWork* __restrict__ vwork,
+                                std::int32_t* __restrict__ state_rows, int n_layers) {
   ChainedKernelEntry();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n_seqs * kKvHeads) return;
@@ -37,13 +38,30 @@ __global__ void BatchPlanKernel(const std::int32_t* __restrict__ lens, const Bat
     u.page_end = k == bs.n_units - 1 ? pages : min((k + 1) * unit_pages, pages);
     u.n_keys = n;
     u.partial = first + k;
-    u.pad = 0;
+    u.pad = bs.open_cur;
     units[first + k] = u;
   }
   if (h == 0) {
     std::int32_t page = tables[static_cast<std::size_t>(bs.seq_row) * table_stride + min(pos / kPageTokens, table_stride - 1)];
     page = min(max(page, 0), num_pages - 1);
     slots[b] = static_cast<std::int64_t>(page) * kPageTokens + pos % kPageTokens;
+    if (vwork != nullptr) {
+      // Tile formats: the step's token is key pos % 16 of tile pos / 16. A single-token append stays in the
+      // sequence's current open buffer (the host planner's rule for a call that touches one tile), and the tile is
+      // quantized when this is its 16th key.
+      VTileWork w;
+      w.state_row = bs.seq_row * n_layers;
+      w.phys_tile = page * kTilesPerPage + (pos % kPageTokens) / kTileKeys;
+      w.n_old = pos % kTileKeys;
+      w.n_keys = w.n_old + 1;
+      w.read_buf = bs.open_cur;
+      w.write_buf = bs.open_cur;
+      w.complete = w.n_keys == kTileKeys ? 1 : 0;
+      w.pad = 0;
+      for (int j = 0; j < kTileKeys; ++j) w.src[j] = j == w.n_old ? b : -1;
+      vwork[b] = w;
+      state_rows[b] = bs.seq_row * n_layers;
+    }
   }
 }
 
@@ -76,11 +94,12 @@ cudaError_t LaunchWaitProbe(int* status_dev, std::uint64_t limit_ns, cudaStream_
 cudaError_t LaunchBatchPlan(const std::int32_t* lens_dev, const BatchSeq* seqs_dev, int n_seqs,
                             const std::int32_t* tables_dev, int table_stride, int unit_pages, int num_pages,
                             DecodeUnit* units_dev, CombineItem* items_dev, std::int64_t* slots_dev,
-                            cudaStream_t stream) {
+                            VTileWork* vwork_dev, std::int32_t* state_rows_dev, int n_layers, cudaStream_t stream) {
   if (n_seqs <= 0) return cudaSuccess;
   const int threads = n_seqs * kKvHeads;
   return LaunchChained(BatchPlanKernel, (threads + 127) / 128, 128, 0, stream, lens_dev, seqs_dev, n_seqs, tables_dev,
-                       table_stride, unit_pages, num_pages, units_dev, items_dev, slots_dev);
+                       table_stride, unit_pages, num_pages, units_dev, items_dev, slots_dev, vwork_dev, state_rows_dev,
+                       n_layers);
 }
 
 cudaError_t LaunchBatchAdvance(std::int32_t* lens_dev, int n_seqs, int by, cudaStream_t stream) {

@@ -96,12 +96,15 @@ struct BatchSeq {
   std::int32_t seq_row;
   std::int32_t first_unit;
   std::int32_t n_units;
-  std::int32_t pad;
+  std::int32_t open_cur;    // tile formats: the sequence's current open-tile buffer (the same in every layer)
 };
+struct VTileWork;
+// vwork_dev / state_rows_dev: tile formats only (else null): per batch row the V tile work item of this step's token and
+// the row of the sequence's layer-0 state (the kernels add the layer).
 cudaError_t LaunchBatchPlan(const std::int32_t* lens_dev, const BatchSeq* seqs_dev, int n_seqs,
                             const std::int32_t* tables_dev, int table_stride, int unit_pages, int num_pages,
                             DecodeUnit* units_dev, CombineItem* items_dev, std::int64_t* slots_dev,
-                            cudaStream_t stream);
+                            VTileWork* vwork_dev, std::int32_t* state_rows_dev, int n_layers, cudaStream_t stream);
 cudaError_t LaunchBatchAdvance(std::int32_t* lens_dev, int n_seqs, int by, cudaStream_t stream);
 
 // Prefill attention reads a dequantized fp16 copy of the sequences' K and V (the reference's yah_kdeq / yah_vdeq
@@ -195,7 +198,7 @@ cudaError_t LaunchDecodePart(const DecodeLaunch& a, cudaStream_t stream);
 constexpr int kOpenTileHalfs = kKvHeads * kHeadDim * kTileKeys;   // one buffer, in fp16 elements
 // One 16-key V tile touched by an append call.
 struct VTileWork {
-  std::int32_t state_row;   // (sequence * n_layers + layer): index of the open-tile pair
+  std::int32_t state_row;   // (sequence * n_layers + layer): index of the open-tile pair (+ the launch's state_row_add)
   std::int32_t phys_tile;   // page * 4 + tile in page: the pool slot of the tile
   std::int32_t n_old;       // keys 0 .. n_old - 1 were appended earlier and come from open buffer read_buf
   std::int32_t n_keys;      // keys of the tile after this call
@@ -206,11 +209,13 @@ struct VTileWork {
   std::int32_t src[kTileKeys];   // input token index of key j for j >= n_old
 };
 static_assert(sizeof(VTileWork) == 96, "uploaded as an array");
+// state_row_add is added to every state row of the call: 0 when the host listed (sequence * n_layers + layer) rows,
+// the layer when a decode batch's plan kernel listed layer-0 rows once for all layers of a step.
 cudaError_t LaunchKv8AppendK(const PoolView& pool, int layer, int n_tokens, const std::int64_t* slots_dev,
-                             const std::int32_t* state_rows_dev, const float* kmean_dev, const void* k_dev,
-                             cudaStream_t stream);
-cudaError_t LaunchKv8AppendV(const PoolView& pool, int layer, int n_work, const VTileWork* work_dev, void* open_tiles_dev,
-                             const void* v_dev, cudaStream_t stream);
+                             const std::int32_t* state_rows_dev, int state_row_add, const float* kmean_dev,
+                             const void* k_dev, cudaStream_t stream);
+cudaError_t LaunchKv8AppendV(const PoolView& pool, int layer, int n_work, const VTileWork* work_dev, int state_row_add,
+                             void* open_tiles_dev, const void* v_dev, cudaStream_t stream);
 // Decode attention over kv8a16 pools. DecodeUnit::pad carries the sequence's current open buffer (0 | 1);
 // state_stride = n_layers (the open-tile pair of (sequence, layer) is row seq * n_layers + layer).
 cudaError_t LaunchKv8DecodePart(const DecodeLaunch& a, const void* open_tiles_dev, int n_layers, cudaStream_t stream);
@@ -218,8 +223,8 @@ cudaError_t ConfigureKv8Kernels();
 // kv4a16 (kv4a16.cu): the K append (rotation + 4-bit groups) and decode attention; the V append and the prefill
 // dequantize pass are the kv8a16 launchers above and below, which switch on pool.fmt.
 cudaError_t LaunchKv4AppendK(const PoolView& pool, int layer, int n_tokens, const std::int64_t* slots_dev,
-                             const std::int32_t* state_rows_dev, const float* kmean_dev, const void* k_dev,
-                             cudaStream_t stream);
+                             const std::int32_t* state_rows_dev, int state_row_add, const float* kmean_dev,
+                             const void* k_dev, cudaStream_t stream);
 cudaError_t LaunchKv4DecodePart(const DecodeLaunch& a, const void* open_tiles_dev, int n_layers, cudaStream_t stream);
 cudaError_t ConfigureKv4Kernels();
 cudaError_t LaunchDecodeCombine(const DecodeLaunch& a, cudaStream_t stream);

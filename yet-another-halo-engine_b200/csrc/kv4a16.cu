@@ -53,7 +53,7 @@ __device__ __forceinline__ int NibbleShift(int i) { return 4 * (i >> 1) + ((i & 
 // Append, K side: one warp per (token, kv head); lane l holds dims 8 l .. 8 l + 7, a 32-dim group is 4 lanes.
 // ---------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) Kv4AppendKKernel(PoolView pool, int layer, const std::int64_t* __restrict__ slots,
-                                                        const std::int32_t* __restrict__ state_rows,
+                                                        const std::int32_t* __restrict__ state_rows, int state_row_add,
                                                         const float* __restrict__ kmean,
                                                         const __half* __restrict__ k_in) {
   ChainedKernelEntry();
@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(128) Kv4AppendKKernel(PoolView pool, int layer
   const int tok = static_cast<int>(slot % kPageTokens);
   page = min(max(page, static_cast<std::int64_t>(0)), static_cast<std::int64_t>(pool.num_pages - 1));
   const uint4 raw = *reinterpret_cast<const uint4*>(k_in + (static_cast<std::size_t>(token) * kKvHeads + h) * kHeadDim + lane * 8);
-  const float* mean = kmean + (static_cast<std::size_t>(state_rows[token]) * kKvHeads + h) * kHeadDim + lane * 8;
+  const float* mean = kmean + (static_cast<std::size_t>(state_rows[token] + state_row_add) * kKvHeads + h) * kHeadDim + lane * 8;
   const float4 m0 = *reinterpret_cast<const float4*>(mean), m1 = *reinterpret_cast<const float4*>(mean + 4);
   const float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
   const __half2* hp = reinterpret_cast<const __half2*>(&raw);
@@ -639,11 +639,11 @@ cudaError_t ConfigureKv4Kernels() {
 }
 
 cudaError_t LaunchKv4AppendK(const PoolView& pool, int layer, int n_tokens, const std::int64_t* slots_dev,
-                             const std::int32_t* state_rows_dev, const float* kmean_dev, const void* k_dev,
-                             cudaStream_t stream) {
+                             const std::int32_t* state_rows_dev, int state_row_add, const float* kmean_dev,
+                             const void* k_dev, cudaStream_t stream) {
   if (n_tokens <= 0) return cudaSuccess;
-  return LaunchChained(Kv4AppendKKernel, n_tokens, 128, 0, stream, pool, layer, slots_dev, state_rows_dev, kmean_dev,
-                       static_cast<const __half*>(k_dev));
+  return LaunchChained(Kv4AppendKKernel, n_tokens, 128, 0, stream, pool, layer, slots_dev, state_rows_dev, state_row_add,
+                       kmean_dev, static_cast<const __half*>(k_dev));
 }
 
 cudaError_t LaunchKv4DecodePart(const DecodeLaunch& a, const void* open_tiles_dev, int n_layers, cudaStream_t stream) {

@@ -39,7 +39,7 @@ namespace {
 // Append, K side: one warp per (token, kv head); lane l holds dims 8 l .. 8 l + 7, a 128-dim half is 16 lanes.
 // ---------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) Kv8AppendKKernel(PoolView pool, int layer, const std::int64_t* __restrict__ slots,
-                                                        const std::int32_t* __restrict__ state_rows,
+                                                        const std::int32_t* __restrict__ state_rows, int state_row_add,
                                                         const float* __restrict__ kmean,
                                                         const __half* __restrict__ k_in) {
   ChainedKernelEntry();
@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(128) Kv8AppendKKernel(PoolView pool, int layer
   const int tok = static_cast<int>(slot % kPageTokens);
   page = min(max(page, static_cast<std::int64_t>(0)), static_cast<std::int64_t>(pool.num_pages - 1));
   const uint4 raw = *reinterpret_cast<const uint4*>(k_in + (static_cast<std::size_t>(token) * kKvHeads + h) * kHeadDim + lane * 8);
-  const float* mean = kmean + (static_cast<std::size_t>(state_rows[token]) * kKvHeads + h) * kHeadDim + lane * 8;
+  const float* mean = kmean + (static_cast<std::size_t>(state_rows[token] + state_row_add) * kKvHeads + h) * kHeadDim + lane * 8;
   const float4 m0 = *reinterpret_cast<const float4*>(mean), m1 = *reinterpret_cast<const float4*>(mean + 4);
   const float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
   const __half2* hp = reinterpret_cast<const __half2*>(&raw);
@@ -95,13 +95,13 @@ __global__ void __launch_bounds__(128) Kv8AppendKKernel(PoolView pool, int layer
 // key 8w + 2p (p < 4) or 8w + 2(p - 4) + 1, pair (16 sf, cf - 23 sf).
 template <int kBits>
 __global__ void __launch_bounds__(kHeadDim) Kv8AppendVKernel(PoolView pool, int layer, const VTileWork* __restrict__ work,
-                                                             __half* __restrict__ open_tiles,
+                                                             int state_row_add, __half* __restrict__ open_tiles,
                                                              const __half* __restrict__ v_in) {
   ChainedKernelEntry();
   const VTileWork wk = work[blockIdx.x];
   const int h = blockIdx.y, ch = threadIdx.x;
   if (!pool.OwnsKvHead(h)) return;
-  __half* open_pair = open_tiles + static_cast<std::size_t>(wk.state_row) * 2 * kOpenTileHalfs;
+  __half* open_pair = open_tiles + static_cast<std::size_t>(wk.state_row + state_row_add) * 2 * kOpenTileHalfs;
   const std::size_t ch_off = (static_cast<std::size_t>(h) * kHeadDim + ch) * kTileKeys;
   __align__(16) __half v[kTileKeys];
   {
@@ -698,21 +698,21 @@ cudaError_t ConfigureKv8Kernels() {
 }
 
 cudaError_t LaunchKv8AppendK(const PoolView& pool, int layer, int n_tokens, const std::int64_t* slots_dev,
-                             const std::int32_t* state_rows_dev, const float* kmean_dev, const void* k_dev,
-                             cudaStream_t stream) {
+                             const std::int32_t* state_rows_dev, int state_row_add, const float* kmean_dev,
+                             const void* k_dev, cudaStream_t stream) {
   if (n_tokens <= 0) return cudaSuccess;
-  return LaunchChained(Kv8AppendKKernel, n_tokens, 128, 0, stream, pool, layer, slots_dev, state_rows_dev, kmean_dev,
-                       static_cast<const __half*>(k_dev));
+  return LaunchChained(Kv8AppendKKernel, n_tokens, 128, 0, stream, pool, layer, slots_dev, state_rows_dev, state_row_add,
+                       kmean_dev, static_cast<const __half*>(k_dev));
 }
 
-cudaError_t LaunchKv8AppendV(const PoolView& pool, int layer, int n_work, const VTileWork* work_dev, void* open_tiles_dev,
-                             const void* v_dev, cudaStream_t stream) {
+cudaError_t LaunchKv8AppendV(const PoolView& pool, int layer, int n_work, const VTileWork* work_dev, int state_row_add,
+                             void* open_tiles_dev, const void* v_dev, cudaStream_t stream) {
   if (n_work <= 0) return cudaSuccess;
   if (pool.fmt == kFmtKv4)
     return LaunchChained(Kv8AppendVKernel<4>, dim3(n_work, kKvHeads), kHeadDim, 0, stream, pool, layer, work_dev,
-                         static_cast<__half*>(open_tiles_dev), static_cast<const __half*>(v_dev));
+                         state_row_add, static_cast<__half*>(open_tiles_dev), static_cast<const __half*>(v_dev));
   return LaunchChained(Kv8AppendVKernel<8>, dim3(n_work, kKvHeads), kHeadDim, 0, stream, pool, layer, work_dev,
-                       static_cast<__half*>(open_tiles_dev), static_cast<const __half*>(v_dev));
+                       state_row_add, static_cast<__half*>(open_tiles_dev), static_cast<const __half*>(v_dev));
 }
 
 cudaError_t LaunchKv8DecodePart(const DecodeLaunch& a, const void* open_tiles_dev, int n_layers, cudaStream_t stream) {

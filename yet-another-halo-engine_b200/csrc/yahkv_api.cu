@@ -613,8 +613,8 @@ int yahkv_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int32_t*
       return r;
     TimedLaunch tl(ctx, YAHKV_KERNEL_APPEND, st);
     YAHKV_CUDA(ctx, (ctx->cfg.fmt == YAHKV_FMT_KV4A16 ? LaunchKv4AppendK : LaunchKv8AppendK)(
-                        ctx->pool, layer, n_tokens, ctx->slots_dev, ctx->state_rows_dev, ctx->kmean_dev, k_dev, st));
-    YAHKV_CUDA(ctx, LaunchKv8AppendV(ctx->pool, layer, static_cast<int>(ctx->vwork_scratch.size()), ctx->vwork_dev,
+                        ctx->pool, layer, n_tokens, ctx->slots_dev, ctx->state_rows_dev, 0, ctx->kmean_dev, k_dev, st));
+    YAHKV_CUDA(ctx, LaunchKv8AppendV(ctx->pool, layer, static_cast<int>(ctx->vwork_scratch.size()), ctx->vwork_dev, 0,
                                      ctx->open_tiles_dev, v_dev, st));
     tl.End();
     ctx->launches += 2;
@@ -718,10 +718,17 @@ int yahkv_attend_decode(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int
   cudaStream_t st = StreamOf(ctx, stream);
   if (int r = FlushTables(ctx, st); r != YAHKV_OK) return r;
   const bool kv8 = IsTileFmt(ctx->cfg.fmt);
-  if (kv8) {   // every unit carries its sequence's current open-tile buffer of THIS layer: uploaded on every call
-    ctx->unit_scratch = ctx->host.units();
-    for (DecodeUnit& u : ctx->unit_scratch) u.pad = ctx->host.open_cur(u.seq, layer);
-    changed = true;
+  if (kv8) {
+    // Every unit carries its sequence's current open-tile buffer of THIS layer. The layers of a step usually agree on
+    // it, so the list is uploaded again only when the plan or one of those indices differs from what the device holds.
+    const auto& planned = ctx->host.units();
+    bool same = !changed && ctx->unit_scratch.size() == planned.size();
+    if (!same) ctx->unit_scratch = planned;
+    for (DecodeUnit& u : ctx->unit_scratch) {
+      const std::int32_t cur = ctx->host.open_cur(u.seq, layer);
+      if (u.pad != cur) u.pad = cur, same = false;
+    }
+    changed = !same;
   }
   const auto& units = kv8 ? ctx->unit_scratch : ctx->host.units();
   const auto& items = ctx->host.items();
@@ -1023,13 +1030,16 @@ struct yahkv_batch {
   DecodeUnit* units_dev = nullptr;
   CombineItem* items_dev = nullptr;
   std::int64_t* slots_dev = nullptr;
+  VTileWork* vwork_dev = nullptr;          // tile formats: the step's V tile work item per row
+  std::int32_t* state_rows_dev = nullptr;  // tile formats: layer-0 state row per row
   int units_cap = 0;
 };
 namespace {
 constexpr int kBatchUnitPages = 24;   // the automatic planner's unit size on large batches (kv_host.hpp)
 void BatchFree(yahkv_batch* b) {
   for (void* p : {static_cast<void*>(b->lens_dev), static_cast<void*>(b->rows_dev), static_cast<void*>(b->units_dev),
-                  static_cast<void*>(b->items_dev), static_cast<void*>(b->slots_dev)})
+                  static_cast<void*>(b->items_dev), static_cast<void*>(b->slots_dev), static_cast<void*>(b->vwork_dev),
+                  static_cast<void*>(b->state_rows_dev)})
     if (p != nullptr) cudaFree(p);
   delete b;
 }
@@ -1037,7 +1047,6 @@ void BatchFree(yahkv_batch* b) {
 
 int yahkv_batch_create(yahkv_ctx* ctx, int32_t n_seqs, const int32_t* seq_ids, yahkv_batch** out) {
   if (int r = RequireDevice(ctx, "batch_create"); r != YAHKV_OK) return r;
-  if (IsTileFmt(ctx->cfg.fmt)) return Fail(ctx, YAHKV_ERR_INVALID, "batch_create: not available for YAHKV_FMT_KV8A16 / YAHKV_FMT_KV4A16");
   if (out == nullptr) return Fail(ctx, YAHKV_ERR_INVALID, "batch_create: null out pointer");
   *out = nullptr;
   if (n_seqs <= 0 || n_seqs > ctx->cfg.max_seqs || seq_ids == nullptr) return Fail(ctx, YAHKV_ERR_INVALID, "batch_create: bad sequence list");
@@ -1066,6 +1075,8 @@ int yahkv_batch_create(yahkv_ctx* ctx, int32_t n_seqs, const int32_t* seq_ids, y
   if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&b->units_dev), sizeof(DecodeUnit) * b->units_cap);
   if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&b->items_dev), sizeof(CombineItem) * n_seqs * kKvHeads);
   if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&b->slots_dev), sizeof(std::int64_t) * n_seqs);
+  if (e == cudaSuccess && IsTileFmt(ctx->cfg.fmt)) e = cudaMalloc(reinterpret_cast<void**>(&b->vwork_dev), sizeof(VTileWork) * n_seqs);
+  if (e == cudaSuccess && IsTileFmt(ctx->cfg.fmt)) e = cudaMalloc(reinterpret_cast<void**>(&b->state_rows_dev), sizeof(std::int32_t) * n_seqs);
   if (e != cudaSuccess) {
     BatchFree(b);
     return FailCuda(ctx, "batch_create", e);
@@ -1093,6 +1104,12 @@ int yahkv_batch_prepare(yahkv_batch* b, int32_t horizon_steps, int32_t* layout_c
   for (int i = 0; i < n; ++i) {
     if (!ctx->host.live(b->seqs[i]) || ctx->host.len(b->seqs[i], 0) != b->lens[i])
       return Fail(ctx, YAHKV_ERR_ORDER, "batch_prepare: a sequence of the batch was freed or changed outside the batch");
+    // Tile formats: the layers of a sequence share one plan per step, so they must agree on the open-tile buffer
+    // (they do whenever every layer was appended with the same calls).
+    for (int l = 1; IsTileFmt(ctx->cfg.fmt) && l < ctx->cfg.n_layers; ++l)
+      if (ctx->host.open_cur(b->seqs[i], l) != ctx->host.open_cur(b->seqs[i], 0))
+        return Fail(ctx, YAHKV_ERR_ORDER, "batch_prepare: the layers of sequence " + std::to_string(b->seqs[i]) +
+                                              " were appended with different chunkings (their open tiles differ)");
     const std::int64_t need = (static_cast<std::int64_t>(b->lens[i]) + horizon_steps + kPageTokens - 1) / kPageTokens;
     if (need > ctx->cfg.max_pages_per_seq) return Fail(ctx, YAHKV_ERR_CAPACITY, "batch_prepare: horizon exceeds max_pages_per_seq");
     new_pages += std::max<std::int64_t>(need - ctx->host.n_pages(b->seqs[i]), 0);
@@ -1114,6 +1131,7 @@ int yahkv_batch_prepare(yahkv_batch* b, int32_t horizon_steps, int32_t* layout_c
     const int pages = (b->lens[i] + horizon_steps + kPageTokens - 1) / kPageTokens;
     BatchSeq r{};
     r.seq_row = b->seqs[i];
+    r.open_cur = IsTileFmt(ctx->cfg.fmt) ? ctx->host.open_cur(b->seqs[i], 0) : 0;
     r.n_units = std::min(std::max((pages + kBatchUnitPages - 1) / kBatchUnitPages, 1), ctx->cfg.max_splits);
     r.first_unit = total;
     total += r.n_units * kKvHeads;
@@ -1149,7 +1167,8 @@ int yahkv_batch_plan(yahkv_batch* b, void* stream) {
   if (b->total_units == 0) return Fail(ctx, YAHKV_ERR_ORDER, "batch_plan: call batch_prepare first");
   YAHKV_CUDA(ctx, LaunchBatchPlan(b->lens_dev, b->rows_dev, static_cast<int>(b->seqs.size()), ctx->tables_dev,
                                   ctx->cfg.max_pages_per_seq, kBatchUnitPages, ctx->cfg.num_pages, b->units_dev,
-                                  b->items_dev, b->slots_dev, StreamOf(ctx, stream)));
+                                  b->items_dev, b->slots_dev, b->vwork_dev, b->state_rows_dev, ctx->cfg.n_layers,
+                                  StreamOf(ctx, stream)));
   ctx->launches += 1;
   return YAHKV_OK;
 }
@@ -1166,7 +1185,14 @@ int yahkv_batch_decode_layer(yahkv_batch* b, int32_t layer, const void* k_dev, c
   if (b->total_units == 0) return Fail(ctx, YAHKV_ERR_ORDER, "batch_decode_layer: call batch_prepare first");
   cudaStream_t st = StreamOf(ctx, stream);
   const int n = static_cast<int>(b->seqs.size());
-  YAHKV_CUDA(ctx, LaunchAppend(ctx->pool, layer, n, b->slots_dev, k_dev, v_dev, st));
+  const bool tile_fmt = IsTileFmt(ctx->cfg.fmt);
+  if (tile_fmt) {
+    YAHKV_CUDA(ctx, (ctx->cfg.fmt == YAHKV_FMT_KV4A16 ? LaunchKv4AppendK : LaunchKv8AppendK)(
+                        ctx->pool, layer, n, b->slots_dev, b->state_rows_dev, layer, ctx->kmean_dev, k_dev, st));
+    YAHKV_CUDA(ctx, LaunchKv8AppendV(ctx->pool, layer, n, b->vwork_dev, layer, ctx->open_tiles_dev, v_dev, st));
+  } else {
+    YAHKV_CUDA(ctx, LaunchAppend(ctx->pool, layer, n, b->slots_dev, k_dev, v_dev, st));
+  }
   DecodeLaunch a{};
   a.kmap = &ctx->kmap, a.vmap = &ctx->vmap, a.pool = ctx->pool, a.layer = layer;
   a.tables_dev = ctx->tables_dev, a.table_stride = ctx->cfg.max_pages_per_seq;
@@ -1175,9 +1201,11 @@ int yahkv_batch_decode_layer(yahkv_batch* b, int32_t layer, const void* k_dev, c
   a.q_dev = q_dev, a.gate_dev = gate_dev, a.out_dev = out_dev, a.out_f32 = out_dtype == YAHKV_OUT_F32;
   a.scale_log2 = ctx->scale_log2;
   a.partial_acc = ctx->partial_acc, a.partial_ml = ctx->partial_ml, a.status_dev = ctx->status_dev;
-  YAHKV_CUDA(ctx, LaunchDecodePart(a, st));
+  YAHKV_CUDA(ctx, ctx->cfg.fmt == YAHKV_FMT_KV4A16   ? LaunchKv4DecodePart(a, ctx->open_tiles_dev, ctx->cfg.n_layers, st)
+                  : ctx->cfg.fmt == YAHKV_FMT_KV8A16 ? LaunchKv8DecodePart(a, ctx->open_tiles_dev, ctx->cfg.n_layers, st)
+                                                     : LaunchDecodePart(a, st));
   YAHKV_CUDA(ctx, LaunchDecodeCombine(a, st));
-  ctx->launches += 3;
+  ctx->launches += tile_fmt ? 4 : 3;
   return YAHKV_OK;
 }
 
