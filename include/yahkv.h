@@ -49,9 +49,9 @@ extern "C" {
  * (its dequantize pass reads the tile of each sequence's newest key from the open buffer, the others from the pools),
  * the host-buffer decode steps, yahkv_read_page / yahkv_write_page, yahkv_seq_set_kmean, yahkv_read_open_tile,
  * yahkv_snapshot_save / yahkv_snapshot_load (pages plus, per layer, the mean and the open tile), decode batches
- * (yahkv_batch_*; the layers of a sequence must have been appended with the same calls). Not supported (refused with
- * YAHKV_ERR_INVALID): the fused RoPE append, yahkv_export_token, head-sharded contexts, and yahkv_seq_set_len to
- * anything but 0. */
+ * (yahkv_batch_*; the layers of a sequence must have been appended with the same calls), yahkv_rope_append (the RoPE
+ * kernel leaves fp16 rows for the format's own append kernels). Not supported (refused with YAHKV_ERR_INVALID):
+ * yahkv_export_token, yahkv_append_slots, head-sharded contexts, and yahkv_seq_set_len to anything but 0. */
 #define YAHKV_FMT_KV8A16 2
 /* Its 4-bit sibling kv4a16 (engine/gpu/loom/tools/gen_kvq.py:288-463, :474-660 with 4-bit V), same pages, tiles, open
  * tile, mean and supported calls as YAHKV_FMT_KV8A16:

@@ -193,3 +193,47 @@ def test_chunked_prefill_attention():
     assert err <= 2e-3 and err / np.abs(want).max() < 1e-4, err
     cache.close()
 
+
+
+@pytest.mark.parametrize("fmt", [yahkv.FMT_KV8A16, yahkv.FMT_KV4A16])
+def test_fused_rope_append_is_rope_then_append(fmt):
+    """yahkv_rope_append on the tile formats == the oracle's RMSNorm + RoPE (rounded to fp16) followed by the format's
+    own append, bit for bit: q_out halves, pool codes, pairs, the open tile. Two sequences, a chunk then single tokens."""
+    rng = np.random.default_rng(13)
+    num_pages, eps = 12, 1e-6
+    Pool = O.Kv8Pool if fmt == yahkv.FMT_KV8A16 else O.Kv4Pool
+    cache = yahkv.KvCache(n_layers=2, num_pages=num_pages, fmt=fmt, max_seqs=2, max_pages_per_seq=5, max_batch_tokens=512)
+    pool = Pool(num_pages)
+    qw = (1.0 + 0.2 * rng.standard_normal(256)).astype(np.float32)
+    kw = (1.0 + 0.2 * rng.standard_normal(256)).astype(np.float32)
+    seqs = [cache.seq_create(), cache.seq_create()]
+    states = []
+    for s in seqs:
+        cache.seq_reserve(s, 300)
+        m = (0.5 * rng.standard_normal((4, 256))).astype(np.float32)
+        cache.seq_set_kmean(s, m)
+        states.append(pool.new_sequence(m))
+    calls = [(np.array([seqs[0]] * 130 + [seqs[1]] * 77, np.int32), np.concatenate([np.arange(130), np.arange(77)]))]
+    calls += [(np.array(seqs, np.int32), np.array([130 + i, 77 + i])) for i in range(5)]
+    for ids, pos in calls:
+        n = len(ids)
+        q = (rng.standard_normal((n, 24, 256)) * 2).astype(np.float32)
+        k = (rng.standard_normal((n, 4, 256)) * 3).astype(np.float32)
+        v = rng.standard_normal((n, 4, 256)).astype(np.float32)
+        q_out = torch.zeros((n, 24, 256), dtype=torch.float16, device="cuda")
+        torch.cuda.synchronize()
+        cache.rope_append(1, ids, pos, dev(q), dev(k), dev(v), dev(qw), dev(kw), eps, q_out)
+        cache.sync()
+        want_q = O.rope_rows(q, qw, eps, np.repeat(pos, 24))
+        assert np.array_equal(q_out.cpu().numpy().view(np.uint16).reshape(-1, 256), want_q.view(np.uint16))
+        k16 = O.rope_rows(k, kw, eps, np.repeat(pos, 4)).reshape(n, 4, 256)
+        v16 = v.astype(np.float16)
+        for s, st in zip(seqs, states):
+            sel = ids == s
+            pool.append(cache.seq_table(s), int(pos[sel][0]), k16[sel], v16[sel], *st)
+    assert_pools(cache, 1, pool)
+    for s, st, n in zip(seqs, states, (135, 82)):
+        used = n - 16 * ((n - 1) // 16)
+        assert np.array_equal(cache.read_open_tile(s, 1).view(np.uint16)[:, :, :used], st[0][:, :, :used])
+        assert cache.seq_len(s, 1) == n
+    cache.close()

@@ -168,7 +168,8 @@ cudaError_t LaunchAppend(const PoolView& pool, int layer, int n_tokens, const st
 cudaError_t LaunchRopeAppend(const PoolView& pool, int layer, int n_tokens, const std::int64_t* slots_dev,
                              const std::int32_t* positions_dev, const float* q_dev, const float* k_dev,
                              const float* v_dev, const float* q_weight_dev, const float* k_weight_dev, float eps,
-                             const float2* rope_tab_dev, int rope_rows, void* q_out_dev, cudaStream_t stream);
+                             const float2* rope_tab_dev, int rope_rows, void* q_out_dev, void* kv16_out_dev,
+                             cudaStream_t stream);
 
 struct DecodeLaunch {
   const CUtensorMap* kmap;  // host pointers to the encoded maps (passed by value to the kernel)

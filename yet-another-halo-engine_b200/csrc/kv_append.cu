@@ -144,7 +144,7 @@ __global__ void __launch_bounds__(kRopeThreads)
                      const std::int32_t* __restrict__ positions, const float* __restrict__ q_in,
                      const float* __restrict__ k_in, const float* __restrict__ v_in, const float* __restrict__ q_weight,
                      const float* __restrict__ k_weight, float eps, const float2* __restrict__ rope_tab, int rope_rows,
-                     __half* __restrict__ q_out) {
+                     __half* __restrict__ q_out, __half* __restrict__ kv16_out) {
   const int token = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool is_q = warp < kQHeads, is_v = warp >= kQHeads + kKvHeads;
@@ -191,17 +191,25 @@ __global__ void __launch_bounds__(kRopeThreads)
         *reinterpret_cast<const uint4*>(hx);
     return;
   }
-  const std::int64_t slot = slots[token];
-  if (slot < 0 || !pool.OwnsKvHead(h)) return;  // padding token, or a head another context holds
-  std::int64_t page = slot / kPageTokens;
-  const int tok = static_cast<int>(slot % kPageTokens);
-  page = min(max(page, static_cast<std::int64_t>(0)), static_cast<std::int64_t>(pool.num_pages - 1));
+  if constexpr (kFmt == kFmtKv8) {
+    // The tile formats quantize K against a mean and V per 16-key tile: this kernel leaves the fp16 rows (K after
+    // norm and RoPE) in a scratch, [2 sides][tokens][4][256], and the format's own append kernels take them from there.
+    __half* dst = kv16_out + ((static_cast<std::size_t>(is_v ? gridDim.x : 0) + token) * kKvHeads + h) * kHeadDim + lane * 8;
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(hx);
+    return;
+  } else {
+    const std::int64_t slot = slots[token];
+    if (slot < 0 || !pool.OwnsKvHead(h)) return;  // padding token, or a head another context holds
+    std::int64_t page = slot / kPageTokens;
+    const int tok = static_cast<int>(slot % kPageTokens);
+    page = min(max(page, static_cast<std::int64_t>(0)), static_cast<std::int64_t>(pool.num_pages - 1));
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 f = __half22float2(hx[i]);
-    x[2 * i] = f.x, x[2 * i + 1] = f.y;
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(hx[i]);
+      x[2 * i] = f.x, x[2 * i + 1] = f.y;
+    }
+    QuantizeStoreRow<kFmt>(pool, layer, page, tok, is_v ? 1 : 0, h, lane, x);
   }
-  QuantizeStoreRow<kFmt>(pool, layer, page, tok, is_v ? 1 : 0, h, lane, x);
 }
 
 }  // namespace
@@ -219,17 +227,23 @@ cudaError_t LaunchAppend(const PoolView& pool, int layer, int n_tokens, const st
 cudaError_t LaunchRopeAppend(const PoolView& pool, int layer, int n_tokens, const std::int64_t* slots_dev,
                              const std::int32_t* positions_dev, const float* q_dev, const float* k_dev,
                              const float* v_dev, const float* q_weight_dev, const float* k_weight_dev, float eps,
-                             const float2* rope_tab_dev, int rope_rows, void* q_out_dev, cudaStream_t stream) {
+                             const float2* rope_tab_dev, int rope_rows, void* q_out_dev, void* kv16_out_dev,
+                             cudaStream_t stream) {
   if (n_tokens <= 0) return cudaSuccess;
   auto* qo = static_cast<__half*>(q_out_dev);
-  if (pool.fmt == kFmtQ8)
+  auto* kv = static_cast<__half*>(kv16_out_dev);
+  if (IsTileFmt(pool.fmt))
+    RopeAppendKernel<kFmtKv8><<<n_tokens, kRopeThreads, 0, stream>>>(pool, layer, slots_dev, positions_dev, q_dev, k_dev,
+                                                                     v_dev, q_weight_dev, k_weight_dev, eps, rope_tab_dev,
+                                                                     rope_rows, qo, kv);
+  else if (pool.fmt == kFmtQ8)
     RopeAppendKernel<kFmtQ8><<<n_tokens, kRopeThreads, 0, stream>>>(pool, layer, slots_dev, positions_dev, q_dev, k_dev,
                                                                     v_dev, q_weight_dev, k_weight_dev, eps, rope_tab_dev,
-                                                                    rope_rows, qo);
+                                                                    rope_rows, qo, kv);
   else
     RopeAppendKernel<kFmtQ4><<<n_tokens, kRopeThreads, 0, stream>>>(pool, layer, slots_dev, positions_dev, q_dev, k_dev,
                                                                     v_dev, q_weight_dev, k_weight_dev, eps, rope_tab_dev,
-                                                                    rope_rows, qo);
+                                                                    rope_rows, qo, kv);
   return cudaGetLastError();
 }
 

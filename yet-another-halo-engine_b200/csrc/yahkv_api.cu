@@ -118,6 +118,7 @@ struct yahkv_ctx {
   float2* rope_tab_dev = nullptr;
   int rope_rows = 0;
   std::int32_t* rope_pos_dev = nullptr;
+  std::uint16_t* rope_kv16_dev = nullptr;   // tile formats: fp16 [2 sides][tokens][4][256] out of the RoPE kernel
   std::vector<std::int32_t> rope_pos_scratch;
   int hst_next = 0;
   cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
@@ -289,7 +290,7 @@ void FreeDevice(yahkv_ctx* ctx) {
                   ctx->tiles_dev,   ctx->status_dev,  ctx->pseqs_dev, ctx->k16_dev, ctx->v16_dev,
                   ctx->merges_dev, ctx->part_acc_dev, ctx->part_ml_dev,
                   ctx->rope_tab_dev, ctx->rope_pos_dev, ctx->open_tiles_dev, ctx->kmean_dev, ctx->state_rows_dev,
-                  ctx->vwork_dev};
+                  ctx->vwork_dev,   ctx->rope_kv16_dev};
   for (void* p : ptrs)
     if (p != nullptr) cudaFree(p);
   for (cudaStream_t st : {ctx->h2d_stream, ctx->d2h_stream})
@@ -587,6 +588,30 @@ int yahkv_pages_free(const yahkv_ctx* ctx, int32_t* n) {
   return YAHKV_OK;
 }
 
+// The append of the tile formats once the slots are planned and uploaded. K: one row per token against its sequence's
+// mean. V: one work item per 16-key tile the call touches; the tile of each sequence's newest key also stays in fp16
+// (engine/gpu/loom/tools/gen_decode_attn.py:436-573). k_dev / v_dev: fp16 [n_tokens][4][256].
+static int TileAppend(yahkv_ctx* ctx, int layer, int n_tokens, const int32_t* seq_ids, const int64_t* positions,
+                      const void* k_dev, const void* v_dev, cudaStream_t st) {
+  ctx->host.PlanKv8Tiles(layer, n_tokens, seq_ids, positions, &ctx->vwork_scratch);
+  ctx->state_row_scratch.resize(static_cast<std::size_t>(n_tokens));
+  for (int i = 0; i < n_tokens; ++i)
+    ctx->state_row_scratch[static_cast<std::size_t>(i)] = seq_ids[i] * ctx->cfg.n_layers + layer;
+  if (int r = StagedUpload(ctx, ctx->state_rows_dev, ctx->state_row_scratch.data(), static_cast<std::size_t>(n_tokens) * 4, st); r != YAHKV_OK)
+    return r;
+  if (int r = StagedUpload(ctx, ctx->vwork_dev, ctx->vwork_scratch.data(), ctx->vwork_scratch.size() * sizeof(VTileWork), st);
+      r != YAHKV_OK)
+    return r;
+  TimedLaunch tl(ctx, YAHKV_KERNEL_APPEND, st);
+  YAHKV_CUDA(ctx, (ctx->cfg.fmt == YAHKV_FMT_KV4A16 ? LaunchKv4AppendK : LaunchKv8AppendK)(
+                      ctx->pool, layer, n_tokens, ctx->slots_dev, ctx->state_rows_dev, 0, ctx->kmean_dev, k_dev, st));
+  YAHKV_CUDA(ctx, LaunchKv8AppendV(ctx->pool, layer, static_cast<int>(ctx->vwork_scratch.size()), ctx->vwork_dev, 0,
+                                   ctx->open_tiles_dev, v_dev, st));
+  tl.End();
+  ctx->launches += 2;
+  return YAHKV_OK;
+}
+
 int yahkv_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int32_t* seq_ids, const int64_t* positions,
                  const void* k_dev, const void* v_dev, void* stream) {
   if (int r = RequireDevice(ctx, "append"); r != YAHKV_OK) return r;
@@ -599,27 +624,7 @@ int yahkv_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int32_t*
   if (int r = FlushTables(ctx, st); r != YAHKV_OK) return r;
   if (int r = StagedUpload(ctx, ctx->slots_dev, ctx->slot_scratch.data(), static_cast<std::size_t>(n_tokens) * 8, st); r != YAHKV_OK)
     return r;
-  if (IsTileFmt(ctx->cfg.fmt)) {
-    // K: one row per token against its sequence's mean. V: one work item per 16-key tile the call touches; the tile
-    // of each sequence's newest key also stays in fp16 (engine/gpu/loom/tools/gen_decode_attn.py:436-573).
-    ctx->host.PlanKv8Tiles(layer, n_tokens, seq_ids, positions, &ctx->vwork_scratch);
-    ctx->state_row_scratch.resize(static_cast<std::size_t>(n_tokens));
-    for (int i = 0; i < n_tokens; ++i)
-      ctx->state_row_scratch[static_cast<std::size_t>(i)] = seq_ids[i] * ctx->cfg.n_layers + layer;
-    if (int r = StagedUpload(ctx, ctx->state_rows_dev, ctx->state_row_scratch.data(), static_cast<std::size_t>(n_tokens) * 4, st); r != YAHKV_OK)
-      return r;
-    if (int r = StagedUpload(ctx, ctx->vwork_dev, ctx->vwork_scratch.data(), ctx->vwork_scratch.size() * sizeof(VTileWork), st);
-        r != YAHKV_OK)
-      return r;
-    TimedLaunch tl(ctx, YAHKV_KERNEL_APPEND, st);
-    YAHKV_CUDA(ctx, (ctx->cfg.fmt == YAHKV_FMT_KV4A16 ? LaunchKv4AppendK : LaunchKv8AppendK)(
-                        ctx->pool, layer, n_tokens, ctx->slots_dev, ctx->state_rows_dev, 0, ctx->kmean_dev, k_dev, st));
-    YAHKV_CUDA(ctx, LaunchKv8AppendV(ctx->pool, layer, static_cast<int>(ctx->vwork_scratch.size()), ctx->vwork_dev, 0,
-                                     ctx->open_tiles_dev, v_dev, st));
-    tl.End();
-    ctx->launches += 2;
-    return YAHKV_OK;
-  }
+  if (IsTileFmt(ctx->cfg.fmt)) return TileAppend(ctx, layer, n_tokens, seq_ids, positions, k_dev, v_dev, st);
   TimedLaunch tl(ctx, YAHKV_KERNEL_APPEND, st);
   YAHKV_CUDA(ctx, LaunchAppend(ctx->pool, layer, n_tokens, ctx->slots_dev, k_dev, v_dev, st));
   tl.End();
@@ -642,6 +647,8 @@ static int EnsureRopeTable(yahkv_ctx* ctx) {
     }
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->rope_tab_dev, tab.size(), false));
   YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->rope_pos_dev, static_cast<std::size_t>(ctx->cfg.max_batch_tokens), false));
+  if (IsTileFmt(ctx->cfg.fmt))   // fp16 K and V rows between the RoPE kernel and the tile appends
+    YAHKV_CUDA(ctx, DevAlloc(ctx, &ctx->rope_kv16_dev, static_cast<std::size_t>(ctx->cfg.max_batch_tokens) * 2 * kKvHeads * kHeadDim, false));
   YAHKV_CUDA(ctx, cudaMemcpy(ctx->rope_tab_dev, tab.data(), tab.size() * sizeof(float2), cudaMemcpyHostToDevice));
   ctx->rope_rows = rows;
   return YAHKV_OK;
@@ -651,7 +658,6 @@ int yahkv_rope_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int
                       const float* q_dev, const float* k_dev, const float* v_dev, const float* q_weight_dev,
                       const float* k_weight_dev, float eps, void* q_out_dev, void* stream) {
   if (int r = RequireDevice(ctx, "rope_append"); r != YAHKV_OK) return r;
-  if (IsTileFmt(ctx->cfg.fmt)) return Fail(ctx, YAHKV_ERR_INVALID, "rope_append: not available for YAHKV_FMT_KV8A16 / YAHKV_FMT_KV4A16");
   if (n_tokens > ctx->cfg.max_batch_tokens) return Fail(ctx, YAHKV_ERR_CAPACITY, "rope_append: more tokens than max_batch_tokens");
   if (n_tokens > 0 && (q_dev == nullptr || k_dev == nullptr || v_dev == nullptr || q_weight_dev == nullptr ||
                        k_weight_dev == nullptr || q_out_dev == nullptr))
@@ -672,9 +678,15 @@ int yahkv_rope_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int
     return r;
   TimedLaunch tl(ctx, YAHKV_KERNEL_APPEND, st);
   YAHKV_CUDA(ctx, LaunchRopeAppend(ctx->pool, layer, n_tokens, ctx->slots_dev, ctx->rope_pos_dev, q_dev, k_dev, v_dev,
-                                   q_weight_dev, k_weight_dev, eps, ctx->rope_tab_dev, ctx->rope_rows, q_out_dev, st));
+                                   q_weight_dev, k_weight_dev, eps, ctx->rope_tab_dev, ctx->rope_rows, q_out_dev,
+                                   ctx->rope_kv16_dev, st));
   tl.End();
   ctx->launches += 1;
+  if (IsTileFmt(ctx->cfg.fmt)) {   // the kernel left fp16 rows (K after norm and RoPE): the format's own appends take them
+    const std::uint16_t* k16 = ctx->rope_kv16_dev;
+    const std::uint16_t* v16 = k16 + static_cast<std::size_t>(n_tokens) * kKvHeads * kHeadDim;
+    return TileAppend(ctx, layer, n_tokens, seq_ids, positions, k16, v16, st);
+  }
   return YAHKV_OK;
 }
 
