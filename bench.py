@@ -77,13 +77,42 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 50 ms; started ahead of the warm-up (the tool takes a
-    moment to come up) and cut to the timed region by its own timestamps."""
+    """SM clock and throttle reasons of one GPU during the timed region. Read in-process through NVML (the library
+    nvidia-smi itself reads) every 5 ms by a thread, so that even a region of a few tens of milliseconds holds samples;
+    where the NVML binding is missing, `nvidia-smi -lms 50` in a child process stands in. Reading only: nothing is
+    set. Samples are cut to the timed region by their own time stamps."""
     Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
+    REASON_BITS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
 
     def __init__(self, gpu_index):
+        self.samples, self.max_mhz, self.thread, self.p, self.halt = [], None, None, None, False
+        try:
+            import threading
+            import pynvml
+            pynvml.nvmlInit()
+            try:     # the device this process computes on, whatever CUDA_VISIBLE_DEVICES did to the numbering
+                uuid = str(torch.cuda.get_device_properties(gpu_index).uuid)
+                handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+            except Exception:
+                handle = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+
+            def loop():
+                while not self.halt:
+                    try:
+                        mhz = pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
+                        bits = pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                        self.samples.append((time.time(), float(mhz), int(bits)))
+                    except Exception:
+                        pass
+                    time.sleep(0.005)
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         try:
             self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms",
@@ -93,6 +122,13 @@ class ClockSampler:
 
     def stop(self, t_begin=None, t_end=None):
         """t_begin / t_end: time.time() bounds of the timed region (None = keep every sample)."""
+        if self.thread is not None:
+            self.halt = True
+            self.thread.join(timeout=1.0)
+            rows = [r for r in self.samples if t_begin is None or t_begin <= r[0] <= t_end]
+            reasons = sorted({name for _, _, bits in rows for name, bit in self.REASON_BITS if bits & bit})
+            return {"sm_mhz": float(np.median([r[1] for r in rows])) if rows else None, "sm_max_mhz": self.max_mhz,
+                    "reasons": reasons, "samples": len(rows), "source": "nvml, every 5 ms"}
         if self.p is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.p.terminate()
@@ -129,7 +165,7 @@ class ClockSampler:
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None,
                 "sm_max_mhz": float(rows[0][2]) if rows and len(rows[0]) >= 3 else None,
-                "reasons": sorted(reasons), "samples": len(sm),
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi -lms 50",
                 **({"window": f"timed region widened by {widened} s on both sides to catch samples"} if widened else {})}
 
 
