@@ -201,3 +201,66 @@ def test_chunked_prefill_configuration_against_the_oracle():
     assert checked >= 16
     cache.close()
     print(f"chunked-prefill configuration: {checked} rows, worst max-abs error {worst:.2e}")
+
+
+@pytest.mark.parametrize("fmt", [yahkv.FMT_KV8A16, yahkv.FMT_KV4A16])
+def test_batch_decode_configuration_in_the_reference_formats(fmt):
+    """The benchmark batch's longest and shortest contexts and the configuration's maximum (32768) in the reference's
+    own cache formats: chunked fill with a per-sequence K mean, then two decode steps (append one token, attend) with
+    automatic, single and 64-way splits, every row against the float64 model over the oracle's own pools."""
+    lens_all = np.random.default_rng(0).integers(1024, 32768 + 1, 32)
+    lens = [int(lens_all.max()), int(lens_all.min()), 32768 - 2]
+    steps = 2
+    pages = [(n + steps + 63) // 64 for n in lens]
+    num_pages = sum(pages) + 9
+    rng = np.random.default_rng(4321 + fmt)
+    cache = yahkv.KvCache(n_layers=1, num_pages=num_pages, fmt=fmt, max_seqs=len(lens), max_pages_per_seq=max(pages) + 1)
+    pool = (O.Kv8Pool if fmt == yahkv.FMT_KV8A16 else O.Kv4Pool)(num_pages)
+    perm = rng.permutation(num_pages).astype(np.int32)
+    seqs, tables, states, off = [], [], [], 0
+    for i, n in enumerate(lens):
+        s = cache.seq_create()
+        table = perm[off:off + pages[i]].copy()
+        off += pages[i]
+        cache.seq_set_table(s, table)
+        m = (0.5 * rng.standard_normal((4, 256))).astype(np.float32)
+        cache.seq_set_kmean(s, m)
+        st = pool.new_sequence(m)
+        for c0 in range(0, n, 8192):
+            c1 = min(n, c0 + 8192)
+            K = (rng.standard_normal((c1 - c0, 4, 256), dtype=np.float32) + m).astype(np.float16)
+            V = rng.standard_normal((c1 - c0, 4, 256), dtype=np.float32).astype(np.float16)
+            cache.append(0, np.full(c1 - c0, s, np.int32), np.arange(c0, c1, dtype=np.int64), dev(K), dev(V))
+            pool.append(table, c0, K, V, *st)
+        seqs.append(s), tables.append(table), states.append(st)
+    cache.sync()
+    b = len(lens)
+    cur = list(lens)
+    for step in range(steps):
+        k = rng.standard_normal((b, 4, 256)).astype(np.float16)
+        v = rng.standard_normal((b, 4, 256)).astype(np.float16)
+        q = rng.standard_normal((b, 24, 256)).astype(np.float16)
+        gate = rng.standard_normal((b, 24, 256)).astype(np.float32)
+        cache.append(0, seqs, cur, dev(k), dev(v))
+        for i in range(b):
+            pool.append(tables[i], cur[i], k[i:i + 1], v[i:i + 1], *states[i])
+        cur = [n + 1 for n in cur]
+        want = np.stack([pool.attend_decode_f64(tables[i], cur[i], q[i], states[i][0], gate[i]) for i in range(b)])
+        for n_splits in (0, 1, 64):
+            out = torch.full((b, 24, 256), float("nan"), device="cuda")
+            torch.cuda.synchronize()
+            cache.attend_decode(0, seqs, dev(q), out, gate=dev(gate), out_dtype=yahkv.OUT_F32, n_splits=n_splits)
+            cache.sync()
+            check(out.cpu().numpy(), want, (fmt, step, n_splits))
+    # the last page of every sequence, byte for byte (K rows of the decode steps, the V tiles they completed)
+    for i in range(b):
+        p = int(tables[i][(cur[i] - 1) // 64])
+        for side, codes, pairs in ((yahkv.SIDE_K, pool.kcodes, pool.kscales), (yahkv.SIDE_V, pool.vcodes, pool.vstats)):
+            got_c, got_p = cache.read_page(0, side, p)
+            if side == yahkv.SIDE_K:
+                n_tok = (cur[i] - 1) % 64 + 1
+                assert np.array_equal(got_c[:, :n_tok], codes[p][:, :n_tok]) and np.array_equal(got_p[:, :n_tok], pairs[p][:, :n_tok])
+            else:
+                n_tiles = ((cur[i] - 1) % 64 + 1) // 16       # complete tiles of the page
+                assert np.array_equal(got_c[:, :n_tiles], codes[p][:, :n_tiles]) and np.array_equal(got_p[:, :n_tiles], pairs[p][:, :n_tiles])
+    cache.close()
