@@ -760,7 +760,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="yahkv", choices=["yahkv", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers per step (16 = the configuration)")
-    ap.add_argument("--fmt", default="q8_0", choices=["q8_0", "q4_0", "kv8a16", "kv4a16"],
+    ap.add_argument("--fmt", default="q8_0", choices=["q8_0", "q4_0", "kv8a16", "kv4a16", "f16"],
                     help="cache format (q8_0 = the configuration; kv8a16 / kv4a16 = the reference's own formats)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "longctx", "churn", "headshard"],
                     help="decode = the batch-32 configuration (default, the headline metric); prefill = chunked "
@@ -810,7 +810,7 @@ def main():
     grow = total_steps + graph_steps + e2e_steps + 2
     pages = [(int(n) + grow + 63) // 64 for n in lens]
     num_pages = sum(pages) + 64
-    fmt = {"q8_0": yahkv.FMT_Q8_0, "q4_0": yahkv.FMT_Q4_0, "kv8a16": yahkv.FMT_KV8A16, "kv4a16": yahkv.FMT_KV4A16}[args.fmt]
+    fmt = {"q8_0": yahkv.FMT_Q8_0, "q4_0": yahkv.FMT_Q4_0, "kv8a16": yahkv.FMT_KV8A16, "kv4a16": yahkv.FMT_KV4A16, "f16": yahkv.FMT_F16}[args.fmt]
     cache = yahkv.KvCache(device=local_rank, n_layers=layers, num_pages=num_pages, fmt=fmt,
                           max_seqs=BATCH, max_pages_per_seq=max(pages) + 1, max_batch_tokens=8192)
     perm = rng.permutation(num_pages).astype(np.int32)
@@ -1030,7 +1030,7 @@ def main():
             line["roofline"]["traffic_note"] = ("(dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of "
                                                 "one ncu-captured launch of this workload, times this run's bytes "
                                                 "per launch")
-        if world == 1 and not args.no_cpu and args.fmt not in ("kv8a16", "kv4a16"):
+        if world == 1 and not args.no_cpu and args.fmt not in ("kv8a16", "kv4a16", "f16"):
             res = cpu_arm(args.fmt, lens=None if args.workload == "decode" else lens[:1])
             line["cpu_baseline"] = {"value": res["gbs"], "unit": UNIT, "cores": res["threads"], "kind": "port",
                                     "sample": res["sample"], "append_mtok_s": res["append_mtok_s_port"],

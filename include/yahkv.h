@@ -65,6 +65,12 @@ extern "C" {
  *      pools: codes [page][4][4 tiles][256][8 B], pairs [page][4][4][256][2] fp16.
  * 1408 B per token per layer. */
 #define YAHKV_FMT_KV4A16 3
+/* Unquantized fp16 pages, the reference's fp16 cache mode (dattn_kvappend / dattn_part,
+ * engine/gpu/loom/tools/gen_decode_attn.py:30-94, :97-335): K and V rows as they arrive, token-major on both sides
+ * (the reference keeps V transposed in 16-key tiles; here V is token-major like the GGUF formats), no scale pools.
+ * pools: [page][4][64 tokens][512 B] per side; 4096 B per token per layer. Every call of the GGUF formats works except
+ * yahkv_export_token (there is no block form: use yahkv_read_page; its scales argument receives nothing). */
+#define YAHKV_FMT_F16 4
 
 #define YAHKV_SIDE_K 0
 #define YAHKV_SIDE_V 1

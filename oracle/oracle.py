@@ -17,7 +17,7 @@ ORACLE_SO = os.path.join(_HERE, "libyahkv_oracle.so")
 REF_SO = os.path.join(_HERE, "_ref", "libyah_ref_codec.so")
 
 Q_HEADS, KV_HEADS, HEAD_DIM, PAGE_TOKENS, BLOCKS = 24, 4, 256, 64, 8
-FMT_Q8_0, FMT_Q4_0, FMT_KV8A16, FMT_KV4A16 = 0, 1, 2, 3
+FMT_Q8_0, FMT_Q4_0, FMT_KV8A16, FMT_KV4A16, FMT_F16 = 0, 1, 2, 3, 4
 GGML_Q4_0, GGML_Q8_0 = 2, 8  # ggml type ids the reference's Dequantize takes
 
 
@@ -45,7 +45,7 @@ def have_ref():
 
 
 def code_bytes(fmt):
-    return 256 if fmt == FMT_Q8_0 else 128
+    return 512 if fmt == FMT_F16 else (256 if fmt == FMT_Q8_0 else 128)
 
 
 def block_bytes(fmt):
@@ -117,7 +117,7 @@ class PagedPool:
         cb = code_bytes(fmt)
         self.kcodes = np.zeros((num_pages, KV_HEADS, PAGE_TOKENS, cb), np.uint8)
         self.vcodes = np.zeros_like(self.kcodes)
-        self.kscales = np.zeros((num_pages, KV_HEADS, PAGE_TOKENS, BLOCKS), np.uint16)
+        self.kscales = np.zeros((num_pages, KV_HEADS, PAGE_TOKENS, 0 if fmt == FMT_F16 else BLOCKS), np.uint16)
         self.vscales = np.zeros_like(self.kscales)
 
     def append(self, table, pos0, k, v, threads=THREADS):

@@ -77,6 +77,12 @@ def check_appended_token(cache, layer, seq, pos, k_row, v_row):
         want_c, want_s = quant(np.asarray(k_row, np.float16), np.zeros((4, 256), np.float32))
         tok = int(pos) % O.PAGE_TOKENS
         return bool(np.array_equal(codes[:, tok], want_c) and np.array_equal(scales[:, tok], want_s))
+    if cache.fmt == O.FMT_F16:        # fp16 pages hold the rows as they came
+        page, tok = int(cache.seq_table(seq)[int(pos) // O.PAGE_TOKENS]), int(pos) % O.PAGE_TOKENS
+        kc, _ = cache.read_page(layer, 0, page)
+        vc, _ = cache.read_page(layer, 1, page)
+        return bool(np.array_equal(kc[:, tok].view(np.float16), np.asarray(k_row, np.float16)) and
+                    np.array_equal(vc[:, tok].view(np.float16), np.asarray(v_row, np.float16)))
     kb, vb = cache.export_token(layer, seq, int(pos))
     k32 = np.asarray(k_row, np.float16).astype(np.float32)
     v32 = np.asarray(v_row, np.float16).astype(np.float32)

@@ -46,12 +46,12 @@ inline float HalfBitsToFloat(std::uint16_t h) { return static_cast<float>(std::b
 inline std::uint16_t FloatToHalfBits(float f) { return std::bit_cast<std::uint16_t>(static_cast<_Float16>(f)); }
 
 struct Geometry {
-  int fmt;          // 0 = q8_0, 1 = q4_0
+  int fmt;          // 0 = q8_0, 1 = q4_0, 4 = fp16 pages (rows as they are, no scales)
   int page_tokens;  // 64
   int num_pages;
-  int code_bytes() const { return fmt == 0 ? 256 : 128; }
+  int code_bytes() const { return fmt == 4 ? 512 : (fmt == 0 ? 256 : 128); }
   std::size_t record_codes() const { return static_cast<std::size_t>(page_tokens) * code_bytes(); }
-  std::size_t record_scales() const { return static_cast<std::size_t>(page_tokens) * kBlocks; }
+  std::size_t record_scales() const { return fmt == 4 ? 0 : static_cast<std::size_t>(page_tokens) * kBlocks; }
 };
 
 // One 32-value block -> int8 codes + fp16 scale, exactly as QuantizeQ8_0: d = amax / 127 (f32 divide),
@@ -101,6 +101,12 @@ void DecodeRow(const Geometry& g, const std::uint8_t* codes, const std::uint16_t
   const std::int64_t page = slot / g.page_tokens, tok = slot % g.page_tokens;
   const std::size_t rec = static_cast<std::size_t>(page) * kKvHeads + h;
   const std::uint8_t* c = codes + rec * g.record_codes() + static_cast<std::size_t>(tok) * g.code_bytes();
+  if (g.fmt == 4) {   // fp16 pages (the reference's fp16 pools, gen_decode_attn.py:4-6, :296-303: f16 widened to f32)
+    std::uint16_t hbits[kHeadDim];
+    std::memcpy(hbits, c, sizeof(hbits));
+    for (int i = 0; i < kHeadDim; ++i) y[i] = HalfBitsToFloat(hbits[i]);
+    return;
+  }
   const std::uint16_t* s = scales + rec * g.record_scales() + static_cast<std::size_t>(tok) * kBlocks;
   for (int b = 0; b < kBlocks; ++b) {
     const float d = HalfBitsToFloat(s[b]);
@@ -243,6 +249,10 @@ void yahkv_oracle_append_slots(int fmt, int page_tokens, int num_pages, std::uin
       for (int i = 0; i < kHeadDim; ++i) row[i] = HalfBitsToFloat(src[i]);  // exact widening
       const std::size_t rec = static_cast<std::size_t>(page) * kKvHeads + h;
       std::uint8_t* c = codes + rec * g.record_codes() + static_cast<std::size_t>(tok) * g.code_bytes();
+      if (fmt == 4) {   // fp16 pages: the row as it came
+        std::memcpy(c, src, kHeadDim * 2);
+        continue;
+      }
       std::uint16_t* s = scales + rec * g.record_scales() + static_cast<std::size_t>(tok) * kBlocks;
       for (int b = 0; b < kBlocks; ++b) {
         if (fmt == 0)

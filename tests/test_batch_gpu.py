@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 LAYERS = 2
 
 
-FORMATS = [yahkv.FMT_Q8_0, yahkv.FMT_KV8A16, yahkv.FMT_KV4A16]
+FORMATS = [yahkv.FMT_Q8_0, yahkv.FMT_KV8A16, yahkv.FMT_KV4A16, yahkv.FMT_F16]
 
 
 def twin_caches(lens, seed, extra_tokens, fmt=yahkv.FMT_Q8_0):

@@ -1,4 +1,4 @@
-"""Randomised decode attention over all four cache formats: many small batches with ragged lengths (1 token up to a
+"""Randomised decode attention over all five cache formats: many small batches with ragged lengths (1 token up to a
 dozen pages, lengths on and around tile and page edges), shuffled tables, every split count from one unit per sequence
 to more units than pages, with and without the gate, each output row against the float64 oracle over the pools the
 oracle itself filled (appends byte-exact). Bars: 2e-3 max-abs and 1e-4 of the largest output
@@ -12,7 +12,7 @@ import yahkv
 from gpu_util import dev
 
 pytestmark = pytest.mark.gpu
-FORMATS = [yahkv.FMT_Q8_0, yahkv.FMT_Q4_0, yahkv.FMT_KV8A16, yahkv.FMT_KV4A16]
+FORMATS = [yahkv.FMT_Q8_0, yahkv.FMT_Q4_0, yahkv.FMT_KV8A16, yahkv.FMT_KV4A16, yahkv.FMT_F16]
 EDGES = [1, 2, 15, 16, 17, 31, 32, 33, 63, 64, 65, 127, 128, 129, 191, 192, 193, 255, 256, 257]
 
 

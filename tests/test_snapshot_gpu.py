@@ -18,7 +18,7 @@ def attend(cache, layer, seqs, q):
     return out.cpu().numpy()
 
 
-@pytest.mark.parametrize("fmt", [yahkv.FMT_Q8_0, yahkv.FMT_Q4_0, yahkv.FMT_KV8A16, yahkv.FMT_KV4A16])
+@pytest.mark.parametrize("fmt", [yahkv.FMT_Q8_0, yahkv.FMT_Q4_0, yahkv.FMT_KV8A16, yahkv.FMT_KV4A16, yahkv.FMT_F16])
 def test_snapshot_round_trip_onto_other_pages(tmp_path, fmt):
     rng = np.random.default_rng(51)
     a = yahkv.KvCache(n_layers=2, num_pages=12, fmt=fmt, max_seqs=3, max_pages_per_seq=6)

@@ -26,6 +26,9 @@ constexpr int kFmtKv8 = 2;
 // 32-dim group with an (16 s, lo - 16 s) pair; V 15 levels per (tile, channel) with a (16 sf, cf - 23 sf) pair
 // (kv4a16.cu).
 constexpr int kFmtKv4 = 3;
+// Unquantized fp16 pages, the reference's fp16 cache mode (engine/gpu/loom/tools/gen_decode_attn.py:30-94, :97-335):
+// K and V rows as they arrive, token-major on both sides, no scale pools (decode_f16.cu).
+constexpr int kFmtF16 = 4;
 constexpr int kTileKeys = 16;
 constexpr int kTilesPerPage = kPageTokens / kTileKeys;
 // The reference's own formats: V in 16-key tiles, an open fp16 tile and a K mean per (sequence, layer).
@@ -33,7 +36,9 @@ __host__ __device__ constexpr bool IsTileFmt(int fmt) { return fmt == kFmtKv8 ||
 
 // Bytes of one token row of one kv head on the K side (the rows of the K tensor map). The V side of a page record has
 // the same total size in every format (a tile format stores it as [tile][channel][16 or 8 bytes]).
-__host__ __device__ constexpr int CodeBytes(int fmt) { return fmt == kFmtQ4 || fmt == kFmtKv4 ? 128 : 256; }
+__host__ __device__ constexpr int CodeBytes(int fmt) {
+  return fmt == kFmtF16 ? 512 : (fmt == kFmtQ4 || fmt == kFmtKv4 ? 128 : 256);
+}
 // One page record of one kv head: codes then (in a separate pool) scales.
 __host__ __device__ constexpr int RecordCodeBytes(int fmt) { return kPageTokens * CodeBytes(fmt); }
 constexpr int kRecordScaleBytes = kPageTokens * kBlocksPerRow * 2;   // q8_0 / q4_0: 8 fp16 block scales per token
@@ -41,7 +46,8 @@ constexpr int kRecordScaleBytes = kPageTokens * kBlocksPerRow * 2;   // q8_0 / q
 // kv8a16 K holds 2 halves x an fp16 pair per token, kv4a16 K 8 groups x a pair; the V side of both holds an fp16 pair
 // per (tile, channel).
 __host__ __device__ constexpr int RecordScaleBytes(int fmt, int side) {
-  return !IsTileFmt(fmt) ? kRecordScaleBytes
+  return fmt == kFmtF16  ? 0
+         : !IsTileFmt(fmt) ? kRecordScaleBytes
          : side == 1     ? kTilesPerPage * kHeadDim * 2 * 2
                          : kPageTokens * (fmt == kFmtKv8 ? 2 : 8) * 2 * 2;
 }
@@ -192,6 +198,9 @@ struct DecodeLaunch {
   int* status_dev;          // sticky error word, 0 = ok
 };
 cudaError_t LaunchDecodePart(const DecodeLaunch& a, cudaStream_t stream);
+// fp16 pages (decode_f16.cu)
+cudaError_t LaunchF16DecodePart(const DecodeLaunch& a, cudaStream_t stream);
+cudaError_t ConfigureF16Kernels();
 
 // ---- kv8a16 (kv8a16.cu) ----
 // Per-sequence state of the format beyond the pools, per layer: two open-tile buffers [2][4 heads][256][16] fp16 (the

@@ -36,7 +36,13 @@ __device__ __forceinline__ void QuantizeStoreRow(const PoolView& pool, int layer
                           static_cast<std::size_t>(tok) * kBlocksPerRow;
   const int blk = lane >> 2, sub = lane & 3;
 
-  if constexpr (kFmt == kFmtQ8) {
+  if constexpr (kFmt == kFmtF16) {   // fp16 pages: the row as it came (x holds fp16 values exactly)
+    __half2 hx[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) hx[i] = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
+    *reinterpret_cast<uint4*>(codes + lane * 16) = *reinterpret_cast<const uint4*>(hx);
+    (void)scales, (void)blk, (void)sub;
+  } else if constexpr (kFmt == kFmtQ8) {
     float amax = 0.0F;
 #pragma unroll
     for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
@@ -221,6 +227,8 @@ cudaError_t LaunchAppend(const PoolView& pool, int layer, int n_tokens, const st
   const auto* v = static_cast<const __half*>(v_dev);
   if (pool.fmt == kFmtQ8)
     return LaunchChained(AppendKernel<kFmtQ8>, n_tokens, kAppendThreads, 0, stream, pool, layer, slots_dev, k, v);
+  if (pool.fmt == kFmtF16)
+    return LaunchChained(AppendKernel<kFmtF16>, n_tokens, kAppendThreads, 0, stream, pool, layer, slots_dev, k, v);
   return LaunchChained(AppendKernel<kFmtQ4>, n_tokens, kAppendThreads, 0, stream, pool, layer, slots_dev, k, v);
 }
 
@@ -234,6 +242,10 @@ cudaError_t LaunchRopeAppend(const PoolView& pool, int layer, int n_tokens, cons
   auto* kv = static_cast<__half*>(kv16_out_dev);
   if (IsTileFmt(pool.fmt))
     RopeAppendKernel<kFmtKv8><<<n_tokens, kRopeThreads, 0, stream>>>(pool, layer, slots_dev, positions_dev, q_dev, k_dev,
+                                                                     v_dev, q_weight_dev, k_weight_dev, eps, rope_tab_dev,
+                                                                     rope_rows, qo, kv);
+  else if (pool.fmt == kFmtF16)
+    RopeAppendKernel<kFmtF16><<<n_tokens, kRopeThreads, 0, stream>>>(pool, layer, slots_dev, positions_dev, q_dev, k_dev,
                                                                      v_dev, q_weight_dev, k_weight_dev, eps, rope_tab_dev,
                                                                      rope_rows, qo, kv);
   else if (pool.fmt == kFmtQ8)

@@ -49,8 +49,9 @@ class KvHost {
     if (c.n_q_heads != kQHeads || c.n_kv_heads != kKvHeads || c.head_dim != kHeadDim)
       return bad("geometry must be 24 query heads, 4 kv heads, head_dim 256");
     if (c.page_tokens != kPageTokens) return bad("page_tokens must be 64");
-    if (c.fmt != YAHKV_FMT_Q8_0 && c.fmt != YAHKV_FMT_Q4_0 && c.fmt != YAHKV_FMT_KV8A16 && c.fmt != YAHKV_FMT_KV4A16)
-      return bad("fmt must be YAHKV_FMT_Q8_0, YAHKV_FMT_Q4_0, YAHKV_FMT_KV8A16 or YAHKV_FMT_KV4A16");
+    if (c.fmt != YAHKV_FMT_Q8_0 && c.fmt != YAHKV_FMT_Q4_0 && c.fmt != YAHKV_FMT_KV8A16 && c.fmt != YAHKV_FMT_KV4A16 &&
+        c.fmt != YAHKV_FMT_F16)
+      return bad("fmt must be YAHKV_FMT_Q8_0, YAHKV_FMT_Q4_0, YAHKV_FMT_KV8A16, YAHKV_FMT_KV4A16 or YAHKV_FMT_F16");
     if ((c.fmt == YAHKV_FMT_KV8A16 || c.fmt == YAHKV_FMT_KV4A16) && c.kv_head_count != 0 && c.kv_head_count != kKvHeads)
       return bad("YAHKV_FMT_KV8A16 / YAHKV_FMT_KV4A16 contexts hold all four kv heads");
     if (c.n_layers < 1 || c.n_layers > 1024) return bad("n_layers out of range");

@@ -72,6 +72,12 @@ __global__ void __launch_bounds__(kDequantThreads)
     const std::uint8_t* codes = (side == 0 ? pool.kcodes : pool.vcodes) + rec * RecordCodeBytes(kFmt);
     const std::uint16_t* scales = (side == 0 ? pool.kscales : pool.vscales) + rec * (kPageTokens * kBlocksPerRow);
     __half* out = (side == 0 ? k16 : v16) + out_row0 * kHeadDim;
+    if constexpr (kFmt == kFmtF16) {   // fp16 pages: a gather of the rows as they are
+      for (int gidx = threadIdx.x; gidx < kPageTokens * (kHeadDim / 8); gidx += kDequantThreads)
+        *reinterpret_cast<uint4*>(out + static_cast<std::size_t>(gidx >> 5) * kHeadDim + (gidx & 31) * 8) =
+            *reinterpret_cast<const uint4*>(codes + static_cast<std::size_t>(gidx) * 16);
+      continue;
+    }
     // thread -> 8 consecutive elements of a token row; 64 tokens x 32 groups = 2048 groups, 8 per thread
     for (int gidx = threadIdx.x; gidx < kPageTokens * (kHeadDim / 8); gidx += kDequantThreads) {
       const int tok = gidx >> 5, grp = gidx & 31;   // grp: elements 8 grp .. 8 grp + 7, block grp / 4
@@ -607,6 +613,9 @@ cudaError_t LaunchPrefillDequant(const PrefillLaunch& a, cudaStream_t stream) {
   if (a.pool.fmt == kFmtQ8)
     DequantPagesKernel<kFmtQ8><<<grid, kDequantThreads, 0, stream>>>(a.pool, a.layer, a.tables_dev, a.table_stride,
                                                                      a.seqs_dev, k16, v16);
+  else if (a.pool.fmt == kFmtF16)
+    DequantPagesKernel<kFmtF16><<<grid, kDequantThreads, 0, stream>>>(a.pool, a.layer, a.tables_dev, a.table_stride,
+                                                                      a.seqs_dev, k16, v16);
   else
     DequantPagesKernel<kFmtQ4><<<grid, kDequantThreads, 0, stream>>>(a.pool, a.layer, a.tables_dev, a.table_stride,
                                                                      a.seqs_dev, k16, v16);

@@ -275,6 +275,7 @@ int InitDevice(yahkv_ctx* ctx) {
   if (c.max_prefill_keys > 0)
     if (int r = ResizePrefillScratch(ctx, static_cast<std::int64_t>(c.max_prefill_keys) * kKvHeads); r != YAHKV_OK) return r;
   YAHKV_CUDA(ctx, ConfigureDecodeKernels());
+  if (c.fmt == YAHKV_FMT_F16) YAHKV_CUDA(ctx, ConfigureF16Kernels());
   YAHKV_CUDA(ctx, ConfigurePrefillKernels());
   YAHKV_CUDA(ctx, cudaDeviceSynchronize());
   ctx->has_device = true;
@@ -768,6 +769,7 @@ int yahkv_attend_decode(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int
   TimedLaunch tp(ctx, YAHKV_KERNEL_DECODE_PART, st);
   cudaError_t le = ctx->cfg.fmt == YAHKV_FMT_KV4A16 ? LaunchKv4DecodePart(a, ctx->open_tiles_dev, ctx->cfg.n_layers, st)
                    : kv8                            ? LaunchKv8DecodePart(a, ctx->open_tiles_dev, ctx->cfg.n_layers, st)
+                   : ctx->cfg.fmt == YAHKV_FMT_F16  ? LaunchF16DecodePart(a, st)
                                                     : LaunchDecodePart(a, st);
   tp.End();
   if (le == cudaSuccess) {
@@ -969,7 +971,8 @@ int yahkv_write_page(yahkv_ctx* ctx, int32_t layer, int32_t side, int32_t page, 
 
 int yahkv_export_token(yahkv_ctx* ctx, int32_t layer, int32_t seq, int64_t pos, void* k_blocks, void* v_blocks) {
   if (int r = RequireDevice(ctx, "export_token"); r != YAHKV_OK) return r;
-  if (IsTileFmt(ctx->cfg.fmt)) return Fail(ctx, YAHKV_ERR_INVALID, "export_token: YAHKV_FMT_KV8A16 / YAHKV_FMT_KV4A16 have no GGUF block form (use yahkv_read_page)");
+  if (IsTileFmt(ctx->cfg.fmt) || ctx->cfg.fmt == YAHKV_FMT_F16)
+    return Fail(ctx, YAHKV_ERR_INVALID, "export_token: only the GGUF formats have a block form (use yahkv_read_page)");
   if (layer < 0 || layer >= ctx->cfg.n_layers) return Fail(ctx, YAHKV_ERR_INVALID, "export_token: layer out of range");
   if (!ctx->host.live(seq)) return Fail(ctx, YAHKV_ERR_INVALID, "export_token: not a live sequence");
   if (pos < 0 || pos >= static_cast<std::int64_t>(ctx->host.n_pages(seq)) * kPageTokens)
@@ -1215,6 +1218,7 @@ int yahkv_batch_decode_layer(yahkv_batch* b, int32_t layer, const void* k_dev, c
   a.partial_acc = ctx->partial_acc, a.partial_ml = ctx->partial_ml, a.status_dev = ctx->status_dev;
   YAHKV_CUDA(ctx, ctx->cfg.fmt == YAHKV_FMT_KV4A16   ? LaunchKv4DecodePart(a, ctx->open_tiles_dev, ctx->cfg.n_layers, st)
                   : ctx->cfg.fmt == YAHKV_FMT_KV8A16 ? LaunchKv8DecodePart(a, ctx->open_tiles_dev, ctx->cfg.n_layers, st)
+                  : ctx->cfg.fmt == YAHKV_FMT_F16    ? LaunchF16DecodePart(a, st)
                                                      : LaunchDecodePart(a, st));
   YAHKV_CUDA(ctx, LaunchDecodeCombine(a, st));
   ctx->launches += tile_fmt ? 4 : 3;

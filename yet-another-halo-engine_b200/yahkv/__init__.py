@@ -17,7 +17,7 @@ _PKG_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB_PATH = os.path.join(_PKG_DIR, "libyahkv.so")
 INCLUDE_DIR = os.path.join(os.path.dirname(_PKG_DIR), "include")
 
-FMT_Q8_0, FMT_Q4_0, FMT_KV8A16, FMT_KV4A16 = 0, 1, 2, 3
+FMT_Q8_0, FMT_Q4_0, FMT_KV8A16, FMT_KV4A16, FMT_F16 = 0, 1, 2, 3, 4
 SIDE_K, SIDE_V = 0, 1
 OUT_F16, OUT_F32 = 0, 1
 KERNEL_APPEND, KERNEL_DECODE_PART, KERNEL_DECODE_COMBINE, KERNEL_PREFILL, KERNEL_PREFILL_DEQUANT = 0, 1, 2, 3, 4
@@ -28,7 +28,7 @@ Q_HEADS, KV_HEADS, HEAD_DIM, PAGE_TOKENS, BLOCKS = 24, 4, 256, 64, 8
 
 
 def code_bytes(fmt):
-    return 128 if fmt in (FMT_Q4_0, FMT_KV4A16) else 256
+    return 512 if fmt == FMT_F16 else (128 if fmt in (FMT_Q4_0, FMT_KV4A16) else 256)
 
 
 def bytes_per_token(fmt):
@@ -37,11 +37,15 @@ def bytes_per_token(fmt):
         return KV_HEADS * (256 + 8) + KV_HEADS * (256 + 64)
     if fmt == FMT_KV4A16:     # K: 128 B + 8 pairs per head; V: 128 B + a sixteenth of 256 pairs per head
         return KV_HEADS * (128 + 32) + KV_HEADS * (128 + 64)
+    if fmt == FMT_F16:        # fp16 rows, no scales
+        return 2 * KV_HEADS * 512
     return 2 * KV_HEADS * (code_bytes(fmt) + BLOCKS * 2)
 
 
 def page_shapes(fmt, side):
     """(codes shape, scales shape) of one page record as yahkv_read_page returns it."""
+    if fmt == FMT_F16:
+        return (KV_HEADS, PAGE_TOKENS, 512), (KV_HEADS, PAGE_TOKENS, 0)
     if fmt not in (FMT_KV8A16, FMT_KV4A16):
         return (KV_HEADS, PAGE_TOKENS, code_bytes(fmt)), (KV_HEADS, PAGE_TOKENS, BLOCKS)
     wide = fmt == FMT_KV8A16
