@@ -45,6 +45,7 @@
 
 #include <cmath>
 
+#include "decode_ring.cuh"
 #include "kernels.cuh"
 #include "ptx.cuh"
 
@@ -77,10 +78,7 @@ struct StageLayout {
   static constexpr int kBytes = kVsOff + kRecordScaleBytes;  // 34816 (q8_0) or 18432 (q4_0), a multiple of 1024
   static constexpr int kStages = kFmt == kFmtQ8 ? YAHKV_Q8_STAGES : YAHKV_Q4_STAGES;
 };
-// Cross-warp merge scratch at the end of a unit: per warp acc [6][kMergeStride] f32 and (m, l) [8][2].
-constexpr int kMergeStride = kHeadDim + 8;
-constexpr int kMergeGroupFloats = kGroup * kMergeStride + 16;
-constexpr int kMergeBytes = kWarps * kMergeGroupFloats * 4;
+constexpr int kMergeBytes = kWarps * kDecodeMergeWarpFloats * 4;   // the merge scratch at the end of a unit
 
 // fp16 number i (0..3) of four packed in a uint2, widened to f32. i is a compile-time constant after unrolling.
 __device__ __forceinline__ float ScaleOf(const uint2& v, int i) {
@@ -207,7 +205,7 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
     for (int i = 0; i < L::kStages && i < n_pages; ++i) issue(i, __ldg(row + i));
   }
 
-  const int g = lane >> 2, t = lane & 3;
+  const int t = lane & 3;
   // Query planes through shared memory. Warp h < 6 quantizes head h of the group: lane l holds dims 8 l .. 8 l + 7
   // (block l / 4, elements 8 (l % 4) .. + 7 of it). q16 = rint(q * 32000 / amax), hi = (q16 + 128) >> 8,
   // lo = q16 - 256 hi in [-128, 127]. The A operand of block b for lane (g = head, t) is four registers:
@@ -288,35 +286,10 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
   for (int i = par; i < n_pages; i += kPageSets) {
     const int s = i % L::kStages;    // ring stage of page i
     const int gen = i / L::kStages;  // fills of that stage before this page's
-    const std::uint32_t phase = static_cast<std::uint32_t>(gen) & 1U;   // parity of the mbarrier phase that fills it
     // Table entry of the page that will take this stage next, fetched a whole iteration before it is needed.
     std::int32_t refill_page = 0;
     if (lane == 0 && i + L::kStages < n_pages) refill_page = __ldg(row + i + L::kStages);
-    // A wait that gives up does not stop the warp half-way through a unit: it stops waiting, raises the CTA's abort
-    // flag so that nothing more is fetched, finishes on whatever the ring holds, and the status word marks the call's
-    // results invalid.
-    // The mbarrier wait names its phase by parity only, so it is safe only for a warp that is not a whole phase ahead
-    // of the barrier. A page's stage is refilled by the OTHER page set, whose progress this warp does not otherwise
-    // depend on, so the warp first makes sure (a bounded poll of the stage's fill counter, almost always true at
-    // once) that the fill it wants has at least been issued; from then on the parity is unambiguous.
-    if (alive) {
-      const int need = gen + 1;
-      volatile int* fills = fill_cnt + s;
-      bool ok = *abort_flag == 0;
-      if (ok && *fills < need) {
-        const std::uint64_t t0 = GlobalTimerNs();
-        while (*fills < need) {
-          if (*abort_flag != 0 || GlobalTimerNs() - t0 > kWaitLimitNs) {
-            ok = false;
-            break;
-          }
-        }
-      }
-      if (!ok || !__all_sync(0xFFFFFFFFU, MbarWait(&full_bar[s], phase))) {
-        alive = false;
-        *abort_flag = 1;
-      }
-    }
+    alive = RingWait(alive, fill_cnt + s, &full_bar[s], gen, abort_flag);
     const std::uint8_t* st = ring + s * L::kBytes;
     const std::uint32_t k_base = SmemAddr(st + L::kKOff), v_base = SmemAddr(st + L::kVOff);
 
@@ -482,19 +455,8 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
     }
 
     // The last of the page's four warps to finish with the stage refills it (no warp ever waits for another one).
-    // The MMAs above consumed every ldmatrix result, so this warp's reads of the stage are complete.
-    __syncwarp();
-    int last = 0;
-    if (lane == 0) {
-      __threadfence_block();
-      last = atomicAdd(&done_cnt[s], 1) == kKeyGroups - 1;
-      if (last) {
-        done_cnt[s] = 0;
-        __threadfence_block();
-      }
-    }
-    last = __shfl_sync(0xFFFFFFFFU, last, 0);
-    if (last != 0 && i + L::kStages < n_pages) issue(s, __shfl_sync(0xFFFFFFFFU, refill_page, 0));
+    const bool last = RingRelease(&done_cnt[s], lane, kKeyGroups);
+    if (last && i + L::kStages < n_pages) issue(s, __shfl_sync(0xFFFFFFFFU, refill_page, 0));
   }
   if (!alive && lane == 0) atomicExch(status, kStatusWaitTimeout);
   l_run += __shfl_xor_sync(0xFFFFFFFFU, l_run, 1);
@@ -502,59 +464,10 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
 
   // Every stage has been consumed (or a wait gave up): the ring is free to hold the merge scratch.
   __syncthreads();
-  if (*abort_flag != 0) {   // the same value in every thread now
-    // On the way out after a wait gave up: the copies this CTA still has in flight get one more bounded wait each
-    // (the fill counters say which phase of which stage is outstanding), so that none lands in shared memory that
-    // is being reused. The unit's partial is still written; the status word invalidates the call.
-    if (threadIdx.x == 0)
-      for (int x = 0; x < L::kStages; ++x)
-        if (fill_cnt[x] > 0) MbarWait(&full_bar[x], static_cast<std::uint32_t>(fill_cnt[x] - 1) & 1U, 20000000ULL);
-    __syncthreads();
-  }
-  float* merge = reinterpret_cast<float*>(ring);
-  {
-    float* mine = merge + warp * kMergeGroupFloats;
-#pragma unroll
-    for (int c = 0; c < 16; ++c) {
-      // o_acc[c][0..3] = (dim 16c + 2g, head 2t), (dim 16c + 2g, head 2t+1), (dim 16c + 2g + 1, head 2t), (.., 2t+1)
-      if (2 * t < kGroup) {
-        *reinterpret_cast<float2*>(mine + (2 * t) * kMergeStride + 16 * c + 2 * g) =
-            make_float2(o_acc[c][0], o_acc[c][2]);
-        *reinterpret_cast<float2*>(mine + (2 * t + 1) * kMergeStride + 16 * c + 2 * g) =
-            make_float2(o_acc[c][1], o_acc[c][3]);
-      }
-    }
-    if (t == 0 && g < kGroup) {
-      float* ml = mine + kGroup * kMergeStride;
-      ml[2 * g] = m_run;
-      ml[2 * g + 1] = l_run;
-    }
-  }
-  __syncthreads();
-  {
-    const int tid = threadIdx.x;  // 0..255: one dim per thread per head
-    float* acc_out = partial_acc + static_cast<std::size_t>(u.partial) * kPartialAccFloats;
-    float* ml_out = partial_ml + static_cast<std::size_t>(u.partial) * kPartialMlFloats;
-#pragma unroll
-    for (int h = 0; h < kGroup; ++h) {
-      float mw[kWarps], M = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < kWarps; ++w) {
-        mw[w] = merge[w * kMergeGroupFloats + kGroup * kMergeStride + 2 * h];
-        M = fmaxf(M, mw[w]);
-      }
-      float a = 0.0F, lsum = 0.0F;
-#pragma unroll
-      for (int w = 0; w < kWarps; ++w) {   // a warp that saw no page has max -inf and weight 0
-        const float wgt = mw[w] == -INFINITY ? 0.0F : exp2f(mw[w] - M);
-        const float* src = merge + w * kMergeGroupFloats;
-        a = fmaf(wgt, src[h * kMergeStride + tid], a);
-        lsum = fmaf(wgt, src[kGroup * kMergeStride + 2 * h + 1], lsum);
-      }
-      acc_out[h * kHeadDim + tid] = a;
-      if (tid == 0) ml_out[2 * h] = M, ml_out[2 * h + 1] = lsum;
-    }
-  }
+  RingDrainAfterAbort(abort_flag, fill_cnt, full_bar, L::kStages);
+  MergeUnitAndStore<kWarps, true>(reinterpret_cast<float*>(ring), o_acc, m_run, l_run, warp, lane,
+                                  partial_acc + static_cast<std::size_t>(u.partial) * kPartialAccFloats,
+                                  partial_ml + static_cast<std::size_t>(u.partial) * kPartialMlFloats);
 }
 
 // Merge the units of one (batch row, query head): out = (sum w_i acc_i) / (sum w_i l_i) * sigmoid(gate) with

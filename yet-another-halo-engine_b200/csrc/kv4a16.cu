@@ -18,6 +18,7 @@
 
 #include <cmath>
 
+#include "decode_ring.cuh"
 #include "kernels.cuh"
 #include "ptx.cuh"
 
@@ -148,9 +149,7 @@ constexpr int kQSumOff = kQStepOff + 32;                           // [8 heads][
 constexpr int kAbortOff = kQSumOff + 8 * 8 * 4;
 constexpr int kSmemBytes = (kAbortOff + 4 + 127) / 128 * 128;
 static_assert(2 * (kSmemBytes + 1024) <= 228 * 1024, "two CTAs per SM");
-constexpr int kMergeStride = kHeadDim + 8;
-constexpr int kMergeWarpFloats = kGroup * kMergeStride + 16;
-static_assert(kWarps * kMergeWarpFloats * 4 <= kRingBytes, "the merge scratch aliases the ring");
+static_assert(kWarps * kDecodeMergeWarpFloats * 4 <= kRingBytes, "the merge scratch aliases the ring");
 constexpr float kLazyRescale = 4.0F;
 constexpr float kQSteps = 32000.0F;
 constexpr int kStatusSmemMisaligned = 2;
@@ -320,31 +319,9 @@ __global__ void __launch_bounds__(kThreads, 2)
   for (int i = par; i < n_pages; i += kPageSets) {
     const int s = i % kStages;
     const int gen = i / kStages;
-    const std::uint32_t phase = static_cast<std::uint32_t>(gen) & 1U;
     std::int32_t refill_page = 0;
     if (lane == 0 && i + kStages < n_pages) refill_page = __ldg(row + i + kStages);
-    // The mbarrier wait names its phase by parity only; the stage is refilled by the other page set, so the warp first
-    // makes sure (a bounded poll, almost always true at once) that the fill it wants has been issued. A wait that
-    // gives up raises the CTA's abort flag, the warp finishes on whatever the ring holds and the status word marks the
-    // call's results invalid.
-    if (alive) {
-      const int need = gen + 1;
-      volatile int* fills = fill_cnt + s;
-      bool ok = *abort_flag == 0;
-      if (ok && *fills < need) {
-        const std::uint64_t t0 = GlobalTimerNs();
-        while (*fills < need) {
-          if (*abort_flag != 0 || GlobalTimerNs() - t0 > kWaitLimitNs) {
-            ok = false;
-            break;
-          }
-        }
-      }
-      if (!ok || !__all_sync(0xFFFFFFFFU, MbarWait(&full_bar[s], phase))) {
-        alive = false;
-        *abort_flag = 1;
-      }
-    }
+    alive = RingWait(alive, fill_cnt + s, &full_bar[s], gen, abort_flag);
     const int tile = (u.page_begin + i) * kTilesPerPage + kw;
     if (tile <= cur_tile) {   // warp-uniform: tiles past the newest key hold nothing
       const std::uint32_t k_base = SmemAddr(smem + kKOff + s * kKBytes);
@@ -472,18 +449,8 @@ __global__ void __launch_bounds__(kThreads, 2)
 
     // The last of the page's four warps to finish with the stage refills it. The MMAs above consumed every shared
     // memory read of the stage, so this warp's reads are complete.
-    __syncwarp();
-    int last = 0;
-    if (lane == 0) {
-      __threadfence_block();
-      last = atomicAdd(&done_cnt[s], 1) == kKeyGroups - 1;
-      if (last) {
-        done_cnt[s] = 0;
-        __threadfence_block();
-      }
-    }
-    last = __shfl_sync(0xFFFFFFFFU, last, 0);
-    if (last != 0 && i + kStages < n_pages) issue(s, __shfl_sync(0xFFFFFFFFU, refill_page, 0));
+    const bool last = RingRelease(&done_cnt[s], lane, kKeyGroups);
+    if (last && i + kStages < n_pages) issue(s, __shfl_sync(0xFFFFFFFFU, refill_page, 0));
   }
   if (!alive && lane == 0) atomicExch(status, kStatusWaitTimeout);
   l_run += __shfl_xor_sync(0xFFFFFFFFU, l_run, 1);
@@ -491,56 +458,10 @@ __global__ void __launch_bounds__(kThreads, 2)
 
   // Every stage has been consumed (or a wait gave up): the ring is free to hold the merge scratch.
   __syncthreads();
-  if (*abort_flag != 0) {   // the same value in every thread now
-    // Copies still in flight get one more bounded wait each, so that none lands in shared memory that is being reused.
-    if (threadIdx.x == 0)
-      for (int x = 0; x < kStages; ++x)
-        if (fill_cnt[x] > 0) MbarWait(&full_bar[x], static_cast<std::uint32_t>(fill_cnt[x] - 1) & 1U, 20000000ULL);
-    __syncthreads();
-  }
-  float* merge = reinterpret_cast<float*>(smem);
-  {
-    float* mine = merge + warp * kMergeWarpFloats;
-#pragma unroll
-    for (int c = 0; c < 16; ++c) {
-      if (2 * t < kGroup) {
-        mine[(2 * t) * kMergeStride + 16 * c + g] = o_acc[c][0];
-        mine[(2 * t + 1) * kMergeStride + 16 * c + g] = o_acc[c][1];
-        mine[(2 * t) * kMergeStride + 16 * c + g + 8] = o_acc[c][2];
-        mine[(2 * t + 1) * kMergeStride + 16 * c + g + 8] = o_acc[c][3];
-      }
-    }
-    if (t == 0 && g < kGroup) {
-      float* ml = mine + kGroup * kMergeStride;
-      ml[2 * g] = m_run;
-      ml[2 * g + 1] = l_run;
-    }
-  }
-  __syncthreads();
-  {
-    const int tid = threadIdx.x;
-    float* acc_out = partial_acc + static_cast<std::size_t>(u.partial) * kPartialAccFloats;
-    float* ml_out = partial_ml + static_cast<std::size_t>(u.partial) * kPartialMlFloats;
-#pragma unroll
-    for (int h = 0; h < kGroup; ++h) {
-      float mw[kWarps], M = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < kWarps; ++w) {
-        mw[w] = merge[w * kMergeWarpFloats + kGroup * kMergeStride + 2 * h];
-        M = fmaxf(M, mw[w]);
-      }
-      float a = 0.0F, lsum = 0.0F;
-#pragma unroll
-      for (int w = 0; w < kWarps; ++w) {   // a warp that saw no tile has max -inf and weight 0
-        const float wgt = mw[w] == -INFINITY ? 0.0F : exp2f(mw[w] - M);
-        const float* src = merge + w * kMergeWarpFloats;
-        a = fmaf(wgt, src[h * kMergeStride + tid], a);
-        lsum = fmaf(wgt, src[kGroup * kMergeStride + 2 * h + 1], lsum);
-      }
-      acc_out[h * kHeadDim + tid] = a;
-      if (tid == 0) ml_out[2 * h] = M, ml_out[2 * h + 1] = lsum;
-    }
-  }
+  RingDrainAfterAbort(abort_flag, fill_cnt, full_bar, kStages);
+  MergeUnitAndStore<kWarps, false>(reinterpret_cast<float*>(smem), o_acc, m_run, l_run, warp, lane,
+                                     partial_acc + static_cast<std::size_t>(u.partial) * kPartialAccFloats,
+                                     partial_ml + static_cast<std::size_t>(u.partial) * kPartialMlFloats);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
