@@ -29,6 +29,7 @@
 
 #include <cmath>
 
+#include "decode_ring.cuh"
 #include "kernels.cuh"
 #include "ptx.cuh"
 
@@ -186,9 +187,6 @@ __global__ void __launch_bounds__(kHeadDim) Kv8AppendVKernel(PoolView pool, int 
 // the tile's sums: o += a d + b sum(p). The tile that holds the newest key is read in fp16 from the sequence's open
 // buffer (in the same key order), by plain loads: one tile per sequence and kv head.
 // ---------------------------------------------------------------------------------------------------------------
-// The wait / release / merge steps below are written out here although decode_ring.cuh holds them for the other
-// formats' kernels: with the shared inline functions this kernel's register allocation spills inside the tile loop
-// and it runs 18 % slower (273 against 231 us per layer), with the same source otherwise.
 constexpr int kKv8Stages = 3;
 constexpr int kKv8KeyGroups = 4;
 constexpr int kKv8PageSets = 2;
@@ -220,9 +218,7 @@ constexpr int kKv8QCorrOff = (kKv8QStepOff + 32 + 7) / 8 * 8;         // [2 halv
 constexpr int kKv8AbortOff = kKv8QCorrOff + 2 * 8 * 8;
 constexpr int kKv8SmemBytes = (kKv8AbortOff + 4 + 127) / 128 * 128;
 static_assert(2 * (kKv8SmemBytes + 1024) <= 228 * 1024, "two CTAs per SM");
-constexpr int kMergeStride = kHeadDim + 8;
-constexpr int kMergeWarpFloats = kGroup * kMergeStride + 16;
-static_assert(kKv8Warps * kMergeWarpFloats * 4 <= kKv8RingBytes, "the merge scratch aliases the ring");
+static_assert(kKv8Warps * kDecodeMergeWarpFloats * 4 <= kKv8RingBytes, "the merge scratch aliases the ring");
 constexpr float kLazyRescale = 4.0F;
 constexpr float kQSteps = 32000.0F;
 constexpr int kStatusSmemMisaligned = 2;
@@ -357,7 +353,7 @@ __global__ void __launch_bounds__(kKv8Threads, 2)
   const std::uint32_t qa_addr = SmemAddr(qfrag + (qlane << 2));
   // softmax scale x log2(e) x the head's query step x 1 / 256 (the K pair's first value is 256 s)
   const float score_scale = scale_log2 * q_step[qlane >> 2] * (1.0F / 256.0F);
-  const int2 corr0 = q_corr[qlane >> 2], corr1 = q_corr[8 + (qlane >> 2)];
+  const int2* my_corr = q_corr + (qlane >> 2);   // [half][head]: loaded at use, the loop has no registers to spare
 
   float o_acc[16][4];   // [c][0..3] = (channel 16c + g, head 2t), (16c + g, 2t+1), (16c + g + 8, 2t), (16c + g + 8, 2t+1)
 #pragma unroll
@@ -372,37 +368,13 @@ __global__ void __launch_bounds__(kKv8Threads, 2)
   const int lm_key = kw * kTileKeys + 4 * ((lane & 7) >> 1) + 2 * ((lane >> 3) & 1) + (lane & 1);
   const std::uint32_t lm0 = lm_key * 128 + (((lane >> 4) ^ (lm_key & 7)) << 4);
   const int cur_tile = (u.n_keys - 1) / kTileKeys;
-  const __half* open_buf = open_tiles + ((static_cast<std::size_t>(u.seq) * n_layers + layer) * 2 + (u.pad & 1)) * kOpenTileHalfs +
-                           static_cast<std::size_t>(u.kvh) * kHeadDim * kTileKeys;
 
   for (int i = par; i < n_pages; i += kKv8PageSets) {
     const int s = i % kKv8Stages;
     const int gen = i / kKv8Stages;
-    const std::uint32_t phase = static_cast<std::uint32_t>(gen) & 1U;
     std::int32_t refill_page = 0;
     if (lane == 0 && i + kKv8Stages < n_pages) refill_page = __ldg(row + i + kKv8Stages);
-    // The mbarrier wait names its phase by parity only; the stage is refilled by the other page set, so the warp first
-    // makes sure (a bounded poll, almost always true at once) that the fill it wants has been issued. A wait that
-    // gives up raises the CTA's abort flag, the warp finishes on whatever the ring holds and the status word marks the
-    // call's results invalid.
-    if (alive) {
-      const int need = gen + 1;
-      volatile int* fills = fill_cnt + s;
-      bool ok = *abort_flag == 0;
-      if (ok && *fills < need) {
-        const std::uint64_t t0 = GlobalTimerNs();
-        while (*fills < need) {
-          if (*abort_flag != 0 || GlobalTimerNs() - t0 > kWaitLimitNs) {
-            ok = false;
-            break;
-          }
-        }
-      }
-      if (!ok || !__all_sync(0xFFFFFFFFU, MbarWait(&full_bar[s], phase))) {
-        alive = false;
-        *abort_flag = 1;
-      }
-    }
+    alive = RingWait(alive, fill_cnt + s, &full_bar[s], gen, abort_flag);
     const int tile = (u.page_begin + i) * kTilesPerPage + kw;
     if (tile <= cur_tile) {   // warp-uniform: tiles past the newest key hold nothing
       const std::uint32_t k_base = SmemAddr(smem + kKv8KOff + s * kKv8KBytes);
@@ -411,7 +383,7 @@ __global__ void __launch_bounds__(kKv8Threads, 2)
       int acc[2][2][4];   // [key tile][half][hi col 2t, hi col 2t+1, lo col 2t, lo col 2t+1]
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
-        const int2 cr = hf == 0 ? corr0 : corr1;
+        const int2 cr = my_corr[8 * hf];
 #pragma unroll
         for (int kt = 0; kt < 2; ++kt) acc[kt][hf][0] = cr.x, acc[kt][hf][1] = cr.x, acc[kt][hf][2] = cr.y, acc[kt][hf][3] = cr.y;
 #pragma unroll
@@ -483,6 +455,8 @@ __global__ void __launch_bounds__(kKv8Threads, 2)
 
       // ---- O^T += V^T P^T: k-slots (2t, 2t+1) = keys 4t, 4t+1 and (2t+8, 2t+9) = keys 4t+2, 4t+3 ----
       if (tile == cur_tile) {   // the open tile, fp16 [channel][16 keys]
+        const __half* open_buf = open_tiles + ((static_cast<std::size_t>(u.seq) * n_layers + layer) * 2 + (u.pad & 1)) * kOpenTileHalfs +
+            static_cast<std::size_t>(u.kvh) * kHeadDim * kTileKeys;
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
           const uint2 r0 = *reinterpret_cast<const uint2*>(open_buf + (16 * c + g) * kTileKeys + 4 * t);
@@ -528,18 +502,8 @@ __global__ void __launch_bounds__(kKv8Threads, 2)
 
     // The last of the page's four warps to finish with the stage refills it. The MMAs above consumed every shared
     // memory read of the stage, so this warp's reads are complete.
-    __syncwarp();
-    int last = 0;
-    if (lane == 0) {
-      __threadfence_block();
-      last = atomicAdd(&done_cnt[s], 1) == kKv8KeyGroups - 1;
-      if (last) {
-        done_cnt[s] = 0;
-        __threadfence_block();
-      }
-    }
-    last = __shfl_sync(0xFFFFFFFFU, last, 0);
-    if (last != 0 && i + kKv8Stages < n_pages) issue(s, __shfl_sync(0xFFFFFFFFU, refill_page, 0));
+    const bool last = RingRelease(&done_cnt[s], lane, kKv8KeyGroups);
+    if (last && i + kKv8Stages < n_pages) issue(s, __shfl_sync(0xFFFFFFFFU, refill_page, 0));
   }
   if (!alive && lane == 0) atomicExch(status, kStatusWaitTimeout);
   l_run += __shfl_xor_sync(0xFFFFFFFFU, l_run, 1);
@@ -547,56 +511,10 @@ __global__ void __launch_bounds__(kKv8Threads, 2)
 
   // Every stage has been consumed (or a wait gave up): the ring is free to hold the merge scratch.
   __syncthreads();
-  if (*abort_flag != 0) {   // the same value in every thread now
-    // Copies still in flight get one more bounded wait each, so that none lands in shared memory that is being reused.
-    if (threadIdx.x == 0)
-      for (int x = 0; x < kKv8Stages; ++x)
-        if (fill_cnt[x] > 0) MbarWait(&full_bar[x], static_cast<std::uint32_t>(fill_cnt[x] - 1) & 1U, 20000000ULL);
-    __syncthreads();
-  }
-  float* merge = reinterpret_cast<float*>(smem);
-  {
-    float* mine = merge + warp * kMergeWarpFloats;
-#pragma unroll
-    for (int c = 0; c < 16; ++c) {
-      if (2 * t < kGroup) {
-        mine[(2 * t) * kMergeStride + 16 * c + g] = o_acc[c][0];
-        mine[(2 * t + 1) * kMergeStride + 16 * c + g] = o_acc[c][1];
-        mine[(2 * t) * kMergeStride + 16 * c + g + 8] = o_acc[c][2];
-        mine[(2 * t + 1) * kMergeStride + 16 * c + g + 8] = o_acc[c][3];
-      }
-    }
-    if (t == 0 && g < kGroup) {
-      float* ml = mine + kGroup * kMergeStride;
-      ml[2 * g] = m_run;
-      ml[2 * g + 1] = l_run;
-    }
-  }
-  __syncthreads();
-  {
-    const int tid = threadIdx.x;
-    float* acc_out = partial_acc + static_cast<std::size_t>(u.partial) * kPartialAccFloats;
-    float* ml_out = partial_ml + static_cast<std::size_t>(u.partial) * kPartialMlFloats;
-#pragma unroll
-    for (int h = 0; h < kGroup; ++h) {
-      float mw[kKv8Warps], M = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < kKv8Warps; ++w) {
-        mw[w] = merge[w * kMergeWarpFloats + kGroup * kMergeStride + 2 * h];
-        M = fmaxf(M, mw[w]);
-      }
-      float a = 0.0F, lsum = 0.0F;
-#pragma unroll
-      for (int w = 0; w < kKv8Warps; ++w) {   // a warp that saw no tile has max -inf and weight 0
-        const float wgt = mw[w] == -INFINITY ? 0.0F : exp2f(mw[w] - M);
-        const float* src = merge + w * kMergeWarpFloats;
-        a = fmaf(wgt, src[h * kMergeStride + tid], a);
-        lsum = fmaf(wgt, src[kGroup * kMergeStride + 2 * h + 1], lsum);
-      }
-      acc_out[h * kHeadDim + tid] = a;
-      if (tid == 0) ml_out[2 * h] = M, ml_out[2 * h + 1] = lsum;
-    }
-  }
+  RingDrainAfterAbort(abort_flag, fill_cnt, full_bar, kKv8Stages);
+  MergeUnitAndStore<kKv8Warps, false>(reinterpret_cast<float*>(smem), o_acc, m_run, l_run, warp, lane,
+                                      partial_acc + static_cast<std::size_t>(u.partial) * kPartialAccFloats,
+                                      partial_ml + static_cast<std::size_t>(u.partial) * kPartialMlFloats);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
