@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(kHeadDim) Kv8AppendVKernel(PoolView pool, int 
 // consecutive keys, and their scale pairs two 16-byte loads.
 // Values: v = a (u - 128) + b per (tile, channel), a = S / 256, b = 1.5 S + C'. u - 128 enters the f16 MMA as exact
 // integers against the weights' hi and lo parts (both into one fresh accumulator); a and b are applied in fp32 to
-// the tile's sums: o += a d + b sum(p). The tile that holds the newest key is read in fp16 from the sequence's open
+// the tile's sums: o += a d + b sum(p) (with the codes entering as 1024 + u and b shifted to match). The tile that holds the newest key is read in fp16 from the sequence's open
 // buffer (in the same key order), by plain loads: one tile per sequence and kv head.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kKv8Stages = 3;
@@ -480,17 +480,19 @@ __global__ void __launch_bounds__(kKv8Threads, 2)
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
             const int c = 2 * cp + x;
-            std::uint32_t a0, a1, a2, a3;
-            Offset8x4ToHalf2(w[2 * x], a0, a2);       // bytes (0, 2) = keys 4t, 4t+1;  bytes (1, 3) = keys 4t+2, 4t+3
-            Offset8x4ToHalf2(w[2 * x + 1], a1, a3);
+            // bytes (0, 2) = keys 4t, 4t+1; bytes (1, 3) = keys 4t+2, 4t+3. A byte permuted under 0x64 is the f16
+            // 1024 + u: the offset is not subtracted here but joins the per-channel affine below
+            // (v = a (u - 128) + b = a (1024 + u) + (b - 1152 a), and b - 1152 a = C' - 3 S).
+            const std::uint32_t a0 = __byte_perm(w[2 * x], 0x64646464U, 0x4240), a2 = __byte_perm(w[2 * x], 0x64646464U, 0x4341);
+            const std::uint32_t a1 = __byte_perm(w[2 * x + 1], 0x64646464U, 0x4240), a3 = __byte_perm(w[2 * x + 1], 0x64646464U, 0x4341);
             float d[4];
             MmaF16Zero(d, a0, a1, a2, a3, p_hi[0], p_hi[1]);
             MmaF16(d, a0, a1, a2, a3, p_lo[0], p_lo[1]);
             const std::uint32_t s0 = vs[16 * c], s1 = vs[16 * c + 8];
             const float2 st0 = __half22float2(*reinterpret_cast<const __half2*>(&s0));
             const float2 st1 = __half22float2(*reinterpret_cast<const __half2*>(&s1));
-            const float sa0 = st0.x * (1.0F / 256.0F), sb0 = fmaf(1.5F, st0.x, st0.y);
-            const float sa1 = st1.x * (1.0F / 256.0F), sb1 = fmaf(1.5F, st1.x, st1.y);
+            const float sa0 = st0.x * (1.0F / 256.0F), sb0 = fmaf(-3.0F, st0.x, st0.y);
+            const float sa1 = st1.x * (1.0F / 256.0F), sb1 = fmaf(-3.0F, st1.x, st1.y);
             o_acc[c][0] = fmaf(sa0, d[0], fmaf(sb0, ps0, o_acc[c][0]));
             o_acc[c][1] = fmaf(sa0, d[1], fmaf(sb0, ps1, o_acc[c][1]));
             o_acc[c][2] = fmaf(sa1, d[2], fmaf(sb1, ps0, o_acc[c][2]));
