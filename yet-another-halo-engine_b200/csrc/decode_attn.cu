@@ -52,20 +52,38 @@
 namespace yahkv {
 namespace {
 
-// Resident CTAs per SM and ring depth per CTA (stage = one page of one kv head: 34 KB q8_0, 18 KB q4_0).
-#ifndef YAHKV_DECODE_CTAS
-#define YAHKV_DECODE_CTAS 2
+// The shape of a CTA per format: page sets (pages in work at a time; warp w takes the pages i with
+// i % kPageSets = w / 4), ring stages (a stage = one page of one kv head: 34 KB q8_0, 18 KB q4_0) and resident CTAs per
+// SM. q8_0 is bound by memory: two sets of four warps on a three-stage ring, two CTAs per SM. q4_0 is bound by
+// instruction latency, and more, smaller CTAs overlap their prologues and merges better: one set of four warps on a
+// two-stage ring, four CTAs per SM (measured on 8 x 131072 tokens: 275 us per layer against 295 with the q8_0 shape;
+// three CTAs with three stages 283, three CTAs with four stages 342).
+#ifndef YAHKV_Q8_PAGE_SETS
+#define YAHKV_Q8_PAGE_SETS 2
 #endif
 #ifndef YAHKV_Q8_STAGES
 #define YAHKV_Q8_STAGES 3
 #endif
+#ifndef YAHKV_Q8_CTAS
+#define YAHKV_Q8_CTAS 2
+#endif
+#ifndef YAHKV_Q4_PAGE_SETS
+#define YAHKV_Q4_PAGE_SETS 1
+#endif
 #ifndef YAHKV_Q4_STAGES
-#define YAHKV_Q4_STAGES 5
+#define YAHKV_Q4_STAGES 2
+#endif
+#ifndef YAHKV_Q4_CTAS
+#define YAHKV_Q4_CTAS 4
 #endif
 constexpr int kKeyGroups = 4;              // 16 keys of a page each
-constexpr int kPageSets = 2;               // pages in work at a time: warp w takes the pages of parity w / 4
-constexpr int kWarps = kPageSets * kKeyGroups;
-constexpr int kDecodeThreads = kWarps * 32;
+template <int kFmt>
+struct Shape {
+  static constexpr int kPageSets = kFmt == kFmtQ8 ? YAHKV_Q8_PAGE_SETS : YAHKV_Q4_PAGE_SETS;
+  static constexpr int kCtas = kFmt == kFmtQ8 ? YAHKV_Q8_CTAS : YAHKV_Q4_CTAS;
+  static constexpr int kWarps = kPageSets * kKeyGroups;
+  static constexpr int kThreads = kWarps * 32;
+};
 constexpr int kBoxBytes = 64 * 128;        // one swizzled TMA box: 64 token rows x 128 B
 
 template <int kFmt>
@@ -78,7 +96,6 @@ struct StageLayout {
   static constexpr int kBytes = kVsOff + kRecordScaleBytes;  // 34816 (q8_0) or 18432 (q4_0), a multiple of 1024
   static constexpr int kStages = kFmt == kFmtQ8 ? YAHKV_Q8_STAGES : YAHKV_Q4_STAGES;
 };
-constexpr int kMergeBytes = kWarps * kDecodeMergeWarpFloats * 4;   // the merge scratch at the end of a unit
 
 // fp16 number i (0..3) of four packed in a uint2, widened to f32. i is a compile-time constant after unrolling.
 __device__ __forceinline__ float ScaleOf(const uint2& v, int i) {
@@ -116,7 +133,7 @@ constexpr int kQfragBytes = kBlocksPerRow * kQLanes * 16;   // per 32-element bl
 template <int kFmt>
 struct SmemLayout {
   static constexpr int kRing = StageLayout<kFmt>::kStages * StageLayout<kFmt>::kBytes;
-  static_assert(kRing >= kMergeBytes, "the merge scratch aliases the ring");
+  static_assert(kRing >= Shape<kFmt>::kWarps * kDecodeMergeWarpFloats * 4, "the merge scratch of a unit's end aliases the ring");
   static constexpr int kQfragOff = kRing;
   static constexpr int kBarOff = kQfragOff + kQfragBytes;
   static constexpr int kCntOff = kBarOff + 8 * StageLayout<kFmt>::kStages;
@@ -136,7 +153,7 @@ constexpr int kStatusSmemMisaligned = 2;
 constexpr float kLazyRescale = 4.0F;
 
 template <int kFmt>
-__global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
+__global__ void __launch_bounds__(Shape<kFmt>::kThreads, Shape<kFmt>::kCtas)
     DecodePartKernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                      PoolView pool, int layer, const std::int32_t* __restrict__ tables, int table_stride,
                      const DecodeUnit* __restrict__ units, const __half* __restrict__ q, float scale_log2,
@@ -144,6 +161,7 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
   ChainedKernelEntry();
   using L = StageLayout<kFmt>;
   using S = SmemLayout<kFmt>;
+  constexpr int kPageSets = Shape<kFmt>::kPageSets, kWarps = Shape<kFmt>::kWarps;
   extern __shared__ __align__(1024) std::uint8_t smem_raw[];
   std::uint8_t* ring = smem_raw;
   std::uint32_t* qfrag = reinterpret_cast<std::uint32_t*>(smem_raw + S::kQfragOff);   // [8 blocks][24 lanes][4]
@@ -211,8 +229,8 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
   // lo = q16 - 256 hi in [-128, 127]. The A operand of block b for lane (g = head, t) is four registers:
   //   a0 = hi of elements 4t .. 4t+3, a1 = lo of the same, a2 = hi of elements 16+4t .. 16+4t+3, a3 = lo of those,
   // so that rows 0-5 of the MMA are the hi plane and rows 8-13 the lo plane of the six heads.
-  if (warp < kGroup) {
-    const __half* qrow = q + (static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + warp) * kHeadDim;
+  for (int hq = warp; hq < kGroup; hq += kWarps) {   // one head per warp (per pass, in a CTA of fewer than six warps)
+    const __half* qrow = q + (static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + hq) * kHeadDim;
     const uint4 raw = *reinterpret_cast<const uint4*>(qrow + 8 * lane);
     const __half2* hp = reinterpret_cast<const __half2*>(&raw);
     float x[8];
@@ -239,12 +257,12 @@ __global__ void __launch_bounds__(kDecodeThreads, YAHKV_DECODE_CTAS)
     const int reg = e0 < 16 ? 0 : 2, t0 = (e0 & 15) >> 2;
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
-      std::uint32_t* dst = qfrag + ((blk * kQLanes + warp * 4 + t0 + j) << 2) + reg;
+      std::uint32_t* dst = qfrag + ((blk * kQLanes + hq * 4 + t0 + j) << 2) + reg;
       dst[0] = hi_w[j];
       dst[1] = lo_w[j];
     }
     // q = step (256 hi + lo); q4_0 codes enter the MMA as 16 (n - 8), which the step absorbs
-    if (lane == 0) q_scale[warp] = (amax / kQSteps) * (kFmt == kFmtQ8 ? 1.0F : 0.0625F);
+    if (lane == 0) q_scale[hq] = (amax / kQSteps) * (kFmt == kFmtQ8 ? 1.0F : 0.0625F);
   }
   __syncthreads();   // barriers initialised, query planes visible
   const int qlane = lane < kQLanes ? lane : lane - 8;
@@ -545,10 +563,10 @@ cudaError_t LaunchDecodePart(const DecodeLaunch& a, cudaStream_t stream) {
   if (a.n_units <= 0 || a.n_seqs <= 0) return cudaSuccess;
   const auto* q = static_cast<const __half*>(a.q_dev);
   if (a.pool.fmt == kFmtQ8)
-    return LaunchChained(DecodePartKernel<kFmtQ8>, a.n_units, kDecodeThreads, DecodeSmemBytes<kFmtQ8>(), stream, *a.kmap,
+    return LaunchChained(DecodePartKernel<kFmtQ8>, a.n_units, Shape<kFmtQ8>::kThreads, DecodeSmemBytes<kFmtQ8>(), stream, *a.kmap,
                          *a.vmap, a.pool, a.layer, a.tables_dev, a.table_stride, a.units_dev, q, a.scale_log2,
                          a.partial_acc, a.partial_ml, a.status_dev);
-  return LaunchChained(DecodePartKernel<kFmtQ4>, a.n_units, kDecodeThreads, DecodeSmemBytes<kFmtQ4>(), stream, *a.kmap,
+  return LaunchChained(DecodePartKernel<kFmtQ4>, a.n_units, Shape<kFmtQ4>::kThreads, DecodeSmemBytes<kFmtQ4>(), stream, *a.kmap,
                        *a.vmap, a.pool, a.layer, a.tables_dev, a.table_stride, a.units_dev, q, a.scale_log2,
                        a.partial_acc, a.partial_ml, a.status_dev);
 }

@@ -104,7 +104,7 @@ __device__ __forceinline__ void MergeUnitAndStore(float* merge, const float (&o_
     }
   }
   __syncthreads();
-  const int tid = threadIdx.x;  // 0 .. 255: one dim per thread per head
+  // one output dim per thread and head (a CTA of fewer than 256 threads takes several dims per thread)
 #pragma unroll
   for (int h = 0; h < kGroup; ++h) {
     float mw[kWarps], M = -INFINITY;
@@ -113,16 +113,19 @@ __device__ __forceinline__ void MergeUnitAndStore(float* merge, const float (&o_
       mw[w] = merge[w * kDecodeMergeWarpFloats + kGroup * kDecodeMergeStride + 2 * h];
       M = fmaxf(M, mw[w]);
     }
-    float a = 0.0F, lsum = 0.0F;
+    float wgt[kWarps], lsum = 0.0F;
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) {
-      const float wgt = mw[w] == -INFINITY ? 0.0F : exp2f(mw[w] - M);
-      const float* src = merge + w * kDecodeMergeWarpFloats;
-      a = fmaf(wgt, src[h * kDecodeMergeStride + tid], a);
-      lsum = fmaf(wgt, src[kGroup * kDecodeMergeStride + 2 * h + 1], lsum);
+      wgt[w] = mw[w] == -INFINITY ? 0.0F : exp2f(mw[w] - M);
+      lsum = fmaf(wgt[w], merge[w * kDecodeMergeWarpFloats + kGroup * kDecodeMergeStride + 2 * h + 1], lsum);
     }
-    acc_out[h * kHeadDim + tid] = a;
-    if (tid == 0) ml_out[2 * h] = M, ml_out[2 * h + 1] = lsum;
+    for (int dim = threadIdx.x; dim < kHeadDim; dim += kWarps * 32) {
+      float a = 0.0F;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) a = fmaf(wgt[w], merge[w * kDecodeMergeWarpFloats + h * kDecodeMergeStride + dim], a);
+      acc_out[h * kHeadDim + dim] = a;
+    }
+    if (threadIdx.x == 0) ml_out[2 * h] = M, ml_out[2 * h + 1] = lsum;
   }
 }
 

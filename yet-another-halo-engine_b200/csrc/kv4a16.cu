@@ -105,11 +105,13 @@ __global__ void __launch_bounds__(128) Kv4AppendKKernel(PoolView pool, int layer
 
 // ---------------------------------------------------------------------------------------------------------------
 // Decode attention: one CTA per split-K unit; the shape of the other formats' kernel (a ring of page stages filled by
-// non-multicast TMA on one mbarrier each, eight warps on two pages at a time, warp = one 16-key tile with all 256
-// dims, last-arriver refill, fill-generation guard, bounded waits with the abort drain).
+// non-multicast TMA on one mbarrier each, warp = one 16-key tile with all 256 dims, four warps per page in work,
+// last-arriver refill, fill-generation guard, bounded waits with the abort drain).
 //
 // A stage: the page's K codes as one swizzled 64 x 128 B box, its K pairs (2 KB), its four V tiles as stored (8 KB)
-// and the V pairs (4 KB): 22,528 B, four stages.
+// and the V pairs (4 KB): 22,528 B. The kernel is bound by instruction latency, not by memory, and runs best as many
+// small CTAs whose prologues and merges overlap: one set of four warps on a two-stage ring, four CTAs per SM (242 us
+// per layer on the batch-32 workload against 251 as two sets on four stages with two CTAs per SM).
 //
 // Scores. With the query rotated and quantized to two int8 planes (q = step (256 hi + lo)):
 //   q.r = sum_g [ (S_g / 16) sum_{d in g} q_d u_d  +  (S_g + C'_g) sum_{d in g} q_d ].
@@ -124,9 +126,19 @@ __global__ void __launch_bounds__(128) Kv4AppendKKernel(PoolView pool, int layer
 // a key pair's nibbles sit at bits 4-7 / 20-23 and or-ed into 0x5400 they are the f16 pair 64 + u (a rotate and one
 // logic instruction per MMA register, no subtract), so o += (S / 16) sum p (64 + u) + (C' - 3 S) sum p.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int kStages = 4;
+#ifndef YAHKV_KV4_STAGES
+#define YAHKV_KV4_STAGES 2
+#endif
+#ifndef YAHKV_KV4_PAGE_SETS
+#define YAHKV_KV4_PAGE_SETS 1
+#endif
+#ifndef YAHKV_KV4_CTAS
+#define YAHKV_KV4_CTAS 4
+#endif
+constexpr int kStages = YAHKV_KV4_STAGES;
 constexpr int kKeyGroups = 4;
-constexpr int kPageSets = 2;
+constexpr int kPageSets = YAHKV_KV4_PAGE_SETS;
+constexpr int kCtas = YAHKV_KV4_CTAS;
 constexpr int kWarps = kKeyGroups * kPageSets;
 constexpr int kThreads = kWarps * 32;
 constexpr int kKBytes = RecordCodeBytes(kFmtKv4);           // 8192: one 64 x 128 B box
@@ -148,7 +160,7 @@ constexpr int kQStepOff = kFillOff + 4 * kStages;                  // [8] f32
 constexpr int kQSumOff = kQStepOff + 32;                           // [8 heads][8 groups] u32: f16 hi | f16 residual << 16
 constexpr int kAbortOff = kQSumOff + 8 * 8 * 4;
 constexpr int kSmemBytes = (kAbortOff + 4 + 127) / 128 * 128;
-static_assert(2 * (kSmemBytes + 1024) <= 228 * 1024, "two CTAs per SM");
+static_assert(kCtas * (kSmemBytes + 1024) <= 228 * 1024, "the resident CTAs of an SM");
 static_assert(kWarps * kDecodeMergeWarpFloats * 4 <= kRingBytes, "the merge scratch aliases the ring");
 constexpr float kLazyRescale = 4.0F;
 constexpr float kQSteps = 32000.0F;
@@ -177,7 +189,7 @@ __device__ __forceinline__ std::uint32_t PackBytes(int b0, int b1, int b2, int b
          ((static_cast<std::uint32_t>(b2) & 255U) << 16) | ((static_cast<std::uint32_t>(b3) & 255U) << 24);
 }
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, kCtas)
     Kv4DecodePartKernel(const __grid_constant__ CUtensorMap kmap, PoolView pool, int layer,
                         const std::int32_t* __restrict__ tables, int table_stride, const DecodeUnit* __restrict__ units,
                         const __half* __restrict__ q, float scale_log2, const __half* __restrict__ open_tiles,
@@ -241,8 +253,8 @@ __global__ void __launch_bounds__(kThreads, 2)
   // row's largest magnitude (q16 = rint(r * 32000 / amax), hi = (q16 + 128) >> 8, lo = q16 - 256 hi) and leaves, per
   // group (4 lanes) and lane, the A operand of the integer MMA: bytes in the order the code nibbles unpack
   // (dims 0, 4, 1, 5 of the lane's 8, then 2, 6, 3, 7), hi plane in rows 0-5, lo plane in rows 8-13.
-  if (warp < kGroup) {
-    const __half* qrow = q + (static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + warp) * kHeadDim;
+  for (int hq = warp; hq < kGroup; hq += kWarps) {   // one head per warp and pass
+    const __half* qrow = q + (static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + hq) * kHeadDim;
     const uint4 raw = *reinterpret_cast<const uint4*>(qrow + 8 * lane);
     const __half2* hp = reinterpret_cast<const __half2*>(&raw);
     float x[8];
@@ -269,17 +281,17 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
     const uint4 frag = make_uint4(PackBytes(hi[0], hi[4], hi[1], hi[5]), PackBytes(lo[0], lo[4], lo[1], lo[5]),
                                   PackBytes(hi[2], hi[6], hi[3], hi[7]), PackBytes(lo[2], lo[6], lo[3], lo[7]));
-    *reinterpret_cast<uint4*>(qfrag + (((lane >> 2) * kQLanes + warp * 4 + (lane & 3)) << 2)) = frag;
+    *reinterpret_cast<uint4*>(qfrag + (((lane >> 2) * kQLanes + hq * 4 + (lane & 3)) << 2)) = frag;
     sum += __shfl_xor_sync(0xFFFFFFFFU, sum, 1);
     sum += __shfl_xor_sync(0xFFFFFFFFU, sum, 2);   // the group's sum of the quantized query, exact
     if ((lane & 3) == 0) {
       const float qf = static_cast<float>(sum) * step;
       const __half h16 = __float2half_rn(qf);
       const __half l16 = __float2half_rn(qf - __half2float(h16));
-      q_sum[warp * 8 + (lane >> 2)] = static_cast<std::uint32_t>(__half_as_ushort(h16)) |
+      q_sum[hq * 8 + (lane >> 2)] = static_cast<std::uint32_t>(__half_as_ushort(h16)) |
                                       (static_cast<std::uint32_t>(__half_as_ushort(l16)) << 16);
     }
-    if (lane == 0) q_step[warp] = step;
+    if (lane == 0) q_step[hq] = step;
   }
   __syncthreads();   // barriers initialised, query operands visible
   const int qlane = lane < kQLanes ? lane : lane - 8;   // the two padding rows of the MMA reuse heads 4, 5
