@@ -125,10 +125,16 @@ class ClockSampler:
         if self.thread is not None:
             self.halt = True
             self.thread.join(timeout=1.0)
-            rows = [r for r in self.samples if t_begin is None or t_begin <= r[0] <= t_end]
+            rows, widened = [], None
+            for pad in (0.0, 0.1, 0.5):      # a very short region may fall between two samples: then its surroundings
+                rows = [r for r in self.samples if t_begin is None or t_begin - pad <= r[0] <= t_end + pad]
+                if rows or t_begin is None:
+                    widened = pad if pad > 0 else None
+                    break
             reasons = sorted({name for _, _, bits in rows for name, bit in self.REASON_BITS if bits & bit})
             return {"sm_mhz": float(np.median([r[1] for r in rows])) if rows else None, "sm_max_mhz": self.max_mhz,
-                    "reasons": reasons, "samples": len(rows), "source": "nvml, every 5 ms"}
+                    "reasons": reasons, "samples": len(rows), "source": "nvml, every 5 ms",
+                    **({"window": f"timed region widened by {widened} s on both sides to catch samples"} if widened else {})}
         if self.p is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.p.terminate()
@@ -329,6 +335,7 @@ def prefill_arm(args, local_rank):
         cache.append(0, ids, pos, k, v, stream=sptr)
         cache.attend_prefill(0, seqs, [chunk] * n_seq, qq, out, stream=sptr)
 
+    sampler = ClockSampler(local_rank)   # ahead of the warm-up: the timed region is only tens of milliseconds long
     warm = max(args.warmup, 3)
     for _ in range(warm):
         step()
@@ -347,7 +354,6 @@ def prefill_arm(args, local_rank):
         if not ok:
             raise SystemExit(f"parity check failed before timing: {parity}")
     cache.kernel_timing(True)
-    sampler = ClockSampler(local_rank)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_begin = time.time()
     ev0.record(stream)
