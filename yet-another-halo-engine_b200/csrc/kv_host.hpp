@@ -248,13 +248,30 @@ class KvHost {
       // The part kernel's two page sets take alternate pages of a unit: an odd count leaves one set idle for a page,
       // so a unit costs as much as the next even count. Rounding up never raises the number of units.
       if (per > 1) per += per & 1;
-      const int nu = (pages + per - 1) / per;
+      int nu = (pages + per - 1) / per;
+      // Graded sizes: with eight or more units the last quarter of them is half as long (and the others a little
+      // longer, the count stays). CTAs take units longest first, so the short ones of all sequences run last and fill
+      // the gaps of the final wave: equal units on a grid that is not a multiple of the resident CTAs leave a last
+      // wave that is mostly idle (8 x 131072 tokens in 64 splits: 1952 equal units on 592 CTA slots).
+      bounds_.clear();
+      if (nu >= 8) {
+        const int n_small = nu / 4, n_big = nu - n_small;
+        int big = (2 * pages + 2 * n_big + n_small - 1) / (2 * n_big + n_small);
+        big += big & 1;
+        const int small = std::max(((big / 2) + 1) & ~1, 2);
+        int p = 0;
+        for (int k = 0; k < n_big && p < pages; ++k) bounds_.push_back(p = std::min(p + big, pages));
+        while (p < pages) bounds_.push_back(p = std::min(p + small, pages));
+      } else {
+        for (int k = 0; k < nu; ++k) bounds_.push_back(std::min(pages, (k + 1) * per));
+      }
+      nu = static_cast<int>(bounds_.size());
       for (int h = hb; h < hb + hc; ++h) {   // heads outside the context's range keep n_partials = 0
         items[static_cast<std::size_t>(b) * kKvHeads + h] = {static_cast<std::int32_t>(units.size()), nu};
         for (int k = 0; k < nu; ++k) {
           DecodeUnit u{};
           u.batch = b, u.seq = s, u.kvh = h;
-          u.page_begin = k * per, u.page_end = std::min(pages, (k + 1) * per);
+          u.page_begin = k == 0 ? 0 : bounds_[static_cast<std::size_t>(k) - 1], u.page_end = bounds_[static_cast<std::size_t>(k)];
           u.n_keys = static_cast<std::int32_t>(n);
           u.partial = static_cast<std::int32_t>(units.size());
           units.push_back(u);
@@ -477,6 +494,7 @@ class KvHost {
   std::vector<DecodeUnit> units_;
   std::vector<CombineItem> items_;
   std::vector<int> open_cur_;   // kv8a16: current open-tile buffer per (sequence, layer)
+  std::vector<int> bounds_;     // PlanDecode: page boundaries of one sequence's units
 };
 
 }  // namespace yahkv
