@@ -138,8 +138,9 @@ struct PrefillTile {
 };
 static_assert(sizeof(PrefillTile) == 32, "uploaded as an array");
 
-// A tile of the call's last, partly filled wave that was split along the keys into n_parts CTAs (consecutive entries
-// of the tile list from tile_index on, consecutive part slots): the merge kernel joins their partial results.
+// A tile of the call's last, partly filled wave that was split along the keys into n_parts CTAs (every second entry
+// of the tile list from tile_index on, every second part slot, because tiles come as pairs of heads): the merge
+// kernel joins their partial results.
 struct PrefillMerge {
   std::int32_t tile_index;
   std::int32_t n_parts;
@@ -272,7 +273,7 @@ cudaError_t LaunchKv8PrefillDequant(const PrefillLaunch& a, const void* open_til
 // kv4a16 (kv4a16.cu): K rows are rotated back (the transform is its own inverse) so the chunk's q needs no rotation.
 cudaError_t LaunchKv4PrefillDequant(const PrefillLaunch& a, const void* open_tiles_dev, int n_layers, cudaStream_t stream);
 cudaError_t LaunchPrefill(const PrefillLaunch& a, cudaStream_t stream);
-cudaError_t ConfigurePrefillKernels();
+cudaError_t ConfigurePrefillKernels(int* max_active_pairs);   // also: how many CTA pairs the device runs at once
 // Encodes a 2-D tiled tensor map (row-major, `inner` elements of `elem_bytes` per row, 128-byte swizzle). Host only.
 bool EncodeTensorMap2D(CUtensorMap* map, int elem_bytes, void* base, std::uint64_t inner, std::uint64_t rows,
                        std::uint32_t box_inner, std::uint32_t box_rows);

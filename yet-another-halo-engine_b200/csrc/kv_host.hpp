@@ -357,7 +357,8 @@ class KvHost {
   // Work lists of one prefill call: per sequence the span of the fp16 scratch it is dequantized into, and tiles of
   // 128 query rows x one query head, the ones with the most keys first so that the short ones fill the tail.
   // n_sm > 0: the tiles of the last, partly filled wave (one CTA per SM and wave, all tiles cost about the same) are
-  // split along their keys into parts that fill the wave's idle SMs; `merges` lists them for the merge kernel.
+  // split along their keys into parts that fill the wave's idle SMs; `merges` lists them for the merge kernel, one
+  // entry per head.
   HostError PlanPrefill(int layer, int n_seqs, const std::int32_t* seq_ids, const std::int32_t* chunk_lens,
                         int max_rows, int n_sm, std::vector<PrefillSeq>* seqs, std::vector<PrefillTile>* tiles,
                         std::vector<PrefillMerge>* merges, int* n_parts, std::int64_t* total_rows,
@@ -406,30 +407,39 @@ class KvHost {
                      [](const PrefillTile& a, const PrefillTile& b) { return a.pos0 + a.n_rows > b.pos0 + b.n_rows; });
     merges->clear();
     *n_parts = 0;
-    const int n_tiles = static_cast<int>(tiles->size());
-    const int tail = n_sm > 0 ? n_tiles % n_sm : 0;   // a call of fewer tiles than SMs is all tail
-    // Split factor: the tail's tiles cut into f key ranges take ceil(tail f / n_sm) waves of 1 / f tile time each.
+    // The kernel runs the two heads of a pair (entries 2 i and 2 i + 1: equal sort keys keep the neighbours of the loop
+    // above together) as one CTA pair on two SMs, so the wave is counted in pairs.
+    const int n_pairs = static_cast<int>(tiles->size()) / 2;
+    const int wave = n_sm / 2;
+    const int tail = wave > 0 ? n_pairs % wave : 0;   // a call of fewer pairs than the wave is all tail
+    // Split factor: the tail's pairs cut into f key ranges take ceil(tail f / wave) waves of 1 / f tile time each.
     int f = 1;
     double best = 1.0;
     for (int c = 2; c <= kPrefillMaxParts && tail > 0; ++c) {
-      const double cost = static_cast<double>((tail * c + n_sm - 1) / n_sm) / c;
+      const double cost = static_cast<double>((tail * c + wave - 1) / wave) / c;
       if (cost < best - 1e-9) best = cost, f = c;
     }
     if (f > 1) {
-      const std::vector<PrefillTile> last(tiles->end() - tail, tiles->end());
-      tiles->resize(static_cast<std::size_t>(n_tiles - tail));
-      for (const PrefillTile& t : last) {
+      const std::vector<PrefillTile> last(tiles->end() - 2 * tail, tiles->end());
+      tiles->resize(static_cast<std::size_t>(2 * (n_pairs - tail)));
+      for (std::size_t i = 0; i + 1 < last.size(); i += 2) {
+        const PrefillTile& t = last[i];
         const int ff = std::min(f, t.jt_end / 2);   // a part covers at least two key tiles
         if (ff < 2) {
-          tiles->push_back(t);
+          tiles->push_back(last[i]);
+          tiles->push_back(last[i + 1]);
           continue;
         }
+        // part k of the two heads sits at entries first + 2 k, first + 2 k + 1 and takes the part slots of the same
+        // parity: the merge kernel steps by two
         merges->push_back({static_cast<std::int32_t>(tiles->size()), ff});
-        for (int k = 0; k < ff; ++k) {
-          PrefillTile p = t;
-          p.jt_begin = t.jt_end * k / ff, p.jt_end = t.jt_end * (k + 1) / ff, p.part = (*n_parts)++;
-          tiles->push_back(p);
-        }
+        merges->push_back({static_cast<std::int32_t>(tiles->size()) + 1, ff});
+        for (int k = 0; k < ff; ++k)
+          for (int h = 0; h < 2; ++h) {
+            PrefillTile p = last[i + static_cast<std::size_t>(h)];
+            p.jt_begin = t.jt_end * k / ff, p.jt_end = t.jt_end * (k + 1) / ff, p.part = (*n_parts)++;
+            tiles->push_back(p);
+          }
       }
     }
     *total_rows = row;

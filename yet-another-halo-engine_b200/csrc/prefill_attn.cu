@@ -10,42 +10,50 @@
 // Pass 1, DequantPagesKernel (HBM-bound): every page of every sequence of the call, through the block table, to a
 // token-major fp16 scratch (K and V), value = fp16(code * scale). 34.8 KB read and 64 KB written per page and kv head.
 //
-// Pass 2, PrefillKernel (tensor-bound): one CTA per tile of 128 query rows of one query head; head_dim 256.
-//   S = Q K^T   tcgen05.mma kind::f16, M 128, N 64 (one 64-key tile), K 256 in 16 steps; A = Q held in tensor memory
-//               for the whole CTA, B = the K tile in shared memory (K-major, 128-byte swizzle, four 64-dim TMA
-//               boxes), D = S in TMEM.
-//   softmax     two warpgroups of one thread per query row; tiles alternate between them. tcgen05.ld of the 64
-//               scores, causal mask, reference max with a lazy rescale of O (threshold 2^8) handed from the group of
-//               tile j to the group of tile j + 1 through shared memory, P = 2^(s - m) as fp16 written back over S
-//               with tcgen05.st. Each group keeps a partial row sum; the epilogue joins them.
-//   O += P V    tcgen05.mma M 128, N 256, K 64 in 4 steps; A = P from tensor memory, B = the V tile as loaded
-//               (token-major = MN-major B operand, 128-byte swizzle), D = O in TMEM (256 columns).
-// Both A operands live in tensor memory because with them in shared memory the kernel was bound by shared-memory
-// bandwidth (the 64 KB Q tile re-read for every key tile).
-// TMEM columns (all 512): S / P double-buffered 2 x 64, O 256, Q 128. Shared memory: three stages of K tile + V tile
-// (64 KB each), one full / empty barrier pair per stage.
-// Warp roles: 0-7 softmax / correction / epilogue, 8 TMA producer, 9 MMA issuer and TMEM owner; the producer and the
-// issuer run their loops as converged warps and predicate only the asynchronous instructions on an elected lane
-// (issued from inside a lane-0 branch a tcgen05.mma cost ~67 clocks of issue, from a converged warp ~27). No
-// multicast, no cluster. Every mbarrier wait is bounded and abortable: a wait that gives up raises a CTA-wide abort
-// flag, every role leaves its loop, TMEM is freed, and the status word tells the host the call's results are invalid.
+// Pass 2, PrefillKernel (tensor-bound): one CTA pair (a cluster of two CTAs on the two SMs of a TPC, cta_group::2)
+// per tile of 128 query rows of two query heads of one KV head; head_dim 256. The pair shares every K and V tile:
+// each CTA loads half of it, so a 64-key tile costs each SM 32 KB of L2 reads instead of 64 KB.
+//   S = Q K^T   tcgen05.mma kind::f16, M 256 over the pair (128 rows = one head per CTA), N 64 (one 64-key tile), K 256
+//               in 16 steps; A = Q held in each CTA's tensor memory for the whole CTA, B = the K tile in shared
+//               memory (K-major, 128-byte swizzle), keys 0-31 in the leader, 32-63 in the peer; D = S in TMEM.
+//   softmax     per CTA, two warpgroups of one thread per query row; tiles alternate between them. tcgen05.ld of the
+//               64 scores (which frees the S buffer), causal mask, reference max with a lazy rescale of O (threshold
+//               2^8) handed from the group of tile j to the group of tile j + 1 through shared memory, P = 2^(s - m)
+//               as fp16 into a swizzled shared-memory tile. Each group keeps a partial row sum; the epilogue joins them.
+//   O += P V    tcgen05.mma M 256, N 256, K 64 in 4 steps; A = P from each CTA's shared memory, B = the V tile as
+//               loaded (token-major = MN-major B operand, 128-byte swizzle), dims 0-127 in the leader, 128-255 in the
+//               peer; D = O in TMEM (256 columns).
+// Q lives in tensor memory because with it in shared memory the kernel was bound by shared-memory bandwidth (the
+// 64 KB Q tile re-read for every key tile). P goes through shared memory (16 KB per tile) so that the S buffer is
+// free as soon as it has been read: S then runs two tiles ahead of P.V and the softmax of a tile, with its signals
+// across the pair, has two tile periods before the tensor pipe waits for it.
+// TMEM columns (all 512): S double-buffered 2 x 64, O 256, Q 128. Shared memory per CTA: YAHKV_PREFILL_STAGES stages
+// of half a K tile + half a V tile (32 KB each), two P tiles, the barriers.
+// Warp roles: 0-7 softmax / correction / epilogue, 8 TMA producer, 9 MMA issuer (leader CTA only) and TMEM owner; the
+// producer and the issuer run their loops as converged warps and predicate only the asynchronous instructions on an
+// elected lane. The TMA loads of both CTAs count their bytes on the leader's barrier (cta_group::2 loads, no
+// multicast); the leader's commits arrive on the barriers of both CTAs; the peer's softmax warps arrive on the
+// leader's barriers with plain (CTA-scope) remote arrivals. Every mbarrier wait is bounded and abortable: a wait that
+// gives up raises a CTA-wide abort flag, every role leaves its loop, both CTAs meet at the cluster barrier, TMEM is
+// freed, and the status word tells the host the call's results are invalid.
 //
 // Tiles of a call's last, partly filled wave arrive split along the keys (PrefillTile::jt_begin / jt_end / part): such
 // a CTA leaves its unnormalised accumulator and the rows' (max, sum) in a workspace and PrefillMergeKernel joins the
 // parts.
 //
-// What bounds it: the tensor pipe needs 1,024 clocks per 64-key tile (16 x 32 + 4 x 128) and the measured steady
-// state is ~1,430. The six query heads of a GQA group times the query tiles are separate CTAs, so every CTA pulls
-// its own 64 KB per tile from L2: 45 B/clock/SM, about 10.5 TB/s over the chip, which is where the MMA warp's waits
-// for loads come from (~125 clocks per tile). A CTA pair per two heads (cta_group::2, half of each B operand per
-// CTA) removes those waits but puts two cross-CTA signals into the S -> softmax -> P.V chain, and with only two S
-// buffers in TMEM that chain then bounds the tile at ~1,700 clocks; it needs a third S buffer (Q out of TMEM) to pay.
+// What bounds it: the tensor pipe needs 1,024 clocks per 64-key tile (16 x 32 + 4 x 128). One CTA per (tile, head)
+// with the whole K / V tile in each SM ran at ~1,430: every CTA pulled its own 64 KB per tile from L2, 45 B/clock/SM
+// or about 10.5 TB/s over the chip. The pair halves that traffic.
 #include <cuda_fp16.h>
 
 #include <cmath>
 
 #include "kernels.cuh"
 #include "ptx.cuh"
+
+#ifndef YAHKV_PREFILL_STAGES
+#define YAHKV_PREFILL_STAGES 5   // K / V half tiles in flight per CTA (at least 3: S runs two tiles ahead of P.V)
+#endif
 
 namespace yahkv {
 namespace {
@@ -109,23 +117,31 @@ __global__ void __launch_bounds__(kDequantThreads)
 }
 
 // ----------------------------------------------------------------------------------------------------------------
-// Pass 2: tcgen05 flash attention
+// Pass 2: tcgen05 flash attention, one CTA pair (cta_group::2) per two query heads of a KV head
 // ----------------------------------------------------------------------------------------------------------------
-constexpr int kTileM = kPrefillTileRows;   // 128 query rows
+constexpr int kTileM = kPrefillTileRows;   // 128 query rows per CTA, 256 per pair
 constexpr int kTileN = 64;                 // keys per KV tile
-constexpr int kSoftmaxThreads = 256;       // warps 0-7: two threads per query row, 32 of a tile's 64 columns each
-constexpr int kPrefillThreads = 320;       // + warp 8 TMA producer, warp 9 MMA issuer
+constexpr int kSoftmaxThreads = 256;       // warps 0-7: two warpgroups of one thread per query row
+constexpr int kPrefillThreads = 320;       // + warp 8 TMA producer, warp 9 MMA issuer (leader CTA) and TMEM owner
 constexpr int kWarpTma = 8, kWarpMma = 9;
-constexpr int kKvTileBytes = kTileN * kHeadDim * 2;  // 32768: four [64 keys][64 dims] boxes
-constexpr int kKvStages = 3;
+// Each CTA of a pair holds half of every B operand: K rows (keys) 32 rank .. + 31 of the tile as four [32 keys][64 dims]
+// boxes, V columns (dims) 128 rank .. + 127 as two [64 keys][64 dims] boxes. 16 KB each per tile.
+constexpr int kKHalfBytes = (kTileN / 2) * kHeadDim * 2;
+constexpr int kVHalfBytes = kTileN * (kHeadDim / 2) * 2;
+constexpr int kKBlockBytes = (kTileN / 2) * 128;   // one [32 keys][64 dims] box
+constexpr int kVBlockBytes = kTileN * 128;         // one [64 keys][64 dims] box
+constexpr int kPBytes = kTileM * kTileN * 2;       // P of one tile: [128 rows][64 fp16], K-major, 128-byte swizzle
+constexpr int kKvStages = YAHKV_PREFILL_STAGES;
 constexpr int kSmemK = 0;
-constexpr int kSmemV = kSmemK + kKvStages * kKvTileBytes;
-constexpr int kSmemBars = kSmemV + kKvStages * kKvTileBytes;
+constexpr int kSmemV = kSmemK + kKvStages * kKHalfBytes;
+constexpr int kSmemP = kSmemV + kKvStages * kVHalfBytes;
+constexpr int kSmemBars = kSmemP + 2 * kPBytes;
 constexpr int kBarBytes = 256;
 constexpr int kPrefillSmemBytes = kSmemBars + kBarBytes + 4 * kTileM * 4;   // barriers, then the max / sum exchange
-// TMEM columns (512 in all): S / P double-buffered, O, and Q as the A operand of S = Q K^T.
+static_assert(kPrefillSmemBytes <= 232448, "shared memory of one CTA");
+// TMEM columns (512 in all, the same in both CTAs): S double-buffered, O, and Q as the A operand of S = Q K^T.
 constexpr int kTmemCols = 512;
-constexpr int kColS = 0;      // two buffers of 64 fp32 columns; P (fp16 pairs) overwrites the first 32 of its buffer
+constexpr int kColS = 0;      // two buffers of 64 fp32 columns
 constexpr int kColO = 128;    // 256 fp32 columns
 constexpr int kColQ = 384;    // 128 columns = 256 fp16 per row
 constexpr float kPrefillLazyRescale = 8.0F;
@@ -135,30 +151,56 @@ constexpr int kStatusPrefillAbort = 3;
 // >> 4, 16-29 leading byte offset >> 4, 32-45 stride byte offset >> 4, bit 46 version, 61-63 layout.
 //   K-major operand  [rows][64 fp16]: rows 128 B apart, groups of 8 rows 1024 B apart (stride byte offset).
 //   MN-major operand [keys][64 fp16] x blocks: 8-key groups 1024 B apart (stride), 64-element blocks `lbo` apart.
+// The high word is the same for every operand of this kernel.
+constexpr std::uint32_t kDescHi = (1024U >> 4) | (1U << 14) | (2U << 29);
+__device__ __forceinline__ std::uint32_t DescLo(std::uint32_t addr, std::uint32_t lbo_bytes) {
+  return ((addr >> 4) & 0x3FFFU) | (((lbo_bytes >> 4) & 0x3FFFU) << 16);
+}
 // Instruction descriptor of kind::f16: fp16 A and B, fp32 accumulate, A K-major.
 __host__ __device__ constexpr std::uint32_t InstrDesc(int m, int n, bool b_mn_major) {
   return (1U << 4) | (0U << 7) | (0U << 10) | (0U << 15) | ((b_mn_major ? 1U : 0U) << 16) |
          (static_cast<std::uint32_t>(n >> 3) << 17) | (static_cast<std::uint32_t>(m >> 4) << 24);
 }
 
-// D(tmem) (+)= A(tmem) * B(smem). The A operand sits in tensor memory (row = lane, two fp16 per 32-bit column), so an
-// MMA step reads only its B slice from shared memory: with both operands in shared memory this kernel was bound by
-// shared-memory bandwidth (the 64 KB Q tile was re-read for every 64-key tile).
-__device__ __forceinline__ void UmmaF16Ts(std::uint32_t d_tmem, std::uint32_t a_tmem, std::uint32_t b_desc_lo,
-                                          std::uint32_t b_desc_hi, std::uint32_t idesc, bool accumulate) {
+// D(tmem) (+)= A * B over the CTA pair: M = 256 (128 rows in each CTA's tensor memory, the same columns in both), the
+// B half of each CTA from its shared memory at the same offset. Issued by one thread of the leader CTA.
+//   Ts: A from each CTA's own tensor memory (two fp16 per 32-bit column). Q is held there for the whole CTA: with it
+//       in shared memory the kernel was bound by shared-memory bandwidth (the 64 KB tile re-read for every key tile).
+//   Ss: A from each CTA's own shared memory (descriptor), used for P.
+__device__ __forceinline__ void UmmaF16Ts2(std::uint32_t d_tmem, std::uint32_t a_tmem, std::uint32_t b_desc_lo,
+                                           std::uint32_t idesc, bool accumulate) {
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
       ".reg .b64 bd;\n"
       "setp.ne.b32 p, %5, 0;\n"
       "mov.b64 bd, {%2, %3};\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %4, p;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], bd, %4, p;\n"
       "}\n" ::"r"(d_tmem),
-      "r"(a_tmem), "r"(b_desc_lo), "r"(b_desc_hi), "r"(idesc), "r"(accumulate ? 1U : 0U)
+      "r"(a_tmem), "r"(b_desc_lo), "r"(kDescHi), "r"(idesc), "r"(accumulate ? 1U : 0U)
       : "memory");
 }
-__device__ __forceinline__ void UmmaCommit(std::uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(SmemAddr(bar))
+__device__ __forceinline__ void UmmaF16Ss2(std::uint32_t d_tmem, std::uint32_t a_desc_lo, std::uint32_t b_desc_lo,
+                                           std::uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 ad, bd;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "mov.b64 ad, {%1, %3};\n"
+      "mov.b64 bd, {%2, %3};\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], ad, bd, %4, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_desc_lo), "r"(b_desc_lo), "r"(kDescHi), "r"(idesc), "r"(accumulate ? 1U : 0U)
+      : "memory");
+}
+// Arrives, once every tcgen05 operation this thread issued before has completed, on the barrier at this shared-memory
+// offset in both CTAs of the pair (one commit per CTA).
+__device__ __forceinline__ void UmmaCommitPair(std::uint64_t* bar) {
+  const std::uint32_t a = SmemAddr(bar);
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(MapToCta(a, 0))
+               : "memory");
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(MapToCta(a, 1))
                : "memory");
 }
 __device__ __forceinline__ void TcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -186,14 +228,17 @@ __device__ __forceinline__ void TmemSt32(std::uint32_t addr, const std::uint32_t
 __device__ __forceinline__ void TmemWaitLd() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void TmemWaitSt() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// Bounded, abortable wait: gives up after ~2 s or as soon as another role has raised the abort flag.
+// Bounded, abortable wait: gives up after ~2 s or as soon as another role of this CTA has raised the abort flag.
+// kCluster: the barrier is arrived on from the other CTA of the pair (acquire at cluster scope).
+template <bool kCluster = false>
 __device__ __forceinline__ bool WaitOrAbort(std::uint64_t* bar, std::uint32_t parity, volatile int* abort_flag) {
-  if (MbarTryWait(bar, parity)) return true;
+  auto poll = [&]() { return kCluster ? MbarTryWaitCluster(bar, parity) : MbarTryWait(bar, parity); };
+  if (poll()) return true;
   const std::uint64_t t0 = GlobalTimerNs();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
-      if (MbarTryWait(bar, parity)) return true;
+      if (poll()) return true;
     if (*abort_flag != 0) return false;
     if (GlobalTimerNs() - t0 > 2000000000ULL) {
       *abort_flag = 1;
@@ -202,22 +247,25 @@ __device__ __forceinline__ bool WaitOrAbort(std::uint64_t* bar, std::uint32_t pa
   }
 }
 
+// The barriers sit at the same shared-memory offsets in both CTAs of a pair. "leader": only the leader's copy is
+// used (the peer arrives on it remotely). "both": the leader's MMA warp commits to the copy of each CTA, and each
+// CTA waits on its own. "local": used inside one CTA only.
 struct PrefillBars {
-  std::uint64_t q_full;    // softmax threads -> MMA: Q is in tensor memory
-  std::uint64_t kv_full[kKvStages];    // TMA -> MMA: K(j) and V(j) have landed (one wait per tile for both)
-  std::uint64_t kv_empty[kKvStages];   // MMA -> TMA: P(j) V(j), the last reader of the stage, is complete
-  std::uint64_t s_full[2]; // MMA -> softmax: S(j) is in its buffer
-  std::uint64_t p_full[2]; // softmax -> MMA: P(j) written over S(j), O rescaled; one per tile parity
-  std::uint64_t m_posted[2];   // softmax group of tile j -> group of tile j + 1: m(j) is in shared memory
-  std::uint64_t pv_done;   // MMA -> softmax: O += P(j) V(j) complete
-  std::uint64_t o_done;    // MMA -> softmax: the last P.V is complete (a parity wait on pv_done may lag at most one phase,
-                           // which the epilogue cannot guarantee)
+  std::uint64_t q_full;                // leader: softmax warps of both CTAs -> MMA: Q is in tensor memory
+  std::uint64_t kv_full[kKvStages];    // leader: TMA of both CTAs -> MMA: both halves of K(j) and V(j) have landed
+  std::uint64_t kv_empty[kKvStages];   // both: MMA -> TMA: P(j) V(j), the last reader of the stage, is complete
+  std::uint64_t s_full[2];             // both: MMA -> softmax: S(j) is in its buffer
+  std::uint64_t s_free[2];             // leader: softmax warps of both CTAs -> MMA: S(j) has been read into registers
+  std::uint64_t p_full[2];             // leader: softmax warps of both CTAs -> MMA: P(j) is in shared memory, O rescaled
+  std::uint64_t m_posted[2];           // local: softmax group of tile j -> group of tile j + 1: m(j) is in shared memory
+  std::uint64_t pv_done[2];            // both: MMA -> softmax: O += P(j) V(j) complete, one barrier per tile parity
+  std::uint64_t o_done;                // both: the last P.V is complete
   std::uint32_t tmem_base;
   int abort_flag;
 };
 static_assert(sizeof(PrefillBars) <= kBarBytes, "the max / sum exchange follows the barriers");
 
-__global__ void __launch_bounds__(kPrefillThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPrefillThreads, 1)
     PrefillKernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                   const PrefillTile* __restrict__ tiles, const __half* __restrict__ q, const float* __restrict__ gate,
                   void* out, int out_f32, float scale_log2, float* __restrict__ part_acc, float* __restrict__ part_ml,
@@ -225,7 +273,10 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
   extern __shared__ __align__(1024) std::uint8_t smem[];
   PrefillBars* bars = reinterpret_cast<PrefillBars*>(smem + kSmemBars);
   volatile int* abort_flag = &bars->abort_flag;
+  // Blocks 2 i and 2 i + 1 hold the tiles of two query heads of one KV head over the same query rows: the same key
+  // range, the same K and V tiles, the same number of tiles (the planner emits them as neighbours).
   const PrefillTile tile = tiles[blockIdx.x];
+  const std::uint32_t rank = ClusterCtaRank();   // 0 = leader: its MMA warp issues for the pair
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Key tiles jt0 .. jt0 + n_tiles - 1 of the keys the tile's rows can see: all of them, or one slice of a tile
   // that the planner split along the keys. Every loop below runs on the local index j; only the load coordinate and
@@ -233,124 +284,129 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
   const int jt0 = tile.jt_begin;
   const int n_tiles = tile.jt_end - tile.jt_begin;
 
-  if ((SmemAddr(smem) & 1023U) != 0) {   // the swizzled operands need the 1024-byte aligned base
+  // The swizzled operands need the 1024-byte aligned base. The dynamic shared memory starts at the same offset in
+  // both CTAs, so either both leave here or neither does.
+  if ((SmemAddr(smem) & 1023U) != 0) {
     if (threadIdx.x == 0) atomicExch(status, kStatusPrefillAbort);
     return;
   }
   if (threadIdx.x == 0) {
-    MbarInit(&bars->q_full, kSoftmaxThreads / 32);   // one arrival per softmax warp
+    MbarInit(&bars->q_full, 2 * kSoftmaxThreads / 32);   // one arrival per softmax warp of the pair
     for (int s = 0; s < kKvStages; ++s) {
-      MbarInit(&bars->kv_full[s], 1);
+      MbarInit(&bars->kv_full[s], 1);                     // the leader's expect_tx; both CTAs' copies count bytes on it
       MbarInit(&bars->kv_empty[s], 1);
     }
-    MbarInit(&bars->s_full[0], 1);
-    MbarInit(&bars->s_full[1], 1);
     for (int g = 0; g < 2; ++g) {
-      MbarInit(&bars->p_full[g], kSoftmaxThreads / 64);   // one arrival per warp of the tile's group
+      MbarInit(&bars->s_full[g], 1);
+      MbarInit(&bars->s_free[g], 2 * kSoftmaxThreads / 64);   // one arrival per warp of the tile's group, both CTAs
+      MbarInit(&bars->p_full[g], 2 * kSoftmaxThreads / 64);
       MbarInit(&bars->m_posted[g], kSoftmaxThreads / 64);
+      MbarInit(&bars->pv_done[g], 1);
     }
-    MbarInit(&bars->pv_done, 1);
     MbarInit(&bars->o_done, 1);
     bars->abort_flag = 0;
     FenceBarrierInit();
   }
-  if (warp == kWarpMma) {   // TMEM: one warp allocates, the same warp frees
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(&bars->tmem_base)),
+  if (warp == kWarpMma) {   // TMEM: the same warp of both CTAs allocates for the pair, and frees at the end
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(&bars->tmem_base)),
                  "r"(kTmemCols)
                  : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
   TcFenceBefore();
-  __syncthreads();
+  ClusterSync();   // both CTAs' barriers are initialised before either arrives on the other's
   TcFenceAfter();
   const std::uint32_t tmem = bars->tmem_base;
 
   if (warp == kWarpTma) {
-    // ------------------------------ TMA producer: K and V tiles into their rings ------------------------------
-    {   // the warp stays converged; one elected lane issues the copies
-      const bool elected = ElectOne();
+    // ------------------------------ TMA producer: this CTA's halves of the K and V tiles ------------------------------
+    // The warp stays converged; one elected lane issues the copies. All bytes of a stage, from both CTAs, are counted
+    // on the leader's barrier, whose one arrival is the leader's expect_tx.
+    const bool elected = ElectOne();
+    if (elected) {
+      PrefetchTensorMap(&kmap);
+      PrefetchTensorMap(&vmap);
+    }
+    bool ok = true;
+    int s = 0;
+    std::uint32_t ph = 1;   // parity of the "empty" phase to wait for: 0 on the ring's second round, then alternating
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int y = tile.kv_row0 + (jt0 + j) * kTileN;
+      if (j >= kKvStages) ok = WaitOrAbort(&bars->kv_empty[s], ph, abort_flag);
+      if (!ok) break;
       if (elected) {
-        PrefetchTensorMap(&kmap);
-        PrefetchTensorMap(&vmap);
-      }
-      bool ok = true;
-      int s = 0;
-      std::uint32_t ph = 1;   // parity of the "empty" phase to wait for: 0 on the ring's second round, then alternating
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int y = tile.kv_row0 + (jt0 + j) * kTileN;
-        if (j >= kKvStages) ok = WaitOrAbort(&bars->kv_empty[s], ph, abort_flag);
-        if (!ok) break;
-        if (elected) {
-          MbarArriveExpectTx(&bars->kv_full[s], 2 * kKvTileBytes);
+        const std::uint32_t full = MapToCta(SmemAddr(&bars->kv_full[s]), 0);
+        if (rank == 0) MbarArriveExpectTx(&bars->kv_full[s], 2 * (kKHalfBytes + kVHalfBytes));
 #pragma unroll
-          for (int kb = 0; kb < 4; ++kb)
-            TmaLoad2D(smem + kSmemK + s * kKvTileBytes + kb * (kTileN * 128), &kmap, kb * 64, y, &bars->kv_full[s]);
+        for (int kb = 0; kb < 4; ++kb)   // keys 32 rank .. + 31 of the tile, 64 dims per box
+          TmaLoad2DPair(smem + kSmemK + s * kKHalfBytes + kb * kKBlockBytes, &kmap, kb * 64,
+                        y + static_cast<int>(rank) * (kTileN / 2), full);
 #pragma unroll
-          for (int kb = 0; kb < 4; ++kb)
-            TmaLoad2D(smem + kSmemV + s * kKvTileBytes + kb * (kTileN * 128), &vmap, kb * 64, y, &bars->kv_full[s]);
-        }
-        if (++s == kKvStages) s = 0, ph ^= 1U;
+        for (int kb = 0; kb < 2; ++kb)   // all 64 keys, dims 128 rank + 64 kb .. + 63
+          TmaLoad2DPair(smem + kSmemV + s * kVHalfBytes + kb * kVBlockBytes, &vmap,
+                        (static_cast<int>(rank) * 2 + kb) * 64, y, full);
       }
+      if (++s == kKvStages) s = 0, ph ^= 1U;
     }
   } else if (warp == kWarpMma) {
-    // ------------------------------ MMA issuer ------------------------------
-    // The tensor pipe executes in issue order, which is what makes the buffer reuse safe without further barriers:
-    // S(j+2) is issued after P(j) V(j), the last reader of that S / P buffer.
-    // Issue cost is what bounds this kernel, so the whole warp runs the loop converged and only the tcgen05.mma /
-    // tcgen05.commit instructions are predicated on the elected lane: operands that are uniform across a converged
-    // warp reach the instruction without per-lane register traffic (measured: ~67 clocks per MMA issued from inside
-    // a lane-0 branch, under 40 from a converged warp). Descriptors are a constant high word and a low word = stage
-    // base + compile-time offset; ring positions are running counters.
-    {
+    // ------------------------------ MMA issuer (leader CTA only) ------------------------------
+    // Issue order: S(0), S(1), then for every tile j: S(j + 2), P(j) V(j). The tensor pipe executes one thread's
+    // instructions in that order, so between the end of S(j) and the start of P(j) V(j) it has two tiles of other
+    // work (P(j-2) V(j-2), S(j+1), P(j-1) V(j-1), S(j+2)): the softmax of tile j, with its two signals across the
+    // pair, may take two tile periods before the pipe waits for it. S(j + 2) reuses the buffer of S(j), which is
+    // free as soon as the softmax threads have read it into registers (s_free), because P goes to shared memory.
+    // The whole warp runs the loop converged and only the tcgen05 instructions are predicated on the elected lane:
+    // operands that are uniform across a converged warp reach the instruction without per-lane register traffic.
+    if (rank == 0) {
       const bool elected = ElectOne();
-      constexpr std::uint32_t idesc_s = InstrDesc(kTileM, kTileN, false);
-      constexpr std::uint32_t idesc_o = InstrDesc(kTileM, kHeadDim, true);
-      // descriptor words: K-major operand lbo 16 B, sbo 1024 B; MN-major V lbo = 64-dim block pitch
-      constexpr std::uint32_t desc_hi = (1024U >> 4) | (1U << 14) | (2U << 29);
-      std::uint32_t k_lo[kKvStages], v_lo[kKvStages];
-#pragma unroll
-      for (int s = 0; s < kKvStages; ++s) {
-        k_lo[s] = ((SmemAddr(smem + kSmemK + s * kKvTileBytes) >> 4) & 0x3FFFU) | ((16U >> 4) << 16);
-        v_lo[s] = ((SmemAddr(smem + kSmemV + s * kKvTileBytes) >> 4) & 0x3FFFU) |
-                  ((static_cast<std::uint32_t>(kTileN * 128) >> 4) << 16);
-      }
+      constexpr std::uint32_t idesc_s = InstrDesc(2 * kTileM, kTileN, false);
+      constexpr std::uint32_t idesc_o = InstrDesc(2 * kTileM, kHeadDim, true);
+      const std::uint32_t k_lo0 = DescLo(SmemAddr(smem + kSmemK), 16);             // K-major: lbo unused (16 B)
+      const std::uint32_t v_lo0 = DescLo(SmemAddr(smem + kSmemV), kVBlockBytes);   // MN-major: lbo = 64-dim block pitch
+      const std::uint32_t p_lo0 = DescLo(SmemAddr(smem + kSmemP), 16);             // K-major A operand
       const std::uint32_t q_col = tmem + kColQ, o_col = tmem + kColO;
+      int ks = 0;                        // ring stage of the next S tile
+      std::uint32_t kph = 0;
       int pv_s = 0;                      // ring stage of the next P.V tile (its V arrived with the K of S(j))
-      auto issue_pv = [&](int j) -> bool {   // O += P(j) V(j), A = P from its S buffer, 16 keys (8 columns) per step
-        if (!WaitOrAbort(&bars->p_full[j & 1], static_cast<std::uint32_t>(j >> 1) & 1U, abort_flag)) return false;
+      auto issue_s = [&](int j) -> bool {   // S(j) = Q K(j)^T, A = Q from tensor memory, 16 dims (8 columns) per step
+        if (!WaitOrAbort<true>(&bars->kv_full[ks], kph, abort_flag)) return false;
+        if (j >= 2 && !WaitOrAbort<true>(&bars->s_free[j & 1], static_cast<std::uint32_t>((j - 2) >> 1) & 1U, abort_flag))
+          return false;
         TcFenceAfter();
-        const std::uint32_t p_col = tmem + kColS + (j & 1) * kTileN;
-        const std::uint32_t lo = pv_s == 0 ? v_lo[0] : pv_s == 1 ? v_lo[1] : v_lo[2];
-        if (elected) UmmaF16Ts(o_col, p_col, lo, desc_hi, idesc_o, j > 0);
+        const std::uint32_t lo = k_lo0 + ks * (kKHalfBytes >> 4);
+        const std::uint32_t s_col = tmem + kColS + (j & 1) * kTileN;
+        if (elected) {   // one divergent region per batch of instructions, not one per instruction
 #pragma unroll
-        for (int k16 = 1; k16 < kTileN / 16; ++k16)
-          if (elected) UmmaF16Ts(o_col, p_col + k16 * 8, lo + k16 * ((16 * 128) >> 4), desc_hi, idesc_o, true);
-        if (elected) UmmaCommit(&bars->kv_empty[pv_s]);
-        if (elected) UmmaCommit(&bars->pv_done);
+          for (int i = 0; i < 16; ++i)   // 64-dim blocks 4 KB apart, 16 dims = 32 B inside a block
+            UmmaF16Ts2(s_col, q_col + i * 8, lo + (((i >> 2) * kKBlockBytes + (i & 3) * 32) >> 4), idesc_s, i > 0);
+          UmmaCommitPair(&bars->s_full[j & 1]);
+        }
+        if (++ks == kKvStages) ks = 0, kph ^= 1U;
+        return true;
+      };
+      auto issue_pv = [&](int j) -> bool {   // O += P(j) V(j), A = P from shared memory, 16 keys (32 B of a row) per step
+        if (!WaitOrAbort<true>(&bars->p_full[j & 1], static_cast<std::uint32_t>(j >> 1) & 1U, abort_flag)) return false;
+        TcFenceAfter();
+        const std::uint32_t plo = p_lo0 + (j & 1) * (kPBytes >> 4);
+        const std::uint32_t lo = v_lo0 + pv_s * (kVHalfBytes >> 4);
+        if (elected) {
+#pragma unroll
+          for (int k16 = 0; k16 < kTileN / 16; ++k16)
+            UmmaF16Ss2(o_col, plo + k16 * (32 >> 4), lo + k16 * ((16 * 128) >> 4), idesc_o, j > 0 || k16 > 0);
+          UmmaCommitPair(&bars->kv_empty[pv_s]);
+          UmmaCommitPair(&bars->pv_done[j & 1]);
+        }
         if (++pv_s == kKvStages) pv_s = 0;
         return true;
       };
-      static_assert(kKvStages == 3, "the stage selects above are written for three stages");
-      bool ok = WaitOrAbort(&bars->q_full, 0, abort_flag);
-      int s = 0;
-      std::uint32_t ph = 0;
+      bool ok = WaitOrAbort<true>(&bars->q_full, 0, abort_flag);
+      if (ok && n_tiles > 0) ok = issue_s(0);
+      if (ok && n_tiles > 1) ok = issue_s(1);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int b = j & 1;
-        ok = WaitOrAbort(&bars->kv_full[s], ph, abort_flag);
-        if (!ok) break;
-        TcFenceAfter();
-        const std::uint32_t lo = s == 0 ? k_lo[0] : s == 1 ? k_lo[1] : k_lo[2];
-        const std::uint32_t s_col = tmem + kColS + b * kTileN;
-#pragma unroll
-        for (int i = 0; i < 16; ++i)   // A = Q from tensor memory, 16 dims (8 columns) per step; 64-dim blocks 8 KB apart
-          if (elected) UmmaF16Ts(s_col, q_col + i * 8, lo + (((i >> 2) * (kTileN * 128) + (i & 3) * 32) >> 4), desc_hi, idesc_s, i > 0);
-        if (elected) UmmaCommit(&bars->s_full[b]);
-        if (++s == kKvStages) s = 0, ph ^= 1U;
-        // the previous tile's P.V goes behind this tile's S, so the tensor pipe has work while softmax(j) runs
-        if (j >= 1) ok = issue_pv(j - 1);
+        if (j + 2 < n_tiles) ok = issue_s(j + 2);
+        if (ok) ok = issue_pv(j);
       }
-      if (ok && n_tiles > 0) ok = issue_pv(n_tiles - 1);
-      if (ok && elected) UmmaCommit(&bars->o_done);
+      if (ok && elected) UmmaCommitPair(&bars->o_done);
     }
   } else {
     // ------------------ softmax, correction, epilogue: two warpgroups of one thread per query row ------------------
@@ -377,7 +433,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       TmemWaitSt();
       TcFenceBefore();
       __syncwarp();
-      if (lane == 0) MbarArrive(&bars->q_full);
+      if (lane == 0) MbarArriveCluster(MapToCta(SmemAddr(&bars->q_full), 0));
     }
     // Tiles alternate between the two warpgroups: group g = hc runs the softmax of tiles j = g, g + 2, ..., one
     // thread per query row with all 64 columns, so a tile's softmax may take up to two tile periods before it holds
@@ -398,6 +454,9 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       TmemLd32(lane_addr + kColS + hc * kTileN, *reinterpret_cast<std::uint32_t(*)[32]>(&sraw[0]));
       TmemLd32(lane_addr + kColS + hc * kTileN + 32, *reinterpret_cast<std::uint32_t(*)[32]>(&sraw[32]));
       TmemWaitLd();
+      TcFenceBefore();
+      __syncwarp();   // every lane holds its row of S: the buffer may take S(j + 2)
+      if (lane == 0) MbarArriveCluster(MapToCta(SmemAddr(&bars->s_free[hc]), 0));
       // Row max on the raw scores (the scale is positive); the causal mask only on tiles that reach past the tile's
       // first row (a warp-uniform test), where a masked score becomes -inf.
       const int key0 = (jt0 + j) * kTileN;
@@ -426,7 +485,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         // O may only be rescaled once P(j-1) V(j-1) has completed, which also means the other group has finished
         // tile j - 1 (rare path: the reference settles after the first few tiles)
         if (j >= 1) {
-          ok = WaitOrAbort(&bars->pv_done, static_cast<std::uint32_t>(j - 1) & 1U, abort_flag);
+          ok = WaitOrAbort(&bars->pv_done[hc ^ 1], static_cast<std::uint32_t>((j - 1) >> 1) & 1U, abort_flag);
           ok = __all_sync(0xFFFFFFFFU, ok);
           if (!ok) break;
           TcFenceAfter();
@@ -453,7 +512,8 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       if (lane == 0) MbarArrive(&bars->m_posted[hc]);   // release: the warp's 32 rows of m(j) are posted
       const float neg_m = m_ref == -INFINITY ? 0.0F : -m_ref;
       // p = 2^(s * scale - m): one fma + one ex2 per element; the row sum in fp32 before the fp16 rounding. P goes
-      // back into tensor memory as the A operand of P.V: 64 fp16 = the first 32 columns of this S buffer.
+      // to shared memory as the A operand of P.V: this thread's row of 64 fp16 = one 128-byte row of the K-major,
+      // 128-byte swizzled tile (16-byte chunk c of row r sits at chunk c ^ (r % 8)).
       float ls[4] = {0.0F, 0.0F, 0.0F, 0.0F};
       std::uint32_t pk[32];
 #pragma unroll
@@ -465,11 +525,21 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         pk[i] = *reinterpret_cast<const std::uint32_t*>(&h);
       }
       l_mine += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      TmemSt32(lane_addr + kColS + hc * kTileN, pk);
-      TmemWaitSt();
-      TcFenceBefore();
-      __syncwarp();   // every lane's P columns are in tensor memory: one arrival stands for the warp
-      if (lane == 0) MbarArrive(&bars->p_full[hc]);
+      if (j >= 2) {   // this group's P buffer was last read by P(j-2) V(j-2)
+        ok = WaitOrAbort(&bars->pv_done[hc], static_cast<std::uint32_t>((j - 2) >> 1) & 1U, abort_flag);
+        ok = __all_sync(0xFFFFFFFFU, ok);
+        if (!ok) break;
+      }
+      {
+        std::uint8_t* prow = smem + kSmemP + hc * kPBytes + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      }
+      FenceProxyAsync();   // the tensor core reads the tile through the async proxy
+      TcFenceBefore();     // orders a rescale of O (tcgen05.st) before the arrival
+      __syncwarp();        // every lane's row is written: one arrival stands for the warp
+      if (lane == 0) MbarArriveCluster(MapToCta(SmemAddr(&bars->p_full[hc]), 0));
     }
     // ---- epilogue: O / l * sigmoid(gate); the two groups bring their partial sums to the final reference ----
     if (ok && n_tiles > 0) {
@@ -539,18 +609,19 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
       }
     }
   }
-  // ---- teardown: every role arrives here, also after an abort ----
+  // ---- teardown: every role of both CTAs arrives here, also after an abort. Past the cluster barrier neither CTA
+  // issues tensor work on, nor arrives on barriers of, the other; then the pair's tensor memory is freed. ----
   TcFenceBefore();
-  __syncthreads();
+  ClusterSync();
   if (threadIdx.x == 0 && bars->abort_flag != 0) atomicExch(status, kStatusPrefillAbort);
   if (warp == kWarpMma) {
     TcFenceAfter();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
   }
 }
 
 // Joins the parts of a split tile: out = (sum_i 2^(m_i - M) O_i) / (sum_i 2^(m_i - M) l_i) * sigmoid(gate), parts in
-// order. One CTA per (split tile, group of 4 rows), thread = output dim; the rows of a group are independent, so their
+// order. Tiles come as pairs of heads, so the part slots of one head are two apart. One CTA per (split tile, group of 4 rows), thread = output dim; the rows of a group are independent, so their
 // loads overlap (one CTA walking all 128 rows one after the other spent ~2 us of load latency per row).
 constexpr int kMergeRows = 4;
 constexpr int kMergeMaxParts = kPrefillMaxParts;
@@ -569,7 +640,7 @@ __global__ void __launch_bounds__(kHeadDim)
 #pragma unroll
     for (int i = 0; i < kMergeMaxParts; ++i) {
       const bool on = i < np && r < t.n_rows;
-      const std::size_t row = static_cast<std::size_t>(t.part + (on ? i : 0)) * kTileM + (on ? r : 0);
+      const std::size_t row = static_cast<std::size_t>(t.part + (on ? 2 * i : 0)) * kTileM + (on ? r : 0);
       acc[rr][i] = on ? part_acc[row * kHeadDim + d] : 0.0F;
       m[rr][i] = on ? part_ml[row * 2] : -INFINITY;
       l[rr][i] = on ? part_ml[row * 2 + 1] : 0.0F;
@@ -601,8 +672,21 @@ __global__ void __launch_bounds__(kHeadDim)
 
 }  // namespace
 
-cudaError_t ConfigurePrefillKernels() {
-  return cudaFuncSetAttribute(PrefillKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmemBytes);
+cudaError_t ConfigurePrefillKernels(int* max_active_pairs) {
+  cudaError_t e = cudaFuncSetAttribute(PrefillKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmemBytes);
+  if (e != cudaSuccess) return e;
+  // A pair needs two SMs of one GPC; a GPC with an odd number of usable SMs leaves one idle.
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(2, 1, 1), cfg.blockDim = dim3(kPrefillThreads, 1, 1), cfg.dynamicSmemBytes = kPrefillSmemBytes;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr, cfg.numAttrs = 1;
+  int n = 0;
+  e = cudaOccupancyMaxActiveClusters(&n, PrefillKernel, &cfg);
+  if (e != cudaSuccess) return e;
+  *max_active_pairs = n;
+  return cudaSuccess;
 }
 
 cudaError_t LaunchPrefillDequant(const PrefillLaunch& a, cudaStream_t stream) {
@@ -624,6 +708,7 @@ cudaError_t LaunchPrefillDequant(const PrefillLaunch& a, cudaStream_t stream) {
 
 cudaError_t LaunchPrefill(const PrefillLaunch& a, cudaStream_t stream) {
   if (a.n_tiles <= 0) return cudaSuccess;
+  if ((a.n_tiles & 1) != 0) return cudaErrorInvalidValue;   // tiles come as pairs of query heads, one cluster each
   PrefillKernel<<<a.n_tiles, kPrefillThreads, kPrefillSmemBytes, stream>>>(
       *a.k16map, *a.v16map, a.tiles_dev, static_cast<const __half*>(a.q_dev), a.gate_dev, a.out_dev, a.out_f32,
       a.scale_log2, a.part_acc, a.part_ml, a.status_dev);

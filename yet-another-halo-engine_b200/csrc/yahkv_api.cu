@@ -276,7 +276,11 @@ int InitDevice(yahkv_ctx* ctx) {
     if (int r = ResizePrefillScratch(ctx, static_cast<std::int64_t>(c.max_prefill_keys) * kKvHeads); r != YAHKV_OK) return r;
   YAHKV_CUDA(ctx, ConfigureDecodeKernels());
   if (c.fmt == YAHKV_FMT_F16) YAHKV_CUDA(ctx, ConfigureF16Kernels());
-  YAHKV_CUDA(ctx, ConfigurePrefillKernels());
+  {
+    int pairs = 0;   // CTA pairs of the prefill kernel that run at the same time: the planner's wave
+    YAHKV_CUDA(ctx, ConfigurePrefillKernels(&pairs));
+    if (pairs > 0) ctx->n_sm = std::min(ctx->n_sm, 2 * pairs);
+  }
   YAHKV_CUDA(ctx, cudaDeviceSynchronize());
   ctx->has_device = true;
   return YAHKV_OK;
@@ -402,7 +406,8 @@ int ResizePrefillScratch(yahkv_ctx* ctx, std::int64_t rows) {
   YAHKV_CUDA(ctx, cudaMalloc(&ctx->v16_dev, bytes));
   ctx->device_bytes += 2 * static_cast<std::int64_t>(bytes);
   ctx->p16_rows = rows;
-  if (!EncodeTensorMap2D(&ctx->k16map, 2, ctx->k16_dev, kHeadDim, static_cast<std::uint64_t>(rows), 64, 64) ||
+  // boxes: K [32 keys][64 dims] (each CTA of a pair loads half of a tile's keys), V [64 keys][64 dims]
+  if (!EncodeTensorMap2D(&ctx->k16map, 2, ctx->k16_dev, kHeadDim, static_cast<std::uint64_t>(rows), 64, 32) ||
       !EncodeTensorMap2D(&ctx->v16map, 2, ctx->v16_dev, kHeadDim, static_cast<std::uint64_t>(rows), 64, 64))
     return Fail(ctx, YAHKV_ERR_CUDA, "tensor map encode failed for the prefill scratch");
   return YAHKV_OK;
