@@ -168,7 +168,8 @@ int yahkv_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int32_t*
  * engine/model/loom_decoder.hpp:250-261) in one launch. q_dev [n][24][256], k_dev, v_dev [n][4][256] f32 as the
  * projections produce them; q_weight_dev, k_weight_dev [256] f32 norm weights; eps the norm epsilon.
  *   K: normed, rotated, rounded to fp16, quantized and scattered exactly as yahkv_append would store that fp16 row;
- *   V: rounded to fp16, quantized and scattered;  q_out_dev [n][24][256] fp16: normed, rotated q for yahkv_attend_*.
+ *   V: rounded to fp16, quantized and scattered;  q_out_dev [n][24][256] fp16: normed, rotated q for yahkv_attend_*
+ *   (NULL: no q output, for callers that hand the raw q to yahkv_attend_prefill_qraw).
  * seq_ids / positions and the order rule as in yahkv_append. */
 int yahkv_rope_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int32_t* seq_ids, const int64_t* positions,
                       const float* q_dev, const float* k_dev, const float* v_dev, const float* q_weight_dev,
@@ -193,6 +194,16 @@ int yahkv_attend_decode(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int
 int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids,
                          const int32_t* chunk_lens, const void* q_dev, const float* gate_dev, void* out_dev,
                          int32_t out_dtype, void* stream);
+
+/* The same with the query side of the fused norm + RoPE done in the attention kernel's prologue, as the reference's
+ * prefill kernel does with its QNORM option (engine/gpu/loom/tools/gen_attn_fa.py:56-61): q_raw_dev
+ * [sum chunk_lens][24][256] f32 is the raw q projection; every row is normed (RMS over its 256 dims, x q_weight_dev
+ * [256] f32, epsilon eps), rotated at its position (len_i - chunk_lens[i] + j) and rounded to fp16 with the
+ * arithmetic of yahkv_rope_append, so the result has the bits of yahkv_rope_append's q_out_dev followed by
+ * yahkv_attend_prefill. Call yahkv_rope_append first for K and V (its q_out_dev may then be NULL). */
+int yahkv_attend_prefill_qraw(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids,
+                              const int32_t* chunk_lens, const float* q_raw_dev, const float* q_weight_dev, float eps,
+                              const float* gate_dev, void* out_dev, int32_t out_dtype, void* stream);
 
 /* One decode step of one layer with HOST buffers (what an engine without device-resident activations calls):
  * copies k/v/q (and gate) in, appends one token per sequence at its current length, attends, copies out back and

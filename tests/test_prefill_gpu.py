@@ -162,3 +162,63 @@ def test_prefill_errors_launch_nothing():
             cache.attend_prefill(0, seq_ids, chunks, q, out)
         assert e.value.code == code
     assert cache.launch_count() == before
+
+
+@pytest.mark.parametrize("fmt", [yahkv.FMT_Q8_0, yahkv.FMT_KV8A16])
+def test_raw_query_prologue_is_rope_then_attend(fmt):
+    """yahkv_attend_prefill_qraw (norm + RoPE of the raw f32 q rows inside the attention kernel's prologue, the
+    reference's QNORM option, gen_attn_fa.py:56-61) against the two-step path: the oracle's normed, rotated fp16 q rows
+    (the bits yahkv_rope_append's q_out holds) through the float64 attention model, and bit for bit against
+    yahkv_rope_append's q_out followed by yahkv_attend_prefill. A ragged batch of chunks, a 127 / 128 tile edge, rows past
+    the last tile's end, chunk positions up to 1299."""
+    rng = np.random.default_rng(45)
+    eps = 1e-6
+    cached, chunks = [0, 1000, 70], [129, 300, 58]
+    totals = [a + b for a, b in zip(cached, chunks)]
+    num_pages = sum((n + 63) // 64 for n in totals) + 2
+    cache = yahkv.KvCache(n_layers=1, num_pages=num_pages, fmt=fmt, max_seqs=3, max_pages_per_seq=24, max_batch_tokens=1024)
+    qw = (1.0 + 0.2 * rng.standard_normal(256)).astype(np.float32)
+    kw = (1.0 + 0.2 * rng.standard_normal(256)).astype(np.float32)
+    pool = O.PagedPool(yahkv.FMT_Q8_0, num_pages)   # followed for q8_0 only (the tile formats have their own tests)
+    seqs = []
+    for n, c0 in zip(totals, cached):
+        s = cache.seq_create()
+        cache.seq_reserve(s, n)
+        if c0:   # the cached part: plain fp16 rows
+            K = rng.standard_normal((c0, 4, 256)).astype(np.float16)
+            V = rng.standard_normal((c0, 4, 256)).astype(np.float16)
+            cache.append(0, np.full(c0, s, np.int32), np.arange(c0), dev(K), dev(V))
+            pool.append(cache.seq_table(s), 0, K, V)
+        seqs.append(s)
+    ids = np.concatenate([np.full(c, s, np.int32) for s, c in zip(seqs, chunks)])
+    pos = np.concatenate([np.arange(c0, c0 + c) for c0, c in zip(cached, chunks)])
+    n = len(ids)
+    q = (rng.standard_normal((n, 24, 256)) * 2).astype(np.float32)
+    k = rng.standard_normal((n, 4, 256)).astype(np.float32)
+    v = rng.standard_normal((n, 4, 256)).astype(np.float32)
+    q_dev, qw_dev = dev(q), dev(qw)
+    q_out = torch.zeros((n, 24, 256), dtype=torch.float16, device="cuda")
+    torch.cuda.synchronize()
+    cache.rope_append(0, ids, pos, q_dev, dev(k), dev(v), qw_dev, dev(kw), eps, q_out)   # K, V into the cache; q_out to compare
+    cache.sync()
+    want_q = O.rope_rows(q, qw, eps, np.repeat(pos, 24)).reshape(n, 24, 256)
+    assert np.array_equal(q_out.cpu().numpy().view(np.uint16), want_q.view(np.uint16))
+    two_step = torch.full((n, 24, 256), float("nan"), device="cuda", dtype=torch.float32)
+    fused = torch.full((n, 24, 256), float("nan"), device="cuda", dtype=torch.float32)
+    torch.cuda.synchronize()
+    cache.attend_prefill(0, seqs, chunks, q_out, two_step, out_dtype=yahkv.OUT_F32)
+    cache.attend_prefill_qraw(0, seqs, chunks, q_dev, qw_dev, eps, fused, out_dtype=yahkv.OUT_F32)
+    cache.sync()
+    a, b = two_step.cpu().numpy(), fused.cpu().numpy()
+    assert np.isfinite(b).all()
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))   # the same q bits into the same kernel
+    if fmt == yahkv.FMT_Q8_0:   # and against the float64 model
+        k16 = O.rope_rows(k, kw, eps, np.repeat(pos, 4)).reshape(n, 4, 256)
+        v16 = v.astype(np.float16)
+        row = 0
+        for s_, c0, c in zip(seqs, cached, chunks):
+            pool.append(cache.seq_table(s_), c0, k16[row:row + c], v16[row:row + c])
+            want = pool.attend_prefill_f64(cache.seq_table(s_), c0, want_q[row:row + c])
+            assert np.abs(b[row:row + c] - want).max() <= ABS_TOL
+            row += c
+    cache.close()

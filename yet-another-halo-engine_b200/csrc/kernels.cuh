@@ -124,6 +124,14 @@ struct PrefillSeq {
   std::int32_t kv_row0;     // first scratch row of the sequence
   std::int32_t pad[3];      // pad[0]: kv8a16 only, which of the sequence's two open-tile buffers is current
 };
+// What the prefill kernel's prologue needs to norm and rotate raw f32 query rows itself.
+struct PrefillQRaw {
+  const float* q;           // [rows][24][256] f32
+  const float* weight;      // [256] f32
+  const float2* rope_tab;   // (cos, sin) [rope_rows][32]
+  float eps;
+  int rope_rows;
+};
 // One tile of prefill attention: 128 query rows of one sequence for one query head.
 constexpr int kPrefillTileRows = 128;
 struct PrefillTile {
@@ -252,7 +260,12 @@ struct PrefillLaunch {
   int max_pages;            // largest n_pages of the call (grid of the dequantize pass)
   void* k16_dev;            // fp16 scratch [rows][256], K and V
   void* v16_dev;
-  const void* q_dev;        // [rows][24][256] fp16
+  const void* q_dev;        // [rows][24][256] fp16, or f32 when q_raw is set
+  bool q_raw;               // the query is the raw f32 projection: the kernel's prologue norms and rotates its rows
+  const float* q_weight_dev;   // q_raw: [256] f32 norm weights
+  float q_eps;              // q_raw: norm epsilon
+  const float2* rope_tab_dev;  // q_raw: (cos, sin) [rope_rows][32]
+  int rope_rows;
   const CUtensorMap* k16map;  // scratch as [rows][256] fp16, box 64 x 64, 128-byte swizzle
   const CUtensorMap* v16map;
   const PrefillTile* tiles_dev;

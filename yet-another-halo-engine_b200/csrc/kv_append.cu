@@ -192,7 +192,7 @@ __global__ void __launch_bounds__(kRopeThreads)
 #pragma unroll
   for (int i = 0; i < 4; ++i) hx[i] = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
   if (is_q) {
-    if (!pool.OwnsKvHead(h / kGroup)) return;   // q rows of heads another context holds stay untouched
+    if (q_out == nullptr || !pool.OwnsKvHead(h / kGroup)) return;   // no q output asked for; heads of another context
     *reinterpret_cast<uint4*>(q_out + (static_cast<std::size_t>(token) * kQHeads + h) * kHeadDim + lane * 8) =
         *reinterpret_cast<const uint4*>(hx);
     return;

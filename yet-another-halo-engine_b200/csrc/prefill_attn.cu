@@ -265,11 +265,16 @@ struct PrefillBars {
 };
 static_assert(sizeof(PrefillBars) <= kBarBytes, "the max / sum exchange follows the barriers");
 
+// kQRaw: the query arrives as the raw f32 projection (qraw) and the prologue does the query side of the fused norm +
+// RoPE kernel for its rows, to the same bits: head RMS norm with that kernel's summation order (32 chains of 8
+// consecutive dims, joined as a balanced tree), x inv x weight, NeoX RoPE on dims < 64 (pairs p, p + 32) at position
+// pos0 + row, rounded to fp16. Stands in for the reference's QNORM prologue (engine/gpu/loom/tools/gen_attn_fa.py:56-61).
+template <bool kQRaw>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPrefillThreads, 1)
     PrefillKernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
-                  const PrefillTile* __restrict__ tiles, const __half* __restrict__ q, const float* __restrict__ gate,
-                  void* out, int out_f32, float scale_log2, float* __restrict__ part_acc, float* __restrict__ part_ml,
-                  int* status) {
+                  const PrefillTile* __restrict__ tiles, const __half* __restrict__ q, const PrefillQRaw qraw,
+                  const float* __restrict__ gate, void* out, int out_f32, float scale_log2,
+                  float* __restrict__ part_acc, float* __restrict__ part_ml, int* status) {
   extern __shared__ __align__(1024) std::uint8_t smem[];
   PrefillBars* bars = reinterpret_cast<PrefillBars*>(smem + kSmemBars);
   volatile int* abort_flag = &bars->abort_flag;
@@ -416,7 +421,68 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPrefillThreads, 1)
     const int hc = threadIdx.x >> 7;                             // warpgroup
     const std::uint32_t lane_addr = tmem + (static_cast<std::uint32_t>((warp & 3) * 32) << 16);
     // Q row -> tensor memory: this thread's 128 dims (256 B) as 64 columns of fp16 pairs. Rows past the chunk are zero.
-    {
+    if constexpr (kQRaw) {
+      const bool valid = r < tile.n_rows;
+      const float* row = qraw.q + (static_cast<std::size_t>(tile.q_row0 + (valid ? r : 0)) * kQHeads + tile.head) * kHeadDim;
+      // sum of squares over the whole row: chain l covers dims 8 l .. 8 l + 7; the tree joins chain l with l + 16,
+      // then + 8, + 4, + 2, + 1 (the order of a butterfly over 32 lanes of 8 dims each)
+      float ss[32];
+#pragma unroll
+      for (int l = 0; l < 32; ++l) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(row + l * 8));
+        const float4 b = __ldg(reinterpret_cast<const float4*>(row + l * 8 + 4));
+        float acc = 0.0F;
+        acc = fmaf(a.x, a.x, acc), acc = fmaf(a.y, a.y, acc), acc = fmaf(a.z, a.z, acc), acc = fmaf(a.w, a.w, acc);
+        acc = fmaf(b.x, b.x, acc), acc = fmaf(b.y, b.y, acc), acc = fmaf(b.z, b.z, acc), acc = fmaf(b.w, b.w, acc);
+        ss[l] = acc;
+      }
+#pragma unroll
+      for (int m = 16; m >= 1; m >>= 1)
+#pragma unroll
+        for (int l = 0; l < m; ++l) ss[l] = __fadd_rn(ss[l], ss[l + m]);
+      const float inv = __fdiv_rn(1.0F, __fsqrt_rn(__fadd_rn(__fmul_rn(ss[0], 1.0F / kHeadDim), qraw.eps)));
+      const int pos = min(max(tile.pos0 + r, 0), qraw.rope_rows - 1);
+      const float2* cs_row = qraw.rope_tab + static_cast<std::size_t>(pos) * 32;
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        const int d0 = hc * (kHeadDim / 2) + part * 64;   // this thread's 64 dims of the part
+        std::uint32_t qr[32];
+        if (d0 == 0) {   // the rotary dims: pairs (p, p + 32)
+#pragma unroll
+          for (int p = 0; p < 32; p += 2) {
+            float lo[2], hi[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const float xl = __fmul_rn(__fmul_rn(__ldg(row + p + e), inv), __ldg(qraw.weight + p + e));
+              const float xh = __fmul_rn(__fmul_rn(__ldg(row + p + e + 32), inv), __ldg(qraw.weight + p + e + 32));
+              const float2 cs = __ldg(cs_row + p + e);
+              lo[e] = __fsub_rn(__fmul_rn(xl, cs.x), __fmul_rn(xh, cs.y));
+              hi[e] = __fadd_rn(__fmul_rn(xl, cs.y), __fmul_rn(xh, cs.x));
+            }
+            const __half2 hl = __floats2half2_rn(lo[0], lo[1]), hh = __floats2half2_rn(hi[0], hi[1]);
+            qr[p / 2] = *reinterpret_cast<const std::uint32_t*>(&hl);
+            qr[16 + p / 2] = *reinterpret_cast<const std::uint32_t*>(&hh);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float2 x = __ldg(reinterpret_cast<const float2*>(row + d0 + 2 * i));
+            const float2 w = __ldg(reinterpret_cast<const float2*>(qraw.weight + d0 + 2 * i));
+            const __half2 h = __floats2half2_rn(__fmul_rn(__fmul_rn(x.x, inv), w.x), __fmul_rn(__fmul_rn(x.y, inv), w.y));
+            qr[i] = *reinterpret_cast<const std::uint32_t*>(&h);
+          }
+        }
+        if (!valid) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) qr[i] = 0U;
+        }
+        TmemSt32(lane_addr + kColQ + hc * 64 + part * 32, qr);
+      }
+      TmemWaitSt();
+      TcFenceBefore();
+      __syncwarp();
+      if (lane == 0) MbarArriveCluster(MapToCta(SmemAddr(&bars->q_full), 0));
+    } else {
       const uint4* src = reinterpret_cast<const uint4*>(
           q + (static_cast<std::size_t>(tile.q_row0 + r) * kQHeads + tile.head) * kHeadDim + hc * (kHeadDim / 2));
       const bool valid = r < tile.n_rows;
@@ -673,7 +739,9 @@ __global__ void __launch_bounds__(kHeadDim)
 }  // namespace
 
 cudaError_t ConfigurePrefillKernels(int* max_active_pairs) {
-  cudaError_t e = cudaFuncSetAttribute(PrefillKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmemBytes);
+  cudaError_t e = cudaFuncSetAttribute(PrefillKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmemBytes);
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(PrefillKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmemBytes);
   if (e != cudaSuccess) return e;
   // A pair needs two SMs of one GPC; a GPC with an odd number of usable SMs leaves one idle.
   cudaLaunchConfig_t cfg{};
@@ -683,7 +751,7 @@ cudaError_t ConfigurePrefillKernels(int* max_active_pairs) {
   attr.val.clusterDim.x = 2, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
   cfg.attrs = &attr, cfg.numAttrs = 1;
   int n = 0;
-  e = cudaOccupancyMaxActiveClusters(&n, PrefillKernel, &cfg);
+  e = cudaOccupancyMaxActiveClusters(&n, PrefillKernel<false>, &cfg);
   if (e != cudaSuccess) return e;
   *max_active_pairs = n;
   return cudaSuccess;
@@ -709,9 +777,16 @@ cudaError_t LaunchPrefillDequant(const PrefillLaunch& a, cudaStream_t stream) {
 cudaError_t LaunchPrefill(const PrefillLaunch& a, cudaStream_t stream) {
   if (a.n_tiles <= 0) return cudaSuccess;
   if ((a.n_tiles & 1) != 0) return cudaErrorInvalidValue;   // tiles come as pairs of query heads, one cluster each
-  PrefillKernel<<<a.n_tiles, kPrefillThreads, kPrefillSmemBytes, stream>>>(
-      *a.k16map, *a.v16map, a.tiles_dev, static_cast<const __half*>(a.q_dev), a.gate_dev, a.out_dev, a.out_f32,
-      a.scale_log2, a.part_acc, a.part_ml, a.status_dev);
+  if (a.q_raw) {
+    const PrefillQRaw qr{static_cast<const float*>(a.q_dev), a.q_weight_dev, a.rope_tab_dev, a.q_eps, a.rope_rows};
+    PrefillKernel<true><<<a.n_tiles, kPrefillThreads, kPrefillSmemBytes, stream>>>(
+        *a.k16map, *a.v16map, a.tiles_dev, nullptr, qr, a.gate_dev, a.out_dev, a.out_f32, a.scale_log2, a.part_acc,
+        a.part_ml, a.status_dev);
+  } else {
+    PrefillKernel<false><<<a.n_tiles, kPrefillThreads, kPrefillSmemBytes, stream>>>(
+        *a.k16map, *a.v16map, a.tiles_dev, static_cast<const __half*>(a.q_dev), PrefillQRaw{}, a.gate_dev, a.out_dev,
+        a.out_f32, a.scale_log2, a.part_acc, a.part_ml, a.status_dev);
+  }
   if (a.n_merges > 0)
     PrefillMergeKernel<<<dim3(a.n_merges, kTileM / kMergeRows), kHeadDim, 0, stream>>>(a.merges_dev, a.tiles_dev, a.part_acc, a.part_ml, a.gate_dev,
                                                           a.out_dev, a.out_f32);

@@ -666,7 +666,7 @@ int yahkv_rope_append(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const int
   if (int r = RequireDevice(ctx, "rope_append"); r != YAHKV_OK) return r;
   if (n_tokens > ctx->cfg.max_batch_tokens) return Fail(ctx, YAHKV_ERR_CAPACITY, "rope_append: more tokens than max_batch_tokens");
   if (n_tokens > 0 && (q_dev == nullptr || k_dev == nullptr || v_dev == nullptr || q_weight_dev == nullptr ||
-                       k_weight_dev == nullptr || q_out_dev == nullptr))
+                       k_weight_dev == nullptr))   // q_out_dev may be null: the query side is then left to the caller
     return Fail(ctx, YAHKV_ERR_INVALID, "rope_append: null pointer");
   if (!(eps >= 0.0F)) return Fail(ctx, YAHKV_ERR_INVALID, "rope_append: eps must be non-negative");
   if (int r = EnsureRopeTable(ctx); r != YAHKV_OK) return r;   // before the plan: a failure here changes no state
@@ -788,10 +788,33 @@ int yahkv_attend_decode(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int
   return YAHKV_OK;
 }
 
+static int AttendPrefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids, const int32_t* chunk_lens,
+                         const void* q_dev, bool q_raw, const float* q_weight_dev, float eps, const float* gate_dev,
+                         void* out_dev, int32_t out_dtype, void* stream);
+
 int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids,
                          const int32_t* chunk_lens, const void* q_dev, const float* gate_dev, void* out_dev,
                          int32_t out_dtype, void* stream) {
+  return AttendPrefill(ctx, layer, n_seqs, seq_ids, chunk_lens, q_dev, false, nullptr, 0.0F, gate_dev, out_dev, out_dtype,
+                       stream);
+}
+
+int yahkv_attend_prefill_qraw(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids,
+                              const int32_t* chunk_lens, const float* q_raw_dev, const float* q_weight_dev, float eps,
+                              const float* gate_dev, void* out_dev, int32_t out_dtype, void* stream) {
+  if (ctx == nullptr) return YAHKV_ERR_INVALID;
+  if (n_seqs > 0 && q_weight_dev == nullptr) return Fail(ctx, YAHKV_ERR_INVALID, "attend_prefill_qraw: null norm weights");
+  if (!(eps >= 0.0F)) return Fail(ctx, YAHKV_ERR_INVALID, "attend_prefill_qraw: eps must be non-negative");
+  return AttendPrefill(ctx, layer, n_seqs, seq_ids, chunk_lens, q_raw_dev, true, q_weight_dev, eps, gate_dev, out_dev,
+                       out_dtype, stream);
+}
+
+static int AttendPrefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids, const int32_t* chunk_lens,
+                         const void* q_dev, bool q_raw, const float* q_weight_dev, float eps, const float* gate_dev,
+                         void* out_dev, int32_t out_dtype, void* stream) {
   if (int r = RequireDevice(ctx, "attend_prefill"); r != YAHKV_OK) return r;
+  if (q_raw)
+    if (int r = EnsureRopeTable(ctx); r != YAHKV_OK) return r;
   if (out_dtype != YAHKV_OUT_F16 && out_dtype != YAHKV_OUT_F32) return Fail(ctx, YAHKV_ERR_INVALID, "attend_prefill: bad out_dtype");
   if (n_seqs > 0 && (q_dev == nullptr || out_dev == nullptr)) return Fail(ctx, YAHKV_ERR_INVALID, "attend_prefill: null q or out pointer");
   if ((reinterpret_cast<std::uintptr_t>(q_dev) & 15) != 0 || (reinterpret_cast<std::uintptr_t>(out_dev) & 15) != 0)
@@ -838,6 +861,7 @@ int yahkv_attend_prefill(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const in
   a.seqs_dev = ctx->pseqs_dev, a.n_seqs = n_seqs, a.max_pages = max_pages;
   a.k16_dev = ctx->k16_dev, a.v16_dev = ctx->v16_dev;
   a.q_dev = q_dev, a.k16map = &ctx->k16map, a.v16map = &ctx->v16map;
+  a.q_raw = q_raw, a.q_weight_dev = q_weight_dev, a.q_eps = eps, a.rope_tab_dev = ctx->rope_tab_dev, a.rope_rows = ctx->rope_rows;
   a.tiles_dev = ctx->tiles_dev, a.n_tiles = static_cast<int>(ctx->tile_scratch.size());
   a.merges_dev = ctx->merges_dev, a.n_merges = static_cast<int>(ctx->merge_scratch.size());
   a.part_acc = ctx->part_acc_dev, a.part_ml = ctx->part_ml_dev;

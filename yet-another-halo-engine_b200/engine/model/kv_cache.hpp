@@ -126,6 +126,15 @@ class KvCache {
     Check(yahkv_attend_prefill(ctx_, layer, static_cast<std::int32_t>(seqs.size()), seqs.data(), chunks.data(), q_dev,
                                gate_dev, out_dev, out_dtype, stream));
   }
+  // AttendPrefill on the raw f32 q projection: the attention kernel's prologue norms and rotates its rows (the
+  // reference's QNORM option, engine/gpu/loom/tools/gen_attn_fa.py:56-61); RopeAppend may then get a null q_out_dev.
+  void AttendPrefillRawQ(std::int32_t layer, const std::vector<std::int32_t>& seqs, const std::vector<std::int32_t>& chunks,
+                         const float* q_raw_dev, const float* q_weight_dev, float eps, const float* gate_dev,
+                         void* out_dev, std::int32_t out_dtype = YAHKV_OUT_F16, void* stream = nullptr) {
+    if (seqs.size() != chunks.size()) throw KvError(YAHKV_ERR_INVALID, "kv cache: one chunk length per sequence expected");
+    Check(yahkv_attend_prefill_qraw(ctx_, layer, static_cast<std::int32_t>(seqs.size()), seqs.data(), chunks.data(),
+                                    q_raw_dev, q_weight_dev, eps, gate_dev, out_dev, out_dtype, stream));
+  }
   // One layer of a decode step with page-locked HOST buffers, queued without waiting; WaitHostSteps() collects them.
   void DecodeStepHostAsync(std::int32_t layer, const std::vector<std::int32_t>& seqs, const void* k_host,
                            const void* v_host, const void* q_host, const float* gate_host, void* out_host,

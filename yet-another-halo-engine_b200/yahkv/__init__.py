@@ -144,6 +144,7 @@ SIGNATURES = {
     "yahkv_append_slots": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP]),
     "yahkv_attend_decode": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _I32, _I32, _VP]),
     "yahkv_attend_prefill": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _VP, _I32, _VP]),
+    "yahkv_attend_prefill_qraw": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, ctypes.c_float, _VP, _VP, _I32, _VP]),
     "yahkv_decode_step_host": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _VP, _VP, _I32]),
     "yahkv_decode_step_host_async": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _VP, _VP, _I32]),
     "yahkv_decode_step_host_wait": (_I32, [_VP]),
@@ -367,6 +368,14 @@ class KvCache:
         seq_ids, chunk_lens = _i32(seq_ids), _i32(chunk_lens)
         self._check(lib.yahkv_attend_prefill(self._h, layer, len(seq_ids), _ptr(seq_ids), _ptr(chunk_lens), _ptr(q),
                                              _ptr(gate), _ptr(out), out_dtype, _ptr(stream)))
+
+    def attend_prefill_qraw(self, layer, seq_ids, chunk_lens, q_raw, q_weight, eps, out, gate=None, out_dtype=OUT_F16,
+                            stream=None):
+        """attend_prefill on the raw f32 q projection: the kernel's prologue norms and rotates its rows."""
+        seq_ids, chunk_lens = _i32(seq_ids), _i32(chunk_lens)
+        self._check(lib.yahkv_attend_prefill_qraw(self._h, layer, len(seq_ids), _ptr(seq_ids), _ptr(chunk_lens),
+                                                  _ptr(q_raw), _ptr(q_weight), float(eps), _ptr(gate), _ptr(out),
+                                                  out_dtype, _ptr(stream)))
 
     def decode_step_host(self, layer, seq_ids, k, v, q, out, gate=None, out_dtype=OUT_F16):
         seq_ids = _i32(seq_ids)
