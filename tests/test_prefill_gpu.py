@@ -127,8 +127,8 @@ def test_full_size_chunk_properties():
 
 
 def test_tail_tiles_split_along_the_keys():
-    """With 20 SMs to fill, the 48 tiles of this call leave a last wave of 8: those are split into two key ranges each
-    and joined by the merge kernel (three launches instead of two). Results against the oracle, gate and fp16 output
+    """With 20 SMs (10 SM pairs) to fill, the 24 tile pairs of this call leave a last wave of 4: those are split into
+    two key ranges each and joined by the merge kernel (three launches instead of two). Results against the oracle, gate and fp16 output
     included, and against the unsplit run."""
     cached, chunk = 500, 129
     runs = []
