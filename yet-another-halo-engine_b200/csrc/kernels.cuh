@@ -266,7 +266,7 @@ struct PrefillLaunch {
   float q_eps;              // q_raw: norm epsilon
   const float2* rope_tab_dev;  // q_raw: (cos, sin) [rope_rows][32]
   int rope_rows;
-  const CUtensorMap* k16map;  // scratch as [rows][256] fp16, box 64 x 64, 128-byte swizzle
+  const CUtensorMap* k16map;  // scratch as [rows][256] fp16, 128-byte swizzle; boxes K 64 dims x 32 keys, V 64 x 64
   const CUtensorMap* v16map;
   const PrefillTile* tiles_dev;
   int n_tiles;
