@@ -281,8 +281,9 @@ int yahkv_launch_count(const yahkv_ctx* ctx, int64_t* launches);
  * its device-side polls the same way and leaves a sticky status (engine/gpu/loom/tools/gen_chain.py:12-19). Nothing
  * traps or faults, the context stays usable.
  * yahkv_debug_set_prefill_sms sets the number of SMs whose last partly filled wave the prefill planner splits along
- * the keys (0 = never split, at most the device's count, which is the default), so a small test reaches the split
- * and merge path. */
+ * the keys (0 = never split, at most the device's count; the default is twice the number of CTA pairs the device
+ * runs at once). The kernel runs CTA pairs, so the wave is n_sm / 2 pairs. A small test reaches the split and merge
+ * path this way. */
 int yahkv_debug_wait_timeout(yahkv_ctx* ctx, int64_t limit_us, void* stream);
 int yahkv_debug_set_prefill_sms(yahkv_ctx* ctx, int32_t n_sm);
 
