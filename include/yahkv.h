@@ -187,6 +187,16 @@ int yahkv_append_slots(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const in
 int yahkv_attend_decode(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids, const void* q_dev,
                         const float* gate_dev, void* out_dev, int32_t out_dtype, int32_t n_splits, void* stream);
 
+/* The same on the raw f32 q projection (q_raw_dev [n_seqs][24][256] f32): the attention kernel's prologue norms every
+ * head row (RMS over its 256 dims, x q_weight_dev [256] f32, epsilon eps), rotates it at the position of the
+ * sequence's newest key (len - 1: append first) and rounds it to fp16 with the arithmetic of yahkv_rope_append, so the
+ * result has the bits of yahkv_rope_append's q_out_dev followed by yahkv_attend_decode. The attend-side half of the
+ * reference's norm + RoPE fusion (engine/gpu/loom/yah_fused_qk_rope_f32.loom:1-9; gen_attn_fa.py:56-61 for prefill).
+ * q_raw_dev and q_weight_dev 16-byte aligned. */
+int yahkv_attend_decode_qraw(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids, const float* q_raw_dev,
+                             const float* q_weight_dev, float eps, const float* gate_dev, void* out_dev,
+                             int32_t out_dtype, int32_t n_splits, void* stream);
+
 /* Replaces yah_attn_wmma (engine/model/loom_prefill.hpp:3393-3447): causal attention of one chunk per sequence over
  * the cache, which already holds the chunk (append first). Sequence i contributes chunk_lens[i] query rows, packed in
  * order: q_dev [sum chunk_lens][24][256] fp16; row j of sequence i sits at position len_i - chunk_lens[i] + j and sees

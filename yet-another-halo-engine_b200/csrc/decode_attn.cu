@@ -46,6 +46,7 @@
 #include <cmath>
 
 #include "decode_ring.cuh"
+#include "qrope.cuh"
 #include "kernels.cuh"
 #include "ptx.cuh"
 
@@ -152,12 +153,14 @@ constexpr int kStatusSmemMisaligned = 2;
 // <= 2^4, so weight x scale fits fp16 for every representable fp16 input.
 constexpr float kLazyRescale = 4.0F;
 
-template <int kFmt>
+// kQRaw: the query is the raw f32 projection (qraw) and the prologue norms and rotates the unit's six head rows itself,
+// at the position of the sequence's newest key (qrope.cuh).
+template <int kFmt, bool kQRaw>
 __global__ void __launch_bounds__(Shape<kFmt>::kThreads, Shape<kFmt>::kCtas)
     DecodePartKernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                      PoolView pool, int layer, const std::int32_t* __restrict__ tables, int table_stride,
-                     const DecodeUnit* __restrict__ units, const __half* __restrict__ q, float scale_log2,
-                     float* __restrict__ partial_acc, float* __restrict__ partial_ml, int* status) {
+                     const DecodeUnit* __restrict__ units, const __half* __restrict__ q, const QueryRaw qraw,
+                     float scale_log2, float* __restrict__ partial_acc, float* __restrict__ partial_ml, int* status) {
   ChainedKernelEntry();
   using L = StageLayout<kFmt>;
   using S = SmemLayout<kFmt>;
@@ -230,8 +233,8 @@ __global__ void __launch_bounds__(Shape<kFmt>::kThreads, Shape<kFmt>::kCtas)
   //   a0 = hi of elements 4t .. 4t+3, a1 = lo of the same, a2 = hi of elements 16+4t .. 16+4t+3, a3 = lo of those,
   // so that rows 0-5 of the MMA are the hi plane and rows 8-13 the lo plane of the six heads.
   for (int hq = warp; hq < kGroup; hq += kWarps) {   // one head per warp (per pass, in a CTA of fewer than six warps)
-    const __half* qrow = q + (static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + hq) * kHeadDim;
-    const uint4 raw = *reinterpret_cast<const uint4*>(qrow + 8 * lane);
+    const uint4 raw = LoadQueryLane8<kQRaw>(q, qraw, static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + hq,
+                                            u.n_keys - 1, lane);
     const __half2* hp = reinterpret_cast<const __half2*>(&raw);
     float x[8];
     float amax = 0.0F;
@@ -552,23 +555,30 @@ __global__ void __launch_bounds__(kHeadDim)
 }  // namespace
 
 cudaError_t ConfigureDecodeKernels() {
-  cudaError_t e = cudaFuncSetAttribute(DecodePartKernel<kFmtQ8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(DecodePartKernel<kFmtQ8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        DecodeSmemBytes<kFmtQ8>());
-  if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(DecodePartKernel<kFmtQ4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              DecodeSmemBytes<kFmtQ4>());
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(DecodePartKernel<kFmtQ8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeSmemBytes<kFmtQ8>());
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(DecodePartKernel<kFmtQ4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeSmemBytes<kFmtQ4>());
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(DecodePartKernel<kFmtQ4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeSmemBytes<kFmtQ4>());
+  return e;
+}
+
+template <int kFmt, bool kQRaw>
+static cudaError_t LaunchPart(const DecodeLaunch& a, cudaStream_t stream) {
+  const QueryRaw qr{kQRaw ? static_cast<const float*>(a.q_dev) : nullptr, a.q_weight_dev, a.rope_tab_dev, a.q_eps, a.rope_rows};
+  return LaunchChained(DecodePartKernel<kFmt, kQRaw>, a.n_units, Shape<kFmt>::kThreads, DecodeSmemBytes<kFmt>(), stream,
+                       *a.kmap, *a.vmap, a.pool, a.layer, a.tables_dev, a.table_stride, a.units_dev,
+                       kQRaw ? nullptr : static_cast<const __half*>(a.q_dev), qr, a.scale_log2, a.partial_acc,
+                       a.partial_ml, a.status_dev);
 }
 
 cudaError_t LaunchDecodePart(const DecodeLaunch& a, cudaStream_t stream) {
   if (a.n_units <= 0 || a.n_seqs <= 0) return cudaSuccess;
-  const auto* q = static_cast<const __half*>(a.q_dev);
-  if (a.pool.fmt == kFmtQ8)
-    return LaunchChained(DecodePartKernel<kFmtQ8>, a.n_units, Shape<kFmtQ8>::kThreads, DecodeSmemBytes<kFmtQ8>(), stream, *a.kmap,
-                         *a.vmap, a.pool, a.layer, a.tables_dev, a.table_stride, a.units_dev, q, a.scale_log2,
-                         a.partial_acc, a.partial_ml, a.status_dev);
-  return LaunchChained(DecodePartKernel<kFmtQ4>, a.n_units, Shape<kFmtQ4>::kThreads, DecodeSmemBytes<kFmtQ4>(), stream, *a.kmap,
-                       *a.vmap, a.pool, a.layer, a.tables_dev, a.table_stride, a.units_dev, q, a.scale_log2,
-                       a.partial_acc, a.partial_ml, a.status_dev);
+  if (a.pool.fmt == kFmtQ8) return a.q_raw ? LaunchPart<kFmtQ8, true>(a, stream) : LaunchPart<kFmtQ8, false>(a, stream);
+  return a.q_raw ? LaunchPart<kFmtQ4, true>(a, stream) : LaunchPart<kFmtQ4, false>(a, stream);
 }
 
 cudaError_t LaunchDecodeCombine(const DecodeLaunch& a, cudaStream_t stream) {

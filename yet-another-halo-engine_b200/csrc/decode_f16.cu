@@ -16,6 +16,7 @@
 #include <cmath>
 
 #include "decode_ring.cuh"
+#include "qrope.cuh"
 #include "kernels.cuh"
 #include "ptx.cuh"
 
@@ -46,10 +47,12 @@ static_assert(kWarps * kDecodeMergeWarpFloats * 4 <= kRingBytes, "the merge scra
 constexpr float kLazyRescale = 4.0F;
 constexpr int kStatusSmemMisaligned = 2;
 
+template <bool kQRaw>   // kQRaw: the raw f32 query, normed and rotated in the prologue (qrope.cuh)
 __global__ void __launch_bounds__(kThreads, 1)
     F16DecodePartKernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                         PoolView pool, int layer, const std::int32_t* __restrict__ tables, int table_stride,
-                        const DecodeUnit* __restrict__ units, const __half* __restrict__ q, float scale_log2,
+                        const DecodeUnit* __restrict__ units, const __half* __restrict__ q, const QueryRaw qraw,
+                        float scale_log2,
                         float* __restrict__ partial_acc, float* __restrict__ partial_ml, int* status) {
   ChainedKernelEntry();
   extern __shared__ __align__(1024) std::uint8_t smem[];
@@ -111,8 +114,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   // (g = head, t) are a0 = dims 16 ks + 2t, + 1 and a2 = dims 16 ks + 8 + 2t, + 1 (rows 8-15 of the MMA stay zero).
   // Lane l of the warp holds dims 8 l .. 8 l + 7 = step l / 2, half l % 2: its four dword pairs go to t = 0 .. 3.
   if (warp < kGroup) {
-    const __half* qrow = q + (static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + warp) * kHeadDim;
-    const uint4 raw = *reinterpret_cast<const uint4*>(qrow + 8 * lane);
+    const uint4 raw = LoadQueryLane8<kQRaw>(q, qraw, static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + warp,
+                                            u.n_keys - 1, lane);
     const std::uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
     const int ks = lane >> 1, half = lane & 1;
 #pragma unroll
@@ -228,14 +231,22 @@ __global__ void __launch_bounds__(kThreads, 1)
 }  // namespace
 
 cudaError_t ConfigureF16Kernels() {
-  return cudaFuncSetAttribute(F16DecodePartKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  cudaError_t e = cudaFuncSetAttribute(F16DecodePartKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(F16DecodePartKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
 }
 
 cudaError_t LaunchF16DecodePart(const DecodeLaunch& a, cudaStream_t stream) {
   if (a.n_units <= 0 || a.n_seqs <= 0) return cudaSuccess;
-  return LaunchChained(F16DecodePartKernel, a.n_units, kThreads, kSmemBytes, stream, *a.kmap, *a.vmap, a.pool, a.layer,
-                       a.tables_dev, a.table_stride, a.units_dev, static_cast<const __half*>(a.q_dev), a.scale_log2,
-                       a.partial_acc, a.partial_ml, a.status_dev);
+  if (a.q_raw) {
+    const QueryRaw qr{static_cast<const float*>(a.q_dev), a.q_weight_dev, a.rope_tab_dev, a.q_eps, a.rope_rows};
+    return LaunchChained(F16DecodePartKernel<true>, a.n_units, kThreads, kSmemBytes, stream, *a.kmap, *a.vmap, a.pool,
+                         a.layer, a.tables_dev, a.table_stride, a.units_dev, static_cast<const __half*>(nullptr), qr,
+                         a.scale_log2, a.partial_acc, a.partial_ml, a.status_dev);
+  }
+  return LaunchChained(F16DecodePartKernel<false>, a.n_units, kThreads, kSmemBytes, stream, *a.kmap, *a.vmap, a.pool,
+                       a.layer, a.tables_dev, a.table_stride, a.units_dev, static_cast<const __half*>(a.q_dev), QueryRaw{},
+                       a.scale_log2, a.partial_acc, a.partial_ml, a.status_dev);
 }
 
 }  // namespace yahkv

@@ -124,10 +124,11 @@ struct PrefillSeq {
   std::int32_t kv_row0;     // first scratch row of the sequence
   std::int32_t pad[3];      // pad[0]: kv8a16 only, which of the sequence's two open-tile buffers is current
 };
-// What the prefill kernel's prologue needs to norm and rotate raw f32 query rows itself.
-struct PrefillQRaw {
-  const float* q;           // [rows][24][256] f32
-  const float* weight;      // [256] f32
+// What an attention kernel needs to norm and rotate raw f32 query rows itself (the query side of the fused norm + RoPE
+// kernel, done in the attention kernel's prologue).
+struct QueryRaw {
+  const float* q;           // [rows][24][256] f32, the raw q projection
+  const float* weight;      // [256] f32 norm weights
   const float2* rope_tab;   // (cos, sin) [rope_rows][32]
   float eps;
   int rope_rows;
@@ -197,7 +198,12 @@ struct DecodeLaunch {
   int n_units;
   const CombineItem* items_dev;
   int n_seqs;
-  const void* q_dev;
+  const void* q_dev;        // [n_seqs][24][256] fp16, or f32 when q_raw is set
+  bool q_raw;               // the query is the raw f32 projection: the part kernel's prologue norms and rotates it
+  const float* q_weight_dev;   // q_raw: [256] f32 norm weights
+  float q_eps;
+  const float2* rope_tab_dev;  // q_raw: (cos, sin) [rope_rows][32]
+  int rope_rows;
   const float* gate_dev;
   void* out_dev;
   int out_f32;

@@ -19,6 +19,7 @@
 #include <cmath>
 
 #include "decode_ring.cuh"
+#include "qrope.cuh"
 #include "kernels.cuh"
 #include "ptx.cuh"
 
@@ -189,10 +190,12 @@ __device__ __forceinline__ std::uint32_t PackBytes(int b0, int b1, int b2, int b
          ((static_cast<std::uint32_t>(b2) & 255U) << 16) | ((static_cast<std::uint32_t>(b3) & 255U) << 24);
 }
 
+template <bool kQRaw>   // kQRaw: the raw f32 query, normed and rotated in the prologue (qrope.cuh)
 __global__ void __launch_bounds__(kThreads, kCtas)
     Kv4DecodePartKernel(const __grid_constant__ CUtensorMap kmap, PoolView pool, int layer,
                         const std::int32_t* __restrict__ tables, int table_stride, const DecodeUnit* __restrict__ units,
-                        const __half* __restrict__ q, float scale_log2, const __half* __restrict__ open_tiles,
+                        const __half* __restrict__ q, const QueryRaw qraw, float scale_log2,
+                        const __half* __restrict__ open_tiles,
                         int n_layers, float* __restrict__ partial_acc, float* __restrict__ partial_ml, int* status) {
   ChainedKernelEntry();
   extern __shared__ __align__(1024) std::uint8_t smem[];
@@ -254,8 +257,8 @@ __global__ void __launch_bounds__(kThreads, kCtas)
   // group (4 lanes) and lane, the A operand of the integer MMA: bytes in the order the code nibbles unpack
   // (dims 0, 4, 1, 5 of the lane's 8, then 2, 6, 3, 7), hi plane in rows 0-5, lo plane in rows 8-13.
   for (int hq = warp; hq < kGroup; hq += kWarps) {   // one head per warp and pass
-    const __half* qrow = q + (static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + hq) * kHeadDim;
-    const uint4 raw = *reinterpret_cast<const uint4*>(qrow + 8 * lane);
+    const uint4 raw = LoadQueryLane8<kQRaw>(q, qraw, static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + hq,
+                                            u.n_keys - 1, lane);
     const __half2* hp = reinterpret_cast<const __half2*>(&raw);
     float x[8];
 #pragma unroll
@@ -568,7 +571,9 @@ __global__ void __launch_bounds__(kDequantThreads)
 }  // namespace
 
 cudaError_t ConfigureKv4Kernels() {
-  return cudaFuncSetAttribute(Kv4DecodePartKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  cudaError_t e = cudaFuncSetAttribute(Kv4DecodePartKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(Kv4DecodePartKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
 }
 
 cudaError_t LaunchKv4AppendK(const PoolView& pool, int layer, int n_tokens, const std::int64_t* slots_dev,
@@ -581,9 +586,16 @@ cudaError_t LaunchKv4AppendK(const PoolView& pool, int layer, int n_tokens, cons
 
 cudaError_t LaunchKv4DecodePart(const DecodeLaunch& a, const void* open_tiles_dev, int n_layers, cudaStream_t stream) {
   if (a.n_units <= 0 || a.n_seqs <= 0) return cudaSuccess;
-  return LaunchChained(Kv4DecodePartKernel, a.n_units, kThreads, kSmemBytes, stream, *a.kmap, a.pool, a.layer,
-                       a.tables_dev, a.table_stride, a.units_dev, static_cast<const __half*>(a.q_dev), a.scale_log2,
-                       static_cast<const __half*>(open_tiles_dev), n_layers, a.partial_acc, a.partial_ml, a.status_dev);
+  const auto* open16 = static_cast<const __half*>(open_tiles_dev);
+  if (a.q_raw) {
+    const QueryRaw qr{static_cast<const float*>(a.q_dev), a.q_weight_dev, a.rope_tab_dev, a.q_eps, a.rope_rows};
+    return LaunchChained(Kv4DecodePartKernel<true>, a.n_units, kThreads, kSmemBytes, stream, *a.kmap, a.pool, a.layer,
+                         a.tables_dev, a.table_stride, a.units_dev, static_cast<const __half*>(nullptr), qr, a.scale_log2,
+                         open16, n_layers, a.partial_acc, a.partial_ml, a.status_dev);
+  }
+  return LaunchChained(Kv4DecodePartKernel<false>, a.n_units, kThreads, kSmemBytes, stream, *a.kmap, a.pool, a.layer,
+                       a.tables_dev, a.table_stride, a.units_dev, static_cast<const __half*>(a.q_dev), QueryRaw{},
+                       a.scale_log2, open16, n_layers, a.partial_acc, a.partial_ml, a.status_dev);
 }
 
 cudaError_t LaunchKv4PrefillDequant(const PrefillLaunch& a, const void* open_tiles_dev, int n_layers, cudaStream_t stream) {

@@ -30,6 +30,7 @@
 #include <cmath>
 
 #include "decode_ring.cuh"
+#include "qrope.cuh"
 #include "kernels.cuh"
 #include "ptx.cuh"
 
@@ -241,10 +242,12 @@ __device__ __forceinline__ void LoadQ4(std::uint32_t (&a)[4], std::uint32_t addr
   asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(addr));
 }
 
+template <bool kQRaw>   // kQRaw: the raw f32 query, normed and rotated in the prologue (qrope.cuh)
 __global__ void __launch_bounds__(kKv8Threads, 2)
     Kv8DecodePartKernel(const __grid_constant__ CUtensorMap kmap, PoolView pool, int layer,
                         const std::int32_t* __restrict__ tables, int table_stride, const DecodeUnit* __restrict__ units,
-                        const __half* __restrict__ q, float scale_log2, const __half* __restrict__ open_tiles,
+                        const __half* __restrict__ q, const QueryRaw qraw, float scale_log2,
+                        const __half* __restrict__ open_tiles,
                         int n_layers, float* __restrict__ partial_acc, float* __restrict__ partial_ml, int* status) {
   ChainedKernelEntry();
   extern __shared__ __align__(1024) std::uint8_t smem[];
@@ -307,8 +310,8 @@ __global__ void __launch_bounds__(kKv8Threads, 2)
   // lo = q16 - 256 hi. The A operand of 32-byte block b for lane (g = head, t): a0 = hi bytes 4t .. 4t+3, a1 = lo of the
   // same, a2 = hi bytes 16+4t .., a3 = lo of those: rows 0-5 of the MMA are the hi plane, rows 8-13 the lo plane.
   if (warp < kGroup) {
-    const __half* qrow = q + (static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + warp) * kHeadDim;
-    const uint4 raw = *reinterpret_cast<const uint4*>(qrow + 8 * lane);
+    const uint4 raw = LoadQueryLane8<kQRaw>(q, qraw, static_cast<std::size_t>(u.batch) * kQHeads + u.kvh * kGroup + warp,
+                                            u.n_keys - 1, lane);
     const __half2* hp = reinterpret_cast<const __half2*>(&raw);
     float x[8], amax = 0.0F;
 #pragma unroll
@@ -617,7 +620,9 @@ __global__ void __launch_bounds__(kKv8DequantThreads)
 }  // namespace
 
 cudaError_t ConfigureKv8Kernels() {
-  return cudaFuncSetAttribute(Kv8DecodePartKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kKv8SmemBytes);
+  cudaError_t e = cudaFuncSetAttribute(Kv8DecodePartKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kKv8SmemBytes);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(Kv8DecodePartKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kKv8SmemBytes);
 }
 
 cudaError_t LaunchKv8AppendK(const PoolView& pool, int layer, int n_tokens, const std::int64_t* slots_dev,
@@ -640,9 +645,16 @@ cudaError_t LaunchKv8AppendV(const PoolView& pool, int layer, int n_work, const 
 
 cudaError_t LaunchKv8DecodePart(const DecodeLaunch& a, const void* open_tiles_dev, int n_layers, cudaStream_t stream) {
   if (a.n_units <= 0 || a.n_seqs <= 0) return cudaSuccess;
-  return LaunchChained(Kv8DecodePartKernel, a.n_units, kKv8Threads, kKv8SmemBytes, stream, *a.kmap, a.pool, a.layer,
-                       a.tables_dev, a.table_stride, a.units_dev, static_cast<const __half*>(a.q_dev), a.scale_log2,
-                       static_cast<const __half*>(open_tiles_dev), n_layers, a.partial_acc, a.partial_ml, a.status_dev);
+  const auto* open16 = static_cast<const __half*>(open_tiles_dev);
+  if (a.q_raw) {
+    const QueryRaw qr{static_cast<const float*>(a.q_dev), a.q_weight_dev, a.rope_tab_dev, a.q_eps, a.rope_rows};
+    return LaunchChained(Kv8DecodePartKernel<true>, a.n_units, kKv8Threads, kKv8SmemBytes, stream, *a.kmap, a.pool, a.layer,
+                         a.tables_dev, a.table_stride, a.units_dev, static_cast<const __half*>(nullptr), qr, a.scale_log2,
+                         open16, n_layers, a.partial_acc, a.partial_ml, a.status_dev);
+  }
+  return LaunchChained(Kv8DecodePartKernel<false>, a.n_units, kKv8Threads, kKv8SmemBytes, stream, *a.kmap, a.pool, a.layer,
+                       a.tables_dev, a.table_stride, a.units_dev, static_cast<const __half*>(a.q_dev), QueryRaw{},
+                       a.scale_log2, open16, n_layers, a.partial_acc, a.partial_ml, a.status_dev);
 }
 
 cudaError_t LaunchKv8PrefillDequant(const PrefillLaunch& a, const void* open_tiles_dev, int n_layers, cudaStream_t stream) {

@@ -18,6 +18,7 @@
 
 #include "kernels.cuh"
 #include "ptx.cuh"
+#include "qrope.cuh"
 
 namespace yahkv {
 namespace {
@@ -142,7 +143,6 @@ __global__ void __launch_bounds__(kAppendThreads) AppendKernel(PoolView pool, in
 // reproduces the bits.
 // ----------------------------------------------------------------------------------------------------------------
 constexpr int kRopeThreads = 32 * (kQHeads + 2 * kKvHeads);
-constexpr int kHalfRot = 32;   // rotary_dim 64
 
 template <int kFmt>
 __global__ void __launch_bounds__(kRopeThreads)
@@ -163,31 +163,7 @@ __global__ void __launch_bounds__(kRopeThreads)
     const float4 b = *reinterpret_cast<const float4*>(src + lane * 8 + 4);
     x[0] = a.x, x[1] = a.y, x[2] = a.z, x[3] = a.w, x[4] = b.x, x[5] = b.y, x[6] = b.z, x[7] = b.w;
   }
-  if (!is_v) {
-    float acc = 0.0F;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc = fmaf(x[j], x[j], acc);
-#pragma unroll
-    for (int m = 16; m >= 1; m >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFU, acc, m));
-    const float inv = __fdiv_rn(1.0F, __fsqrt_rn(__fadd_rn(__fmul_rn(acc, 1.0F / kHeadDim), eps)));
-    const float* wp = (is_q ? q_weight : k_weight) + lane * 8;
-    const float4 wa = *reinterpret_cast<const float4*>(wp), wb = *reinterpret_cast<const float4*>(wp + 4);
-    const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
-#pragma unroll
-    for (int j = 0; j < 8; ++j) x[j] = __fmul_rn(__fmul_rn(x[j], inv), w[j]);
-    // dims 0 .. 63 sit in lanes 0 .. 7; dim p pairs with p + 32, i.e. lane l with lane l ^ 4, same j
-    const int pos = min(max(positions[token], 0), rope_rows - 1);
-    const float2* cs_row = rope_tab + static_cast<std::size_t>(pos) * kHalfRot + (lane & 3) * 8;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float other = __shfl_xor_sync(0xFFFFFFFFU, x[j], 4);
-      if (lane < 8) {
-        const float2 cs = cs_row[j];
-        x[j] = lane < 4 ? __fsub_rn(__fmul_rn(x[j], cs.x), __fmul_rn(other, cs.y))
-                        : __fadd_rn(__fmul_rn(other, cs.y), __fmul_rn(x[j], cs.x));
-      }
-    }
-  }
+  if (!is_v) NormRopeLane8(x, is_q ? q_weight : k_weight, eps, rope_tab, rope_rows, positions[token], lane);
   __half2 hx[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) hx[i] = __floats2half2_rn(x[2 * i], x[2 * i + 1]);

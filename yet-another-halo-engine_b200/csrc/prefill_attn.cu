@@ -272,7 +272,7 @@ static_assert(sizeof(PrefillBars) <= kBarBytes, "the max / sum exchange follows 
 template <bool kQRaw>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPrefillThreads, 1)
     PrefillKernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
-                  const PrefillTile* __restrict__ tiles, const __half* __restrict__ q, const PrefillQRaw qraw,
+                  const PrefillTile* __restrict__ tiles, const __half* __restrict__ q, const QueryRaw qraw,
                   const float* __restrict__ gate, void* out, int out_f32, float scale_log2,
                   float* __restrict__ part_acc, float* __restrict__ part_ml, int* status) {
   extern __shared__ __align__(1024) std::uint8_t smem[];
@@ -778,13 +778,13 @@ cudaError_t LaunchPrefill(const PrefillLaunch& a, cudaStream_t stream) {
   if (a.n_tiles <= 0) return cudaSuccess;
   if ((a.n_tiles & 1) != 0) return cudaErrorInvalidValue;   // tiles come as pairs of query heads, one cluster each
   if (a.q_raw) {
-    const PrefillQRaw qr{static_cast<const float*>(a.q_dev), a.q_weight_dev, a.rope_tab_dev, a.q_eps, a.rope_rows};
+    const QueryRaw qr{static_cast<const float*>(a.q_dev), a.q_weight_dev, a.rope_tab_dev, a.q_eps, a.rope_rows};
     PrefillKernel<true><<<a.n_tiles, kPrefillThreads, kPrefillSmemBytes, stream>>>(
         *a.k16map, *a.v16map, a.tiles_dev, nullptr, qr, a.gate_dev, a.out_dev, a.out_f32, a.scale_log2, a.part_acc,
         a.part_ml, a.status_dev);
   } else {
     PrefillKernel<false><<<a.n_tiles, kPrefillThreads, kPrefillSmemBytes, stream>>>(
-        *a.k16map, *a.v16map, a.tiles_dev, static_cast<const __half*>(a.q_dev), PrefillQRaw{}, a.gate_dev, a.out_dev,
+        *a.k16map, *a.v16map, a.tiles_dev, static_cast<const __half*>(a.q_dev), QueryRaw{}, a.gate_dev, a.out_dev,
         a.out_f32, a.scale_log2, a.part_acc, a.part_ml, a.status_dev);
   }
   if (a.n_merges > 0)

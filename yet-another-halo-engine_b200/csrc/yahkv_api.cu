@@ -715,9 +715,34 @@ int yahkv_append_slots(yahkv_ctx* ctx, int32_t layer, int32_t n_tokens, const in
   return YAHKV_OK;
 }
 
+static int AttendDecode(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids, const void* q_dev, bool q_raw,
+                        const float* q_weight_dev, float eps, const float* gate_dev, void* out_dev, int32_t out_dtype,
+                        int32_t n_splits, void* stream);
+
 int yahkv_attend_decode(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids, const void* q_dev,
                         const float* gate_dev, void* out_dev, int32_t out_dtype, int32_t n_splits, void* stream) {
+  return AttendDecode(ctx, layer, n_seqs, seq_ids, q_dev, false, nullptr, 0.0F, gate_dev, out_dev, out_dtype, n_splits,
+                      stream);
+}
+
+int yahkv_attend_decode_qraw(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids, const float* q_raw_dev,
+                             const float* q_weight_dev, float eps, const float* gate_dev, void* out_dev,
+                             int32_t out_dtype, int32_t n_splits, void* stream) {
+  if (ctx == nullptr) return YAHKV_ERR_INVALID;
+  if (n_seqs > 0 && q_weight_dev == nullptr) return Fail(ctx, YAHKV_ERR_INVALID, "attend_decode_qraw: null norm weights");
+  if (!(eps >= 0.0F)) return Fail(ctx, YAHKV_ERR_INVALID, "attend_decode_qraw: eps must be non-negative");
+  if ((reinterpret_cast<std::uintptr_t>(q_raw_dev) & 15) != 0 || (reinterpret_cast<std::uintptr_t>(q_weight_dev) & 15) != 0)
+    return Fail(ctx, YAHKV_ERR_INVALID, "attend_decode_qraw: q and the norm weights must be 16-byte aligned");
+  return AttendDecode(ctx, layer, n_seqs, seq_ids, q_raw_dev, true, q_weight_dev, eps, gate_dev, out_dev, out_dtype,
+                      n_splits, stream);
+}
+
+static int AttendDecode(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int32_t* seq_ids, const void* q_dev, bool q_raw,
+                        const float* q_weight_dev, float eps, const float* gate_dev, void* out_dev, int32_t out_dtype,
+                        int32_t n_splits, void* stream) {
   if (int r = RequireDevice(ctx, "attend_decode"); r != YAHKV_OK) return r;
+  if (q_raw)
+    if (int r = EnsureRopeTable(ctx); r != YAHKV_OK) return r;   // before the plan: a failure here changes no state
   if (out_dtype != YAHKV_OUT_F16 && out_dtype != YAHKV_OUT_F32) return Fail(ctx, YAHKV_ERR_INVALID, "attend_decode: bad out_dtype");
   if (n_seqs > 0 && (q_dev == nullptr || out_dev == nullptr)) return Fail(ctx, YAHKV_ERR_INVALID, "attend_decode: null q or out pointer");
   bool changed = false;
@@ -767,6 +792,7 @@ int yahkv_attend_decode(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, const int
   a.units_dev = ctx->units_dev, a.n_units = static_cast<int>(units.size());
   a.items_dev = ctx->items_dev, a.n_seqs = n_seqs;
   a.q_dev = q_dev, a.gate_dev = gate_dev, a.out_dev = out_dev, a.out_f32 = out_dtype == YAHKV_OUT_F32;
+  a.q_raw = q_raw, a.q_weight_dev = q_weight_dev, a.q_eps = eps, a.rope_tab_dev = ctx->rope_tab_dev, a.rope_rows = ctx->rope_rows;
   a.scale_log2 = ctx->scale_log2;
   a.partial_acc = ctx->partial_acc, a.partial_ml = ctx->partial_ml, a.status_dev = ctx->status_dev;
   // The merge runs as its own small launch: letting the last-arriving unit merge inside the part kernel was measured
@@ -805,6 +831,8 @@ int yahkv_attend_prefill_qraw(yahkv_ctx* ctx, int32_t layer, int32_t n_seqs, con
   if (ctx == nullptr) return YAHKV_ERR_INVALID;
   if (n_seqs > 0 && q_weight_dev == nullptr) return Fail(ctx, YAHKV_ERR_INVALID, "attend_prefill_qraw: null norm weights");
   if (!(eps >= 0.0F)) return Fail(ctx, YAHKV_ERR_INVALID, "attend_prefill_qraw: eps must be non-negative");
+  if ((reinterpret_cast<std::uintptr_t>(q_weight_dev) & 7) != 0)
+    return Fail(ctx, YAHKV_ERR_INVALID, "attend_prefill_qraw: the norm weights must be 8-byte aligned");
   return AttendPrefill(ctx, layer, n_seqs, seq_ids, chunk_lens, q_raw_dev, true, q_weight_dev, eps, gate_dev, out_dev,
                        out_dtype, stream);
 }

@@ -126,6 +126,14 @@ class KvCache {
     Check(yahkv_attend_prefill(ctx_, layer, static_cast<std::int32_t>(seqs.size()), seqs.data(), chunks.data(), q_dev,
                                gate_dev, out_dev, out_dtype, stream));
   }
+  // AttendDecode on the raw f32 q projection: the part kernel's prologue norms and rotates each head row at the
+  // position of the sequence's newest key; RopeAppend may then get a null q_out_dev.
+  void AttendDecodeRawQ(std::int32_t layer, const std::vector<std::int32_t>& seqs, const float* q_raw_dev,
+                        const float* q_weight_dev, float eps, const float* gate_dev, void* out_dev,
+                        std::int32_t out_dtype = YAHKV_OUT_F16, std::int32_t n_splits = 0, void* stream = nullptr) {
+    Check(yahkv_attend_decode_qraw(ctx_, layer, static_cast<std::int32_t>(seqs.size()), seqs.data(), q_raw_dev,
+                                   q_weight_dev, eps, gate_dev, out_dev, out_dtype, n_splits, stream));
+  }
   // AttendPrefill on the raw f32 q projection: the attention kernel's prologue norms and rotates its rows (the
   // reference's QNORM option, engine/gpu/loom/tools/gen_attn_fa.py:56-61); RopeAppend may then get a null q_out_dev.
   void AttendPrefillRawQ(std::int32_t layer, const std::vector<std::int32_t>& seqs, const std::vector<std::int32_t>& chunks,

@@ -143,6 +143,7 @@ SIGNATURES = {
     "yahkv_rope_append": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _VP, _VP, _VP, ctypes.c_float, _VP, _VP]),
     "yahkv_append_slots": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP]),
     "yahkv_attend_decode": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _I32, _I32, _VP]),
+    "yahkv_attend_decode_qraw": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, ctypes.c_float, _VP, _VP, _I32, _I32, _VP]),
     "yahkv_attend_prefill": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _VP, _I32, _VP]),
     "yahkv_attend_prefill_qraw": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, ctypes.c_float, _VP, _VP, _I32, _VP]),
     "yahkv_decode_step_host": (_I32, [_VP, _I32, _I32, _VP, _VP, _VP, _VP, _VP, _VP, _I32]),
@@ -363,6 +364,13 @@ class KvCache:
         seq_ids = _i32(seq_ids)
         self._check(lib.yahkv_attend_decode(self._h, layer, len(seq_ids), _ptr(seq_ids), _ptr(q), _ptr(gate),
                                             _ptr(out), out_dtype, n_splits, _ptr(stream)))
+
+    def attend_decode_qraw(self, layer, seq_ids, q_raw, q_weight, eps, out, gate=None, out_dtype=OUT_F16, n_splits=0,
+                           stream=None):
+        """attend_decode on the raw f32 q projection: the kernel's prologue norms and rotates each head row."""
+        seq_ids = _i32(seq_ids)
+        self._check(lib.yahkv_attend_decode_qraw(self._h, layer, len(seq_ids), _ptr(seq_ids), _ptr(q_raw), _ptr(q_weight),
+                                                 float(eps), _ptr(gate), _ptr(out), out_dtype, n_splits, _ptr(stream)))
 
     def attend_prefill(self, layer, seq_ids, chunk_lens, q, out, gate=None, out_dtype=OUT_F16, stream=None):
         seq_ids, chunk_lens = _i32(seq_ids), _i32(chunk_lens)
