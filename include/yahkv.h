@@ -268,6 +268,16 @@ int yahkv_batch_prepare(yahkv_batch* batch, int32_t horizon_steps, int32_t* layo
 int yahkv_batch_plan(yahkv_batch* batch, void* stream);
 int yahkv_batch_decode_layer(yahkv_batch* batch, int32_t layer, const void* k_dev, const void* v_dev, const void* q_dev,
                              const float* gate_dev, void* out_dev, int32_t out_dtype, void* stream);
+/* batch_decode_layer on the raw f32 projections (capturable; q_dev [n][24][256], k_dev, v_dev [n][4][256] f32, norm
+ * weights [256] f32, epsilon eps): the reference's whole per-layer attention section in the engine's own terms
+ * (rope, append, part, reduce with the position on the device: engine/model/loom_decoder.hpp:250-268, :131-133).
+ * K is normed, rotated at the sequences' device-resident positions and appended with V as yahkv_rope_append does; the
+ * query side is done in the part kernel's prologue as in yahkv_attend_decode_qraw. The cos / sin table is built by the
+ * first call that needs it, which therefore cannot be inside a capture: run one step eagerly (or any
+ * yahkv_rope_append) first. q_dev and q_weight_dev 16-byte aligned. */
+int yahkv_batch_decode_layer_raw(yahkv_batch* batch, int32_t layer, const float* q_dev, const float* k_dev,
+                                 const float* v_dev, const float* q_weight_dev, const float* k_weight_dev, float eps,
+                                 const float* gate_dev, void* out_dev, int32_t out_dtype, void* stream);
 int yahkv_batch_advance(yahkv_batch* batch, void* stream);
 int yahkv_batch_commit(yahkv_batch* batch, int32_t steps);
 

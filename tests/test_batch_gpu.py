@@ -154,3 +154,82 @@ def test_batch_refuses_what_it_cannot_hold():
     assert e.value.code == yahkv.ERR_CAPACITY
     batch.prepare(5)
     batch.close()
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+def test_raw_projection_steps_eager_and_replayed(fmt):
+    """batch_decode_layer_raw (norm + RoPE + append of K / V at the device-resident positions, the query side in the
+    part kernel's prologue) against yahkv_rope_append + yahkv_attend_decode on a twin cache: one eager step (which
+    also builds the RoPE table), then steps replayed from a captured graph; the pools end up byte for byte equal."""
+    lens = [300, 64 * 24 - 3, 1000, 1, 15]
+    ref, cache, seqs, num_pages, rng = twin_caches(lens, 63, extra_tokens=8, fmt=fmt)
+    n, eps = len(seqs), 1e-6
+    qw = dev((1.0 + 0.2 * rng.standard_normal(256)).astype(np.float32))
+    kw = dev((1.0 + 0.2 * rng.standard_normal(256)).astype(np.float32))
+    batch = yahkv.DecodeBatch(cache, seqs)
+    batch.prepare(6)
+
+    def raw_inputs():
+        return ((rng.standard_normal((LAYERS, n, 24, 256)) * 2).astype(np.float32),
+                rng.standard_normal((LAYERS, n, 4, 256)).astype(np.float32),
+                rng.standard_normal((LAYERS, n, 4, 256)).astype(np.float32),
+                rng.standard_normal((LAYERS, n, 24, 256)).astype(np.float32))
+
+    def ref_step(cur, q, k, v, gate):
+        outs = []
+        for layer in range(LAYERS):
+            q16 = torch.zeros(n, 24, 256, dtype=torch.float16, device="cuda")
+            out = torch.zeros(n, 24, 256, device="cuda")
+            torch.cuda.synchronize()
+            ref.rope_append(layer, seqs, np.array(cur, np.int64), dev(q[layer]), dev(k[layer]), dev(v[layer]), qw, kw, eps, q16)
+            ref.attend_decode(layer, seqs, q16, out, gate=dev(gate[layer]), out_dtype=yahkv.OUT_F32)
+            ref.sync()
+            outs.append(out.cpu().numpy())
+        return outs
+
+    cur = list(lens)
+    q, k, v, gate = raw_inputs()                      # one eager step
+    want = ref_step(cur, q, k, v, gate)
+    batch.plan()
+    for layer in range(LAYERS):
+        out = torch.zeros(n, 24, 256, device="cuda")
+        torch.cuda.synchronize()
+        batch.decode_layer_raw(layer, dev(q[layer]), dev(k[layer]), dev(v[layer]), qw, kw, eps, out, gate=dev(gate[layer]),
+                               out_dtype=yahkv.OUT_F32)
+        cache.sync()
+        assert np.abs(out.cpu().numpy() - want[layer]).max() <= 1e-4, layer
+    batch.advance()
+    cur = [x + 1 for x in cur]
+    side = torch.cuda.Stream()
+    q_s = torch.zeros(LAYERS, n, 24, 256, device="cuda")
+    k_s = torch.zeros(LAYERS, n, 4, 256, device="cuda")
+    v_s = torch.zeros_like(k_s)
+    g_s = torch.zeros(LAYERS, n, 24, 256, device="cuda")
+    o_s = torch.zeros(LAYERS, n, 24, 256, device="cuda")
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        sp = torch.cuda.current_stream().cuda_stream
+        batch.plan(stream=sp)
+        for layer in range(LAYERS):
+            batch.decode_layer_raw(layer, q_s[layer], k_s[layer], v_s[layer], qw, kw, eps, o_s[layer], gate=g_s[layer],
+                                   out_dtype=yahkv.OUT_F32, stream=sp)
+        batch.advance(stream=sp)
+    for step in range(4):
+        q, k, v, gate = raw_inputs()
+        want = ref_step(cur, q, k, v, gate)
+        q_s.copy_(torch.from_numpy(q)); k_s.copy_(torch.from_numpy(k))
+        v_s.copy_(torch.from_numpy(v)); g_s.copy_(torch.from_numpy(gate))
+        graph.replay()
+        torch.cuda.synchronize()
+        got = o_s.cpu().numpy()
+        for layer in range(LAYERS):
+            assert np.abs(got[layer] - want[layer]).max() <= 1e-4, (step, layer)
+        cur = [x + 1 for x in cur]
+    batch.commit(5)
+    cache.sync()
+    assert [cache.seq_len(s, 1) for s in seqs] == cur
+    for layer in range(LAYERS):
+        a, b = pool_pages(ref, layer, num_pages), pool_pages(cache, layer, num_pages)
+        assert all(np.array_equal(x, y) for x, y in zip(a, b))
+    batch.close()

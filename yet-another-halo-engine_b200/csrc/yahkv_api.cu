@@ -1282,6 +1282,60 @@ int yahkv_batch_decode_layer(yahkv_batch* b, int32_t layer, const void* k_dev, c
   return YAHKV_OK;
 }
 
+int yahkv_batch_decode_layer_raw(yahkv_batch* b, int32_t layer, const float* q_dev, const float* k_dev, const float* v_dev,
+                                 const float* q_weight_dev, const float* k_weight_dev, float eps, const float* gate_dev,
+                                 void* out_dev, int32_t out_dtype, void* stream) {
+  if (b == nullptr) return YAHKV_ERR_INVALID;
+  yahkv_ctx* ctx = b->ctx;
+  if (int r = RequireDevice(ctx, "batch_decode_layer_raw"); r != YAHKV_OK) return r;
+  if (layer < 0 || layer >= ctx->cfg.n_layers) return Fail(ctx, YAHKV_ERR_INVALID, "batch_decode_layer_raw: layer out of range");
+  if (out_dtype != YAHKV_OUT_F16 && out_dtype != YAHKV_OUT_F32) return Fail(ctx, YAHKV_ERR_INVALID, "batch_decode_layer_raw: bad out_dtype");
+  if (k_dev == nullptr || v_dev == nullptr || q_dev == nullptr || out_dev == nullptr || q_weight_dev == nullptr ||
+      k_weight_dev == nullptr)
+    return Fail(ctx, YAHKV_ERR_INVALID, "batch_decode_layer_raw: null device pointer");
+  if (!(eps >= 0.0F)) return Fail(ctx, YAHKV_ERR_INVALID, "batch_decode_layer_raw: eps must be non-negative");
+  if ((reinterpret_cast<std::uintptr_t>(q_dev) & 15) != 0 || (reinterpret_cast<std::uintptr_t>(q_weight_dev) & 15) != 0)
+    return Fail(ctx, YAHKV_ERR_INVALID, "batch_decode_layer_raw: q and the norm weights must be 16-byte aligned");
+  if (b->total_units == 0) return Fail(ctx, YAHKV_ERR_ORDER, "batch_decode_layer_raw: call batch_prepare first");
+  cudaStream_t st = StreamOf(ctx, stream);
+  if (ctx->rope_tab_dev == nullptr) {   // the cos / sin table is built once, with an allocation and a blocking copy
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    YAHKV_CUDA(ctx, cudaStreamIsCapturing(st, &cs));
+    if (cs != cudaStreamCaptureStatusNone)
+      return Fail(ctx, YAHKV_ERR_ORDER, "batch_decode_layer_raw: the RoPE table does not exist yet; run one step eagerly (or yahkv_rope_append) before capturing");
+    if (int r = EnsureRopeTable(ctx); r != YAHKV_OK) return r;
+  }
+  const int n = static_cast<int>(b->seqs.size());
+  const bool tile_fmt = IsTileFmt(ctx->cfg.fmt);
+  // K and V: norm + RoPE + append at the planned slots, positions = the device-resident lengths; no q output (the part
+  // kernel's prologue does the query side)
+  YAHKV_CUDA(ctx, LaunchRopeAppend(ctx->pool, layer, n, b->slots_dev, b->lens_dev, q_dev, k_dev, v_dev, q_weight_dev,
+                                   k_weight_dev, eps, ctx->rope_tab_dev, ctx->rope_rows, nullptr, ctx->rope_kv16_dev, st));
+  if (tile_fmt) {   // the kernel left fp16 rows: the format's own appends take them
+    const std::uint16_t* k16 = ctx->rope_kv16_dev;
+    const std::uint16_t* v16 = k16 + static_cast<std::size_t>(n) * kKvHeads * kHeadDim;
+    YAHKV_CUDA(ctx, (ctx->cfg.fmt == YAHKV_FMT_KV4A16 ? LaunchKv4AppendK : LaunchKv8AppendK)(
+                        ctx->pool, layer, n, b->slots_dev, b->state_rows_dev, layer, ctx->kmean_dev, k16, st));
+    YAHKV_CUDA(ctx, LaunchKv8AppendV(ctx->pool, layer, n, b->vwork_dev, layer, ctx->open_tiles_dev, v16, st));
+  }
+  DecodeLaunch a{};
+  a.kmap = &ctx->kmap, a.vmap = &ctx->vmap, a.pool = ctx->pool, a.layer = layer;
+  a.tables_dev = ctx->tables_dev, a.table_stride = ctx->cfg.max_pages_per_seq;
+  a.units_dev = b->units_dev, a.n_units = b->total_units;
+  a.items_dev = b->items_dev, a.n_seqs = n;
+  a.q_dev = q_dev, a.gate_dev = gate_dev, a.out_dev = out_dev, a.out_f32 = out_dtype == YAHKV_OUT_F32;
+  a.q_raw = true, a.q_weight_dev = q_weight_dev, a.q_eps = eps, a.rope_tab_dev = ctx->rope_tab_dev, a.rope_rows = ctx->rope_rows;
+  a.scale_log2 = ctx->scale_log2;
+  a.partial_acc = ctx->partial_acc, a.partial_ml = ctx->partial_ml, a.status_dev = ctx->status_dev;
+  YAHKV_CUDA(ctx, ctx->cfg.fmt == YAHKV_FMT_KV4A16   ? LaunchKv4DecodePart(a, ctx->open_tiles_dev, ctx->cfg.n_layers, st)
+                  : ctx->cfg.fmt == YAHKV_FMT_KV8A16 ? LaunchKv8DecodePart(a, ctx->open_tiles_dev, ctx->cfg.n_layers, st)
+                  : ctx->cfg.fmt == YAHKV_FMT_F16    ? LaunchF16DecodePart(a, st)
+                                                     : LaunchDecodePart(a, st));
+  YAHKV_CUDA(ctx, LaunchDecodeCombine(a, st));
+  ctx->launches += tile_fmt ? 5 : 3;
+  return YAHKV_OK;
+}
+
 int yahkv_batch_advance(yahkv_batch* b, void* stream) {
   if (b == nullptr) return YAHKV_ERR_INVALID;
   yahkv_ctx* ctx = b->ctx;

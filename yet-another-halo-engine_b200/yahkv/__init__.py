@@ -158,6 +158,7 @@ SIGNATURES = {
     "yahkv_batch_prepare": (_I32, [_VP, _I32, _PI32, _VP]),
     "yahkv_batch_plan": (_I32, [_VP, _VP]),
     "yahkv_batch_decode_layer": (_I32, [_VP, _I32, _VP, _VP, _VP, _VP, _VP, _I32, _VP]),
+    "yahkv_batch_decode_layer_raw": (_I32, [_VP, _I32, _VP, _VP, _VP, _VP, _VP, ctypes.c_float, _VP, _VP, _I32, _VP]),
     "yahkv_batch_advance": (_I32, [_VP, _VP]),
     "yahkv_batch_commit": (_I32, [_VP, _I32]),
     "yahkv_snapshot_save": (_I32, [_VP, _I32, _VP, _c.c_char_p]),
@@ -268,6 +269,12 @@ class DecodeBatch:
     def decode_layer(self, layer, k, v, q, out, gate=None, out_dtype=OUT_F16, stream=None):
         self.cache._check(lib.yahkv_batch_decode_layer(self._h, layer, _ptr(k), _ptr(v), _ptr(q), _ptr(gate), _ptr(out),
                                                        out_dtype, _ptr(stream)))
+
+    def decode_layer_raw(self, layer, q, k, v, q_weight, k_weight, eps, out, gate=None, out_dtype=OUT_F16, stream=None):
+        """decode_layer on the raw f32 projections: norm + RoPE + append of K / V, the query side in the part kernel."""
+        self.cache._check(lib.yahkv_batch_decode_layer_raw(self._h, layer, _ptr(q), _ptr(k), _ptr(v), _ptr(q_weight),
+                                                           _ptr(k_weight), float(eps), _ptr(gate), _ptr(out), out_dtype,
+                                                           _ptr(stream)))
 
     def advance(self, stream=None):
         self.cache._check(lib.yahkv_batch_advance(self._h, _ptr(stream)))
