@@ -1,10 +1,11 @@
 // The C++ adapter (engine/model/kv_cache.hpp) driving the GPU path the way the engine's drivers would: one sequence,
-// a prompt appended as one chunk and attended with AttendPrefill, then decode steps (Append + AttendDecode), all with
+// a prompt appended as one chunk and attended with AttendPrefill, then decode steps (Append + AttendDecode, then a
+// DecodeBatch), a snapshot saved and loaded back, all with
 // device buffers this program owns. Inputs come from raw files written by tests/test_cpp_adapter_gpu.py, outputs go
 // back to raw files that the test compares with the CPU oracle.
 //   usage: kv_cache_gpu_test <dir> <n_prompt> <n_decode> <fmt>
 //   reads  <dir>/k.f16 v.f16 [n][4][256], q.f16 [n][24][256], table.i32   (n = n_prompt + n_decode)
-//   writes <dir>/prefill.f32 [n_prompt][24][256], decode.f32 [n_decode][24][256]
+//   writes <dir>/prefill.f32 [n_prompt][24][256], decode.f32 [n_decode][24][256], loaded.f32 [24][256]
 #include <cuda_runtime.h>
 
 #include <cstdio>
@@ -55,6 +56,8 @@ int main(int argc, char** argv) {
   CUDA_OK(cudaMalloc(&vd, v.size()));
   CUDA_OK(cudaMalloc(&qd, q.size()));
   CUDA_OK(cudaMalloc(&od, static_cast<std::size_t>(n) * o_row));
+  void* ld = nullptr;   // output of the sequence loaded back from a snapshot
+  CUDA_OK(cudaMalloc(&ld, o_row));
   CUDA_OK(cudaMemcpy(kd, k.data(), k.size(), cudaMemcpyHostToDevice));
   CUDA_OK(cudaMemcpy(vd, v.data(), v.size(), cudaMemcpyHostToDevice));
   CUDA_OK(cudaMemcpy(qd, q.data(), q.size(), cudaMemcpyHostToDevice));
@@ -71,14 +74,34 @@ int main(int argc, char** argv) {
     kv.Append(0, ids, pos, kd, vd);
     kv.AttendPrefill(0, {seq}, {n_prompt}, qd, nullptr, od, YAHKV_OUT_F32);
     // decode steps: append position p, attend over 0 .. p (LoomDecoder::Step's attention section)
-    for (int s = 0; s < n_decode; ++s) {
+    const int n_eager = n_decode / 2;
+    for (int s = 0; s < n_eager; ++s) {
       const int p = n_prompt + s;
       kv.Append(0, {seq}, {p}, static_cast<const char*>(kd) + p * kv_row, static_cast<const char*>(vd) + p * kv_row);
       kv.AttendDecode(0, {seq}, static_cast<const char*>(qd) + p * q_row, nullptr, static_cast<char*>(od) + p * o_row,
                       YAHKV_OUT_F32);
     }
+    // the remaining steps as a device-resident batch: the position lives on the device, the host only queues launches
+    {
+      KvCache::DecodeBatch batch(kv, {seq});
+      batch.Prepare(n_decode - n_eager);
+      for (int s = n_eager; s < n_decode; ++s) {
+        const int p = n_prompt + s;
+        batch.Plan();
+        batch.DecodeLayer(0, static_cast<const char*>(kd) + p * kv_row, static_cast<const char*>(vd) + p * kv_row,
+                          static_cast<const char*>(qd) + p * q_row, nullptr, static_cast<char*>(od) + p * o_row, YAHKV_OUT_F32);
+        batch.Advance();
+      }
+      batch.Commit(n_decode - n_eager);
+    }
     kv.Synchronize();
     if (kv.Length(seq, 0) != n) return 4;
+    // snapshot round trip: the sequence comes back on other pages under another id and attends to the same result
+    kv.SaveState({seq}, dir + "/state.yahkv");
+    const std::vector<std::int32_t> loaded = kv.LoadState(dir + "/state.yahkv", 1);
+    if (loaded.size() != 1 || loaded[0] == seq || kv.Length(loaded[0], 0) != n) return 7;
+    kv.AttendDecode(0, loaded, static_cast<const char*>(qd) + (n - 1) * q_row, nullptr, ld, YAHKV_OUT_F32);
+    kv.Synchronize();
     // an order error is thrown before anything is launched and leaves the cache as it was
     bool thrown = false;
     try {
@@ -96,6 +119,9 @@ int main(int argc, char** argv) {
   WriteFile(dir + "/prefill.f32", out.data(), static_cast<std::size_t>(n_prompt) * o_row);
   WriteFile(dir + "/decode.f32", out.data() + static_cast<std::size_t>(n_prompt) * o_row,
             static_cast<std::size_t>(n_decode) * o_row);
+  std::vector<char> lout(o_row);
+  CUDA_OK(cudaMemcpy(lout.data(), ld, lout.size(), cudaMemcpyDeviceToHost));
+  WriteFile(dir + "/loaded.f32", lout.data(), lout.size());
   std::puts("kv_cache_gpu_test: ok");
   return 0;
 }

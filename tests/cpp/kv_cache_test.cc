@@ -56,6 +56,19 @@ int main() {
   EXPECT(CodeOf([&] { kv.DecodeStepHostAsync(0, seqs, dummy, dummy, dummy, nullptr, dummy); }) == YAHKV_ERR_NO_DEVICE);
   EXPECT(CodeOf([&] { kv.WaitHostSteps(); }) == YAHKV_ERR_NO_DEVICE);
   EXPECT(CodeOf([&] { kv.AttendPrefill(0, seqs, {1}, dummy, nullptr, dummy); }) == YAHKV_ERR_NO_DEVICE);
+  alignas(16) float fal[4] = {};
+  EXPECT(CodeOf([&] { kv.AttendDecodeRawQ(0, seqs, fal, fal, 1e-6F, nullptr, dummy); }) == YAHKV_ERR_NO_DEVICE);
+  EXPECT(CodeOf([&] { kv.AttendPrefillRawQ(0, seqs, {1}, fal, fal, 1e-6F, nullptr, dummy); }) == YAHKV_ERR_NO_DEVICE);
+  EXPECT(CodeOf([&] { kv.SaveState(seqs, "/nonexistent-dir/x.yahkv"); }) != YAHKV_OK);
+  EXPECT(CodeOf([&] { (void)kv.LoadState("/nonexistent-dir/x.yahkv", 1); }) != YAHKV_OK);
+  EXPECT(CodeOf([&] {   // a batch needs the device too
+           KvCache::DecodeBatch batch(kv, seqs);
+           batch.Prepare(1);
+           batch.Plan();
+           batch.DecodeLayerRaw(0, fal, fal, fal, fal, fal, 1e-6F, nullptr, dummy);
+           batch.Advance();
+           batch.Commit(1);
+         }) != YAHKV_OK);
   EXPECT(kv.Length(b, 0) == 0);
   // a bad geometry is refused at creation
   yahkv_config bad = KvCache::Config(-1, 1, 4, 1, 1);

@@ -1,6 +1,6 @@
 """The C++ adapter (engine/model/kv_cache.hpp) on the GPU: a compiled program appends a prompt, runs chunked-prefill
-attention and decode steps through the adapter with its own device buffers, and this test compares what it wrote
-with the float64 oracle."""
+attention, decode steps (eager and as a device-resident batch) and a snapshot round trip through the adapter with its
+own device buffers, and this test compares what it wrote with the float64 oracle."""
 import os
 import subprocess
 
@@ -46,3 +46,6 @@ def test_cpp_adapter_prefill_and_decode_against_the_oracle(tmp_path, fmt):
     for s in range(n_decode):
         p = n_prompt + s
         assert np.abs(dec[s] - pool.attend_decode_f64(table, p + 1, q[p])).max() <= 2e-3, s
+    loaded = np.fromfile(tmp_path / "loaded.f32", np.float32).reshape(24, 256)
+    assert np.abs(loaded - pool.attend_decode_f64(table, n, q[n - 1])).max() <= 2e-3
+    assert np.abs(loaded - dec[-1]).max() <= 1e-5   # the same bytes on other pages (the split may differ)

@@ -153,6 +153,57 @@ class KvCache {
   void WaitHostSteps() { Check(yahkv_decode_step_host_wait(ctx_)); }
   void Synchronize() { Check(yahkv_sync(ctx_)); }
 
+  // ---- snapshots (LoomPrefill::SaveState / LoadState, engine/model/loom_prefill.hpp:973-1024) ----
+  void SaveState(const std::vector<std::int32_t>& seqs, const std::string& path) {
+    Check(yahkv_snapshot_save(ctx_, static_cast<std::int32_t>(seqs.size()), seqs.data(), path.c_str()));
+  }
+  // The sequences of the file, on fresh pages and under fresh ids (at most `max_seqs` of them).
+  [[nodiscard]] std::vector<std::int32_t> LoadState(const std::string& path, std::int32_t max_seqs) {
+    std::vector<std::int32_t> ids(static_cast<std::size_t>(max_seqs > 0 ? max_seqs : 0));
+    std::int32_t n = max_seqs;
+    Check(yahkv_snapshot_load(ctx_, path.c_str(), ids.data(), &n));
+    ids.resize(static_cast<std::size_t>(n));
+    return ids;
+  }
+
+  // ---- decode steps with no host work in between (engine/model/loom_decoder.hpp:131-133: the position lives on the
+  // device). Prepare is host work; Plan / DecodeLayer / DecodeLayerRaw / Advance are plain launches and may be
+  // captured into a CUDA graph; Commit tells the cache how many steps were queued. ----
+  class DecodeBatch {
+   public:
+    DecodeBatch(KvCache& cache, const std::vector<std::int32_t>& seqs) : cache_(&cache) {
+      cache.Check(yahkv_batch_create(cache.ctx_, static_cast<std::int32_t>(seqs.size()), seqs.data(), &b_));
+    }
+    DecodeBatch(const DecodeBatch&) = delete;
+    DecodeBatch& operator=(const DecodeBatch&) = delete;
+    ~DecodeBatch() { yahkv_batch_destroy(b_); }
+    // Reserves pages for `horizon_steps` more positions; true when the unit layout changed (capture again).
+    bool Prepare(std::int32_t horizon_steps, void* stream = nullptr) {
+      std::int32_t changed = 0;
+      cache_->Check(yahkv_batch_prepare(b_, horizon_steps, &changed, stream));
+      return changed != 0;
+    }
+    void Plan(void* stream = nullptr) { cache_->Check(yahkv_batch_plan(b_, stream)); }
+    void DecodeLayer(std::int32_t layer, const void* k_dev, const void* v_dev, const void* q_dev, const float* gate_dev,
+                     void* out_dev, std::int32_t out_dtype = YAHKV_OUT_F16, void* stream = nullptr) {
+      cache_->Check(yahkv_batch_decode_layer(b_, layer, k_dev, v_dev, q_dev, gate_dev, out_dev, out_dtype, stream));
+    }
+    // The layer on the raw f32 projections: the reference's rope, append, part, reduce sequence
+    // (engine/model/loom_decoder.hpp:250-268).
+    void DecodeLayerRaw(std::int32_t layer, const float* q_dev, const float* k_dev, const float* v_dev,
+                        const float* q_weight_dev, const float* k_weight_dev, float eps, const float* gate_dev,
+                        void* out_dev, std::int32_t out_dtype = YAHKV_OUT_F16, void* stream = nullptr) {
+      cache_->Check(yahkv_batch_decode_layer_raw(b_, layer, q_dev, k_dev, v_dev, q_weight_dev, k_weight_dev, eps, gate_dev,
+                                                 out_dev, out_dtype, stream));
+    }
+    void Advance(void* stream = nullptr) { cache_->Check(yahkv_batch_advance(b_, stream)); }
+    void Commit(std::int32_t steps) { cache_->Check(yahkv_batch_commit(b_, steps)); }
+
+   private:
+    KvCache* cache_;
+    yahkv_batch* b_ = nullptr;
+  };
+
  private:
   explicit KvCache(yahkv_ctx* ctx) : ctx_(ctx) {}
   void Check(int rc) const {
