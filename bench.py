@@ -49,6 +49,11 @@ METRIC, UNIT = "q8_0_paged_decode_attn_kv_gbps", "GB/s"
 # q4_0: the long-context launch (1.2094 GB + 22.8 MB for 1.2080 GB), profiles/decode_longctx_q4_0.md; kv8a16: the
 # batch-32 launch (1.3311 GB + 14.8 MB for 1.3271 GB), profiles/decode_part_kv8a16_batch32.md.
 NCU_DRAM_PER_ALGORITHMIC_BYTE = {"q8_0": 1.0114, "q4_0": 1.0200, "kv8a16": 1.0142}
+# kv4a16: the batch-32 launch (803.0 MB + 14.9 MB for 0.800 GB), profiles/decode_part_kv4a16_batch32.md.
+NCU_DRAM_PER_ALGORITHMIC_BYTE["kv4a16"] = 1.0224
+# The prefill kernel's DRAM bytes per launch of the chunked-prefill workload (5.920 GB read + 0.101 GB written: the fp16
+# scratch is streamed once per wave of query tiles), profiles/prefill_q8_0_chunk2048.md.
+NCU_DRAM_BYTES_PREFILL_LAUNCH = 6.021e9
 
 
 def workload(rank, world, layers):
@@ -437,7 +442,10 @@ def prefill_arm(args, local_rank):
                      "peak": peak_at_clock, "unit": "TFLOP/s", "frac": achieved / peak_at_clock,
                      "peak_kind": f"of {peak_kind}: burst bf16 peak x (median SM MHz in the run / max SM MHz)",
                      "frac_of_burst": achieved / peaks["bf16_tflops"],
-                     "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"], "traffic": None},
+                     "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
+                     "traffic": NCU_DRAM_BYTES_PREFILL_LAUNCH,
+                     "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu-captured launch of this "
+                                     "workload; the kernel is tensor-bound, its algorithmic unit is the flop"},
         "e2e": {"value": flops * args.steps / e_s / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": n_seq * chunk * (2 * 4 * 256 + 24 * 256) * 2,
                 "d2h_bytes_per_step": n_seq * chunk * 24 * 256 * 2, "steps": args.steps,
