@@ -849,7 +849,7 @@ def main():
     rng, lens, layers = w["rng"], w["lens"].copy(), w["layers"]
     total_steps = args.warmup + args.steps
     e2e_steps = 0 if args.no_e2e else args.steps + 1
-    graph_steps = 0 if (args.no_graph or N_SPLITS) else args.steps + 3
+    graph_steps = 0 if args.no_graph else args.steps + 3
     grow = total_steps + graph_steps + e2e_steps + 2
     pages = [(int(n) + grow + 63) // 64 for n in lens]
     num_pages = sum(pages) + 64
@@ -947,6 +947,8 @@ def main():
     g_ms = g_bytes = None
     if graph_steps:
         batch = yahkv.DecodeBatch(cache, seq_ids)
+        if N_SPLITS:
+            batch.set_splits(N_SPLITS)     # the configuration's split count, as the eager calls pass it
         batch.prepare(graph_steps, stream=sptr)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
@@ -1043,7 +1045,7 @@ def main():
                        "layers": layers, "mean_ctx": float(lens.mean()), "pages_shuffled": True,
                        "l2": "inputs larger than L2: each layer reads its own ~1.2 GB of cache per step",
                        "sharding": "sequences partitioned across GPUs, no collective on the data path"},
-            "extra": {"step_mode": "one captured CUDA graph per 16-layer step (yahkv_batch_*)" if use_graph
+            "extra": {"step_mode": f"one captured CUDA graph per {layers}-layer step (yahkv_batch_*)" if use_graph
                       else "eager per-layer calls (yahkv_append + yahkv_attend_decode)",
                       "eager_value": eager_value, "eager_ms_per_step": eager_ms_per_step,
                       "append_mtok_s": (app_n * BATCH) / (app_ms * 1e-3) / 1e6 if app_n else None,

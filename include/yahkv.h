@@ -253,8 +253,8 @@ int yahkv_sync(yahkv_ctx* ctx);
  * once and replayed.
  *   batch_create        the sequences must have equal lengths in all layers; allocates the batch's device arrays.
  *   batch_prepare       NOT capturable. Reserves pages for the next horizon_steps positions, uploads block tables and
- *                       lengths, and fixes the number of split-K units per sequence for that horizon.
- *                       *layout_changed = 1 when that number changed, i.e. a captured graph must be captured again.
+ *                       lengths, and fixes the pages per split-K unit and the units per sequence for that horizon.
+ *                       *layout_changed = 1 when either changed, i.e. a captured graph must be captured again.
  *   batch_plan          capturable; once per step: slots of the new tokens and the step's units from the lengths.
  *   batch_decode_layer  capturable; per layer: append k/v [n][4][256] fp16 at the planned slots, then attend with
  *                       q [n][24][256] over lengths + 1 keys (rows in batch_create's order).
@@ -264,6 +264,9 @@ int yahkv_sync(yahkv_ctx* ctx);
 typedef struct yahkv_batch yahkv_batch;
 int yahkv_batch_create(yahkv_ctx* ctx, int32_t n_seqs, const int32_t* seq_ids, yahkv_batch** out);
 void yahkv_batch_destroy(yahkv_batch* batch);
+/* Split-K units per (sequence, kv head) for the batch's longest sequence, as n_splits of yahkv_attend_decode (0 =
+ * automatic, the default); shorter sequences get units of the same page count. Takes effect at the next batch_prepare. */
+int yahkv_batch_set_splits(yahkv_batch* batch, int32_t n_splits);
 int yahkv_batch_prepare(yahkv_batch* batch, int32_t horizon_steps, int32_t* layout_changed, void* stream);
 int yahkv_batch_plan(yahkv_batch* batch, void* stream);
 int yahkv_batch_decode_layer(yahkv_batch* batch, int32_t layer, const void* k_dev, const void* v_dev, const void* q_dev,

@@ -14,11 +14,12 @@ LAYERS = 2
 FORMATS = [yahkv.FMT_Q8_0, yahkv.FMT_KV8A16, yahkv.FMT_KV4A16, yahkv.FMT_F16]
 
 
-def twin_caches(lens, seed, extra_tokens, fmt=yahkv.FMT_Q8_0):
+def twin_caches(lens, seed, extra_tokens, fmt=yahkv.FMT_Q8_0, **config):
     rng = np.random.default_rng(seed)
     pages = [(n + extra_tokens + 63) // 64 for n in lens]
     num_pages = sum(pages) + 2
-    caches = [yahkv.KvCache(n_layers=LAYERS, num_pages=num_pages, max_seqs=len(lens), max_pages_per_seq=max(pages), fmt=fmt)
+    caches = [yahkv.KvCache(n_layers=LAYERS, num_pages=num_pages, max_seqs=len(lens), max_pages_per_seq=max(pages), fmt=fmt,
+                            **config)
               for _ in range(2)]
     perm = rng.permutation(num_pages).astype(np.int32)
     seqs, off = [], 0
@@ -232,4 +233,40 @@ def test_raw_projection_steps_eager_and_replayed(fmt):
     for layer in range(LAYERS):
         a, b = pool_pages(ref, layer, num_pages), pool_pages(cache, layer, num_pages)
         assert all(np.array_equal(x, y) for x, y in zip(a, b))
+    batch.close()
+
+
+@pytest.mark.parametrize("n_splits", [0, 3])
+def test_long_sequences_get_longer_units_not_a_long_tail(n_splits):
+    """A sequence that needs more than max_splits units of the automatic size gets longer units (the same page count
+    for every sequence of the batch) instead of one last unit that takes all the rest; yahkv_batch_set_splits asks for
+    a unit count outright. Outputs against the host-planned calls; a change of the unit size reports a changed layout."""
+    lens = [64 * 130 + 5, 500, 64 * 40]
+    ref, cache, seqs, num_pages, rng = twin_caches(lens, 64, extra_tokens=8, fmt=yahkv.FMT_Q8_0, max_splits=4,
+                                                   max_batch_tokens=16384)
+    batch = yahkv.DecodeBatch(cache, seqs)
+    if n_splits:
+        batch.set_splits(n_splits)
+    assert batch.prepare(4) is True
+    assert batch.prepare(4) is False
+    cur = list(lens)
+    for step in range(3):
+        k, v, q, gate = step_inputs(rng, len(seqs))
+        want = host_step(ref, seqs, cur, k, v, q, gate)
+        batch.plan()
+        for layer in range(LAYERS):
+            out = torch.zeros(len(seqs), 24, 256, device="cuda")
+            torch.cuda.synchronize()
+            batch.decode_layer(layer, dev(k[layer]), dev(v[layer]), dev(q[layer]), out, gate=dev(gate[layer]),
+                               out_dtype=yahkv.OUT_F32)
+            cache.sync()
+            assert np.abs(out.cpu().numpy() - want[layer]).max() <= 1e-4, (step, layer)
+        batch.advance()
+        batch.commit(1)
+        cur = [n + 1 for n in cur]
+    batch.set_splits(2 if n_splits else 1)       # other units: a captured graph would have to be captured again
+    assert batch.prepare(2) is True
+    with pytest.raises(yahkv.YahkvError) as e:
+        batch.set_splits(5)                      # above max_splits
+    assert e.value.code == yahkv.ERR_CAPACITY
     batch.close()

@@ -1105,6 +1105,8 @@ struct yahkv_batch {
   VTileWork* vwork_dev = nullptr;          // tile formats: the step's V tile work item per row
   std::int32_t* state_rows_dev = nullptr;  // tile formats: layer-0 state row per row
   int units_cap = 0;
+  int n_splits = 0;      // units per (sequence, kv head) asked for with yahkv_batch_set_splits; 0 = automatic
+  int unit_pages = 0;    // pages per unit of the prepared horizon (a parameter of the plan kernel)
 };
 namespace {
 constexpr int kBatchUnitPages = 24;   // the automatic planner's unit size on large batches (kv_host.hpp)
@@ -1164,6 +1166,15 @@ void yahkv_batch_destroy(yahkv_batch* b) {
   BatchFree(b);
 }
 
+int yahkv_batch_set_splits(yahkv_batch* b, int32_t n_splits) {
+  if (b == nullptr) return YAHKV_ERR_INVALID;
+  yahkv_ctx* ctx = b->ctx;
+  if (n_splits < 0) return Fail(ctx, YAHKV_ERR_INVALID, "batch_set_splits: negative n_splits");
+  if (n_splits > ctx->cfg.max_splits) return Fail(ctx, YAHKV_ERR_CAPACITY, "batch_set_splits: n_splits above max_splits");
+  b->n_splits = n_splits;   // takes effect at the next batch_prepare
+  return YAHKV_OK;
+}
+
 int yahkv_batch_prepare(yahkv_batch* b, int32_t horizon_steps, int32_t* layout_changed, void* stream) {
   if (b == nullptr) return YAHKV_ERR_INVALID;
   yahkv_ctx* ctx = b->ctx;
@@ -1193,6 +1204,17 @@ int yahkv_batch_prepare(yahkv_batch* b, int32_t horizon_steps, int32_t* layout_c
     HostError e = ctx->host.SeqReserve(b->seqs[i], static_cast<std::int64_t>(b->lens[i]) + horizon_steps);
     if (e.code != YAHKV_OK) return FailHost(ctx, std::move(e));
   }
+  // Pages per unit, the same for every sequence of the batch (the plan kernel cuts every sequence at multiples of it):
+  // the automatic size, or what the asked-for split count gives on the longest sequence; never so small that a
+  // sequence would need more than max_splits units (its last unit would otherwise take all the rest). Even, because
+  // the part kernels' two page sets take alternate pages.
+  int unit_pages = b->n_splits > 0 ? 1 : kBatchUnitPages;
+  for (int i = 0; i < n; ++i) {
+    const int pages = (b->lens[i] + horizon_steps + kPageTokens - 1) / kPageTokens;
+    const int cap = b->n_splits > 0 ? b->n_splits : ctx->cfg.max_splits;
+    unit_pages = std::max(unit_pages, (pages + cap - 1) / cap);
+  }
+  if (unit_pages > 1) unit_pages += unit_pages & 1;
   // units reserved per sequence, the longest sequences first (CTAs are handed out in index order)
   std::vector<int> order(static_cast<std::size_t>(n));
   for (int i = 0; i < n; ++i) order[static_cast<std::size_t>(i)] = i;
@@ -1204,13 +1226,13 @@ int yahkv_batch_prepare(yahkv_batch* b, int32_t horizon_steps, int32_t* layout_c
     BatchSeq r{};
     r.seq_row = b->seqs[i];
     r.open_cur = IsTileFmt(ctx->cfg.fmt) ? ctx->host.open_cur(b->seqs[i], 0) : 0;
-    r.n_units = std::min(std::max((pages + kBatchUnitPages - 1) / kBatchUnitPages, 1), ctx->cfg.max_splits);
+    r.n_units = std::min(std::max((pages + unit_pages - 1) / unit_pages, 1), ctx->cfg.max_splits);
     r.first_unit = total;
     total += r.n_units * kKvHeads;
     rows[static_cast<std::size_t>(i)] = r;
   }
   if (total > b->units_cap) return Fail(ctx, YAHKV_ERR_CAPACITY, "batch_prepare: more split-K units than the workspace holds");
-  bool changed = rows.size() != b->rows.size() || total != b->total_units;
+  bool changed = rows.size() != b->rows.size() || total != b->total_units || unit_pages != b->unit_pages;
   for (std::size_t i = 0; !changed && i < rows.size(); ++i)
     changed = rows[i].n_units != b->rows[i].n_units || rows[i].first_unit != b->rows[i].first_unit;
   if (layout_changed != nullptr) *layout_changed = changed ? 1 : 0;
@@ -1228,6 +1250,7 @@ int yahkv_batch_prepare(yahkv_batch* b, int32_t horizon_steps, int32_t* layout_c
   }
   b->rows = std::move(rows);
   b->total_units = total;
+  b->unit_pages = unit_pages;
   b->horizon = horizon_steps;
   return YAHKV_OK;
 }
@@ -1238,7 +1261,7 @@ int yahkv_batch_plan(yahkv_batch* b, void* stream) {
   if (int r = RequireDevice(ctx, "batch_plan"); r != YAHKV_OK) return r;
   if (b->total_units == 0) return Fail(ctx, YAHKV_ERR_ORDER, "batch_plan: call batch_prepare first");
   YAHKV_CUDA(ctx, LaunchBatchPlan(b->lens_dev, b->rows_dev, static_cast<int>(b->seqs.size()), ctx->tables_dev,
-                                  ctx->cfg.max_pages_per_seq, kBatchUnitPages, ctx->cfg.num_pages, b->units_dev,
+                                  ctx->cfg.max_pages_per_seq, b->unit_pages, ctx->cfg.num_pages, b->units_dev,
                                   b->items_dev, b->slots_dev, b->vwork_dev, b->state_rows_dev, ctx->cfg.n_layers,
                                   StreamOf(ctx, stream)));
   ctx->launches += 1;

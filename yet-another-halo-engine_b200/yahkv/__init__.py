@@ -156,6 +156,7 @@ SIGNATURES = {
     "yahkv_batch_create": (_I32, [_VP, _I32, _VP, _c.POINTER(_VP)]),
     "yahkv_batch_destroy": (None, [_VP]),
     "yahkv_batch_prepare": (_I32, [_VP, _I32, _PI32, _VP]),
+    "yahkv_batch_set_splits": (_I32, [_VP, _I32]),
     "yahkv_batch_plan": (_I32, [_VP, _VP]),
     "yahkv_batch_decode_layer": (_I32, [_VP, _I32, _VP, _VP, _VP, _VP, _VP, _I32, _VP]),
     "yahkv_batch_decode_layer_raw": (_I32, [_VP, _I32, _VP, _VP, _VP, _VP, _VP, ctypes.c_float, _VP, _VP, _I32, _VP]),
@@ -265,6 +266,10 @@ class DecodeBatch:
 
     def plan(self, stream=None):
         self.cache._check(lib.yahkv_batch_plan(self._h, _ptr(stream)))
+
+    def set_splits(self, n_splits):
+        """Split-K units per (sequence, kv head) of the longest sequence from the next prepare() on; 0 = automatic."""
+        self.cache._check(lib.yahkv_batch_set_splits(self._h, int(n_splits)))
 
     def decode_layer(self, layer, k, v, q, out, gate=None, out_dtype=OUT_F16, stream=None):
         self.cache._check(lib.yahkv_batch_decode_layer(self._h, layer, _ptr(k), _ptr(v), _ptr(q), _ptr(gate), _ptr(out),
