@@ -132,6 +132,7 @@ constexpr int kKBlockBytes = (kTileN / 2) * 128;   // one [32 keys][64 dims] box
 constexpr int kVBlockBytes = kTileN * 128;         // one [64 keys][64 dims] box
 constexpr int kPBytes = kTileM * kTileN * 2;       // P of one tile: [128 rows][64 fp16], K-major, 128-byte swizzle
 constexpr int kKvStages = YAHKV_PREFILL_STAGES;
+static_assert(kKvStages >= 3, "S(j + 2) is issued before P(j) V(j): the loads of tile j + 2 must not wait for the stage of tile j");
 constexpr int kSmemK = 0;
 constexpr int kSmemV = kSmemK + kKvStages * kKHalfBytes;
 constexpr int kSmemP = kSmemV + kKvStages * kVHalfBytes;
